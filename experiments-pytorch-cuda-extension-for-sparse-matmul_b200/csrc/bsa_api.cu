@@ -1,0 +1,147 @@
+// C-ABI entry points that are not tied to one kernel file: version and status
+// text, the matmul dispatcher with its argument validation, the dense <->
+// block-sparse converters and the workspace status word.
+#include <cstdlib>
+#include <cstring>
+
+#include "bsa_common.cuh"
+
+namespace bsa {
+namespace {
+
+// to_sparse / to_dense (reference sparse/layout.py:40-57 are Python loops over
+// the nonzero blocks).  One CTA per (block, batch); 16-byte chunks.
+template <bool kToSparse>
+__global__ void __launch_bounds__(256)
+convert_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, const BlockDesc* __restrict__ row_blocks,
+               int64_t nnz, int64_t rows, int64_t cols, int block, int chunks_per_row) {
+    const BlockDesc d = row_blocks[blockIdx.x];
+    const int64_t z = blockIdx.y;
+    const int64_t dense_row_chunks = cols * chunks_per_row;              // chunks in one dense row
+    const size_t dense_base = ((size_t)z * rows * block + (size_t)d.row() * block) * dense_row_chunks
+                              + (size_t)d.col() * chunks_per_row;
+    const size_t sparse_base = ((size_t)z * nnz + d.idx) * block * chunks_per_row;
+    for (int t = threadIdx.x; t < block * chunks_per_row; t += blockDim.x) {
+        const int i = t / chunks_per_row, c = t - i * chunks_per_row;
+        const size_t dn = dense_base + (size_t)i * dense_row_chunks + c;
+        if (kToSparse) dst[sparse_base + t] = src[dn];
+        else           dst[dn] = src[sparse_base + t];
+    }
+}
+
+int convert(bool to_sparse, int dtype, const void* src, void* dst, const int32_t* row_blocks,
+            int64_t nnz, int64_t batches, int64_t rows, int64_t cols, int block, cudaStream_t stream) {
+    if (!src || !dst || !row_blocks) return BSA_ERR_NULL_POINTER;
+    if (dtype != BSA_DTYPE_F32 && dtype != BSA_DTYPE_F16 && dtype != BSA_DTYPE_BF16) return BSA_ERR_BAD_DTYPE;
+    if (block != 32 && block != 64 && block != 128) return BSA_ERR_BAD_BLOCK;
+    if (nnz < 0 || batches < 0 || rows <= 0 || cols <= 0) return BSA_ERR_BAD_SHAPE;
+    if (batches > 65535 || nnz > (int64_t)INT32_MAX) return BSA_ERR_TOO_LARGE;
+    if (!aligned16(src) || !aligned16(dst)) return BSA_ERR_ALIGNMENT;
+    const int cpr = block * dtype_bytes(dtype) / 16;
+    if (!to_sparse) {
+        cudaError_t e = cudaMemsetAsync(dst, 0, (size_t)batches * rows * cols * block * block * dtype_bytes(dtype), stream);
+        if (e != cudaSuccess) return BSA_ERR_LAUNCH;
+    }
+    if (nnz == 0 || batches == 0) return BSA_OK;
+    const dim3 grid((unsigned)nnz, (unsigned)batches);
+    const BlockDesc* rb = reinterpret_cast<const BlockDesc*>(row_blocks);
+    if (to_sparse)
+        convert_kernel<true><<<grid, 256, 0, stream>>>((const uint4*)src, (uint4*)dst, rb, nnz, rows, cols, block, cpr);
+    else
+        convert_kernel<false><<<grid, 256, 0, stream>>>((const uint4*)src, (uint4*)dst, rb, nnz, rows, cols, block, cpr);
+    return launch_status();
+}
+
+}  // namespace
+}  // namespace bsa
+
+extern "C" int bsa_version(void) { return 100; /* 0.1.0 */ }
+
+extern "C" const char* bsa_status_string(int status) {
+    switch (status) {
+        case BSA_OK: return "ok";
+        case BSA_ERR_NULL_POINTER: return "a required pointer is NULL";
+        case BSA_ERR_BAD_MODE: return "mode must be sdd (0), dsd (1) or dds (2)";
+        case BSA_ERR_BAD_DTYPE: return "unsupported dtype";
+        case BSA_ERR_BAD_SHAPE: return "bad shape: sizes must be positive and the sparse sides multiples of the block size";
+        case BSA_ERR_BAD_BLOCK: return "block size must be 32, 64 or 128";
+        case BSA_ERR_ALIGNMENT: return "device pointers must be 16-byte aligned";
+        case BSA_ERR_WORKSPACE: return "workspace missing or smaller than BSA_WORKSPACE_BYTES";
+        case BSA_ERR_LAUNCH: return "CUDA launch failed";
+        case BSA_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel ran out";
+        case BSA_ERR_TOO_LARGE: return "a size exceeds the supported maximum";
+        case BSA_ERR_DRIVER: return "could not resolve a CUDA driver entry point";
+        default: return "unknown status";
+    }
+}
+
+extern "C" int bsa_matmul(int mode, int dtype, int trans_a, int trans_b,
+                          const void* a, const void* b, void* c,
+                          const int32_t* blocks, const int32_t* table,
+                          int64_t nnz, int64_t groups, int64_t batches,
+                          int64_t size_m, int64_t size_n, int64_t size_k, int block,
+                          void* workspace, size_t workspace_bytes, int engine, void* stream) {
+    using namespace bsa;
+    if (mode != BSA_MODE_SDD && mode != BSA_MODE_DSD && mode != BSA_MODE_DDS) return BSA_ERR_BAD_MODE;
+    if (dtype != BSA_DTYPE_F32 && dtype != BSA_DTYPE_F16 && dtype != BSA_DTYPE_BF16) return BSA_ERR_BAD_DTYPE;
+    if (block != 32 && block != 64 && block != 128) return BSA_ERR_BAD_BLOCK;
+    if (!a || !b || !c || !blocks || !table) return BSA_ERR_NULL_POINTER;
+    if (!workspace || workspace_bytes < BSA_WORKSPACE_BYTES) return BSA_ERR_WORKSPACE;
+    if (nnz < 0 || groups <= 0 || batches < 0 || size_m <= 0 || size_n <= 0 || size_k <= 0) return BSA_ERR_BAD_SHAPE;
+    if (nnz > (int64_t)INT32_MAX / 2 || groups > 65535 || batches > 65535) return BSA_ERR_TOO_LARGE;
+    if (engine != BSA_ENGINE_AUTO && engine != BSA_ENGINE_SIMT && engine != BSA_ENGINE_TCGEN05) return BSA_ERR_BAD_MODE;
+    // The grouped axis of the sparse operand must match the table.
+    const int64_t grouped = groups * block;
+    if (mode == BSA_MODE_SDD) {
+        // sdd walks the row layout as a flat list: rows of C are the groups.
+        if (size_m != grouped || size_n % block != 0) return BSA_ERR_BAD_SHAPE;
+    } else if (mode == BSA_MODE_DSD) {
+        if (size_m != grouped || size_k % block != 0) return BSA_ERR_BAD_SHAPE;
+    } else {
+        if (size_n != grouped || size_k % block != 0) return BSA_ERR_BAD_SHAPE;
+    }
+    if (!aligned16(a) || !aligned16(b) || !aligned16(c)) return BSA_ERR_ALIGNMENT;
+    if (batches == 0) return BSA_OK;
+
+    MatmulArgs args{mode, dtype, trans_a != 0, trans_b != 0, a, b, c,
+                    reinterpret_cast<const BlockDesc*>(blocks), table,
+                    nnz, groups, batches, size_m, size_n, size_k, block,
+                    static_cast<uint32_t*>(workspace), static_cast<cudaStream_t>(stream)};
+    if (engine == BSA_ENGINE_AUTO) {
+        const char* env = std::getenv("BSA_MATMUL_ENGINE");
+        if (env && std::strcmp(env, "simt") == 0) engine = BSA_ENGINE_SIMT;
+        else if (env && std::strcmp(env, "tcgen05") == 0) engine = BSA_ENGINE_TCGEN05;
+    }
+    if (engine == BSA_ENGINE_TCGEN05) {
+        if (!tc_supports(args)) return BSA_ERR_BAD_SHAPE;
+        return matmul_tc(args);
+    }
+    if (engine == BSA_ENGINE_AUTO && tc_supports(args)) return matmul_tc(args);
+    return matmul_simt(args);
+}
+
+extern "C" int bsa_dense_to_sparse(int dtype, const void* dense, void* sparse,
+                                   const int32_t* row_blocks, int64_t nnz, int64_t batches,
+                                   int64_t rows, int64_t cols, int block, void* stream) {
+    return bsa::convert(true, dtype, dense, sparse, row_blocks, nnz, batches, rows, cols, block,
+                        static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bsa_sparse_to_dense(int dtype, const void* sparse, void* dense,
+                                   const int32_t* row_blocks, int64_t nnz, int64_t batches,
+                                   int64_t rows, int64_t cols, int block, void* stream) {
+    return bsa::convert(false, dtype, sparse, dense, row_blocks, nnz, batches, rows, cols, block,
+                        static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bsa_workspace_status(void* workspace, void* stream) {
+    if (!workspace) return BSA_ERR_NULL_POINTER;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    uint32_t word = 0;
+    if (cudaMemcpyAsync(&word, workspace, sizeof(word), cudaMemcpyDeviceToHost, s) != cudaSuccess) return BSA_ERR_LAUNCH;
+    if (cudaStreamSynchronize(s) != cudaSuccess) return BSA_ERR_LAUNCH;
+    if (word == 0) return BSA_OK;
+    if (cudaMemsetAsync(workspace, 0, sizeof(word), s) != cudaSuccess) return BSA_ERR_LAUNCH;
+    if (cudaStreamSynchronize(s) != cudaSuccess) return BSA_ERR_LAUNCH;
+    return BSA_ERR_DEVICE_TIMEOUT;
+}

@@ -1,0 +1,355 @@
+// Block-sparse row softmax, forward and backward.
+//
+// Semantics follow the reference kernels sparse_softmax_32x32_forward_kernel
+// (sparse_softmax.cu:113-155) and ..._backward_kernel (:165-205): every dense
+// row is normalised over the elements of the nonzero blocks of its block row.
+// The reference makes 4 reads + 2 writes (forward) and 5 reads + 2 writes
+// (backward) per element; here a row is held in registers, so the forward
+// moves 1 read + 1 write and the backward 2 reads + 1 write per element,
+// all as 128-bit accesses.  Scale, causal and key-padding masks are fused.
+//
+// Work decomposition: one CTA per (batch, block row).  A dense row of that
+// block row is n_blocks segments of `block` contiguous elements, i.e.
+// n_blocks * CPS 16-byte chunks.  A team of L lanes (L a power of two,
+// 1..256, uniform per CTA) owns one row; lane t holds chunks t, t+L, ...
+// (at most kMaxChunks).  Teams narrower than a warp reduce with xor
+// shuffles, wider ones add one shared-memory exchange.  Block rows too long
+// for registers take a streaming three-pass path.
+#include <math_constants.h>
+
+#include "bsa_common.cuh"
+
+namespace bsa {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kMaxChunks = 8;             // 16-byte chunks a lane keeps in registers
+constexpr int kMaxRowBlocksSmem = 2048;   // descriptors staged in shared memory
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <typename T> struct Vec;
+template <> struct Vec<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+        const float4 r = *reinterpret_cast<const float4*>(p);
+        v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct Vec<__half> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const __half* p, float (&v)[8]) {
+        const uint4 r = *reinterpret_cast<const uint4*>(p);
+        const __half2* h = reinterpret_cast<const __half2*>(&r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+    }
+    static __device__ __forceinline__ void store(__half* p, const float (&v)[8]) {
+        uint4 r;
+        __half2* h = reinterpret_cast<__half2*>(&r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4*>(p) = r;
+    }
+};
+template <> struct Vec<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+        const uint4 r = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+        uint4 r;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4*>(p) = r;
+    }
+};
+
+struct SoftmaxParams {
+    const void* in0;   // forward: x          backward: y
+    const void* in1;   // forward: unused     backward: dy
+    void* out;         // forward: y          backward: dx
+    const BlockDesc* row_blocks;
+    const int32_t* row_table;
+    int64_t nnz;
+    int block_rows;
+    int block;
+    float scale;
+    int causal;
+    const uint8_t* kpm;
+    int64_t kpm_stride;
+    int64_t batches_per_kpm;
+};
+
+// Reduce over a team of L lanes.  For L <= 32 the team lies inside one warp.
+// For L > 32 it is L/32 consecutive warps and `exchange` (kWarps floats) is
+// used; every thread of the CTA must call this the same number of times.
+template <bool kIsMax>
+__device__ __forceinline__ float team_reduce(float v, int L, float* exchange) {
+    const int lim = L < 32 ? L : 32;
+    for (int d = lim >> 1; d > 0; d >>= 1) {
+        const float o = __shfl_xor_sync(0xffffffffu, v, d);
+        v = kIsMax ? fmaxf(v, o) : v + o;
+    }
+    if (L > 32) {
+        const int warp = threadIdx.x >> 5;
+        if ((threadIdx.x & 31) == 0) exchange[warp] = v;
+        __syncthreads();
+        const int wpt = L >> 5;
+        const int first = (warp / wpt) * wpt;
+        v = exchange[first];
+        for (int w = 1; w < wpt; ++w) v = kIsMax ? fmaxf(v, exchange[first + w]) : v + exchange[first + w];
+    }
+    return v;
+}
+
+// Scale the logits of one chunk into the log2 domain and mask them.
+template <int N>
+__device__ __forceinline__ void scale_and_mask(float (&v)[N], float scale_log2e, int q_pos, int k_pos0,
+                                               bool causal, const uint8_t* kpm_row) {
+#pragma unroll
+    for (int e = 0; e < N; ++e) {
+        float s = v[e] * scale_log2e;
+        if (causal && k_pos0 + e > q_pos) s = -CUDART_INF_F;
+        if (kpm_row != nullptr && kpm_row[k_pos0 + e] != 0) s = -CUDART_INF_F;
+        v[e] = s;
+    }
+}
+
+template <typename T, bool kBackward>
+__global__ void __launch_bounds__(kThreads)
+softmax_kernel(const SoftmaxParams p) {
+    constexpr int N = Vec<T>::N;
+    __shared__ BlockDesc s_desc[kMaxRowBlocksSmem];
+    __shared__ float s_red0[kWarps], s_red1[kWarps];
+
+    const int block = p.block;
+    const int cps = block / N;                    // chunks per segment
+    const int r = blockIdx.x;                     // block row
+    const int64_t z = blockIdx.y;                 // flattened batch * head
+    const int first = p.row_table[r];
+    const int n_blocks = p.row_table[r + 1] - first;
+    if (n_blocks <= 0) return;                    // uniform for the CTA
+    const int n_chunks = n_blocks * cps;
+
+    for (int j = threadIdx.x; j < n_blocks && j < kMaxRowBlocksSmem; j += kThreads)
+        s_desc[j] = p.row_blocks[first + j];
+    __syncthreads();
+
+    const T* in0 = static_cast<const T*>(p.in0) + z * p.nnz * block * block;
+    const T* in1 = kBackward ? static_cast<const T*>(p.in1) + z * p.nnz * block * block : nullptr;
+    T* out = static_cast<T*>(p.out) + z * p.nnz * block * block;
+    const uint8_t* kpm_row = (!kBackward && p.kpm) ? p.kpm + (z / p.batches_per_kpm) * p.kpm_stride : nullptr;
+    const float scale_log2e = p.scale * kLog2e;
+    const bool causal = !kBackward && p.causal != 0;
+
+    // team width: smallest power of two with L * kMaxChunks >= n_chunks
+    int L = 1;
+    while (L * kMaxChunks < n_chunks && L < kThreads) L <<= 1;
+
+    if (L * kMaxChunks >= n_chunks) {
+        // ---------------- register-resident path ----------------
+        const int team = threadIdx.x / L, t = threadIdx.x % L;
+        const int rows_per_pass = kThreads / L;
+        for (int i0 = 0; i0 < block; i0 += rows_per_pass) {
+            const int i = i0 + team;
+            const bool active = i < block;
+            float v[kMaxChunks][N];
+            float w[kBackward ? kMaxChunks : 1][N];
+            size_t off[kMaxChunks];
+            float acc = kBackward ? 0.f : -CUDART_INF_F;
+#pragma unroll
+            for (int k = 0; k < kMaxChunks; ++k) {
+                const int q = t + k * L;
+                if (active && q < n_chunks) {
+                    const int j = q / cps, s = q - j * cps;
+                    const BlockDesc d = s_desc[j];
+                    off[k] = ((size_t)d.idx * block + i) * block + s * N;
+                    Vec<T>::load(in0 + off[k], v[k]);
+                    if (kBackward) {
+                        Vec<T>::load(in1 + off[k], w[k]);
+#pragma unroll
+                        for (int e = 0; e < N; ++e) acc += v[k][e] * w[k][e];
+                    } else {
+                        scale_and_mask<N>(v[k], scale_log2e, r * block + i, d.col() * block + s * N, causal, kpm_row);
+#pragma unroll
+                        for (int e = 0; e < N; ++e) acc = fmaxf(acc, v[k][e]);
+                    }
+                }
+            }
+            if (kBackward) {
+                const float dot = team_reduce<false>(acc, L, s_red0);
+#pragma unroll
+                for (int k = 0; k < kMaxChunks; ++k) {
+                    const int q = t + k * L;
+                    if (active && q < n_chunks) {
+                        float o[N];
+#pragma unroll
+                        for (int e = 0; e < N; ++e) o[e] = p.scale * v[k][e] * (w[k][e] - dot);
+                        Vec<T>::store(out + off[k], o);
+                    }
+                }
+                if (L > 32) __syncthreads();   // s_red0 is rewritten by the next pass
+            } else {
+                float mx = team_reduce<true>(acc, L, s_red0);
+                if (mx == -CUDART_INF_F) mx = 0.f;   // fully masked row: exp2(-inf) = 0 below
+                float sum = 0.f;
+#pragma unroll
+                for (int k = 0; k < kMaxChunks; ++k) {
+                    const int q = t + k * L;
+                    if (active && q < n_chunks) {
+#pragma unroll
+                        for (int e = 0; e < N; ++e) { v[k][e] = exp2f(v[k][e] - mx); sum += v[k][e]; }
+                    }
+                }
+                sum = team_reduce<false>(sum, L, s_red1);
+                const float inv = sum > 0.f ? 1.f / sum : 0.f;
+#pragma unroll
+                for (int k = 0; k < kMaxChunks; ++k) {
+                    const int q = t + k * L;
+                    if (active && q < n_chunks) {
+#pragma unroll
+                        for (int e = 0; e < N; ++e) v[k][e] *= inv;
+                        Vec<T>::store(out + off[k], v[k]);
+                    }
+                }
+            }
+        }
+        return;
+    }
+
+    // ---------------- streaming path: the whole CTA walks one row at a time,
+    // re-reading it for each pass (rows longer than 2048 chunks) -------------
+    for (int i = 0; i < block; ++i) {
+        float acc = kBackward ? 0.f : -CUDART_INF_F;
+        for (int q = threadIdx.x; q < n_chunks; q += kThreads) {
+            const int j = q / cps, s = q - j * cps;
+            const BlockDesc d = j < kMaxRowBlocksSmem ? s_desc[j] : p.row_blocks[first + j];
+            const size_t o = ((size_t)d.idx * block + i) * block + s * N;
+            float a[N];
+            Vec<T>::load(in0 + o, a);
+            if (kBackward) {
+                float b[N];
+                Vec<T>::load(in1 + o, b);
+#pragma unroll
+                for (int e = 0; e < N; ++e) acc += a[e] * b[e];
+            } else {
+                scale_and_mask<N>(a, scale_log2e, r * block + i, d.col() * block + s * N, causal, kpm_row);
+#pragma unroll
+                for (int e = 0; e < N; ++e) acc = fmaxf(acc, a[e]);
+            }
+        }
+        float first_red = kBackward ? team_reduce<false>(acc, kThreads, s_red0)
+                                    : team_reduce<true>(acc, kThreads, s_red0);
+        float inv = 0.f;
+        if (!kBackward) {
+            if (first_red == -CUDART_INF_F) first_red = 0.f;
+            float sum = 0.f;
+            for (int q = threadIdx.x; q < n_chunks; q += kThreads) {
+                const int j = q / cps, s = q - j * cps;
+                const BlockDesc d = j < kMaxRowBlocksSmem ? s_desc[j] : p.row_blocks[first + j];
+                const size_t o = ((size_t)d.idx * block + i) * block + s * N;
+                float a[N];
+                Vec<T>::load(in0 + o, a);
+                scale_and_mask<N>(a, scale_log2e, r * block + i, d.col() * block + s * N, causal, kpm_row);
+#pragma unroll
+                for (int e = 0; e < N; ++e) sum += exp2f(a[e] - first_red);
+            }
+            sum = team_reduce<false>(sum, kThreads, s_red1);
+            inv = sum > 0.f ? 1.f / sum : 0.f;
+        }
+        for (int q = threadIdx.x; q < n_chunks; q += kThreads) {
+            const int j = q / cps, s = q - j * cps;
+            const BlockDesc d = j < kMaxRowBlocksSmem ? s_desc[j] : p.row_blocks[first + j];
+            const size_t o = ((size_t)d.idx * block + i) * block + s * N;
+            float a[N], res[N];
+            Vec<T>::load(in0 + o, a);
+            if (kBackward) {
+                float b[N];
+                Vec<T>::load(in1 + o, b);
+#pragma unroll
+                for (int e = 0; e < N; ++e) res[e] = p.scale * a[e] * (b[e] - first_red);
+            } else {
+                scale_and_mask<N>(a, scale_log2e, r * block + i, d.col() * block + s * N, causal, kpm_row);
+#pragma unroll
+                for (int e = 0; e < N; ++e) res[e] = exp2f(a[e] - first_red) * inv;
+            }
+            Vec<T>::store(out + o, res);
+        }
+        __syncthreads();   // exchange buffers are reused by the next row
+    }
+}
+
+int check_common(int dtype, const void* a, const void* b, const void* c,
+                 const int32_t* row_blocks, const int32_t* row_table,
+                 int64_t nnz, int64_t block_rows, int64_t batches, int block) {
+    if (!a || !b || !c || !row_blocks || !row_table) return BSA_ERR_NULL_POINTER;
+    if (dtype != BSA_DTYPE_F32 && dtype != BSA_DTYPE_F16 && dtype != BSA_DTYPE_BF16) return BSA_ERR_BAD_DTYPE;
+    if (block != 32 && block != 64 && block != 128) return BSA_ERR_BAD_BLOCK;
+    if (nnz < 0 || block_rows <= 0 || batches < 0) return BSA_ERR_BAD_SHAPE;
+    if (block_rows > 65535 || batches > 65535 || nnz > (int64_t)INT32_MAX) return BSA_ERR_TOO_LARGE;
+    if (!aligned16(a) || !aligned16(b) || !aligned16(c)) return BSA_ERR_ALIGNMENT;
+    return BSA_OK;
+}
+
+template <bool kBackward>
+int launch(int dtype, const SoftmaxParams& p, int64_t batches, cudaStream_t stream) {
+    if (batches == 0 || p.nnz == 0) return BSA_OK;
+    const dim3 grid((unsigned)p.block_rows, (unsigned)batches);
+    switch (dtype) {
+        case BSA_DTYPE_F32: softmax_kernel<float, kBackward><<<grid, kThreads, 0, stream>>>(p); break;
+        case BSA_DTYPE_F16: softmax_kernel<__half, kBackward><<<grid, kThreads, 0, stream>>>(p); break;
+        default: softmax_kernel<__nv_bfloat16, kBackward><<<grid, kThreads, 0, stream>>>(p); break;
+    }
+    return launch_status();
+}
+
+}  // namespace
+}  // namespace bsa
+
+extern "C" int bsa_softmax_forward(int dtype, const void* x, void* y,
+                                   const int32_t* row_blocks, const int32_t* row_table,
+                                   int64_t nnz, int64_t block_rows, int64_t batches, int block,
+                                   float scale, int causal,
+                                   const uint8_t* key_padding_mask, int64_t kpm_batches,
+                                   int64_t kpm_stride, void* stream) {
+    using namespace bsa;
+    int st = check_common(dtype, x, x, y, row_blocks, row_table, nnz, block_rows, batches, block);
+    if (st != BSA_OK) return st;
+    SoftmaxParams p{};
+    p.in0 = x; p.in1 = nullptr; p.out = y;
+    p.row_blocks = reinterpret_cast<const BlockDesc*>(row_blocks);
+    p.row_table = row_table;
+    p.nnz = nnz; p.block_rows = (int)block_rows; p.block = block;
+    p.scale = scale; p.causal = causal;
+    p.kpm = key_padding_mask; p.kpm_stride = kpm_stride; p.batches_per_kpm = 1;
+    if (key_padding_mask) {
+        if (kpm_batches <= 0 || batches % kpm_batches != 0 || kpm_stride <= 0) return BSA_ERR_BAD_SHAPE;
+        p.batches_per_kpm = batches / kpm_batches;
+    }
+    return launch<false>(dtype, p, batches, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bsa_softmax_backward(int dtype, const void* y, const void* dy, void* dx,
+                                    const int32_t* row_blocks, const int32_t* row_table,
+                                    int64_t nnz, int64_t block_rows, int64_t batches, int block,
+                                    float scale, void* stream) {
+    using namespace bsa;
+    int st = check_common(dtype, y, dy, dx, row_blocks, row_table, nnz, block_rows, batches, block);
+    if (st != BSA_OK) return st;
+    SoftmaxParams p{};
+    p.in0 = y; p.in1 = dy; p.out = dx;
+    p.row_blocks = reinterpret_cast<const BlockDesc*>(row_blocks);
+    p.row_table = row_table;
+    p.nnz = nnz; p.block_rows = (int)block_rows; p.block = block;
+    p.scale = scale; p.causal = 0;
+    p.kpm = nullptr; p.kpm_stride = 0; p.batches_per_kpm = 1;
+    return launch<true>(dtype, p, batches, static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,11 @@
+"""Block-sparse attention primitives for NVIDIA B200 (sm_100a).
+
+Same public surface as the reference package (sparse/__init__.py:1-2):
+``SparseLayout`` and ``matmul``; ``softmax`` is the op the reference left
+unbound (sparse_softmax.cu:208-236).
+"""
+from .layout import SparseLayout
+from .matmul import matmul, SparseMatMul
+from .softmax import softmax, SparseSoftmax
+
+__all__ = ["SparseLayout", "matmul", "SparseMatMul", "softmax", "SparseSoftmax"]

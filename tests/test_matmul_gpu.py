@@ -1,0 +1,151 @@
+"""GPU parity of the block-sparse matmul against the masked dense CPU oracle.
+
+Tolerance (stated by the parity contract): max |got - ref| / max |ref| <= 1e-4
+for fp32 and <= 1e-2 for fp16 (bf16: 3e-2), ref = dense CPU torch computation
+masked by the same layout on the same seeded inputs.
+"""
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_close, load_golden_layout, seeded
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+VARIANTS = [(m, ta, tb) for m in ("sdd", "dsd", "dds") for ta in (False, True) for tb in (False, True)]
+
+
+def operands(mode, ta, tb, pattern, block, inner, batch, seed, dtype, dist="normal"):
+    """Seeded CPU operands for op(A)[m,k] @ op(B)[k,n]; `inner` is the free dense size."""
+    rows, cols = pattern.shape[0] * block, pattern.shape[1] * block
+    nnz = int((np.asarray(pattern) != 0).sum())
+    if mode == "sdd":
+        m, n, k = rows, cols, inner
+    elif mode == "dsd":
+        m, k, n = (cols, rows, inner) if ta else (rows, cols, inner)
+    else:
+        k, n, m = (cols, rows, inner) if tb else (rows, cols, inner)
+    a_shape = batch + ((nnz, block, block) if mode[1] == "s" else ((k, m) if ta else (m, k)))
+    b_shape = batch + ((nnz, block, block) if mode[2] == "s" else ((n, k) if tb else (k, n)))
+    return seeded(a_shape, seed, dtype, dist), seeded(b_shape, seed + 1, dtype, dist)
+
+
+def run_case(mode, ta, tb, pattern, block, inner, dtype, engine, batch=(2,), seed=0, dist="normal"):
+    from sparse import SparseLayout
+    from sparse.kernel import sparse_ops
+    pattern = np.asarray(pattern)
+    layout = SparseLayout(torch.as_tensor(pattern), block=block)
+    a, b = operands(mode, ta, tb, pattern, block, inner, batch, seed, dtype, dist)
+    got = sparse_ops.sparse_matmul(a.cuda(), b.cuda(), mode, layout.row_layout, layout.col_layout, ta, tb,
+                                   block, engine)
+    torch.cuda.synchronize()
+    sparse_ops.check_device_status(0)
+    ref = oracle.sparse_matmul(a, b, mode, pattern, block, ta, tb,
+                               dtype=torch.float64 if dtype == torch.float32 else torch.float32)
+    assert got.dtype == dtype and tuple(got.shape) == tuple(ref.shape)
+    assert_close(got, ref, dtype, "%s ta=%s tb=%s block=%d %s %s" % (mode, ta, tb, block, dtype, engine))
+    return got
+
+
+def engines_for(dtype, block, inner):
+    """Every case runs on the CUDA-core engine and on whatever `auto` selects (tcgen05 where it applies)."""
+    return ["simt", "auto"]
+
+
+@pytest.mark.parametrize("mode,ta,tb", VARIANTS)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_all_variants_nonsquare_block32(mode, ta, tb, dtype):
+    g = load_golden_layout("kat_4x3")
+    for engine in engines_for(dtype, 32, 64):
+        run_case(mode, ta, tb, g["pattern"], 32, 64, dtype, engine, seed=3)
+
+
+@pytest.mark.parametrize("mode,ta,tb", VARIANTS)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_all_variants_nonsquare_block64(mode, ta, tb, dtype):
+    g = load_golden_layout("empty_row_col_5x4")   # has an empty block row and an empty block column
+    for inner in (64, 128):
+        for engine in engines_for(dtype, 64, inner):
+            run_case(mode, ta, tb, g["pattern"], 64, inner, dtype, engine, seed=5)
+
+
+@pytest.mark.parametrize("mode,ta,tb", VARIANTS)
+def test_all_variants_block128_and_odd_inner(mode, ta, tb):
+    run_case(mode, ta, tb, [[1, 0], [1, 1]], 128, 64, torch.float16, "auto", batch=(1,), seed=7)
+    run_case(mode, ta, tb, [[1, 0, 1], [0, 1, 1]], 32, 40, torch.float32, "auto", batch=(1, 2), seed=9)
+
+
+@pytest.mark.parametrize("name", ["single_block_3x3", "full_3x5", "one_by_one"])
+@pytest.mark.parametrize("mode,ta,tb", VARIANTS)
+def test_edge_layouts(name, mode, ta, tb):
+    g = load_golden_layout(name)
+    for dtype, block in ((torch.float32, 32), (torch.float16, 64)):
+        for engine in engines_for(dtype, block, 64):
+            run_case(mode, ta, tb, g["pattern"], block, 64, dtype, engine, batch=(3,), seed=11)
+
+
+def test_config1_sdd_fp32_per_head_layouts():
+    """BASELINE config 1: batch 1, heads 2, seq 256, head_dim 64, block 32, Bernoulli(0.5) + diagonal
+    per head, Q.K^T as sdd(N,T) in fp32."""
+    for head in range(2):
+        g = load_golden_layout("cfg1_head%d" % head)
+        q = seeded((1, 256, 64), 1000 + head)
+        k = seeded((1, 256, 64), 1100 + head)
+        from sparse import SparseLayout, matmul
+        layout = SparseLayout(torch.tensor(g["pattern"]))
+        got = matmul(q.cuda(), k.cuda(), "sdd", layout, False, True)
+        ref = oracle.sparse_matmul(q, k, "sdd", np.array(g["pattern"]), 32, False, True, dtype=torch.float64)
+        assert_close(got, ref, torch.float32, "config 1 head %d" % head)
+
+
+@pytest.mark.parametrize("mode,ta,tb", VARIANTS)
+def test_config4_fp32_stress_slice(mode, ta, tb):
+    """BASELINE config 4 on one head: seq 2048, head_dim 128, block 32, Bernoulli(0.1) + diagonal,
+    inputs U(-1, 1), all modes and transpositions, fp32 tolerance 1e-4."""
+    g = load_golden_layout("cfg4_head0")
+    run_case(mode, ta, tb, g["pattern"], 32, 128, torch.float32, "auto", batch=(1,), seed=4000, dist="uniform")
+
+
+def test_autograd_matches_dense_autograd():
+    """Gradients through sparse.matmul equal those of the dense masked computation."""
+    from sparse import SparseLayout, matmul
+    g = load_golden_layout("kat_4x3")
+    pattern = np.array(g["pattern"])
+    block = 32
+    layout = SparseLayout(torch.tensor(pattern), block=block)
+    for mode, ta, tb in VARIANTS:
+        a, b = operands(mode, ta, tb, pattern, block, 64, (2,), 21, torch.float32)
+        ag, bg = a.cuda().requires_grad_(True), b.cuda().requires_grad_(True)
+        out = matmul(ag, bg, mode, layout, ta, tb)
+        dc = seeded(tuple(out.shape), 23)
+        out.backward(dc.cuda())
+        ad, bd = a.double().requires_grad_(True), b.double().requires_grad_(True)
+        a_full = oracle.to_dense(ad, pattern, block) if mode[1] == "s" else ad
+        b_full = oracle.to_dense(bd, pattern, block) if mode[2] == "s" else bd
+        c = (a_full.transpose(-1, -2) if ta else a_full) @ (b_full.transpose(-1, -2) if tb else b_full)
+        if mode[0] == "s":
+            c = oracle.to_sparse(c, pattern, block)
+        c.backward(dc.double())
+        assert_close(ag.grad, ad.grad, torch.float32, "dA %s %s %s" % (mode, ta, tb))
+        assert_close(bg.grad, bd.grad, torch.float32, "dB %s %s %s" % (mode, ta, tb))
+
+
+def test_argument_validation_raises():
+    from sparse import SparseLayout
+    from sparse.kernel import sparse_ops
+    layout = SparseLayout(torch.tensor([[1, 0], [1, 1]]))
+    q = torch.randn(1, 64, 64, device="cuda")
+    with pytest.raises(RuntimeError):
+        sparse_ops.sparse_matmul(q, q, "ssd", layout.row_layout, layout.col_layout, False, True, 32, "auto")
+    with pytest.raises(RuntimeError):
+        sparse_ops.sparse_matmul(q, q.double(), "sdd", layout.row_layout, layout.col_layout, False, True, 32, "auto")
+    with pytest.raises(RuntimeError):   # seq 96 does not match the 2-row layout
+        sparse_ops.sparse_matmul(torch.randn(1, 96, 64, device="cuda"), q, "sdd", layout.row_layout,
+                                 layout.col_layout, False, True, 32, "auto")
+    with pytest.raises(RuntimeError):   # int tensors are rejected, not silently ignored
+        sparse_ops.sparse_matmul(q.int(), q.int(), "sdd", layout.row_layout, layout.col_layout, False, True, 32,
+                                 "auto")
+    with pytest.raises(RuntimeError):   # wrong number of blocks in the sparse operand
+        sparse_ops.sparse_matmul(torch.randn(1, 5, 32, 32, device="cuda"), q, "dsd", layout.row_layout,
+                                 layout.col_layout, False, False, 32, "auto")

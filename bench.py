@@ -156,11 +156,11 @@ def device_step(ops, lay, q, k, v, do, scale, block, events=None):
     rl, cl = lay.row_layout, lay.col_layout
     calls = [
         lambda st: ops.sparse_matmul(q, k, "sdd", rl, cl, False, True, block),
-        lambda st: ops.sparse_softmax_forward(st["s"], rl[0], rl[1], scale, False, None),
+        lambda st: ops.sparse_softmax_forward(st["s"], rl[0], rl[1], scale, False, None, lay.max_row_blocks),
         lambda st: ops.sparse_matmul(st["p"], v, "dsd", rl, cl, False, False, block),
         lambda st: ops.sparse_matmul(do, v, "sdd", rl, cl, False, True, block),
         lambda st: ops.sparse_matmul(st["p"], do, "dsd", rl, cl, True, False, block),
-        lambda st: ops.sparse_softmax_backward(st["p"], st["dp"], rl[0], rl[1], scale),
+        lambda st: ops.sparse_softmax_backward(st["p"], st["dp"], rl[0], rl[1], scale, lay.max_row_blocks),
         lambda st: ops.sparse_matmul(st["ds"], k, "dsd", rl, cl, False, False, block),
         lambda st: ops.sparse_matmul(st["ds"], q, "dsd", rl, cl, True, False, block),
     ]

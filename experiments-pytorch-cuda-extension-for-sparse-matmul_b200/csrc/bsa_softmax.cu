@@ -17,6 +17,8 @@
 // for registers take a streaming three-pass path.
 #include <math_constants.h>
 
+#include <algorithm>
+
 #include "bsa_common.cuh"
 
 namespace bsa {
@@ -35,6 +37,9 @@ template <> struct Vec<float> {
         const float4 r = *reinterpret_cast<const float4*>(p);
         v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
     }
+    static __device__ __forceinline__ void unpack(const uint4& r, float (&v)[4]) {
+        v[0] = __uint_as_float(r.x); v[1] = __uint_as_float(r.y); v[2] = __uint_as_float(r.z); v[3] = __uint_as_float(r.w);
+    }
     static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
         *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
     }
@@ -43,6 +48,11 @@ template <> struct Vec<__half> {
     static constexpr int N = 8;
     static __device__ __forceinline__ void load(const __half* p, float (&v)[8]) {
         const uint4 r = *reinterpret_cast<const uint4*>(p);
+        const __half2* h = reinterpret_cast<const __half2*>(&r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+    }
+    static __device__ __forceinline__ void unpack(const uint4& r, float (&v)[8]) {
         const __half2* h = reinterpret_cast<const __half2*>(&r);
 #pragma unroll
         for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
@@ -59,6 +69,11 @@ template <> struct Vec<__nv_bfloat16> {
     static constexpr int N = 8;
     static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
         const uint4 r = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+    }
+    static __device__ __forceinline__ void unpack(const uint4& r, float (&v)[8]) {
         const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
 #pragma unroll
         for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
@@ -86,6 +101,7 @@ struct SoftmaxParams {
     const uint8_t* kpm;
     int64_t kpm_stride;
     int64_t batches_per_kpm;
+    int skip_upto_chunks;   // general kernel: rows this short were done by the fast kernel
 };
 
 // Reduce over a team of L lanes.  For L <= 32 the team lies inside one warp.
@@ -138,6 +154,7 @@ softmax_kernel(const SoftmaxParams p) {
     const int n_blocks = p.row_table[r + 1] - first;
     if (n_blocks <= 0) return;                    // uniform for the CTA
     const int n_chunks = n_blocks * cps;
+    if (n_chunks <= p.skip_upto_chunks) return;
 
     for (int j = threadIdx.x; j < n_blocks && j < kMaxRowBlocksSmem; j += kThreads)
         s_desc[j] = p.row_blocks[first + j];
@@ -287,6 +304,142 @@ softmax_kernel(const SoftmaxParams p) {
     }
 }
 
+
+// Fast path: rows of at most 256 * CH chunks, CH chunks per lane in registers, the next row of
+// the team prefetched (as raw 16-byte chunks) while the current one is reduced and written.
+// The block descriptor of each of a lane's chunks is the same for every row of the block row,
+// so it is looked up once per CTA.  Longer rows are left to softmax_kernel.
+template <typename T, int CH, bool kBackward>
+__global__ void __launch_bounds__(kThreads)
+softmax_rows_kernel(const SoftmaxParams p) {
+    constexpr int N = Vec<T>::N;
+    __shared__ float s_red0[kWarps], s_red1[kWarps];
+
+    const int block = p.block;
+    const int cps = block / N;                    // chunks per segment (a power of two)
+    const int cps_shift = 31 - __clz(cps);
+    const int r = blockIdx.x;
+    const int64_t z = blockIdx.y;
+    const int first = p.row_table[r];
+    const int n_blocks = p.row_table[r + 1] - first;
+    if (n_blocks <= 0) return;
+    const int n_chunks = n_blocks << cps_shift;
+    if (n_chunks > kThreads * CH) return;         // left to the general kernel
+
+    int L = 1;
+    while (L * CH < n_chunks) L <<= 1;            // <= 256
+    const int team = threadIdx.x / L, t = threadIdx.x & (L - 1);
+    const int rows_per_pass = kThreads / L;
+
+    uint32_t base[CH];
+    int kpos[CH];
+#pragma unroll
+    for (int k = 0; k < CH; ++k) {
+        const int q = t + k * L;
+        base[k] = 0xFFFFFFFFu;
+        kpos[k] = 0;
+        if (q < n_chunks) {
+            const int j = q >> cps_shift, s = q & (cps - 1);
+            const BlockDesc d = p.row_blocks[first + j];
+            base[k] = (uint32_t)d.idx * (uint32_t)(block * block) + (uint32_t)(s * N);
+            kpos[k] = d.col() * block + s * N;
+        }
+    }
+
+    const size_t zoff = (size_t)z * p.nnz * block * block;
+    const T* in0 = static_cast<const T*>(p.in0) + zoff;
+    const T* in1 = kBackward ? static_cast<const T*>(p.in1) + zoff : nullptr;
+    T* out = static_cast<T*>(p.out) + zoff;
+    const uint8_t* kpm_row = (!kBackward && p.kpm) ? p.kpm + (z / p.batches_per_kpm) * p.kpm_stride : nullptr;
+    const float scale_log2e = p.scale * kLog2e;
+    const bool causal = !kBackward && p.causal != 0;
+    const bool masked = causal || kpm_row != nullptr;
+
+    uint4 raw0[CH], raw1[kBackward ? CH : 1];
+    {
+        const int i = team;
+#pragma unroll
+        for (int k = 0; k < CH; ++k) {
+            if (i < block && base[k] != 0xFFFFFFFFu) {
+                raw0[k] = *reinterpret_cast<const uint4*>(in0 + base[k] + i * block);
+                if (kBackward) raw1[k] = *reinterpret_cast<const uint4*>(in1 + base[k] + i * block);
+            }
+        }
+    }
+    for (int i0 = 0; i0 < block; i0 += rows_per_pass) {
+        const int i = i0 + team;
+        const bool active = i < block;
+        float v[CH][N];
+        float w[kBackward ? CH : 1][N];
+        float acc = kBackward ? 0.f : -CUDART_INF_F;
+#pragma unroll
+        for (int k = 0; k < CH; ++k) {
+            if (active && base[k] != 0xFFFFFFFFu) {
+                Vec<T>::unpack(raw0[k], v[k]);
+                if (kBackward) {
+                    Vec<T>::unpack(raw1[k], w[k]);
+#pragma unroll
+                    for (int e = 0; e < N; ++e) acc += v[k][e] * w[k][e];
+                } else {
+                    if (masked) {
+                        scale_and_mask<N>(v[k], scale_log2e, r * block + i, kpos[k], causal, kpm_row);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < N; ++e) v[k][e] *= scale_log2e;
+                    }
+#pragma unroll
+                    for (int e = 0; e < N; ++e) acc = fmaxf(acc, v[k][e]);
+                }
+            }
+        }
+        // prefetch the team's next row
+        {
+            const int in = i + rows_per_pass;
+#pragma unroll
+            for (int k = 0; k < CH; ++k) {
+                if (in < block && base[k] != 0xFFFFFFFFu) {
+                    raw0[k] = *reinterpret_cast<const uint4*>(in0 + base[k] + in * block);
+                    if (kBackward) raw1[k] = *reinterpret_cast<const uint4*>(in1 + base[k] + in * block);
+                }
+            }
+        }
+        if (kBackward) {
+            const float dot = team_reduce<false>(acc, L, s_red0);
+#pragma unroll
+            for (int k = 0; k < CH; ++k) {
+                if (active && base[k] != 0xFFFFFFFFu) {
+                    float o[N];
+#pragma unroll
+                    for (int e = 0; e < N; ++e) o[e] = p.scale * v[k][e] * (w[k][e] - dot);
+                    Vec<T>::store(out + base[k] + i * block, o);
+                }
+            }
+            if (L > 32) __syncthreads();
+        } else {
+            float mx = team_reduce<true>(acc, L, s_red0);
+            if (mx == -CUDART_INF_F) mx = 0.f;
+            float sum = 0.f;
+#pragma unroll
+            for (int k = 0; k < CH; ++k) {
+                if (active && base[k] != 0xFFFFFFFFu) {
+#pragma unroll
+                    for (int e = 0; e < N; ++e) { v[k][e] = exp2f(v[k][e] - mx); sum += v[k][e]; }
+                }
+            }
+            sum = team_reduce<false>(sum, L, s_red1);
+            const float inv = sum > 0.f ? 1.f / sum : 0.f;
+#pragma unroll
+            for (int k = 0; k < CH; ++k) {
+                if (active && base[k] != 0xFFFFFFFFu) {
+#pragma unroll
+                    for (int e = 0; e < N; ++e) v[k][e] *= inv;
+                    Vec<T>::store(out + base[k] + i * block, v[k]);
+                }
+            }
+        }
+    }
+}
+
 int check_common(int dtype, const void* a, const void* b, const void* c,
                  const int32_t* row_blocks, const int32_t* row_table,
                  int64_t nnz, int64_t block_rows, int64_t batches, int block) {
@@ -299,16 +452,44 @@ int check_common(int dtype, const void* a, const void* b, const void* c,
     return BSA_OK;
 }
 
-template <bool kBackward>
-int launch(int dtype, const SoftmaxParams& p, int64_t batches, cudaStream_t stream) {
-    if (batches == 0 || p.nnz == 0) return BSA_OK;
+template <typename T, bool kBackward>
+int launch_typed(const SoftmaxParams& base, int64_t batches, int64_t max_row_blocks, cudaStream_t stream) {
+    SoftmaxParams p = base;
     const dim3 grid((unsigned)p.block_rows, (unsigned)batches);
-    switch (dtype) {
-        case BSA_DTYPE_F32: softmax_kernel<float, kBackward><<<grid, kThreads, 0, stream>>>(p); break;
-        case BSA_DTYPE_F16: softmax_kernel<__half, kBackward><<<grid, kThreads, 0, stream>>>(p); break;
-        default: softmax_kernel<__nv_bfloat16, kBackward><<<grid, kThreads, 0, stream>>>(p); break;
+    const int cps = p.block / Vec<T>::N;
+    // chunks per lane: enough for an average row in one warp and, when the longest row is known,
+    // for that row in one CTA
+    const int64_t avg_chunks = (p.nnz * cps + p.block_rows - 1) / p.block_rows;
+    int64_t need = (avg_chunks + 31) / 32;
+    if (max_row_blocks > 0) need = std::max<int64_t>(need, (max_row_blocks * cps + kThreads - 1) / kThreads);
+    int ch = need <= 1 ? 1 : need <= 2 ? 2 : need <= 3 ? 3 : need <= 4 ? 4 : 8;
+    switch (ch) {
+        case 1: softmax_rows_kernel<T, 1, kBackward><<<grid, kThreads, 0, stream>>>(p); break;
+        case 2: softmax_rows_kernel<T, 2, kBackward><<<grid, kThreads, 0, stream>>>(p); break;
+        case 3: softmax_rows_kernel<T, 3, kBackward><<<grid, kThreads, 0, stream>>>(p); break;
+        case 4: softmax_rows_kernel<T, 4, kBackward><<<grid, kThreads, 0, stream>>>(p); break;
+        default: softmax_rows_kernel<T, 8, kBackward><<<grid, kThreads, 0, stream>>>(p); break;
     }
-    return launch_status();
+    int st = launch_status();
+    if (st != BSA_OK) return st;
+    // rows longer than the fast kernel holds (or of unknown length) go to the general kernel
+    if (max_row_blocks <= 0 || max_row_blocks * cps > (int64_t)kThreads * ch) {
+        p.skip_upto_chunks = kThreads * ch;
+        softmax_kernel<T, kBackward><<<grid, kThreads, 0, stream>>>(p);
+        st = launch_status();
+    }
+    return st;
+}
+
+template <bool kBackward>
+int launch(int dtype, const SoftmaxParams& p, int64_t batches, int64_t max_row_blocks, cudaStream_t stream) {
+    if (batches == 0 || p.nnz == 0) return BSA_OK;
+    if (p.nnz * (int64_t)p.block * p.block >= ((int64_t)1 << 32)) return BSA_ERR_TOO_LARGE;
+    switch (dtype) {
+        case BSA_DTYPE_F32: return launch_typed<float, kBackward>(p, batches, max_row_blocks, stream);
+        case BSA_DTYPE_F16: return launch_typed<__half, kBackward>(p, batches, max_row_blocks, stream);
+        default: return launch_typed<__nv_bfloat16, kBackward>(p, batches, max_row_blocks, stream);
+    }
 }
 
 }  // namespace
@@ -319,7 +500,7 @@ extern "C" int bsa_softmax_forward(int dtype, const void* x, void* y,
                                    int64_t nnz, int64_t block_rows, int64_t batches, int block,
                                    float scale, int causal,
                                    const uint8_t* key_padding_mask, int64_t kpm_batches,
-                                   int64_t kpm_stride, void* stream) {
+                                   int64_t kpm_stride, int64_t max_row_blocks, void* stream) {
     using namespace bsa;
     int st = check_common(dtype, x, x, y, row_blocks, row_table, nnz, block_rows, batches, block);
     if (st != BSA_OK) return st;
@@ -334,13 +515,13 @@ extern "C" int bsa_softmax_forward(int dtype, const void* x, void* y,
         if (kpm_batches <= 0 || batches % kpm_batches != 0 || kpm_stride <= 0) return BSA_ERR_BAD_SHAPE;
         p.batches_per_kpm = batches / kpm_batches;
     }
-    return launch<false>(dtype, p, batches, static_cast<cudaStream_t>(stream));
+    return launch<false>(dtype, p, batches, max_row_blocks, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int bsa_softmax_backward(int dtype, const void* y, const void* dy, void* dx,
                                     const int32_t* row_blocks, const int32_t* row_table,
                                     int64_t nnz, int64_t block_rows, int64_t batches, int block,
-                                    float scale, void* stream) {
+                                    float scale, int64_t max_row_blocks, void* stream) {
     using namespace bsa;
     int st = check_common(dtype, y, dy, dx, row_blocks, row_table, nnz, block_rows, batches, block);
     if (st != BSA_OK) return st;
@@ -351,5 +532,5 @@ extern "C" int bsa_softmax_backward(int dtype, const void* y, const void* dy, vo
     p.nnz = nnz; p.block_rows = (int)block_rows; p.block = block;
     p.scale = scale; p.causal = 0;
     p.kpm = nullptr; p.kpm_stride = 0; p.batches_per_kpm = 1;
-    return launch<true>(dtype, p, batches, static_cast<cudaStream_t>(stream));
+    return launch<true>(dtype, p, batches, max_row_blocks, static_cast<cudaStream_t>(stream));
 }

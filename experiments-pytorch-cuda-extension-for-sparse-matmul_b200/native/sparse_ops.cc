@@ -140,7 +140,8 @@ torch::Tensor sparse_matmul(torch::Tensor a, torch::Tensor b, const std::string&
 }
 
 torch::Tensor sparse_softmax_forward(torch::Tensor x, torch::Tensor row_blocks, torch::Tensor row_table,
-                                     double scale, bool causal, c10::optional<torch::Tensor> key_padding_mask) {
+                                     double scale, bool causal, c10::optional<torch::Tensor> key_padding_mask,
+                                     int64_t max_row_blocks) {
     TORCH_CHECK(x.is_cuda() && x.dim() >= 4, "x must be a CUDA tensor [..., nnz, block, block]");
     check_layout({row_blocks, row_table}, x.device(), "row layout");
     const int dtype = dtype_code(x);
@@ -165,13 +166,14 @@ torch::Tensor sparse_softmax_forward(torch::Tensor x, torch::Tensor row_blocks, 
         check_status(bsa_softmax_forward(dtype, x.data_ptr(), y.data_ptr(), row_blocks.data_ptr<int>(),
                                          row_table.data_ptr<int>(), nnz, row_table.size(0) - 1, x.size(0),
                                          static_cast<int>(block), static_cast<float>(scale), causal, kpm,
-                                         kpm_batches, kpm_stride, at::cuda::getCurrentCUDAStream().stream()),
+                                         kpm_batches, kpm_stride, max_row_blocks,
+                                         at::cuda::getCurrentCUDAStream().stream()),
                      "sparse_softmax_forward");
     return y.reshape(shape);
 }
 
 torch::Tensor sparse_softmax_backward(torch::Tensor y, torch::Tensor dy, torch::Tensor row_blocks,
-                                      torch::Tensor row_table, double scale) {
+                                      torch::Tensor row_table, double scale, int64_t max_row_blocks) {
     TORCH_CHECK(y.is_cuda() && dy.is_cuda() && y.dim() >= 4 && y.sizes() == dy.sizes(),
                 "y and dy must be CUDA tensors of one shape [..., nnz, block, block]");
     TORCH_CHECK(y.scalar_type() == dy.scalar_type(), "y and dy must have the same dtype");
@@ -188,7 +190,8 @@ torch::Tensor sparse_softmax_backward(torch::Tensor y, torch::Tensor dy, torch::
         check_status(bsa_softmax_backward(dtype, y.data_ptr(), dy.data_ptr(), dx.data_ptr(),
                                           row_blocks.data_ptr<int>(), row_table.data_ptr<int>(), nnz,
                                           row_table.size(0) - 1, y.size(0), static_cast<int>(block),
-                                          static_cast<float>(scale), at::cuda::getCurrentCUDAStream().stream()),
+                                          static_cast<float>(scale), max_row_blocks,
+                                          at::cuda::getCurrentCUDAStream().stream()),
                      "sparse_softmax_backward");
     return dx.reshape(shape);
 }
@@ -284,9 +287,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("tr_a") = false, py::arg("tr_b") = false, py::arg("block") = 0, py::arg("engine") = "auto");
     m.def("sparse_softmax_forward", &sparse_softmax_forward, "Block-sparse row softmax.",
           py::arg("x"), py::arg("row_blocks"), py::arg("row_table"), py::arg("scale") = 1.0,
-          py::arg("causal") = false, py::arg("key_padding_mask") = py::none());
+          py::arg("causal") = false, py::arg("key_padding_mask") = py::none(), py::arg("max_row_blocks") = 0);
     m.def("sparse_softmax_backward", &sparse_softmax_backward, "Gradient of the block-sparse row softmax.",
-          py::arg("y"), py::arg("dy"), py::arg("row_blocks"), py::arg("row_table"), py::arg("scale") = 1.0);
+          py::arg("y"), py::arg("dy"), py::arg("row_blocks"), py::arg("row_table"), py::arg("scale") = 1.0,
+          py::arg("max_row_blocks") = 0);
     m.def("build_layout", &build_layout, "Build row / column layout metadata on the device.", py::arg("pattern"));
     m.def("dense_to_sparse", &dense_to_sparse, "Gather the layout's blocks from a dense matrix.");
     m.def("sparse_to_dense", &sparse_to_dense, "Scatter blocks into a zero-filled dense matrix.");

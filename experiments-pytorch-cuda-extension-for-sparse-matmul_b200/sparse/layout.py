@@ -38,6 +38,10 @@ class SparseLayout:
             device = pattern.device if pattern.is_cuda else torch.device("cuda", torch.cuda.current_device())
         self.device = torch.device(device)
         self.row_layout, self.col_layout = self._create_layouts(pattern)
+        # longest block row / column: a hint that lets the softmax cover every row in one launch
+        on = pattern != 0
+        self.max_row_blocks = int(on.sum(dim=1).max()) if on.numel() else 0
+        self.max_col_blocks = int(on.sum(dim=0).max()) if on.numel() else 0
 
     def _create_layouts(self, pattern: torch.Tensor
                         ) -> Tuple[Tuple[torch.Tensor, torch.Tensor], Tuple[torch.Tensor, torch.Tensor]]:

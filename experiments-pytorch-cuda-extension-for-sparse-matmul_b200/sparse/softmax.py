@@ -27,7 +27,7 @@ class SparseSoftmax(torch.autograd.Function):
                 key_padding_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
         row_blocks, row_table = layout.row_layout
         y = kernel.sparse_ops.sparse_softmax_forward(x, row_blocks, row_table, float(scale), bool(causal),
-                                                     key_padding_mask)
+                                                     key_padding_mask, getattr(layout, "max_row_blocks", 0))
         ctx.save_for_backward(y)
         ctx.layout, ctx.scale = layout, float(scale)
         return y
@@ -38,7 +38,8 @@ class SparseSoftmax(torch.autograd.Function):
         row_blocks, row_table = ctx.layout.row_layout
         dx = None
         if ctx.needs_input_grad[0]:
-            dx = kernel.sparse_ops.sparse_softmax_backward(y, dy.contiguous(), row_blocks, row_table, ctx.scale)
+            dx = kernel.sparse_ops.sparse_softmax_backward(y, dy.contiguous(), row_blocks, row_table, ctx.scale,
+                                                           getattr(ctx.layout, "max_row_blocks", 0))
         return dx, None, None, None, None
 
 

@@ -134,13 +134,15 @@ int bsa_matmul(int mode, int dtype, int trans_a, int trans_b,
  *   key_padding_mask  NULL or device uint8 [kpm_batches, kpm_stride]; nonzero
  *                   marks a key position as padding (masked) for the batch
  *                   index z / (batches / kpm_batches)
+ *   max_row_blocks  largest number of blocks in any block row, or 0 if not
+ *                   known; a hint that lets one kernel launch cover all rows
  */
 int bsa_softmax_forward(int dtype, const void* x, void* y,
                         const int32_t* row_blocks, const int32_t* row_table,
                         int64_t nnz, int64_t block_rows, int64_t batches, int block,
                         float scale, int causal,
                         const uint8_t* key_padding_mask, int64_t kpm_batches,
-                        int64_t kpm_stride, void* stream);
+                        int64_t kpm_stride, int64_t max_row_blocks, void* stream);
 
 /*
  * Gradient of bsa_softmax_forward with respect to x:
@@ -150,7 +152,7 @@ int bsa_softmax_forward(int dtype, const void* x, void* y,
 int bsa_softmax_backward(int dtype, const void* y, const void* dy, void* dx,
                          const int32_t* row_blocks, const int32_t* row_table,
                          int64_t nnz, int64_t block_rows, int64_t batches, int block,
-                         float scale, void* stream);
+                         float scale, int64_t max_row_blocks, void* stream);
 
 /*
  * Gather the blocks of a dense [batches, rows*block, cols*block] matrix into

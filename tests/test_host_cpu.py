@@ -79,13 +79,13 @@ def test_softmax_and_layout_validation_codes(lib):
     lib.bsa_softmax_forward.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                         ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                         ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_void_p,
-                                        ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p]
+                                        ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p]
     f = lib.bsa_softmax_forward
-    assert f(1, None, 16, 16, 16, 1, 1, 1, 64, 1.0, 0, None, 0, 0, None) == 1
-    assert f(9, 16, 16, 16, 16, 1, 1, 1, 64, 1.0, 0, None, 0, 0, None) == 3
-    assert f(1, 16, 16, 16, 16, 1, 1, 1, 48, 1.0, 0, None, 0, 0, None) == 5
-    assert f(1, 16, 24, 16, 16, 1, 1, 1, 64, 1.0, 0, None, 0, 0, None) == 6
-    assert f(1, 16, 16, 16, 16, 1, 1, 3, 64, 1.0, 0, 16, 2, 64, None) == 4     # 2 mask rows do not divide 3
+    assert f(1, None, 16, 16, 16, 1, 1, 1, 64, 1.0, 0, None, 0, 0, 0, None) == 1
+    assert f(9, 16, 16, 16, 16, 1, 1, 1, 64, 1.0, 0, None, 0, 0, 0, None) == 3
+    assert f(1, 16, 16, 16, 16, 1, 1, 1, 48, 1.0, 0, None, 0, 0, 0, None) == 5
+    assert f(1, 16, 24, 16, 16, 1, 1, 1, 64, 1.0, 0, None, 0, 0, 0, None) == 6
+    assert f(1, 16, 16, 16, 16, 1, 1, 3, 64, 1.0, 0, 16, 2, 64, 0, None) == 4     # 2 mask rows do not divide 3
     lib.bsa_layout_build.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int] + \
         [ctypes.c_void_p] * 6
     g = lib.bsa_layout_build

@@ -202,7 +202,7 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     w = WORKLOAD
-    z = w["batch"] * w["heads"]
+    z = args.slices or w["batch"] * w["heads"]
     block, seq, dim, scale = w["block"], w["seq"], w["head_dim"], w["scale"]
     pattern = workload_pattern()
     lay = SparseLayout(pattern, block=block, device=dev)
@@ -318,7 +318,8 @@ def run_ours(args):
             "metric": METRIC, "value": round(value, 3), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": w["name"], "batch_per_gpu": w["batch"], "heads": w["heads"], "seq": seq,
+            "config": {"workload": w["name"] + ("" if z == w["batch"] * w["heads"] else "_REDUCED_%d_slices" % z),
+                       "batch_per_gpu": w["batch"], "heads": w["heads"], "slices_per_gpu": z, "seq": seq,
                        "head_dim": dim, "block": block, "nnz_blocks_per_head": nnz,
                        "layout": "strided(8)+local(2), non-causal", "parallelism": "head-sharded x%d" % world,
                        "l2": "no flush: the four sparse tensors of a step are 400 MB each, above the 126 MB L2"},
@@ -349,6 +350,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--slices", type=int, default=0,
+                    help="(batch*head) slices per GPU; default is the workload's 64. A smaller value is a reduced "
+                         "case for profiler captures, not a benchmark result")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -13,18 +13,28 @@
 // coordinates).  A persistent CTA per SM walks work items; an item is one
 // group of the layout (a block row or block column) of one batch entry:
 //   sdd  item = block row r.  Its blocks are taken two at a time; a pair is
-//        one accumulation: A = rows r of op(A), B0/B1 = rows c0/c1 of op(B)^T,
-//        K-steps over the dense inner size.  Output: the pair's two blocks.
+//        one accumulation: A = rows r of op(A), B0|B1 = rows c0, c1 of op(B)^T
+//        (adjacent in shared memory, one N = 128 operand), K-steps over the
+//        dense inner size.  Output: the pair's two blocks.
 //   dsd  item = group m (and a 128-wide slice of N).  One accumulation over
-//        the group's blocks: A = the sparse block, B0/B1 = the k-block rows of
+//        the group's blocks: A = the sparse block, B0|B1 = the k-block rows of
 //        op(B).  Output: C[m*64.., slice].
-//   dds  item = group n (and a 128-tall slice of M).  One accumulation over
-//        the group's blocks: A0/A1 = op(A)[slice, k-block], B = the sparse
-//        block.  Output: C[slice, n*64..].
-// Warp roles: warp 0 = TMA producer (one lane), warp 1 = tcgen05.mma issuer
-// (one lane, also owns the TMEM allocation), warps 2-5 = epilogue
-// (tcgen05.ld -> fp16 -> swizzled shared tile -> TMA store).  Shared-memory
-// stages and the two TMEM accumulator buffers are handed over with mbarriers.
+//   dds  item = group n (and a 64-tall slice of M).  One accumulation over the
+//        group's blocks: A = op(A)[slice, k-block], B = the sparse block.
+//        Output: C[slice, n*64..].
+// Warp roles (10 warps):
+//   warp 0      TMA producer of the A tiles (lane 0 issues; arms the stage barrier)
+//   warp 1      TMA producer of the B tiles
+//   warps 2-5   tcgen05.mma issuers.  A single thread issues one MMA per ~150
+//               cycles whatever its shape, which is slower than these small
+//               MMAs execute, so the K = 64 of a stage is split over 4 (N = 64)
+//               or 2 (N = 128) issuers.  Each issuer owns a private partial
+//               accumulator in TMEM, so no ordering between issuers is needed.
+//   warps 6-9   epilogue: tcgen05.ld of the partials, sum, convert, swizzled
+//               shared tile, TMA store (up to 6 stores in flight).
+// Shared-memory stages and the two TMEM accumulator buffers are handed over
+// with mbarriers.  Group offsets and block descriptors are prefetched one to
+// two items ahead so no role waits on a dependent global load per step.
 // Every mbarrier wait is bounded: on a time-out the CTA records
 // BSA_ERR_DEVICE_TIMEOUT in the workspace word, stops issuing work, drains
 // what it has in flight, frees its TMEM and returns.
@@ -38,26 +48,40 @@ namespace {
 
 constexpr int kTile = 64;                       // tile edge in elements
 constexpr int kTileBytes = kTile * kTile * 2;   // 8 KB
-constexpr int kSlots = 3;                       // operand tiles per pipeline stage
-constexpr int kStages = 6;
-constexpr int kOutBufs = 2;                     // epilogue staging tiles
-constexpr int kAccCols = 128;                   // TMEM columns per accumulator buffer (two 64-wide tiles)
+constexpr int kMaxStages = 9;
+constexpr int kStageBytesTotal = 18 * kTileBytes;   // 144 KB of operand stages (9 x 2 or 6 x 3 tiles)
+constexpr int kOutBufs = 6;                     // epilogue staging tiles (TMA stores in flight)
+constexpr int kAccCols = 256;                   // TMEM columns per accumulator buffer (all partials)
 constexpr int kTmemCols = 2 * kAccCols;
-constexpr int kThreads = 192;
+constexpr int kMmaWarps = 4;
+constexpr int kFirstMmaWarp = 2;
+constexpr int kFirstEpilogueWarp = kFirstMmaWarp + kMmaWarps;
+constexpr int kThreads = (kFirstEpilogueWarp + 4) * 32;
 constexpr int kEpilogueThreads = 128;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // 2 s
 
+// Optional role timing (compile with -DBSA_TC_TIMING): CTA 0 adds the cycles each role spent in
+// its waits to 64-bit counters at byte offset 64 of the workspace.
+#ifdef BSA_TC_TIMING
+#define TC_TIME_DECL(name) long long name = 0
+#define TC_TIMED(name, stmt) { const long long tic_ = clock64(); stmt; name += clock64() - tic_; }
+#define TC_TIME_OUT(slot, name) if (blockIdx.x == 0) atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 8 + (slot), (unsigned long long)(name))
+#else
+#define TC_TIME_DECL(name)
+#define TC_TIMED(name, stmt) { stmt; }
+#define TC_TIME_OUT(slot, name)
+#endif
+
 struct __align__(8) Barriers {
-    uint64_t full[kStages];
-    uint64_t empty[kStages];
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
     uint64_t drain;
     uint32_t tmem_base;
     int abort_flag;
 };
-constexpr int kSmemBytes = 1024 /* alignment slack */ + kStages * kSlots * kTileBytes + kOutBufs * kTileBytes
-                           + (int)sizeof(Barriers);
+constexpr int kSmemBytes = 1024 /* alignment slack */ + kStageBytesTotal + kOutBufs * kTileBytes + (int)sizeof(Barriers);
 
 struct TcParams {
     const BlockDesc* blocks;
@@ -66,9 +90,12 @@ struct TcParams {
     int nnz, groups, batches;
     int size_m, size_n, size_k;
     int mode, trans_a, trans_b;
-    int chunks;              // dsd: 128-wide slices of N; dds: 128-tall slices of M; sdd: 1
-    long long items;
-    uint32_t idesc;
+    int chunks;              // dsd: 128-wide slices of N; dds: 64-tall slices of M; sdd: 1
+    int items;
+    int slots;               // operand tiles per stage: 2 (A + B) or 3 (A + B0 + B1)
+    int stages;              // pipeline depth
+    int issuers;             // MMA issuing warps in use: 4 (N = 64) or 2 (N up to 128)
+    uint32_t idesc64, idesc128;   // instruction descriptors for N = 64 and N = 128
 };
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -174,64 +201,107 @@ __device__ __forceinline__ bool epilogue_all(bool v) {
     return r != 0;
 }
 
-// Shared-memory matrix descriptor of one 64x64 16-bit tile stored as 64 rows
-// of 128 bytes with the 128-byte swizzle.  For a K-major operand a row is one
-// M/N index and the 8-row groups (1024 B apart, the stride byte offset) run
-// along M/N; for an MN-major operand a row is one K index and the 8-row
-// groups run along K.  The leading byte offset is unused (one swizzle atom
-// wide in both cases).  Bits: start address >> 4 in [0,14), LBO >> 4 in
-// [16,30), SBO >> 4 in [32,46), descriptor version 1 in [46,48), layout type
-// SWIZZLE_128B = 2 in [61,64).
-__device__ __forceinline__ uint64_t make_tile_desc(uint32_t smem_addr) {
+// Shared-memory matrix descriptor of a 16-bit operand made of 64x64 tiles, each stored as 64
+// rows of 128 bytes with the 128-byte swizzle.  For a K-major operand a row is one M/N index
+// and the 8-row groups (1024 B apart, the stride byte offset) run along M/N, so a second tile
+// placed right behind the first continues the operand to 128 rows.  For an MN-major operand a
+// row is one K index, the 8-row groups run along K, and the leading byte offset (8192 B) is
+// the distance to the tile holding M/N indices 64-127.
+// Bits: start address >> 4 in [0,14), LBO >> 4 in [16,30), SBO >> 4 in [32,46), descriptor
+// version 1 in [46,48), layout type SWIZZLE_128B = 2 in [61,64).
+__device__ __forceinline__ uint64_t make_tile_desc(uint32_t smem_addr, bool mn_major) {
     uint64_t d = (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(mn_major ? (kTileBytes >> 4) : 1) << 16;
     d |= (uint64_t)(1024 >> 4) << 32;
     d |= (uint64_t)1 << 46;
     d |= (uint64_t)2 << 61;
     return d;
 }
 
-struct Item {
-    int z, g, chunk;
-    int first, count;      // range of the group in `blocks`
+// Iterates the work items of one CTA (item = blockIdx.x + n * gridDim.x) and keeps the group
+// offset-table words of the next two items in flight, so that by the time an item becomes
+// current its words have arrived and no role stalls on a dependent global load per item.
+struct Cursor {
+    int item, stride, items, chunks, per_z;
+    const int32_t* table;
+    int z, g, chunk, first, count;      // current item: batch entry, group, slice, block range
+    int n1_a, n1_b, n2_a, n2_b;         // table[g], table[g + 1] of the next item and the one after
+
+    __device__ __forceinline__ void load_words(int it, int& a, int& b) const {
+        a = 0; b = 0;
+        if (it < items) { const int gg = (it % per_z) / chunks; a = table[gg]; b = table[gg + 1]; }
+    }
+    __device__ __forceinline__ void set_current(int a, int b) {
+        z = item / per_z;
+        const int rem = item - z * per_z;
+        g = rem / chunks;
+        chunk = rem - g * chunks;
+        first = a;
+        count = b - a;
+    }
+    __device__ __forceinline__ void init(const TcParams& p) {
+        item = (int)blockIdx.x; stride = (int)gridDim.x; items = p.items;
+        chunks = p.chunks; per_z = p.groups * p.chunks; table = p.table;
+        z = g = chunk = first = count = 0;
+        int a, b;
+        load_words(item, a, b);
+        load_words(item + stride, n1_a, n1_b);
+        load_words(item + 2 * stride, n2_a, n2_b);
+        if (item < items) set_current(a, b);
+    }
+    __device__ __forceinline__ bool valid() const { return item < items; }
+    __device__ __forceinline__ bool has_next() const { return item + stride < items; }
+    __device__ __forceinline__ int next_first() const { return n1_a; }
+    __device__ __forceinline__ int next_count() const { return n1_b - n1_a; }
+    __device__ __forceinline__ void advance() {
+        item += stride;
+        const int a = n1_a, b = n1_b;
+        n1_a = n2_a; n1_b = n2_b;
+        load_words(item + 2 * stride, n2_a, n2_b);
+        if (item < items) set_current(a, b);
+    }
 };
 
-__device__ __forceinline__ Item decode_item(const TcParams& p, long long item) {
-    Item it;
-    const long long per_z = (long long)p.groups * p.chunks;
-    it.z = (int)(item / per_z);
-    const int rem = (int)(item - (long long)it.z * per_z);
-    it.g = rem / p.chunks;
-    it.chunk = rem - it.g * p.chunks;
-    it.first = p.table[it.g];
-    it.count = p.table[it.g + 1] - it.first;
-    return it;
+// A warp-wide window of 32 block descriptors of the current group: lane l holds descriptor
+// base + l, the following 32 are already being loaded.  get() must be called by all 32 lanes
+// with the same, non-decreasing index.
+struct DescWindow {
+    BlockDesc mine, ahead;
+    __device__ __forceinline__ void begin(const BlockDesc& first_chunk) { mine = first_chunk; ahead = BlockDesc{0, 0}; }
+    __device__ __forceinline__ BlockDesc get(const BlockDesc* blocks, int first, int count, int i, int lane) {
+        if ((i & 31) == 0) {
+            if (i > 0) mine = ahead;
+            if (i + 32 + lane < count) ahead = blocks[first + i + 32 + lane];
+        }
+        BlockDesc d;
+        d.idx = __shfl_sync(0xffffffffu, mine.idx, i & 31);
+        d.packed = __shfl_sync(0xffffffffu, mine.packed, i & 31);
+        return d;
+    }
+};
+
+__device__ __forceinline__ BlockDesc load_first_chunk(const BlockDesc* blocks, int first, int count, int lane) {
+    BlockDesc d{0, 0};
+    if (lane < count) d = blocks[first + lane];
+    return d;
 }
 
-// Number of accumulations (each ends in an epilogue) and K-steps per
-// accumulation of an item.
-__device__ __forceinline__ void item_shape(const TcParams& p, const Item& it, int& flushes, int& ksteps) {
+// Number of accumulations (each ends in an epilogue) and K-steps per accumulation of an item.
+__device__ __forceinline__ void item_shape(const TcParams& p, int count, int& flushes, int& ksteps) {
     if (p.mode == BSA_MODE_SDD) {
-        flushes = (it.count + 1) >> 1;
+        flushes = (count + 1) >> 1;
         ksteps = (p.size_k + kTile - 1) / kTile;
     } else {
         flushes = 1;
-        ksteps = it.count;
+        ksteps = count;
     }
 }
 
-// Tiles of operand A and of operand B used by one accumulation.
-__device__ __forceinline__ void tile_counts(const TcParams& p, const Item& it, int flush, int& na, int& nb) {
-    if (p.mode == BSA_MODE_SDD) {
-        na = 1;
-        nb = min(2, it.count - 2 * flush);
-    } else if (p.mode == BSA_MODE_DSD) {
-        na = 1;
-        nb = min(2, (p.size_n - it.chunk * 2 * kTile + kTile - 1) / kTile);
-    } else {
-        na = min(2, (p.size_m - it.chunk * 2 * kTile + kTile - 1) / kTile);
-        nb = 1;
-    }
+// Number of B tiles (64 output columns each) of one accumulation; there is always one A tile.
+__device__ __forceinline__ int b_tiles(const TcParams& p, int count, int chunk, int flush) {
+    if (p.mode == BSA_MODE_SDD) return min(2, count - 2 * flush);
+    if (p.mode == BSA_MODE_DSD) return min(2, (p.size_n - chunk * 2 * kTile + kTile - 1) / kTile);
+    return 1;
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -239,21 +309,22 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                  const __grid_constant__ CUtensorMap map_c, const TcParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t* stage_base = smem;                                           // kStages * kSlots tiles
-    uint8_t* out_base = smem + kStages * kSlots * kTileBytes;             // kOutBufs tiles
+    uint8_t* stage_base = smem;                                   // p.stages * p.slots tiles
+    uint8_t* out_base = smem + kStageBytesTotal;                  // kOutBufs tiles
     Barriers* bars = reinterpret_cast<Barriers*>(out_base + kOutBufs * kTileBytes);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int stage_bytes = p.slots * kTileBytes;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
-        for (int s = 0; s < 2; ++s) { mbar_init(&bars->acc_full[s], 1); mbar_init(&bars->acc_empty[s], 4); }
-        mbar_init(&bars->drain, 1);
+        for (int s = 0; s < kMaxStages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], p.issuers); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&bars->acc_full[s], p.issuers); mbar_init(&bars->acc_empty[s], 4); }
+        mbar_init(&bars->drain, p.issuers);
         bars->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_shared();
     }
-    if (warp == 1) {
+    if (warp == kFirstMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(smem_u32(&bars->tmem_base)), "r"((uint32_t)kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -266,157 +337,238 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const bool a_mn_major = p.trans_a != 0;      // op(A) tile arrives with M contiguous
     const bool b_mn_major = p.trans_b == 0;      // op(B) tile arrives with N contiguous
 
-    if (warp == 0 && lane == 0) {
-        // ------------------------------------------------------------ TMA producer
+    if (warp < 2) {
+        // ------------------------------------------------------------ TMA producers
+        // Warp 0 loads the A tile of every stage and arms its barrier with the byte count of
+        // the whole stage; warp 1 loads the B tile(s).  All 32 lanes walk the items together
+        // (descriptor windows are warp-wide); lane 0 waits and issues.
+        const bool load_a = warp == 0;
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (long long item = blockIdx.x; ok && item < p.items; item += gridDim.x) {
-            const Item it = decode_item(p, item);
+        TC_TIME_DECL(t_wait); TC_TIME_DECL(t_issue); TC_TIME_DECL(t_all);
+#ifdef BSA_TC_TIMING
+        const long long t_begin = clock64();
+#endif
+        Cursor cur;
+        cur.init(p);
+        BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
+        while (ok && cur.valid()) {
+            BlockDesc pre_next{0, 0};
+            if (cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
             int flushes, ksteps;
-            item_shape(p, it, flushes, ksteps);
+            item_shape(p, cur.count, flushes, ksteps);
+            DescWindow win;
+            win.begin(pre);
             for (int f = 0; ok && f < flushes; ++f) {
-                int na, nb;
-                tile_counts(p, it, f, na, nb);
-                BlockDesc d0{}, d1{};
+                const int nb = b_tiles(p, cur.count, cur.chunk, f);
+                BlockDesc d0{0, 0}, d1{0, 0};
                 if (p.mode == BSA_MODE_SDD) {
-                    d0 = p.blocks[it.first + 2 * f];
-                    if (nb > 1) d1 = p.blocks[it.first + 2 * f + 1];
+                    d0 = win.get(p.blocks, cur.first, cur.count, 2 * f, lane);
+                    d1 = win.get(p.blocks, cur.first, cur.count, 2 * f + 1, lane);
                 }
-                for (int k = 0; k < ksteps; ++k) {
-                    if (!(ok = mbar_wait(&bars->empty[stage], phase ^ 1, bars, p.status))) break;
-                    uint8_t* slot = stage_base + stage * kSlots * kTileBytes;
-                    uint64_t* full = &bars->full[stage];
-                    mbar_expect_tx(full, (uint32_t)((na + nb) * kTileBytes));
-                    if (p.mode == BSA_MODE_SDD) {
-                        const int k0 = k * kTile, m0 = it.g * kTile;
-                        if (a_mn_major) tma_load_3d(slot, &map_a, full, m0, k0, it.z);
-                        else            tma_load_3d(slot, &map_a, full, k0, m0, it.z);
-                        for (int j = 0; j < nb; ++j) {
-                            const int n0 = (j == 0 ? d0.col() : d1.col()) * kTile;
-                            if (b_mn_major) tma_load_3d(slot + (1 + j) * kTileBytes, &map_b, full, n0, k0, it.z);
-                            else            tma_load_3d(slot + (1 + j) * kTileBytes, &map_b, full, k0, n0, it.z);
+                for (int k = 0; ok && k < ksteps; ++k) {
+                    BlockDesc d{0, 0};
+                    if (p.mode != BSA_MODE_SDD) d = win.get(p.blocks, cur.first, cur.count, k, lane);
+                    if (lane == 0) {
+                        TC_TIMED(t_wait, ok = mbar_wait(&bars->empty[stage], phase ^ 1, bars, p.status));
+#ifdef BSA_TC_TIMING
+                        const long long tic_issue = clock64();
+#endif
+                        if (ok) {
+                            uint8_t* slot = stage_base + stage * stage_bytes;
+                            uint64_t* full = &bars->full[stage];
+                            if (load_a) mbar_expect_tx(full, (uint32_t)((1 + nb) * kTileBytes));
+                            if (p.mode == BSA_MODE_SDD) {
+                                const int k0 = k * kTile, m0 = cur.g * kTile;
+                                if (load_a) {
+                                    if (a_mn_major) tma_load_3d(slot, &map_a, full, m0, k0, cur.z);
+                                    else            tma_load_3d(slot, &map_a, full, k0, m0, cur.z);
+                                } else {
+                                    for (int j = 0; j < nb; ++j) {
+                                        const int n0 = (j == 0 ? d0.col() : d1.col()) * kTile;
+                                        if (b_mn_major) tma_load_3d(slot + (1 + j) * kTileBytes, &map_b, full, n0, k0, cur.z);
+                                        else            tma_load_3d(slot + (1 + j) * kTileBytes, &map_b, full, k0, n0, cur.z);
+                                    }
+                                }
+                            } else if (p.mode == BSA_MODE_DSD) {
+                                const int k0 = (p.trans_a ? d.row() : d.col()) * kTile;
+                                if (load_a) {
+                                    tma_load_3d(slot, &map_a, full, 0, d.idx * kTile, cur.z);
+                                } else {
+                                    for (int j = 0; j < nb; ++j) {
+                                        const int n0 = (cur.chunk * 2 + j) * kTile;
+                                        if (b_mn_major) tma_load_3d(slot + (1 + j) * kTileBytes, &map_b, full, n0, k0, cur.z);
+                                        else            tma_load_3d(slot + (1 + j) * kTileBytes, &map_b, full, k0, n0, cur.z);
+                                    }
+                                }
+                            } else {
+                                const int k0 = (p.trans_b ? d.col() : d.row()) * kTile;
+                                if (load_a) {
+                                    const int m0 = cur.chunk * kTile;
+                                    if (a_mn_major) tma_load_3d(slot, &map_a, full, m0, k0, cur.z);
+                                    else            tma_load_3d(slot, &map_a, full, k0, m0, cur.z);
+                                } else {
+                                    tma_load_3d(slot + kTileBytes, &map_b, full, 0, d.idx * kTile, cur.z);
+                                }
+                            }
                         }
-                    } else if (p.mode == BSA_MODE_DSD) {
-                        const BlockDesc d = p.blocks[it.first + k];
-                        const int k0 = (p.trans_a ? d.row() : d.col()) * kTile;
-                        tma_load_3d(slot, &map_a, full, 0, d.idx * kTile, it.z);
-                        for (int j = 0; j < nb; ++j) {
-                            const int n0 = (it.chunk * 2 + j) * kTile;
-                            if (b_mn_major) tma_load_3d(slot + (1 + j) * kTileBytes, &map_b, full, n0, k0, it.z);
-                            else            tma_load_3d(slot + (1 + j) * kTileBytes, &map_b, full, k0, n0, it.z);
-                        }
-                    } else {
-                        const BlockDesc d = p.blocks[it.first + k];
-                        const int k0 = (p.trans_b ? d.col() : d.row()) * kTile;
-                        for (int i = 0; i < na; ++i) {
-                            const int m0 = (it.chunk * 2 + i) * kTile;
-                            if (a_mn_major) tma_load_3d(slot + i * kTileBytes, &map_a, full, m0, k0, it.z);
-                            else            tma_load_3d(slot + i * kTileBytes, &map_a, full, k0, m0, it.z);
-                        }
-                        tma_load_3d(slot + 2 * kTileBytes, &map_b, full, 0, d.idx * kTile, it.z);
+#ifdef BSA_TC_TIMING
+                        t_issue += clock64() - tic_issue;
+#endif
                     }
-                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                    ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+                    if (++stage == p.stages) { stage = 0; phase ^= 1; }
                 }
             }
+            pre = pre_next;
+            cur.advance();
         }
-        if (!ok) {
-            // Give loads that were issued a bounded chance to land before the CTA exits.
+#ifdef BSA_TC_TIMING
+        t_all = clock64() - t_begin;
+        if (lane == 0) { TC_TIME_OUT(warp * 3 + 0, t_all); TC_TIME_OUT(warp * 3 + 1, t_wait); TC_TIME_OUT(warp * 3 + 2, t_issue); }
+#endif
+        if (!ok && lane == 0) {
+            // Give copies that were issued a bounded chance to land before the CTA exits.
             const unsigned long long t0 = global_ns();
-            for (int s = 0; s < kStages; ++s)
+            for (int s = 0; s < p.stages; ++s)
                 while (!mbar_try_wait(&bars->full[s], 0) && !mbar_try_wait(&bars->full[s], 1) &&
                        global_ns() - t0 < kWaitLimitNs / 4) {}
         }
-    } else if (warp == 1 && lane == 0) {
-        // ------------------------------------------------------------ MMA issuer
-        int stage = 0, acc = 0;
-        uint32_t phase = 0, acc_phase = 0;
-        bool ok = true;
-        const uint32_t a_kstep = a_mn_major ? 2048u >> 4 : 32u >> 4;   // descriptor advance per K = 16
-        const uint32_t b_kstep = b_mn_major ? 2048u >> 4 : 32u >> 4;
-        for (long long item = blockIdx.x; ok && item < p.items; item += gridDim.x) {
-            const Item it = decode_item(p, item);
-            int flushes, ksteps;
-            item_shape(p, it, flushes, ksteps);
-            if (ksteps == 0) continue;          // empty group: the epilogue writes zeros on its own
-            for (int f = 0; ok && f < flushes; ++f) {
-                int na, nb;
-                tile_counts(p, it, f, na, nb);
-                if (!(ok = mbar_wait(&bars->acc_empty[acc], acc_phase ^ 1, bars, p.status))) break;
-                tc_fence_after();
-                const uint32_t d_base = tmem_base + (uint32_t)(acc * kAccCols);
-                for (int k = 0; k < ksteps; ++k) {
-                    if (!(ok = mbar_wait(&bars->full[stage], phase, bars, p.status))) break;
+        __syncwarp();
+    } else if (warp < kFirstEpilogueWarp) {
+        // ------------------------------------------------------------ MMA issuers
+        const int w = warp - kFirstMmaWarp;
+        if (lane == 0 && w < p.issuers) {
+            int stage = 0, acc = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            bool ok = true;
+            const uint32_t a_kstep = a_mn_major ? 2048u >> 4 : 32u >> 4;   // descriptor advance per K = 16
+            const uint32_t b_kstep = b_mn_major ? 2048u >> 4 : 32u >> 4;
+            const int kk_per_issuer = (kTile / 16) / p.issuers;            // 1 or 2 K = 16 slices of each stage
+            // private partial accumulator of this issuer inside an accumulator buffer
+            const uint32_t part_col = (uint32_t)(w * (kAccCols / p.issuers));
+            TC_TIME_DECL(t_full); TC_TIME_DECL(t_acc); TC_TIME_DECL(t_all);
+#ifdef BSA_TC_TIMING
+            const long long t_begin = clock64();
+#endif
+            Cursor cur;
+            cur.init(p);
+            for (; ok && cur.valid(); cur.advance()) {
+                int flushes, ksteps;
+                item_shape(p, cur.count, flushes, ksteps);
+                if (ksteps == 0) continue;          // empty group: the epilogue writes zeros on its own
+                for (int f = 0; ok && f < flushes; ++f) {
+                    const int nb = b_tiles(p, cur.count, cur.chunk, f);
+                    const uint32_t idesc = nb == 2 ? p.idesc128 : p.idesc64;
+                    TC_TIMED(t_acc, ok = mbar_wait(&bars->acc_empty[acc], acc_phase ^ 1, bars, p.status));
+                    if (!ok) break;
                     tc_fence_after();
-                    const uint32_t slot = smem_u32(stage_base + stage * kSlots * kTileBytes);
-                    const int b_first = (p.mode == BSA_MODE_DDS) ? 2 : 1;
-                    for (int i = 0; i < na; ++i) {
-                        const uint64_t da = make_tile_desc(slot + i * kTileBytes);
-                        for (int j = 0; j < nb; ++j) {
-                            const uint64_t db = make_tile_desc(slot + (b_first + j) * kTileBytes);
-                            const uint32_t d = d_base + (uint32_t)((i * nb + j) * kTile);
-#pragma unroll
-                            for (int kk = 0; kk < kTile / 16; ++kk)
-                                tc_mma_f16(d, da + (uint64_t)(kk * a_kstep), db + (uint64_t)(kk * b_kstep), p.idesc,
-                                           (k > 0 || kk > 0) ? 1u : 0u);
+                    const uint32_t d = tmem_base + (uint32_t)(acc * kAccCols) + part_col;
+                    for (int k = 0; k < ksteps; ++k) {
+                        TC_TIMED(t_full, ok = mbar_wait(&bars->full[stage], phase, bars, p.status));
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t slot = smem_u32(stage_base + stage * stage_bytes);
+                        const uint64_t da = make_tile_desc(slot, a_mn_major);
+                        const uint64_t db = make_tile_desc(slot + kTileBytes, b_mn_major);
+                        for (int s = 0; s < kk_per_issuer; ++s) {
+                            const int kk = w + s * p.issuers;
+                            tc_mma_f16(d, da + (uint64_t)(kk * a_kstep), db + (uint64_t)(kk * b_kstep), idesc,
+                                       (k > 0 || s > 0) ? 1u : 0u);
                         }
+                        tc_commit(&bars->empty[stage]);      // this issuer's reads of the stage are done
+                        if (++stage == p.stages) { stage = 0; phase ^= 1; }
                     }
-                    tc_commit(&bars->empty[stage]);      // frees the stage once these MMAs have read it
-                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                    if (!ok) break;
+                    tc_commit(&bars->acc_full[acc]);         // this issuer's partial is complete
+                    if (++acc == 2) { acc = 0; acc_phase ^= 1; }
                 }
-                if (!ok) break;
-                tc_commit(&bars->acc_full[acc]);         // accumulator complete
-                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
             }
+            // All MMAs issued by this thread must have retired before TMEM is freed.
+            tc_commit(&bars->drain);
+            mbar_wait(&bars->drain, 0, bars, p.status);
+#ifdef BSA_TC_TIMING
+            t_all = clock64() - t_begin;
+            if (w == 0) { TC_TIME_OUT(6, t_all); TC_TIME_OUT(7, t_full); TC_TIME_OUT(8, t_acc); }
+#endif
         }
-        // All MMAs issued by this thread must have retired before TMEM is freed.
-        tc_commit(&bars->drain);
-        mbar_wait(&bars->drain, 0, bars, p.status);
-    } else if (warp >= 2) {
+        __syncwarp();
+    } else {
         // ------------------------------------------------------------ epilogue
         const int quad = warp & 3;                   // TMEM sub-partition this warp may read
-        const int et = threadIdx.x - 64;             // 0..127 among the epilogue threads
+        const int et = threadIdx.x - kFirstEpilogueWarp * 32;   // 0..127 among the epilogue threads
         const int row = quad * 16 + lane;            // accumulator row held by this lane (lanes 0-15 only)
         const bool row_lane = lane < 16;
+        const bool is_sdd = p.mode == BSA_MODE_SDD;
+        const bool bf16_out = (p.idesc64 & (1u << 7)) != 0;
+        const int part_stride = kAccCols / p.issuers;
         int acc = 0, out_buf = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
-        for (long long item = blockIdx.x; ok && item < p.items; item += gridDim.x) {
-            const Item it = decode_item(p, item);
+        TC_TIME_DECL(t_accf); TC_TIME_DECL(t_ld); TC_TIME_DECL(t_store); TC_TIME_DECL(t_write); TC_TIME_DECL(t_all);
+#ifdef BSA_TC_TIMING
+        const long long t_begin = clock64();
+#endif
+        Cursor cur;
+        cur.init(p);
+        BlockDesc pre{0, 0};
+        if (is_sdd && cur.valid()) pre = load_first_chunk(p.blocks, cur.first, cur.count, lane);
+        while (ok && cur.valid()) {
+            BlockDesc pre_next{0, 0};
+            if (is_sdd && cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
             int flushes, ksteps;
-            item_shape(p, it, flushes, ksteps);
-            if (p.mode == BSA_MODE_SDD && it.count == 0) continue;
+            item_shape(p, cur.count, flushes, ksteps);
+            DescWindow win;
+            win.begin(pre);
             for (int f = 0; ok && f < flushes; ++f) {
-                int na, nb;
-                tile_counts(p, it, f, na, nb);
+                const int tiles = b_tiles(p, cur.count, cur.chunk, f);
                 const bool have_acc = ksteps > 0;
                 if (have_acc) {
-                    ok = epilogue_all(mbar_wait(&bars->acc_full[acc], acc_phase, bars, p.status));
+                    TC_TIMED(t_accf, ok = epilogue_all(mbar_wait(&bars->acc_full[acc], acc_phase, bars, p.status)));
                     if (!ok) break;
                     tc_fence_after();
                 }
-                const int tiles = na * nb;
                 for (int t = 0; t < tiles; ++t) {
-                    uint32_t v[2][32];
+                    int out_idx = 0;
+                    if (is_sdd) out_idx = win.get(p.blocks, cur.first, cur.count, 2 * f + t, lane).idx;
+                    float v[kTile];
+#pragma unroll
+                    for (int c = 0; c < kTile; ++c) v[c] = 0.f;
+#ifdef BSA_TC_TIMING
+                    const long long tic_ld = clock64();
+#endif
                     if (have_acc) {
                         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16)
                                                + (uint32_t)(acc * kAccCols + t * kTile);
-                        tc_ld_32x32b_x32(taddr, v[0]);
-                        tc_ld_32x32b_x32(taddr + 32, v[1]);
-                        tc_wait_ld();
-                    } else {
+                        for (int part = 0; part < p.issuers; ++part) {
 #pragma unroll
-                        for (int c = 0; c < 32; ++c) { v[0][c] = 0u; v[1][c] = 0u; }
+                            for (int h = 0; h < 2; ++h) {
+                                uint32_t r[32];
+                                tc_ld_32x32b_x32(taddr + (uint32_t)(part * part_stride + h * 32), r);
+                                tc_wait_ld();
+#pragma unroll
+                                for (int c = 0; c < 32; ++c) v[h * 32 + c] += __uint_as_float(r[c]);
+                            }
+                        }
                     }
                     if (have_acc && t == tiles - 1) {
-                        // accumulator fully read: hand the TMEM buffer back to the MMA warp
+                        // accumulator fully read: hand the TMEM buffer back to the MMA warps
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&bars->acc_empty[acc]);
                     }
-                    // staging buffer `out_buf` was last read by the store issued two tiles ago
+#ifdef BSA_TC_TIMING
+                    t_ld += clock64() - tic_ld;
+                    const long long tic_st = clock64();
+#endif
+                    // staging tile `out_buf` was last read by the store issued kOutBufs tiles ago
                     if (et == 0) tma_store_wait_read<kOutBufs - 1>();
                     asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
+#ifdef BSA_TC_TIMING
+                    t_store += clock64() - tic_st;
+                    const long long tic_wr = clock64();
+#endif
                     uint8_t* out = out_base + out_buf * kTileBytes;
                     if (row_lane) {
 #pragma unroll
@@ -424,10 +576,8 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                             uint32_t packed[4];
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
-                                const int col = c * 8 + e * 2;
-                                const float lo = __uint_as_float(v[col >> 5][col & 31]);
-                                const float hi = __uint_as_float(v[(col + 1) >> 5][(col + 1) & 31]);
-                                if (p.idesc & (1u << 7)) {       // bf16 operands -> bf16 output
+                                const float lo = v[c * 8 + e * 2], hi = v[c * 8 + e * 2 + 1];
+                                if (bf16_out) {
                                     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
                                     packed[e] = *reinterpret_cast<uint32_t*>(&h);
                                 } else {
@@ -442,28 +592,36 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     fence_async_shared();
                     asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
                     if (et == 0) {
-                        if (p.mode == BSA_MODE_SDD) {
-                            const BlockDesc d = p.blocks[it.first + 2 * f + t];
-                            tma_store_3d(&map_c, out, 0, d.idx * kTile, it.z);
+                        if (is_sdd) {
+                            tma_store_3d(&map_c, out, 0, out_idx * kTile, cur.z);
                         } else if (p.mode == BSA_MODE_DSD) {
-                            tma_store_3d(&map_c, out, (it.chunk * 2 + t) * kTile, it.g * kTile, it.z);
+                            tma_store_3d(&map_c, out, (cur.chunk * 2 + t) * kTile, cur.g * kTile, cur.z);
                         } else {
-                            tma_store_3d(&map_c, out, it.g * kTile, (it.chunk * 2 + t) * kTile, it.z);
+                            tma_store_3d(&map_c, out, cur.g * kTile, cur.chunk * kTile, cur.z);
                         }
                         tma_store_commit();
                     }
-                    out_buf ^= 1;
+                    if (++out_buf == kOutBufs) out_buf = 0;
+#ifdef BSA_TC_TIMING
+                    t_write += clock64() - tic_wr;
+#endif
                 }
                 if (have_acc && ++acc == 2) { acc = 0; acc_phase ^= 1; }
             }
+            pre = pre_next;
+            cur.advance();
         }
         if (et == 0) tma_store_wait_all();
+#ifdef BSA_TC_TIMING
+        t_all = clock64() - t_begin;
+        if (et == 0) { TC_TIME_OUT(9, t_all); TC_TIME_OUT(10, t_accf); TC_TIME_OUT(11, t_ld); TC_TIME_OUT(12, t_store); TC_TIME_OUT(13, t_write); }
+#endif
     }
 
     // ---------------------------------------------------------------- teardown
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == kFirstMmaWarp) {
         __syncwarp();
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols)
@@ -518,6 +676,12 @@ int sm_count() {
 
 bool dense_dim_ok(int64_t v) { return v >= kTile && v % 8 == 0 && v < ((int64_t)1 << 31); }
 
+int64_t slices_of(const MatmulArgs& g) {
+    if (g.mode == BSA_MODE_DSD) return (g.size_n + 2 * kTile - 1) / (2 * kTile);
+    if (g.mode == BSA_MODE_DDS) return (g.size_m + kTile - 1) / kTile;
+    return 1;
+}
+
 }  // namespace
 
 bool tc_supports(const MatmulArgs& g) {
@@ -525,6 +689,8 @@ bool tc_supports(const MatmulArgs& g) {
     if (g.block != kTile) return false;
     if (g.nnz <= 0 || g.nnz * kTile >= ((int64_t)1 << 31) || g.batches > 65535) return false;
     if (!dense_dim_ok(g.size_m) || !dense_dim_ok(g.size_n) || !dense_dim_ok(g.size_k)) return false;
+    // work items are indexed with 32-bit integers
+    if (g.batches * g.groups * slices_of(g) >= ((int64_t)1 << 30)) return false;
     return true;
 }
 
@@ -562,14 +728,19 @@ int matmul_tc(const MatmulArgs& g) {
     p.nnz = (int)g.nnz; p.groups = (int)g.groups; p.batches = (int)g.batches;
     p.size_m = (int)g.size_m; p.size_n = (int)g.size_n; p.size_k = (int)g.size_k;
     p.mode = g.mode; p.trans_a = g.trans_a; p.trans_b = g.trans_b;
-    p.chunks = 1;
-    if (g.mode == BSA_MODE_DSD) p.chunks = (int)((g.size_n + 2 * kTile - 1) / (2 * kTile));
-    if (g.mode == BSA_MODE_DDS) p.chunks = (int)((g.size_m + 2 * kTile - 1) / (2 * kTile));
-    p.items = (long long)g.batches * g.groups * p.chunks;
-    // instruction descriptor: fp32 accumulate, fp16 / bf16 operands, M = 64, N = 64
+    p.chunks = (int)slices_of(g);
+    p.items = (int)(g.batches * g.groups * p.chunks);
+    // two B tiles per stage (N = 128, two issuers) for sdd pairs and for dsd with more than 64 columns
+    const bool wide = g.mode == BSA_MODE_SDD || (g.mode == BSA_MODE_DSD && g.size_n > kTile);
+    p.slots = wide ? 3 : 2;
+    p.stages = kStageBytesTotal / (p.slots * kTileBytes);
+    p.issuers = wide ? 2 : 4;
+    // instruction descriptor: fp32 accumulate, fp16 / bf16 operands, M = 64, N = 64 or 128
     const uint32_t fmt = g.dtype == BSA_DTYPE_BF16 ? 1u : 0u;
-    p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((g.trans_a ? 1u : 0u) << 15) | ((g.trans_b ? 0u : 1u) << 16)
-              | ((uint32_t)(kTile >> 3) << 17) | ((uint32_t)(kTile >> 4) << 24);
+    const uint32_t common = (1u << 4) | (fmt << 7) | (fmt << 10) | ((g.trans_a ? 1u : 0u) << 15)
+                            | ((g.trans_b ? 0u : 1u) << 16) | ((uint32_t)(kTile >> 4) << 24);
+    p.idesc64 = common | ((uint32_t)(kTile >> 3) << 17);
+    p.idesc128 = common | ((uint32_t)(2 * kTile >> 3) << 17);
 
     const int sms = sm_count();
     if (sms <= 0) return BSA_ERR_LAUNCH;

@@ -141,7 +141,7 @@ extern "C" int bsa_workspace_status(void* workspace, void* stream) {
     if (cudaMemcpyAsync(&word, workspace, sizeof(word), cudaMemcpyDeviceToHost, s) != cudaSuccess) return BSA_ERR_LAUNCH;
     if (cudaStreamSynchronize(s) != cudaSuccess) return BSA_ERR_LAUNCH;
     if (word == 0) return BSA_OK;
-    if (cudaMemsetAsync(workspace, 0, sizeof(word), s) != cudaSuccess) return BSA_ERR_LAUNCH;
+    if (cudaMemsetAsync(workspace, 0, 2 * sizeof(word), s) != cudaSuccess) return BSA_ERR_LAUNCH;
     if (cudaStreamSynchronize(s) != cudaSuccess) return BSA_ERR_LAUNCH;
-    return BSA_ERR_DEVICE_TIMEOUT;
+    return word == (uint32_t)BSA_ERR_BAD_SHAPE ? BSA_ERR_BAD_SHAPE : BSA_ERR_DEVICE_TIMEOUT;
 }

@@ -12,26 +12,32 @@
 // major-ness (so trans_a / trans_b only flip descriptor bits and swap two TMA
 // coordinates).  A persistent CTA per SM walks work items; an item is one
 // group of the layout (a block row or block column) of one batch entry:
-//   sdd  item = block row r.  Its blocks are taken two at a time; a pair is
-//        one accumulation: A = rows r of op(A), B0|B1 = rows c0, c1 of op(B)^T
-//        (adjacent in shared memory, one N = 128 operand), K-steps over the
-//        dense inner size.  Output: the pair's two blocks.
+//   sdd  item = block row r.  Its blocks are taken four at a time; such a
+//        quad is one accumulation: A = rows r of op(A), B0..B3 = rows c0..c3 of
+//        op(B)^T placed back to back in shared memory (one N = 256 operand),
+//        K-steps over the dense inner size.  Output: the quad's four blocks.
 //   dsd  item = group m (and a 128-wide slice of N).  One accumulation over
 //        the group's blocks: A = the sparse block, B0|B1 = the k-block rows of
 //        op(B).  Output: C[m*64.., slice].
 //   dds  item = group n (and a 64-tall slice of M).  One accumulation over the
 //        group's blocks: A = op(A)[slice, k-block], B = the sparse block.
 //        Output: C[slice, n*64..].
-// Warp roles (10 warps):
-//   warp 0      TMA producer of the A tiles (lane 0 issues; arms the stage barrier)
-//   warp 1      TMA producer of the B tiles
-//   warps 2-5   tcgen05.mma issuers.  A single thread issues one MMA per ~150
-//               cycles whatever its shape, which is slower than these small
-//               MMAs execute, so the K = 64 of a stage is split over 4 (N = 64)
-//               or 2 (N = 128) issuers.  Each issuer owns a private partial
-//               accumulator in TMEM, so no ordering between issuers is needed.
-//   warps 6-9   epilogue: tcgen05.ld of the partials, sum, convert, swizzled
-//               shared tile, TMA store (up to 6 stores in flight).
+// Measured on B200: one thread issues a tcgen05.mma or a TMA copy only every
+// 150-300 cycles whatever its size, a 64x64x16 MMA executes in ~32 cycles and
+// 8 KB boxes need about four issuing threads to saturate the L2 -> SM path.
+// Hence the warp roles (16 warps):
+//   warps 0-3   TMA producers; K-step n of the CTA belongs to producer n % 4,
+//               which loads all of its tiles (lane 0 issues).
+//   warps 4-7   tcgen05.mma issuers (lane 0).  sdd: issuer b owns accumulator
+//               buffer b and issues every second quad (N up to 256, no sharing).
+//               dsd / dds: the K = 64 of a stage is split over 4 (N = 64) or 2
+//               (N = 128) issuers, each with a private partial accumulator, so
+//               no ordering between issuers is needed; the epilogue adds them.
+//   warps 8-15  two epilogue warpgroups; group b drains accumulator buffer b:
+//               tcgen05.ld, (sum of partials), convert, and 256-bit global
+//               stores straight from registers: every lane owns a whole 128-byte
+//               output row, so no shared-memory staging or block-level
+//               synchronisation is needed and the warps run independently.
 // Shared-memory stages and the two TMEM accumulator buffers are handed over
 // with mbarriers.  Group offsets and block descriptors are prefetched one to
 // two items ahead so no role waits on a dependent global load per step.
@@ -48,28 +54,25 @@ namespace {
 
 constexpr int kTile = 64;                       // tile edge in elements
 constexpr int kTileBytes = kTile * kTile * 2;   // 8 KB
-constexpr int kMaxStages = 9;
-constexpr int kStageBytesTotal = 18 * kTileBytes;   // 144 KB of operand stages (9 x 2 or 6 x 3 tiles)
-constexpr int kOutBufs = 6;                     // epilogue staging tiles (TMA stores in flight)
-constexpr int kAccCols = 256;                   // TMEM columns per accumulator buffer (all partials)
+constexpr int kMaxStages = 13;
+constexpr int kStageTiles = 27;                 // operand tiles in all stages: 13 x 2, 9 x 3 or 5 x 5
+constexpr int kAccCols = 256;                   // TMEM columns per accumulator buffer
 constexpr int kTmemCols = 2 * kAccCols;
+constexpr int kProducerWarps = 4;
 constexpr int kMmaWarps = 4;
-constexpr int kFirstMmaWarp = 2;
+constexpr int kFirstMmaWarp = kProducerWarps;
 constexpr int kFirstEpilogueWarp = kFirstMmaWarp + kMmaWarps;
-constexpr int kThreads = (kFirstEpilogueWarp + 4) * 32;
-constexpr int kEpilogueThreads = 128;
+constexpr int kThreads = (kFirstEpilogueWarp + 8) * 32;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // 2 s
 
 // Optional role timing (compile with -DBSA_TC_TIMING): CTA 0 adds the cycles each role spent in
-// its waits to 64-bit counters at byte offset 64 of the workspace.
+// its waits to 64-bit counters at byte offset 64 of the workspace (slot = counter index).
 #ifdef BSA_TC_TIMING
-#define TC_TIME_DECL(name) long long name = 0
-#define TC_TIMED(name, stmt) { const long long tic_ = clock64(); stmt; name += clock64() - tic_; }
-#define TC_TIME_OUT(slot, name) if (blockIdx.x == 0) atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 8 + (slot), (unsigned long long)(name))
+#define TC_CLOCK() clock64()
+#define TC_TIME_OUT(slot, cycles) do { if (blockIdx.x == 0) atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 8 + (slot), (unsigned long long)(cycles)); } while (0)
 #else
-#define TC_TIME_DECL(name)
-#define TC_TIMED(name, stmt) { stmt; }
-#define TC_TIME_OUT(slot, name)
+#define TC_CLOCK() 0ll
+#define TC_TIME_OUT(slot, cycles) do { } while (0)
 #endif
 
 struct __align__(8) Barriers {
@@ -81,7 +84,7 @@ struct __align__(8) Barriers {
     uint32_t tmem_base;
     int abort_flag;
 };
-constexpr int kSmemBytes = 1024 /* alignment slack */ + kStageBytesTotal + kOutBufs * kTileBytes + (int)sizeof(Barriers);
+constexpr int kSmemBytes = 1024 /* alignment slack */ + kStageTiles * kTileBytes + (int)sizeof(Barriers);
 
 struct TcParams {
     const BlockDesc* blocks;
@@ -92,10 +95,14 @@ struct TcParams {
     int mode, trans_a, trans_b;
     int chunks;              // dsd: 128-wide slices of N; dds: 64-tall slices of M; sdd: 1
     int items;
-    int slots;               // operand tiles per stage: 2 (A + B) or 3 (A + B0 + B1)
+    int nb_max;              // B tiles per stage: sdd 4, dsd 1 or 2, dds 1
     int stages;              // pipeline depth
-    int issuers;             // MMA issuing warps in use: 4 (N = 64) or 2 (N up to 128)
-    uint32_t idesc64, idesc128;   // instruction descriptors for N = 64 and N = 128
+    int issuers;             // MMA issuing warps in use
+    uint32_t idesc;          // instruction descriptor without the N field
+    uint16_t* c;             // output (16-bit elements)
+    int ldc;                 // elements between output rows
+    int c_vec8;              // rows start on 32-byte boundaries: 256-bit stores are legal
+    long long c_elems;       // elements in the output (bounds check of every store)
 };
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -150,15 +157,6 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, u
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
-__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* src, int c0, int c1, int c2) {
-    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
-                 ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2) : "memory");
-}
-__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void tma_store_wait_read() {
-    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -186,27 +184,35 @@ __device__ __forceinline__ void tc_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[3
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr) : "memory");
 }
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// AND-vote over the 128 epilogue threads (named barrier 2), so that giving up on a wait is a
-// decision all of them take together and none is left alone at a later named barrier.
-__device__ __forceinline__ bool epilogue_all(bool v) {
-    uint32_t r;
+__device__ __forceinline__ void tc_ld_32x32b_x64(uint32_t taddr, uint32_t (&r)[64]) {
     asm volatile(
-        "{\n\t.reg .pred p, q;\n\t"
-        "setp.ne.u32 q, %1, 0;\n\t"
-        "bar.red.and.pred p, 2, %2, q;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(r) : "r"((uint32_t)v), "n"(kEpilogueThreads) : "memory");
-    return r != 0;
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+        "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+        "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]),
+          "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]),
+          "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]),
+          "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]),
+          "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t (&w)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
 }
 
 // Shared-memory matrix descriptor of a 16-bit operand made of 64x64 tiles, each stored as 64
 // rows of 128 bytes with the 128-byte swizzle.  For a K-major operand a row is one M/N index
-// and the 8-row groups (1024 B apart, the stride byte offset) run along M/N, so a second tile
-// placed right behind the first continues the operand to 128 rows.  For an MN-major operand a
-// row is one K index, the 8-row groups run along K, and the leading byte offset (8192 B) is
-// the distance to the tile holding M/N indices 64-127.
+// and the 8-row groups (1024 B apart, the stride byte offset) run along M/N, so tiles placed
+// back to back continue the operand to 128, 192, 256 rows.  For an MN-major operand a row is
+// one K index, the 8-row groups run along K, and the leading byte offset (8192 B) is the
+// distance between tiles holding consecutive 64-wide ranges of M/N.
 // Bits: start address >> 4 in [0,14), LBO >> 4 in [16,30), SBO >> 4 in [32,46), descriptor
 // version 1 in [46,48), layout type SWIZZLE_128B = 2 in [61,64).
 __device__ __forceinline__ uint64_t make_tile_desc(uint32_t smem_addr, bool mn_major) {
@@ -263,19 +269,27 @@ struct Cursor {
 };
 
 // A warp-wide window of 32 block descriptors of the current group: lane l holds descriptor
-// base + l, the following 32 are already being loaded.  get() must be called by all 32 lanes
-// with the same, non-decreasing index.
+// base + l and the following 32 are already being loaded.  get() must be called by all 32
+// lanes with the same index, in non-decreasing order; indices may be skipped.
 struct DescWindow {
     BlockDesc mine, ahead;
-    __device__ __forceinline__ void begin(const BlockDesc& first_chunk) { mine = first_chunk; ahead = BlockDesc{0, 0}; }
+    int base;
+    __device__ __forceinline__ void begin(const BlockDesc* blocks, int first, int count, const BlockDesc& first_chunk,
+                                          int lane) {
+        mine = first_chunk;
+        base = 0;
+        ahead = BlockDesc{0, 0};
+        if (32 + lane < count) ahead = blocks[first + 32 + lane];
+    }
     __device__ __forceinline__ BlockDesc get(const BlockDesc* blocks, int first, int count, int i, int lane) {
-        if ((i & 31) == 0) {
-            if (i > 0) mine = ahead;
-            if (i + 32 + lane < count) ahead = blocks[first + i + 32 + lane];
+        while (i >= base + 32) {
+            mine = ahead;
+            base += 32;
+            if (base + 32 + lane < count) ahead = blocks[first + base + 32 + lane];
         }
         BlockDesc d;
-        d.idx = __shfl_sync(0xffffffffu, mine.idx, i & 31);
-        d.packed = __shfl_sync(0xffffffffu, mine.packed, i & 31);
+        d.idx = __shfl_sync(0xffffffffu, mine.idx, i - base);
+        d.packed = __shfl_sync(0xffffffffu, mine.packed, i - base);
         return d;
     }
 };
@@ -289,7 +303,7 @@ __device__ __forceinline__ BlockDesc load_first_chunk(const BlockDesc* blocks, i
 // Number of accumulations (each ends in an epilogue) and K-steps per accumulation of an item.
 __device__ __forceinline__ void item_shape(const TcParams& p, int count, int& flushes, int& ksteps) {
     if (p.mode == BSA_MODE_SDD) {
-        flushes = (count + 1) >> 1;
+        flushes = (count + 3) >> 2;
         ksteps = (p.size_k + kTile - 1) / kTile;
     } else {
         flushes = 1;
@@ -299,27 +313,28 @@ __device__ __forceinline__ void item_shape(const TcParams& p, int count, int& fl
 
 // Number of B tiles (64 output columns each) of one accumulation; there is always one A tile.
 __device__ __forceinline__ int b_tiles(const TcParams& p, int count, int chunk, int flush) {
-    if (p.mode == BSA_MODE_SDD) return min(2, count - 2 * flush);
+    if (p.mode == BSA_MODE_SDD) return min(4, count - 4 * flush);
     if (p.mode == BSA_MODE_DSD) return min(2, (p.size_n - chunk * 2 * kTile + kTile - 1) / kTile);
     return 1;
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
-tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 const __grid_constant__ CUtensorMap map_c, const TcParams p) {
+tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t* stage_base = smem;                                   // p.stages * p.slots tiles
-    uint8_t* out_base = smem + kStageBytesTotal;                  // kOutBufs tiles
-    Barriers* bars = reinterpret_cast<Barriers*>(out_base + kOutBufs * kTileBytes);
+    uint8_t* stage_base = smem;                                   // p.stages * (1 + p.nb_max) tiles
+    Barriers* bars = reinterpret_cast<Barriers*>(smem + kStageTiles * kTileBytes);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int stage_bytes = p.slots * kTileBytes;
+    const int stage_bytes = (1 + p.nb_max) * kTileBytes;
+    const bool is_sdd = p.mode == BSA_MODE_SDD;
+    // sdd: one issuer per accumulation; dsd / dds: all issuers work on every stage
+    const uint32_t arrivals = is_sdd ? 1u : (uint32_t)p.issuers;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kMaxStages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], p.issuers); }
-        for (int s = 0; s < 2; ++s) { mbar_init(&bars->acc_full[s], p.issuers); mbar_init(&bars->acc_empty[s], 4); }
-        mbar_init(&bars->drain, p.issuers);
+        for (int s = 0; s < kMaxStages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], arrivals); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&bars->acc_full[s], arrivals); mbar_init(&bars->acc_empty[s], 4); }
+        mbar_init(&bars->drain, (uint32_t)p.issuers);
         bars->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_shared();
@@ -337,19 +352,15 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const bool a_mn_major = p.trans_a != 0;      // op(A) tile arrives with M contiguous
     const bool b_mn_major = p.trans_b == 0;      // op(B) tile arrives with N contiguous
 
-    if (warp < 2) {
+    if (warp < kProducerWarps) {
         // ------------------------------------------------------------ TMA producers
-        // Warp 0 loads the A tile of every stage and arms its barrier with the byte count of
-        // the whole stage; warp 1 loads the B tile(s).  All 32 lanes walk the items together
-        // (descriptor windows are warp-wide); lane 0 waits and issues.
-        const bool load_a = warp == 0;
-        int stage = 0;
+        // Every producer walks all items (all 32 lanes together: descriptor windows are
+        // warp-wide) and loads the K-steps whose sequence number is its own modulo 4.
+        int stage = 0, step = 0;
         uint32_t phase = 0;
         bool ok = true;
-        TC_TIME_DECL(t_wait); TC_TIME_DECL(t_issue); TC_TIME_DECL(t_all);
-#ifdef BSA_TC_TIMING
-        const long long t_begin = clock64();
-#endif
+        long long t_wait = 0, t_issue = 0;
+        const long long t_begin = TC_CLOCK();
         Cursor cur;
         cur.init(p);
         BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
@@ -359,76 +370,74 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             int flushes, ksteps;
             item_shape(p, cur.count, flushes, ksteps);
             DescWindow win;
-            win.begin(pre);
+            win.begin(p.blocks, cur.first, cur.count, pre, lane);
             for (int f = 0; ok && f < flushes; ++f) {
                 const int nb = b_tiles(p, cur.count, cur.chunk, f);
-                BlockDesc d0{0, 0}, d1{0, 0};
-                if (p.mode == BSA_MODE_SDD) {
-                    d0 = win.get(p.blocks, cur.first, cur.count, 2 * f, lane);
-                    d1 = win.get(p.blocks, cur.first, cur.count, 2 * f + 1, lane);
-                }
                 for (int k = 0; ok && k < ksteps; ++k) {
-                    BlockDesc d{0, 0};
-                    if (p.mode != BSA_MODE_SDD) d = win.get(p.blocks, cur.first, cur.count, k, lane);
-                    if (lane == 0) {
-                        TC_TIMED(t_wait, ok = mbar_wait(&bars->empty[stage], phase ^ 1, bars, p.status));
-#ifdef BSA_TC_TIMING
-                        const long long tic_issue = clock64();
-#endif
-                        if (ok) {
-                            uint8_t* slot = stage_base + stage * stage_bytes;
-                            uint64_t* full = &bars->full[stage];
-                            if (load_a) mbar_expect_tx(full, (uint32_t)((1 + nb) * kTileBytes));
-                            if (p.mode == BSA_MODE_SDD) {
-                                const int k0 = k * kTile, m0 = cur.g * kTile;
-                                if (load_a) {
+                    // The stage count is a multiple of the producer count, so a stage is always
+                    // filled by the same producer.  This matters: an mbarrier parity wait can only
+                    // tell the current phase from the one before it, so a thread must take part in
+                    // every phase of each barrier it ever waits on.
+                    if ((step & (kProducerWarps - 1)) == warp) {
+                        int cols[4] = {0, 0, 0, 0};
+                        BlockDesc d{0, 0};
+                        if (is_sdd) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                if (j < nb) cols[j] = win.get(p.blocks, cur.first, cur.count, 4 * f + j, lane).col();
+                        } else {
+                            d = win.get(p.blocks, cur.first, cur.count, k, lane);
+                        }
+                        if (lane == 0) {
+                            const long long t0 = TC_CLOCK();
+                            ok = mbar_wait(&bars->empty[stage], phase ^ 1, bars, p.status);
+                            const long long t1 = TC_CLOCK();
+                            t_wait += t1 - t0;
+                            if (ok) {
+                                uint8_t* slot = stage_base + stage * stage_bytes;
+                                uint64_t* full = &bars->full[stage];
+                                mbar_expect_tx(full, (uint32_t)((1 + nb) * kTileBytes));
+                                if (is_sdd) {
+                                    const int k0 = k * kTile, m0 = cur.g * kTile;
                                     if (a_mn_major) tma_load_3d(slot, &map_a, full, m0, k0, cur.z);
                                     else            tma_load_3d(slot, &map_a, full, k0, m0, cur.z);
-                                } else {
-                                    for (int j = 0; j < nb; ++j) {
-                                        const int n0 = (j == 0 ? d0.col() : d1.col()) * kTile;
-                                        if (b_mn_major) tma_load_3d(slot + (1 + j) * kTileBytes, &map_b, full, n0, k0, cur.z);
-                                        else            tma_load_3d(slot + (1 + j) * kTileBytes, &map_b, full, k0, n0, cur.z);
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j) {
+                                        if (j < nb) {
+                                            const int n0 = cols[j] * kTile;
+                                            if (b_mn_major) tma_load_3d(slot + (1 + j) * kTileBytes, &map_b, full, n0, k0, cur.z);
+                                            else            tma_load_3d(slot + (1 + j) * kTileBytes, &map_b, full, k0, n0, cur.z);
+                                        }
                                     }
-                                }
-                            } else if (p.mode == BSA_MODE_DSD) {
-                                const int k0 = (p.trans_a ? d.row() : d.col()) * kTile;
-                                if (load_a) {
+                                } else if (p.mode == BSA_MODE_DSD) {
+                                    const int k0 = (p.trans_a ? d.row() : d.col()) * kTile;
                                     tma_load_3d(slot, &map_a, full, 0, d.idx * kTile, cur.z);
-                                } else {
                                     for (int j = 0; j < nb; ++j) {
                                         const int n0 = (cur.chunk * 2 + j) * kTile;
                                         if (b_mn_major) tma_load_3d(slot + (1 + j) * kTileBytes, &map_b, full, n0, k0, cur.z);
                                         else            tma_load_3d(slot + (1 + j) * kTileBytes, &map_b, full, k0, n0, cur.z);
                                     }
-                                }
-                            } else {
-                                const int k0 = (p.trans_b ? d.col() : d.row()) * kTile;
-                                if (load_a) {
+                                } else {
+                                    const int k0 = (p.trans_b ? d.col() : d.row()) * kTile;
                                     const int m0 = cur.chunk * kTile;
                                     if (a_mn_major) tma_load_3d(slot, &map_a, full, m0, k0, cur.z);
                                     else            tma_load_3d(slot, &map_a, full, k0, m0, cur.z);
-                                } else {
                                     tma_load_3d(slot + kTileBytes, &map_b, full, 0, d.idx * kTile, cur.z);
                                 }
                             }
+                            t_issue += TC_CLOCK() - t1;
                         }
-#ifdef BSA_TC_TIMING
-                        t_issue += clock64() - tic_issue;
-#endif
+                        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
                     }
-                    ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+                    ++step;
                     if (++stage == p.stages) { stage = 0; phase ^= 1; }
                 }
             }
             pre = pre_next;
             cur.advance();
         }
-#ifdef BSA_TC_TIMING
-        t_all = clock64() - t_begin;
-        if (lane == 0) { TC_TIME_OUT(warp * 3 + 0, t_all); TC_TIME_OUT(warp * 3 + 1, t_wait); TC_TIME_OUT(warp * 3 + 2, t_issue); }
-#endif
-        if (!ok && lane == 0) {
+        if (lane == 0 && warp == 0) { TC_TIME_OUT(0, TC_CLOCK() - t_begin); TC_TIME_OUT(1, t_wait); TC_TIME_OUT(2, t_issue); }
+        if (lane == 0 && *(volatile int*)&bars->abort_flag) {
             // Give copies that were issued a bounded chance to land before the CTA exits.
             const unsigned long long t0 = global_ns();
             for (int s = 0; s < p.stages; ++s)
@@ -440,40 +449,52 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // ------------------------------------------------------------ MMA issuers
         const int w = warp - kFirstMmaWarp;
         if (lane == 0 && w < p.issuers) {
-            int stage = 0, acc = 0;
-            uint32_t phase = 0, acc_phase = 0;
+            int stage = 0, flush_no = 0;
+            uint32_t phase = 0;
             bool ok = true;
             const uint32_t a_kstep = a_mn_major ? 2048u >> 4 : 32u >> 4;   // descriptor advance per K = 16
             const uint32_t b_kstep = b_mn_major ? 2048u >> 4 : 32u >> 4;
-            const int kk_per_issuer = (kTile / 16) / p.issuers;            // 1 or 2 K = 16 slices of each stage
-            // private partial accumulator of this issuer inside an accumulator buffer
-            const uint32_t part_col = (uint32_t)(w * (kAccCols / p.issuers));
-            TC_TIME_DECL(t_full); TC_TIME_DECL(t_acc); TC_TIME_DECL(t_all);
-#ifdef BSA_TC_TIMING
-            const long long t_begin = clock64();
-#endif
+            const int kk_count = is_sdd ? kTile / 16 : (kTile / 16) / p.issuers;
+            const int kk_stride = is_sdd ? 1 : p.issuers;
+            const int kk_first = is_sdd ? 0 : w;
+            // dsd / dds: private partial accumulator of this issuer inside the buffer
+            const uint32_t part_col = is_sdd ? 0u : (uint32_t)(w * (kAccCols / p.issuers));
+            long long t_full = 0, t_acc = 0;
+            const long long t_begin = TC_CLOCK();
             Cursor cur;
             cur.init(p);
             for (; ok && cur.valid(); cur.advance()) {
                 int flushes, ksteps;
                 item_shape(p, cur.count, flushes, ksteps);
                 if (ksteps == 0) continue;          // empty group: the epilogue writes zeros on its own
-                for (int f = 0; ok && f < flushes; ++f) {
+                for (int f = 0; ok && f < flushes; ++f, ++flush_no) {
+                    const int acc = flush_no & 1;
+                    if (is_sdd && p.issuers == 2 && acc != w) {
+                        // the other issuer's accumulation: only keep the stage counters in step
+                        // (the host guarantees that a stage always belongs to the same issuer)
+                        stage += ksteps;
+                        while (stage >= p.stages) { stage -= p.stages; phase ^= 1; }
+                        continue;
+                    }
                     const int nb = b_tiles(p, cur.count, cur.chunk, f);
-                    const uint32_t idesc = nb == 2 ? p.idesc128 : p.idesc64;
-                    TC_TIMED(t_acc, ok = mbar_wait(&bars->acc_empty[acc], acc_phase ^ 1, bars, p.status));
+                    const uint32_t idesc = p.idesc | ((uint32_t)((nb * kTile) >> 3) << 17);
+                    { const long long t0 = TC_CLOCK();
+                      ok = mbar_wait(&bars->acc_empty[acc], ((uint32_t)(flush_no >> 1) & 1u) ^ 1u, bars, p.status);
+                      t_acc += TC_CLOCK() - t0; }
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t d = tmem_base + (uint32_t)(acc * kAccCols) + part_col;
                     for (int k = 0; k < ksteps; ++k) {
-                        TC_TIMED(t_full, ok = mbar_wait(&bars->full[stage], phase, bars, p.status));
+                        { const long long t0 = TC_CLOCK();
+                          ok = mbar_wait(&bars->full[stage], phase, bars, p.status);
+                          t_full += TC_CLOCK() - t0; }
                         if (!ok) break;
                         tc_fence_after();
                         const uint32_t slot = smem_u32(stage_base + stage * stage_bytes);
                         const uint64_t da = make_tile_desc(slot, a_mn_major);
                         const uint64_t db = make_tile_desc(slot + kTileBytes, b_mn_major);
-                        for (int s = 0; s < kk_per_issuer; ++s) {
-                            const int kk = w + s * p.issuers;
+                        for (int s = 0; s < kk_count; ++s) {
+                            const int kk = kk_first + s * kk_stride;
                             tc_mma_f16(d, da + (uint64_t)(kk * a_kstep), db + (uint64_t)(kk * b_kstep), idesc,
                                        (k > 0 || s > 0) ? 1u : 0u);
                         }
@@ -481,35 +502,28 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         if (++stage == p.stages) { stage = 0; phase ^= 1; }
                     }
                     if (!ok) break;
-                    tc_commit(&bars->acc_full[acc]);         // this issuer's partial is complete
-                    if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                    tc_commit(&bars->acc_full[acc]);         // this issuer's accumulation is complete
                 }
             }
             // All MMAs issued by this thread must have retired before TMEM is freed.
             tc_commit(&bars->drain);
             mbar_wait(&bars->drain, 0, bars, p.status);
-#ifdef BSA_TC_TIMING
-            t_all = clock64() - t_begin;
-            if (w == 0) { TC_TIME_OUT(6, t_all); TC_TIME_OUT(7, t_full); TC_TIME_OUT(8, t_acc); }
-#endif
+            if (w == 0) { TC_TIME_OUT(3, TC_CLOCK() - t_begin); TC_TIME_OUT(4, t_full); TC_TIME_OUT(5, t_acc); }
         }
         __syncwarp();
     } else {
-        // ------------------------------------------------------------ epilogue
+        // ------------------------------------------------------------ epilogue groups
+        const int group = (warp - kFirstEpilogueWarp) >> 2;     // drains accumulator buffer `group`
         const int quad = warp & 3;                   // TMEM sub-partition this warp may read
-        const int et = threadIdx.x - kFirstEpilogueWarp * 32;   // 0..127 among the epilogue threads
         const int row = quad * 16 + lane;            // accumulator row held by this lane (lanes 0-15 only)
         const bool row_lane = lane < 16;
-        const bool is_sdd = p.mode == BSA_MODE_SDD;
-        const bool bf16_out = (p.idesc64 & (1u << 7)) != 0;
+        const bool bf16_out = (p.idesc & (1u << 7)) != 0;
+        const int parts = is_sdd ? 1 : p.issuers;
         const int part_stride = kAccCols / p.issuers;
-        int acc = 0, out_buf = 0;
-        uint32_t acc_phase = 0;
+        int flush_no = 0;
         bool ok = true;
-        TC_TIME_DECL(t_accf); TC_TIME_DECL(t_ld); TC_TIME_DECL(t_store); TC_TIME_DECL(t_write); TC_TIME_DECL(t_all);
-#ifdef BSA_TC_TIMING
-        const long long t_begin = clock64();
-#endif
+        long long t_accf = 0, t_ld = 0, t_write = 0;
+        const long long t_begin = TC_CLOCK();
         Cursor cur;
         cur.init(p);
         BlockDesc pre{0, 0};
@@ -519,38 +533,62 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             if (is_sdd && cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
             int flushes, ksteps;
             item_shape(p, cur.count, flushes, ksteps);
+            const bool have_acc = ksteps > 0;
             DescWindow win;
-            win.begin(pre);
+            if (is_sdd) win.begin(p.blocks, cur.first, cur.count, pre, lane);
             for (int f = 0; ok && f < flushes; ++f) {
+                // accumulations alternate between the two buffers / groups; groups that write
+                // zeros for an empty group of blocks are chosen by item parity
+                const int owner = have_acc ? (flush_no & 1) : ((cur.item / cur.stride) & 1);
+                const uint32_t acc_phase = (uint32_t)(flush_no >> 1) & 1u;
+                if (have_acc) ++flush_no;
+                if (owner != group) continue;
+                const int acc = group;
                 const int tiles = b_tiles(p, cur.count, cur.chunk, f);
-                const bool have_acc = ksteps > 0;
                 if (have_acc) {
-                    TC_TIMED(t_accf, ok = epilogue_all(mbar_wait(&bars->acc_full[acc], acc_phase, bars, p.status)));
+                    const long long t0 = TC_CLOCK();
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_full[acc], acc_phase, bars, p.status)) != 0;
+                    t_accf += TC_CLOCK() - t0;
                     if (!ok) break;
                     tc_fence_after();
                 }
                 for (int t = 0; t < tiles; ++t) {
-                    int out_idx = 0;
-                    if (is_sdd) out_idx = win.get(p.blocks, cur.first, cur.count, 2 * f + t, lane).idx;
-                    float v[kTile];
-#pragma unroll
-                    for (int c = 0; c < kTile; ++c) v[c] = 0.f;
-#ifdef BSA_TC_TIMING
-                    const long long tic_ld = clock64();
-#endif
+                    // destination of this 64x64 tile: first element, valid rows and columns
+                    size_t dst0;
+                    int rows_valid = kTile, cols_valid = kTile;
+                    if (is_sdd) {
+                        const int out_idx = win.get(p.blocks, cur.first, cur.count, 4 * f + t, lane).idx;
+                        dst0 = ((size_t)cur.z * p.nnz + out_idx) * (kTile * kTile);
+                    } else if (p.mode == BSA_MODE_DSD) {
+                        const int n0 = (cur.chunk * 2 + t) * kTile;
+                        dst0 = ((size_t)cur.z * p.size_m + (size_t)cur.g * kTile) * p.size_n + n0;
+                        cols_valid = min(kTile, p.size_n - n0);
+                    } else {
+                        const int m0 = cur.chunk * kTile;
+                        dst0 = ((size_t)cur.z * p.size_m + m0) * p.size_n + (size_t)cur.g * kTile;
+                        rows_valid = min(kTile, p.size_m - m0);
+                    }
+                    const long long t_a = TC_CLOCK();
+                    uint32_t v[kTile];          // fp32 bit patterns of this lane's row
                     if (have_acc) {
                         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16)
                                                + (uint32_t)(acc * kAccCols + t * kTile);
-                        for (int part = 0; part < p.issuers; ++part) {
+                        tc_ld_32x32b_x64(taddr, v);
+                        tc_wait_ld();
+                        for (int part = 1; part < parts; ++part) {
 #pragma unroll
                             for (int h = 0; h < 2; ++h) {
                                 uint32_t r[32];
                                 tc_ld_32x32b_x32(taddr + (uint32_t)(part * part_stride + h * 32), r);
                                 tc_wait_ld();
 #pragma unroll
-                                for (int c = 0; c < 32; ++c) v[h * 32 + c] += __uint_as_float(r[c]);
+                                for (int c = 0; c < 32; ++c)
+                                    v[h * 32 + c] = __float_as_uint(__uint_as_float(v[h * 32 + c]) + __uint_as_float(r[c]));
                             }
                         }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < kTile; ++c) v[c] = 0u;
                     }
                     if (have_acc && t == tiles - 1) {
                         // accumulator fully read: hand the TMEM buffer back to the MMA warps
@@ -558,25 +596,22 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&bars->acc_empty[acc]);
                     }
-#ifdef BSA_TC_TIMING
-                    t_ld += clock64() - tic_ld;
-                    const long long tic_st = clock64();
-#endif
-                    // staging tile `out_buf` was last read by the store issued kOutBufs tiles ago
-                    if (et == 0) tma_store_wait_read<kOutBufs - 1>();
-                    asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
-#ifdef BSA_TC_TIMING
-                    t_store += clock64() - tic_st;
-                    const long long tic_wr = clock64();
-#endif
-                    uint8_t* out = out_base + out_buf * kTileBytes;
-                    if (row_lane) {
+                    const long long t_b = TC_CLOCK();
+                    // never write outside the output: a descriptor that does not belong to this
+                    // layout is reported in the workspace instead (word 1 = offending offset >> 12)
+                    const bool in_bounds = dst0 + (size_t)(rows_valid - 1) * p.ldc + cols_valid <= (size_t)p.c_elems;
+                    if (!in_bounds && lane == 0) {
+                        atomicExch(p.status, (uint32_t)BSA_ERR_BAD_SHAPE);
+                        atomicExch(p.status + 1, (uint32_t)(dst0 >> 12));
+                    }
+                    if (row_lane && row < rows_valid && in_bounds) {
+                        uint16_t* dst = p.c + dst0 + (size_t)row * p.ldc;
 #pragma unroll
-                        for (int c = 0; c < 8; ++c) {            // 16-byte chunk = 8 columns
-                            uint32_t packed[4];
+                        for (int c = 0; c < 4; ++c) {            // 32-byte piece = 16 columns
+                            uint32_t packed[8];
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const float lo = v[c * 8 + e * 2], hi = v[c * 8 + e * 2 + 1];
+                            for (int e = 0; e < 8; ++e) {
+                                const float lo = __uint_as_float(v[c * 16 + e * 2]), hi = __uint_as_float(v[c * 16 + e * 2 + 1]);
                                 if (bf16_out) {
                                     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
                                     packed[e] = *reinterpret_cast<uint32_t*>(&h);
@@ -585,37 +620,25 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                     packed[e] = *reinterpret_cast<uint32_t*>(&h);
                                 }
                             }
-                            *reinterpret_cast<uint4*>(out + row * 128 + ((c ^ (row & 7)) << 4)) =
-                                make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                            if (p.c_vec8 && c * 16 + 16 <= cols_valid) {
+                                st_global_v8(dst + c * 16, packed);
+                            } else {
+                                if (c * 16 + 8 <= cols_valid)
+                                    *reinterpret_cast<uint4*>(dst + c * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                                if (c * 16 + 16 <= cols_valid)
+                                    *reinterpret_cast<uint4*>(dst + c * 16 + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                            }
                         }
                     }
-                    fence_async_shared();
-                    asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
-                    if (et == 0) {
-                        if (is_sdd) {
-                            tma_store_3d(&map_c, out, 0, out_idx * kTile, cur.z);
-                        } else if (p.mode == BSA_MODE_DSD) {
-                            tma_store_3d(&map_c, out, (cur.chunk * 2 + t) * kTile, cur.g * kTile, cur.z);
-                        } else {
-                            tma_store_3d(&map_c, out, cur.g * kTile, cur.chunk * kTile, cur.z);
-                        }
-                        tma_store_commit();
-                    }
-                    if (++out_buf == kOutBufs) out_buf = 0;
-#ifdef BSA_TC_TIMING
-                    t_write += clock64() - tic_wr;
-#endif
+                    t_ld += t_b - t_a; t_write += TC_CLOCK() - t_b;
                 }
-                if (have_acc && ++acc == 2) { acc = 0; acc_phase ^= 1; }
             }
             pre = pre_next;
             cur.advance();
         }
-        if (et == 0) tma_store_wait_all();
-#ifdef BSA_TC_TIMING
-        t_all = clock64() - t_begin;
-        if (et == 0) { TC_TIME_OUT(9, t_all); TC_TIME_OUT(10, t_accf); TC_TIME_OUT(11, t_ld); TC_TIME_OUT(12, t_store); TC_TIME_OUT(13, t_write); }
-#endif
+        if (lane == 0 && quad == 0 && group == 0) {
+            TC_TIME_OUT(6, TC_CLOCK() - t_begin); TC_TIME_OUT(7, t_accf); TC_TIME_OUT(8, t_ld); TC_TIME_OUT(10, t_write);
+        }
     }
 
     // ---------------------------------------------------------------- teardown
@@ -704,22 +727,19 @@ int matmul_tc(const MatmulArgs& g) {
         return BSA_ERR_LAUNCH;
     }
     if (cudaFree(nullptr) != cudaSuccess) { cudaGetLastError(); return BSA_ERR_LAUNCH; }
-    CUtensorMap map_a, map_b, map_c;
+    CUtensorMap map_a, map_b;
     const int64_t sparse_rows = g.nnz * kTile;
     bool ok = true;
     // stored shapes: a dense operand is [rows, cols] = op^-1 of its logical shape
     if (g.mode == BSA_MODE_SDD) {
         ok &= make_map(&map_a, g.dtype, g.a, g.batches, g.trans_a ? g.size_k : g.size_m, g.trans_a ? g.size_m : g.size_k);
         ok &= make_map(&map_b, g.dtype, g.b, g.batches, g.trans_b ? g.size_n : g.size_k, g.trans_b ? g.size_k : g.size_n);
-        ok &= make_map(&map_c, g.dtype, g.c, g.batches, sparse_rows, kTile);
     } else if (g.mode == BSA_MODE_DSD) {
         ok &= make_map(&map_a, g.dtype, g.a, g.batches, sparse_rows, kTile);
         ok &= make_map(&map_b, g.dtype, g.b, g.batches, g.trans_b ? g.size_n : g.size_k, g.trans_b ? g.size_k : g.size_n);
-        ok &= make_map(&map_c, g.dtype, g.c, g.batches, g.size_m, g.size_n);
     } else {
         ok &= make_map(&map_a, g.dtype, g.a, g.batches, g.trans_a ? g.size_k : g.size_m, g.trans_a ? g.size_m : g.size_k);
         ok &= make_map(&map_b, g.dtype, g.b, g.batches, sparse_rows, kTile);
-        ok &= make_map(&map_c, g.dtype, g.c, g.batches, g.size_m, g.size_n);
     }
     if (!ok) return BSA_ERR_DRIVER;
 
@@ -730,22 +750,34 @@ int matmul_tc(const MatmulArgs& g) {
     p.mode = g.mode; p.trans_a = g.trans_a; p.trans_b = g.trans_b;
     p.chunks = (int)slices_of(g);
     p.items = (int)(g.batches * g.groups * p.chunks);
-    // two B tiles per stage (N = 128, two issuers) for sdd pairs and for dsd with more than 64 columns
-    const bool wide = g.mode == BSA_MODE_SDD || (g.mode == BSA_MODE_DSD && g.size_n > kTile);
-    p.slots = wide ? 3 : 2;
-    p.stages = kStageBytesTotal / (p.slots * kTileBytes);
-    p.issuers = wide ? 2 : 4;
-    // instruction descriptor: fp32 accumulate, fp16 / bf16 operands, M = 64, N = 64 or 128
+    if (g.mode == BSA_MODE_SDD) { p.nb_max = 4; p.issuers = 2; }
+    else if (g.mode == BSA_MODE_DSD && g.size_n > kTile) { p.nb_max = 2; p.issuers = 2; }
+    else { p.nb_max = 1; p.issuers = 4; }
+    // Every mbarrier must be waited on by the same threads in every phase (a parity wait cannot
+    // tell phases two apart), so the stage count is a multiple of the producer count, and for sdd,
+    // where the two issuers alternate accumulations of `ksteps` stages, a multiple of 2 * ksteps;
+    // otherwise one issuer does all accumulations.
+    p.stages = (kStageTiles / (1 + p.nb_max)) / kProducerWarps * kProducerWarps;
+    if (p.stages > kMaxStages) p.stages = kMaxStages / kProducerWarps * kProducerWarps;
+    if (g.mode == BSA_MODE_SDD) {
+        const int ksteps = (int)((g.size_k + kTile - 1) / kTile);
+        if (p.stages % (2 * ksteps) != 0) p.issuers = 1;
+    }
+    // instruction descriptor: fp32 accumulate, fp16 / bf16 operands, M = 64; N is added per accumulation
     const uint32_t fmt = g.dtype == BSA_DTYPE_BF16 ? 1u : 0u;
-    const uint32_t common = (1u << 4) | (fmt << 7) | (fmt << 10) | ((g.trans_a ? 1u : 0u) << 15)
-                            | ((g.trans_b ? 0u : 1u) << 16) | ((uint32_t)(kTile >> 4) << 24);
-    p.idesc64 = common | ((uint32_t)(kTile >> 3) << 17);
-    p.idesc128 = common | ((uint32_t)(2 * kTile >> 3) << 17);
+    p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((g.trans_a ? 1u : 0u) << 15)
+              | ((g.trans_b ? 0u : 1u) << 16) | ((uint32_t)(kTile >> 4) << 24);
+
+    p.c = static_cast<uint16_t*>(g.c);
+    p.ldc = g.mode == BSA_MODE_SDD ? kTile : (int)g.size_n;
+    p.c_vec8 = (reinterpret_cast<uintptr_t>(g.c) % 32 == 0 && p.ldc % 16 == 0) ? 1 : 0;
+    p.c_elems = g.mode == BSA_MODE_SDD ? (long long)g.batches * g.nnz * kTile * kTile
+                                       : (long long)g.batches * g.size_m * g.size_n;
 
     const int sms = sm_count();
     if (sms <= 0) return BSA_ERR_LAUNCH;
     const unsigned grid = (unsigned)(p.items < sms ? p.items : sms);
-    tc_matmul_kernel<<<grid, kThreads, kSmemBytes, g.stream>>>(map_a, map_b, map_c, p);
+    tc_matmul_kernel<<<grid, kThreads, kSmemBytes, g.stream>>>(map_a, map_b, p);
     return launch_status();
 }
 

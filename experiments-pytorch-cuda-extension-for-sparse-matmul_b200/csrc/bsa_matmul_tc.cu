@@ -726,7 +726,10 @@ int matmul_tc(const MatmulArgs& g) {
         cudaGetLastError();
         return BSA_ERR_LAUNCH;
     }
-    if (cudaFree(nullptr) != cudaSuccess) { cudaGetLastError(); return BSA_ERR_LAUNCH; }
+    {
+        int dev = 0;   // cudaSetDevice on the current device binds its primary context to this thread
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) { cudaGetLastError(); return BSA_ERR_LAUNCH; }
+    }
     CUtensorMap map_a, map_b;
     const int64_t sparse_rows = g.nnz * kTile;
     bool ok = true;

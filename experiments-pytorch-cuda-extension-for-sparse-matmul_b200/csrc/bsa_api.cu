@@ -3,6 +3,7 @@
 // block-sparse converters and the workspace status word.
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "bsa_common.cuh"
 
@@ -75,18 +76,15 @@ extern "C" const char* bsa_status_string(int status) {
     }
 }
 
-extern "C" int bsa_matmul(int mode, int dtype, int trans_a, int trans_b,
-                          const void* a, const void* b, void* c,
-                          const int32_t* blocks, const int32_t* table,
-                          int64_t nnz, int64_t groups, int64_t batches,
-                          int64_t size_m, int64_t size_n, int64_t size_k, int block,
-                          void* workspace, size_t workspace_bytes, int engine, void* stream) {
-    using namespace bsa;
+namespace {
+// Host-side argument checks of the matmul entry points; nothing is launched when they fail.
+int check_matmul_args(int mode, int dtype, const void* a, const void* b, const void* c,
+                      const int32_t* blocks, const int32_t* table, int64_t nnz, int64_t groups, int64_t batches,
+                      int64_t size_m, int64_t size_n, int64_t size_k, int block, int engine) {
     if (mode != BSA_MODE_SDD && mode != BSA_MODE_DSD && mode != BSA_MODE_DDS) return BSA_ERR_BAD_MODE;
     if (dtype != BSA_DTYPE_F32 && dtype != BSA_DTYPE_F16 && dtype != BSA_DTYPE_BF16) return BSA_ERR_BAD_DTYPE;
     if (block != 32 && block != 64 && block != 128) return BSA_ERR_BAD_BLOCK;
     if (!a || !b || !c || !blocks || !table) return BSA_ERR_NULL_POINTER;
-    if (!workspace || workspace_bytes < BSA_WORKSPACE_BYTES) return BSA_ERR_WORKSPACE;
     if (nnz < 0 || groups <= 0 || batches < 0 || size_m <= 0 || size_n <= 0 || size_k <= 0) return BSA_ERR_BAD_SHAPE;
     if (nnz > (int64_t)INT32_MAX / 2 || groups > 65535 || batches > 65535) return BSA_ERR_TOO_LARGE;
     if (engine != BSA_ENGINE_AUTO && engine != BSA_ENGINE_SIMT && engine != BSA_ENGINE_TCGEN05) return BSA_ERR_BAD_MODE;
@@ -100,7 +98,27 @@ extern "C" int bsa_matmul(int mode, int dtype, int trans_a, int trans_b,
     } else {
         if (size_n != grouped || size_k % block != 0) return BSA_ERR_BAD_SHAPE;
     }
-    if (!aligned16(a) || !aligned16(b) || !aligned16(c)) return BSA_ERR_ALIGNMENT;
+    if (!bsa::aligned16(a) || !bsa::aligned16(b) || !bsa::aligned16(c)) return BSA_ERR_ALIGNMENT;
+    return BSA_OK;
+}
+}  // namespace
+
+extern "C" int bsa_matmul(int mode, int dtype, int trans_a, int trans_b,
+                          const void* a, const void* b, void* c,
+                          const int32_t* blocks, const int32_t* table,
+                          int64_t nnz, int64_t groups, int64_t batches,
+                          int64_t size_m, int64_t size_n, int64_t size_k, int block,
+                          void* workspace, size_t workspace_bytes, int engine, void* stream) {
+    using namespace bsa;
+    // same order of checks as before the split: mode, dtype, block, pointers, workspace, sizes
+    if (mode != BSA_MODE_SDD && mode != BSA_MODE_DSD && mode != BSA_MODE_DDS) return BSA_ERR_BAD_MODE;
+    if (dtype != BSA_DTYPE_F32 && dtype != BSA_DTYPE_F16 && dtype != BSA_DTYPE_BF16) return BSA_ERR_BAD_DTYPE;
+    if (block != 32 && block != 64 && block != 128) return BSA_ERR_BAD_BLOCK;
+    if (!a || !b || !c || !blocks || !table) return BSA_ERR_NULL_POINTER;
+    if (!workspace || workspace_bytes < BSA_WORKSPACE_BYTES) return BSA_ERR_WORKSPACE;
+    const int checked = check_matmul_args(mode, dtype, a, b, c, blocks, table, nnz, groups, batches,
+                                          size_m, size_n, size_k, block, engine);
+    if (checked != BSA_OK) return checked;
     if (batches == 0) return BSA_OK;
 
     MatmulArgs args{mode, dtype, trans_a != 0, trans_b != 0, a, b, c,
@@ -144,4 +162,60 @@ extern "C" int bsa_workspace_status(void* workspace, void* stream) {
     if (cudaMemsetAsync(workspace, 0, 2 * sizeof(word), s) != cudaSuccess) return BSA_ERR_LAUNCH;
     if (cudaStreamSynchronize(s) != cudaSuccess) return BSA_ERR_LAUNCH;
     return word == (uint32_t)BSA_ERR_BAD_SHAPE ? BSA_ERR_BAD_SHAPE : BSA_ERR_DEVICE_TIMEOUT;
+}
+
+// ---------------------------------------------------------------------------
+// bsa_matmul_noalloc: the matmul for callers that must not allocate.
+//
+// The matmul kernels need BSA_WORKSPACE_BYTES of device scratch (the word in which a
+// kernel reports a bounded wait that ran out, plus diagnostics).  bsa_matmul takes that scratch
+// from the caller.  Code that runs where cudaMalloc is off limits -- inside another
+// framework's memory pool, in a real-time loop, in a plugin that was handed fixed buffers --
+// has nowhere to get it from, so this entry point keeps the scratch in device memory that is
+// part of the library image itself.
+namespace {
+constexpr size_t kStaticWorkspaceBytes = 256;      // the stated maximum of scratch this entry point can serve
+constexpr int kMaxDevices = 64;
+static __device__ __align__(256) unsigned char g_static_workspace[kStaticWorkspaceBytes];
+}  // namespace
+
+extern "C" int bsa_matmul_noalloc(int mode, int dtype, int trans_a, int trans_b,
+                                  const void* a, const void* b, void* c,
+                                  const int32_t* blocks, const int32_t* table,
+                                  int64_t nnz, int64_t groups, int64_t batches,
+                                  int64_t size_m, int64_t size_n, int64_t size_k, int block,
+                                  int engine, int wait_and_check, void* stream) {
+    // Scratch the kernels need versus what the static array holds.
+    if (BSA_WORKSPACE_BYTES > kStaticWorkspaceBytes) return BSA_ERR_WORKSPACE;
+    const int checked = check_matmul_args(mode, dtype, a, b, c, blocks, table, nnz, groups, batches,
+                                          size_m, size_n, size_k, block, engine);
+    if (checked != BSA_OK) return checked;      // refused before the device is touched
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return BSA_ERR_LAUNCH; }
+    if (dev < 0 || dev >= kMaxDevices) return BSA_ERR_TOO_LARGE;
+    // In host code `g_static_workspace` is only a handle of the symbol, not an address the GPU
+    // can use.  The device address differs per device, so it is looked up once per device, with
+    // that device current (first call on the device; no allocation happens here).
+    static std::mutex mutex;
+    static void* device_ptr[kMaxDevices] = {};
+    void* ws = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(mutex);
+        if (device_ptr[dev] == nullptr) {
+            void* ptr = nullptr;
+            if (cudaGetSymbolAddress(&ptr, g_static_workspace) != cudaSuccess || ptr == nullptr) {
+                cudaGetLastError();
+                return BSA_ERR_LAUNCH;
+            }
+            device_ptr[dev] = ptr;
+        }
+        ws = device_ptr[dev];
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // The array keeps whatever the previous call left in it; the status words must start at zero.
+    if (cudaMemsetAsync(ws, 0, kStaticWorkspaceBytes, s) != cudaSuccess) { cudaGetLastError(); return BSA_ERR_LAUNCH; }
+    const int st = bsa_matmul(mode, dtype, trans_a, trans_b, a, b, c, blocks, table, nnz, groups, batches,
+                              size_m, size_n, size_k, block, ws, kStaticWorkspaceBytes, engine, stream);
+    if (st != BSA_OK || !wait_and_check) return st;
+    return bsa_workspace_status(ws, stream);
 }

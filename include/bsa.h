@@ -174,6 +174,38 @@ int bsa_sparse_to_dense(int dtype, const void* sparse, void* dense,
  */
 int bsa_workspace_status(void* workspace, void* stream);
 
+/*
+ * bsa_matmul for callers that cannot allocate device memory.
+ * No counterpart in the reference (its binding allocates through torch on every call).
+ *
+ * Same product, same arguments and same kernels as bsa_matmul, except that the
+ * BSA_WORKSPACE_BYTES of scratch are not passed in: they live in a fixed
+ * 256-byte array in the library's own device image (one copy per GPU that
+ * loads the library, held until the process exits).  This is for code that
+ * runs where cudaMalloc is not an option -- a plugin inside another
+ * framework's memory pool, a latency-critical loop, a host that was only
+ * handed fixed buffers.  The entry point calls no cudaMalloc, cudaFree or
+ * other allocating routine; inputs and the output are still the caller's.
+ *
+ *   wait_and_check  0: return right after the asynchronous launch.
+ *                   nonzero: synchronise `stream` and return
+ *                   BSA_ERR_DEVICE_TIMEOUT if a kernel gave up on a bounded wait.
+ *
+ * Limits.  The scratch requirement of the kernels is fixed (it does not grow
+ * with the problem); should it ever exceed the 256 bytes of the static array
+ * the call is refused with BSA_ERR_WORKSPACE.  At most 64 devices.
+ * The first call on each device looks up the array's device address; make it
+ * before any stream capture.  All calls on a device share the one array and
+ * each call clears it first, so two calls whose kernels overlap on the GPU
+ * (different streams or threads) race on the status words: serialise them.
+ */
+int bsa_matmul_noalloc(int mode, int dtype, int trans_a, int trans_b,
+                       const void* a, const void* b, void* c,
+                       const int32_t* blocks, const int32_t* table,
+                       int64_t nnz, int64_t groups, int64_t batches,
+                       int64_t size_m, int64_t size_n, int64_t size_k, int block,
+                       int engine, int wait_and_check, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -126,6 +126,13 @@ __device__ __forceinline__ float team_reduce(float v, int L, float* exchange) {
     return v;
 }
 
+// 2^x by the special-function unit (relative error about 2^-22; 2^-inf = 0).
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // Scale the logits of one chunk into the log2 domain and mask them.
 template <int N>
 __device__ __forceinline__ void scale_and_mask(float (&v)[N], float scale_log2e, int q_pos, int k_pos0,
@@ -305,12 +312,61 @@ softmax_kernel(const SoftmaxParams p) {
 }
 
 
-// Fast path: rows of at most 256 * CH chunks, CH chunks per lane in registers, the next row of
-// the team prefetched (as raw 16-byte chunks) while the current one is reduced and written.
-// The block descriptor of each of a lane's chunks is the same for every row of the block row,
-// so it is looked up once per CTA.  Longer rows are left to softmax_kernel.
+// Fast path: rows of at most 256 * CH chunks.  A measured copy kernel with exactly this traversal
+// (a warp per dense row, 16-byte chunks, no prefetch) reaches 93 % of the HBM copy peak at full
+// occupancy, so the kernel is built to stay small: a lane keeps its CH chunks packed in the
+// input type (4 registers per chunk) through all three phases -- maximum (taken on the packed
+// values for 16-bit types), exponentials (written back packed, so a 16-bit result carries two
+// roundings, about 1e-3 relative), normalisation -- and converts on the fly.  The block
+// descriptor of each of a lane's chunks is the same for every row of the block row, so it is
+// looked up once per CTA.  Longer rows are left to softmax_kernel.
+template <typename T> struct Packed;
+template <> struct Packed<float> {
+    static __device__ __forceinline__ uint4 pack(const float (&v)[4]) {
+        return make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
+    }
+    // max over the chunk of sign * x
+    static __device__ __forceinline__ float signed_max(const uint4& r, bool negate) {
+        const float m0 = negate ? fminf(fminf(__uint_as_float(r.x), __uint_as_float(r.y)), fminf(__uint_as_float(r.z), __uint_as_float(r.w)))
+                                : fmaxf(fmaxf(__uint_as_float(r.x), __uint_as_float(r.y)), fmaxf(__uint_as_float(r.z), __uint_as_float(r.w)));
+        return negate ? -m0 : m0;
+    }
+};
+template <> struct Packed<__half> {
+    static __device__ __forceinline__ uint4 pack(const float (&v)[8]) {
+        uint4 r;
+        __half2* h = reinterpret_cast<__half2*>(&r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+        return r;
+    }
+    static __device__ __forceinline__ float signed_max(const uint4& r, bool negate) {
+        const __half2* h = reinterpret_cast<const __half2*>(&r);
+        const __half2 m = negate ? __hmin2(__hmin2(h[0], h[1]), __hmin2(h[2], h[3]))
+                                 : __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
+        const float2 f = __half22float2(m);
+        return negate ? -fminf(f.x, f.y) : fmaxf(f.x, f.y);
+    }
+};
+template <> struct Packed<__nv_bfloat16> {
+    static __device__ __forceinline__ uint4 pack(const float (&v)[8]) {
+        uint4 r;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        return r;
+    }
+    static __device__ __forceinline__ float signed_max(const uint4& r, bool negate) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+        const __nv_bfloat162 m = negate ? __hmin2(__hmin2(h[0], h[1]), __hmin2(h[2], h[3]))
+                                        : __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
+        const float2 f = __bfloat1622float2(m);
+        return negate ? -fminf(f.x, f.y) : fmaxf(f.x, f.y);
+    }
+};
+
 template <typename T, int CH, bool kBackward>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, kBackward ? 4 : 5)
 softmax_rows_kernel(const SoftmaxParams p) {
     constexpr int N = Vec<T>::N;
     __shared__ float s_red0[kWarps], s_red1[kWarps];
@@ -331,8 +387,8 @@ softmax_rows_kernel(const SoftmaxParams p) {
     const int team = threadIdx.x / L, t = threadIdx.x & (L - 1);
     const int rows_per_pass = kThreads / L;
 
-    uint32_t base[CH];
-    int kpos[CH];
+    uint32_t base[CH];                            // element offset of the lane's chunk in row 0, or ~0
+    int kpos[CH];                                 // key position of the chunk's first element
 #pragma unroll
     for (int k = 0; k < CH; ++k) {
         const int q = t + k * L;
@@ -354,86 +410,95 @@ softmax_rows_kernel(const SoftmaxParams p) {
     const float scale_log2e = p.scale * kLog2e;
     const bool causal = !kBackward && p.causal != 0;
     const bool masked = causal || kpm_row != nullptr;
+    const bool negate = scale_log2e < 0.f;
 
-    uint4 raw0[CH], raw1[kBackward ? CH : 1];
-    {
-        const int i = team;
-#pragma unroll
-        for (int k = 0; k < CH; ++k) {
-            if (i < block && base[k] != 0xFFFFFFFFu) {
-                raw0[k] = *reinterpret_cast<const uint4*>(in0 + base[k] + i * block);
-                if (kBackward) raw1[k] = *reinterpret_cast<const uint4*>(in1 + base[k] + i * block);
-            }
-        }
-    }
     for (int i0 = 0; i0 < block; i0 += rows_per_pass) {
         const int i = i0 + team;
         const bool active = i < block;
-        float v[CH][N];
-        float w[kBackward ? CH : 1][N];
-        float acc = kBackward ? 0.f : -CUDART_INF_F;
+        uint4 x[CH], g[kBackward ? CH : 1];
 #pragma unroll
         for (int k = 0; k < CH; ++k) {
             if (active && base[k] != 0xFFFFFFFFu) {
-                Vec<T>::unpack(raw0[k], v[k]);
-                if (kBackward) {
-                    Vec<T>::unpack(raw1[k], w[k]);
-#pragma unroll
-                    for (int e = 0; e < N; ++e) acc += v[k][e] * w[k][e];
-                } else {
-                    if (masked) {
-                        scale_and_mask<N>(v[k], scale_log2e, r * block + i, kpos[k], causal, kpm_row);
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < N; ++e) v[k][e] *= scale_log2e;
-                    }
-#pragma unroll
-                    for (int e = 0; e < N; ++e) acc = fmaxf(acc, v[k][e]);
-                }
-            }
-        }
-        // prefetch the team's next row
-        {
-            const int in = i + rows_per_pass;
-#pragma unroll
-            for (int k = 0; k < CH; ++k) {
-                if (in < block && base[k] != 0xFFFFFFFFu) {
-                    raw0[k] = *reinterpret_cast<const uint4*>(in0 + base[k] + in * block);
-                    if (kBackward) raw1[k] = *reinterpret_cast<const uint4*>(in1 + base[k] + in * block);
-                }
+                x[k] = *reinterpret_cast<const uint4*>(in0 + base[k] + i * block);
+                if (kBackward) g[k] = *reinterpret_cast<const uint4*>(in1 + base[k] + i * block);
             }
         }
         if (kBackward) {
+            float acc = 0.f;
+#pragma unroll
+            for (int k = 0; k < CH; ++k) {
+                if (active && base[k] != 0xFFFFFFFFu) {
+                    float v[N], w[N];
+                    Vec<T>::unpack(x[k], v);
+                    Vec<T>::unpack(g[k], w);
+#pragma unroll
+                    for (int e = 0; e < N; ++e) acc = fmaf(v[e], w[e], acc);
+                }
+            }
             const float dot = team_reduce<false>(acc, L, s_red0);
 #pragma unroll
             for (int k = 0; k < CH; ++k) {
                 if (active && base[k] != 0xFFFFFFFFu) {
-                    float o[N];
+                    float v[N], w[N];
+                    Vec<T>::unpack(x[k], v);
+                    Vec<T>::unpack(g[k], w);
 #pragma unroll
-                    for (int e = 0; e < N; ++e) o[e] = p.scale * v[k][e] * (w[k][e] - dot);
-                    Vec<T>::store(out + base[k] + i * block, o);
+                    for (int e = 0; e < N; ++e) v[e] = (p.scale * v[e]) * (w[e] - dot);
+                    *reinterpret_cast<uint4*>(out + base[k] + i * block) = Packed<T>::pack(v);
                 }
             }
             if (L > 32) __syncthreads();
         } else {
+            // phase 1: row maximum of scale*log2e*x (masked elements are -inf)
+            float acc = -CUDART_INF_F;
+#pragma unroll
+            for (int k = 0; k < CH; ++k) {
+                if (active && base[k] != 0xFFFFFFFFu) {
+                    if (masked) {
+                        float v[N];
+                        Vec<T>::unpack(x[k], v);
+                        scale_and_mask<N>(v, scale_log2e, r * block + i, kpos[k], causal, kpm_row);
+#pragma unroll
+                        for (int e = 0; e < N; ++e) acc = fmaxf(acc, v[e]);
+                    } else {
+                        acc = fmaxf(acc, Packed<T>::signed_max(x[k], negate));
+                    }
+                }
+            }
             float mx = team_reduce<true>(acc, L, s_red0);
             if (mx == -CUDART_INF_F) mx = 0.f;
+            if (!masked) mx *= fabsf(scale_log2e);       // max of sign*x -> max of scale*log2e*x
+            // phase 2: exponentials (kept packed) and their sum
             float sum = 0.f;
 #pragma unroll
             for (int k = 0; k < CH; ++k) {
                 if (active && base[k] != 0xFFFFFFFFu) {
+                    float v[N];
+                    Vec<T>::unpack(x[k], v);
+                    if (masked) {
+                        scale_and_mask<N>(v, scale_log2e, r * block + i, kpos[k], causal, kpm_row);
 #pragma unroll
-                    for (int e = 0; e < N; ++e) { v[k][e] = exp2f(v[k][e] - mx); sum += v[k][e]; }
+                        for (int e = 0; e < N; ++e) v[e] = fast_exp2(v[e] - mx);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < N; ++e) v[e] = fast_exp2(fmaf(v[e], scale_log2e, -mx));
+                    }
+#pragma unroll
+                    for (int e = 0; e < N; ++e) sum += v[e];
+                    x[k] = Packed<T>::pack(v);
                 }
             }
             sum = team_reduce<false>(sum, L, s_red1);
             const float inv = sum > 0.f ? 1.f / sum : 0.f;
+            // phase 3: normalise and store
 #pragma unroll
             for (int k = 0; k < CH; ++k) {
                 if (active && base[k] != 0xFFFFFFFFu) {
+                    float v[N];
+                    Vec<T>::unpack(x[k], v);
 #pragma unroll
-                    for (int e = 0; e < N; ++e) v[k][e] *= inv;
-                    Vec<T>::store(out + base[k] + i * block, v[k]);
+                    for (int e = 0; e < N; ++e) v[e] *= inv;
+                    *reinterpret_cast<uint4*>(out + base[k] + i * block) = Packed<T>::pack(v);
                 }
             }
         }

@@ -102,6 +102,7 @@ struct TcParams {
     uint16_t* c;             // output (16-bit elements)
     int ldc;                 // elements between output rows
     int c_vec8;              // rows start on 32-byte boundaries: 256-bit stores are legal
+    int stride_z, stride_rem;  // gridDim.x divided by the items per batch entry: quotient and remainder
     long long c_elems;       // elements in the output (bounds check of every store)
 };
 
@@ -227,20 +228,28 @@ __device__ __forceinline__ uint64_t make_tile_desc(uint32_t smem_addr, bool mn_m
 // Iterates the work items of one CTA (item = blockIdx.x + n * gridDim.x) and keeps the group
 // offset-table words of the next two items in flight, so that by the time an item becomes
 // current its words have arrived and no role stalls on a dependent global load per item.
+// Positions advance incrementally (the host passes gridDim.x split by the items per batch
+// entry): an integer division by a run-time value costs a lone thread hundreds of cycles.
 struct Cursor {
-    int item, stride, items, chunks, per_z;
+    int item, stride, items, chunks, per_z, stride_z, stride_rem;
     const int32_t* table;
+    int item_no;                        // how many items this CTA has finished
     int z, g, chunk, first, count;      // current item: batch entry, group, slice, block range
-    int n1_a, n1_b, n2_a, n2_b;         // table[g], table[g + 1] of the next item and the one after
+    int z1, r1, a1, b1;                 // next item: batch entry, index inside it, table[g], table[g + 1]
+    int z2, r2, a2, b2;                 // the item after that
 
-    __device__ __forceinline__ void load_words(int it, int& a, int& b) const {
+    __device__ __forceinline__ void load_words(bool in_range, int rem, int& a, int& b) const {
         a = 0; b = 0;
-        if (it < items) { const int gg = (it % per_z) / chunks; a = table[gg]; b = table[gg + 1]; }
+        if (in_range) { const int gg = chunks == 1 ? rem : rem / chunks; a = table[gg]; b = table[gg + 1]; }
     }
-    __device__ __forceinline__ void set_current(int a, int b) {
-        z = item / per_z;
-        const int rem = item - z * per_z;
-        g = rem / chunks;
+    __device__ __forceinline__ void step_pos(int& zz, int& rem) const {
+        zz += stride_z;
+        rem += stride_rem;
+        if (rem >= per_z) { rem -= per_z; ++zz; }
+    }
+    __device__ __forceinline__ void set_current(int zz, int rem, int a, int b) {
+        z = zz;
+        g = chunks == 1 ? rem : rem / chunks;
         chunk = rem - g * chunks;
         first = a;
         count = b - a;
@@ -248,23 +257,29 @@ struct Cursor {
     __device__ __forceinline__ void init(const TcParams& p) {
         item = (int)blockIdx.x; stride = (int)gridDim.x; items = p.items;
         chunks = p.chunks; per_z = p.groups * p.chunks; table = p.table;
+        stride_z = p.stride_z; stride_rem = p.stride_rem;
+        item_no = 0;
         z = g = chunk = first = count = 0;
-        int a, b;
-        load_words(item, a, b);
-        load_words(item + stride, n1_a, n1_b);
-        load_words(item + 2 * stride, n2_a, n2_b);
-        if (item < items) set_current(a, b);
+        int z0 = item / per_z, r0 = item - z0 * per_z, a0, b0;
+        load_words(item < items, r0, a0, b0);
+        z1 = z0; r1 = r0; step_pos(z1, r1);
+        load_words(item + stride < items, r1, a1, b1);
+        z2 = z1; r2 = r1; step_pos(z2, r2);
+        load_words(item + 2 * stride < items, r2, a2, b2);
+        if (item < items) set_current(z0, r0, a0, b0);
     }
     __device__ __forceinline__ bool valid() const { return item < items; }
     __device__ __forceinline__ bool has_next() const { return item + stride < items; }
-    __device__ __forceinline__ int next_first() const { return n1_a; }
-    __device__ __forceinline__ int next_count() const { return n1_b - n1_a; }
+    __device__ __forceinline__ int next_first() const { return a1; }
+    __device__ __forceinline__ int next_count() const { return b1 - a1; }
     __device__ __forceinline__ void advance() {
         item += stride;
-        const int a = n1_a, b = n1_b;
-        n1_a = n2_a; n1_b = n2_b;
-        load_words(item + 2 * stride, n2_a, n2_b);
-        if (item < items) set_current(a, b);
+        ++item_no;
+        const int zc = z1, rc = r1, ac = a1, bc = b1;
+        z1 = z2; r1 = r2; a1 = a2; b1 = b2;
+        step_pos(z2, r2);
+        load_words(item + 2 * stride < items, r2, a2, b2);
+        if (item < items) set_current(zc, rc, ac, bc);
     }
 };
 
@@ -318,6 +333,42 @@ __device__ __forceinline__ int b_tiles(const TcParams& p, int count, int chunk, 
     return 1;
 }
 
+// Hands a fully read TMEM accumulator buffer back to the MMA warps (one arrival per warp).
+__device__ __forceinline__ void release_accumulator(uint64_t* acc_empty, int lane) {
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(acc_empty);
+}
+
+// Converts NCOLS fp32 values of one output row to the 16-bit output type and stores the first
+// `cols_valid` of them (a multiple of 8) with 256-bit stores where the row alignment allows.
+template <int NCOLS>
+__device__ __forceinline__ void store_row(uint16_t* dst, const uint32_t (&v)[NCOLS], int cols_valid, bool vec8, bool bf16_out) {
+#pragma unroll
+    for (int c = 0; c < NCOLS / 16; ++c) {            // 32-byte piece = 16 columns
+        uint32_t packed[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float lo = __uint_as_float(v[c * 16 + e * 2]), hi = __uint_as_float(v[c * 16 + e * 2 + 1]);
+            if (bf16_out) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+                packed[e] = *reinterpret_cast<uint32_t*>(&h);
+            } else {
+                __half2 h = __floats2half2_rn(lo, hi);
+                packed[e] = *reinterpret_cast<uint32_t*>(&h);
+            }
+        }
+        if (vec8 && c * 16 + 16 <= cols_valid) {
+            st_global_v8(dst + c * 16, packed);
+        } else {
+            if (c * 16 + 8 <= cols_valid)
+                *reinterpret_cast<uint4*>(dst + c * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            if (c * 16 + 16 <= cols_valid)
+                *reinterpret_cast<uint4*>(dst + c * 16 + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -328,11 +379,11 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int stage_bytes = (1 + p.nb_max) * kTileBytes;
     const bool is_sdd = p.mode == BSA_MODE_SDD;
-    // sdd: one issuer per accumulation; dsd / dds: all issuers work on every stage
+    // sdd: one issuer per accumulation; dsd / dds: every issuer reports on every accumulation
     const uint32_t arrivals = is_sdd ? 1u : (uint32_t)p.issuers;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kMaxStages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], arrivals); }
+        for (int s = 0; s < kMaxStages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
         for (int s = 0; s < 2; ++s) { mbar_init(&bars->acc_full[s], arrivals); mbar_init(&bars->acc_empty[s], 4); }
         mbar_init(&bars->drain, (uint32_t)p.issuers);
         bars->abort_flag = 0;
@@ -355,30 +406,35 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (warp < kProducerWarps) {
         // ------------------------------------------------------------ TMA producers
         // Every producer walks all items (all 32 lanes together: descriptor windows are
-        // warp-wide) and loads the K-steps whose sequence number is its own modulo 4.
-        int stage = 0, step = 0;
+        // warp-wide) and loads the K-steps whose sequence number is its own modulo 4.  Those
+        // are steps warp, warp + 4, ... of the CTA, so (the stage count being a multiple of 4)
+        // its stage pointer simply advances by 4, whatever the item and accumulation borders.
+        int stage = warp, step0 = 0;         // step0: sequence number of the accumulation's first K-step
         uint32_t phase = 0;
         bool ok = true;
-        long long t_wait = 0, t_issue = 0;
+        long long t_wait = 0, t_issue = 0, t_get = 0, t_item = 0;
         const long long t_begin = TC_CLOCK();
         Cursor cur;
         cur.init(p);
         BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
         while (ok && cur.valid()) {
+            const long long t_i0 = TC_CLOCK();
             BlockDesc pre_next{0, 0};
             if (cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
             int flushes, ksteps;
             item_shape(p, cur.count, flushes, ksteps);
             DescWindow win;
             win.begin(p.blocks, cur.first, cur.count, pre, lane);
+            t_item += TC_CLOCK() - t_i0;
             for (int f = 0; ok && f < flushes; ++f) {
                 const int nb = b_tiles(p, cur.count, cur.chunk, f);
-                for (int k = 0; ok && k < ksteps; ++k) {
-                    // The stage count is a multiple of the producer count, so a stage is always
-                    // filled by the same producer.  This matters: an mbarrier parity wait can only
-                    // tell the current phase from the one before it, so a thread must take part in
-                    // every phase of each barrier it ever waits on.
-                    if ((step & (kProducerWarps - 1)) == warp) {
+                // The stage count is a multiple of the producer count, so a stage is always
+                // filled by the same producer.  This matters: an mbarrier parity wait can only
+                // tell the current phase from the one before it, so a thread must take part in
+                // every phase of each barrier it ever waits on.
+                for (int k = (warp - step0) & (kProducerWarps - 1); ok && k < ksteps; k += kProducerWarps) {
+                    {
+                        const long long t_g0 = TC_CLOCK();
                         int cols[4] = {0, 0, 0, 0};
                         BlockDesc d{0, 0};
                         if (is_sdd) {
@@ -388,6 +444,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         } else {
                             d = win.get(p.blocks, cur.first, cur.count, k, lane);
                         }
+                        t_get += TC_CLOCK() - t_g0;
                         if (lane == 0) {
                             const long long t0 = TC_CLOCK();
                             ok = mbar_wait(&bars->empty[stage], phase ^ 1, bars, p.status);
@@ -429,14 +486,15 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         }
                         ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
                     }
-                    ++step;
-                    if (++stage == p.stages) { stage = 0; phase ^= 1; }
+                    stage += kProducerWarps;
+                    if (stage >= p.stages) { stage -= p.stages; phase ^= 1; }
                 }
+                step0 += ksteps;
             }
             pre = pre_next;
             cur.advance();
         }
-        if (lane == 0 && warp == 0) { TC_TIME_OUT(0, TC_CLOCK() - t_begin); TC_TIME_OUT(1, t_wait); TC_TIME_OUT(2, t_issue); }
+        if (lane == 0 && warp == 0) { TC_TIME_OUT(0, TC_CLOCK() - t_begin); TC_TIME_OUT(1, t_wait); TC_TIME_OUT(2, t_issue); TC_TIME_OUT(9, t_get); TC_TIME_OUT(11, t_item); }
         if (lane == 0 && *(volatile int*)&bars->abort_flag) {
             // Give copies that were issued a bounded chance to land before the CTA exits.
             const unsigned long long t0 = global_ns();
@@ -449,17 +507,20 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // ------------------------------------------------------------ MMA issuers
         const int w = warp - kFirstMmaWarp;
         if (lane == 0 && w < p.issuers) {
-            int stage = 0, flush_no = 0;
+            // Own stage pointer.  dsd / dds: this issuer's K-steps are w, w + issuers, ... of the CTA,
+            // so the pointer advances by `issuers`.  sdd with two issuers: accumulations alternate,
+            // so it runs through one accumulation's stages and then skips the other issuer's.
+            int flush_no = 0, step0 = 0;
+            int stage = is_sdd ? 0 : w;
             uint32_t phase = 0;
             bool ok = true;
             const uint32_t a_kstep = a_mn_major ? 2048u >> 4 : 32u >> 4;   // descriptor advance per K = 16
             const uint32_t b_kstep = b_mn_major ? 2048u >> 4 : 32u >> 4;
-            const int kk_count = is_sdd ? kTile / 16 : (kTile / 16) / p.issuers;
-            const int kk_stride = is_sdd ? 1 : p.issuers;
-            const int kk_first = is_sdd ? 0 : w;
             // dsd / dds: private partial accumulator of this issuer inside the buffer
             const uint32_t part_col = is_sdd ? 0u : (uint32_t)(w * (kAccCols / p.issuers));
-            long long t_full = 0, t_acc = 0;
+            const int issuer_mask = p.issuers - 1;       // issuers is 1, 2 or 4 (no runtime division here:
+                                                         // it costs a lone thread hundreds of cycles)
+            long long t_full = 0, t_acc = 0, t_mma = 0, t_commit = 0, t_desc = 0, t_kloop = 0, t_accfull = 0;
             const long long t_begin = TC_CLOCK();
             Cursor cur;
             cur.init(p);
@@ -470,8 +531,8 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 for (int f = 0; ok && f < flushes; ++f, ++flush_no) {
                     const int acc = flush_no & 1;
                     if (is_sdd && p.issuers == 2 && acc != w) {
-                        // the other issuer's accumulation: only keep the stage counters in step
-                        // (the host guarantees that a stage always belongs to the same issuer)
+                        // the other issuer's accumulation: skip its stages (the host guarantees
+                        // that a stage always belongs to the same issuer)
                         stage += ksteps;
                         while (stage >= p.stages) { stage -= p.stages; phase ^= 1; }
                         continue;
@@ -484,31 +545,51 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t d = tmem_base + (uint32_t)(acc * kAccCols) + part_col;
-                    for (int k = 0; k < ksteps; ++k) {
-                        { const long long t0 = TC_CLOCK();
-                          ok = mbar_wait(&bars->full[stage], phase, bars, p.status);
-                          t_full += TC_CLOCK() - t0; }
-                        if (!ok) break;
-                        tc_fence_after();
-                        const uint32_t slot = smem_u32(stage_base + stage * stage_bytes);
-                        const uint64_t da = make_tile_desc(slot, a_mn_major);
-                        const uint64_t db = make_tile_desc(slot + kTileBytes, b_mn_major);
-                        for (int s = 0; s < kk_count; ++s) {
-                            const int kk = kk_first + s * kk_stride;
-                            tc_mma_f16(d, da + (uint64_t)(kk * a_kstep), db + (uint64_t)(kk * b_kstep), idesc,
-                                       (k > 0 || s > 0) ? 1u : 0u);
+                    bool issued = false;
+                    const long long tk0 = TC_CLOCK();
+                    // dsd / dds: K-step n belongs to issuer n % issuers (the stage count is a
+                    // multiple of it, so a stage always belongs to the same issuer)
+                    const int k_first = is_sdd ? 0 : ((w - step0) & issuer_mask);
+                    const int k_inc = is_sdd ? 1 : p.issuers;
+                    for (int k = k_first; k < ksteps; k += k_inc) {
+                        {
+                            { const long long t0 = TC_CLOCK();
+                              ok = mbar_wait(&bars->full[stage], phase, bars, p.status);
+                              t_full += TC_CLOCK() - t0; }
+                            if (!ok) break;
+                            const long long tm0 = TC_CLOCK();
+                            tc_fence_after();
+                            const uint32_t slot = smem_u32(stage_base + stage * stage_bytes);
+                            const uint64_t da = make_tile_desc(slot, a_mn_major);
+                            const uint64_t db = make_tile_desc(slot + kTileBytes, b_mn_major);
+                            const long long tm1 = TC_CLOCK();
+#pragma unroll
+                            for (int kk = 0; kk < kTile / 16; ++kk)
+                                tc_mma_f16(d, da + (uint64_t)(kk * a_kstep), db + (uint64_t)(kk * b_kstep), idesc,
+                                           (issued || kk > 0) ? 1u : 0u);
+                            issued = true;
+                            const long long tm2 = TC_CLOCK();
+                            tc_commit(&bars->empty[stage]);      // the stage is free once these MMAs have read it
+                            t_desc += tm1 - tm0; t_mma += tm2 - tm1; t_commit += TC_CLOCK() - tm2;
                         }
-                        tc_commit(&bars->empty[stage]);      // this issuer's reads of the stage are done
-                        if (++stage == p.stages) { stage = 0; phase ^= 1; }
+                        stage += k_inc;
+                        if (stage >= p.stages) { stage -= p.stages; phase ^= 1; }
                     }
+                    step0 += ksteps;
                     if (!ok) break;
-                    tc_commit(&bars->acc_full[acc]);         // this issuer's accumulation is complete
+                    const long long tk1 = TC_CLOCK();
+                    // the accumulation (dsd / dds: this issuer's partial, if it had a K-step) is complete
+                    if (issued) tc_commit(&bars->acc_full[acc]);
+                    else        mbar_arrive(&bars->acc_full[acc]);
+                    t_kloop += tk1 - tk0; t_accfull += TC_CLOCK() - tk1;
                 }
             }
             // All MMAs issued by this thread must have retired before TMEM is freed.
             tc_commit(&bars->drain);
             mbar_wait(&bars->drain, 0, bars, p.status);
-            if (w == 0) { TC_TIME_OUT(3, TC_CLOCK() - t_begin); TC_TIME_OUT(4, t_full); TC_TIME_OUT(5, t_acc); }
+            if (w == 0) { TC_TIME_OUT(3, TC_CLOCK() - t_begin); TC_TIME_OUT(4, t_full); TC_TIME_OUT(5, t_acc);
+                          TC_TIME_OUT(12, t_mma); TC_TIME_OUT(13, t_commit); TC_TIME_OUT(14, t_desc);
+                          TC_TIME_OUT(15, t_kloop); TC_TIME_OUT(16, t_accfull); }
         }
         __syncwarp();
     } else {
@@ -520,7 +601,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const bool bf16_out = (p.idesc & (1u << 7)) != 0;
         const int parts = is_sdd ? 1 : p.issuers;
         const int part_stride = kAccCols / p.issuers;
-        int flush_no = 0;
+        int flush_no = 0, step = 0;
         bool ok = true;
         long long t_accf = 0, t_ld = 0, t_write = 0;
         const long long t_begin = TC_CLOCK();
@@ -539,8 +620,10 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             for (int f = 0; ok && f < flushes; ++f) {
                 // accumulations alternate between the two buffers / groups; groups that write
                 // zeros for an empty group of blocks are chosen by item parity
-                const int owner = have_acc ? (flush_no & 1) : ((cur.item / cur.stride) & 1);
+                const int owner = have_acc ? (flush_no & 1) : (cur.item_no & 1);
                 const uint32_t acc_phase = (uint32_t)(flush_no >> 1) & 1u;
+                const int step0 = step;             // sequence number of this accumulation's first K-step
+                step += ksteps;
                 if (have_acc) ++flush_no;
                 if (owner != group) continue;
                 const int acc = group;
@@ -568,35 +651,6 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         dst0 = ((size_t)cur.z * p.size_m + m0) * p.size_n + (size_t)cur.g * kTile;
                         rows_valid = min(kTile, p.size_m - m0);
                     }
-                    const long long t_a = TC_CLOCK();
-                    uint32_t v[kTile];          // fp32 bit patterns of this lane's row
-                    if (have_acc) {
-                        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16)
-                                               + (uint32_t)(acc * kAccCols + t * kTile);
-                        tc_ld_32x32b_x64(taddr, v);
-                        tc_wait_ld();
-                        for (int part = 1; part < parts; ++part) {
-#pragma unroll
-                            for (int h = 0; h < 2; ++h) {
-                                uint32_t r[32];
-                                tc_ld_32x32b_x32(taddr + (uint32_t)(part * part_stride + h * 32), r);
-                                tc_wait_ld();
-#pragma unroll
-                                for (int c = 0; c < 32; ++c)
-                                    v[h * 32 + c] = __float_as_uint(__uint_as_float(v[h * 32 + c]) + __uint_as_float(r[c]));
-                            }
-                        }
-                    } else {
-#pragma unroll
-                        for (int c = 0; c < kTile; ++c) v[c] = 0u;
-                    }
-                    if (have_acc && t == tiles - 1) {
-                        // accumulator fully read: hand the TMEM buffer back to the MMA warps
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&bars->acc_empty[acc]);
-                    }
-                    const long long t_b = TC_CLOCK();
                     // never write outside the output: a descriptor that does not belong to this
                     // layout is reported in the workspace instead (word 1 = offending offset >> 12)
                     const bool in_bounds = dst0 + (size_t)(rows_valid - 1) * p.ldc + cols_valid <= (size_t)p.c_elems;
@@ -604,33 +658,51 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         atomicExch(p.status, (uint32_t)BSA_ERR_BAD_SHAPE);
                         atomicExch(p.status + 1, (uint32_t)(dst0 >> 12));
                     }
-                    if (row_lane && row < rows_valid && in_bounds) {
-                        uint16_t* dst = p.c + dst0 + (size_t)row * p.ldc;
+                    const bool writer = row_lane && row < rows_valid && in_bounds;
+                    uint16_t* dst = p.c + dst0 + (size_t)row * p.ldc;
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16)
+                                           + (uint32_t)(acc * kAccCols + t * kTile);
+                    const bool last_tile = have_acc && t == tiles - 1;
+                    const long long t_a = TC_CLOCK();
+                    if (!have_acc || parts == 1) {
+                        uint32_t v[kTile];          // fp32 bit patterns of this lane's row
+                        if (have_acc) {
+                            tc_ld_32x32b_x64(taddr, v);
+                            tc_wait_ld();
+                        } else {
 #pragma unroll
-                        for (int c = 0; c < 4; ++c) {            // 32-byte piece = 16 columns
-                            uint32_t packed[8];
+                            for (int c = 0; c < kTile; ++c) v[c] = 0u;
+                        }
+                        const long long t_m = TC_CLOCK();
+                        if (last_tile) release_accumulator(&bars->acc_empty[acc], lane);
+                        if (writer) store_row<kTile>(dst, v, cols_valid, p.c_vec8 != 0, bf16_out);
+                        t_write += TC_CLOCK() - t_m;
+                        t_ld -= TC_CLOCK() - t_m;
+                    } else {
+                        // dsd / dds: issuer w holds a partial sum iff one of the K-steps
+                        // step0 .. step0 + ksteps - 1 is congruent to w; the first K-step's issuer
+                        // always does, so its partial seeds the sum.  Two 32-column halves keep the
+                        // register footprint small.
+                        const int first_part = step0 & (parts - 1);
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) {
-                                const float lo = __uint_as_float(v[c * 16 + e * 2]), hi = __uint_as_float(v[c * 16 + e * 2 + 1]);
-                                if (bf16_out) {
-                                    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-                                    packed[e] = *reinterpret_cast<uint32_t*>(&h);
-                                } else {
-                                    __half2 h = __floats2half2_rn(lo, hi);
-                                    packed[e] = *reinterpret_cast<uint32_t*>(&h);
-                                }
+                        for (int h = 0; h < 2; ++h) {
+                            uint32_t v[32];
+                            tc_ld_32x32b_x32(taddr + (uint32_t)(first_part * part_stride + h * 32), v);
+                            tc_wait_ld();
+                            for (int j = 1; j < parts && j < ksteps; ++j) {
+                                const int part = (first_part + j) & (parts - 1);
+                                uint32_t r[32];
+                                tc_ld_32x32b_x32(taddr + (uint32_t)(part * part_stride + h * 32), r);
+                                tc_wait_ld();
+#pragma unroll
+                                for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) + __uint_as_float(r[c]));
                             }
-                            if (p.c_vec8 && c * 16 + 16 <= cols_valid) {
-                                st_global_v8(dst + c * 16, packed);
-                            } else {
-                                if (c * 16 + 8 <= cols_valid)
-                                    *reinterpret_cast<uint4*>(dst + c * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                                if (c * 16 + 16 <= cols_valid)
-                                    *reinterpret_cast<uint4*>(dst + c * 16 + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                            }
+                            if (last_tile && h == 1) release_accumulator(&bars->acc_empty[acc], lane);
+                            if (writer) store_row<32>(dst + h * 32, v, cols_valid - h * 32, p.c_vec8 != 0, bf16_out);
                         }
                     }
-                    t_ld += t_b - t_a; t_write += TC_CLOCK() - t_b;
+                    const long long t_b = TC_CLOCK();
+                    t_ld += t_b - t_a;
                 }
             }
             pre = pre_next;
@@ -780,6 +852,9 @@ int matmul_tc(const MatmulArgs& g) {
     const int sms = sm_count();
     if (sms <= 0) return BSA_ERR_LAUNCH;
     const unsigned grid = (unsigned)(p.items < sms ? p.items : sms);
+    const int per_z = p.groups * p.chunks;
+    p.stride_z = (int)grid / per_z;
+    p.stride_rem = (int)grid % per_z;
     tc_matmul_kernel<<<grid, kThreads, kSmemBytes, g.stream>>>(map_a, map_b, p);
     return launch_status();
 }

@@ -202,6 +202,20 @@ __device__ __forceinline__ void tc_ld_32x32b_x64(uint32_t taddr, uint32_t (&r)[6
           "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
         : "r"(taddr) : "memory");
 }
+// 16 TMEM lanes x 64 columns spread over all 32 threads: thread t gets, for each 8-column
+// unit u, r[4u + 0,1] = (lane t/4, columns 8u + 2(t%4) + 0,1) and r[4u + 2,3] = the same columns
+// of lane t/4 + 8 (the layout of an m16n8 accumulator fragment).
+__device__ __forceinline__ void tc_ld_16x256b_x8(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t (&w)[8]) {
     asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
@@ -316,8 +330,9 @@ __device__ __forceinline__ BlockDesc load_first_chunk(const BlockDesc* blocks, i
 }
 
 // Number of accumulations (each ends in an epilogue) and K-steps per accumulation of an item.
+template <int MODE>
 __device__ __forceinline__ void item_shape(const TcParams& p, int count, int& flushes, int& ksteps) {
-    if (p.mode == BSA_MODE_SDD) {
+    if (MODE == BSA_MODE_SDD) {
         flushes = (count + 3) >> 2;
         ksteps = (p.size_k + kTile - 1) / kTile;
     } else {
@@ -327,10 +342,54 @@ __device__ __forceinline__ void item_shape(const TcParams& p, int count, int& fl
 }
 
 // Number of B tiles (64 output columns each) of one accumulation; there is always one A tile.
+template <int MODE>
 __device__ __forceinline__ int b_tiles(const TcParams& p, int count, int chunk, int flush) {
-    if (p.mode == BSA_MODE_SDD) return min(4, count - 4 * flush);
-    if (p.mode == BSA_MODE_DSD) return min(2, (p.size_n - chunk * 2 * kTile + kTile - 1) / kTile);
+    if (MODE == BSA_MODE_SDD) return min(4, count - 4 * flush);
+    if (MODE == BSA_MODE_DSD) return min(2, (p.size_n - chunk * 2 * kTile + kTile - 1) / kTile);
     return 1;
+}
+
+// 4x4 transpose of 32-bit words among the four threads of a quad (lanes 4i .. 4i+3): on entry
+// thread q holds m[u] = element (u, q); on return it holds m[j] = element (q, j).
+__device__ __forceinline__ void quad_transpose(uint32_t (&m)[4], int q) {
+    const bool b0 = (q & 1) != 0, b1 = (q & 2) != 0;
+    uint32_t s0 = b0 ? m[0] : m[1], s1 = b0 ? m[2] : m[3];
+    s0 = __shfl_xor_sync(0xffffffffu, s0, 1);
+    s1 = __shfl_xor_sync(0xffffffffu, s1, 1);
+    if (b0) { m[0] = s0; m[2] = s1; } else { m[1] = s0; m[3] = s1; }
+    s0 = b1 ? m[0] : m[2];
+    s1 = b1 ? m[1] : m[3];
+    s0 = __shfl_xor_sync(0xffffffffu, s0, 2);
+    s1 = __shfl_xor_sync(0xffffffffu, s1, 2);
+    if (b1) { m[0] = s0; m[1] = s1; } else { m[2] = s0; m[3] = s1; }
+}
+
+// Full 64x64 tile of a sparse output: the warp converts its 16 accumulator rows with all 32
+// lanes (the 32x32b load shape would leave half of the lanes without data), transposes inside
+// quads so that every thread owns 16 contiguous bytes, and stores 64 bytes of 8 rows per
+// instruction.  thread_dst = element (row lane / 4, column 8 * (lane % 4)) of the warp's rows.
+__device__ __forceinline__ void store_tile_rows16(uint16_t* thread_dst, const uint32_t (&r)[32], int q, bool bf16_out) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {            // rows g and g + 8
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {           // columns 32 * blk .. 32 * blk + 31
+            uint32_t m[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float lo = __uint_as_float(r[4 * (4 * blk + u) + 2 * half]);
+                const float hi = __uint_as_float(r[4 * (4 * blk + u) + 2 * half + 1]);
+                if (bf16_out) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+                    m[u] = *reinterpret_cast<uint32_t*>(&h);
+                } else {
+                    __half2 h = __floats2half2_rn(lo, hi);
+                    m[u] = *reinterpret_cast<uint32_t*>(&h);
+                }
+            }
+            quad_transpose(m, q);                     // now words 4q .. 4q + 3 of this 32-column block
+            *reinterpret_cast<uint4*>(thread_dst + half * 8 * kTile + blk * 32) = make_uint4(m[0], m[1], m[2], m[3]);
+        }
+    }
 }
 
 // Hands a fully read TMEM accumulator buffer back to the MMA warps (one arrival per warp).
@@ -369,6 +428,9 @@ __device__ __forceinline__ void store_row(uint16_t* dst, const uint32_t (&v)[NCO
     }
 }
 
+// One instantiation per mode keeps each role's loop small (the sixteen warps of a CTA run
+// four different code paths through the same instruction caches).
+template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -378,7 +440,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int stage_bytes = (1 + p.nb_max) * kTileBytes;
-    const bool is_sdd = p.mode == BSA_MODE_SDD;
+    constexpr bool is_sdd = MODE == BSA_MODE_SDD;
     // sdd: one issuer per accumulation; dsd / dds: every issuer reports on every accumulation
     const uint32_t arrivals = is_sdd ? 1u : (uint32_t)p.issuers;
 
@@ -422,12 +484,12 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             BlockDesc pre_next{0, 0};
             if (cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
             int flushes, ksteps;
-            item_shape(p, cur.count, flushes, ksteps);
+            item_shape<MODE>(p, cur.count, flushes, ksteps);
             DescWindow win;
             win.begin(p.blocks, cur.first, cur.count, pre, lane);
             t_item += TC_CLOCK() - t_i0;
             for (int f = 0; ok && f < flushes; ++f) {
-                const int nb = b_tiles(p, cur.count, cur.chunk, f);
+                const int nb = b_tiles<MODE>(p, cur.count, cur.chunk, f);
                 // The stage count is a multiple of the producer count, so a stage is always
                 // filled by the same producer.  This matters: an mbarrier parity wait can only
                 // tell the current phase from the one before it, so a thread must take part in
@@ -466,7 +528,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                             else            tma_load_3d(slot + (1 + j) * kTileBytes, &map_b, full, k0, n0, cur.z);
                                         }
                                     }
-                                } else if (p.mode == BSA_MODE_DSD) {
+                                } else if (MODE == BSA_MODE_DSD) {
                                     const int k0 = (p.trans_a ? d.row() : d.col()) * kTile;
                                     tma_load_3d(slot, &map_a, full, 0, d.idx * kTile, cur.z);
                                     for (int j = 0; j < nb; ++j) {
@@ -526,7 +588,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             cur.init(p);
             for (; ok && cur.valid(); cur.advance()) {
                 int flushes, ksteps;
-                item_shape(p, cur.count, flushes, ksteps);
+                item_shape<MODE>(p, cur.count, flushes, ksteps);
                 if (ksteps == 0) continue;          // empty group: the epilogue writes zeros on its own
                 for (int f = 0; ok && f < flushes; ++f, ++flush_no) {
                     const int acc = flush_no & 1;
@@ -537,7 +599,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         while (stage >= p.stages) { stage -= p.stages; phase ^= 1; }
                         continue;
                     }
-                    const int nb = b_tiles(p, cur.count, cur.chunk, f);
+                    const int nb = b_tiles<MODE>(p, cur.count, cur.chunk, f);
                     const uint32_t idesc = p.idesc | ((uint32_t)((nb * kTile) >> 3) << 17);
                     { const long long t0 = TC_CLOCK();
                       ok = mbar_wait(&bars->acc_empty[acc], ((uint32_t)(flush_no >> 1) & 1u) ^ 1u, bars, p.status);
@@ -613,7 +675,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             BlockDesc pre_next{0, 0};
             if (is_sdd && cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
             int flushes, ksteps;
-            item_shape(p, cur.count, flushes, ksteps);
+            item_shape<MODE>(p, cur.count, flushes, ksteps);
             const bool have_acc = ksteps > 0;
             DescWindow win;
             if (is_sdd) win.begin(p.blocks, cur.first, cur.count, pre, lane);
@@ -627,7 +689,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (have_acc) ++flush_no;
                 if (owner != group) continue;
                 const int acc = group;
-                const int tiles = b_tiles(p, cur.count, cur.chunk, f);
+                const int tiles = b_tiles<MODE>(p, cur.count, cur.chunk, f);
                 if (have_acc) {
                     const long long t0 = TC_CLOCK();
                     ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_full[acc], acc_phase, bars, p.status)) != 0;
@@ -642,7 +704,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     if (is_sdd) {
                         const int out_idx = win.get(p.blocks, cur.first, cur.count, 4 * f + t, lane).idx;
                         dst0 = ((size_t)cur.z * p.nnz + out_idx) * (kTile * kTile);
-                    } else if (p.mode == BSA_MODE_DSD) {
+                    } else if (MODE == BSA_MODE_DSD) {
                         const int n0 = (cur.chunk * 2 + t) * kTile;
                         dst0 = ((size_t)cur.z * p.size_m + (size_t)cur.g * kTile) * p.size_n + n0;
                         cols_valid = min(kTile, p.size_n - n0);
@@ -664,7 +726,15 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                            + (uint32_t)(acc * kAccCols + t * kTile);
                     const bool last_tile = have_acc && t == tiles - 1;
                     const long long t_a = TC_CLOCK();
-                    if (!have_acc || parts == 1) {
+                    if (is_sdd && have_acc) {
+                        uint32_t r[32];
+                        tc_ld_16x256b_x8(taddr, r);
+                        tc_wait_ld();
+                        if (last_tile) release_accumulator(&bars->acc_empty[acc], lane);
+                        if (in_bounds)
+                            store_tile_rows16(p.c + dst0 + (size_t)(quad * 16 + (lane >> 2)) * kTile + (lane & 3) * 8, r,
+                                              lane & 3, bf16_out);
+                    } else if (!have_acc || parts == 1) {
                         uint32_t v[kTile];          // fp32 bit patterns of this lane's row
                         if (have_acc) {
                             tc_ld_32x32b_x64(taddr, v);
@@ -794,7 +864,10 @@ int matmul_tc(const MatmulArgs& g) {
     // host-side update).  Doing it first also binds the device's primary context to the calling
     // thread: cuTensorMapEncodeTiled below is a driver call and fails with "invalid context" on a
     // thread (e.g. an autograd worker) that has not made a runtime call needing the context yet.
-    if (cudaFuncSetAttribute(tc_matmul_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
+    const void* kernel = g.mode == BSA_MODE_SDD ? (const void*)tc_matmul_kernel<BSA_MODE_SDD>
+                       : g.mode == BSA_MODE_DSD ? (const void*)tc_matmul_kernel<BSA_MODE_DSD>
+                                                : (const void*)tc_matmul_kernel<BSA_MODE_DDS>;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
         cudaGetLastError();
         return BSA_ERR_LAUNCH;
     }
@@ -855,7 +928,9 @@ int matmul_tc(const MatmulArgs& g) {
     const int per_z = p.groups * p.chunks;
     p.stride_z = (int)grid / per_z;
     p.stride_rem = (int)grid % per_z;
-    tc_matmul_kernel<<<grid, kThreads, kSmemBytes, g.stream>>>(map_a, map_b, p);
+    if (g.mode == BSA_MODE_SDD)      tc_matmul_kernel<BSA_MODE_SDD><<<grid, kThreads, kSmemBytes, g.stream>>>(map_a, map_b, p);
+    else if (g.mode == BSA_MODE_DSD) tc_matmul_kernel<BSA_MODE_DSD><<<grid, kThreads, kSmemBytes, g.stream>>>(map_a, map_b, p);
+    else                             tc_matmul_kernel<BSA_MODE_DDS><<<grid, kThreads, kSmemBytes, g.stream>>>(map_a, map_b, p);
     return launch_status();
 }
 

@@ -226,11 +226,13 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # clocks are sampled from before the warm-up until after the end-to-end loop, so both timed
+    # regions are covered (a timed region of a few tens of ms is shorter than one sampling period)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
     # ---- device-resident timing (value) with per-op events
     for _ in range(args.warmup):
         device_step(sparse_ops, lay, q, k, v, do, scale, block)
     barrier()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
     ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in OPS]
           for _ in range(args.steps)]
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -239,32 +241,58 @@ def run_ours(args):
         device_step(sparse_ops, lay, q, k, v, do, scale, block, ev[i])
     stop.record()
     barrier()
-    clocks = sampler.stop() if sampler else None
     sparse_ops.check_device_status(local_rank)
     elapsed_ms = start.elapsed_time(stop)
     op_ms = {name: sum(ev[i][j][0].elapsed_time(ev[i][j][1]) for i in range(args.steps)) / args.steps
              for j, name in enumerate(OPS)}
 
-    # ---- end-to-end timing through the public API with host buffers
-    outs_host = [torch.empty(z, seq, dim, dtype=torch.float16).pin_memory() for _ in range(4)]
-    e2e_steps = max(1, min(args.steps, 10))
+    # ---- end-to-end timing through the public API with host buffers.  Every step copies its four
+    # inputs from pinned host memory, runs forward + backward through the autograd ops and copies the
+    # four results back to pinned host memory.  Copies run on their own streams so that step i + 1's
+    # upload and step i - 1's download overlap step i's kernels (double-buffered device inputs and
+    # host outputs); the timed region covers all of it.
+    e2e_steps = max(1, min(args.steps, 50))
+    outs_host = [[torch.empty(z, seq, dim, dtype=torch.float16).pin_memory() for _ in range(4)] for _ in range(2)]
+    dev_in = [[torch.empty(z, seq, dim, dtype=torch.float16, device=dev) for _ in range(4)] for _ in range(2)]
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    main = torch.cuda.current_stream(dev)
 
-    def e2e_once():
-        dq, dk, dv, ddo = (t.to(dev, non_blocking=True) for t in host)
-        res = api_step(lay, dq, dk, dv, ddo, scale)
-        for dst, src in zip(outs_host, res):
-            dst.copy_(src, non_blocking=True)
+    def e2e_run(steps):
+        computed = [None, None]          # event: kernels that read dev_in[b] are done
+        downloaded = [None, None]        # event: outs_host[b] has been filled
+        for i in range(steps):
+            b = i & 1
+            with torch.cuda.stream(s_in):
+                if computed[b] is not None:
+                    s_in.wait_event(computed[b])
+                for dst, src in zip(dev_in[b], host):
+                    dst.copy_(src, non_blocking=True)
+                uploaded = torch.cuda.Event()
+                uploaded.record(s_in)
+            main.wait_event(uploaded)
+            res = api_step(lay, *(t.detach() for t in dev_in[b]), scale)
+            computed[b] = torch.cuda.Event()
+            computed[b].record(main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(computed[b])
+                for dst, src in zip(outs_host[b], res):
+                    dst.copy_(src, non_blocking=True)
+                    src.record_stream(s_out)
+                downloaded[b] = torch.cuda.Event()
+                downloaded[b].record(s_out)
+        for ev in downloaded:
+            if ev is not None:
+                main.wait_event(ev)
 
-    for _ in range(min(args.warmup, 3)):
-        e2e_once()
+    e2e_run(min(args.warmup, 3))
     barrier()
     e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e_start.record()
-    for _ in range(e2e_steps):
-        e2e_once()
+    e2e_run(e2e_steps)
     e_stop.record()
     barrier()
     e2e_ms = e_start.elapsed_time(e_stop)
+    clocks = sampler.stop() if sampler else None
 
     # ---- DDS side measurement (not part of the step): dV^T = dO^T . P as dds(T,N)
     p_blocks = device_step(sparse_ops, lay, q, k, v, do, scale, block)["p"]
@@ -313,7 +341,11 @@ def run_ours(args):
             dom_bytes = (alg_bytes["softmax_fwd"] + alg_bytes["softmax_bwd"]) / 2
             dom_ms = softmax_ms / 2
         achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
-        cpu_dt, cpu_flops = cpu_attention_sample(2) if world == 1 and not args.no_cpu else (None, None)
+        cpu_dt = cpu_flops = cpu_heads = None
+        if world == 1 and not args.no_cpu:
+            probe_dt, _ = cpu_attention_sample(1)                    # size the sample: about 10 s of CPU work
+            cpu_heads = int(max(2, min(z, 10.0 / max(probe_dt, 1e-3))))
+            cpu_dt, cpu_flops = cpu_attention_sample(cpu_heads)
         line = {
             "metric": METRIC, "value": round(value, 3), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
@@ -336,7 +368,7 @@ def run_ours(args):
         if cpu_dt is not None:
             line["cpu_baseline"] = {"value": round(cpu_flops / cpu_dt / 1e12, 5), "unit": "TFLOP/s",
                                     "cores": torch.get_num_threads(), "kind": "port",
-                                    "sample": "2 of %d (batch*head) slices, masked dense torch fp32 fwd+bwd, %.1f s" % (z, cpu_dt)}
+                                    "sample": "%d of %d (batch*head) slices, masked dense torch fp32 fwd+bwd, %.1f s" % (cpu_heads, z, cpu_dt)}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -346,8 +378,8 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--slices", type=int, default=0,

@@ -430,7 +430,7 @@ __device__ __forceinline__ void store_row(uint16_t* dst, const uint32_t (&v)[NCO
 
 // One instantiation per mode keeps each role's loop small (the sixteen warps of a CTA run
 // four different code paths through the same instruction caches).
-template <int MODE>
+template <int MODE, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -660,7 +660,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int quad = warp & 3;                   // TMEM sub-partition this warp may read
         const int row = quad * 16 + lane;            // accumulator row held by this lane (lanes 0-15 only)
         const bool row_lane = lane < 16;
-        const bool bf16_out = (p.idesc & (1u << 7)) != 0;
+        constexpr bool bf16_out = BF16;
         const int parts = is_sdd ? 1 : p.issuers;
         const int part_stride = kAccCols / p.issuers;
         int flush_no = 0, step = 0;
@@ -864,9 +864,12 @@ int matmul_tc(const MatmulArgs& g) {
     // host-side update).  Doing it first also binds the device's primary context to the calling
     // thread: cuTensorMapEncodeTiled below is a driver call and fails with "invalid context" on a
     // thread (e.g. an autograd worker) that has not made a runtime call needing the context yet.
-    const void* kernel = g.mode == BSA_MODE_SDD ? (const void*)tc_matmul_kernel<BSA_MODE_SDD>
-                       : g.mode == BSA_MODE_DSD ? (const void*)tc_matmul_kernel<BSA_MODE_DSD>
-                                                : (const void*)tc_matmul_kernel<BSA_MODE_DDS>;
+    using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const TcParams);
+    const bool bf16 = g.dtype == BSA_DTYPE_BF16;
+    KernelFn kernel;
+    if (g.mode == BSA_MODE_SDD)      kernel = bf16 ? tc_matmul_kernel<BSA_MODE_SDD, true> : tc_matmul_kernel<BSA_MODE_SDD, false>;
+    else if (g.mode == BSA_MODE_DSD) kernel = bf16 ? tc_matmul_kernel<BSA_MODE_DSD, true> : tc_matmul_kernel<BSA_MODE_DSD, false>;
+    else                             kernel = bf16 ? tc_matmul_kernel<BSA_MODE_DDS, true> : tc_matmul_kernel<BSA_MODE_DDS, false>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
         cudaGetLastError();
         return BSA_ERR_LAUNCH;
@@ -928,9 +931,7 @@ int matmul_tc(const MatmulArgs& g) {
     const int per_z = p.groups * p.chunks;
     p.stride_z = (int)grid / per_z;
     p.stride_rem = (int)grid % per_z;
-    if (g.mode == BSA_MODE_SDD)      tc_matmul_kernel<BSA_MODE_SDD><<<grid, kThreads, kSmemBytes, g.stream>>>(map_a, map_b, p);
-    else if (g.mode == BSA_MODE_DSD) tc_matmul_kernel<BSA_MODE_DSD><<<grid, kThreads, kSmemBytes, g.stream>>>(map_a, map_b, p);
-    else                             tc_matmul_kernel<BSA_MODE_DDS><<<grid, kThreads, kSmemBytes, g.stream>>>(map_a, map_b, p);
+    kernel<<<grid, kThreads, kSmemBytes, g.stream>>>(map_a, map_b, p);
     return launch_status();
 }
 

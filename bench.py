@@ -331,15 +331,22 @@ def run_ours(args):
                                  "hbm_frac": round(dds_gbs / peaks["hbm_gbs"], 4),
                                  "TFLOP/s": round(flops_matmul / (dds_ms * 1e-3) / 1e12, 1),
                                  "tensor_frac": round(flops_matmul / (dds_ms * 1e-3) / 1e12 / peaks["bf16_tflops"], 4)}
-        # dominant kernel = the op family with the largest share of the step
-        matmul_ms = sum(op_ms[n] for n in OPS if not n.startswith("softmax"))
-        softmax_ms = op_ms["softmax_fwd"] + op_ms["softmax_bwd"]
-        if matmul_ms >= softmax_ms:
-            dom, dom_bytes, dom_ms = "block-sparse matmul (6 launches/step)", alg_bytes["sdd_qk"], matmul_ms / 6
-        else:
-            dom = "block-sparse softmax (fwd + bwd)"
-            dom_bytes = (alg_bytes["softmax_fwd"] + alg_bytes["softmax_bwd"]) / 2
-            dom_ms = softmax_ms / 2
+        # dominant kernel = the kernel with the largest total time inside a step
+        kernels = {
+            "tc_matmul_kernel<dsd> (4 launches/step)": ["dsd_pv", "dsd_dv", "dsd_dq", "dsd_dk"],
+            "tc_matmul_kernel<sdd> (2 launches/step)": ["sdd_qk", "sdd_dp"],
+            "softmax_rows_kernel<fwd>": ["softmax_fwd"],
+            "softmax_rows_kernel<bwd>": ["softmax_bwd"],
+        }
+        dom = max(kernels, key=lambda name: sum(op_ms[n] for n in kernels[name]))
+        dom_ops = kernels[dom]
+        dom_bytes = alg_bytes[dom_ops[0]]
+        dom_ms = sum(op_ms[n] for n in dom_ops) / len(dom_ops)
+        # DRAM bytes per launch from the ncu capture under profiles/ (taken at 32 slices, where every
+        # byte of the sparse operand is read once; traffic grows in proportion to the slices)
+        ncu_traffic_per_slice = {"tc_matmul_kernel<dsd> (4 launches/step)": 231.0e6 / 32}
+        traffic = ncu_traffic_per_slice.get(dom)
+        traffic = None if traffic is None else round(traffic * z)
         achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
         cpu_dt = cpu_flops = cpu_heads = None
         if world == 1 and not args.no_cpu:
@@ -356,7 +363,7 @@ def run_ours(args):
                        "layout": "strided(8)+local(2), non-causal", "parallelism": "head-sharded x%d" % world,
                        "l2": "no flush: the four sparse tensors of a step are 400 MB each, above the 126 MB L2"},
             "roofline": {"bound": "hbm", "kernel": dom, "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
-                         "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None,
+                         "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": traffic,
                          "peak_source": peaks["source"]},
             "e2e": {"value": round(e2e_value, 3), "unit": "TFLOP/s", "steps": e2e_steps,
                     "ms_per_step": round(e2e_ms / e2e_steps, 4),

@@ -130,11 +130,11 @@ extern "C" int bsa_matmul(int mode, int dtype, int trans_a, int trans_b,
         if (env && std::strcmp(env, "simt") == 0) engine = BSA_ENGINE_SIMT;
         else if (env && std::strcmp(env, "tcgen05") == 0) engine = BSA_ENGINE_TCGEN05;
     }
-    if (engine == BSA_ENGINE_TCGEN05) {
-        if (!tc_supports(args)) return BSA_ERR_BAD_SHAPE;
-        return matmul_tc(args);
+    if (engine != BSA_ENGINE_SIMT) {
+        if (tc_supports(args)) return matmul_tc(args);        // block 64, 16-bit types
+        if (tc32_supports(args)) return matmul_tc32(args);    // block 32, 16-bit types and fp32 (3xTF32)
+        if (engine == BSA_ENGINE_TCGEN05) return BSA_ERR_BAD_SHAPE;
     }
-    if (engine == BSA_ENGINE_AUTO && tc_supports(args)) return matmul_tc(args);
     return matmul_simt(args);
 }
 

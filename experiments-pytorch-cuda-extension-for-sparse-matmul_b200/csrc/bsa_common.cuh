@@ -67,5 +67,8 @@ int matmul_simt(const MatmulArgs& args);
 // tcgen05 engine covers a problem at all.
 bool tc_supports(const MatmulArgs& args);
 int matmul_tc(const MatmulArgs& args);
+// The same for the block-32 tcgen05 engine (fp16 / bf16, and fp32 as a 3xTF32 split).
+bool tc32_supports(const MatmulArgs& args);
+int matmul_tc32(const MatmulArgs& args);
 
 }  // namespace bsa

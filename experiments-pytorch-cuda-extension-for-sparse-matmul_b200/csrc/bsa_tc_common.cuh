@@ -1,0 +1,256 @@
+// Building blocks shared by the tcgen05 / TMEM matmul kernels (sm_100a only): inline-PTX
+// wrappers for mbarriers, TMA loads, tcgen05 MMA / commit / TMEM loads, bounded waits, the
+// persistent work-item cursor, the warp-wide block-descriptor window and the host-side tensor
+// map encoder.  Everything lives in an anonymous namespace: each kernel file gets its own copy.
+#pragma once
+#include <cstdio>
+#include <mutex>
+
+#include "bsa_common.cuh"
+
+namespace bsa {
+namespace {
+
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // 2 s
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait.  Returns false if the wait was given up (time-out here, or an abort raised by
+// another role of this CTA through `abort_flag`, a word in shared memory).
+__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int* abort_flag, uint32_t* status) {
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+        for (int i = 0; i < 256; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*(volatile int*)abort_flag) return false;
+        if (global_ns() - t0 > kWaitLimitNs) {
+            *(volatile int*)abort_flag = 1;
+            atomicExch(status, (uint32_t)BSA_ERR_DEVICE_TIMEOUT);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* abort_flag, uint32_t* status) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, status);
+}
+
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_ld_32x32b_x64(uint32_t taddr, uint32_t (&r)[64]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+        "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+        "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]),
+          "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]),
+          "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]),
+          "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]),
+          "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+        : "r"(taddr) : "memory");
+}
+// 16 TMEM lanes x 64 columns spread over all 32 threads: thread t gets, for each 8-column
+// unit u, r[4u + 0,1] = (lane t/4, columns 8u + 2(t%4) + 0,1) and r[4u + 2,3] = the same columns
+// of lane t/4 + 8 (the layout of an m16n8 accumulator fragment).
+__device__ __forceinline__ void tc_ld_16x256b_x8(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t (&w)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+}
+
+// Iterates the work items of one CTA (item = blockIdx.x + n * gridDim.x) and keeps the group
+// offset-table words of the next two items in flight, so that by the time an item becomes
+// current its words have arrived and no role stalls on a dependent global load per item.
+// Positions advance incrementally (the host passes gridDim.x split by the items per batch
+// entry): an integer division by a run-time value costs a lone thread hundreds of cycles.
+struct Cursor {
+    int item, stride, items, chunks, per_z, stride_z, stride_rem;
+    const int32_t* table;
+    int item_no;                        // how many items this CTA has finished
+    int z, g, chunk, first, count;      // current item: batch entry, group, slice, block range
+    int z1, r1, a1, b1;                 // next item: batch entry, index inside it, table[g], table[g + 1]
+    int z2, r2, a2, b2;                 // the item after that
+
+    __device__ __forceinline__ void load_words(bool in_range, int rem, int& a, int& b) const {
+        a = 0; b = 0;
+        if (in_range) { const int gg = chunks == 1 ? rem : rem / chunks; a = table[gg]; b = table[gg + 1]; }
+    }
+    __device__ __forceinline__ void step_pos(int& zz, int& rem) const {
+        zz += stride_z;
+        rem += stride_rem;
+        if (rem >= per_z) { rem -= per_z; ++zz; }
+    }
+    __device__ __forceinline__ void set_current(int zz, int rem, int a, int b) {
+        z = zz;
+        g = chunks == 1 ? rem : rem / chunks;
+        chunk = rem - g * chunks;
+        first = a;
+        count = b - a;
+    }
+    template <class Params>
+    __device__ __forceinline__ void init(const Params& p) {
+        item = (int)blockIdx.x; stride = (int)gridDim.x; items = p.items;
+        chunks = p.chunks; per_z = p.groups * p.chunks; table = p.table;
+        stride_z = p.stride_z; stride_rem = p.stride_rem;
+        item_no = 0;
+        z = g = chunk = first = count = 0;
+        int z0 = item / per_z, r0 = item - z0 * per_z, a0, b0;
+        load_words(item < items, r0, a0, b0);
+        z1 = z0; r1 = r0; step_pos(z1, r1);
+        load_words(item + stride < items, r1, a1, b1);
+        z2 = z1; r2 = r1; step_pos(z2, r2);
+        load_words(item + 2 * stride < items, r2, a2, b2);
+        if (item < items) set_current(z0, r0, a0, b0);
+    }
+    __device__ __forceinline__ bool valid() const { return item < items; }
+    __device__ __forceinline__ bool has_next() const { return item + stride < items; }
+    __device__ __forceinline__ int next_first() const { return a1; }
+    __device__ __forceinline__ int next_count() const { return b1 - a1; }
+    __device__ __forceinline__ void advance() {
+        item += stride;
+        ++item_no;
+        const int zc = z1, rc = r1, ac = a1, bc = b1;
+        z1 = z2; r1 = r2; a1 = a2; b1 = b2;
+        step_pos(z2, r2);
+        load_words(item + 2 * stride < items, r2, a2, b2);
+        if (item < items) set_current(zc, rc, ac, bc);
+    }
+};
+
+// A warp-wide window of 32 block descriptors of the current group: lane l holds descriptor
+// base + l and the following 32 are already being loaded.  get() must be called by all 32
+// lanes with the same index, in non-decreasing order; indices may be skipped.
+struct DescWindow {
+    BlockDesc mine, ahead;
+    int base;
+    __device__ __forceinline__ void begin(const BlockDesc* blocks, int first, int count, const BlockDesc& first_chunk,
+                                          int lane) {
+        mine = first_chunk;
+        base = 0;
+        ahead = BlockDesc{0, 0};
+        if (32 + lane < count) ahead = blocks[first + 32 + lane];
+    }
+    __device__ __forceinline__ BlockDesc get(const BlockDesc* blocks, int first, int count, int i, int lane) {
+        while (i >= base + 32) {
+            mine = ahead;
+            base += 32;
+            if (base + 32 + lane < count) ahead = blocks[first + base + 32 + lane];
+        }
+        BlockDesc d;
+        d.idx = __shfl_sync(0xffffffffu, mine.idx, i - base);
+        d.packed = __shfl_sync(0xffffffffu, mine.packed, i - base);
+        return d;
+    }
+};
+
+__device__ __forceinline__ BlockDesc load_first_chunk(const BlockDesc* blocks, int first, int count, int lane) {
+    BlockDesc d{0, 0};
+    if (lane < count) d = blocks[first + lane];
+    return d;
+}
+
+// Hands a fully read TMEM accumulator buffer back to the MMA warps (one arrival per warp).
+__device__ __forceinline__ void release_accumulator(uint64_t* acc_empty, int lane) {
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(acc_empty);
+}
+
+// ------------------------------------------------------------------ host side
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    });
+    return fn;
+}
+
+int sm_count() {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    return sms;
+}
+
+}  // namespace
+}  // namespace bsa

@@ -85,6 +85,27 @@ def test_edge_layouts(name, mode, ta, tb):
             run_case(mode, ta, tb, g["pattern"], block, 64, dtype, engine, batch=(3,), seed=11)
 
 
+def _wide_pattern():
+    """40 x 48 blocks, about 30 % full, with a full row (48 blocks: several accumulations and more than
+    one 32-descriptor window), a full column and an empty row."""
+    rng = np.random.default_rng(0)
+    pattern = (rng.random((40, 48)) < 0.3).astype(np.int64)
+    pattern[3, :] = 1
+    pattern[:, 5] = 1
+    pattern[7, :] = 0
+    return pattern
+
+
+@pytest.mark.parametrize("mode,ta,tb", VARIANTS)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_block32_on_tensor_cores(mode, ta, tb, dtype):
+    """Block 32 on the tcgen05 engine, requested explicitly (it must not fall back): 16-bit types and
+    fp32 as a 3xTF32 split, dense sizes that leave partial slices (96, 160) and the minimum (32)."""
+    pattern = _wide_pattern()
+    for inner in (32, 96, 160):
+        run_case(mode, ta, tb, pattern, 32, inner, dtype, "tcgen05", batch=(2,), seed=31 + inner)
+
+
 def test_config1_sdd_fp32_per_head_layouts():
     """BASELINE config 1: batch 1, heads 2, seq 256, head_dim 64, block 32, Bernoulli(0.5) + diagonal
     per head, Q.K^T as sdd(N,T) in fp32."""

@@ -49,8 +49,6 @@
 namespace bsa {
 namespace {
 
-constexpr int kTile = 64;                       // tile edge in elements
-constexpr int kTileBytes = kTile * kTile * 2;   // 8 KB
 constexpr int kMaxStages = 13;
 constexpr int kStageTiles = 27;                 // operand tiles in all stages: 13 x 2, 9 x 3 or 5 x 5
 constexpr int kAccCols = 256;                   // TMEM columns per accumulator buffer
@@ -103,23 +101,6 @@ struct TcParams {
 };
 
 
-// Shared-memory matrix descriptor of a 16-bit operand made of 64x64 tiles, each stored as 64
-// rows of 128 bytes with the 128-byte swizzle.  For a K-major operand a row is one M/N index
-// and the 8-row groups (1024 B apart, the stride byte offset) run along M/N, so tiles placed
-// back to back continue the operand to 128, 192, 256 rows.  For an MN-major operand a row is
-// one K index, the 8-row groups run along K, and the leading byte offset (8192 B) is the
-// distance between tiles holding consecutive 64-wide ranges of M/N.
-// Bits: start address >> 4 in [0,14), LBO >> 4 in [16,30), SBO >> 4 in [32,46), descriptor
-// version 1 in [46,48), layout type SWIZZLE_128B = 2 in [61,64).
-__device__ __forceinline__ uint64_t make_tile_desc(uint32_t smem_addr, bool mn_major) {
-    uint64_t d = (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)(mn_major ? (kTileBytes >> 4) : 1) << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
-
 // Number of accumulations (each ends in an epilogue) and K-steps per accumulation of an item.
 template <int MODE>
 __device__ __forceinline__ void item_shape(const TcParams& p, int count, int& flushes, int& ksteps) {
@@ -138,21 +119,6 @@ __device__ __forceinline__ int b_tiles(const TcParams& p, int count, int chunk, 
     if (MODE == BSA_MODE_SDD) return min(4, count - 4 * flush);
     if (MODE == BSA_MODE_DSD) return min(2, (p.size_n - chunk * 2 * kTile + kTile - 1) / kTile);
     return 1;
-}
-
-// 4x4 transpose of 32-bit words among the four threads of a quad (lanes 4i .. 4i+3): on entry
-// thread q holds m[u] = element (u, q); on return it holds m[j] = element (q, j).
-__device__ __forceinline__ void quad_transpose(uint32_t (&m)[4], int q) {
-    const bool b0 = (q & 1) != 0, b1 = (q & 2) != 0;
-    uint32_t s0 = b0 ? m[0] : m[1], s1 = b0 ? m[2] : m[3];
-    s0 = __shfl_xor_sync(0xffffffffu, s0, 1);
-    s1 = __shfl_xor_sync(0xffffffffu, s1, 1);
-    if (b0) { m[0] = s0; m[2] = s1; } else { m[1] = s0; m[3] = s1; }
-    s0 = b1 ? m[0] : m[2];
-    s1 = b1 ? m[1] : m[3];
-    s0 = __shfl_xor_sync(0xffffffffu, s0, 2);
-    s1 = __shfl_xor_sync(0xffffffffu, s1, 2);
-    if (b1) { m[0] = s0; m[1] = s1; } else { m[2] = s0; m[3] = s1; }
 }
 
 // Full 64x64 tile of a sparse output: the warp converts its 16 accumulator rows with all 32
@@ -576,26 +542,6 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols)
                      : "memory");
     }
-}
-
-// 3-D tensor map over a row-major [batches, rows, cols] 16-bit tensor with a 64x64x1 box and the
-// 128-byte swizzle.  Out-of-range parts of a box read as zero and are not written.
-bool make_map(CUtensorMap* map, int dtype, const void* base, int64_t batches, int64_t rows, int64_t cols) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return false;
-    const cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batches};
-    const cuuint64_t strides[2] = {(cuuint64_t)cols * 2, (cuuint64_t)rows * (cuuint64_t)cols * 2};
-    const cuuint32_t box[3] = {kTile, kTile, 1};
-    const cuuint32_t elem[3] = {1, 1, 1};
-    const CUtensorMapDataType type = dtype == BSA_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                             : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    const CUresult res = fn(map, type, 3, const_cast<void*>(base), dims, strides, box, elem,
-                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (res != CUDA_SUCCESS)
-        std::fprintf(stderr, "bsa: cuTensorMapEncodeTiled failed with CUresult %d (base %p, dims %lld x %lld x %lld)\n",
-                     (int)res, base, (long long)batches, (long long)rows, (long long)cols);
-    return res == CUDA_SUCCESS;
 }
 
 bool dense_dim_ok(int64_t v) { return v >= kTile && v % 8 == 0 && v < ((int64_t)1 << 31); }

@@ -196,6 +196,55 @@ torch::Tensor sparse_softmax_backward(torch::Tensor y, torch::Tensor dy, torch::
     return dx.reshape(shape);
 }
 
+// Fused block-sparse attention forward: (O, lse) = attention(Q, K, V) over the row layout.
+// q [..., seq_q, d], k and v [..., seq_k, d]; 16-bit types, block 64, d = 64 or 128.
+std::tuple<torch::Tensor, torch::Tensor> sparse_attention_forward(
+        torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor row_blocks, torch::Tensor row_table,
+        int64_t block, int64_t block_cols, double scale, bool causal, c10::optional<torch::Tensor> key_padding_mask) {
+    TORCH_CHECK(q.is_cuda() && k.is_cuda() && v.is_cuda(), "q, k, v must be CUDA tensors");
+    TORCH_CHECK(q.dim() >= 3 && k.dim() == q.dim() && v.dim() == q.dim(), "q, k, v must be [..., seq, head_dim]");
+    TORCH_CHECK(q.scalar_type() == k.scalar_type() && q.scalar_type() == v.scalar_type(), "q, k, v must share a dtype");
+    check_layout({row_blocks, row_table}, q.device(), "row layout");
+    const int dtype = dtype_code(q);
+    const int64_t nnz = row_blocks.size(0) / 2, block_rows = row_table.size(0) - 1, d = q.size(-1);
+    TORCH_CHECK(q.size(-2) == block_rows * block, "q has ", q.size(-2), " rows, the layout ", block_rows * block);
+    TORCH_CHECK(k.size(-2) == block_cols * block && v.size(-2) == block_cols * block,
+                "k and v must have ", block_cols * block, " rows");
+    TORCH_CHECK(k.size(-1) == d && v.size(-1) == d, "q, k, v must share the head dimension");
+    auto lead = q.sizes().vec();
+    lead.pop_back(); lead.pop_back();
+    q = q.flatten(0, -3).contiguous();
+    k = k.flatten(0, -3).contiguous();
+    v = v.flatten(0, -3).contiguous();
+    TORCH_CHECK(k.size(0) == q.size(0) && v.size(0) == q.size(0), "q, k, v must share the leading dimensions");
+    auto o = torch::empty_like(q);
+    auto lse = torch::empty({q.size(0), q.size(1)}, q.options().dtype(torch::kFloat));
+    c10::cuda::CUDAGuard guard(q.device());
+    const uint8_t* kpm = nullptr;
+    int64_t kpm_batches = 0, kpm_stride = 0;
+    torch::Tensor mask;
+    if (key_padding_mask.has_value() && key_padding_mask->defined()) {
+        mask = key_padding_mask->to(q.device()).ne(0).to(torch::kUInt8).contiguous();
+        TORCH_CHECK(mask.dim() == 2, "key_padding_mask must be [batch, seq_k]");
+        TORCH_CHECK(q.size(0) % mask.size(0) == 0, "key_padding_mask batch does not divide the flattened batch");
+        kpm = mask.data_ptr<uint8_t>();
+        kpm_batches = mask.size(0);
+        kpm_stride = mask.size(1);
+    }
+    if (q.numel() > 0) {
+        torch::Tensor ws = workspace_for(q.device());
+        check_status(bsa_attention_forward(dtype, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                           lse.data_ptr<float>(), row_blocks.data_ptr<int>(), row_table.data_ptr<int>(),
+                                           nnz, block_rows, block_cols, q.size(0), d, static_cast<int>(block),
+                                           static_cast<float>(scale), causal, kpm, kpm_batches, kpm_stride,
+                                           ws.data_ptr(), BSA_WORKSPACE_BYTES, at::cuda::getCurrentCUDAStream().stream()),
+                     "sparse_attention_forward");
+    }
+    auto o_shape = lead; o_shape.push_back(q.size(1)); o_shape.push_back(d);
+    auto l_shape = lead; l_shape.push_back(q.size(1));
+    return {o.reshape(o_shape), lse.reshape(l_shape)};
+}
+
 // (row_blocks, row_table, col_blocks, col_table) of a 2-D pattern, built on
 // the pattern's CUDA device.  One host read-back (the block count) sizes the
 // descriptor tensors, like torch.nonzero in the reference (sparse/layout.py:8).
@@ -291,6 +340,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("sparse_softmax_backward", &sparse_softmax_backward, "Gradient of the block-sparse row softmax.",
           py::arg("y"), py::arg("dy"), py::arg("row_blocks"), py::arg("row_table"), py::arg("scale") = 1.0,
           py::arg("max_row_blocks") = 0);
+    m.def("sparse_attention_forward", &sparse_attention_forward,
+          "Fused block-sparse attention forward; returns (output, log-sum-exp).",
+          py::arg("q"), py::arg("k"), py::arg("v"), py::arg("row_blocks"), py::arg("row_table"), py::arg("block"),
+          py::arg("block_cols"), py::arg("scale") = 1.0, py::arg("causal") = false,
+          py::arg("key_padding_mask") = py::none());
     m.def("build_layout", &build_layout, "Build row / column layout metadata on the device.", py::arg("pattern"));
     m.def("dense_to_sparse", &dense_to_sparse, "Gather the layout's blocks from a dense matrix.");
     m.def("sparse_to_dense", &sparse_to_dense, "Scatter blocks into a zero-filled dense matrix.");

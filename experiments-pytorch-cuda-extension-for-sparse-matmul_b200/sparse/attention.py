@@ -1,0 +1,88 @@
+"""Fused block-sparse attention.
+
+    out = softmax(scale * Q K^T + masks, restricted to the layout) V
+
+The reference has no such op: a caller composes it from its matmul in "sdd"
+mode (sparse/matmul.py:55-57), a softmax and its matmul in "dsd" mode, and
+every step writes the ``[..., nnz, block, block]`` tensor to memory.
+``attention`` computes the same result in one kernel launch where the fused
+kernel applies (fp16 / bf16, block 64, head dim 64 or 128) and composes the
+three unfused ops otherwise, so it can be called for any layout and dtype.
+
+The backward pass of the fused path recomputes the probabilities with the
+unfused kernels (the forward keeps only the output and the row
+log-sum-exp), then follows the usual attention gradients:
+
+    P  = softmax(scale * sdd(Q, K^T))          dV = dsd(P^T, dO)
+    dP = sdd(dO, V^T)                          dS = softmax_backward(P, dP)
+    dQ = dsd(dS, K)                            dK = dsd(dS^T, Q)
+"""
+from typing import Any, Optional, Tuple
+
+import torch
+
+from . import kernel
+from .layout import SparseLayout
+from .matmul import matmul
+from .softmax import softmax
+
+
+def fused_supported(q: torch.Tensor, layout: SparseLayout) -> bool:
+    """True where the one-kernel forward applies."""
+    return (q.is_cuda and q.dtype in (torch.float16, torch.bfloat16) and layout.block == 64
+            and q.size(-1) in (64, 128))
+
+
+class SparseAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx: Any, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, layout: SparseLayout,
+                scale: float = 1.0, causal: bool = False,
+                key_padding_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+        row_blocks, row_table = layout.row_layout
+        out, lse = kernel.sparse_ops.sparse_attention_forward(
+            q, k, v, row_blocks, row_table, layout.block, layout.pattern.size(1), float(scale), bool(causal),
+            key_padding_mask)
+        ctx.save_for_backward(q, k, v)
+        ctx.layout, ctx.scale, ctx.causal, ctx.kpm = layout, float(scale), bool(causal), key_padding_mask
+        ctx.lse = lse
+        return out
+
+    @staticmethod
+    def backward(ctx: Any, dout: torch.Tensor) -> Tuple[Optional[torch.Tensor], ...]:
+        q, k, v = ctx.saved_tensors
+        layout, ops = ctx.layout, kernel.sparse_ops
+        rows, cols, block = layout.row_layout, layout.col_layout, layout.block
+        hint = getattr(layout, "max_row_blocks", 0)
+        dout = dout.contiguous()
+        s = ops.sparse_matmul(q, k, "sdd", rows, cols, False, True, block)
+        p = ops.sparse_softmax_forward(s, rows[0], rows[1], ctx.scale, ctx.causal, ctx.kpm, hint)
+        dq = dk = dv = None
+        if ctx.needs_input_grad[2]:
+            dv = ops.sparse_matmul(p, dout, "dsd", rows, cols, True, False, block)
+        if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
+            dp = ops.sparse_matmul(dout, v, "sdd", rows, cols, False, True, block)
+            ds = ops.sparse_softmax_backward(p, dp, rows[0], rows[1], ctx.scale, hint)
+            if ctx.needs_input_grad[0]:
+                dq = ops.sparse_matmul(ds, k, "dsd", rows, cols, False, False, block)
+            if ctx.needs_input_grad[1]:
+                dk = ops.sparse_matmul(ds, q, "dsd", rows, cols, True, False, block)
+        return dq, dk, dv, None, None, None, None
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, layout: SparseLayout, scale: float = 1.0,
+              causal: bool = False, key_padding_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Block-sparse attention of ``q [..., seq_q, d]`` over ``k, v [..., seq_k, d]``."""
+    if fused_supported(q, layout):
+        return SparseAttention.apply(q, k, v, layout, scale, causal, key_padding_mask)
+    scores = matmul(q, k, "sdd", layout, False, True)
+    probs = softmax(scores, layout, scale, causal, key_padding_mask)
+    return matmul(probs, v, "dsd", layout, False, False)
+
+
+def attention_lse(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, layout: SparseLayout, scale: float = 1.0,
+                  causal: bool = False, key_padding_mask: Optional[torch.Tensor] = None):
+    """Forward only: (output, log-sum-exp of the scaled masked scores per query row)."""
+    row_blocks, row_table = layout.row_layout
+    return kernel.sparse_ops.sparse_attention_forward(
+        q, k, v, row_blocks, row_table, layout.block, layout.pattern.size(1), float(scale), bool(causal),
+        key_padding_mask)

@@ -155,6 +155,38 @@ int bsa_softmax_backward(int dtype, const void* y, const void* dy, void* dx,
                          float scale, int64_t max_row_blocks, void* stream);
 
 /*
+ * Fused block-sparse attention forward:
+ *   O = softmax_rows(scale * Q K^T + masks, restricted to the layout) V
+ * in one kernel; the score / probability blocks never reach memory.
+ * No single counterpart in the reference: it composes the same result from
+ * sparse_matmul("sdd", tr_b) (sparse/native/sparse_kernels.cc:7-50), the
+ * softmax kernels (sparse_softmax.cu:208-231) and sparse_matmul("dsd"), with
+ * the [batches, nnz, block, block] tensor written and re-read in between.
+ * This entry point exists beside the three unfused operators; results agree
+ * with their composition within the 16-bit tolerance.
+ *
+ *   q               [batches, block_rows * block, head_dim]
+ *   k, v            [batches, block_cols * block, head_dim]
+ *   o               [batches, block_rows * block, head_dim], same dtype
+ *   lse             NULL or float [batches, block_rows * block]: natural log of
+ *                   the row sums of exp(scale * s + mask); -inf for rows with
+ *                   no unmasked element (their output rows are 0)
+ *   row_blocks,
+ *   row_table       the ROW layout
+ *   causal, key_padding_mask, kpm_batches, kpm_stride
+ *                   as in bsa_softmax_forward
+ * Supported: BSA_DTYPE_F16 / BSA_DTYPE_BF16, block 64, head_dim 64 or 128;
+ * anything else returns BSA_ERR_BAD_DTYPE / BSA_ERR_BAD_SHAPE without
+ * launching (callers then compose the unfused operators).
+ */
+int bsa_attention_forward(int dtype, const void* q, const void* k, const void* v, void* o, float* lse,
+                          const int32_t* row_blocks, const int32_t* row_table,
+                          int64_t nnz, int64_t block_rows, int64_t block_cols, int64_t batches,
+                          int64_t head_dim, int block, float scale, int causal,
+                          const uint8_t* key_padding_mask, int64_t kpm_batches, int64_t kpm_stride,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Gather the blocks of a dense [batches, rows*block, cols*block] matrix into
  * sparse storage (to_sparse, sparse/layout.py:40-45) or scatter them back
  * with zeros elsewhere (to_dense, sparse/layout.py:47-57).  `blocks` is the

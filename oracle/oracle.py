@@ -174,6 +174,23 @@ def attention_forward(q, k, v, pattern, block: int, scale: float, causal: bool =
     return o, p
 
 
+def attention_forward_dense(q, k, v, pattern, block: int, scale: float, causal: bool = False,
+                            key_padding_mask: Optional[torch.Tensor] = None, dtype=torch.float32):
+    """Masked dense attention forward: (out, lse) with lse = log sum exp of the scaled, masked scores
+    per query row (-inf and a zero output row where every score is masked).  This is the composition
+    sdd (sparse_smm_gpu.cu:22-99) -> softmax (sparse_softmax.cu:113-155) -> dsd (sparse_smm_gpu.cu:101-183)
+    written densely."""
+    q = q.detach().cpu().to(dtype)
+    k = k.detach().cpu().to(dtype)
+    v = v.detach().cpu().to(dtype)
+    keep = _score_mask(pattern, block, causal, key_padding_mask, q.shape[:-2])
+    scores = (q @ k.transpose(-1, -2)) * scale
+    scores = scores.masked_fill(~keep, float("-inf"))
+    lse = torch.logsumexp(scores, dim=-1)
+    probs = torch.nan_to_num(torch.softmax(scores, dim=-1), nan=0.0)
+    return probs @ v, lse
+
+
 def attention_step_dense(q, k, v, do, pattern, block: int, scale: float, causal: bool = False,
                          dtype=torch.float32):
     """Forward and backward of masked dense attention through torch autograd.

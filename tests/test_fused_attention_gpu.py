@@ -1,0 +1,123 @@
+"""GPU parity of the fused block-sparse attention kernel (one launch for sdd -> softmax -> dsd)
+against dense masked attention on the CPU.  Tolerance: the 16-bit contract of the unfused
+operators (max |got - ref| / max |ref| <= 1e-2 for fp16, 3e-2 for bf16); the log-sum-exp is an
+fp32 output and is compared absolutely (1e-3)."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_close, load_golden_layout, seeded
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _forward_case(pattern, block, batch, dim, dtype, scale, causal=False, kpm=None, seed=0):
+    from sparse import SparseLayout
+    from sparse.attention import attention_lse
+    from sparse.kernel import sparse_ops
+    pattern = torch.as_tensor(np.asarray(pattern))
+    layout = SparseLayout(pattern, block=block)
+    seq_q, seq_k = pattern.shape[0] * block, pattern.shape[1] * block
+    q = seeded(tuple(batch) + (seq_q, dim), seed, dtype)
+    k = seeded(tuple(batch) + (seq_k, dim), seed + 1, dtype)
+    v = seeded(tuple(batch) + (seq_k, dim), seed + 2, dtype)
+    out, lse = attention_lse(q.cuda(), k.cuda(), v.cuda(), layout, scale, causal,
+                             None if kpm is None else kpm.cuda())
+    torch.cuda.synchronize()
+    sparse_ops.check_device_status(0)
+    ref, ref_lse = oracle.attention_forward_dense(q, k, v, pattern.numpy(), block, scale, causal, kpm)
+    assert out.dtype == dtype and tuple(out.shape) == tuple(ref.shape)
+    assert_close(out, ref, dtype, "fused attention output")
+    lse = lse.float().cpu()
+    dead = torch.isinf(ref_lse)
+    assert torch.equal(torch.isinf(lse), dead), "rows without an unmasked score must report lse = -inf"
+    if (~dead).any():
+        assert float((lse[~dead] - ref_lse[~dead]).abs().max()) <= 1e-3
+    if dead.any():
+        assert float(out.float().cpu()[dead].abs().max()) == 0.0
+    return out
+
+
+@pytest.mark.parametrize("dim", [64, 128])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_fused_forward_strided_local(dim, dtype):
+    from sparse.patterns import strided_local
+    _forward_case(strided_local(64, 8, 2), 64, (2,), dim, dtype, dim ** -0.5, seed=10)
+
+
+@pytest.mark.parametrize("dim", [64, 128])
+def test_fused_forward_empty_rows_nonsquare(dim):
+    g = load_golden_layout("empty_row_col_5x4")     # an empty block row: zeros and lse = -inf
+    _forward_case(g["pattern"], 64, (3,), dim, torch.float16, 0.2, seed=20)
+
+
+def test_fused_forward_many_items_per_cta():
+    """More work items than resident CTAs (8 heads x 64 block rows = 512 items): every CTA walks
+    several items, including rows of 1 block and of 64 blocks (BigBird-style global rows)."""
+    from sparse.patterns import bigbird
+    _forward_case(bigbird(64, 1, 2, 3, 77), 64, (8,), 64, torch.float16, 0.125, seed=30)
+
+
+def test_fused_forward_causal_and_key_padding():
+    from sparse.patterns import local_global_causal
+    pattern = local_global_causal(16, 3, 1)
+    _forward_case(pattern, 64, (2, 2), 64, torch.float16, 0.125, causal=True, seed=40)
+    kpm = torch.zeros(2, 16 * 64, dtype=torch.uint8)
+    kpm[0, 700:] = 1          # pads the tail of batch entry 0, so some rows lose whole blocks
+    kpm[1, 5] = 1
+    kpm[1, 64:128] = 1        # a whole block column padded
+    _forward_case(pattern, 64, (2, 2), 128, torch.bfloat16, 0.1, causal=True, kpm=kpm, seed=41)
+    full = np.ones((4, 4), dtype=np.int64)
+    dead = torch.zeros(1, 256, dtype=torch.uint8)
+    dead[0, :] = 1            # every key padded: all rows dead
+    _forward_case(full, 64, (1,), 64, torch.float16, 1.0, kpm=dead, seed=42)
+
+
+def test_fused_forward_negative_scale_and_large_scores():
+    """The row maximum is taken after scaling (a negative scale flips it), and scores of a few
+    hundred do not overflow the exponentials."""
+    from sparse.patterns import strided_local
+    _forward_case(strided_local(8, 4, 1), 64, (2,), 64, torch.float16, -0.3, seed=50)
+    _forward_case(strided_local(8, 4, 1), 64, (2,), 64, torch.float16, 6.0, seed=51)
+
+
+def test_fused_agrees_with_unfused_composition():
+    """The fused kernel and the three unfused kernels agree far inside the tolerance."""
+    from sparse import SparseLayout, matmul, softmax
+    from sparse.attention import attention_lse
+    from sparse.patterns import strided_local
+    layout = SparseLayout(strided_local(64, 8, 2), block=64)
+    q, k, v = (seeded((4, 4096, 64), 60 + i, torch.float16).cuda() for i in range(3))
+    fused, _ = attention_lse(q, k, v, layout, 0.125)
+    p = softmax(matmul(q, k, "sdd", layout, False, True), layout, 0.125)
+    unfused = matmul(p, v, "dsd", layout, False, False)
+    err = float((fused.float() - unfused.float()).abs().max() / unfused.float().abs().max())
+    assert err <= 3e-3, err
+
+
+def test_autograd_through_fused_attention():
+    from sparse import SparseLayout, attention
+    from sparse.patterns import strided_local
+    pattern = strided_local(16, 4, 1)
+    layout = SparseLayout(pattern, block=64)
+    q, k, v, do = (seeded((2, 1024, 64), 70 + i, torch.float16) for i in range(4))
+    qg, kg, vg = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    out = attention(qg, kg, vg, layout, 0.125)
+    out.backward(do.cuda())
+    ref, dq, dk, dv = oracle.attention_step_dense(q, k, v, do, pattern.numpy(), 64, 0.125, False)
+    assert_close(out, ref, torch.float16, "output")
+    assert_close(qg.grad, dq, torch.float16, "dQ")
+    assert_close(kg.grad, dk, torch.float16, "dK")
+    assert_close(vg.grad, dv, torch.float16, "dV")
+
+
+def test_attention_composes_unfused_ops_where_the_fused_kernel_does_not_apply():
+    from sparse import SparseLayout, attention
+    from sparse.patterns import local_global_causal
+    pattern = local_global_causal(8, 2, 1)
+    layout = SparseLayout(pattern, block=32)
+    q, k, v = (seeded((2, 256, 64), 80 + i) for i in range(3))
+    out = attention(q.cuda(), k.cuda(), v.cuda(), layout, 0.125, True)
+    ref, _ = oracle.attention_forward_dense(q, k, v, pattern.numpy(), 32, 0.125, True)
+    assert_close(out, ref, torch.float32, "fp32 block-32 attention")

@@ -16,12 +16,16 @@
 // rescaling of O (and its dependency chain between softmax and the second matmul) that a
 // one-pass online softmax needs.  K tiles are read twice, the second time from L2.
 //
-// A CTA has 6 warps and 256 TMEM columns, two CTAs share an SM and overlap each other's
-// prologues and epilogues:
+// One thread can issue a tcgen05.mma or commit only every ~150 cycles whatever the MMA's size, and
+// a 64 x 64 block needs 8 + 4 of them, so the issuing is spread over three warps.  A CTA has 8
+// warps and 256 TMEM columns; two CTAs share an SM and overlap each other's prologues and
+// epilogues:
 //   warp 0     TMA producer: Q once per item, K tiles (pass 1), K and V tiles (pass 2)
-//   warp 1     tcgen05.mma issuer; S is double buffered so Q K^T of block j + 1 runs while the
-//              softmax warps work on block j
-//   warps 2-5  softmax: tcgen05.ld with the 16x256b shape (every lane owns 2 rows x 16 columns
+//   warps 1-2  Q K^T issuers: S is double buffered and issuer b owns buffer b (every second
+//              block), so Q K^T of block j + 1 runs while the softmax warps work on block j;
+//              one commit per block signals both "S is ready" and "the K stage is free"
+//   warp 3     P V issuer; one commit per block signals "the P buffer and the V stage are free"
+//   warps 4-7  softmax: tcgen05.ld with the 16x256b shape (every lane owns 2 rows x 16 columns
 //              of a 64 x 64 block), masks, max / exp / sum, pack, 4x4 quad transposes, swizzled
 //              128-bit shared-memory stores of P; at the end the same for O to global memory.
 // All waits are bounded (BSA_ERR_DEVICE_TIMEOUT in the workspace word).
@@ -30,7 +34,17 @@
 namespace bsa {
 namespace {
 
-constexpr int kAttnWarps = 6;
+// Optional role timing (compile with -DBSA_ATTN_TIMING): CTA 0 adds the cycles its roles spent in
+// each phase to 64-bit counters at byte offset 64 of the workspace (slot = counter index).
+#ifdef BSA_ATTN_TIMING
+#define AT_CLOCK() clock64()
+#define AT_ADD(slot, cycles) do { if (blockIdx.x == 0) atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 8 + (slot), (unsigned long long)(cycles)); } while (0)
+#else
+#define AT_CLOCK() 0ll
+#define AT_ADD(slot, cycles) do { } while (0)
+#endif
+
+constexpr int kAttnWarps = 8;
 constexpr int kAttnThreads = kAttnWarps * 32;
 constexpr int kAttnTmemCols = 256;      // O: columns 0 .. head_dim - 1; S buffers: 128 .. 191, 192 .. 255
 constexpr int kSCol0 = 128;
@@ -38,10 +52,12 @@ constexpr int kMaxRing = 4;
 
 struct __align__(8) AttnBarriers {
     uint64_t q_full, q_empty;
-    uint64_t k_full[kMaxRing], k_empty[kMaxRing];
-    uint64_t v_full[kMaxRing], v_empty[kMaxRing];
-    uint64_t s_full[2], s_empty[2];
-    uint64_t p_full[2], p_empty[2];
+    uint64_t k_full[kMaxRing];
+    uint64_t qk_done[kMaxRing];     // the MMAs of one Q K^T have retired: S is ready and the K stage is free
+    uint64_t v_full[kMaxRing];
+    uint64_t pv_done[kMaxRing];     // the MMAs of one P V have retired: the P buffer and the V stage are free
+    uint64_t s_empty[2];
+    uint64_t p_full[kMaxRing];
     uint64_t o_full, o_empty;
     uint64_t drain;
     uint32_t tmem_base;
@@ -57,7 +73,8 @@ struct AttnParams {
     int stride_z, stride_rem;
     int seq_q, seq_k, head_dim;
     int dtiles;                // head_dim / 64
-    int ring, ring_shift;      // K and V pipeline depth (a power of two) and its log2
+    int ring, ring_shift;      // K pipeline depth (a power of two) and its log2
+    int vring, vring_shift;    // V pipeline depth = number of P buffers, and its log2
     float scale_log2;          // scale * log2(e)
     int causal;
     const uint8_t* kpm;        // key padding mask or nullptr
@@ -84,36 +101,33 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
-template <bool BF16>
+template <bool BF16, bool MASKED>
 __global__ void __launch_bounds__(kAttnThreads, 2)
 attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    // tiles: Q (dtiles), K ring (ring x dtiles), V ring (ring x dtiles), P (2)
+    // tiles: Q (dtiles), K ring (ring x dtiles), V ring (vring x dtiles), P (vring)
     const int set_bytes = p.dtiles * kTileBytes;            // one Q / K / V tile set
     uint8_t* q_smem = smem;
     uint8_t* k_smem = q_smem + set_bytes;
     uint8_t* v_smem = k_smem + p.ring * set_bytes;
-    uint8_t* p_smem = v_smem + p.ring * set_bytes;
-    AttnBarriers* bars = reinterpret_cast<AttnBarriers*>(p_smem + 2 * kTileBytes);
+    uint8_t* p_smem = v_smem + p.vring * set_bytes;
+    AttnBarriers* bars = reinterpret_cast<AttnBarriers*>(p_smem + p.vring * kTileBytes);
     int* abort_flag = &bars->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int ring_mask = p.ring - 1;
+    const int ring_mask = p.ring - 1, vring_mask = p.vring - 1;
 
     if (threadIdx.x == 0) {
-        mbar_init(&bars->q_full, 1); mbar_init(&bars->q_empty, 1);
+        mbar_init(&bars->q_full, 1); mbar_init(&bars->q_empty, 2);
         for (int s = 0; s < kMaxRing; ++s) {
-            mbar_init(&bars->k_full[s], 1); mbar_init(&bars->k_empty[s], 1);
-            mbar_init(&bars->v_full[s], 1); mbar_init(&bars->v_empty[s], 1);
+            mbar_init(&bars->k_full[s], 1); mbar_init(&bars->qk_done[s], 1);
+            mbar_init(&bars->v_full[s], 1); mbar_init(&bars->pv_done[s], 1); mbar_init(&bars->p_full[s], 4);
         }
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(&bars->s_full[s], 1); mbar_init(&bars->s_empty[s], 4);
-            mbar_init(&bars->p_full[s], 4); mbar_init(&bars->p_empty[s], 1);
-        }
+        for (int s = 0; s < 2; ++s) mbar_init(&bars->s_empty[s], 4);
         mbar_init(&bars->o_full, 1); mbar_init(&bars->o_empty, 4);
-        mbar_init(&bars->drain, 1);
+        mbar_init(&bars->drain, 3);
         bars->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_shared();
@@ -132,6 +146,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         // ------------------------------------------------------------ TMA producer
         int k_no = 0, v_no = 0, q_no = 0;          // tile sets loaded so far
         bool ok = true;
+        const long long tp_begin = AT_CLOCK();
         Cursor cur;
         cur.init(p);
         BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
@@ -141,7 +156,9 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             const int n = cur.count;
             if (n > 0) {
                 if (lane == 0) {
+                    const long long tq = AT_CLOCK();
                     ok = mbar_wait(&bars->q_empty, (uint32_t)(q_no & 1) ^ 1u, abort_flag, p.status);
+                    AT_ADD(0, AT_CLOCK() - tq);
                     if (ok) {
                         mbar_expect_tx(&bars->q_full, (uint32_t)set_bytes);
                         for (int t = 0; t < p.dtiles; ++t)
@@ -155,73 +172,65 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     win.begin(p.blocks, cur.first, cur.count, pre, lane);
                     for (int j = 0; ok && j < n; ++j) {
                         const int col = win.get(p.blocks, cur.first, cur.count, j, lane).col();
-                        if (lane == 0) {
-                            const int ks = k_no & ring_mask;
-                            ok = mbar_wait(&bars->k_empty[ks], ((uint32_t)(k_no >> p.ring_shift) & 1u) ^ 1u, abort_flag, p.status);
-                            if (ok) {
-                                mbar_expect_tx(&bars->k_full[ks], (uint32_t)set_bytes);
-                                for (int t = 0; t < p.dtiles; ++t)
-                                    tma_load_3d(k_smem + ks * set_bytes + t * kTileBytes, &map_k, &bars->k_full[ks],
-                                                t * kTile, col * kTile, cur.z);
-                            }
-                            if (ok && pass == 1) {
-                                const int vs = v_no & ring_mask;
-                                ok = mbar_wait(&bars->v_empty[vs], ((uint32_t)(v_no >> p.ring_shift) & 1u) ^ 1u, abort_flag, p.status);
-                                if (ok) {
-                                    mbar_expect_tx(&bars->v_full[vs], (uint32_t)set_bytes);
-                                    for (int t = 0; t < p.dtiles; ++t)
-                                        tma_load_3d(v_smem + vs * set_bytes + t * kTileBytes, &map_v, &bars->v_full[vs],
-                                                    t * kTile, col * kTile, cur.z);
-                                }
-                            }
+                        // One copy per lane, all issued by the same instruction (issuing costs a thread
+                        // ~300 cycles per instruction, not per copy): lanes 0 .. dtiles-1 load the K
+                        // tiles, in pass 2 lanes dtiles .. 2*dtiles-1 the V tiles of this block.
+                        const bool is_v = lane >= p.dtiles;
+                        const bool mine = lane < (pass == 1 ? 2 * p.dtiles : p.dtiles);
+                        const int t = is_v ? lane - p.dtiles : lane;
+                        const int no = is_v ? v_no : k_no;
+                        const int stage = is_v ? (no & vring_mask) : (no & ring_mask);
+                        const uint32_t parity = ((uint32_t)(no >> (is_v ? p.vring_shift : p.ring_shift)) & 1u) ^ 1u;
+                        uint64_t* reuse = is_v ? &bars->pv_done[stage] : &bars->qk_done[stage];
+                        uint64_t* full = is_v ? &bars->v_full[stage] : &bars->k_full[stage];
+                        uint8_t* dst = (is_v ? v_smem : k_smem) + stage * set_bytes + t * kTileBytes;
+                        const CUtensorMap* map = is_v ? &map_v : &map_k;
+                        bool lane_ok = true;
+                        if (mine) {
+                            const long long t0 = AT_CLOCK();
+                            lane_ok = mbar_wait(reuse, parity, abort_flag, p.status);
+                            if (lane == 0) AT_ADD(1, AT_CLOCK() - t0);
+                        }
+                        ok = __all_sync(0xffffffffu, lane_ok) != 0;
+                        if (ok && mine) {
+                            const long long t1 = AT_CLOCK();
+                            if (t == 0) mbar_expect_tx(full, (uint32_t)set_bytes);
+                            tma_load_3d(dst, map, full, t * kTile, col * kTile, cur.z);
+                            if (lane == 0) AT_ADD(3, AT_CLOCK() - t1);
                         }
                         ++k_no;
                         if (pass == 1) ++v_no;
-                        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
                     }
                 }
             }
             pre = pre_next;
             cur.advance();
         }
+        if (lane == 0) AT_ADD(4, AT_CLOCK() - tp_begin);
         if (lane == 0 && *(volatile int*)abort_flag) {
             // Give copies that were issued a bounded chance to land before the CTA exits.
             const unsigned long long t0 = global_ns();
-            for (int s = 0; s < p.ring; ++s) {
+            for (int s = 0; s < p.ring; ++s)
                 while (!mbar_try_wait(&bars->k_full[s], 0) && !mbar_try_wait(&bars->k_full[s], 1) &&
                        global_ns() - t0 < kWaitLimitNs / 4) {}
+            for (int s = 0; s < p.vring; ++s)
                 while (!mbar_try_wait(&bars->v_full[s], 0) && !mbar_try_wait(&bars->v_full[s], 1) &&
                        global_ns() - t0 < kWaitLimitNs / 4) {}
-            }
             while (!mbar_try_wait(&bars->q_full, 0) && !mbar_try_wait(&bars->q_full, 1) &&
                    global_ns() - t0 < kWaitLimitNs / 4) {}
         }
         __syncwarp();
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer
+    } else if (warp == 1 || warp == 2) {
+        // ------------------------------------------------------------ Q K^T issuers
+        // The S tiles of a CTA are numbered in the order they are produced (per item: pass 1
+        // blocks, then pass 2 blocks); tile s goes to S buffer s & 1 and is issued by issuer s & 1.
+        // K stage s & (ring - 1) therefore always belongs to the same issuer.
+        const int w = warp - 1;
         if (lane == 0) {
-            int k_no = 0, v_no = 0, s_no = 0, p_no = 0, q_no = 0;   // consumed K / V sets, produced S, consumed P, items
+            int s_no = 0, q_no = 0;
             bool ok = true;
-            const uint32_t idesc_qk = p.idesc_qk, idesc_pv = p.idesc_pv;
-            // S_j = Q K_{c_j}^T into S buffer s_no & 1
-            auto issue_qk = [&]() -> bool {
-                const int ks = k_no & ring_mask, sb = s_no & 1;
-                if (!mbar_wait(&bars->k_full[ks], (uint32_t)(k_no >> p.ring_shift) & 1u, abort_flag, p.status)) return false;
-                if (!mbar_wait(&bars->s_empty[sb], ((uint32_t)(s_no >> 1) & 1u) ^ 1u, abort_flag, p.status)) return false;
-                tc_fence_after();
-                const uint32_t d = tmem_base + (uint32_t)(kSCol0 + sb * kTile);
-                for (int t = 0; t < p.dtiles; ++t) {
-                    const uint64_t da = make_tile_desc(smem_u32(q_smem + t * kTileBytes), false);
-                    const uint64_t db = make_tile_desc(smem_u32(k_smem + ks * set_bytes + t * kTileBytes), false);
-#pragma unroll
-                    for (int kk = 0; kk < kTile / 16; ++kk)
-                        tc_mma_f16(d, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc_qk, (t > 0 || kk > 0) ? 1u : 0u);
-                }
-                tc_commit(&bars->k_empty[ks]);
-                tc_commit(&bars->s_full[sb]);
-                ++k_no; ++s_no;
-                return true;
-            };
+            const uint32_t idesc_qk = p.idesc_qk;
+            const uint32_t d = tmem_base + (uint32_t)(kSCol0 + w * kTile);
             Cursor cur;
             cur.init(p);
             for (; ok && cur.valid(); cur.advance()) {
@@ -229,36 +238,71 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 if (n == 0) continue;               // empty row: the softmax warps write zeros on their own
                 ok = mbar_wait(&bars->q_full, (uint32_t)(q_no & 1), abort_flag, p.status);
                 if (!ok) break;
-                for (int j = 0; ok && j < n; ++j) ok = issue_qk();          // pass 1
-                if (ok) ok = issue_qk();                                    // pass 2, block 0
-                for (int j = 0; ok && j < n; ++j) {
-                    if (j + 1 < n) {
-                        ok = issue_qk();            // runs while the softmax warps work on block j
-                        if (!ok) break;
-                    } else {
-                        tc_commit(&bars->q_empty);  // last read of Q has been issued
-                    }
-                    const int vs = v_no & ring_mask, pb = p_no & 1;
-                    if (j == 0) ok = mbar_wait(&bars->o_empty, (uint32_t)(q_no & 1) ^ 1u, abort_flag, p.status);
-                    if (ok) ok = mbar_wait(&bars->v_full[vs], (uint32_t)(v_no >> p.ring_shift) & 1u, abort_flag, p.status);
-                    if (ok) ok = mbar_wait(&bars->p_full[pb], (uint32_t)(p_no >> 1) & 1u, abort_flag, p.status);
+                const int s_end = s_no + 2 * n;
+                for (int s = s_no + ((w - s_no) & 1); s < s_end; s += 2) {
+                    const int ks = s & ring_mask;
+                    const long long t0 = AT_CLOCK();
+                    ok = mbar_wait(&bars->k_full[ks], (uint32_t)(s >> p.ring_shift) & 1u, abort_flag, p.status);
+                    const long long t1 = AT_CLOCK();
+                    if (ok) ok = mbar_wait(&bars->s_empty[w], ((uint32_t)(s >> 1) & 1u) ^ 1u, abort_flag, p.status);
                     if (!ok) break;
+                    const long long t2 = AT_CLOCK();
+                    tc_fence_after();
+                    for (int t = 0; t < p.dtiles; ++t) {
+                        const uint64_t da = make_tile_desc(smem_u32(q_smem + t * kTileBytes), false);
+                        const uint64_t db = make_tile_desc(smem_u32(k_smem + ks * set_bytes + t * kTileBytes), false);
+#pragma unroll
+                        for (int kk = 0; kk < kTile / 16; ++kk)
+                            tc_mma_f16(d, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc_qk, (t > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    tc_commit(&bars->qk_done[ks]);
+                    if (w == 0) { AT_ADD(11, t1 - t0); AT_ADD(12, t2 - t1); AT_ADD(13, AT_CLOCK() - t2); }
+                }
+                if (!ok) break;
+                tc_commit(&bars->q_empty);          // this issuer's last read of Q has been issued
+                s_no = s_end;
+                ++q_no;
+            }
+            // All MMAs issued by this thread must have retired before TMEM is freed.
+            tc_commit(&bars->drain);
+            mbar_wait(&bars->drain, 0, abort_flag, p.status);
+        }
+        __syncwarp();
+    } else if (warp == 3) {
+        // ------------------------------------------------------------ P V issuer
+        if (lane == 0) {
+            int p_no = 0, o_no = 0;
+            bool ok = true;
+            const uint32_t idesc_pv = p.idesc_pv;
+            Cursor cur;
+            cur.init(p);
+            for (; ok && cur.valid(); cur.advance()) {
+                const int n = cur.count;
+                if (n == 0) continue;
+                for (int j = 0; ok && j < n; ++j, ++p_no) {
+                    const int pb = p_no & vring_mask;
+                    const long long t0 = AT_CLOCK();
+                    if (j == 0) ok = mbar_wait(&bars->o_empty, (uint32_t)(o_no & 1) ^ 1u, abort_flag, p.status);
+                    const long long t1 = AT_CLOCK();
+                    if (ok) ok = mbar_wait(&bars->v_full[pb], (uint32_t)(p_no >> p.vring_shift) & 1u, abort_flag, p.status);
+                    const long long t2 = AT_CLOCK();
+                    if (ok) ok = mbar_wait(&bars->p_full[pb], (uint32_t)(p_no >> p.vring_shift) & 1u, abort_flag, p.status);
+                    if (!ok) break;
+                    const long long t3 = AT_CLOCK();
                     tc_fence_after();
                     // O += P_j V_{c_j}: A = P (K-major), B = V tiles (N contiguous), N = head_dim
                     const uint64_t da = make_tile_desc(smem_u32(p_smem + pb * kTileBytes), false);
-                    const uint64_t db = make_tile_desc(smem_u32(v_smem + vs * set_bytes), true);
+                    const uint64_t db = make_tile_desc(smem_u32(v_smem + pb * set_bytes), true);
 #pragma unroll
                     for (int kk = 0; kk < kTile / 16; ++kk)
                         tc_mma_f16(tmem_base, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * (2048 >> 4)), idesc_pv,
                                    (j > 0 || kk > 0) ? 1u : 0u);
-                    tc_commit(&bars->v_empty[vs]);
-                    tc_commit(&bars->p_empty[pb]);
+                    tc_commit(&bars->pv_done[pb]);
                     if (j == n - 1) tc_commit(&bars->o_full);
-                    ++v_no; ++p_no;
+                    AT_ADD(14, t1 - t0); AT_ADD(15, t2 - t1); AT_ADD(16, t3 - t2); AT_ADD(17, AT_CLOCK() - t3);
                 }
-                ++q_no;
+                ++o_no;
             }
-            // All MMAs issued by this thread must have retired before TMEM is freed.
             tc_commit(&bars->drain);
             mbar_wait(&bars->drain, 0, abort_flag, p.status);
         }
@@ -270,9 +314,11 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const int row_a = quad * 16 + (lane >> 2);  // this lane's two rows of the 64-row block
         const int row_b = row_a + 8;
         const uint32_t lane_field = (uint32_t)(quad * 32) << 16;
-        const bool masked_op = p.causal != 0 || p.kpm != nullptr;
+        // MASKED = false: no causal or key-padding mask, all mask tests fold away
+        const bool masked_op = MASKED && (p.causal != 0 || p.kpm != nullptr);
         int s_no = 0, p_no = 0, o_no = 0;
         bool ok = true;
+        const long long t_begin = AT_CLOCK();
         Cursor cur;
         cur.init(p);
         BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
@@ -317,49 +363,70 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     return m;
                 };
                 const float c2 = p.scale_log2;
-                // ---- pass 1: row maxima of scale * log2(e) * S
-                float m_a = -INFINITY, m_b = -INFINITY;
+                const bool flip = c2 < 0.f;
+                // ---- the row's 2n S tiles as one stream: tiles 0 .. n-1 are pass 1 (row maxima of
+                // scale * log2(e) * S), tiles n .. 2n-1 pass 2 (P = exp2(scale * log2(e) * S - m) as a
+                // K-major operand tile, row sums).  The TMEM load of tile t + 1 is in flight while tile
+                // t is worked on (two register buffers, loop unrolled by two).
+                float m_a = -INFINITY, m_b = -INFINITY, sub_a = 0.f, sub_b = 0.f, l_a = 0.f, l_b = 0.f;
                 DescWindow win;
                 win.begin(p.blocks, cur.first, cur.count, pre, lane);
-                for (int j = 0; ok && j < n; ++j, ++s_no) {
-                    const int sb = s_no & 1;
-                    const int col = masked_op ? win.get(p.blocks, cur.first, cur.count, j, lane).col() : 0;
-                    const uint32_t mask = masked_op ? block_mask(col) : 0u;
-                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[sb], (uint32_t)(s_no >> 1) & 1u, abort_flag, p.status)) != 0;
-                    if (!ok) break;
+                const int tiles = 2 * n;
+                const uint32_t p_row = (uint32_t)(row_a * 128 + 4 * q4), p_xor = (uint32_t)(row_a & 7);
+                auto load = [&](uint32_t (&r)[32], int t) -> bool {       // wait for S tile t, start loading it
+                    const int s = s_no + t;
+                    if (!__all_sync(0xffffffffu, mbar_wait(&bars->qk_done[s & ring_mask], (uint32_t)(s >> p.ring_shift) & 1u,
+                                                           abort_flag, p.status)))
+                        return false;
                     tc_fence_after();
-                    uint32_t r[32];
-                    tc_ld_16x256b_x8(tmem_base + lane_field + (uint32_t)(kSCol0 + sb * kTile), r);
+                    tc_ld_16x256b_x8(tmem_base + lane_field + (uint32_t)(kSCol0 + (s & 1) * kTile), r);
+                    return true;
+                };
+                auto loaded = [&](int t) {                                 // tile t is in registers: free its buffer
                     tc_wait_ld();
-                    release_accumulator(&bars->s_empty[sb], lane);
+                    release_accumulator(&bars->s_empty[(s_no + t) & 1], lane);
+                };
+                auto process = [&](const uint32_t (&r)[32], int t) -> bool {
+                    if (t == n) {
+                        // between the passes: maxima over the quad, scaled; a row without an unmasked
+                        // score subtracts 0 (all its probabilities are masked to 0 below)
+                        m_a = fmaxf(m_a, __shfl_xor_sync(0xffffffffu, m_a, 1)); m_a = fmaxf(m_a, __shfl_xor_sync(0xffffffffu, m_a, 2));
+                        m_b = fmaxf(m_b, __shfl_xor_sync(0xffffffffu, m_b, 1)); m_b = fmaxf(m_b, __shfl_xor_sync(0xffffffffu, m_b, 2));
+                        m_a = m_a == -INFINITY ? -INFINITY : m_a * fabsf(c2);     // now the maxima of c2 * S
+                        m_b = m_b == -INFINITY ? -INFINITY : m_b * fabsf(c2);
+                        sub_a = m_a == -INFINITY ? 0.f : m_a;
+                        sub_b = m_b == -INFINITY ? 0.f : m_b;
+                        if (MASKED) win.begin(p.blocks, cur.first, cur.count, pre, lane);   // indices restart
+                    }
+                    uint32_t mask = 0u;
+                    if (MASKED && masked_op) mask = block_mask(win.get(p.blocks, cur.first, cur.count, t < n ? t : t - n, lane).col());
+                    if (t < n) {
+                        // extreme of the raw scores: the maximum for a positive scale, the minimum
+                        // (kept negated) for a negative one; scaled between the passes
+                        if (!flip) {
 #pragma unroll
-                    for (int u = 0; u < 8; ++u)
+                            for (int i = 0; i < 16; ++i) {
+                                const int u = i >> 1, e = i & 1;
+                                if (!MASKED || !((mask >> i) & 1u)) m_a = fmaxf(m_a, __uint_as_float(r[4 * u + e]));
+                                if (!MASKED || !((mask >> (16 + i)) & 1u)) m_b = fmaxf(m_b, __uint_as_float(r[4 * u + 2 + e]));
+                            }
+                        } else {
 #pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const float ta = __uint_as_float(r[4 * u + e]) * c2, tb = __uint_as_float(r[4 * u + 2 + e]) * c2;
-                            if (!((mask >> (2 * u + e)) & 1u)) m_a = fmaxf(m_a, ta);
-                            if (!((mask >> (16 + 2 * u + e)) & 1u)) m_b = fmaxf(m_b, tb);
+                            for (int i = 0; i < 16; ++i) {
+                                const int u = i >> 1, e = i & 1;
+                                if (!MASKED || !((mask >> i) & 1u)) m_a = fmaxf(m_a, -__uint_as_float(r[4 * u + e]));
+                                if (!MASKED || !((mask >> (16 + i)) & 1u)) m_b = fmaxf(m_b, -__uint_as_float(r[4 * u + 2 + e]));
+                            }
                         }
-                }
-                if (!ok) break;
-                m_a = fmaxf(m_a, __shfl_xor_sync(0xffffffffu, m_a, 1)); m_a = fmaxf(m_a, __shfl_xor_sync(0xffffffffu, m_a, 2));
-                m_b = fmaxf(m_b, __shfl_xor_sync(0xffffffffu, m_b, 1)); m_b = fmaxf(m_b, __shfl_xor_sync(0xffffffffu, m_b, 2));
-                const float sub_a = m_a == -INFINITY ? 0.f : m_a, sub_b = m_b == -INFINITY ? 0.f : m_b;
-                // ---- pass 2: P = exp2(scale * log2(e) * S - m) as a K-major operand tile, row sums
-                float l_a = 0.f, l_b = 0.f;
-                win.begin(p.blocks, cur.first, cur.count, pre, lane);
-                for (int j = 0; ok && j < n; ++j, ++s_no, ++p_no) {
-                    const int sb = s_no & 1, pb = p_no & 1;
-                    const int col = masked_op ? win.get(p.blocks, cur.first, cur.count, j, lane).col() : 0;
-                    const uint32_t mask = masked_op ? block_mask(col) : 0u;
-                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[sb], (uint32_t)(s_no >> 1) & 1u, abort_flag, p.status)) != 0;
-                    if (!ok) break;
-                    tc_fence_after();
-                    uint32_t r[32];
-                    tc_ld_16x256b_x8(tmem_base + lane_field + (uint32_t)(kSCol0 + sb * kTile), r);
-                    tc_wait_ld();
-                    release_accumulator(&bars->s_empty[sb], lane);
-                    uint32_t w_a[8], w_b[8];            // packed pairs: columns 8u + 2 * q4 + {0, 1}
+                        return true;
+                    }
+                    // the P buffer must have been read by the MMAs that used it last
+                    const int pb = p_no & vring_mask;
+                    if (!__all_sync(0xffffffffu, mbar_wait(&bars->pv_done[pb], ((uint32_t)(p_no >> p.vring_shift) & 1u) ^ 1u, abort_flag, p.status)))
+                        return false;
+                    // every lane owns the column pairs 8u + 2 * q4 + {0, 1} of its two rows: one 32-bit
+                    // word each, stored straight into the 128-byte-swizzled tile (32 lanes hit 32 banks)
+                    const uint32_t tile = smem_u32(p_smem + pb * kTileBytes) + p_row;
 #pragma unroll
                     for (int u = 0; u < 8; ++u) {
                         float pa[2], pb2[2];
@@ -367,39 +434,44 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         for (int e = 0; e < 2; ++e) {
                             pa[e] = attn_exp2(fmaf(__uint_as_float(r[4 * u + e]), c2, -sub_a));
                             pb2[e] = attn_exp2(fmaf(__uint_as_float(r[4 * u + 2 + e]), c2, -sub_b));
-                            if ((mask >> (2 * u + e)) & 1u) pa[e] = 0.f;
-                            if ((mask >> (16 + 2 * u + e)) & 1u) pb2[e] = 0.f;
+                            if (MASKED && ((mask >> (2 * u + e)) & 1u)) pa[e] = 0.f;
+                            if (MASKED && ((mask >> (16 + 2 * u + e)) & 1u)) pb2[e] = 0.f;
                             l_a += pa[e];
                             l_b += pb2[e];
                         }
-                        w_a[u] = pack2<BF16>(pa[0], pa[1]);
-                        w_b[u] = pack2<BF16>(pb2[0], pb2[1]);
-                    }
-                    // the P buffer must have been read by the MMAs of two blocks ago
-                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->p_empty[pb], ((uint32_t)(p_no >> 1) & 1u) ^ 1u, abort_flag, p.status)) != 0;
-                    if (!ok) break;
-                    uint8_t* tile = p_smem + pb * kTileBytes;
-#pragma unroll
-                    for (int half = 0; half < 2; ++half) {     // columns 32 * half .. 32 * half + 31
-                        uint32_t ta[4] = {w_a[4 * half], w_a[4 * half + 1], w_a[4 * half + 2], w_a[4 * half + 3]};
-                        uint32_t tb[4] = {w_b[4 * half], w_b[4 * half + 1], w_b[4 * half + 2], w_b[4 * half + 3]};
-                        quad_transpose(ta, q4);                // now columns 32 * half + 8 * q4 .. + 7 of the row
-                        quad_transpose(tb, q4);
-                        const int chunk = 4 * half + q4;       // 16-byte piece of the 128-byte row
-                        *reinterpret_cast<uint4*>(tile + row_a * 128 + ((chunk ^ (row_a & 7)) << 4)) = make_uint4(ta[0], ta[1], ta[2], ta[3]);
-                        *reinterpret_cast<uint4*>(tile + row_b * 128 + ((chunk ^ (row_b & 7)) << 4)) = make_uint4(tb[0], tb[1], tb[2], tb[3]);
+                        const uint32_t addr = tile + (((uint32_t)u ^ p_xor) << 4);
+                        asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(pack2<BF16>(pa[0], pa[1])) : "memory");
+                        asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + 8 * 128), "r"(pack2<BF16>(pb2[0], pb2[1])) : "memory");
                     }
                     fence_async_shared();           // generic-proxy writes -> visible to the tensor core's reads
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars->p_full[pb]);
+                    ++p_no;
+                    return true;
+                };
+                {
+                    uint32_t ra[32], rb[32];
+                    ok = load(ra, 0);
+                    for (int t = 0; ok && t < tiles; t += 2) {
+                        loaded(t);
+                        if (t + 1 < tiles) ok = load(rb, t + 1);
+                        if (!process(ra, t)) ok = false;
+                        if (!ok || t + 1 >= tiles) break;
+                        loaded(t + 1);
+                        if (t + 2 < tiles) ok = load(ra, t + 2);
+                        if (!process(rb, t + 1)) ok = false;
+                    }
+                    s_no += tiles;
                 }
                 if (!ok) break;
                 l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
                 l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
                 const float inv_a = l_a > 0.f ? 1.f / l_a : 0.f, inv_b = l_b > 0.f ? 1.f / l_b : 0.f;
                 // ---- end of the row: O / l
+                const long long te0 = AT_CLOCK();
                 ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full, (uint32_t)(o_no & 1), abort_flag, p.status)) != 0;
                 if (!ok) break;
+                const long long te1 = AT_CLOCK();
                 tc_fence_after();
                 for (int t = 0; t < p.dtiles; ++t) {
                     uint32_t r[32];
@@ -423,6 +495,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     }
                 }
                 ++o_no;
+                if (warp == 4 && lane == 0) { AT_ADD(8, te1 - te0); AT_ADD(9, AT_CLOCK() - te1); }
                 if (q4 == 0 && p.lse) {
                     // natural-log sum of exponentials of the scaled, masked scores
                     p.lse[lse_a] = l_a > 0.f ? (m_a + log2f(l_a)) * 0.6931471805599453f : -INFINITY;
@@ -432,6 +505,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             pre = pre_next;
             cur.advance();
         }
+        if (warp == 4 && lane == 0) AT_ADD(10, AT_CLOCK() - t_begin);
     }
 
     // ---------------------------------------------------------------- teardown
@@ -454,12 +528,19 @@ int attention_forward(int dtype, const void* q, const void* k, const void* v, vo
                       const uint8_t* kpm, int64_t kpm_batches, int64_t kpm_stride, uint32_t* workspace,
                       cudaStream_t stream) {
     using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const AttnParams);
-    const KernelFn kernel = dtype == BSA_DTYPE_BF16 ? attention_forward_kernel<true> : attention_forward_kernel<false>;
+    const bool masked = causal != 0 || kpm != nullptr;
+    const KernelFn kernel = dtype == BSA_DTYPE_BF16
+        ? (masked ? attention_forward_kernel<true, true> : attention_forward_kernel<true, false>)
+        : (masked ? attention_forward_kernel<false, true> : attention_forward_kernel<false, false>);
     AttnParams p{};
     p.dtiles = (int)(head_dim / kTile);
     p.ring = p.dtiles == 1 ? 4 : 2;
     p.ring_shift = p.dtiles == 1 ? 2 : 1;
-    const int smem_bytes = 1024 + ((1 + 2 * p.ring) * p.dtiles + 2) * kTileBytes + (int)sizeof(AttnBarriers);
+    p.vring = p.dtiles == 1 ? 4 : 2;
+    p.vring_shift = p.dtiles == 1 ? 2 : 1;
+    // at least 80 KB, so that never more than two CTAs (256 TMEM columns each) share an SM
+    int smem_bytes = 1024 + ((1 + p.ring + p.vring) * p.dtiles + p.vring) * kTileBytes + (int)sizeof(AttnBarriers);
+    if (smem_bytes < 80 * 1024) smem_bytes = 80 * 1024;
     // Set on every call (a per-device attribute); this and the cudaSetDevice below also bind the
     // device's primary context to the calling thread, which the driver call behind make_map needs.
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) {

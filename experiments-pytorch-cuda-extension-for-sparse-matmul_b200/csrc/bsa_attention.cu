@@ -6,24 +6,26 @@
 // [batch, nnz, block, block] tensor to memory; this entry point has no counterpart there and
 // exists beside the three unfused operators.
 //
-// Work item = one block row r of one batch entry (64 query rows).  Two passes over the row's
-// blocks c_0 .. c_{n-1}, both on the tensor cores (tcgen05, fp32 accumulators in TMEM):
-//   pass 1   S_j = Q_r K_{c_j}^T              -> row maxima m of scale * S (+ masks)
-//   pass 2   S_j again, P_j = exp(scale * S_j - m) written as a 16-bit K-major operand tile to
-//            shared memory, O += P_j V_{c_j}   -> row sums l accumulate next to it
-//   end      O / l -> global, lse = m + log l
-// Recomputing S costs tensor-core time that is idle anyway and removes the running-maximum
-// rescaling of O (and its dependency chain between softmax and the second matmul) that a
-// one-pass online softmax needs.  K tiles are read twice, the second time from L2.
+// Work item = one block row r of one batch entry (64 query rows).  One pass over the row's
+// blocks c_0 .. c_{n-1}, both products on the tensor cores (tcgen05, fp32 accumulators in TMEM):
+//   S_j = Q_r K_{c_j}^T; P_j = exp(scale * S_j - m) written as a 16-bit K-major operand tile to
+//   shared memory; O += P_j V_{c_j}; the row sums l accumulate next to it; at the end O / l goes
+//   to global memory and lse = m + log l.
+// m is a running row maximum that is raised lazily: only when a block's maximum exceeds it by more
+// than 8 (in units of log2), so P never exceeds 2^8 and the rescaling of O and l by
+// exp(m_old - m_new), a TMEM round trip that has to wait for the previous P V, is rare (for scores
+// of similar size it happens in a row's first blocks only).  The result does not depend on when m
+// is raised: O and l carry the same factor.
 //
 // One thread can issue a tcgen05.mma or commit only every ~150 cycles whatever the MMA's size, and
 // a 64 x 64 block needs 8 + 4 of them, so the issuing is spread over three warps.  A CTA has 8
 // warps and 256 TMEM columns; two CTAs share an SM and overlap each other's prologues and
 // epilogues:
-//   warp 0     TMA producer: Q once per item, K tiles (pass 1), K and V tiles (pass 2)
-//   warps 1-2  Q K^T issuers: S is double buffered and issuer b owns buffer b (every second
-//              block), so Q K^T of block j + 1 runs while the softmax warps work on block j;
-//              one commit per block signals both "S is ready" and "the K stage is free"
+//   warp 0     TMA producer of Q (once per item) and of every block's K tiles (one copy per lane)
+//   warp 1     Q K^T issuer: S is double buffered, so Q K^T of block j + 1 runs while the softmax
+//              warps work on block j; one commit per block signals both "S is ready" and "the K
+//              stage is free"
+//   warp 2     TMA producer of the V tiles
 //   warp 3     P V issuer; one commit per block signals "the P buffer and the V stage are free"
 //   warps 4-7  softmax: tcgen05.ld with the 16x256b shape (every lane owns 2 rows x 16 columns
 //              of a 64 x 64 block), masks, max / exp / sum, pack, 4x4 quad transposes, swizzled
@@ -91,6 +93,20 @@ __device__ __forceinline__ float attn_exp2(float x) {
     return y;
 }
 
+// 16 TMEM lanes x 16 columns, same thread mapping as the .x8 load of the common header:
+// r[4u + 0,1] = (lane t/4, columns 8u + 2(t%4) + 0,1), r[4u + 2,3] = the same columns of lane t/4 + 8.
+__device__ __forceinline__ void tc_ld_16x256b_x2(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_st_16x256b_x2(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.16x256b.x2.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     if (BF16) {
@@ -120,14 +136,14 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int ring_mask = p.ring - 1, vring_mask = p.vring - 1;
 
     if (threadIdx.x == 0) {
-        mbar_init(&bars->q_full, 1); mbar_init(&bars->q_empty, 2);
+        mbar_init(&bars->q_full, 1); mbar_init(&bars->q_empty, 1);
         for (int s = 0; s < kMaxRing; ++s) {
             mbar_init(&bars->k_full[s], 1); mbar_init(&bars->qk_done[s], 1);
             mbar_init(&bars->v_full[s], 1); mbar_init(&bars->pv_done[s], 1); mbar_init(&bars->p_full[s], 4);
         }
         for (int s = 0; s < 2; ++s) mbar_init(&bars->s_empty[s], 4);
         mbar_init(&bars->o_full, 1); mbar_init(&bars->o_empty, 4);
-        mbar_init(&bars->drain, 3);
+        mbar_init(&bars->drain, 2);
         bars->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_shared();
@@ -142,9 +158,12 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     tc_fence_after();
     const uint32_t tmem_base = *(volatile uint32_t*)&bars->tmem_base;
 
-    if (warp == 0) {
-        // ------------------------------------------------------------ TMA producer
-        int k_no = 0, v_no = 0, q_no = 0;          // tile sets loaded so far
+    if (warp == 0 || warp == 2) {
+        // ------------------------------------------------------------ TMA producers
+        // Warp 0 loads Q and the K tiles, warp 2 the V tiles: a K stage is free again as soon as its
+        // Q K^T has retired, long before the block's P V, and must not wait for it.
+        const bool is_v = warp == 2;
+        int kv_no = 0, q_no = 0;                   // blocks (K or V tile sets) and Q tile sets loaded so far
         bool ok = true;
         const long long tp_begin = AT_CLOCK();
         Cursor cur;
@@ -155,7 +174,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             if (cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
             const int n = cur.count;
             if (n > 0) {
-                if (lane == 0) {
+                if (lane == 0 && !is_v) {
                     const long long tq = AT_CLOCK();
                     ok = mbar_wait(&bars->q_empty, (uint32_t)(q_no & 1) ^ 1u, abort_flag, p.status);
                     AT_ADD(0, AT_CLOCK() - tq);
@@ -167,46 +186,40 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 }
                 ++q_no;
                 ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-                for (int pass = 0; ok && pass < 2; ++pass) {
-                    DescWindow win;                 // indices must not decrease: one window per pass
-                    win.begin(p.blocks, cur.first, cur.count, pre, lane);
-                    for (int j = 0; ok && j < n; ++j) {
-                        const int col = win.get(p.blocks, cur.first, cur.count, j, lane).col();
-                        // One copy per lane, all issued by the same instruction (issuing costs a thread
-                        // ~300 cycles per instruction, not per copy): lanes 0 .. dtiles-1 load the K
-                        // tiles, in pass 2 lanes dtiles .. 2*dtiles-1 the V tiles of this block.
-                        const bool is_v = lane >= p.dtiles;
-                        const bool mine = lane < (pass == 1 ? 2 * p.dtiles : p.dtiles);
-                        const int t = is_v ? lane - p.dtiles : lane;
-                        const int no = is_v ? v_no : k_no;
-                        const int stage = is_v ? (no & vring_mask) : (no & ring_mask);
-                        const uint32_t parity = ((uint32_t)(no >> (is_v ? p.vring_shift : p.ring_shift)) & 1u) ^ 1u;
-                        uint64_t* reuse = is_v ? &bars->pv_done[stage] : &bars->qk_done[stage];
-                        uint64_t* full = is_v ? &bars->v_full[stage] : &bars->k_full[stage];
-                        uint8_t* dst = (is_v ? v_smem : k_smem) + stage * set_bytes + t * kTileBytes;
-                        const CUtensorMap* map = is_v ? &map_v : &map_k;
-                        bool lane_ok = true;
-                        if (mine) {
-                            const long long t0 = AT_CLOCK();
-                            lane_ok = mbar_wait(reuse, parity, abort_flag, p.status);
-                            if (lane == 0) AT_ADD(1, AT_CLOCK() - t0);
-                        }
-                        ok = __all_sync(0xffffffffu, lane_ok) != 0;
-                        if (ok && mine) {
-                            const long long t1 = AT_CLOCK();
-                            if (t == 0) mbar_expect_tx(full, (uint32_t)set_bytes);
-                            tma_load_3d(dst, map, full, t * kTile, col * kTile, cur.z);
-                            if (lane == 0) AT_ADD(3, AT_CLOCK() - t1);
-                        }
-                        ++k_no;
-                        if (pass == 1) ++v_no;
+                DescWindow win;
+                win.begin(p.blocks, cur.first, cur.count, pre, lane);
+                for (int j = 0; ok && j < n; ++j) {
+                    const int col = win.get(p.blocks, cur.first, cur.count, j, lane).col();
+                    // One copy per lane, all issued by the same instruction (issuing costs a thread ~300
+                    // cycles per instruction): lane t loads tile t of the block's K (V) tile set.
+                    const bool mine = lane < p.dtiles;
+                    const int t = lane;
+                    const int stage = is_v ? (kv_no & vring_mask) : (kv_no & ring_mask);
+                    const uint32_t parity = ((uint32_t)(kv_no >> (is_v ? p.vring_shift : p.ring_shift)) & 1u) ^ 1u;
+                    uint64_t* reuse = is_v ? &bars->pv_done[stage] : &bars->qk_done[stage];
+                    uint64_t* full = is_v ? &bars->v_full[stage] : &bars->k_full[stage];
+                    uint8_t* dst = (is_v ? v_smem : k_smem) + stage * set_bytes + t * kTileBytes;
+                    const CUtensorMap* map = is_v ? &map_v : &map_k;
+                    bool lane_ok = true;
+                    if (mine) {
+                        const long long t0 = AT_CLOCK();
+                        lane_ok = mbar_wait(reuse, parity, abort_flag, p.status);
+                        if (lane == 0) AT_ADD(is_v ? 2 : 1, AT_CLOCK() - t0);
                     }
+                    ok = __all_sync(0xffffffffu, lane_ok) != 0;
+                    if (ok && mine) {
+                        const long long t1 = AT_CLOCK();
+                        if (t == 0) mbar_expect_tx(full, (uint32_t)set_bytes);
+                        tma_load_3d(dst, map, full, t * kTile, col * kTile, cur.z);
+                        if (lane == 0 && !is_v) AT_ADD(3, AT_CLOCK() - t1);
+                    }
+                    ++kv_no;
                 }
             }
             pre = pre_next;
             cur.advance();
         }
-        if (lane == 0) AT_ADD(4, AT_CLOCK() - tp_begin);
+        if (lane == 0 && !is_v) AT_ADD(4, AT_CLOCK() - tp_begin);
         if (lane == 0 && *(volatile int*)abort_flag) {
             // Give copies that were issued a bounded chance to land before the CTA exits.
             const unsigned long long t0 = global_ns();
@@ -220,17 +233,14 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                    global_ns() - t0 < kWaitLimitNs / 4) {}
         }
         __syncwarp();
-    } else if (warp == 1 || warp == 2) {
-        // ------------------------------------------------------------ Q K^T issuers
-        // The S tiles of a CTA are numbered in the order they are produced (per item: pass 1
-        // blocks, then pass 2 blocks); tile s goes to S buffer s & 1 and is issued by issuer s & 1.
-        // K stage s & (ring - 1) therefore always belongs to the same issuer.
-        const int w = warp - 1;
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ Q K^T issuer
+        // The S tiles (blocks) of a CTA are numbered in the order they are produced; tile s goes to
+        // S buffer s & 1, so Q K^T of block j + 1 runs while the softmax warps work on block j.
         if (lane == 0) {
             int s_no = 0, q_no = 0;
             bool ok = true;
             const uint32_t idesc_qk = p.idesc_qk;
-            const uint32_t d = tmem_base + (uint32_t)(kSCol0 + w * kTile);
             Cursor cur;
             cur.init(p);
             for (; ok && cur.valid(); cur.advance()) {
@@ -238,16 +248,17 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 if (n == 0) continue;               // empty row: the softmax warps write zeros on their own
                 ok = mbar_wait(&bars->q_full, (uint32_t)(q_no & 1), abort_flag, p.status);
                 if (!ok) break;
-                const int s_end = s_no + 2 * n;
-                for (int s = s_no + ((w - s_no) & 1); s < s_end; s += 2) {
-                    const int ks = s & ring_mask;
+                const int s_end = s_no + n;
+                for (int s = s_no; s < s_end; ++s) {
+                    const int ks = s & ring_mask, sb = s & 1;
                     const long long t0 = AT_CLOCK();
                     ok = mbar_wait(&bars->k_full[ks], (uint32_t)(s >> p.ring_shift) & 1u, abort_flag, p.status);
                     const long long t1 = AT_CLOCK();
-                    if (ok) ok = mbar_wait(&bars->s_empty[w], ((uint32_t)(s >> 1) & 1u) ^ 1u, abort_flag, p.status);
+                    if (ok) ok = mbar_wait(&bars->s_empty[sb], ((uint32_t)(s >> 1) & 1u) ^ 1u, abort_flag, p.status);
                     if (!ok) break;
                     const long long t2 = AT_CLOCK();
                     tc_fence_after();
+                    const uint32_t d = tmem_base + (uint32_t)(kSCol0 + sb * kTile);
                     for (int t = 0; t < p.dtiles; ++t) {
                         const uint64_t da = make_tile_desc(smem_u32(q_smem + t * kTileBytes), false);
                         const uint64_t db = make_tile_desc(smem_u32(k_smem + ks * set_bytes + t * kTileBytes), false);
@@ -256,10 +267,10 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                             tc_mma_f16(d, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc_qk, (t > 0 || kk > 0) ? 1u : 0u);
                     }
                     tc_commit(&bars->qk_done[ks]);
-                    if (w == 0) { AT_ADD(11, t1 - t0); AT_ADD(12, t2 - t1); AT_ADD(13, AT_CLOCK() - t2); }
+                    AT_ADD(11, t1 - t0); AT_ADD(12, t2 - t1); AT_ADD(13, AT_CLOCK() - t2);
                 }
                 if (!ok) break;
-                tc_commit(&bars->q_empty);          // this issuer's last read of Q has been issued
+                tc_commit(&bars->q_empty);          // the last read of Q has been issued
                 s_no = s_end;
                 ++q_no;
             }
@@ -364,68 +375,105 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 };
                 const float c2 = p.scale_log2;
                 const bool flip = c2 < 0.f;
-                // ---- the row's 2n S tiles as one stream: tiles 0 .. n-1 are pass 1 (row maxima of
-                // scale * log2(e) * S), tiles n .. 2n-1 pass 2 (P = exp2(scale * log2(e) * S - m) as a
-                // K-major operand tile, row sums).  The TMEM load of tile t + 1 is in flight while tile
-                // t is worked on (two register buffers, loop unrolled by two).
-                float m_a = -INFINITY, m_b = -INFINITY, sub_a = 0.f, sub_b = 0.f, l_a = 0.f, l_b = 0.f;
+                // ---- one pass over the row's blocks with a running row maximum m (in units of
+                // log2: t = scale * log2(e) * s).  P_j = exp2(t_j - m) goes to shared memory as a
+                // K-major operand tile, O += P_j V_j accumulates in TMEM, l sums the P's.  m is only
+                // raised when a block's maximum exceeds it by more than kSlack (P stays <= 2^kSlack,
+                // exact in fp32 sums and well inside the 16-bit range); raising it rescales O in TMEM
+                // and l by exp2(m_old - m_new), which needs the previous P V to have retired.
+                // The TMEM load of block j + 1 is in flight while block j is worked on (two register
+                // buffers, loop unrolled by two).
+                constexpr float kSlack = 8.f;
+                float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
                 DescWindow win;
                 win.begin(p.blocks, cur.first, cur.count, pre, lane);
-                const int tiles = 2 * n;
                 const uint32_t p_row = (uint32_t)(row_a * 128 + 4 * q4), p_xor = (uint32_t)(row_a & 7);
+                const float c2abs = fabsf(c2);
                 auto load = [&](uint32_t (&r)[32], int t) -> bool {       // wait for S tile t, start loading it
                     const int s = s_no + t;
+                    const long long t0 = AT_CLOCK();
                     if (!__all_sync(0xffffffffu, mbar_wait(&bars->qk_done[s & ring_mask], (uint32_t)(s >> p.ring_shift) & 1u,
                                                            abort_flag, p.status)))
                         return false;
                     tc_fence_after();
                     tc_ld_16x256b_x8(tmem_base + lane_field + (uint32_t)(kSCol0 + (s & 1) * kTile), r);
+                    if (warp == 4 && lane == 0) AT_ADD(5, AT_CLOCK() - t0);
                     return true;
                 };
                 auto loaded = [&](int t) {                                 // tile t is in registers: free its buffer
+                    const long long t0 = AT_CLOCK();
                     tc_wait_ld();
                     release_accumulator(&bars->s_empty[(s_no + t) & 1], lane);
+                    if (warp == 4 && lane == 0) AT_ADD(6, AT_CLOCK() - t0);
                 };
                 auto process = [&](const uint32_t (&r)[32], int t) -> bool {
-                    if (t == n) {
-                        // between the passes: maxima over the quad, scaled; a row without an unmasked
-                        // score subtracts 0 (all its probabilities are masked to 0 below)
-                        m_a = fmaxf(m_a, __shfl_xor_sync(0xffffffffu, m_a, 1)); m_a = fmaxf(m_a, __shfl_xor_sync(0xffffffffu, m_a, 2));
-                        m_b = fmaxf(m_b, __shfl_xor_sync(0xffffffffu, m_b, 1)); m_b = fmaxf(m_b, __shfl_xor_sync(0xffffffffu, m_b, 2));
-                        m_a = m_a == -INFINITY ? -INFINITY : m_a * fabsf(c2);     // now the maxima of c2 * S
-                        m_b = m_b == -INFINITY ? -INFINITY : m_b * fabsf(c2);
-                        sub_a = m_a == -INFINITY ? 0.f : m_a;
-                        sub_b = m_b == -INFINITY ? 0.f : m_b;
-                        if (MASKED) win.begin(p.blocks, cur.first, cur.count, pre, lane);   // indices restart
-                    }
                     uint32_t mask = 0u;
-                    if (MASKED && masked_op) mask = block_mask(win.get(p.blocks, cur.first, cur.count, t < n ? t : t - n, lane).col());
-                    if (t < n) {
-                        // extreme of the raw scores: the maximum for a positive scale, the minimum
-                        // (kept negated) for a negative one; scaled between the passes
-                        if (!flip) {
+                    const long long tm0 = AT_CLOCK();
+                    if (MASKED && masked_op) mask = block_mask(win.get(p.blocks, cur.first, cur.count, t, lane).col());
+                    // block maxima of the raw scores (for a negative scale: of their negatives)
+                    float x_a = -INFINITY, x_b = -INFINITY;
+                    if (!flip) {
 #pragma unroll
-                            for (int i = 0; i < 16; ++i) {
-                                const int u = i >> 1, e = i & 1;
-                                if (!MASKED || !((mask >> i) & 1u)) m_a = fmaxf(m_a, __uint_as_float(r[4 * u + e]));
-                                if (!MASKED || !((mask >> (16 + i)) & 1u)) m_b = fmaxf(m_b, __uint_as_float(r[4 * u + 2 + e]));
-                            }
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) {
-                                const int u = i >> 1, e = i & 1;
-                                if (!MASKED || !((mask >> i) & 1u)) m_a = fmaxf(m_a, -__uint_as_float(r[4 * u + e]));
-                                if (!MASKED || !((mask >> (16 + i)) & 1u)) m_b = fmaxf(m_b, -__uint_as_float(r[4 * u + 2 + e]));
-                            }
+                        for (int i = 0; i < 16; ++i) {
+                            const int u = i >> 1, e = i & 1;
+                            if (!MASKED || !((mask >> i) & 1u)) x_a = fmaxf(x_a, __uint_as_float(r[4 * u + e]));
+                            if (!MASKED || !((mask >> (16 + i)) & 1u)) x_b = fmaxf(x_b, __uint_as_float(r[4 * u + 2 + e]));
                         }
-                        return true;
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const int u = i >> 1, e = i & 1;
+                            if (!MASKED || !((mask >> i) & 1u)) x_a = fmaxf(x_a, -__uint_as_float(r[4 * u + e]));
+                            if (!MASKED || !((mask >> (16 + i)) & 1u)) x_b = fmaxf(x_b, -__uint_as_float(r[4 * u + 2 + e]));
+                        }
                     }
-                    // the P buffer must have been read by the MMAs that used it last
+                    x_a = fmaxf(x_a, __shfl_xor_sync(0xffffffffu, x_a, 1)); x_a = fmaxf(x_a, __shfl_xor_sync(0xffffffffu, x_a, 2));
+                    x_b = fmaxf(x_b, __shfl_xor_sync(0xffffffffu, x_b, 1)); x_b = fmaxf(x_b, __shfl_xor_sync(0xffffffffu, x_b, 2));
+                    x_a = x_a == -INFINITY ? -INFINITY : x_a * c2abs;       // maxima of t over the block
+                    x_b = x_b == -INFINITY ? -INFINITY : x_b * c2abs;
                     const int pb = p_no & vring_mask;
+                    if (t == 0) {
+                        m_a = x_a; m_b = x_b;                                 // P V of block 0 overwrites O
+                    } else {
+                        // raise a row's maximum only when it is overdue (or was -inf: nothing kept yet)
+                        const bool up_a = x_a > m_a + kSlack || (m_a == -INFINITY && x_a > -INFINITY);
+                        const bool up_b = x_b > m_b + kSlack || (m_b == -INFINITY && x_b > -INFINITY);
+                        if (__any_sync(0xffffffffu, up_a || up_b)) {
+                            const float al_a = !up_a ? 1.f : (m_a == -INFINITY ? 0.f : attn_exp2(m_a - x_a));
+                            const float al_b = !up_b ? 1.f : (m_b == -INFINITY ? 0.f : attn_exp2(m_b - x_b));
+                            if (up_a) { m_a = x_a; l_a *= al_a; }
+                            if (up_b) { m_b = x_b; l_b *= al_b; }
+                            // O is complete up to block t - 1 once that block's P V has retired
+                            const int prev = p_no - 1;
+                            if (!__all_sync(0xffffffffu, mbar_wait(&bars->pv_done[prev & vring_mask],
+                                                                   (uint32_t)(prev >> p.vring_shift) & 1u, abort_flag, p.status)))
+                                return false;
+                            tc_fence_after();
+                            for (int c = 0; c < p.head_dim; c += 16) {
+                                uint32_t o[8];
+                                tc_ld_16x256b_x2(tmem_base + lane_field + (uint32_t)c, o);
+                                tc_wait_ld();
+#pragma unroll
+                                for (int u = 0; u < 2; ++u) {
+                                    o[4 * u] = __float_as_uint(__uint_as_float(o[4 * u]) * al_a);
+                                    o[4 * u + 1] = __float_as_uint(__uint_as_float(o[4 * u + 1]) * al_a);
+                                    o[4 * u + 2] = __float_as_uint(__uint_as_float(o[4 * u + 2]) * al_b);
+                                    o[4 * u + 3] = __float_as_uint(__uint_as_float(o[4 * u + 3]) * al_b);
+                                }
+                                tc_st_16x256b_x2(tmem_base + lane_field + (uint32_t)c, o);
+                            }
+                            tc_wait_st();
+                            tc_fence_before();      // ordered before the P V this block's arrival releases
+                        }
+                    }
+                    const float sub_a = m_a == -INFINITY ? 0.f : m_a, sub_b = m_b == -INFINITY ? 0.f : m_b;
+                    const long long tm1 = AT_CLOCK();
+                    // the P buffer must have been read by the MMAs that used it last
                     if (!__all_sync(0xffffffffu, mbar_wait(&bars->pv_done[pb], ((uint32_t)(p_no >> p.vring_shift) & 1u) ^ 1u, abort_flag, p.status)))
                         return false;
                     // every lane owns the column pairs 8u + 2 * q4 + {0, 1} of its two rows: one 32-bit
                     // word each, stored straight into the 128-byte-swizzled tile (32 lanes hit 32 banks)
+                    const long long tm2 = AT_CLOCK();
                     const uint32_t tile = smem_u32(p_smem + pb * kTileBytes) + p_row;
 #pragma unroll
                     for (int u = 0; u < 8; ++u) {
@@ -443,25 +491,27 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(pack2<BF16>(pa[0], pa[1])) : "memory");
                         asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + 8 * 128), "r"(pack2<BF16>(pb2[0], pb2[1])) : "memory");
                     }
+                    const long long tm3 = AT_CLOCK();
                     fence_async_shared();           // generic-proxy writes -> visible to the tensor core's reads
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars->p_full[pb]);
+                    if (warp == 4 && lane == 0) { AT_ADD(7, tm1 - tm0); AT_ADD(18, tm2 - tm1); AT_ADD(19, tm3 - tm2); AT_ADD(20, AT_CLOCK() - tm3); }
                     ++p_no;
                     return true;
                 };
                 {
                     uint32_t ra[32], rb[32];
                     ok = load(ra, 0);
-                    for (int t = 0; ok && t < tiles; t += 2) {
+                    for (int t = 0; ok && t < n; t += 2) {
                         loaded(t);
-                        if (t + 1 < tiles) ok = load(rb, t + 1);
+                        if (t + 1 < n) ok = load(rb, t + 1);
                         if (!process(ra, t)) ok = false;
-                        if (!ok || t + 1 >= tiles) break;
+                        if (!ok || t + 1 >= n) break;
                         loaded(t + 1);
-                        if (t + 2 < tiles) ok = load(ra, t + 2);
+                        if (t + 2 < n) ok = load(ra, t + 2);
                         if (!process(rb, t + 1)) ok = false;
                     }
-                    s_no += tiles;
+                    s_no += n;
                 }
                 if (!ok) break;
                 l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);

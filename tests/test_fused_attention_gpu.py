@@ -82,6 +82,30 @@ def test_fused_forward_negative_scale_and_large_scores():
     _forward_case(strided_local(8, 4, 1), 64, (2,), 64, torch.float16, 6.0, seed=51)
 
 
+def test_fused_forward_running_maximum_is_raised_block_after_block():
+    """Keys grow from block to block, so every block's scores exceed the running row maximum by far
+    more than the slack the kernel tolerates: the accumulated output is rescaled at every block.
+    A second case has the largest scores in the first block (never rescaled)."""
+    from sparse import SparseLayout
+    from sparse.attention import attention_lse
+    from sparse.patterns import strided_local
+    pattern = strided_local(16, 4, 2)
+    layout = SparseLayout(pattern, block=64)
+    for dim in (64, 128):
+        for growth in (1.0, -1.0):
+            q = seeded((3, 1024, dim), 90, torch.float16)
+            k = seeded((3, 1024, dim), 91, torch.float16)
+            v = seeded((3, 1024, dim), 92, torch.float16)
+            ramp = torch.exp2(growth * torch.arange(16, dtype=torch.float32) / 3).repeat_interleave(64)   # up to 32x
+            k = (k.float() * ramp[None, :, None] * (1.0 if growth > 0 else 32.0)).half()
+            q = q.abs()          # same sign: the scores of a block scale with its keys
+            k = k.abs()
+            out, lse = attention_lse(q.cuda(), k.cuda(), v.cuda(), layout, 0.5)
+            ref, ref_lse = oracle.attention_forward_dense(q, k, v, pattern.numpy(), 64, 0.5)
+            assert_close(out, ref, torch.float16, "rescaled output dim %d growth %g" % (dim, growth))
+            assert float((lse.float().cpu() - ref_lse).abs().max() / ref_lse.abs().max()) <= 1e-3
+
+
 def test_fused_agrees_with_unfused_composition():
     """The fused kernel and the three unfused kernels agree far inside the tolerance."""
     from sparse import SparseLayout, matmul, softmax

@@ -53,17 +53,19 @@ constexpr int kSCol0 = 128;
 constexpr int kMaxRing = 4;
 
 struct __align__(8) AttnBarriers {
-    uint64_t q_full, q_empty;
+    uint64_t q_full[2], q_empty[2];
     uint64_t k_full[kMaxRing];
     uint64_t qk_done[kMaxRing];     // the MMAs of one Q K^T have retired: S is ready and the K stage is free
     uint64_t v_full[kMaxRing];
     uint64_t pv_done[kMaxRing];     // the MMAs of one P V have retired: the P buffer and the V stage are free
     uint64_t s_empty[2];
-    uint64_t p_full[kMaxRing];
+    uint64_t p_full[2];
     uint64_t o_full, o_empty;
+    uint64_t stat_full[2], stat_empty[2];   // two softmax groups: hand-over of group 1's row maxima and sums
     uint64_t drain;
     uint32_t tmem_base;
     int abort_flag;
+    float stat[2][kTile][2];
 };
 
 struct AttnParams {
@@ -76,7 +78,8 @@ struct AttnParams {
     int seq_q, seq_k, head_dim;
     int dtiles;                // head_dim / 64
     int ring, ring_shift;      // K pipeline depth (a power of two) and its log2
-    int vring, vring_shift;    // V pipeline depth = number of P buffers, and its log2
+    int vring, vring_shift;    // V pipeline depth and its log2 (there are always 2 P buffers)
+    int qbufs;                 // Q buffers: 2 = the next item's Q tile set is prefetched
     float scale_log2;          // scale * log2(e)
     int causal;
     const uint8_t* kpm;        // key padding mask or nullptr
@@ -100,6 +103,12 @@ __device__ __forceinline__ void tc_ld_16x256b_x2(uint32_t taddr, uint32_t (&r)[8
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                  : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tc_ld_16x256b_x4(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tc_st_16x256b_x2(uint32_t taddr, const uint32_t (&r)[8]) {
     asm volatile("tcgen05.st.sync.aligned.16x256b.x2.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
                  ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
@@ -117,31 +126,33 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
-template <bool BF16, bool MASKED>
-__global__ void __launch_bounds__(kAttnThreads, 2)
+template <bool BF16, bool MASKED, int WGS>
+__global__ void __launch_bounds__((4 + 4 * WGS) * 32, 2)
 attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    // tiles: Q (dtiles), K ring (ring x dtiles), V ring (vring x dtiles), P (vring)
+    // tiles: Q (qbufs x dtiles), K ring (ring x dtiles), V ring (vring x dtiles), P (2)
     const int set_bytes = p.dtiles * kTileBytes;            // one Q / K / V tile set
     uint8_t* q_smem = smem;
-    uint8_t* k_smem = q_smem + set_bytes;
+    uint8_t* k_smem = q_smem + p.qbufs * set_bytes;
     uint8_t* v_smem = k_smem + p.ring * set_bytes;
     uint8_t* p_smem = v_smem + p.vring * set_bytes;
-    AttnBarriers* bars = reinterpret_cast<AttnBarriers*>(p_smem + p.vring * kTileBytes);
+    AttnBarriers* bars = reinterpret_cast<AttnBarriers*>(p_smem + 2 * kTileBytes);
     int* abort_flag = &bars->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ring_mask = p.ring - 1, vring_mask = p.vring - 1;
 
     if (threadIdx.x == 0) {
-        mbar_init(&bars->q_full, 1); mbar_init(&bars->q_empty, 1);
+        for (int s = 0; s < 2; ++s) { mbar_init(&bars->q_full[s], 1); mbar_init(&bars->q_empty[s], 1); mbar_init(&bars->p_full[s], 4); }
         for (int s = 0; s < kMaxRing; ++s) {
             mbar_init(&bars->k_full[s], 1); mbar_init(&bars->qk_done[s], 1);
-            mbar_init(&bars->v_full[s], 1); mbar_init(&bars->pv_done[s], 1); mbar_init(&bars->p_full[s], 4);
+            mbar_init(&bars->v_full[s], 1); mbar_init(&bars->pv_done[s], 1);
         }
-        for (int s = 0; s < 2; ++s) mbar_init(&bars->s_empty[s], 4);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&bars->s_empty[s], 4); mbar_init(&bars->stat_full[s], 4); mbar_init(&bars->stat_empty[s], 4);
+        }
         mbar_init(&bars->o_full, 1); mbar_init(&bars->o_empty, 4);
         mbar_init(&bars->drain, 2);
         bars->abort_flag = 0;
@@ -164,6 +175,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         // Q K^T has retired, long before the block's P V, and must not wait for it.
         const bool is_v = warp == 2;
         int kv_no = 0, q_no = 0;                   // blocks (K or V tile sets) and Q tile sets loaded so far
+        bool q_prefetched = false;                 // the current item's Q tile set was requested an item ago
         bool ok = true;
         const long long tp_begin = AT_CLOCK();
         Cursor cur;
@@ -175,14 +187,26 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             const int n = cur.count;
             if (n > 0) {
                 if (lane == 0 && !is_v) {
-                    const long long tq = AT_CLOCK();
-                    ok = mbar_wait(&bars->q_empty, (uint32_t)(q_no & 1) ^ 1u, abort_flag, p.status);
-                    AT_ADD(0, AT_CLOCK() - tq);
-                    if (ok) {
-                        mbar_expect_tx(&bars->q_full, (uint32_t)set_bytes);
+                    // Q tile set number q goes to buffer q % qbufs once the Q K^T of the item that used
+                    // the buffer last have retired.  With two buffers the next item's set is requested
+                    // here, a whole item ahead of its first use.
+                    auto issue_q = [&](int q, int z, int g) -> bool {
+                        const int qb = q & (p.qbufs - 1);
+                        const uint32_t use = (uint32_t)(p.qbufs == 2 ? q >> 1 : q);
+                        if (!mbar_wait(&bars->q_empty[qb], (use & 1u) ^ 1u, abort_flag, p.status)) return false;
+                        mbar_expect_tx(&bars->q_full[qb], (uint32_t)set_bytes);
                         for (int t = 0; t < p.dtiles; ++t)
-                            tma_load_3d(q_smem + t * kTileBytes, &map_q, &bars->q_full, t * kTile, cur.g * kTile, cur.z);
+                            tma_load_3d(q_smem + qb * set_bytes + t * kTileBytes, &map_q, &bars->q_full[qb], t * kTile, g * kTile, z);
+                        return true;
+                    };
+                    const long long tq = AT_CLOCK();
+                    if (!q_prefetched) ok = issue_q(q_no, cur.z, cur.g);
+                    q_prefetched = false;
+                    if (ok && p.qbufs == 2 && cur.has_next() && cur.next_count() > 0) {
+                        ok = issue_q(q_no + 1, cur.z1, cur.r1);
+                        q_prefetched = true;
                     }
+                    AT_ADD(0, AT_CLOCK() - tq);
                 }
                 ++q_no;
                 ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
@@ -229,8 +253,9 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             for (int s = 0; s < p.vring; ++s)
                 while (!mbar_try_wait(&bars->v_full[s], 0) && !mbar_try_wait(&bars->v_full[s], 1) &&
                        global_ns() - t0 < kWaitLimitNs / 4) {}
-            while (!mbar_try_wait(&bars->q_full, 0) && !mbar_try_wait(&bars->q_full, 1) &&
-                   global_ns() - t0 < kWaitLimitNs / 4) {}
+            for (int s = 0; s < p.qbufs; ++s)
+                while (!mbar_try_wait(&bars->q_full[s], 0) && !mbar_try_wait(&bars->q_full[s], 1) &&
+                       global_ns() - t0 < kWaitLimitNs / 4) {}
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -246,7 +271,10 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             for (; ok && cur.valid(); cur.advance()) {
                 const int n = cur.count;
                 if (n == 0) continue;               // empty row: the softmax warps write zeros on their own
-                ok = mbar_wait(&bars->q_full, (uint32_t)(q_no & 1), abort_flag, p.status);
+                const int qb = q_no & (p.qbufs - 1);
+                const long long tq0 = AT_CLOCK();
+                ok = mbar_wait(&bars->q_full[qb], (uint32_t)(p.qbufs == 2 ? q_no >> 1 : q_no) & 1u, abort_flag, p.status);
+                AT_ADD(21, AT_CLOCK() - tq0);
                 if (!ok) break;
                 const int s_end = s_no + n;
                 for (int s = s_no; s < s_end; ++s) {
@@ -260,7 +288,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     tc_fence_after();
                     const uint32_t d = tmem_base + (uint32_t)(kSCol0 + sb * kTile);
                     for (int t = 0; t < p.dtiles; ++t) {
-                        const uint64_t da = make_tile_desc(smem_u32(q_smem + t * kTileBytes), false);
+                        const uint64_t da = make_tile_desc(smem_u32(q_smem + qb * set_bytes + t * kTileBytes), false);
                         const uint64_t db = make_tile_desc(smem_u32(k_smem + ks * set_bytes + t * kTileBytes), false);
 #pragma unroll
                         for (int kk = 0; kk < kTile / 16; ++kk)
@@ -270,7 +298,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     AT_ADD(11, t1 - t0); AT_ADD(12, t2 - t1); AT_ADD(13, AT_CLOCK() - t2);
                 }
                 if (!ok) break;
-                tc_commit(&bars->q_empty);          // the last read of Q has been issued
+                tc_commit(&bars->q_empty[qb]);      // the last read of this Q buffer has been issued
                 s_no = s_end;
                 ++q_no;
             }
@@ -291,24 +319,24 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 const int n = cur.count;
                 if (n == 0) continue;
                 for (int j = 0; ok && j < n; ++j, ++p_no) {
-                    const int pb = p_no & vring_mask;
+                    const int pb = p_no & 1, vs = p_no & vring_mask;
                     const long long t0 = AT_CLOCK();
                     if (j == 0) ok = mbar_wait(&bars->o_empty, (uint32_t)(o_no & 1) ^ 1u, abort_flag, p.status);
                     const long long t1 = AT_CLOCK();
-                    if (ok) ok = mbar_wait(&bars->v_full[pb], (uint32_t)(p_no >> p.vring_shift) & 1u, abort_flag, p.status);
+                    if (ok) ok = mbar_wait(&bars->v_full[vs], (uint32_t)(p_no >> p.vring_shift) & 1u, abort_flag, p.status);
                     const long long t2 = AT_CLOCK();
-                    if (ok) ok = mbar_wait(&bars->p_full[pb], (uint32_t)(p_no >> p.vring_shift) & 1u, abort_flag, p.status);
+                    if (ok) ok = mbar_wait(&bars->p_full[pb], (uint32_t)(p_no >> 1) & 1u, abort_flag, p.status);
                     if (!ok) break;
                     const long long t3 = AT_CLOCK();
                     tc_fence_after();
                     // O += P_j V_{c_j}: A = P (K-major), B = V tiles (N contiguous), N = head_dim
                     const uint64_t da = make_tile_desc(smem_u32(p_smem + pb * kTileBytes), false);
-                    const uint64_t db = make_tile_desc(smem_u32(v_smem + pb * set_bytes), true);
+                    const uint64_t db = make_tile_desc(smem_u32(v_smem + vs * set_bytes), true);
 #pragma unroll
                     for (int kk = 0; kk < kTile / 16; ++kk)
-                        tc_mma_f16(tmem_base, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * (2048 >> 4)), idesc_pv,
-                                   (j > 0 || kk > 0) ? 1u : 0u);
-                    tc_commit(&bars->pv_done[pb]);
+                        tc_mma_f16(tmem_base + (uint32_t)(WGS == 2 ? (p_no & 1) * p.head_dim : 0), da + (uint64_t)(kk * 2),
+                                   db + (uint64_t)(kk * (2048 >> 4)), idesc_pv, (j >= WGS || kk > 0) ? 1u : 0u);
+                    tc_commit(&bars->pv_done[vs]);
                     if (j == n - 1) tc_commit(&bars->o_full);
                     AT_ADD(14, t1 - t0); AT_ADD(15, t2 - t1); AT_ADD(16, t3 - t2); AT_ADD(17, AT_CLOCK() - t3);
                 }
@@ -320,14 +348,19 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         __syncwarp();
     } else {
         // ------------------------------------------------------------ softmax warps
+        // WGS = 2: two warpgroups share an item; group g takes the S tiles with number s & 1 == g
+        // (S buffer g), keeps its own running maxima and sums and its own O accumulator in TMEM
+        // (P V of tile s accumulates into accumulator s & 1), and group 0 merges the two at the end:
+        // the partial results of a softmax over two disjoint key sets combine exactly.
+        const int wg = WGS == 2 ? (warp - 4) >> 2 : 0;
         const int quad = warp & 3;                  // TMEM sub-partition this warp may read
         const int q4 = lane & 3;                    // position in the quad: columns 8u + 2 * q4 + {0, 1}
         const int row_a = quad * 16 + (lane >> 2);  // this lane's two rows of the 64-row block
-        const int row_b = row_a + 8;
         const uint32_t lane_field = (uint32_t)(quad * 32) << 16;
+        const uint32_t o_col = (uint32_t)(wg * p.head_dim);       // this group's O accumulator
         // MASKED = false: no causal or key-padding mask, all mask tests fold away
         const bool masked_op = MASKED && (p.causal != 0 || p.kpm != nullptr);
-        int s_no = 0, p_no = 0, o_no = 0;
+        int s_no = 0, o_no = 0;                     // S tiles and non-empty items before the current item
         bool ok = true;
         const long long t_begin = AT_CLOCK();
         Cursor cur;
@@ -342,11 +375,13 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             const size_t lse_a = (size_t)cur.z * p.seq_q + (size_t)cur.g * kTile + row_a;
             if (n == 0) {
                 // a block row without blocks: zeros, lse = -inf
-                for (int c = q4 * 8; c < p.head_dim; c += 32) {
-                    *reinterpret_cast<uint4*>(p.o + o_row_a + c) = make_uint4(0u, 0u, 0u, 0u);
-                    *reinterpret_cast<uint4*>(p.o + o_row_b + c) = make_uint4(0u, 0u, 0u, 0u);
+                if (wg == 0) {
+                    for (int c = q4 * 8; c < p.head_dim; c += 32) {
+                        *reinterpret_cast<uint4*>(p.o + o_row_a + c) = make_uint4(0u, 0u, 0u, 0u);
+                        *reinterpret_cast<uint4*>(p.o + o_row_b + c) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    if (q4 == 0 && p.lse) { p.lse[lse_a] = -INFINITY; p.lse[lse_a + 8] = -INFINITY; }
                 }
-                if (q4 == 0 && p.lse) { p.lse[lse_a] = -INFINITY; p.lse[lse_a + 8] = -INFINITY; }
             } else {
                 const uint8_t* kpm_row = p.kpm ? p.kpm + (size_t)(cur.z / p.kpm_div) * p.kpm_stride : nullptr;
                 const int qpos_a = cur.g * kTile + row_a;
@@ -380,15 +415,14 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 // K-major operand tile, O += P_j V_j accumulates in TMEM, l sums the P's.  m is only
                 // raised when a block's maximum exceeds it by more than kSlack (P stays <= 2^kSlack,
                 // exact in fp32 sums and well inside the 16-bit range); raising it rescales O in TMEM
-                // and l by exp2(m_old - m_new), which needs the previous P V to have retired.
-                // The TMEM load of block j + 1 is in flight while block j is worked on (two register
-                // buffers, loop unrolled by two).
+                // and l by exp2(m_old - m_new), which needs this group's previous P V to have retired.
                 constexpr float kSlack = 8.f;
                 float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
                 DescWindow win;
                 win.begin(p.blocks, cur.first, cur.count, pre, lane);
                 const uint32_t p_row = (uint32_t)(row_a * 128 + 4 * q4), p_xor = (uint32_t)(row_a & 7);
                 const float c2abs = fabsf(c2);
+                const int t_first = WGS == 2 ? ((wg - s_no) & 1) : 0;     // this group's first tile of the item
                 auto load = [&](uint32_t (&r)[32], int t) -> bool {       // wait for S tile t, start loading it
                     const int s = s_no + t;
                     const long long t0 = AT_CLOCK();
@@ -407,6 +441,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     if (warp == 4 && lane == 0) AT_ADD(6, AT_CLOCK() - t0);
                 };
                 auto process = [&](const uint32_t (&r)[32], int t) -> bool {
+                    const int s = s_no + t;                                  // tile number = P buffer number
                     uint32_t mask = 0u;
                     const long long tm0 = AT_CLOCK();
                     if (MASKED && masked_op) mask = block_mask(win.get(p.blocks, cur.first, cur.count, t, lane).col());
@@ -431,9 +466,9 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     x_b = fmaxf(x_b, __shfl_xor_sync(0xffffffffu, x_b, 1)); x_b = fmaxf(x_b, __shfl_xor_sync(0xffffffffu, x_b, 2));
                     x_a = x_a == -INFINITY ? -INFINITY : x_a * c2abs;       // maxima of t over the block
                     x_b = x_b == -INFINITY ? -INFINITY : x_b * c2abs;
-                    const int pb = p_no & vring_mask;
-                    if (t == 0) {
-                        m_a = x_a; m_b = x_b;                                 // P V of block 0 overwrites O
+                    const int pb = s & 1;
+                    if (t == t_first) {
+                        m_a = x_a; m_b = x_b;                                 // this group's first P V overwrites O
                     } else {
                         // raise a row's maximum only when it is overdue (or was -inf: nothing kept yet)
                         const bool up_a = x_a > m_a + kSlack || (m_a == -INFINITY && x_a > -INFINITY);
@@ -443,15 +478,15 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                             const float al_b = !up_b ? 1.f : (m_b == -INFINITY ? 0.f : attn_exp2(m_b - x_b));
                             if (up_a) { m_a = x_a; l_a *= al_a; }
                             if (up_b) { m_b = x_b; l_b *= al_b; }
-                            // O is complete up to block t - 1 once that block's P V has retired
-                            const int prev = p_no - 1;
+                            // O is complete up to this group's previous tile once that tile's P V has retired
+                            const int prev = s - WGS;
                             if (!__all_sync(0xffffffffu, mbar_wait(&bars->pv_done[prev & vring_mask],
                                                                    (uint32_t)(prev >> p.vring_shift) & 1u, abort_flag, p.status)))
                                 return false;
                             tc_fence_after();
                             for (int c = 0; c < p.head_dim; c += 16) {
                                 uint32_t o[8];
-                                tc_ld_16x256b_x2(tmem_base + lane_field + (uint32_t)c, o);
+                                tc_ld_16x256b_x2(tmem_base + lane_field + o_col + (uint32_t)c, o);
                                 tc_wait_ld();
 #pragma unroll
                                 for (int u = 0; u < 2; ++u) {
@@ -460,7 +495,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                                     o[4 * u + 2] = __float_as_uint(__uint_as_float(o[4 * u + 2]) * al_b);
                                     o[4 * u + 3] = __float_as_uint(__uint_as_float(o[4 * u + 3]) * al_b);
                                 }
-                                tc_st_16x256b_x2(tmem_base + lane_field + (uint32_t)c, o);
+                                tc_st_16x256b_x2(tmem_base + lane_field + o_col + (uint32_t)c, o);
                             }
                             tc_wait_st();
                             tc_fence_before();      // ordered before the P V this block's arrival releases
@@ -468,8 +503,9 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     }
                     const float sub_a = m_a == -INFINITY ? 0.f : m_a, sub_b = m_b == -INFINITY ? 0.f : m_b;
                     const long long tm1 = AT_CLOCK();
-                    // the P buffer must have been read by the MMAs that used it last
-                    if (!__all_sync(0xffffffffu, mbar_wait(&bars->pv_done[pb], ((uint32_t)(p_no >> p.vring_shift) & 1u) ^ 1u, abort_flag, p.status)))
+                    // the P buffer must have been read by the MMAs that used it last (those of tile s - 2)
+                    if (s >= 2 && !__all_sync(0xffffffffu, mbar_wait(&bars->pv_done[(s - 2) & vring_mask],
+                                                                     (uint32_t)((s - 2) >> p.vring_shift) & 1u, abort_flag, p.status)))
                         return false;
                     // every lane owns the column pairs 8u + 2 * q4 + {0, 1} of its two rows: one 32-bit
                     // word each, stored straight into the 128-byte-swizzled tile (32 lanes hit 32 banks)
@@ -496,10 +532,11 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars->p_full[pb]);
                     if (warp == 4 && lane == 0) { AT_ADD(7, tm1 - tm0); AT_ADD(18, tm2 - tm1); AT_ADD(19, tm3 - tm2); AT_ADD(20, AT_CLOCK() - tm3); }
-                    ++p_no;
                     return true;
                 };
-                {
+                if (WGS == 1) {
+                    // The TMEM load of block j + 1 is in flight while block j is worked on (two
+                    // register buffers, loop unrolled by two).
                     uint32_t ra[32], rb[32];
                     ok = load(ra, 0);
                     for (int t = 0; ok && t < n; t += 2) {
@@ -511,46 +548,99 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         if (t + 2 < n) ok = load(ra, t + 2);
                         if (!process(rb, t + 1)) ok = false;
                     }
-                    s_no += n;
+                } else {
+                    // two groups already keep two blocks in flight: one register buffer
+                    uint32_t r[32];
+                    for (int t = t_first; ok && t < n; t += 2) {
+                        ok = load(r, t);
+                        if (!ok) break;
+                        loaded(t);
+                        if (!process(r, t)) ok = false;
+                    }
                 }
+                s_no += n;
                 if (!ok) break;
                 l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
                 l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
-                const float inv_a = l_a > 0.f ? 1.f / l_a : 0.f, inv_b = l_b > 0.f ? 1.f / l_b : 0.f;
-                // ---- end of the row: O / l
-                const long long te0 = AT_CLOCK();
-                ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full, (uint32_t)(o_no & 1), abort_flag, p.status)) != 0;
-                if (!ok) break;
-                const long long te1 = AT_CLOCK();
-                tc_fence_after();
-                for (int t = 0; t < p.dtiles; ++t) {
-                    uint32_t r[32];
-                    tc_ld_16x256b_x8(tmem_base + lane_field + (uint32_t)(t * kTile), r);
-                    tc_wait_ld();
-                    if (t == p.dtiles - 1) release_accumulator(&bars->o_empty, lane);
-#pragma unroll
-                    for (int half = 0; half < 2; ++half) {
+                // weights of this group's (w) and the other group's (v) accumulator in the result
+                float w_a = 1.f, w_b = 1.f, v_a = 0.f, v_b = 0.f;
+                if (WGS == 2) {
+                    // group 1 hands its maxima and sums to group 0 through shared memory (two slots,
+                    // alternating by item); the partial softmaxes over the two groups' key sets merge as
+                    // m = max(m0, m1), l = l0 2^(m0 - m) + l1 2^(m1 - m), O likewise
+                    const int slot = o_no & 1;
+                    float* stat = &bars->stat[slot][0][0];
+                    if (wg == 1) {
+                        ok = __all_sync(0xffffffffu, mbar_wait(&bars->stat_empty[slot], ((uint32_t)(o_no >> 1) & 1u) ^ 1u, abort_flag, p.status)) != 0;
+                        if (!ok) break;
+                        if (q4 == 0) {
+                            stat[row_a * 2] = m_a; stat[row_a * 2 + 1] = l_a;
+                            stat[(row_a + 8) * 2] = m_b; stat[(row_a + 8) * 2 + 1] = l_b;
+                        }
+                        __threadfence_block();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&bars->stat_full[slot]);
+                    } else {
+                        const long long ts0 = AT_CLOCK();
+                        ok = __all_sync(0xffffffffu, mbar_wait(&bars->stat_full[slot], (uint32_t)(o_no >> 1) & 1u, abort_flag, p.status)) != 0;
+                        if (!ok) break;
+                        if (warp == 4 && lane == 0) AT_ADD(22, AT_CLOCK() - ts0);
+                        const float mo_a = stat[row_a * 2], lo_a = stat[row_a * 2 + 1];
+                        const float mo_b = stat[(row_a + 8) * 2], lo_b = stat[(row_a + 8) * 2 + 1];
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&bars->stat_empty[slot]);
+                        const float mm_a = fmaxf(m_a, mo_a), mm_b = fmaxf(m_b, mo_b);
+                        w_a = m_a == -INFINITY ? 0.f : attn_exp2(m_a - mm_a);
+                        v_a = mo_a == -INFINITY ? 0.f : attn_exp2(mo_a - mm_a);
+                        w_b = m_b == -INFINITY ? 0.f : attn_exp2(m_b - mm_b);
+                        v_b = mo_b == -INFINITY ? 0.f : attn_exp2(mo_b - mm_b);
+                        l_a = l_a * w_a + lo_a * v_a;  m_a = mm_a;
+                        l_b = l_b * w_b + lo_b * v_b;  m_b = mm_b;
+                    }
+                }
+                if (wg == 0) {
+                    // ---- end of the row: O / l
+                    const float inv_a = l_a > 0.f ? 1.f / l_a : 0.f, inv_b = l_b > 0.f ? 1.f / l_b : 0.f;
+                    const float sw_a = w_a * inv_a, sv_a = v_a * inv_a, sw_b = w_b * inv_b, sv_b = v_b * inv_b;
+                    const long long te0 = AT_CLOCK();
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full, (uint32_t)(o_no & 1), abort_flag, p.status)) != 0;
+                    if (!ok) break;
+                    const long long te1 = AT_CLOCK();
+                    tc_fence_after();
+                    for (int c = 0; c < p.head_dim; c += 32) {
+                        uint32_t r0[16], r1[16];
+                        tc_ld_16x256b_x4(tmem_base + lane_field + (uint32_t)c, r0);
+                        if (WGS == 2) tc_ld_16x256b_x4(tmem_base + lane_field + (uint32_t)(p.head_dim + c), r1);
+                        tc_wait_ld();
+                        if (c + 32 >= p.head_dim) release_accumulator(&bars->o_empty, lane);
                         uint32_t ta[4], tb[4];
 #pragma unroll
                         for (int u = 0; u < 4; ++u) {
-                            const int uu = 4 * half + u;
-                            ta[u] = pack2<BF16>(__uint_as_float(r[4 * uu]) * inv_a, __uint_as_float(r[4 * uu + 1]) * inv_a);
-                            tb[u] = pack2<BF16>(__uint_as_float(r[4 * uu + 2]) * inv_b, __uint_as_float(r[4 * uu + 3]) * inv_b);
+                            // an accumulator whose weight is 0 may never have been written: do not touch it
+                            float a0 = sw_a > 0.f ? __uint_as_float(r0[4 * u]) * sw_a : 0.f;
+                            float a1 = sw_a > 0.f ? __uint_as_float(r0[4 * u + 1]) * sw_a : 0.f;
+                            float b0 = sw_b > 0.f ? __uint_as_float(r0[4 * u + 2]) * sw_b : 0.f;
+                            float b1 = sw_b > 0.f ? __uint_as_float(r0[4 * u + 3]) * sw_b : 0.f;
+                            if (WGS == 2) {
+                                if (sv_a > 0.f) { a0 = fmaf(__uint_as_float(r1[4 * u]), sv_a, a0); a1 = fmaf(__uint_as_float(r1[4 * u + 1]), sv_a, a1); }
+                                if (sv_b > 0.f) { b0 = fmaf(__uint_as_float(r1[4 * u + 2]), sv_b, b0); b1 = fmaf(__uint_as_float(r1[4 * u + 3]), sv_b, b1); }
+                            }
+                            ta[u] = pack2<BF16>(a0, a1);
+                            tb[u] = pack2<BF16>(b0, b1);
                         }
-                        quad_transpose(ta, q4);
+                        quad_transpose(ta, q4);         // now columns c + 8 * q4 .. + 7 of the row
                         quad_transpose(tb, q4);
-                        const int c = t * kTile + 32 * half + 8 * q4;
-                        *reinterpret_cast<uint4*>(p.o + o_row_a + c) = make_uint4(ta[0], ta[1], ta[2], ta[3]);
-                        *reinterpret_cast<uint4*>(p.o + o_row_b + c) = make_uint4(tb[0], tb[1], tb[2], tb[3]);
+                        *reinterpret_cast<uint4*>(p.o + o_row_a + c + 8 * q4) = make_uint4(ta[0], ta[1], ta[2], ta[3]);
+                        *reinterpret_cast<uint4*>(p.o + o_row_b + c + 8 * q4) = make_uint4(tb[0], tb[1], tb[2], tb[3]);
+                    }
+                    if (warp == 4 && lane == 0) { AT_ADD(8, te1 - te0); AT_ADD(9, AT_CLOCK() - te1); }
+                    if (q4 == 0 && p.lse) {
+                        // natural-log sum of exponentials of the scaled, masked scores
+                        p.lse[lse_a] = l_a > 0.f ? (m_a + log2f(l_a)) * 0.6931471805599453f : -INFINITY;
+                        p.lse[lse_a + 8] = l_b > 0.f ? (m_b + log2f(l_b)) * 0.6931471805599453f : -INFINITY;
                     }
                 }
                 ++o_no;
-                if (warp == 4 && lane == 0) { AT_ADD(8, te1 - te0); AT_ADD(9, AT_CLOCK() - te1); }
-                if (q4 == 0 && p.lse) {
-                    // natural-log sum of exponentials of the scaled, masked scores
-                    p.lse[lse_a] = l_a > 0.f ? (m_a + log2f(l_a)) * 0.6931471805599453f : -INFINITY;
-                    p.lse[lse_a + 8] = l_b > 0.f ? (m_b + log2f(l_b)) * 0.6931471805599453f : -INFINITY;
-                }
             }
             pre = pre_next;
             cur.advance();
@@ -579,9 +669,16 @@ int attention_forward(int dtype, const void* q, const void* k, const void* v, vo
                       cudaStream_t stream) {
     using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const AttnParams);
     const bool masked = causal != 0 || kpm != nullptr;
-    const KernelFn kernel = dtype == BSA_DTYPE_BF16
-        ? (masked ? attention_forward_kernel<true, true> : attention_forward_kernel<true, false>)
-        : (masked ? attention_forward_kernel<false, true> : attention_forward_kernel<false, false>);
+    // two softmax warpgroups where two O accumulators fit into the CTA's 256 TMEM columns
+    const int wgs = head_dim == 64 ? 2 : 1;
+    KernelFn kernel;
+    if (dtype == BSA_DTYPE_BF16) {
+        if (wgs == 2) kernel = masked ? attention_forward_kernel<true, true, 2> : attention_forward_kernel<true, false, 2>;
+        else          kernel = masked ? attention_forward_kernel<true, true, 1> : attention_forward_kernel<true, false, 1>;
+    } else {
+        if (wgs == 2) kernel = masked ? attention_forward_kernel<false, true, 2> : attention_forward_kernel<false, false, 2>;
+        else          kernel = masked ? attention_forward_kernel<false, true, 1> : attention_forward_kernel<false, false, 1>;
+    }
     AttnParams p{};
     p.dtiles = (int)(head_dim / kTile);
     p.ring = p.dtiles == 1 ? 4 : 2;
@@ -589,7 +686,8 @@ int attention_forward(int dtype, const void* q, const void* k, const void* v, vo
     p.vring = p.dtiles == 1 ? 4 : 2;
     p.vring_shift = p.dtiles == 1 ? 2 : 1;
     // at least 80 KB, so that never more than two CTAs (256 TMEM columns each) share an SM
-    int smem_bytes = 1024 + ((1 + p.ring + p.vring) * p.dtiles + p.vring) * kTileBytes + (int)sizeof(AttnBarriers);
+    p.qbufs = p.dtiles == 1 ? 2 : 1;
+    int smem_bytes = 1024 + ((p.qbufs + p.ring + p.vring) * p.dtiles + 2) * kTileBytes + (int)sizeof(AttnBarriers);
     if (smem_bytes < 80 * 1024) smem_bytes = 80 * 1024;
     // Set on every call (a per-device attribute); this and the cudaSetDevice below also bind the
     // device's primary context to the calling thread, which the driver call behind make_map needs.
@@ -634,7 +732,7 @@ int attention_forward(int dtype, const void* q, const void* k, const void* v, vo
     const unsigned grid = (unsigned)(p.items < 2 * sms ? p.items : 2 * sms);
     p.stride_z = (int)grid / p.groups;
     p.stride_rem = (int)grid % p.groups;
-    kernel<<<grid, kAttnThreads, smem_bytes, stream>>>(map_q, map_k, map_v, p);
+    kernel<<<grid, (4 + 4 * wgs) * 32, smem_bytes, stream>>>(map_q, map_k, map_v, p);
     return launch_status();
 }
 

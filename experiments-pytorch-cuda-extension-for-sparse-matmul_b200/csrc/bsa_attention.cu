@@ -90,6 +90,15 @@ struct AttnParams {
     uint32_t idesc_qk, idesc_pv;
 };
 
+// True in exactly one lane of a converged warp.  Code around an `if (elect_one())` stays
+// warp-uniform, so the descriptors of the tcgen05 instructions inside it are computed once per
+// warp in uniform registers instead of being moved there per instruction.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+
 __device__ __forceinline__ float attn_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -262,7 +271,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         // ------------------------------------------------------------ Q K^T issuer
         // The S tiles (blocks) of a CTA are numbered in the order they are produced; tile s goes to
         // S buffer s & 1, so Q K^T of block j + 1 runs while the softmax warps work on block j.
-        if (lane == 0) {
+        {
             int s_no = 0, q_no = 0;
             bool ok = true;
             const uint32_t idesc_qk = p.idesc_qk;
@@ -273,43 +282,50 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 if (n == 0) continue;               // empty row: the softmax warps write zeros on their own
                 const int qb = q_no & (p.qbufs - 1);
                 const long long tq0 = AT_CLOCK();
-                ok = mbar_wait(&bars->q_full[qb], (uint32_t)(p.qbufs == 2 ? q_no >> 1 : q_no) & 1u, abort_flag, p.status);
+                ok = __all_sync(0xffffffffu, mbar_wait(&bars->q_full[qb], (uint32_t)(p.qbufs == 2 ? q_no >> 1 : q_no) & 1u, abort_flag, p.status)) != 0;
                 AT_ADD(21, AT_CLOCK() - tq0);
                 if (!ok) break;
                 const int s_end = s_no + n;
                 for (int s = s_no; s < s_end; ++s) {
                     const int ks = s & ring_mask, sb = s & 1;
                     const long long t0 = AT_CLOCK();
-                    ok = mbar_wait(&bars->k_full[ks], (uint32_t)(s >> p.ring_shift) & 1u, abort_flag, p.status);
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->k_full[ks], (uint32_t)(s >> p.ring_shift) & 1u, abort_flag, p.status)) != 0;
                     const long long t1 = AT_CLOCK();
-                    if (ok) ok = mbar_wait(&bars->s_empty[sb], ((uint32_t)(s >> 1) & 1u) ^ 1u, abort_flag, p.status);
+                    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_empty[sb], ((uint32_t)(s >> 1) & 1u) ^ 1u, abort_flag, p.status)) != 0;
                     if (!ok) break;
                     const long long t2 = AT_CLOCK();
                     tc_fence_after();
                     const uint32_t d = tmem_base + (uint32_t)(kSCol0 + sb * kTile);
-                    for (int t = 0; t < p.dtiles; ++t) {
-                        const uint64_t da = make_tile_desc(smem_u32(q_smem + qb * set_bytes + t * kTileBytes), false);
-                        const uint64_t db = make_tile_desc(smem_u32(k_smem + ks * set_bytes + t * kTileBytes), false);
+                    if (elect_one()) {
+                        for (int t = 0; t < p.dtiles; ++t) {
+                            const uint64_t da = make_tile_desc(smem_u32(q_smem + qb * set_bytes + t * kTileBytes), false);
+                            const uint64_t db = make_tile_desc(smem_u32(k_smem + ks * set_bytes + t * kTileBytes), false);
 #pragma unroll
-                        for (int kk = 0; kk < kTile / 16; ++kk)
-                            tc_mma_f16(d, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc_qk, (t > 0 || kk > 0) ? 1u : 0u);
+                            for (int kk = 0; kk < kTile / 16; ++kk)
+                                tc_mma_f16(d, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc_qk, (t > 0 || kk > 0) ? 1u : 0u);
+                        }
+                        tc_commit(&bars->qk_done[ks]);
                     }
-                    tc_commit(&bars->qk_done[ks]);
-                    AT_ADD(11, t1 - t0); AT_ADD(12, t2 - t1); AT_ADD(13, AT_CLOCK() - t2);
+                    __syncwarp();
+                    if (lane == 0) { AT_ADD(11, t1 - t0); AT_ADD(12, t2 - t1); AT_ADD(13, AT_CLOCK() - t2); }
                 }
                 if (!ok) break;
-                tc_commit(&bars->q_empty[qb]);      // the last read of this Q buffer has been issued
+                if (elect_one()) tc_commit(&bars->q_empty[qb]);      // the last read of this Q buffer has been issued
+                __syncwarp();
                 s_no = s_end;
                 ++q_no;
             }
-            // All MMAs issued by this thread must have retired before TMEM is freed.
-            tc_commit(&bars->drain);
-            mbar_wait(&bars->drain, 0, abort_flag, p.status);
+            // All MMAs issued by the elected lane (the same one every time: the election is
+            // deterministic for a converged warp) must have retired before TMEM is freed.
+            if (elect_one()) {
+                tc_commit(&bars->drain);
+                mbar_wait(&bars->drain, 0, abort_flag, p.status);
+            }
         }
         __syncwarp();
     } else if (warp == 3) {
         // ------------------------------------------------------------ P V issuer
-        if (lane == 0) {
+        {
             int p_no = 0, o_no = 0;
             bool ok = true;
             const uint32_t idesc_pv = p.idesc_pv;
@@ -321,29 +337,35 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 for (int j = 0; ok && j < n; ++j, ++p_no) {
                     const int pb = p_no & 1, vs = p_no & vring_mask;
                     const long long t0 = AT_CLOCK();
-                    if (j == 0) ok = mbar_wait(&bars->o_empty, (uint32_t)(o_no & 1) ^ 1u, abort_flag, p.status);
+                    if (j == 0) ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_empty, (uint32_t)(o_no & 1) ^ 1u, abort_flag, p.status)) != 0;
                     const long long t1 = AT_CLOCK();
-                    if (ok) ok = mbar_wait(&bars->v_full[vs], (uint32_t)(p_no >> p.vring_shift) & 1u, abort_flag, p.status);
+                    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->v_full[vs], (uint32_t)(p_no >> p.vring_shift) & 1u, abort_flag, p.status)) != 0;
                     const long long t2 = AT_CLOCK();
-                    if (ok) ok = mbar_wait(&bars->p_full[pb], (uint32_t)(p_no >> 1) & 1u, abort_flag, p.status);
+                    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->p_full[pb], (uint32_t)(p_no >> 1) & 1u, abort_flag, p.status)) != 0;
                     if (!ok) break;
                     const long long t3 = AT_CLOCK();
                     tc_fence_after();
                     // O += P_j V_{c_j}: A = P (K-major), B = V tiles (N contiguous), N = head_dim
                     const uint64_t da = make_tile_desc(smem_u32(p_smem + pb * kTileBytes), false);
                     const uint64_t db = make_tile_desc(smem_u32(v_smem + vs * set_bytes), true);
+                    const uint32_t d = tmem_base + (uint32_t)(WGS == 2 ? (p_no & 1) * p.head_dim : 0);
+                    if (elect_one()) {
 #pragma unroll
-                    for (int kk = 0; kk < kTile / 16; ++kk)
-                        tc_mma_f16(tmem_base + (uint32_t)(WGS == 2 ? (p_no & 1) * p.head_dim : 0), da + (uint64_t)(kk * 2),
-                                   db + (uint64_t)(kk * (2048 >> 4)), idesc_pv, (j >= WGS || kk > 0) ? 1u : 0u);
-                    tc_commit(&bars->pv_done[vs]);
-                    if (j == n - 1) tc_commit(&bars->o_full);
-                    AT_ADD(14, t1 - t0); AT_ADD(15, t2 - t1); AT_ADD(16, t3 - t2); AT_ADD(17, AT_CLOCK() - t3);
+                        for (int kk = 0; kk < kTile / 16; ++kk)
+                            tc_mma_f16(d, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * (2048 >> 4)), idesc_pv,
+                                       (j >= WGS || kk > 0) ? 1u : 0u);
+                        tc_commit(&bars->pv_done[vs]);
+                        if (j == n - 1) tc_commit(&bars->o_full);
+                    }
+                    __syncwarp();
+                    if (lane == 0) { AT_ADD(14, t1 - t0); AT_ADD(15, t2 - t1); AT_ADD(16, t3 - t2); AT_ADD(17, AT_CLOCK() - t3); }
                 }
                 ++o_no;
             }
-            tc_commit(&bars->drain);
-            mbar_wait(&bars->drain, 0, abort_flag, p.status);
+            if (elect_one()) {
+                tc_commit(&bars->drain);
+                mbar_wait(&bars->drain, 0, abort_flag, p.status);
+            }
         }
         __syncwarp();
     } else {

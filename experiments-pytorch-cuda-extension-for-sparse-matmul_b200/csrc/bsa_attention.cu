@@ -195,26 +195,22 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             if (cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
             const int n = cur.count;
             if (n > 0) {
-                if (lane == 0 && !is_v) {
-                    // Q tile set number q goes to buffer q % qbufs once the Q K^T of the item that used
-                    // the buffer last have retired.  With two buffers the next item's set is requested
-                    // here, a whole item ahead of its first use.
-                    auto issue_q = [&](int q, int z, int g) -> bool {
-                        const int qb = q & (p.qbufs - 1);
-                        const uint32_t use = (uint32_t)(p.qbufs == 2 ? q >> 1 : q);
-                        if (!mbar_wait(&bars->q_empty[qb], (use & 1u) ^ 1u, abort_flag, p.status)) return false;
-                        mbar_expect_tx(&bars->q_full[qb], (uint32_t)set_bytes);
-                        for (int t = 0; t < p.dtiles; ++t)
-                            tma_load_3d(q_smem + qb * set_bytes + t * kTileBytes, &map_q, &bars->q_full[qb], t * kTile, g * kTile, z);
-                        return true;
-                    };
+                // Q tile set number q goes to buffer q % qbufs once the Q K^T of the item that used the
+                // buffer last have retired.  With two buffers the next item's set is requested after
+                // this item's K tiles (before them the request would wait for the previous item's last
+                // Q K^T with nothing in flight behind it).
+                auto issue_q = [&](int q, int z, int g) -> bool {
+                    const int qb = q & (p.qbufs - 1);
+                    const uint32_t use = (uint32_t)(p.qbufs == 2 ? q >> 1 : q);
+                    if (!mbar_wait(&bars->q_empty[qb], (use & 1u) ^ 1u, abort_flag, p.status)) return false;
+                    mbar_expect_tx(&bars->q_full[qb], (uint32_t)set_bytes);
+                    for (int t = 0; t < p.dtiles; ++t)
+                        tma_load_3d(q_smem + qb * set_bytes + t * kTileBytes, &map_q, &bars->q_full[qb], t * kTile, g * kTile, z);
+                    return true;
+                };
+                if (lane == 0 && !is_v && !q_prefetched) {
                     const long long tq = AT_CLOCK();
-                    if (!q_prefetched) ok = issue_q(q_no, cur.z, cur.g);
-                    q_prefetched = false;
-                    if (ok && p.qbufs == 2 && cur.has_next() && cur.next_count() > 0) {
-                        ok = issue_q(q_no + 1, cur.z1, cur.r1);
-                        q_prefetched = true;
-                    }
+                    ok = issue_q(q_no, cur.z, cur.g);
                     AT_ADD(0, AT_CLOCK() - tq);
                 }
                 ++q_no;
@@ -248,6 +244,12 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     }
                     ++kv_no;
                 }
+                q_prefetched = false;
+                if (ok && lane == 0 && !is_v && p.qbufs == 2 && cur.has_next() && cur.next_count() > 0) {
+                    ok = issue_q(q_no, cur.z1, cur.r1);        // q_no already counts this item
+                    q_prefetched = true;
+                }
+                ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
             }
             pre = pre_next;
             cur.advance();

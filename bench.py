@@ -305,6 +305,17 @@ def run_ours(args):
     d1.record()
     torch.cuda.synchronize()
     dds_ms = d0.elapsed_time(d1) / 5
+    # the fused forward (one kernel for sdd -> softmax -> dsd), reported beside the unfused operators
+    from sparse.attention import attention_lse
+    for _ in range(3):
+        attention_lse(q, k, v, lay, scale)
+    d0.record()
+    for _ in range(10):
+        attention_lse(q, k, v, lay, scale)
+    d1.record()
+    torch.cuda.synchronize()
+    sparse_ops.check_device_status(local_rank)
+    fused_ms = d0.elapsed_time(d1) / 10
 
     # ---- max over ranks
     t = torch.tensor([elapsed_ms, e2e_ms], device=dev, dtype=torch.float64)
@@ -331,6 +342,14 @@ def run_ours(args):
                                  "hbm_frac": round(dds_gbs / peaks["hbm_gbs"], 4),
                                  "TFLOP/s": round(flops_matmul / (dds_ms * 1e-3) / 1e12, 1),
                                  "tensor_frac": round(flops_matmul / (dds_ms * 1e-3) / 1e12 / peaks["bf16_tflops"], 4)}
+        unfused_fwd_ms = op_ms["sdd_qk"] + op_ms["softmax_fwd"] + op_ms["dsd_pv"]
+        fused_tf = 2 * flops_matmul / (fused_ms * 1e-3) / 1e12
+        fused_report = {"kernel": "attention_forward_kernel", "ms": round(fused_ms, 4),
+                        "TFLOP/s": round(fused_tf, 1), "tensor_frac": round(fused_tf / peaks["bf16_tflops"], 4),
+                        "unfused_forward_ms": round(unfused_fwd_ms, 4), "speedup": round(unfused_fwd_ms / fused_ms, 2),
+                        "hbm_bytes": 4 * dense_bytes,
+                        "note": "forward only, outside the timed step; Q, K, V read and O written once, "
+                                "scores and probabilities never leave the SM"}
         # dominant kernel = the kernel with the largest total time inside a step
         kernels = {
             "tc_matmul_kernel<dsd> (4 launches/step)": ["dsd_pv", "dsd_dv", "dsd_dq", "dsd_dk"],
@@ -369,7 +388,7 @@ def run_ours(args):
                     "ms_per_step": round(e2e_ms / e2e_steps, 4),
                     "h2d_bytes_per_step": 4 * dense_bytes, "d2h_bytes_per_step": 4 * dense_bytes},
             "gpu_launches": len(OPS) * args.steps,
-            "clocks": clocks, "ops": ops_report,
+            "clocks": clocks, "ops": ops_report, "fused_forward": fused_report,
             "engine": os.environ.get("BSA_MATMUL_ENGINE", "auto"),
         }
         if cpu_dt is not None:

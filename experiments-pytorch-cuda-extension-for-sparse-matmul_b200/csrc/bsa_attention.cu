@@ -90,15 +90,6 @@ struct AttnParams {
     uint32_t idesc_qk, idesc_pv;
 };
 
-// True in exactly one lane of a converged warp.  Code around an `if (elect_one())` stays
-// warp-uniform, so the descriptors of the tcgen05 instructions inside it are computed once per
-// warp in uniform registers instead of being moved there per instruction.
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred;
-    asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
-    return pred != 0;
-}
-
 __device__ __forceinline__ float attn_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

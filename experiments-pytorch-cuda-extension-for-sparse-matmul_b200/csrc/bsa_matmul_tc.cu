@@ -257,12 +257,14 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                             d = win.get(p.blocks, cur.first, cur.count, k, lane);
                         }
                         t_get += TC_CLOCK() - t_g0;
-                        if (lane == 0) {
+                        {
+                            // the whole warp waits and computes the copies' operands (warp-uniform
+                            // code keeps them in uniform registers); one elected lane issues
                             const long long t0 = TC_CLOCK();
-                            ok = mbar_wait(&bars->empty[stage], phase ^ 1, &bars->abort_flag, p.status);
+                            ok = __all_sync(0xffffffffu, mbar_wait(&bars->empty[stage], phase ^ 1, &bars->abort_flag, p.status)) != 0;
                             const long long t1 = TC_CLOCK();
                             t_wait += t1 - t0;
-                            if (ok) {
+                            if (ok && elect_one()) {
                                 uint8_t* slot = stage_base + stage * stage_bytes;
                                 uint64_t* full = &bars->full[stage];
                                 mbar_expect_tx(full, (uint32_t)((1 + nb) * kTileBytes));
@@ -294,9 +296,9 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                     tma_load_3d(slot + kTileBytes, &map_b, full, 0, d.idx * kTile, cur.z);
                                 }
                             }
+                            __syncwarp();
                             t_issue += TC_CLOCK() - t1;
                         }
-                        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
                     }
                     stage += kProducerWarps;
                     if (stage >= p.stages) { stage -= p.stages; phase ^= 1; }
@@ -318,7 +320,10 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     } else if (warp < kFirstEpilogueWarp) {
         // ------------------------------------------------------------ MMA issuers
         const int w = warp - kFirstMmaWarp;
-        if (lane == 0 && w < p.issuers) {
+        if (w < p.issuers) {
+            // The whole warp runs the loop (warp-uniform code keeps the descriptors in uniform registers:
+            // issuing from a single diverged lane costs about twice as much per instruction); one
+            // elected lane executes the tcgen05 instructions.
             // Own stage pointer.  dsd / dds: this issuer's K-steps are w, w + issuers, ... of the CTA,
             // so the pointer advances by `issuers`.  sdd with two issuers: accumulations alternate,
             // so it runs through one accumulation's stages and then skips the other issuer's.
@@ -352,7 +357,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     const int nb = b_tiles<MODE>(p, cur.count, cur.chunk, f);
                     const uint32_t idesc = p.idesc | ((uint32_t)((nb * kTile) >> 3) << 17);
                     { const long long t0 = TC_CLOCK();
-                      ok = mbar_wait(&bars->acc_empty[acc], ((uint32_t)(flush_no >> 1) & 1u) ^ 1u, &bars->abort_flag, p.status);
+                      ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_empty[acc], ((uint32_t)(flush_no >> 1) & 1u) ^ 1u, &bars->abort_flag, p.status)) != 0;
                       t_acc += TC_CLOCK() - t0; }
                     if (!ok) break;
                     tc_fence_after();
@@ -366,7 +371,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     for (int k = k_first; k < ksteps; k += k_inc) {
                         {
                             { const long long t0 = TC_CLOCK();
-                              ok = mbar_wait(&bars->full[stage], phase, &bars->abort_flag, p.status);
+                              ok = __all_sync(0xffffffffu, mbar_wait(&bars->full[stage], phase, &bars->abort_flag, p.status)) != 0;
                               t_full += TC_CLOCK() - t0; }
                             if (!ok) break;
                             const long long tm0 = TC_CLOCK();
@@ -375,13 +380,16 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                             const uint64_t da = make_tile_desc(slot, a_mn_major);
                             const uint64_t db = make_tile_desc(slot + kTileBytes, b_mn_major);
                             const long long tm1 = TC_CLOCK();
+                            if (elect_one()) {
 #pragma unroll
-                            for (int kk = 0; kk < kTile / 16; ++kk)
-                                tc_mma_f16(d, da + (uint64_t)(kk * a_kstep), db + (uint64_t)(kk * b_kstep), idesc,
-                                           (issued || kk > 0) ? 1u : 0u);
+                                for (int kk = 0; kk < kTile / 16; ++kk)
+                                    tc_mma_f16(d, da + (uint64_t)(kk * a_kstep), db + (uint64_t)(kk * b_kstep), idesc,
+                                               (issued || kk > 0) ? 1u : 0u);
+                                tc_commit(&bars->empty[stage]);  // the stage is free once these MMAs have read it
+                            }
+                            __syncwarp();
                             issued = true;
                             const long long tm2 = TC_CLOCK();
-                            tc_commit(&bars->empty[stage]);      // the stage is free once these MMAs have read it
                             t_desc += tm1 - tm0; t_mma += tm2 - tm1; t_commit += TC_CLOCK() - tm2;
                         }
                         stage += k_inc;
@@ -391,15 +399,22 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     if (!ok) break;
                     const long long tk1 = TC_CLOCK();
                     // the accumulation (dsd / dds: this issuer's partial, if it had a K-step) is complete
-                    if (issued) tc_commit(&bars->acc_full[acc]);
-                    else        mbar_arrive(&bars->acc_full[acc]);
+                    if (elect_one()) {
+                        if (issued) tc_commit(&bars->acc_full[acc]);
+                        else        mbar_arrive(&bars->acc_full[acc]);
+                    }
+                    __syncwarp();
                     t_kloop += tk1 - tk0; t_accfull += TC_CLOCK() - tk1;
                 }
             }
-            // All MMAs issued by this thread must have retired before TMEM is freed.
-            tc_commit(&bars->drain);
-            mbar_wait(&bars->drain, 0, &bars->abort_flag, p.status);
-            if (w == 0) { TC_TIME_OUT(3, TC_CLOCK() - t_begin); TC_TIME_OUT(4, t_full); TC_TIME_OUT(5, t_acc);
+            // All MMAs issued by the elected lane (the same one every time) must have retired before
+            // TMEM is freed.
+            if (elect_one()) {
+                tc_commit(&bars->drain);
+                mbar_wait(&bars->drain, 0, &bars->abort_flag, p.status);
+            }
+            __syncwarp();
+            if (w == 0 && lane == 0) { TC_TIME_OUT(3, TC_CLOCK() - t_begin); TC_TIME_OUT(4, t_full); TC_TIME_OUT(5, t_acc);
                           TC_TIME_OUT(12, t_mma); TC_TIME_OUT(13, t_commit); TC_TIME_OUT(14, t_desc);
                           TC_TIME_OUT(15, t_kloop); TC_TIME_OUT(16, t_accfull); }
         }

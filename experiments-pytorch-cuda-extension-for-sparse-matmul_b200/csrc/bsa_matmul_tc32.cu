@@ -237,9 +237,11 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     } else {
                         d = win.get(p.blocks, cur.first, cur.count, k, lane);
                     }
-                    if (lane == 0) {
-                        ok = mbar_wait(&bars->empty[stage], phase ^ 1, abort_flag, p.status);
-                        if (ok) {
+                    {
+                        // the whole warp waits (warp-uniform code keeps the copies' operands in uniform
+                        // registers); one elected lane issues
+                        ok = __all_sync(0xffffffffu, mbar_wait(&bars->empty[stage], phase ^ 1, abort_flag, p.status)) != 0;
+                        if (ok && elect_one()) {
                             uint8_t* slot = stage_base + stage * p.stage_bytes;
                             uint8_t* slot_b = slot + 2 * kPanelBytes;
                             uint64_t* full = &bars->full[stage];
@@ -275,8 +277,8 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                 tma_load_3d(slot_b, &map_b, full, 0, d.idx * kBlk, cur.z);
                             }
                         }
+                        __syncwarp();
                     }
-                    ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
                     stage += kProducerWarps;
                     if (stage >= p.stages) { stage -= p.stages; phase ^= 1; }
                 }
@@ -296,7 +298,9 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     } else if (warp < kFirstEpilogueWarp) {
         // ------------------------------------------------------------ MMA issuers
         const int w = warp - kFirstMmaWarp;
-        if (lane == 0 && w < p.issuers) {
+        if (w < p.issuers) {
+            // (the whole warp runs the loop so that the descriptors stay in uniform registers; one
+            // elected lane executes the tcgen05 instructions)
             // dsd / dds: this issuer's K-steps are w, w + issuers, ... of the CTA.  sdd with two
             // issuers: accumulations alternate, so it runs through one accumulation's stages and
             // then skips the other issuer's (the host guarantees fixed stage ownership).
@@ -325,7 +329,7 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     }
                     const int nb = b_panels<MODE>(p, cur.count, cur.chunk, f);
                     const uint32_t idesc = p.idesc | ((uint32_t)((nb * kBlk) >> 3) << 17);
-                    ok = mbar_wait(&bars->acc_empty[acc], ((uint32_t)(flush_no >> 1) & 1u) ^ 1u, abort_flag, p.status);
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_empty[acc], ((uint32_t)(flush_no >> 1) & 1u) ^ 1u, abort_flag, p.status)) != 0;
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t d = tmem_base + (uint32_t)(acc * kAccCols) + part_col;
@@ -333,39 +337,48 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     const int k_first = is_sdd ? 0 : ((w - step0) & issuer_mask);
                     const int k_inc = is_sdd ? 1 : p.issuers;
                     for (int k = k_first; k < ksteps; k += k_inc) {
-                        ok = mbar_wait(kSplit ? &bars->ready[stage] : &bars->full[stage], phase, abort_flag, p.status);
+                        ok = __all_sync(0xffffffffu, mbar_wait(kSplit ? &bars->ready[stage] : &bars->full[stage], phase, abort_flag, p.status)) != 0;
                         if (!ok) break;
                         tc_fence_after();
                         const uint32_t slot = smem_u32(stage_base + stage * p.stage_bytes);
                         const uint64_t da = desc_a0 | (uint64_t)((slot & 0x3FFFFu) >> 4);
                         const uint64_t db = desc_b0 | (uint64_t)(((slot + 2 * kPanelBytes) & 0x3FFFFu) >> 4);
+                        if (elect_one()) {
 #pragma unroll
-                        for (int kk = 0; kk < kMmasPerStep; ++kk) {
-                            const uint64_t a = da + (uint64_t)(kk * a_kstep), b = db + (uint64_t)(kk * b_kstep);
-                            const uint32_t accumulate = (issued || kk > 0) ? 1u : 0u;
-                            if (kSplit) {
-                                tc_mma_tf32(d, a, b + lo, idesc, accumulate);     // hi * lo
-                                tc_mma_tf32(d, a + lo, b, idesc, 1u);             // lo * hi
-                                tc_mma_tf32(d, a, b, idesc, 1u);                  // hi * hi
-                            } else {
-                                tc_mma_f16(d, a, b, idesc, accumulate);
+                            for (int kk = 0; kk < kMmasPerStep; ++kk) {
+                                const uint64_t a = da + (uint64_t)(kk * a_kstep), b = db + (uint64_t)(kk * b_kstep);
+                                const uint32_t accumulate = (issued || kk > 0) ? 1u : 0u;
+                                if (kSplit) {
+                                    tc_mma_tf32(d, a, b + lo, idesc, accumulate);     // hi * lo
+                                    tc_mma_tf32(d, a + lo, b, idesc, 1u);             // lo * hi
+                                    tc_mma_tf32(d, a, b, idesc, 1u);                  // hi * hi
+                                } else {
+                                    tc_mma_f16(d, a, b, idesc, accumulate);
+                                }
                             }
+                            tc_commit(&bars->empty[stage]);  // the stage is free once these MMAs have read it
                         }
+                        __syncwarp();
                         issued = true;
-                        tc_commit(&bars->empty[stage]);      // the stage is free once these MMAs have read it
                         stage += k_inc;
                         if (stage >= p.stages) { stage -= p.stages; phase ^= 1; }
                     }
                     step0 += ksteps;
                     if (!ok) break;
                     // the accumulation (dsd / dds: this issuer's partial, if it had a K-step) is complete
-                    if (issued) tc_commit(&bars->acc_full[acc]);
-                    else        mbar_arrive(&bars->acc_full[acc]);
+                    if (elect_one()) {
+                        if (issued) tc_commit(&bars->acc_full[acc]);
+                        else        mbar_arrive(&bars->acc_full[acc]);
+                    }
+                    __syncwarp();
                 }
             }
-            // All MMAs issued by this thread must have retired before TMEM is freed.
-            tc_commit(&bars->drain);
-            mbar_wait(&bars->drain, 0, abort_flag, p.status);
+            // All MMAs issued by the elected lane (the same one every time) must have retired before
+            // TMEM is freed.
+            if (elect_one()) {
+                tc_commit(&bars->drain);
+                mbar_wait(&bars->drain, 0, abort_flag, p.status);
+            }
         }
         __syncwarp();
     } else if (kSplit && warp >= kFirstSplitWarp) {

@@ -9,5 +9,6 @@ from .layout import SparseLayout
 from .matmul import matmul, SparseMatMul
 from .softmax import softmax, SparseSoftmax
 from .attention import attention, SparseAttention
+from .module import BlockSparseSelfAttention
 
-__all__ = ["SparseLayout", "matmul", "SparseMatMul", "softmax", "SparseSoftmax", "attention", "SparseAttention"]
+__all__ = ["SparseLayout", "matmul", "SparseMatMul", "softmax", "SparseSoftmax", "attention", "SparseAttention", "BlockSparseSelfAttention"]

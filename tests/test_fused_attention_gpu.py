@@ -145,3 +145,29 @@ def test_attention_composes_unfused_ops_where_the_fused_kernel_does_not_apply():
     out = attention(q.cuda(), k.cuda(), v.cuda(), layout, 0.125, True)
     ref, _ = oracle.attention_forward_dense(q, k, v, pattern.numpy(), 32, 0.125, True)
     assert_close(out, ref, torch.float32, "fp32 block-32 attention")
+
+
+def test_self_attention_module_matches_dense_reference():
+    """The nn.Module (QKV projection -> block-sparse attention -> output projection) against the same
+    computation with dense masked attention, forward and the gradient of the input."""
+    from sparse import SparseLayout, BlockSparseSelfAttention
+    from sparse.patterns import local_global_causal
+    pattern = local_global_causal(8, 3, 1)
+    layout = SparseLayout(pattern, block=64)
+    torch.manual_seed(0)
+    mod = BlockSparseSelfAttention(256, 4, layout, causal=True, device="cuda", dtype=torch.float16)
+    x = (0.5 * seeded((2, 512, 256), 95, torch.float16)).cuda().requires_grad_(True)
+    y = mod(x)
+    y.float().square().mean().backward()
+    # dense reference with the same weights, in fp32 on the CPU
+    xr = x.detach().float().cpu().requires_grad_(True)
+    w_qkv, b_qkv = mod.qkv.weight.detach().float().cpu(), mod.qkv.bias.detach().float().cpu()
+    w_out, b_out = mod.out.weight.detach().float().cpu(), mod.out.bias.detach().float().cpu()
+    qkv = (xr @ w_qkv.t() + b_qkv).view(2, 512, 3, 4, 64).permute(2, 0, 3, 1, 4)
+    keep = oracle._score_mask(pattern.numpy(), 64, True, None, (2, 4))
+    scores = (qkv[0] @ qkv[1].transpose(-1, -2)) * 64 ** -0.5
+    probs = torch.softmax(scores.masked_fill(~keep, float("-inf")), dim=-1)
+    ref = (probs @ qkv[2]).transpose(1, 2).reshape(2, 512, 256) @ w_out.t() + b_out
+    ref.square().mean().backward()
+    assert_close(y, ref.detach(), torch.float16, "module output")
+    assert_close(x.grad, xr.grad, torch.float16, "module input gradient")

@@ -95,6 +95,34 @@ def test_softmax_and_layout_validation_codes(lib):
     assert g(16, 9, 2, 2, 16, 16, 16, 16, 16, None) == 3
 
 
+def test_attention_validation_codes(lib):
+    f = lib.bsa_attention_forward
+    f.argtypes = [ctypes.c_int] + [ctypes.c_void_p] * 7 + [ctypes.c_int64] * 5 + \
+        [ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
+         ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
+
+    def call(dtype=1, q=16, o=16, lse=16, blocks=16, nnz=1, rows=1, cols=1, batches=1, d=64, block=64,
+             kpm=None, kpm_batches=0, kpm_stride=0, ws=16, ws_bytes=256):
+        return f(dtype, q, 16, 16, o, lse, blocks, 16, nnz, rows, cols, batches, d, block, 1.0, 0,
+                 kpm, kpm_batches, kpm_stride, ws, ws_bytes, None)
+
+    # rejected on the host before any CUDA call (the pointers are fake)
+    assert call(dtype=9) == 3                      # BSA_ERR_BAD_DTYPE
+    assert call(dtype=0) == 3                      # fp32 has no fused kernel: callers compose the unfused ops
+    assert call(block=48) == 5                     # BSA_ERR_BAD_BLOCK
+    assert call(block=32) == 4                     # BSA_ERR_BAD_SHAPE: only block 64 is fused
+    assert call(d=96) == 4
+    assert call(q=None) == 1                       # BSA_ERR_NULL_POINTER
+    assert call(ws=None) == 7                      # BSA_ERR_WORKSPACE
+    assert call(q=24) == 6                         # BSA_ERR_ALIGNMENT
+    assert call(nnz=5) == 4                        # more blocks than the 1 x 1 grid holds
+    assert call(batches=70000) == 10               # BSA_ERR_TOO_LARGE
+    assert call(kpm=16, kpm_batches=2, kpm_stride=64, batches=3) == 4
+    assert call(kpm=16, kpm_batches=1, kpm_stride=32) == 4      # mask shorter than the key sequence
+    assert call(batches=0) == 0                    # nothing to do is not an error
+    assert call(lse=None, batches=0) == 0          # the log-sum-exp output is optional
+
+
 class OracleOps:
     """CPU stand-in for the native binding (the oracle as the engine), recording every call."""
 

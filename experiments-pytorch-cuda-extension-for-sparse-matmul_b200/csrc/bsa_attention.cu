@@ -61,11 +61,11 @@ struct __align__(8) AttnBarriers {
     uint64_t s_empty[2];
     uint64_t p_full[2];
     uint64_t o_full, o_empty;
-    uint64_t stat_full[2], stat_empty[2];   // two softmax groups: hand-over of group 1's row maxima and sums
+    uint64_t stat_full[2][2], stat_empty[2][2];   // two softmax groups: hand-over of row maxima and sums, [writer][slot]
     uint64_t drain;
     uint32_t tmem_base;
     int abort_flag;
-    float stat[2][kTile][2];
+    float stat[2][2][kTile][2];
 };
 
 struct AttnParams {
@@ -151,7 +151,8 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             mbar_init(&bars->v_full[s], 1); mbar_init(&bars->pv_done[s], 1);
         }
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&bars->s_empty[s], 4); mbar_init(&bars->stat_full[s], 4); mbar_init(&bars->stat_empty[s], 4);
+            mbar_init(&bars->s_empty[s], 4);
+            for (int d = 0; d < 2; ++d) { mbar_init(&bars->stat_full[d][s], 4); mbar_init(&bars->stat_empty[d][s], 4); }
         }
         mbar_init(&bars->o_full, 1); mbar_init(&bars->o_empty, 4);
         mbar_init(&bars->drain, 2);
@@ -376,6 +377,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         // MASKED = false: no causal or key-padding mask, all mask tests fold away
         const bool masked_op = MASKED && (p.causal != 0 || p.kpm != nullptr);
         int s_no = 0, o_no = 0;                     // S tiles and non-empty items before the current item
+        int x_no[2] = {0, 0};                       // hand-overs so far in which group 0 / group 1 was the writer
         bool ok = true;
         const long long t_begin = AT_CLOCK();
         Cursor cur;
@@ -579,14 +581,20 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
                 // weights of this group's (w) and the other group's (v) accumulator in the result
                 float w_a = 1.f, w_b = 1.f, v_a = 0.f, v_b = 0.f;
+                // The group that owns the item's last tile finishes the item; the other one owns the
+                // next item's first tile and goes on right away.
+                const int epi_wg = WGS == 2 ? ((s_no - 1) & 1) : 0;
                 if (WGS == 2) {
-                    // group 1 hands its maxima and sums to group 0 through shared memory (two slots,
-                    // alternating by item); the partial softmaxes over the two groups' key sets merge as
-                    // m = max(m0, m1), l = l0 2^(m0 - m) + l1 2^(m1 - m), O likewise
-                    const int slot = o_no & 1;
-                    float* stat = &bars->stat[slot][0][0];
-                    if (wg == 1) {
-                        ok = __all_sync(0xffffffffu, mbar_wait(&bars->stat_empty[slot], ((uint32_t)(o_no >> 1) & 1u) ^ 1u, abort_flag, p.status)) != 0;
+                    // the other group hands its maxima and sums over through shared memory (per direction
+                    // two slots, alternating); the partial softmaxes over the two groups' key sets merge
+                    // as m = max(m0, m1), l = l0 2^(m0 - m) + l1 2^(m1 - m), O likewise
+                    const int dir = epi_wg ^ 1;                 // the group that writes
+                    const int slot = x_no[dir] & 1;
+                    const uint32_t par = (uint32_t)(x_no[dir] >> 1) & 1u;
+                    ++x_no[dir];
+                    float* stat = &bars->stat[dir][slot][0][0];
+                    if (wg != epi_wg) {
+                        ok = __all_sync(0xffffffffu, mbar_wait(&bars->stat_empty[dir][slot], par ^ 1u, abort_flag, p.status)) != 0;
                         if (!ok) break;
                         if (q4 == 0) {
                             stat[row_a * 2] = m_a; stat[row_a * 2 + 1] = l_a;
@@ -594,16 +602,16 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         }
                         __threadfence_block();
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(&bars->stat_full[slot]);
+                        if (lane == 0) mbar_arrive(&bars->stat_full[dir][slot]);
                     } else {
                         const long long ts0 = AT_CLOCK();
-                        ok = __all_sync(0xffffffffu, mbar_wait(&bars->stat_full[slot], (uint32_t)(o_no >> 1) & 1u, abort_flag, p.status)) != 0;
+                        ok = __all_sync(0xffffffffu, mbar_wait(&bars->stat_full[dir][slot], par, abort_flag, p.status)) != 0;
                         if (!ok) break;
                         if (warp == 4 && lane == 0) AT_ADD(22, AT_CLOCK() - ts0);
                         const float mo_a = stat[row_a * 2], lo_a = stat[row_a * 2 + 1];
                         const float mo_b = stat[(row_a + 8) * 2], lo_b = stat[(row_a + 8) * 2 + 1];
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(&bars->stat_empty[slot]);
+                        if (lane == 0) mbar_arrive(&bars->stat_empty[dir][slot]);
                         const float mm_a = fmaxf(m_a, mo_a), mm_b = fmaxf(m_b, mo_b);
                         w_a = m_a == -INFINITY ? 0.f : attn_exp2(m_a - mm_a);
                         v_a = mo_a == -INFINITY ? 0.f : attn_exp2(mo_a - mm_a);
@@ -613,9 +621,9 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         l_b = l_b * w_b + lo_b * v_b;  m_b = mm_b;
                     }
                 }
-                if (wg == 0) {
+                if (wg == epi_wg) {
                     // ---- end of the row: O / l
-                    const float inv_a = l_a > 0.f ? 1.f / l_a : 0.f, inv_b = l_b > 0.f ? 1.f / l_b : 0.f;
+                    const float inv_a = l_a > 0.f ? __frcp_rn(l_a) : 0.f, inv_b = l_b > 0.f ? __frcp_rn(l_b) : 0.f;
                     const float sw_a = w_a * inv_a, sv_a = v_a * inv_a, sw_b = w_b * inv_b, sv_b = v_b * inv_b;
                     const long long te0 = AT_CLOCK();
                     ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full, (uint32_t)(o_no & 1), abort_flag, p.status)) != 0;
@@ -624,8 +632,8 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     tc_fence_after();
                     for (int c = 0; c < p.head_dim; c += 32) {
                         uint32_t r0[16], r1[16];
-                        tc_ld_16x256b_x4(tmem_base + lane_field + (uint32_t)c, r0);
-                        if (WGS == 2) tc_ld_16x256b_x4(tmem_base + lane_field + (uint32_t)(p.head_dim + c), r1);
+                        tc_ld_16x256b_x4(tmem_base + lane_field + o_col + (uint32_t)c, r0);
+                        if (WGS == 2) tc_ld_16x256b_x4(tmem_base + lane_field + (uint32_t)((wg ^ 1) * p.head_dim + c), r1);
                         tc_wait_ld();
                         if (c + 32 >= p.head_dim) release_accumulator(&bars->o_empty, lane);
                         uint32_t ta[4], tb[4];
@@ -651,8 +659,8 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     if (warp == 4 && lane == 0) { AT_ADD(8, te1 - te0); AT_ADD(9, AT_CLOCK() - te1); }
                     if (q4 == 0 && p.lse) {
                         // natural-log sum of exponentials of the scaled, masked scores
-                        p.lse[lse_a] = l_a > 0.f ? (m_a + log2f(l_a)) * 0.6931471805599453f : -INFINITY;
-                        p.lse[lse_a + 8] = l_b > 0.f ? (m_b + log2f(l_b)) * 0.6931471805599453f : -INFINITY;
+                        p.lse[lse_a] = l_a > 0.f ? (m_a + __log2f(l_a)) * 0.6931471805599453f : -INFINITY;
+                        p.lse[lse_a + 8] = l_b > 0.f ? (m_b + __log2f(l_b)) * 0.6931471805599453f : -INFINITY;
                     }
                 }
                 ++o_no;

@@ -51,6 +51,7 @@ namespace {
 
 constexpr int kMaxStages = 13;
 constexpr int kStageTiles = 27;                 // operand tiles in all stages: 13 x 2, 9 x 3 or 5 x 5
+constexpr int kSddStagingTile0 = 20;            // sdd: tiles 20 .. 23 hold the epilogue warps' output slabs (4 stages x 5 tiles come first)
 constexpr int kAccCols = 256;                   // TMEM columns per accumulator buffer
 constexpr int kTmemCols = 2 * kAccCols;
 constexpr int kProducerWarps = 4;
@@ -182,7 +183,8 @@ __device__ __forceinline__ void store_row(uint16_t* dst, const uint32_t (&v)[NCO
 // four different code paths through the same instruction caches).
 template <int MODE, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
-tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p) {
+tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const __grid_constant__ CUtensorMap map_c, const TcParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* stage_base = smem;                                   // p.stages * (1 + p.nb_max) tiles
@@ -429,6 +431,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int parts = is_sdd ? 1 : p.issuers;
         const int part_stride = kAccCols / p.issuers;
         int flush_no = 0, step = 0;
+        int tile_no = 0;                    // sdd: slabs this warp has sent so far (staging slab = tile_no & 1)
         bool ok = true;
         long long t_accf = 0, t_ld = 0, t_write = 0;
         const long long t_begin = TC_CLOCK();
@@ -461,6 +464,75 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     t_accf += TC_CLOCK() - t0;
                     if (!ok) break;
                     tc_fence_after();
+                }
+                if (is_sdd) {
+                    // Sparse output tiles leave through shared memory and TMA: the warp converts its 16
+                    // accumulator rows, writes them with four stmatrix instructions (the 16x256b TMEM
+                    // load hands out exactly the m8n8 fragment layout) into its own 128-byte-swizzled
+                    // 2 KB staging slab and sends the slab to global memory with one bulk tensor store
+                    // (box 16 x 64).  About 30 instructions per lane and tile instead of 110 for a
+                    // shuffle-transpose / 128-bit store path, no synchronisation between warps, and
+                    // the stores are asynchronous (two slabs per warp alternate).
+                    // The tiles of an accumulation are ready together: the TMEM load of tile t + 1 is in
+                    // flight while tile t is converted.
+                    const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * kAccCols);
+                    // lane -> row address of its 8x8 matrix: matrix i = lane / 8 holds rows (i & 1) * 8 ..
+                    // of 16-byte column unit u = 2k + (i >> 1)
+                    const int sm_row = ((lane >> 3) & 1) * 8 + (lane & 7);        // row inside the slab
+                    const uint32_t sm_unit = (uint32_t)(lane >> 4);
+                    const int slab0 = ((warp - kFirstEpilogueWarp) * 2) * (16 * 128);   // this warp's two slabs
+                    auto store_tile = [&](const uint32_t (&r)[32], int t) {
+                        const int out_idx = win.get(p.blocks, cur.first, cur.count, 4 * f + t, lane).idx;
+                        // a descriptor that does not belong to this layout is reported in the workspace
+                        // (word 1 = offending tile index); the tensor map clips the store itself
+                        const bool in_bounds = out_idx >= 0 && out_idx < p.nnz;
+                        if (!in_bounds && lane == 0) {
+                            atomicExch(p.status, (uint32_t)BSA_ERR_BAD_SHAPE);
+                            atomicExch(p.status + 1, (uint32_t)out_idx);
+                        }
+                        const uint32_t slab = smem_u32(stage_base + kSddStagingTile0 * kTileBytes + slab0 + (tile_no & 1) * (16 * 128));
+                        // the slab written now was sent two tiles ago: that store must have read it
+                        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                        __syncwarp();
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            uint32_t w[4];                      // matrices (u = 2k, rows a), (2k, b), (2k + 1, a), (2k + 1, b)
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int u = 2 * k + (i >> 1), h = i & 1;
+                                const float lo = __uint_as_float(r[4 * u + 2 * h]), hi = __uint_as_float(r[4 * u + 2 * h + 1]);
+                                if (bf16_out) { __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi); w[i] = *reinterpret_cast<uint32_t*>(&v); }
+                                else          { __half2 v = __floats2half2_rn(lo, hi); w[i] = *reinterpret_cast<uint32_t*>(&v); }
+                            }
+                            const uint32_t addr = slab + (uint32_t)(sm_row * 128) + ((((uint32_t)(2 * k) + sm_unit) ^ (uint32_t)(sm_row & 7)) << 4);
+                            asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1, %2, %3, %4};"
+                                         ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+                        }
+                        fence_async_shared();           // generic-proxy writes -> visible to the bulk store
+                        __syncwarp();
+                        if (lane == 0 && in_bounds) {
+                            asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                                         ::"l"(&map_c), "r"(slab), "r"(0), "r"(out_idx * kTile + quad * 16), "r"(cur.z) : "memory");
+                        }
+                        if (lane == 0) asm volatile("cp.async.bulk.commit_group;" ::: "memory");   // (empty groups keep the count regular)
+                        ++tile_no;
+                    };
+                    const long long t_a = TC_CLOCK();
+                    uint32_t ra[32], rb[32];
+                    tc_ld_16x256b_x8(tbase, ra);
+                    for (int t = 0; t < tiles; t += 2) {
+                        tc_wait_ld();
+                        if (t + 1 < tiles) tc_ld_16x256b_x8(tbase + (uint32_t)((t + 1) * kTile), rb);
+                        else               release_accumulator(&bars->acc_empty[acc], lane);
+                        store_tile(ra, t);
+                        if (t + 1 >= tiles) break;
+                        tc_wait_ld();
+                        if (t + 2 < tiles) tc_ld_16x256b_x8(tbase + (uint32_t)((t + 2) * kTile), ra);
+                        else               release_accumulator(&bars->acc_empty[acc], lane);
+                        store_tile(rb, t + 1);
+                    }
+                    t_ld += TC_CLOCK() - t_a;
+                    continue;
                 }
                 for (int t = 0; t < tiles; ++t) {
                     // destination of this 64x64 tile: first element, valid rows and columns
@@ -543,6 +615,8 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             pre = pre_next;
             cur.advance();
         }
+        // the staging tiles must have been read before the CTA gives its shared memory back
+        if (is_sdd && lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         if (lane == 0 && quad == 0 && group == 0) {
             TC_TIME_OUT(6, TC_CLOCK() - t_begin); TC_TIME_OUT(7, t_accf); TC_TIME_OUT(8, t_ld); TC_TIME_OUT(10, t_write);
         }
@@ -584,7 +658,7 @@ int matmul_tc(const MatmulArgs& g) {
     // host-side update).  Doing it first also binds the device's primary context to the calling
     // thread: cuTensorMapEncodeTiled below is a driver call and fails with "invalid context" on a
     // thread (e.g. an autograd worker) that has not made a runtime call needing the context yet.
-    using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const TcParams);
+    using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const TcParams);
     const bool bf16 = g.dtype == BSA_DTYPE_BF16;
     KernelFn kernel;
     if (g.mode == BSA_MODE_SDD)      kernel = bf16 ? tc_matmul_kernel<BSA_MODE_SDD, true> : tc_matmul_kernel<BSA_MODE_SDD, false>;
@@ -598,13 +672,14 @@ int matmul_tc(const MatmulArgs& g) {
         int dev = 0;   // cudaSetDevice on the current device binds its primary context to this thread
         if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) { cudaGetLastError(); return BSA_ERR_LAUNCH; }
     }
-    CUtensorMap map_a, map_b;
+    CUtensorMap map_a, map_b, map_c;
     const int64_t sparse_rows = g.nnz * kTile;
     bool ok = true;
     // stored shapes: a dense operand is [rows, cols] = op^-1 of its logical shape
     if (g.mode == BSA_MODE_SDD) {
         ok &= make_map(&map_a, g.dtype, g.a, g.batches, g.trans_a ? g.size_k : g.size_m, g.trans_a ? g.size_m : g.size_k);
         ok &= make_map(&map_b, g.dtype, g.b, g.batches, g.trans_b ? g.size_n : g.size_k, g.trans_b ? g.size_k : g.size_n);
+        ok &= make_map(&map_c, g.dtype, g.c, g.batches, sparse_rows, kTile, 16);   // output leaves by TMA, 16 rows a time
     } else if (g.mode == BSA_MODE_DSD) {
         ok &= make_map(&map_a, g.dtype, g.a, g.batches, sparse_rows, kTile);
         ok &= make_map(&map_b, g.dtype, g.b, g.batches, g.trans_b ? g.size_n : g.size_k, g.trans_b ? g.size_k : g.size_n);
@@ -613,6 +688,7 @@ int matmul_tc(const MatmulArgs& g) {
         ok &= make_map(&map_b, g.dtype, g.b, g.batches, sparse_rows, kTile);
     }
     if (!ok) return BSA_ERR_DRIVER;
+    if (g.mode != BSA_MODE_SDD) map_c = map_a;      // unused by dsd / dds
 
     TcParams p{};
     p.blocks = g.blocks; p.table = g.table; p.status = g.workspace;
@@ -651,7 +727,7 @@ int matmul_tc(const MatmulArgs& g) {
     const int per_z = p.groups * p.chunks;
     p.stride_z = (int)grid / per_z;
     p.stride_rem = (int)grid % per_z;
-    kernel<<<grid, kThreads, kSmemBytes, g.stream>>>(map_a, map_b, p);
+    kernel<<<grid, kThreads, kSmemBytes, g.stream>>>(map_a, map_b, map_c, p);
     return launch_status();
 }
 

@@ -290,12 +290,13 @@ EncodeTiledFn encode_fn() {
 
 // 3-D tensor map over a row-major [batches, rows, cols] 16-bit tensor with a 64x64x1 box and the
 // 128-byte swizzle.  Out-of-range parts of a box read as zero and are not written.
-bool make_map(CUtensorMap* map, int dtype, const void* base, int64_t batches, int64_t rows, int64_t cols) {
+bool make_map(CUtensorMap* map, int dtype, const void* base, int64_t batches, int64_t rows, int64_t cols,
+              int box_rows = kTile) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     const cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batches};
     const cuuint64_t strides[2] = {(cuuint64_t)cols * 2, (cuuint64_t)rows * (cuuint64_t)cols * 2};
-    const cuuint32_t box[3] = {kTile, kTile, 1};
+    const cuuint32_t box[3] = {kTile, (cuuint32_t)box_rows, 1};
     const cuuint32_t elem[3] = {1, 1, 1};
     const CUtensorMapDataType type = dtype == BSA_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                              : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;

@@ -12,10 +12,10 @@
 // major-ness (so trans_a / trans_b only flip descriptor bits and swap two TMA
 // coordinates).  A persistent CTA per SM walks work items; an item is one
 // group of the layout (a block row or block column) of one batch entry:
-//   sdd  item = block row r.  Its blocks are taken four at a time; such a
-//        quad is one accumulation: A = rows r of op(A), B0..B3 = rows c0..c3 of
-//        op(B)^T placed back to back in shared memory (one N = 256 operand),
-//        K-steps over the dense inner size.  Output: the quad's four blocks.
+//   sdd  item = block row r.  Its blocks are taken two at a time; such a
+//        pair is one accumulation: A = rows r of op(A), B0, B1 = rows c0, c1 of
+//        op(B)^T placed back to back in shared memory (one N = 128 operand),
+//        K-steps over the dense inner size.  Output: the pair's two blocks.
 //   dsd  item = group m (and a 128-wide slice of N).  One accumulation over
 //        the group's blocks: A = the sparse block, B0|B1 = the k-block rows of
 //        op(B).  Output: C[m*64.., slice].
@@ -27,18 +27,23 @@
 // 8 KB boxes need about four issuing threads to saturate the L2 -> SM path.
 // Hence the warp roles (16 warps):
 //   warps 0-3   TMA producers; K-step n of the CTA belongs to producer n % 4,
-//               which loads all of its tiles (lane 0 issues).
-//   warps 4-7   tcgen05.mma issuers (lane 0).  sdd: issuer b owns accumulator
-//               buffer b and issues every second quad (N up to 256, no sharing).
-//               dsd / dds: the K = 64 of a stage is split over 4 (N = 64) or 2
+//               which loads all of its tiles.
+//   warps 4-7   tcgen05.mma issuers.  sdd: two issuers alternate accumulations
+//               over four accumulator buffers of 128 TMEM columns.
+//               dsd / dds: the K-steps are dealt out to 4 (N = 64) or 2
 //               (N = 128) issuers, each with a private partial accumulator, so
 //               no ordering between issuers is needed; the epilogue adds them.
-//   warps 8-15  two epilogue warpgroups; group b drains accumulator buffer b:
-//               tcgen05.ld, (sum of partials), convert, and 256-bit global
-//               stores straight from registers: every lane owns a whole 128-byte
-//               output row, so no shared-memory staging or block-level
-//               synchronisation is needed and the warps run independently.
-// Shared-memory stages and the two TMEM accumulator buffers are handed over
+//               (Producers and issuers run their loops warp-uniformly and elect
+//               a lane only around the TMA / tcgen05 instructions: issuing from
+//               a diverged lane costs about twice as much per instruction.)
+//   warps 8-15  two epilogue warpgroups taking alternate accumulations.
+//               dsd / dds: tcgen05.ld, sum of partials, convert, 256-bit global
+//               stores straight from registers (every lane owns a whole 128-byte
+//               output row).  sdd: tcgen05.ld in the 16x256b shape, convert,
+//               stmatrix into the warp's own 128-byte-swizzled 2 KB slab, one
+//               asynchronous 16-row TMA tensor store per warp and tile.
+//               No block-level synchronisation: the warps run independently.
+// Shared-memory stages and the TMEM accumulator buffers are handed over
 // with mbarriers.  Group offsets and block descriptors are prefetched one to
 // two items ahead so no role waits on a dependent global load per step.
 // Every mbarrier wait is bounded: on a time-out the CTA records
@@ -50,10 +55,12 @@ namespace bsa {
 namespace {
 
 constexpr int kMaxStages = 13;
-constexpr int kStageTiles = 27;                 // operand tiles in all stages: 13 x 2, 9 x 3 or 5 x 5
-constexpr int kSddStagingTile0 = 20;            // sdd: tiles 20 .. 23 hold the epilogue warps' output slabs (4 stages x 5 tiles come first)
-constexpr int kAccCols = 256;                   // TMEM columns per accumulator buffer
+constexpr int kStageTiles = 28;                 // 8 KB tiles of shared memory: stages of 2 or 3 tiles; sdd: 8 x 3 + 4 for output slabs
+constexpr int kSddStagingTile0 = 24;            // sdd: tiles 24 .. 27 hold the epilogue warps' output slabs (8 stages x 3 tiles come first)
+constexpr int kAccCols = 256;                   // TMEM columns per accumulator buffer (dsd / dds: 2 buffers)
 constexpr int kTmemCols = 2 * kAccCols;
+constexpr int kSddTiles = 2;                    // sdd: output tiles per accumulation; 4 buffers of 128 columns, so that
+                                                // the chain MMA issue -> MMA -> TMEM loads of one buffer is hidden by three others
 constexpr int kProducerWarps = 4;
 constexpr int kMmaWarps = 4;
 constexpr int kFirstMmaWarp = kProducerWarps;
@@ -73,8 +80,8 @@ constexpr int kThreads = (kFirstEpilogueWarp + 8) * 32;
 struct __align__(8) Barriers {
     uint64_t full[kMaxStages];
     uint64_t empty[kMaxStages];
-    uint64_t acc_full[2];
-    uint64_t acc_empty[2];
+    uint64_t acc_full[4];
+    uint64_t acc_empty[4];
     uint64_t drain;
     uint32_t tmem_base;
     int abort_flag;
@@ -106,7 +113,7 @@ struct TcParams {
 template <int MODE>
 __device__ __forceinline__ void item_shape(const TcParams& p, int count, int& flushes, int& ksteps) {
     if (MODE == BSA_MODE_SDD) {
-        flushes = (count + 3) >> 2;
+        flushes = (count + kSddTiles - 1) / kSddTiles;
         ksteps = (p.size_k + kTile - 1) / kTile;
     } else {
         flushes = 1;
@@ -117,37 +124,9 @@ __device__ __forceinline__ void item_shape(const TcParams& p, int count, int& fl
 // Number of B tiles (64 output columns each) of one accumulation; there is always one A tile.
 template <int MODE>
 __device__ __forceinline__ int b_tiles(const TcParams& p, int count, int chunk, int flush) {
-    if (MODE == BSA_MODE_SDD) return min(4, count - 4 * flush);
+    if (MODE == BSA_MODE_SDD) return min(kSddTiles, count - kSddTiles * flush);
     if (MODE == BSA_MODE_DSD) return min(2, (p.size_n - chunk * 2 * kTile + kTile - 1) / kTile);
     return 1;
-}
-
-// Full 64x64 tile of a sparse output: the warp converts its 16 accumulator rows with all 32
-// lanes (the 32x32b load shape would leave half of the lanes without data), transposes inside
-// quads so that every thread owns 16 contiguous bytes, and stores 64 bytes of 8 rows per
-// instruction.  thread_dst = element (row lane / 4, column 8 * (lane % 4)) of the warp's rows.
-__device__ __forceinline__ void store_tile_rows16(uint16_t* thread_dst, const uint32_t (&r)[32], int q, bool bf16_out) {
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {            // rows g and g + 8
-#pragma unroll
-        for (int blk = 0; blk < 2; ++blk) {           // columns 32 * blk .. 32 * blk + 31
-            uint32_t m[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const float lo = __uint_as_float(r[4 * (4 * blk + u) + 2 * half]);
-                const float hi = __uint_as_float(r[4 * (4 * blk + u) + 2 * half + 1]);
-                if (bf16_out) {
-                    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-                    m[u] = *reinterpret_cast<uint32_t*>(&h);
-                } else {
-                    __half2 h = __floats2half2_rn(lo, hi);
-                    m[u] = *reinterpret_cast<uint32_t*>(&h);
-                }
-            }
-            quad_transpose(m, q);                     // now words 4q .. 4q + 3 of this 32-column block
-            *reinterpret_cast<uint4*>(thread_dst + half * 8 * kTile + blk * 32) = make_uint4(m[0], m[1], m[2], m[3]);
-        }
-    }
 }
 
 // Converts NCOLS fp32 values of one output row to the 16-bit output type and stores the first
@@ -193,12 +172,15 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int stage_bytes = (1 + p.nb_max) * kTileBytes;
     constexpr bool is_sdd = MODE == BSA_MODE_SDD;
+    constexpr int kBufs = is_sdd ? 4 : 2;               // accumulator buffers in TMEM
+    constexpr int kBufShift = is_sdd ? 2 : 1;
+    constexpr int kBufCols = kTmemCols / kBufs;
     // sdd: one issuer per accumulation; dsd / dds: every issuer reports on every accumulation
     const uint32_t arrivals = is_sdd ? 1u : (uint32_t)p.issuers;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMaxStages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
-        for (int s = 0; s < 2; ++s) { mbar_init(&bars->acc_full[s], arrivals); mbar_init(&bars->acc_empty[s], 4); }
+        for (int s = 0; s < 4; ++s) { mbar_init(&bars->acc_full[s], arrivals); mbar_init(&bars->acc_empty[s], 4); }
         mbar_init(&bars->drain, (uint32_t)p.issuers);
         bars->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -254,7 +236,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         if (is_sdd) {
 #pragma unroll
                             for (int j = 0; j < 4; ++j)
-                                if (j < nb) cols[j] = win.get(p.blocks, cur.first, cur.count, 4 * f + j, lane).col();
+                                if (j < nb) cols[j] = win.get(p.blocks, cur.first, cur.count, kSddTiles * f + j, lane).col();
                         } else {
                             d = win.get(p.blocks, cur.first, cur.count, k, lane);
                         }
@@ -348,8 +330,8 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 item_shape<MODE>(p, cur.count, flushes, ksteps);
                 if (ksteps == 0) continue;          // empty group: the epilogue writes zeros on its own
                 for (int f = 0; ok && f < flushes; ++f, ++flush_no) {
-                    const int acc = flush_no & 1;
-                    if (is_sdd && p.issuers == 2 && acc != w) {
+                    const int acc = flush_no & (kBufs - 1);
+                    if (is_sdd && p.issuers == 2 && (flush_no & 1) != w) {
                         // the other issuer's accumulation: skip its stages (the host guarantees
                         // that a stage always belongs to the same issuer)
                         stage += ksteps;
@@ -359,11 +341,11 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     const int nb = b_tiles<MODE>(p, cur.count, cur.chunk, f);
                     const uint32_t idesc = p.idesc | ((uint32_t)((nb * kTile) >> 3) << 17);
                     { const long long t0 = TC_CLOCK();
-                      ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_empty[acc], ((uint32_t)(flush_no >> 1) & 1u) ^ 1u, &bars->abort_flag, p.status)) != 0;
+                      ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_empty[acc], ((uint32_t)(flush_no >> kBufShift) & 1u) ^ 1u, &bars->abort_flag, p.status)) != 0;
                       t_acc += TC_CLOCK() - t0; }
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t d = tmem_base + (uint32_t)(acc * kAccCols) + part_col;
+                    const uint32_t d = tmem_base + (uint32_t)(acc * kBufCols) + part_col;
                     bool issued = false;
                     const long long tk0 = TC_CLOCK();
                     // dsd / dds: K-step n belongs to issuer n % issuers (the stage count is a
@@ -451,12 +433,12 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 // accumulations alternate between the two buffers / groups; groups that write
                 // zeros for an empty group of blocks are chosen by item parity
                 const int owner = have_acc ? (flush_no & 1) : (cur.item_no & 1);
-                const uint32_t acc_phase = (uint32_t)(flush_no >> 1) & 1u;
+                const uint32_t acc_phase = (uint32_t)(flush_no >> kBufShift) & 1u;
+                const int acc = flush_no & (kBufs - 1);     // (dsd / dds: the group's own buffer)
                 const int step0 = step;             // sequence number of this accumulation's first K-step
                 step += ksteps;
                 if (have_acc) ++flush_no;
                 if (owner != group) continue;
-                const int acc = group;
                 const int tiles = b_tiles<MODE>(p, cur.count, cur.chunk, f);
                 if (have_acc) {
                     const long long t0 = TC_CLOCK();
@@ -475,14 +457,14 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     // the stores are asynchronous (two slabs per warp alternate).
                     // The tiles of an accumulation are ready together: the TMEM load of tile t + 1 is in
                     // flight while tile t is converted.
-                    const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * kAccCols);
+                    const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * kBufCols);
                     // lane -> row address of its 8x8 matrix: matrix i = lane / 8 holds rows (i & 1) * 8 ..
                     // of 16-byte column unit u = 2k + (i >> 1)
                     const int sm_row = ((lane >> 3) & 1) * 8 + (lane & 7);        // row inside the slab
                     const uint32_t sm_unit = (uint32_t)(lane >> 4);
                     const int slab0 = ((warp - kFirstEpilogueWarp) * 2) * (16 * 128);   // this warp's two slabs
                     auto store_tile = [&](const uint32_t (&r)[32], int t) {
-                        const int out_idx = win.get(p.blocks, cur.first, cur.count, 4 * f + t, lane).idx;
+                        const int out_idx = win.get(p.blocks, cur.first, cur.count, kSddTiles * f + t, lane).idx;
                         // a descriptor that does not belong to this layout is reported in the workspace
                         // (word 1 = offending tile index); the tensor map clips the store itself
                         const bool in_bounds = out_idx >= 0 && out_idx < p.nnz;
@@ -538,10 +520,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     // destination of this 64x64 tile: first element, valid rows and columns
                     size_t dst0;
                     int rows_valid = kTile, cols_valid = kTile;
-                    if (is_sdd) {
-                        const int out_idx = win.get(p.blocks, cur.first, cur.count, 4 * f + t, lane).idx;
-                        dst0 = ((size_t)cur.z * p.nnz + out_idx) * (kTile * kTile);
-                    } else if (MODE == BSA_MODE_DSD) {
+                    if (MODE == BSA_MODE_DSD) {
                         const int n0 = (cur.chunk * 2 + t) * kTile;
                         dst0 = ((size_t)cur.z * p.size_m + (size_t)cur.g * kTile) * p.size_n + n0;
                         cols_valid = min(kTile, p.size_n - n0);
@@ -560,18 +539,10 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     const bool writer = row_lane && row < rows_valid && in_bounds;
                     uint16_t* dst = p.c + dst0 + (size_t)row * p.ldc;
                     const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16)
-                                           + (uint32_t)(acc * kAccCols + t * kTile);
+                                           + (uint32_t)(acc * kBufCols + t * kTile);
                     const bool last_tile = have_acc && t == tiles - 1;
                     const long long t_a = TC_CLOCK();
-                    if (is_sdd && have_acc) {
-                        uint32_t r[32];
-                        tc_ld_16x256b_x8(taddr, r);
-                        tc_wait_ld();
-                        if (last_tile) release_accumulator(&bars->acc_empty[acc], lane);
-                        if (in_bounds)
-                            store_tile_rows16(p.c + dst0 + (size_t)(quad * 16 + (lane >> 2)) * kTile + (lane & 3) * 8, r,
-                                              lane & 3, bf16_out);
-                    } else if (!have_acc || parts == 1) {
+                    if (!have_acc || parts == 1) {
                         uint32_t v[kTile];          // fp32 bit patterns of this lane's row
                         if (have_acc) {
                             tc_ld_32x32b_x64(taddr, v);
@@ -697,14 +668,15 @@ int matmul_tc(const MatmulArgs& g) {
     p.mode = g.mode; p.trans_a = g.trans_a; p.trans_b = g.trans_b;
     p.chunks = (int)slices_of(g);
     p.items = (int)(g.batches * g.groups * p.chunks);
-    if (g.mode == BSA_MODE_SDD) { p.nb_max = 4; p.issuers = 2; }
+    if (g.mode == BSA_MODE_SDD) { p.nb_max = kSddTiles; p.issuers = 2; }
     else if (g.mode == BSA_MODE_DSD && g.size_n > kTile) { p.nb_max = 2; p.issuers = 2; }
     else { p.nb_max = 1; p.issuers = 4; }
     // Every mbarrier must be waited on by the same threads in every phase (a parity wait cannot
     // tell phases two apart), so the stage count is a multiple of the producer count, and for sdd,
     // where the two issuers alternate accumulations of `ksteps` stages, a multiple of 2 * ksteps;
     // otherwise one issuer does all accumulations.
-    p.stages = (kStageTiles / (1 + p.nb_max)) / kProducerWarps * kProducerWarps;
+    const int ring_tiles = g.mode == BSA_MODE_SDD ? kSddStagingTile0 : kStageTiles;
+    p.stages = (ring_tiles / (1 + p.nb_max)) / kProducerWarps * kProducerWarps;
     if (p.stages > kMaxStages) p.stages = kMaxStages / kProducerWarps * kProducerWarps;
     if (g.mode == BSA_MODE_SDD) {
         const int ksteps = (int)((g.size_k + kTile - 1) / kTile);

@@ -95,3 +95,56 @@ def test_full_size_properties_seq4096():
     assert torch.equal(sub, s1[5:7])
     from sparse.kernel import sparse_ops
     sparse_ops.check_device_status(0)
+
+
+def test_full_size_config5_more_than_2_pow_31_elements():
+    """BASELINE config 5 at full size: batch 16 x heads 32 = 512 slices, seq 8192, head dim 128, block 64,
+    BigBird layout with 1262 blocks: every sparse tensor has 2.65e9 elements (5.3 GB), beyond 32-bit
+    element indices.  Checked through size-independent properties: (1) the last slices of the full
+    launch equal the same slices computed alone (any index overflow would hit the high slices),
+    (2) softmax rows sum to one, (3) the whole backward chain of the last slice equals the chain
+    computed alone, (4) the fused forward agrees with the unfused one on the last slices."""
+    from sparse import SparseLayout, matmul, softmax
+    from sparse.attention import attention_lse
+    from sparse.kernel import sparse_ops
+    from sparse.patterns import bigbird
+    free, _ = torch.cuda.mem_get_info()
+    if free < 40 * 2 ** 30:
+        pytest.skip("needs about 30 GB of device memory")
+    layout = SparseLayout(bigbird(128, 1, 2, 3, 5000), block=64)
+    z, seq, d, scale = 512, 8192, 128, 128 ** -0.5
+    assert z * layout.num_blocks * 64 * 64 > 2 ** 31
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    q, k, v, do = (torch.randn(z, seq, d, device="cuda", generator=gen).half() for _ in range(4))
+    tail = slice(z - 3, z)
+
+    def chain(q, k, v, do):
+        s = matmul(q, k, "sdd", layout, False, True)
+        p = softmax(s, layout, scale)
+        del s
+        o = matmul(p, v, "dsd", layout, False, False)
+        dv = matmul(p, do, "dsd", layout, True, False)
+        dp = matmul(do, v, "sdd", layout, False, True)
+        ds = sparse_ops.sparse_softmax_backward(p, dp, layout.row_layout[0], layout.row_layout[1], scale,
+                                                layout.max_row_blocks)
+        del dp
+        dq = matmul(ds, k, "dsd", layout, False, False)
+        dk = matmul(ds, q, "dsd", layout, True, False)
+        return p, o, dv, ds, dq, dk
+
+    full = chain(q, k, v, do)
+    part = chain(q[tail].contiguous(), k[tail].contiguous(), v[tail].contiguous(), do[tail].contiguous())
+    names = ["p", "o", "dv", "ds", "dq", "dk"]
+    for name, a, b in zip(names, full, part):
+        assert torch.equal(a[tail], b), "%s of the last slices differs between the full and the 3-slice launch" % name
+    p_tail = full[0][tail]
+    ones = torch.ones(3, seq, d, device="cuda", dtype=torch.float16)
+    rowsum = matmul(p_tail.contiguous(), ones, "dsd", layout, False, False)
+    assert float((rowsum.float() - 1).abs().max()) < 1e-2
+    o_unfused_tail = full[1][tail].float()
+    del full, part
+    fused, lse = attention_lse(q, k, v, layout, scale)
+    err = float((fused[tail].float() - o_unfused_tail).abs().max() / o_unfused_tail.abs().max())
+    assert err <= 5e-3, err
+    assert bool(torch.isfinite(lse).all())
+    sparse_ops.check_device_status(0)

@@ -325,6 +325,10 @@ template <> struct Packed<float> {
     static __device__ __forceinline__ uint4 pack(const float (&v)[4]) {
         return make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
     }
+    static __device__ __forceinline__ uint4 scaled(const uint4& r, float f) {
+        return make_uint4(__float_as_uint(__uint_as_float(r.x) * f), __float_as_uint(__uint_as_float(r.y) * f),
+                          __float_as_uint(__uint_as_float(r.z) * f), __float_as_uint(__uint_as_float(r.w) * f));
+    }
     // max over the chunk of sign * x
     static __device__ __forceinline__ float signed_max(const uint4& r, bool negate) {
         const float m0 = negate ? fminf(fminf(__uint_as_float(r.x), __uint_as_float(r.y)), fminf(__uint_as_float(r.z), __uint_as_float(r.w)))
@@ -339,6 +343,17 @@ template <> struct Packed<__half> {
 #pragma unroll
         for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
         return r;
+    }
+    // Exponentials in [0, 1] times 1 / sum, multiplied as packed halves: the factor is rounded to
+    // 11 bits first (2^-11 relative, like the product), which keeps the conversion pipe free.
+    static __device__ __forceinline__ uint4 scaled(const uint4& r, float f) {
+        uint4 o;
+        const __half2* h = reinterpret_cast<const __half2*>(&r);
+        __half2* q = reinterpret_cast<__half2*>(&o);
+        const __half2 f2 = __float2half2_rn(f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) q[i] = __hmul2(h[i], f2);
+        return o;
     }
     static __device__ __forceinline__ float signed_max(const uint4& r, bool negate) {
         const __half2* h = reinterpret_cast<const __half2*>(&r);
@@ -355,6 +370,13 @@ template <> struct Packed<__nv_bfloat16> {
 #pragma unroll
         for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
         return r;
+    }
+    static __device__ __forceinline__ uint4 scaled(const uint4& r, float f) {
+        float v[8];
+        Vec<__nv_bfloat16>::unpack(r, v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] *= f;
+        return pack(v);
     }
     static __device__ __forceinline__ float signed_max(const uint4& r, bool negate) {
         const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
@@ -493,13 +515,8 @@ softmax_rows_kernel(const SoftmaxParams p) {
             // phase 3: normalise and store
 #pragma unroll
             for (int k = 0; k < CH; ++k) {
-                if (active && base[k] != 0xFFFFFFFFu) {
-                    float v[N];
-                    Vec<T>::unpack(x[k], v);
-#pragma unroll
-                    for (int e = 0; e < N; ++e) v[e] *= inv;
-                    *reinterpret_cast<uint4*>(out + base[k] + i * block) = Packed<T>::pack(v);
-                }
+                if (active && base[k] != 0xFFFFFFFFu)
+                    *reinterpret_cast<uint4*>(out + base[k] + i * block) = Packed<T>::scaled(x[k], inv);
             }
         }
     }

@@ -474,7 +474,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         }
                         const uint32_t slab = smem_u32(stage_base + kSddStagingTile0 * kTileBytes + slab0 + (tile_no & 1) * (16 * 128));
                         // the slab written now was sent two tiles ago: that store must have read it
-                        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                        if (elect_one()) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
                         __syncwarp();
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
@@ -492,11 +492,14 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         }
                         fence_async_shared();           // generic-proxy writes -> visible to the bulk store
                         __syncwarp();
-                        if (lane == 0 && in_bounds) {
-                            asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
-                                         ::"l"(&map_c), "r"(slab), "r"(0), "r"(out_idx * kTile + quad * 16), "r"(cur.z) : "memory");
+                        // (issued from an elected lane of warp-uniform code: the copy's operands stay in
+                        // uniform registers; the same lane every time, the bulk groups are per thread)
+                        if (elect_one()) {
+                            if (in_bounds)
+                                asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                                             ::"l"(&map_c), "r"(slab), "r"(0), "r"(out_idx * kTile + quad * 16), "r"(cur.z) : "memory");
+                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");   // (empty groups keep the count regular)
                         }
-                        if (lane == 0) asm volatile("cp.async.bulk.commit_group;" ::: "memory");   // (empty groups keep the count regular)
                         ++tile_no;
                     };
                     const long long t_a = TC_CLOCK();
@@ -587,7 +590,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             cur.advance();
         }
         // the staging tiles must have been read before the CTA gives its shared memory back
-        if (is_sdd && lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        if (is_sdd && elect_one()) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         if (lane == 0 && quad == 0 && group == 0) {
             TC_TIME_OUT(6, TC_CLOCK() - t_begin); TC_TIME_OUT(7, t_accf); TC_TIME_OUT(8, t_ld); TC_TIME_OUT(10, t_write);
         }

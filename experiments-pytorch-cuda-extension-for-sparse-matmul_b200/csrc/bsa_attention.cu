@@ -21,7 +21,7 @@
 // a 64 x 64 block needs 8 + 4 of them, so the issuing is spread over three warps.  A CTA has 8
 // warps and 256 TMEM columns; two CTAs share an SM and overlap each other's prologues and
 // epilogues:
-//   warp 0     TMA producer of Q (once per item) and of every block's K tiles (one copy per lane)
+//   warp 0     TMA producer of Q (once per item) and of every block's K tiles
 //   warp 1     Q K^T issuer: S is double buffered, so Q K^T of block j + 1 runs while the softmax
 //              warps work on block j; one commit per block signals both "S is ready" and "the K
 //              stage is free"
@@ -191,57 +191,52 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 // buffer last have retired.  With two buffers the next item's set is requested after
                 // this item's K tiles (before them the request would wait for the previous item's last
                 // Q K^T with nothing in flight behind it).
-                auto issue_q = [&](int q, int z, int g) -> bool {
+                auto issue_q = [&](int q, int z, int g) -> bool {        // called by the whole warp
                     const int qb = q & (p.qbufs - 1);
                     const uint32_t use = (uint32_t)(p.qbufs == 2 ? q >> 1 : q);
-                    if (!mbar_wait(&bars->q_empty[qb], (use & 1u) ^ 1u, abort_flag, p.status)) return false;
-                    mbar_expect_tx(&bars->q_full[qb], (uint32_t)set_bytes);
-                    for (int t = 0; t < p.dtiles; ++t)
-                        tma_load_3d(q_smem + qb * set_bytes + t * kTileBytes, &map_q, &bars->q_full[qb], t * kTile, g * kTile, z);
+                    if (!__all_sync(0xffffffffu, mbar_wait(&bars->q_empty[qb], (use & 1u) ^ 1u, abort_flag, p.status))) return false;
+                    if (elect_one()) {
+                        mbar_expect_tx(&bars->q_full[qb], (uint32_t)set_bytes);
+                        for (int t = 0; t < p.dtiles; ++t)
+                            tma_load_3d(q_smem + qb * set_bytes + t * kTileBytes, &map_q, &bars->q_full[qb], t * kTile, g * kTile, z);
+                    }
+                    __syncwarp();
                     return true;
                 };
-                if (lane == 0 && !is_v && !q_prefetched) {
+                if (!is_v && !q_prefetched) {
                     const long long tq = AT_CLOCK();
                     ok = issue_q(q_no, cur.z, cur.g);
-                    AT_ADD(0, AT_CLOCK() - tq);
+                    if (lane == 0) AT_ADD(0, AT_CLOCK() - tq);
                 }
                 ++q_no;
-                ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
                 DescWindow win;
                 win.begin(p.blocks, cur.first, cur.count, pre, lane);
                 for (int j = 0; ok && j < n; ++j) {
                     const int col = win.get(p.blocks, cur.first, cur.count, j, lane).col();
-                    // One copy per lane, all issued by the same instruction (issuing costs a thread ~300
-                    // cycles per instruction): lane t loads tile t of the block's K (V) tile set.
-                    const bool mine = lane < p.dtiles;
-                    const int t = lane;
+                    // The whole warp waits for the stage and computes the copies' operands
+                    // (warp-uniform code keeps them in uniform registers); an elected lane issues.
                     const int stage = is_v ? (kv_no & vring_mask) : (kv_no & ring_mask);
                     const uint32_t parity = ((uint32_t)(kv_no >> (is_v ? p.vring_shift : p.ring_shift)) & 1u) ^ 1u;
                     uint64_t* reuse = is_v ? &bars->pv_done[stage] : &bars->qk_done[stage];
                     uint64_t* full = is_v ? &bars->v_full[stage] : &bars->k_full[stage];
-                    uint8_t* dst = (is_v ? v_smem : k_smem) + stage * set_bytes + t * kTileBytes;
+                    uint8_t* dst = (is_v ? v_smem : k_smem) + stage * set_bytes;
                     const CUtensorMap* map = is_v ? &map_v : &map_k;
-                    bool lane_ok = true;
-                    if (mine) {
-                        const long long t0 = AT_CLOCK();
-                        lane_ok = mbar_wait(reuse, parity, abort_flag, p.status);
-                        if (lane == 0) AT_ADD(is_v ? 2 : 1, AT_CLOCK() - t0);
+                    const long long t0 = AT_CLOCK();
+                    ok = __all_sync(0xffffffffu, mbar_wait(reuse, parity, abort_flag, p.status)) != 0;
+                    if (lane == 0) AT_ADD(is_v ? 2 : 1, AT_CLOCK() - t0);
+                    if (ok && elect_one()) {
+                        mbar_expect_tx(full, (uint32_t)set_bytes);
+                        for (int t = 0; t < p.dtiles; ++t)
+                            tma_load_3d(dst + t * kTileBytes, map, full, t * kTile, col * kTile, cur.z);
                     }
-                    ok = __all_sync(0xffffffffu, lane_ok) != 0;
-                    if (ok && mine) {
-                        const long long t1 = AT_CLOCK();
-                        if (t == 0) mbar_expect_tx(full, (uint32_t)set_bytes);
-                        tma_load_3d(dst, map, full, t * kTile, col * kTile, cur.z);
-                        if (lane == 0 && !is_v) AT_ADD(3, AT_CLOCK() - t1);
-                    }
+                    __syncwarp();
                     ++kv_no;
                 }
                 q_prefetched = false;
-                if (ok && lane == 0 && !is_v && p.qbufs == 2 && cur.has_next() && cur.next_count() > 0) {
+                if (ok && !is_v && p.qbufs == 2 && cur.has_next() && cur.next_count() > 0) {
                     ok = issue_q(q_no, cur.z1, cur.r1);        // q_no already counts this item
                     q_prefetched = true;
                 }
-                ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
             }
             pre = pre_next;
             cur.advance();

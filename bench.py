@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the block-sparse attention hot path.
 
-Workload (BASELINE configuration "long-sequence strided pattern"): fp16, batch 4 x heads 16
+Workload (benchmark configuration "long-sequence strided pattern"): fp16, batch 4 x heads 16
 (Z = 64 slices per GPU), seq 4096, head_dim 64, block 64, layout = every 8th block diagonal
 plus a band of half-width 2 (762 of 4096 blocks, 18.6 %), non-causal, softmax scale 1/8.
 One step = forward SDD(Q.K^T) -> softmax -> DSD(P.V) and the backward the autograd layer

@@ -72,7 +72,9 @@ def named_patterns():
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path of a checkout of the reference project>")
+    ref_root = sys.argv[1]
     layout_mod, matmul_mod, calls = load_reference(ref_root)
     for name, pattern in named_patterns().items():
         lay = layout_mod.SparseLayout(pattern.long())

@@ -1,5 +1,5 @@
 """GPU parity of the whole block-sparse attention step (sdd -> softmax -> dsd, forward and
-backward through autograd) on the BASELINE configurations, against dense masked attention
+backward through autograd) on the benchmark configurations, against dense masked attention
 on the CPU, plus size-independent properties at the full benchmark size."""
 import numpy as np
 import pytest
@@ -98,7 +98,7 @@ def test_full_size_properties_seq4096():
 
 
 def test_full_size_config5_more_than_2_pow_31_elements():
-    """BASELINE config 5 at full size: batch 16 x heads 32 = 512 slices, seq 8192, head dim 128, block 64,
+    """benchmark configuration 5 at full size: batch 16 x heads 32 = 512 slices, seq 8192, head dim 128, block 64,
     BigBird layout with 1262 blocks: every sparse tensor has 2.65e9 elements (5.3 GB), beyond 32-bit
     element indices.  Checked through size-independent properties: (1) the last slices of the full
     launch equal the same slices computed alone (any index overflow would hit the high slices),

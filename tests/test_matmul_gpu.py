@@ -107,7 +107,7 @@ def test_block32_on_tensor_cores(mode, ta, tb, dtype):
 
 
 def test_config1_sdd_fp32_per_head_layouts():
-    """BASELINE config 1: batch 1, heads 2, seq 256, head_dim 64, block 32, Bernoulli(0.5) + diagonal
+    """benchmark configuration 1: batch 1, heads 2, seq 256, head_dim 64, block 32, Bernoulli(0.5) + diagonal
     per head, Q.K^T as sdd(N,T) in fp32."""
     for head in range(2):
         g = load_golden_layout("cfg1_head%d" % head)
@@ -122,7 +122,7 @@ def test_config1_sdd_fp32_per_head_layouts():
 
 @pytest.mark.parametrize("mode,ta,tb", VARIANTS)
 def test_config4_fp32_stress_slice(mode, ta, tb):
-    """BASELINE config 4 on one head: seq 2048, head_dim 128, block 32, Bernoulli(0.1) + diagonal,
+    """benchmark configuration 4 on one head: seq 2048, head_dim 128, block 32, Bernoulli(0.1) + diagonal,
     inputs U(-1, 1), all modes and transpositions, fp32 tolerance 1e-4."""
     g = load_golden_layout("cfg4_head0")
     run_case(mode, ta, tb, g["pattern"], 32, 128, torch.float32, "auto", batch=(1,), seed=4000, dist="uniform")

@@ -10,5 +10,7 @@ from .matmul import matmul, SparseMatMul
 from .softmax import softmax, SparseSoftmax
 from .attention import attention, SparseAttention
 from .module import BlockSparseSelfAttention
+from .batched import BatchedSparseLayout, batched_matmul, batched_softmax, batched_attention
 
-__all__ = ["SparseLayout", "matmul", "SparseMatMul", "softmax", "SparseSoftmax", "attention", "SparseAttention", "BlockSparseSelfAttention"]
+__all__ = ["SparseLayout", "matmul", "SparseMatMul", "softmax", "SparseSoftmax", "attention", "SparseAttention", "BlockSparseSelfAttention",
+           "BatchedSparseLayout", "batched_matmul", "batched_softmax", "batched_attention"]

@@ -17,19 +17,28 @@
 // of similar size it happens in a row's first blocks only).  The result does not depend on when m
 // is raised: O and l carry the same factor.
 //
-// One thread can issue a tcgen05.mma or commit only every ~150 cycles whatever the MMA's size, and
-// a 64 x 64 block needs 8 + 4 of them, so the issuing is spread over three warps.  A CTA has 8
-// warps and 256 TMEM columns; two CTAs share an SM and overlap each other's prologues and
-// epilogues:
-//   warp 0     TMA producer of Q (once per item) and of every block's K tiles
+// A thread issues a tcgen05.mma, a commit or a TMA copy only every ~100 cycles whatever its size
+// (twice that from a diverged lane: the role loops run warp-uniformly and elect a lane only around
+// the instructions), so producing and issuing are spread over four warps.  A CTA has 256 TMEM
+// columns; two CTAs share an SM and overlap each other's prologues and epilogues:
+//   warp 0     TMA producer of Q (double buffered with head dim 64: the next item's tile set is
+//              requested an item ahead) and of every block's K tiles
 //   warp 1     Q K^T issuer: S is double buffered, so Q K^T of block j + 1 runs while the softmax
 //              warps work on block j; one commit per block signals both "S is ready" and "the K
 //              stage is free"
-//   warp 2     TMA producer of the V tiles
+//   warp 2     TMA producer of the V tiles (a K stage is free long before the block's P V: one
+//              in-order producer would stretch every loop by a TMA latency)
 //   warp 3     P V issuer; one commit per block signals "the P buffer and the V stage are free"
-//   warps 4-7  softmax: tcgen05.ld with the 16x256b shape (every lane owns 2 rows x 16 columns
-//              of a 64 x 64 block), masks, max / exp / sum, pack, 4x4 quad transposes, swizzled
-//              128-bit shared-memory stores of P; at the end the same for O to global memory.
+//   warps 4-   softmax warpgroups: tcgen05.ld with the 16x256b shape (every lane owns 2 rows x 16
+//              columns of a 64 x 64 block), masks, max / exp / sum, pack, 32-bit stores into the
+//              128-byte-swizzled P tile (32 lanes on 32 banks); at the end of a row O goes through
+//              4x4 quad transposes and 128-bit stores to global memory.
+//              Head dim 64: two warpgroups (12 warps) take alternate blocks, each with its own
+//              running maxima, sums and O accumulator; the group that owns a row's last block
+//              merges the two (the partial softmaxes over disjoint key sets combine exactly) and
+//              writes the row while the other one starts the next row.
+//              Head dim 128 (one accumulator fits): one warpgroup (8 warps) with two register
+//              buffers, the TMEM load of block j + 1 in flight while block j is worked on.
 // All waits are bounded (BSA_ERR_DEVICE_TIMEOUT in the workspace word).
 #include "bsa_tc_common.cuh"
 

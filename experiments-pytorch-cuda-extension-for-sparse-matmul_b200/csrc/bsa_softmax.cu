@@ -109,10 +109,17 @@ struct SoftmaxParams {
 // used; every thread of the CTA must call this the same number of times.
 template <bool kIsMax>
 __device__ __forceinline__ float team_reduce(float v, int L, float* exchange) {
-    const int lim = L < 32 ? L : 32;
-    for (int d = lim >> 1; d > 0; d >>= 1) {
-        const float o = __shfl_xor_sync(0xffffffffu, v, d);
-        v = kIsMax ? fmaxf(v, o) : v + o;
+    if (L >= 32) {                                // uniform per CTA: the whole warp, unrolled
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {
+            const float o = __shfl_xor_sync(0xffffffffu, v, d);
+            v = kIsMax ? fmaxf(v, o) : v + o;
+        }
+    } else {
+        for (int d = L >> 1; d > 0; d >>= 1) {
+            const float o = __shfl_xor_sync(0xffffffffu, v, d);
+            v = kIsMax ? fmaxf(v, o) : v + o;
+        }
     }
     if (L > 32) {
         const int warp = threadIdx.x >> 5;
@@ -130,6 +137,13 @@ __device__ __forceinline__ float team_reduce(float v, int L, float* exchange) {
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// 1 / x by the special-function unit (1 ulp).
+__device__ __forceinline__ float fast_rcp(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
 
@@ -387,11 +401,58 @@ template <> struct Packed<__nv_bfloat16> {
     }
 };
 
-template <typename T, int CH, bool kBackward>
-__global__ void __launch_bounds__(kThreads, kBackward ? 4 : 5)
+// team_reduce for R independent values at once: the shuffles of the R butterflies interleave and
+// teams wider than a warp pay one barrier for all of them.  `exchange` holds R * kWarps floats.
+template <bool kIsMax, int R>
+__device__ __forceinline__ void team_reduce_n(float (&v)[R], int L, float* exchange) {
+    if (L >= 32) {
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {
+#pragma unroll
+            for (int u = 0; u < R; ++u) {
+                const float o = __shfl_xor_sync(0xffffffffu, v[u], d);
+                v[u] = kIsMax ? fmaxf(v[u], o) : v[u] + o;
+            }
+        }
+    } else {
+        for (int d = L >> 1; d > 0; d >>= 1) {
+#pragma unroll
+            for (int u = 0; u < R; ++u) {
+                const float o = __shfl_xor_sync(0xffffffffu, v[u], d);
+                v[u] = kIsMax ? fmaxf(v[u], o) : v[u] + o;
+            }
+        }
+    }
+    if (L > 32) {
+        const int warp = threadIdx.x >> 5;
+        if ((threadIdx.x & 31) == 0) {
+#pragma unroll
+            for (int u = 0; u < R; ++u) exchange[u * kWarps + warp] = v[u];
+        }
+        __syncthreads();
+        const int wpt = L >> 5;
+        const int first = (warp / wpt) * wpt;
+#pragma unroll
+        for (int u = 0; u < R; ++u) {
+            float r = exchange[u * kWarps + first];
+            for (int w = 1; w < wpt; ++w)
+                r = kIsMax ? fmaxf(r, exchange[u * kWarps + first + w]) : r + exchange[u * kWarps + first + w];
+            v[u] = r;
+        }
+    }
+}
+
+// Rows a team works on per pass.  A lane keeps RPT * CH chunks in flight; with fewer than about
+// four 16-byte loads per lane outstanding, 32-40 resident warps do not cover the HBM latency.
+constexpr int rows_per_team(int ch, bool backward, bool masked) {
+    return backward ? (ch <= 2 ? 2 : 1) : (ch == 1 ? 4 : ch == 2 ? 2 : (ch == 3 && !masked) ? 2 : 1);
+}
+
+template <typename T, int CH, int RPT, bool kBackward, bool kMasked>
+__global__ void __launch_bounds__(kThreads, CH == 8 ? ((kBackward || kMasked) ? 2 : 3) : (kBackward ? 4 : 5))
 softmax_rows_kernel(const SoftmaxParams p) {
     constexpr int N = Vec<T>::N;
-    __shared__ float s_red0[kWarps], s_red1[kWarps];
+    __shared__ float s_red0[RPT * kWarps], s_red1[RPT * kWarps];
 
     const int block = p.block;
     const int cps = block / N;                    // chunks per segment (a power of two)
@@ -410,17 +471,17 @@ softmax_rows_kernel(const SoftmaxParams p) {
     const int rows_per_pass = kThreads / L;
 
     uint32_t base[CH];                            // element offset of the lane's chunk in row 0, or ~0
-    int kpos[CH];                                 // key position of the chunk's first element
+    int kpos[kMasked ? CH : 1];                   // key position of the chunk's first element
 #pragma unroll
     for (int k = 0; k < CH; ++k) {
         const int q = t + k * L;
         base[k] = 0xFFFFFFFFu;
-        kpos[k] = 0;
+        if (kMasked) kpos[k] = 0;
         if (q < n_chunks) {
             const int j = q >> cps_shift, s = q & (cps - 1);
             const BlockDesc d = p.row_blocks[first + j];
             base[k] = (uint32_t)d.idx * (uint32_t)(block * block) + (uint32_t)(s * N);
-            kpos[k] = d.col() * block + s * N;
+            if (kMasked) kpos[k] = d.col() * block + s * N;
         }
     }
 
@@ -428,95 +489,124 @@ softmax_rows_kernel(const SoftmaxParams p) {
     const T* in0 = static_cast<const T*>(p.in0) + zoff;
     const T* in1 = kBackward ? static_cast<const T*>(p.in1) + zoff : nullptr;
     T* out = static_cast<T*>(p.out) + zoff;
-    const uint8_t* kpm_row = (!kBackward && p.kpm) ? p.kpm + (z / p.batches_per_kpm) * p.kpm_stride : nullptr;
+    const uint8_t* kpm_row = (kMasked && p.kpm) ? p.kpm + (z / p.batches_per_kpm) * p.kpm_stride : nullptr;
     const float scale_log2e = p.scale * kLog2e;
-    const bool causal = !kBackward && p.causal != 0;
-    const bool masked = causal || kpm_row != nullptr;
+    const bool causal = kMasked && p.causal != 0;
     const bool negate = scale_log2e < 0.f;
 
-    for (int i0 = 0; i0 < block; i0 += rows_per_pass) {
-        const int i = i0 + team;
-        const bool active = i < block;
-        uint4 x[CH], g[kBackward ? CH : 1];
+    for (int i0 = team; i0 < block; i0 += rows_per_pass * RPT) {
+        // row u of this pass is i0 + u * rows_per_pass; rows past the block (short rows, where one
+        // pass covers the block) are switched off
+        uint4 x[RPT][CH], g[kBackward ? RPT : 1][kBackward ? CH : 1];
+        bool on[RPT][CH];
 #pragma unroll
-        for (int k = 0; k < CH; ++k) {
-            if (active && base[k] != 0xFFFFFFFFu) {
-                x[k] = *reinterpret_cast<const uint4*>(in0 + base[k] + i * block);
-                if (kBackward) g[k] = *reinterpret_cast<const uint4*>(in1 + base[k] + i * block);
+        for (int u = 0; u < RPT; ++u) {
+            const int i = i0 + u * rows_per_pass;
+#pragma unroll
+            for (int k = 0; k < CH; ++k) {
+                on[u][k] = base[k] != 0xFFFFFFFFu && (u == 0 || i < block);
+                if (on[u][k]) {
+                    x[u][k] = *reinterpret_cast<const uint4*>(in0 + base[k] + i * block);
+                    if (kBackward) g[u][k] = *reinterpret_cast<const uint4*>(in1 + base[k] + i * block);
+                }
             }
         }
         if (kBackward) {
-            float acc = 0.f;
+            float dot[RPT];
 #pragma unroll
-            for (int k = 0; k < CH; ++k) {
-                if (active && base[k] != 0xFFFFFFFFu) {
-                    float v[N], w[N];
-                    Vec<T>::unpack(x[k], v);
-                    Vec<T>::unpack(g[k], w);
+            for (int u = 0; u < RPT; ++u) {
+                dot[u] = 0.f;
 #pragma unroll
-                    for (int e = 0; e < N; ++e) acc = fmaf(v[e], w[e], acc);
+                for (int k = 0; k < CH; ++k) {
+                    if (on[u][k]) {
+                        float v[N], w[N];
+                        Vec<T>::unpack(x[u][k], v);
+                        Vec<T>::unpack(g[u][k], w);
+#pragma unroll
+                        for (int e = 0; e < N; ++e) dot[u] = fmaf(v[e], w[e], dot[u]);
+                    }
                 }
             }
-            const float dot = team_reduce<false>(acc, L, s_red0);
+            team_reduce_n<false, RPT>(dot, L, s_red0);
 #pragma unroll
-            for (int k = 0; k < CH; ++k) {
-                if (active && base[k] != 0xFFFFFFFFu) {
-                    float v[N], w[N];
-                    Vec<T>::unpack(x[k], v);
-                    Vec<T>::unpack(g[k], w);
+            for (int u = 0; u < RPT; ++u) {
+                const int i = i0 + u * rows_per_pass;
 #pragma unroll
-                    for (int e = 0; e < N; ++e) v[e] = (p.scale * v[e]) * (w[e] - dot);
-                    *reinterpret_cast<uint4*>(out + base[k] + i * block) = Packed<T>::pack(v);
+                for (int k = 0; k < CH; ++k) {
+                    if (on[u][k]) {
+                        float v[N], w[N];
+                        Vec<T>::unpack(x[u][k], v);
+                        Vec<T>::unpack(g[u][k], w);
+#pragma unroll
+                        for (int e = 0; e < N; ++e) v[e] = (p.scale * v[e]) * (w[e] - dot[u]);
+                        *reinterpret_cast<uint4*>(out + base[k] + i * block) = Packed<T>::pack(v);
+                    }
                 }
             }
-            if (L > 32) __syncthreads();
+            if (L > 32) __syncthreads();          // s_red0 is rewritten by the next pass
         } else {
-            // phase 1: row maximum of scale*log2e*x (masked elements are -inf)
-            float acc = -CUDART_INF_F;
+            // phase 1: row maximum of scale*log2e*x (masked elements are -inf).  (Sorting chunks into
+            // clean / partly masked / fully masked ones to spare the clean ones the element-wise
+            // masks was measured slower: the classes diverge inside a warp.)
+            float mx[RPT];
 #pragma unroll
-            for (int k = 0; k < CH; ++k) {
-                if (active && base[k] != 0xFFFFFFFFu) {
-                    if (masked) {
-                        float v[N];
-                        Vec<T>::unpack(x[k], v);
-                        scale_and_mask<N>(v, scale_log2e, r * block + i, kpos[k], causal, kpm_row);
+            for (int u = 0; u < RPT; ++u) {
+                const int i = i0 + u * rows_per_pass;
+                mx[u] = -CUDART_INF_F;
 #pragma unroll
-                        for (int e = 0; e < N; ++e) acc = fmaxf(acc, v[e]);
-                    } else {
-                        acc = fmaxf(acc, Packed<T>::signed_max(x[k], negate));
+                for (int k = 0; k < CH; ++k) {
+                    if (on[u][k]) {
+                        if (kMasked) {
+                            float v[N];
+                            Vec<T>::unpack(x[u][k], v);
+                            scale_and_mask<N>(v, scale_log2e, r * block + i, kpos[kMasked ? k : 0], causal, kpm_row);
+#pragma unroll
+                            for (int e = 0; e < N; ++e) mx[u] = fmaxf(mx[u], v[e]);
+                        } else {
+                            mx[u] = fmaxf(mx[u], Packed<T>::signed_max(x[u][k], negate));
+                        }
                     }
                 }
             }
-            float mx = team_reduce<true>(acc, L, s_red0);
-            if (mx == -CUDART_INF_F) mx = 0.f;
-            if (!masked) mx *= fabsf(scale_log2e);       // max of sign*x -> max of scale*log2e*x
+            team_reduce_n<true, RPT>(mx, L, s_red0);
             // phase 2: exponentials (kept packed) and their sum
-            float sum = 0.f;
+            float sum[RPT];
 #pragma unroll
-            for (int k = 0; k < CH; ++k) {
-                if (active && base[k] != 0xFFFFFFFFu) {
-                    float v[N];
-                    Vec<T>::unpack(x[k], v);
-                    if (masked) {
-                        scale_and_mask<N>(v, scale_log2e, r * block + i, kpos[k], causal, kpm_row);
+            for (int u = 0; u < RPT; ++u) {
+                const int i = i0 + u * rows_per_pass;
+                if (mx[u] == -CUDART_INF_F) mx[u] = 0.f;
+                if (!kMasked) mx[u] *= fabsf(scale_log2e);   // max of sign*x -> max of scale*log2e*x
+                sum[u] = 0.f;
 #pragma unroll
-                        for (int e = 0; e < N; ++e) v[e] = fast_exp2(v[e] - mx);
-                    } else {
+                for (int k = 0; k < CH; ++k) {
+                    if (on[u][k]) {
+                        float v[N];
+                        Vec<T>::unpack(x[u][k], v);
+                        if (kMasked) {
+                            scale_and_mask<N>(v, scale_log2e, r * block + i, kpos[kMasked ? k : 0], causal, kpm_row);
 #pragma unroll
-                        for (int e = 0; e < N; ++e) v[e] = fast_exp2(fmaf(v[e], scale_log2e, -mx));
+                            for (int e = 0; e < N; ++e) v[e] = fast_exp2(v[e] - mx[u]);
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < N; ++e) v[e] = fast_exp2(fmaf(v[e], scale_log2e, -mx[u]));
+                        }
+#pragma unroll
+                        for (int e = 0; e < N; ++e) sum[u] += v[e];
+                        x[u][k] = Packed<T>::pack(v);
                     }
-#pragma unroll
-                    for (int e = 0; e < N; ++e) sum += v[e];
-                    x[k] = Packed<T>::pack(v);
                 }
             }
-            sum = team_reduce<false>(sum, L, s_red1);
-            const float inv = sum > 0.f ? 1.f / sum : 0.f;
+            team_reduce_n<false, RPT>(sum, L, s_red1);
             // phase 3: normalise and store
 #pragma unroll
-            for (int k = 0; k < CH; ++k) {
-                if (active && base[k] != 0xFFFFFFFFu)
-                    *reinterpret_cast<uint4*>(out + base[k] + i * block) = Packed<T>::scaled(x[k], inv);
+            for (int u = 0; u < RPT; ++u) {
+                const int i = i0 + u * rows_per_pass;
+                const float inv = sum[u] > 0.f ? fast_rcp(sum[u]) : 0.f;
+#pragma unroll
+                for (int k = 0; k < CH; ++k) {
+                    if (on[u][k])
+                        *reinterpret_cast<uint4*>(out + base[k] + i * block) = Packed<T>::scaled(x[u][k], inv);
+                }
             }
         }
     }
@@ -545,13 +635,22 @@ int launch_typed(const SoftmaxParams& base, int64_t batches, int64_t max_row_blo
     int64_t need = (avg_chunks + 31) / 32;
     if (max_row_blocks > 0) need = std::max<int64_t>(need, (max_row_blocks * cps + kThreads - 1) / kThreads);
     int ch = need <= 1 ? 1 : need <= 2 ? 2 : need <= 3 ? 3 : need <= 4 ? 4 : 8;
+    const bool masked = !kBackward && (p.causal != 0 || p.kpm != nullptr);
+#define BSA_SOFTMAX_ROWS(CH_)                                                                        \
+    if (masked)                                                                                      \
+        softmax_rows_kernel<T, CH_, rows_per_team(CH_, kBackward, true), kBackward, !kBackward>      \
+            <<<grid, kThreads, 0, stream>>>(p);                                                      \
+    else                                                                                             \
+        softmax_rows_kernel<T, CH_, rows_per_team(CH_, kBackward, false), kBackward, false>          \
+            <<<grid, kThreads, 0, stream>>>(p)
     switch (ch) {
-        case 1: softmax_rows_kernel<T, 1, kBackward><<<grid, kThreads, 0, stream>>>(p); break;
-        case 2: softmax_rows_kernel<T, 2, kBackward><<<grid, kThreads, 0, stream>>>(p); break;
-        case 3: softmax_rows_kernel<T, 3, kBackward><<<grid, kThreads, 0, stream>>>(p); break;
-        case 4: softmax_rows_kernel<T, 4, kBackward><<<grid, kThreads, 0, stream>>>(p); break;
-        default: softmax_rows_kernel<T, 8, kBackward><<<grid, kThreads, 0, stream>>>(p); break;
+        case 1: BSA_SOFTMAX_ROWS(1); break;
+        case 2: BSA_SOFTMAX_ROWS(2); break;
+        case 3: BSA_SOFTMAX_ROWS(3); break;
+        case 4: BSA_SOFTMAX_ROWS(4); break;
+        default: BSA_SOFTMAX_ROWS(8); break;
     }
+#undef BSA_SOFTMAX_ROWS
     int st = launch_status();
     if (st != BSA_OK) return st;
     // rows longer than the fast kernel holds (or of unknown length) go to the general kernel

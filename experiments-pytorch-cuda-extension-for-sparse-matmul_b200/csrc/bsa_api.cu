@@ -34,7 +34,7 @@ int convert(bool to_sparse, int dtype, const void* src, void* dst, const int32_t
             int64_t nnz, int64_t batches, int64_t rows, int64_t cols, int block, cudaStream_t stream) {
     if (!src || !dst || !row_blocks) return BSA_ERR_NULL_POINTER;
     if (dtype != BSA_DTYPE_F32 && dtype != BSA_DTYPE_F16 && dtype != BSA_DTYPE_BF16) return BSA_ERR_BAD_DTYPE;
-    if (block != 32 && block != 64 && block != 128) return BSA_ERR_BAD_BLOCK;
+    if (!valid_block(block)) return BSA_ERR_BAD_BLOCK;
     if (nnz < 0 || batches < 0 || rows <= 0 || cols <= 0) return BSA_ERR_BAD_SHAPE;
     if (batches > 65535 || nnz > (int64_t)INT32_MAX) return BSA_ERR_TOO_LARGE;
     if (!aligned16(src) || !aligned16(dst)) return BSA_ERR_ALIGNMENT;
@@ -65,7 +65,7 @@ extern "C" const char* bsa_status_string(int status) {
         case BSA_ERR_BAD_MODE: return "mode must be sdd (0), dsd (1) or dds (2)";
         case BSA_ERR_BAD_DTYPE: return "unsupported dtype";
         case BSA_ERR_BAD_SHAPE: return "bad shape: sizes must be positive and the sparse sides multiples of the block size";
-        case BSA_ERR_BAD_BLOCK: return "block size must be 32, 64 or 128";
+        case BSA_ERR_BAD_BLOCK: return "block size must be 16, 32, 64 or 128";
         case BSA_ERR_ALIGNMENT: return "device pointers must be 16-byte aligned";
         case BSA_ERR_WORKSPACE: return "workspace missing or smaller than BSA_WORKSPACE_BYTES";
         case BSA_ERR_LAUNCH: return "CUDA launch failed";
@@ -83,7 +83,7 @@ int check_matmul_args(int mode, int dtype, const void* a, const void* b, const v
                       int64_t size_m, int64_t size_n, int64_t size_k, int block, int engine) {
     if (mode != BSA_MODE_SDD && mode != BSA_MODE_DSD && mode != BSA_MODE_DDS) return BSA_ERR_BAD_MODE;
     if (dtype != BSA_DTYPE_F32 && dtype != BSA_DTYPE_F16 && dtype != BSA_DTYPE_BF16) return BSA_ERR_BAD_DTYPE;
-    if (block != 32 && block != 64 && block != 128) return BSA_ERR_BAD_BLOCK;
+    if (!bsa::valid_block(block)) return BSA_ERR_BAD_BLOCK;
     if (!a || !b || !c || !blocks || !table) return BSA_ERR_NULL_POINTER;
     if (nnz < 0 || groups <= 0 || batches < 0 || size_m <= 0 || size_n <= 0 || size_k <= 0) return BSA_ERR_BAD_SHAPE;
     if (nnz > (int64_t)INT32_MAX / 2 || groups > 65535 || batches > 65535) return BSA_ERR_TOO_LARGE;
@@ -113,7 +113,7 @@ extern "C" int bsa_matmul(int mode, int dtype, int trans_a, int trans_b,
     // same order of checks as before the split: mode, dtype, block, pointers, workspace, sizes
     if (mode != BSA_MODE_SDD && mode != BSA_MODE_DSD && mode != BSA_MODE_DDS) return BSA_ERR_BAD_MODE;
     if (dtype != BSA_DTYPE_F32 && dtype != BSA_DTYPE_F16 && dtype != BSA_DTYPE_BF16) return BSA_ERR_BAD_DTYPE;
-    if (block != 32 && block != 64 && block != 128) return BSA_ERR_BAD_BLOCK;
+    if (!valid_block(block)) return BSA_ERR_BAD_BLOCK;
     if (!a || !b || !c || !blocks || !table) return BSA_ERR_NULL_POINTER;
     if (!workspace || workspace_bytes < BSA_WORKSPACE_BYTES) return BSA_ERR_WORKSPACE;
     const int checked = check_matmul_args(mode, dtype, a, b, c, blocks, table, nnz, groups, batches,

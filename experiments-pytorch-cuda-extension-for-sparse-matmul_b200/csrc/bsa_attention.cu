@@ -777,7 +777,7 @@ extern "C" int bsa_attention_forward(int dtype, const void* q, const void* k, co
                                      void* workspace, size_t workspace_bytes, void* stream) {
     using namespace bsa;
     if (dtype != BSA_DTYPE_F32 && dtype != BSA_DTYPE_F16 && dtype != BSA_DTYPE_BF16) return BSA_ERR_BAD_DTYPE;
-    if (block != 32 && block != 64 && block != 128) return BSA_ERR_BAD_BLOCK;
+    if (!valid_block(block)) return BSA_ERR_BAD_BLOCK;
     if (!q || !k || !v || !o || !row_blocks || !row_table) return BSA_ERR_NULL_POINTER;
     if (!workspace || workspace_bytes < BSA_WORKSPACE_BYTES) return BSA_ERR_WORKSPACE;
     if (nnz < 0 || block_rows <= 0 || block_cols <= 0 || batches < 0 || head_dim <= 0) return BSA_ERR_BAD_SHAPE;

@@ -41,6 +41,7 @@ template <> struct Scalar<__nv_bfloat16> {
 };
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline bool valid_block(int block) { return block == 16 || block == 32 || block == 64 || block == 128; }
 
 // Turns the sticky/last CUDA error after a launch into a status code.
 inline int launch_status() {

@@ -16,6 +16,8 @@
 // sub-products staged through padded shared memory; operand sub-tiles are
 // described by a base pointer and two strides, so transposition is a choice
 // of strides.  All offsets are 64-bit.
+#include <algorithm>
+
 #include "bsa_common.cuh"
 
 namespace bsa {
@@ -106,15 +108,17 @@ __global__ void __launch_bounds__(kThreads) sdd_kernel(const Params p) {
                 c[(size_t)(si * kTile + r + u) * B + sj * kTile + cc + v] = Scalar<T>::from_float(acc[u][v]);
 }
 
-// DSD and DDS: grid (batches, ceil(M/32), ceil(N/32)); the CTA walks the
-// blocks of the group its output tile belongs to.
+// DSD and DDS: grid (batches, tiles along M, tiles along N); the CTA walks the
+// blocks of the group its output tile belongs to.  Along the sparse operand's
+// grouped axis a tile is min(32, block) wide, so that it never spans two groups.
 template <typename T, bool kSparseA>
 __global__ void __launch_bounds__(kThreads) walk_kernel(const Params p) {
     __shared__ float sa[kTile][kTile + 1], sb[kTile][kTile + 1];
     const int B = p.block, KS = (B + kTile - 1) / kTile;
     const int64_t z = blockIdx.x;
-    const int64_t m0 = (int64_t)blockIdx.y * kTile, n0 = (int64_t)blockIdx.z * kTile;
-    const int lim_i = (int)min((int64_t)kTile, p.size_m - m0), lim_j = (int)min((int64_t)kTile, p.size_n - n0);
+    const int step_m = kSparseA ? min(kTile, B) : kTile, step_n = kSparseA ? kTile : min(kTile, B);
+    const int64_t m0 = (int64_t)blockIdx.y * step_m, n0 = (int64_t)blockIdx.z * step_n;
+    const int lim_i = (int)min((int64_t)step_m, p.size_m - m0), lim_j = (int)min((int64_t)step_n, p.size_n - n0);
     const int64_t walk_pos = kSparseA ? m0 : n0;          // position along the sparse operand's grouped axis
     const int g = (int)(walk_pos / B), sub = (int)(walk_pos % B);   // group and offset inside the block
     const int lim_sub = min(kTile, B - sub);
@@ -167,7 +171,9 @@ int launch(const MatmulArgs& g) {
         if (gx > (int64_t)INT32_MAX || g.batches > 65535) return BSA_ERR_TOO_LARGE;
         sdd_kernel<T><<<dim3((unsigned)gx, (unsigned)g.batches), kThreads, 0, g.stream>>>(p);
     } else {
-        const int64_t gy = (g.size_m + kTile - 1) / kTile, gz = (g.size_n + kTile - 1) / kTile;
+        const int step_m = g.mode == BSA_MODE_DSD ? std::min(kTile, g.block) : kTile;
+        const int step_n = g.mode == BSA_MODE_DSD ? kTile : std::min(kTile, g.block);
+        const int64_t gy = (g.size_m + step_m - 1) / step_m, gz = (g.size_n + step_n - 1) / step_n;
         if (gy > 65535 || gz > 65535) return BSA_ERR_TOO_LARGE;
         const dim3 grid((unsigned)g.batches, (unsigned)gy, (unsigned)gz);
         if (g.mode == BSA_MODE_DSD) walk_kernel<T, true><<<grid, kThreads, 0, g.stream>>>(p);

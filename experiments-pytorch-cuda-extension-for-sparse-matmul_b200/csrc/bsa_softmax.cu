@@ -617,7 +617,7 @@ int check_common(int dtype, const void* a, const void* b, const void* c,
                  int64_t nnz, int64_t block_rows, int64_t batches, int block) {
     if (!a || !b || !c || !row_blocks || !row_table) return BSA_ERR_NULL_POINTER;
     if (dtype != BSA_DTYPE_F32 && dtype != BSA_DTYPE_F16 && dtype != BSA_DTYPE_BF16) return BSA_ERR_BAD_DTYPE;
-    if (block != 32 && block != 64 && block != 128) return BSA_ERR_BAD_BLOCK;
+    if (!valid_block(block)) return BSA_ERR_BAD_BLOCK;
     if (nnz < 0 || block_rows <= 0 || batches < 0) return BSA_ERR_BAD_SHAPE;
     if (block_rows > 65535 || batches > 65535 || nnz > (int64_t)INT32_MAX) return BSA_ERR_TOO_LARGE;
     if (!aligned16(a) || !aligned16(b) || !aligned16(c)) return BSA_ERR_ALIGNMENT;

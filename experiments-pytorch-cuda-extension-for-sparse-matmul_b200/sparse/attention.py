@@ -6,8 +6,12 @@ The reference has no such op: a caller composes it from its matmul in "sdd"
 mode (sparse/matmul.py:55-57), a softmax and its matmul in "dsd" mode, and
 every step writes the ``[..., nnz, block, block]`` tensor to memory.
 ``attention`` computes the same result in one kernel launch where the fused
-kernel applies (fp16 / bf16, block 64, head dim 64 or 128) and composes the
-three unfused ops otherwise, so it can be called for any layout and dtype.
+kernel applies (fp16 / bf16, block 64 or 128, head dim 64 or 128) and composes
+the three unfused ops otherwise, so it can be called for any layout and dtype.
+The kernel works on 64 x 64 blocks and touches no sparse tensor, only the
+positions of the blocks: a block-128 layout runs as the block-64 layout with
+every block split in 2 x 2 (the element-level masks do not depend on the
+block size).
 
 The backward pass of the fused path recomputes the probabilities with the
 unfused kernels (the forward keeps only the output and the row
@@ -29,8 +33,28 @@ from .softmax import softmax
 
 def fused_supported(q: torch.Tensor, layout: SparseLayout) -> bool:
     """True where the one-kernel forward applies."""
-    return (q.is_cuda and q.dtype in (torch.float16, torch.bfloat16) and layout.block == 64
+    return (q.is_cuda and q.dtype in (torch.float16, torch.bfloat16) and layout.block in (64, 128)
+            and 2 * layout.pattern.size(0) <= 65535 and 2 * layout.pattern.size(1) <= 65535
             and q.size(-1) in (64, 128))
+
+
+def _kernel_layout(layout: SparseLayout) -> SparseLayout:
+    """The layout in the kernel's 64 x 64 blocks (built once per layout object)."""
+    if layout.block == 64:
+        return layout
+    split = getattr(layout, "_split64", None)
+    if split is None:
+        pattern = (layout.pattern != 0).to(torch.uint8).repeat_interleave(2, 0).repeat_interleave(2, 1)
+        split = SparseLayout(pattern, block=64, device=layout.device)
+        layout._split64 = split
+    return split
+
+
+def _fused_forward(q, k, v, layout, scale, causal, key_padding_mask):
+    fine = _kernel_layout(layout)
+    row_blocks, row_table = fine.row_layout
+    return kernel.sparse_ops.sparse_attention_forward(
+        q, k, v, row_blocks, row_table, 64, fine.pattern.size(1), float(scale), bool(causal), key_padding_mask)
 
 
 class SparseAttention(torch.autograd.Function):
@@ -38,10 +62,7 @@ class SparseAttention(torch.autograd.Function):
     def forward(ctx: Any, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, layout: SparseLayout,
                 scale: float = 1.0, causal: bool = False,
                 key_padding_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
-        row_blocks, row_table = layout.row_layout
-        out, lse = kernel.sparse_ops.sparse_attention_forward(
-            q, k, v, row_blocks, row_table, layout.block, layout.pattern.size(1), float(scale), bool(causal),
-            key_padding_mask)
+        out, lse = _fused_forward(q, k, v, layout, scale, causal, key_padding_mask)
         ctx.save_for_backward(q, k, v)
         ctx.layout, ctx.scale, ctx.causal, ctx.kpm = layout, float(scale), bool(causal), key_padding_mask
         ctx.lse = lse
@@ -82,7 +103,4 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, layout: SparseL
 def attention_lse(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, layout: SparseLayout, scale: float = 1.0,
                   causal: bool = False, key_padding_mask: Optional[torch.Tensor] = None):
     """Forward only: (output, log-sum-exp of the scaled masked scores per query row)."""
-    row_blocks, row_table = layout.row_layout
-    return kernel.sparse_ops.sparse_attention_forward(
-        q, k, v, row_blocks, row_table, layout.block, layout.pattern.size(1), float(scale), bool(causal),
-        key_padding_mask)
+    return _fused_forward(q, k, v, layout, scale, causal, key_padding_mask)

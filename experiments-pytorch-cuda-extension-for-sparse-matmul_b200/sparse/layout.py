@@ -7,7 +7,7 @@ Differences, all additive:
 
 * the descriptor tensors are built on the GPU by ``sparse_ops.build_layout``
   (bit-identical to the reference's host-side ``_create_layout``, :14-38);
-* ``block`` is an attribute (32, 64 or 128; the reference hard-codes 32);
+* ``block`` is an attribute (16, 32, 64 or 128; the reference hard-codes 32);
 * a ``bool`` pattern is accepted (the reference's ``index_add`` saturates on
   bool and yields a wrong offset table);
 * ``to_dense`` zero-fills outside the layout (the reference leaves that
@@ -26,8 +26,8 @@ class SparseLayout:
         if pattern.dim() != 2:
             raise ValueError("pattern must be a 2-D tensor of 0/1 block flags, got shape %s"
                              % (tuple(pattern.shape),))
-        if block not in (32, 64, 128):
-            raise ValueError("block must be 32, 64 or 128, got %r" % (block,))
+        if block not in (16, 32, 64, 128):
+            raise ValueError("block must be 16, 32, 64 or 128, got %r" % (block,))
         if pattern.size(0) > 65535 or pattern.size(1) > 65535:
             raise ValueError("at most 65535 block rows / columns are supported")
         self.pattern = pattern

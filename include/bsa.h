@@ -40,7 +40,7 @@ enum {
     BSA_ERR_BAD_DTYPE = 3,      /* dtype code unknown or unsupported here     */
     BSA_ERR_BAD_SHAPE = 4,      /* a size is negative, zero where it must not
                                    be, or not a multiple of the block size    */
-    BSA_ERR_BAD_BLOCK = 5,      /* block size is not 32, 64 or 128            */
+    BSA_ERR_BAD_BLOCK = 5,      /* block size is not 16, 32, 64 or 128        */
     BSA_ERR_ALIGNMENT = 6,      /* a pointer is not 16-byte aligned           */
     BSA_ERR_WORKSPACE = 7,      /* workspace missing or too small             */
     BSA_ERR_LAUNCH = 8,         /* the CUDA runtime refused the launch        */

@@ -42,6 +42,14 @@ def test_config2_causal_local_global_fp16():
     _step(local_global_causal(32, 4, 1), 32, 3, 1024, 64, torch.float16, 0.125, True, 2000)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_block16_causal_step(dtype):
+    """The smallest block size through the whole step (CUDA-core matmuls, softmax with 2 or 4 chunks per
+    block row segment), forward and backward."""
+    from sparse.patterns import local_global_causal
+    _step(local_global_causal(16, 3, 1), 16, 3, 256, 64, dtype, 0.125, True, 2100)
+
+
 def test_config3_strided_local_fp16_forward_backward():
     from sparse.patterns import strided_local
     _step(strided_local(64, 8, 2), 64, 2, 4096, 64, torch.float16, 0.125, False, 3000)

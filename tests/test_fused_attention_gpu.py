@@ -136,6 +136,35 @@ def test_autograd_through_fused_attention():
     assert_close(vg.grad, dv, torch.float16, "dV")
 
 
+@pytest.mark.parametrize("dim", [64, 128])
+def test_fused_forward_block128_runs_as_split_block64_layout(dim):
+    """A block-128 layout goes through the same kernel as the block-64 layout with every block
+    split in 2 x 2; causal and key-padding masks are element-level and unchanged."""
+    from sparse.patterns import local_global_causal
+    g = load_golden_layout("empty_row_col_5x4")
+    _forward_case(g["pattern"], 128, (2,), dim, torch.float16, 0.2, seed=90)
+    kpm = torch.zeros(2, 8 * 128, dtype=torch.uint8)
+    kpm[0, 700:] = 1
+    kpm[1, :130] = 1
+    _forward_case(local_global_causal(8, 2, 1), 128, (2, 3), dim, torch.bfloat16, dim ** -0.5, True, kpm, seed=91)
+
+
+def test_autograd_through_fused_attention_block128():
+    from sparse import SparseLayout, attention
+    from sparse.patterns import local_global_causal
+    pattern = local_global_causal(4, 2, 1)
+    layout = SparseLayout(pattern, block=128)
+    q, k, v, do = (seeded((2, 512, 64), 95 + i, torch.float16) for i in range(4))
+    qg, kg, vg = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    out = attention(qg, kg, vg, layout, 0.125, True)
+    out.backward(do.cuda())
+    ref, dq, dk, dv = oracle.attention_step_dense(q, k, v, do, pattern.numpy(), 128, 0.125, True)
+    assert_close(out, ref, torch.float16, "output")
+    assert_close(qg.grad, dq, torch.float16, "dQ")
+    assert_close(kg.grad, dk, torch.float16, "dK")
+    assert_close(vg.grad, dv, torch.float16, "dV")
+
+
 def test_attention_composes_unfused_ops_where_the_fused_kernel_does_not_apply():
     from sparse import SparseLayout, attention
     from sparse.patterns import local_global_causal

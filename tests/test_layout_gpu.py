@@ -55,7 +55,7 @@ def test_converters_roundtrip():
     from sparse import SparseLayout
     g = load_golden_layout("kat_4x3")
     pattern = torch.tensor(g["pattern"])
-    for block in (32, 64):
+    for block in (16, 32, 64):
         layout = SparseLayout(pattern, block=block)
         x = torch.randn(2, 3, 4 * block, 3 * block, device="cuda", dtype=torch.float16)
         s = layout.to_sparse(x)

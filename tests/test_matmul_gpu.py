@@ -106,6 +106,17 @@ def test_block32_on_tensor_cores(mode, ta, tb, dtype):
         run_case(mode, ta, tb, pattern, 32, inner, dtype, "tcgen05", batch=(2,), seed=31 + inner)
 
 
+@pytest.mark.parametrize("mode,ta,tb", VARIANTS)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_block16_and_block128(mode, ta, tb, dtype):
+    """The smallest and the largest block size: 16 (two blocks per 32-wide tile of the CUDA-core engine)
+    and 128, with a dense size that is not a multiple of 32."""
+    g = load_golden_layout("kat_4x3")
+    run_case(mode, ta, tb, g["pattern"], 16, 40, dtype, "auto", batch=(3,), seed=77)
+    run_case(mode, ta, tb, _wide_pattern(), 16, 64, dtype, "auto", batch=(1,), seed=78)
+    run_case(mode, ta, tb, g["pattern"], 128, 64, dtype, "auto", batch=(1,), seed=79)
+
+
 def test_config1_sdd_fp32_per_head_layouts():
     """benchmark configuration 1: batch 1, heads 2, seq 256, head_dim 64, block 32, Bernoulli(0.5) + diagonal
     per head, Q.K^T as sdd(N,T) in fp32."""

@@ -16,7 +16,7 @@ def _layout(pattern, block):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("block", [32, 64, 128])
+@pytest.mark.parametrize("block", [16, 32, 64, 128])
 @pytest.mark.parametrize("name", ["kat_4x3", "empty_row_col_5x4", "one_by_one"])
 def test_forward_backward_matches_oracle(dtype, block, name):
     from sparse import softmax
@@ -36,7 +36,7 @@ def test_forward_backward_matches_oracle(dtype, block, name):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
-@pytest.mark.parametrize("block", [32, 64])
+@pytest.mark.parametrize("block", [16, 32, 64])
 def test_causal_and_key_padding_masks(dtype, block):
     from sparse import softmax
     from sparse.patterns import local_global_causal

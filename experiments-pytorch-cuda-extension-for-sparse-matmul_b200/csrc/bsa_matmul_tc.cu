@@ -3,8 +3,9 @@
 // Replaces the CUDA-core kernels sparse_smm_{sdd,dsd,dds}_32x32x32_kernel
 // (reference sparse/native/sparse_smm_gpu.cu:22-267) and the unfinished
 // half-precision sparse_hmm_sdd_32x32x32_kernel (sparse_hmm_gpu.cu:26-142,
-// fp16 accumulation) for 16-bit inputs with block 64: fp16 / bf16 operands,
-// fp32 accumulation in tensor memory.
+// fp16 accumulation) for 16-bit inputs with block 64 or 128: fp16 / bf16
+// operands, fp32 accumulation in tensor memory.  (Block 128 is walked as 2 x 2
+// tiles of 64 x 64 per block, see tile_desc.)
 //
 // Structure.  Everything is expressed in 64x64 16-bit tiles (8 KB, rows of
 // 128 bytes, 128-byte swizzle), the one shape that is both a TMA box of a
@@ -106,7 +107,32 @@ struct TcParams {
     int c_vec8;              // rows start on 32-byte boundaries: 256-bit stores are legal
     int stride_z, stride_rem;  // gridDim.x divided by the items per batch entry: quotient and remainder
     long long c_elems;       // elements in the output (bounds check of every store)
+    int split;               // block 128: every block is walked as 2 x 2 tiles of 64 x 64 (see tile_desc)
+    int col_walk;            // the groups are block columns (dsd with trans_a, dds without trans_b)
 };
+
+// Block 128.  The kernel keeps working on 64x64 tiles: a real group (block row or column) is two
+// virtual groups and a real block two K-steps / output tiles of each, i.e. the kernel sees the
+// layout with every block split in 2 x 2, without that layout ever being built.  `groups`, `nnz`
+// and `items` of TcParams count virtual units; the cursor reads table[g >> 1] and keeps first /
+// count in real blocks.  Virtual descriptor i of virtual group g is real descriptor i >> 1 with
+// one half taken from g & 1 and the other from i & 1 (which of row / column depends on the walk);
+// its idx is 4 * idx + 2 * row_half + col_half, decoded again by sparse_xy.
+__device__ __forceinline__ BlockDesc tile_desc(DescWindow& win, const TcParams& p, const Cursor& cur, int i, int lane) {
+    if (!p.split) return win.get(p.blocks, cur.first, cur.count, i, lane);
+    const BlockDesc d = win.get(p.blocks, cur.first, cur.count, i >> 1, lane);
+    const int from_step = i & 1, from_group = cur.g & 1;
+    const int rh = p.col_walk ? from_step : from_group, ch = p.col_walk ? from_group : from_step;
+    BlockDesc v;
+    v.idx = d.idx * 4 + rh * 2 + ch;
+    v.packed = (int32_t)(((uint32_t)(2 * d.row() + rh) << 16) | (uint32_t)(2 * d.col() + ch));
+    return v;
+}
+// TMA coordinates (column, row) of a tile inside the sparse tensor viewed as [nnz * block, block].
+__device__ __forceinline__ void sparse_xy(const TcParams& p, int idx, int& x, int& y) {
+    if (p.split) { x = (idx & 1) * kTile; y = (idx >> 2) * (2 * kTile) + ((idx >> 1) & 1) * kTile; }
+    else         { x = 0; y = idx * kTile; }
+}
 
 
 // Number of accumulations (each ends in an epilogue) and K-steps per accumulation of an item.
@@ -211,19 +237,19 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         long long t_wait = 0, t_issue = 0, t_get = 0, t_item = 0;
         const long long t_begin = TC_CLOCK();
         Cursor cur;
-        cur.init(p);
+        cur.init(p, p.split);
         BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
         while (ok && cur.valid()) {
             const long long t_i0 = TC_CLOCK();
             BlockDesc pre_next{0, 0};
             if (cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
             int flushes, ksteps;
-            item_shape<MODE>(p, cur.count, flushes, ksteps);
+            item_shape<MODE>(p, cur.count << p.split, flushes, ksteps);
             DescWindow win;
             win.begin(p.blocks, cur.first, cur.count, pre, lane);
             t_item += TC_CLOCK() - t_i0;
             for (int f = 0; ok && f < flushes; ++f) {
-                const int nb = b_tiles<MODE>(p, cur.count, cur.chunk, f);
+                const int nb = b_tiles<MODE>(p, cur.count << p.split, cur.chunk, f);
                 // The stage count is a multiple of the producer count, so a stage is always
                 // filled by the same producer.  This matters: an mbarrier parity wait can only
                 // tell the current phase from the one before it, so a thread must take part in
@@ -236,9 +262,9 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         if (is_sdd) {
 #pragma unroll
                             for (int j = 0; j < 4; ++j)
-                                if (j < nb) cols[j] = win.get(p.blocks, cur.first, cur.count, kSddTiles * f + j, lane).col();
+                                if (j < nb) cols[j] = tile_desc(win, p, cur, kSddTiles * f + j, lane).col();
                         } else {
-                            d = win.get(p.blocks, cur.first, cur.count, k, lane);
+                            d = tile_desc(win, p, cur, k, lane);
                         }
                         t_get += TC_CLOCK() - t_g0;
                         {
@@ -266,7 +292,9 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                     }
                                 } else if (MODE == BSA_MODE_DSD) {
                                     const int k0 = (p.trans_a ? d.row() : d.col()) * kTile;
-                                    tma_load_3d(slot, &map_a, full, 0, d.idx * kTile, cur.z);
+                                    int sx, sy;
+                                    sparse_xy(p, d.idx, sx, sy);
+                                    tma_load_3d(slot, &map_a, full, sx, sy, cur.z);
                                     for (int j = 0; j < nb; ++j) {
                                         const int n0 = (cur.chunk * 2 + j) * kTile;
                                         if (b_mn_major) tma_load_3d(slot + (1 + j) * kTileBytes, &map_b, full, n0, k0, cur.z);
@@ -277,7 +305,9 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                     const int m0 = cur.chunk * kTile;
                                     if (a_mn_major) tma_load_3d(slot, &map_a, full, m0, k0, cur.z);
                                     else            tma_load_3d(slot, &map_a, full, k0, m0, cur.z);
-                                    tma_load_3d(slot + kTileBytes, &map_b, full, 0, d.idx * kTile, cur.z);
+                                    int sx, sy;
+                                    sparse_xy(p, d.idx, sx, sy);
+                                    tma_load_3d(slot + kTileBytes, &map_b, full, sx, sy, cur.z);
                                 }
                             }
                             __syncwarp();
@@ -324,10 +354,10 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             long long t_full = 0, t_acc = 0, t_mma = 0, t_commit = 0, t_desc = 0, t_kloop = 0, t_accfull = 0;
             const long long t_begin = TC_CLOCK();
             Cursor cur;
-            cur.init(p);
+            cur.init(p, p.split);
             for (; ok && cur.valid(); cur.advance()) {
                 int flushes, ksteps;
-                item_shape<MODE>(p, cur.count, flushes, ksteps);
+                item_shape<MODE>(p, cur.count << p.split, flushes, ksteps);
                 if (ksteps == 0) continue;          // empty group: the epilogue writes zeros on its own
                 for (int f = 0; ok && f < flushes; ++f, ++flush_no) {
                     const int acc = flush_no & (kBufs - 1);
@@ -338,7 +368,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         while (stage >= p.stages) { stage -= p.stages; phase ^= 1; }
                         continue;
                     }
-                    const int nb = b_tiles<MODE>(p, cur.count, cur.chunk, f);
+                    const int nb = b_tiles<MODE>(p, cur.count << p.split, cur.chunk, f);
                     const uint32_t idesc = p.idesc | ((uint32_t)((nb * kTile) >> 3) << 17);
                     { const long long t0 = TC_CLOCK();
                       ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_empty[acc], ((uint32_t)(flush_no >> kBufShift) & 1u) ^ 1u, &bars->abort_flag, p.status)) != 0;
@@ -418,14 +448,14 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         long long t_accf = 0, t_ld = 0, t_write = 0;
         const long long t_begin = TC_CLOCK();
         Cursor cur;
-        cur.init(p);
+        cur.init(p, p.split);
         BlockDesc pre{0, 0};
         if (is_sdd && cur.valid()) pre = load_first_chunk(p.blocks, cur.first, cur.count, lane);
         while (ok && cur.valid()) {
             BlockDesc pre_next{0, 0};
             if (is_sdd && cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
             int flushes, ksteps;
-            item_shape<MODE>(p, cur.count, flushes, ksteps);
+            item_shape<MODE>(p, cur.count << p.split, flushes, ksteps);
             const bool have_acc = ksteps > 0;
             DescWindow win;
             if (is_sdd) win.begin(p.blocks, cur.first, cur.count, pre, lane);
@@ -439,7 +469,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 step += ksteps;
                 if (have_acc) ++flush_no;
                 if (owner != group) continue;
-                const int tiles = b_tiles<MODE>(p, cur.count, cur.chunk, f);
+                const int tiles = b_tiles<MODE>(p, cur.count << p.split, cur.chunk, f);
                 if (have_acc) {
                     const long long t0 = TC_CLOCK();
                     ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_full[acc], acc_phase, &bars->abort_flag, p.status)) != 0;
@@ -464,7 +494,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     const uint32_t sm_unit = (uint32_t)(lane >> 4);
                     const int slab0 = ((warp - kFirstEpilogueWarp) * 2) * (16 * 128);   // this warp's two slabs
                     auto store_tile = [&](const uint32_t (&r)[32], int t) {
-                        const int out_idx = win.get(p.blocks, cur.first, cur.count, kSddTiles * f + t, lane).idx;
+                        const int out_idx = tile_desc(win, p, cur, kSddTiles * f + t, lane).idx;
                         // a descriptor that does not belong to this layout is reported in the workspace
                         // (word 1 = offending tile index); the tensor map clips the store itself
                         const bool in_bounds = out_idx >= 0 && out_idx < p.nnz;
@@ -494,10 +524,12 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         __syncwarp();
                         // (issued from an elected lane of warp-uniform code: the copy's operands stay in
                         // uniform registers; the same lane every time, the bulk groups are per thread)
+                        int sx, sy;
+                        sparse_xy(p, out_idx, sx, sy);
                         if (elect_one()) {
                             if (in_bounds)
                                 asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
-                                             ::"l"(&map_c), "r"(slab), "r"(0), "r"(out_idx * kTile + quad * 16), "r"(cur.z) : "memory");
+                                             ::"l"(&map_c), "r"(slab), "r"(sx), "r"(sy + quad * 16), "r"(cur.z) : "memory");
                             asm volatile("cp.async.bulk.commit_group;" ::: "memory");   // (empty groups keep the count regular)
                         }
                         ++tile_no;
@@ -619,11 +651,13 @@ int64_t slices_of(const MatmulArgs& g) {
 
 bool tc_supports(const MatmulArgs& g) {
     if (g.dtype != BSA_DTYPE_F16 && g.dtype != BSA_DTYPE_BF16) return false;
-    if (g.block != kTile) return false;
-    if (g.nnz <= 0 || g.nnz * kTile >= ((int64_t)1 << 31) || g.batches > 65535) return false;
+    if (g.block != kTile && g.block != 2 * kTile) return false;
+    const int split = g.block == 2 * kTile ? 1 : 0;
+    if (g.nnz <= 0 || g.nnz * g.block >= ((int64_t)1 << 31) || (g.nnz << (2 * split)) >= ((int64_t)1 << 30) ||
+        g.batches > 65535) return false;
     if (!dense_dim_ok(g.size_m) || !dense_dim_ok(g.size_n) || !dense_dim_ok(g.size_k)) return false;
     // work items are indexed with 32-bit integers
-    if (g.batches * g.groups * slices_of(g) >= ((int64_t)1 << 30)) return false;
+    if (g.batches * (g.groups << split) * slices_of(g) >= ((int64_t)1 << 30)) return false;
     return true;
 }
 
@@ -647,30 +681,33 @@ int matmul_tc(const MatmulArgs& g) {
         if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) { cudaGetLastError(); return BSA_ERR_LAUNCH; }
     }
     CUtensorMap map_a, map_b, map_c;
-    const int64_t sparse_rows = g.nnz * kTile;
+    const int split = g.block == 2 * kTile ? 1 : 0;
+    const int64_t sparse_rows = g.nnz * g.block;     // the sparse tensor as a [nnz * block, block] matrix
     bool ok = true;
     // stored shapes: a dense operand is [rows, cols] = op^-1 of its logical shape
     if (g.mode == BSA_MODE_SDD) {
         ok &= make_map(&map_a, g.dtype, g.a, g.batches, g.trans_a ? g.size_k : g.size_m, g.trans_a ? g.size_m : g.size_k);
         ok &= make_map(&map_b, g.dtype, g.b, g.batches, g.trans_b ? g.size_n : g.size_k, g.trans_b ? g.size_k : g.size_n);
-        ok &= make_map(&map_c, g.dtype, g.c, g.batches, sparse_rows, kTile, 16);   // output leaves by TMA, 16 rows a time
+        ok &= make_map(&map_c, g.dtype, g.c, g.batches, sparse_rows, g.block, 16);   // output leaves by TMA, 16 rows a time
     } else if (g.mode == BSA_MODE_DSD) {
-        ok &= make_map(&map_a, g.dtype, g.a, g.batches, sparse_rows, kTile);
+        ok &= make_map(&map_a, g.dtype, g.a, g.batches, sparse_rows, g.block);
         ok &= make_map(&map_b, g.dtype, g.b, g.batches, g.trans_b ? g.size_n : g.size_k, g.trans_b ? g.size_k : g.size_n);
     } else {
         ok &= make_map(&map_a, g.dtype, g.a, g.batches, g.trans_a ? g.size_k : g.size_m, g.trans_a ? g.size_m : g.size_k);
-        ok &= make_map(&map_b, g.dtype, g.b, g.batches, sparse_rows, kTile);
+        ok &= make_map(&map_b, g.dtype, g.b, g.batches, sparse_rows, g.block);
     }
     if (!ok) return BSA_ERR_DRIVER;
     if (g.mode != BSA_MODE_SDD) map_c = map_a;      // unused by dsd / dds
 
     TcParams p{};
     p.blocks = g.blocks; p.table = g.table; p.status = g.workspace;
-    p.nnz = (int)g.nnz; p.groups = (int)g.groups; p.batches = (int)g.batches;
+    p.split = split;
+    p.col_walk = ((g.mode == BSA_MODE_DSD && g.trans_a) || (g.mode == BSA_MODE_DDS && !g.trans_b)) ? 1 : 0;
+    p.nnz = (int)(g.nnz << (2 * split)); p.groups = (int)(g.groups << split); p.batches = (int)g.batches;
     p.size_m = (int)g.size_m; p.size_n = (int)g.size_n; p.size_k = (int)g.size_k;
     p.mode = g.mode; p.trans_a = g.trans_a; p.trans_b = g.trans_b;
     p.chunks = (int)slices_of(g);
-    p.items = (int)(g.batches * g.groups * p.chunks);
+    p.items = (int)(g.batches * p.groups * p.chunks);
     if (g.mode == BSA_MODE_SDD) { p.nb_max = kSddTiles; p.issuers = 2; }
     else if (g.mode == BSA_MODE_DSD && g.size_n > kTile) { p.nb_max = 2; p.issuers = 2; }
     else { p.nb_max = 1; p.issuers = 4; }
@@ -693,7 +730,7 @@ int matmul_tc(const MatmulArgs& g) {
     p.c = static_cast<uint16_t*>(g.c);
     p.ldc = g.mode == BSA_MODE_SDD ? kTile : (int)g.size_n;
     p.c_vec8 = (reinterpret_cast<uintptr_t>(g.c) % 32 == 0 && p.ldc % 16 == 0) ? 1 : 0;
-    p.c_elems = g.mode == BSA_MODE_SDD ? (long long)g.batches * g.nnz * kTile * kTile
+    p.c_elems = g.mode == BSA_MODE_SDD ? (long long)g.batches * g.nnz * g.block * g.block
                                        : (long long)g.batches * g.size_m * g.size_n;
 
     const int sms = sm_count();

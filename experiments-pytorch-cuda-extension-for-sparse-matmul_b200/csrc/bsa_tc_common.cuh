@@ -147,6 +147,7 @@ __device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t (&w)[8]) 
 // entry): an integer division by a run-time value costs a lone thread hundreds of cycles.
 struct Cursor {
     int item, stride, items, chunks, per_z, stride_z, stride_rem;
+    int table_shift;                    // group g reads table[g >> table_shift] (1: two virtual groups per real one)
     const int32_t* table;
     int item_no;                        // how many items this CTA has finished
     int z, g, chunk, first, count;      // current item: batch entry, group, slice, block range
@@ -155,7 +156,10 @@ struct Cursor {
 
     __device__ __forceinline__ void load_words(bool in_range, int rem, int& a, int& b) const {
         a = 0; b = 0;
-        if (in_range) { const int gg = chunks == 1 ? rem : rem / chunks; a = table[gg]; b = table[gg + 1]; }
+        if (in_range) {
+            const int gg = (chunks == 1 ? rem : rem / chunks) >> table_shift;
+            a = table[gg]; b = table[gg + 1];
+        }
     }
     __device__ __forceinline__ void step_pos(int& zz, int& rem) const {
         zz += stride_z;
@@ -170,7 +174,8 @@ struct Cursor {
         count = b - a;
     }
     template <class Params>
-    __device__ __forceinline__ void init(const Params& p) {
+    __device__ __forceinline__ void init(const Params& p, int shift = 0) {
+        table_shift = shift;
         item = (int)blockIdx.x; stride = (int)gridDim.x; items = p.items;
         chunks = p.chunks; per_z = p.groups * p.chunks; table = p.table;
         stride_z = p.stride_z; stride_rem = p.stride_rem;

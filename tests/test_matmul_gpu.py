@@ -117,6 +117,20 @@ def test_block16_and_block128(mode, ta, tb, dtype):
     run_case(mode, ta, tb, g["pattern"], 128, 64, dtype, "auto", batch=(1,), seed=79)
 
 
+@pytest.mark.parametrize("mode,ta,tb", VARIANTS)
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_block128_on_tensor_cores(mode, ta, tb, dtype):
+    """Block 128 on the tcgen05 engine, requested explicitly (it must not fall back): every block is
+    walked as 2 x 2 tiles of 64 x 64.  Non-square pattern with empty groups, several work items per
+    CTA, dense sizes that leave a partial slice."""
+    g = load_golden_layout("empty_row_col_5x4")
+    run_case(mode, ta, tb, g["pattern"], 128, 64, dtype, "tcgen05", batch=(2,), seed=131)
+    rng = np.random.default_rng(5)
+    pattern = (rng.random((9, 7)) < 0.4).astype(np.int64)
+    pattern[3, :] = 0
+    run_case(mode, ta, tb, pattern, 128, 160, dtype, "tcgen05", batch=(5, 8), seed=132)
+
+
 def test_config1_sdd_fp32_per_head_layouts():
     """benchmark configuration 1: batch 1, heads 2, seq 256, head_dim 64, block 32, Bernoulli(0.5) + diagonal
     per head, Q.K^T as sdd(N,T) in fp32."""

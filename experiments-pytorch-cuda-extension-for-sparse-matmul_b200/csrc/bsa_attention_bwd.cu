@@ -1,0 +1,626 @@
+// Fused block-sparse attention backward (sm_100a only): dQ, dK, dV of
+//   O = softmax_rows(scale * Q K^T + masks, restricted to the layout) V
+// from Q, K, V, O, dO and the row log-sum-exp the forward kernel keeps, without the score,
+// probability or score-gradient blocks ever travelling through HBM.  The reference composes the
+// backward from its matmul in sdd / dsd mode (sparse/matmul.py:30-50 over sparse_smm_gpu.cu:22-183)
+// and its softmax backward (sparse_softmax.cu:165-205), each step writing a [batch, nnz, block,
+// block] tensor; this entry point has no counterpart there and exists beside the unfused operators.
+//
+// With D_i = sum_d dO_id O_id and, for every block (r, c) of the layout,
+//   P = exp(scale * Q_r K_c^T - lse_r),  dP = dO_r V_c^T,  dS = scale * P o (dP - D_r):
+//   dQ_r = sum_c dS K_c        dK_c = sum_r dS^T Q_r        dV_c = sum_r P^T dO_r.
+// Three launches: a small kernel writes (lse in log2 units, D) per query row; then one kernel
+// template runs twice:
+//   by rows    item = block row r of a batch entry, resident pair X = (Q_r, dO_r), per block the
+//              pair Y = (K_c, V_c):  T1 = X1 Y1^T = S, T2 = X2 Y2^T = dP, one operand tile dS,
+//              one accumulator dQ += dS Y1.
+//   by columns item = block column c (column layout), X = (K_c, V_c), Y = (Q_r, dO_r):
+//              T1 = S^T, T2 = dP^T (keys on the TMEM lanes, queries along the columns, so lse and
+//              D are per-column vectors read from global memory a block ahead), two operand tiles
+//              P^T and dS^T, two accumulators dV += P^T Y2 and dK += dS^T Y1.
+// All products run on the tensor cores (tcgen05, fp32 accumulators in TMEM, 16-bit operand tiles
+// of 64 x 64 in 128-byte-swizzled shared memory, loaded by TMA); the same shared-memory tile of Y
+// serves as the K-major B operand of T and as the MN-major B operand of the accumulations.
+// One CTA per SM with all 512 TMEM columns: T1 | T2 double buffered (columns 0-255), accumulators
+// from column 256.  Warp roles (12 warps):
+//   warp 0     TMA producer: the item's X pair (double buffered) and every block's Y pair (ring)
+//   warp 1, 3  issuers of T1 and T2 (a thread issues one tcgen05.mma per ~100 cycles whatever its
+//              size, so the two products of a block are issued side by side)
+//   warp 2     issuer of the accumulations; its commit per block frees the Y stage and the
+//              operand tiles
+//   warps 4-11 two compute warpgroups taking alternate blocks: tcgen05.ld of T1 and T2 (16x256b
+//              shape: a lane owns 2 rows x 16 columns), exp2, the dS formula, masks, 32-bit
+//              stores into the swizzled operand tiles; the group that owns an item's last block
+//              converts and stores the accumulators while the other one goes on.
+// Loops are warp-uniform with an elected lane around the TMA / tcgen05 instructions.  All waits are
+// bounded (BSA_ERR_DEVICE_TIMEOUT in the workspace word).
+#include "bsa_tc_common.cuh"
+
+namespace bsa {
+namespace {
+
+constexpr int kBwdThreads = 12 * 32;
+constexpr int kBwdTmemCols = 512;
+constexpr int kBwdAccCol0 = 256;
+constexpr int kBwdRing = 4;                 // Y stages (a power of two)
+constexpr int kBwdRingShift = 2;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct __align__(8) BwdBarriers {
+    uint64_t x_full[2], x_empty[2];
+    uint64_t y_full[kBwdRing];
+    uint64_t out_done[kBwdRing];    // the accumulation MMAs of a block have retired: Y stage and operand tiles are free
+    uint64_t t_full[2], t_empty[2];
+    uint64_t op_full[2];            // the operand tile(s) of a block are written
+    uint64_t o_full, o_empty;
+    uint64_t drain;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+struct BwdParams {
+    const BlockDesc* blocks;   // row layout (by rows) or column layout (by columns)
+    const int32_t* table;
+    uint32_t* status;
+    int nnz, groups, batches;
+    int chunks, items;         // chunks = 1 (kept for the shared cursor)
+    int stride_z, stride_rem;
+    int seq_q, seq_k, head_dim, dtiles;
+    int xbufs;                 // X pairs in shared memory (1 or 2)
+    float scale, scale_log2;
+    int causal;
+    const uint8_t* kpm;
+    int kpm_div;
+    long long kpm_stride;
+    const float2* stats;       // per query row: (lse * log2(e), or +inf for a row without scores; D)
+    uint16_t* out0;            // by rows: dQ; by columns: dV
+    uint16_t* out1;            // by columns: dK
+    uint32_t idesc_t, idesc_acc;
+};
+
+// (lse in log2 units, D_i = sum_d dO_id O_id) per query row; one group of head_dim / 8 lanes per row.
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+attention_backward_stats_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ dout,
+                                const float* __restrict__ lse, float2* __restrict__ stats,
+                                long long rows, int head_dim) {
+    const int lanes = head_dim / 8;                           // 8 or 16
+    const long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / lanes;
+    const int part = (int)(threadIdx.x % lanes);
+    float acc = 0.f;
+    if (row < rows) {
+        const uint4 a = *reinterpret_cast<const uint4*>(o + row * head_dim + part * 8);
+        const uint4 b = *reinterpret_cast<const uint4*>(dout + row * head_dim + part * 8);
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 fa, fb;
+            if (BF16) {
+                fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&aw[i]));
+                fb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bw[i]));
+            } else {
+                fa = __half22float2(*reinterpret_cast<const __half2*>(&aw[i]));
+                fb = __half22float2(*reinterpret_cast<const __half2*>(&bw[i]));
+            }
+            acc = fmaf(fa.x, fb.x, acc);
+            acc = fmaf(fa.y, fb.y, acc);
+        }
+    }
+    for (int d = lanes >> 1; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+    if (row < rows && part == 0) {
+        const float l = lse[row];
+        stats[row] = make_float2(l == -INFINITY ? INFINITY : l * kLog2e, acc);
+    }
+}
+
+template <bool COL, bool BF16, bool MASKED>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid_constant__ CUtensorMap map_x2,
+                          const __grid_constant__ CUtensorMap map_y1, const __grid_constant__ CUtensorMap map_y2,
+                          const BwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr int kOpTiles = COL ? 2 : 1;                  // operand tiles per block
+    const int set_bytes = p.dtiles * kTileBytes;            // one 64-row tile set of Q / K / V / dO
+    uint8_t* x_smem = smem;                                 // [xbufs][2][set]
+    uint8_t* y_smem = x_smem + p.xbufs * 2 * set_bytes;     // [ring][2][set]
+    uint8_t* op_smem = y_smem + kBwdRing * 2 * set_bytes;   // [2][kOpTiles] tiles
+    BwdBarriers* bars = reinterpret_cast<BwdBarriers*>(op_smem + 2 * kOpTiles * kTileBytes);
+    int* abort_flag = &bars->abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int ring_mask = kBwdRing - 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&bars->x_full[s], 1); mbar_init(&bars->x_empty[s], 2);
+            mbar_init(&bars->t_full[s], 2); mbar_init(&bars->t_empty[s], 4);
+            mbar_init(&bars->op_full[s], 4);
+        }
+        for (int s = 0; s < kBwdRing; ++s) { mbar_init(&bars->y_full[s], 1); mbar_init(&bars->out_done[s], 1); }
+        mbar_init(&bars->o_full, 1); mbar_init(&bars->o_empty, 4);
+        mbar_init(&bars->drain, 3);
+        bars->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_shared();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&bars->tmem_base)), "r"((uint32_t)kBwdTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *(volatile uint32_t*)&bars->tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        int y_no = 0, x_no = 0;
+        bool ok = true;
+        Cursor cur;
+        cur.init(p);
+        BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
+        while (ok && cur.valid()) {
+            BlockDesc pre_next{0, 0};
+            if (cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
+            const int n = cur.count;
+            if (n > 0) {
+                const int xb = x_no & (p.xbufs - 1);
+                const uint32_t use = (uint32_t)(p.xbufs == 2 ? x_no >> 1 : x_no);
+                ok = __all_sync(0xffffffffu, mbar_wait(&bars->x_empty[xb], (use & 1u) ^ 1u, abort_flag, p.status)) != 0;
+                if (ok && elect_one()) {
+                    mbar_expect_tx(&bars->x_full[xb], (uint32_t)(2 * set_bytes));
+                    for (int t = 0; t < p.dtiles; ++t) {
+                        tma_load_3d(x_smem + (xb * 2 + 0) * set_bytes + t * kTileBytes, &map_x1, &bars->x_full[xb], t * kTile, cur.g * kTile, cur.z);
+                        tma_load_3d(x_smem + (xb * 2 + 1) * set_bytes + t * kTileBytes, &map_x2, &bars->x_full[xb], t * kTile, cur.g * kTile, cur.z);
+                    }
+                }
+                __syncwarp();
+                ++x_no;
+                DescWindow win;
+                win.begin(p.blocks, cur.first, cur.count, pre, lane);
+                for (int j = 0; ok && j < n; ++j, ++y_no) {
+                    const BlockDesc d = win.get(p.blocks, cur.first, cur.count, j, lane);
+                    const int other = COL ? d.row() : d.col();
+                    const int stage = y_no & ring_mask;
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->out_done[stage], ((uint32_t)(y_no >> kBwdRingShift) & 1u) ^ 1u,
+                                                           abort_flag, p.status)) != 0;
+                    if (ok && elect_one()) {
+                        uint64_t* full = &bars->y_full[stage];
+                        mbar_expect_tx(full, (uint32_t)(2 * set_bytes));
+                        for (int t = 0; t < p.dtiles; ++t) {
+                            tma_load_3d(y_smem + (stage * 2 + 0) * set_bytes + t * kTileBytes, &map_y1, full, t * kTile, other * kTile, cur.z);
+                            tma_load_3d(y_smem + (stage * 2 + 1) * set_bytes + t * kTileBytes, &map_y2, full, t * kTile, other * kTile, cur.z);
+                        }
+                    }
+                    __syncwarp();
+                }
+            }
+            pre = pre_next;
+            cur.advance();
+        }
+        if (lane == 0 && *(volatile int*)abort_flag) {
+            // Give copies that were issued a bounded chance to land before the CTA exits.
+            const unsigned long long t0 = global_ns();
+            for (int s = 0; s < kBwdRing; ++s)
+                while (!mbar_try_wait(&bars->y_full[s], 0) && !mbar_try_wait(&bars->y_full[s], 1) &&
+                       global_ns() - t0 < kWaitLimitNs / 4) {}
+            for (int s = 0; s < p.xbufs; ++s)
+                while (!mbar_try_wait(&bars->x_full[s], 0) && !mbar_try_wait(&bars->x_full[s], 1) &&
+                       global_ns() - t0 < kWaitLimitNs / 4) {}
+        }
+        __syncwarp();
+    } else if (warp == 1 || warp == 3) {
+        // ------------------------------------------------------------ issuers of T1 = X1 Y1^T (warp 1) and T2 = X2 Y2^T (warp 3)
+        const int which = warp == 1 ? 0 : 1;
+        int s_no = 0, x_no = 0;
+        bool ok = true;
+        Cursor cur;
+        cur.init(p);
+        for (; ok && cur.valid(); cur.advance()) {
+            const int n = cur.count;
+            if (n == 0) continue;
+            const int xb = x_no & (p.xbufs - 1);
+            ok = __all_sync(0xffffffffu, mbar_wait(&bars->x_full[xb], (uint32_t)(p.xbufs == 2 ? x_no >> 1 : x_no) & 1u,
+                                                   abort_flag, p.status)) != 0;
+            if (!ok) break;
+            const int s_end = s_no + n;
+            for (int s = s_no; s < s_end; ++s) {
+                const int stage = s & ring_mask, tb = s & 1;
+                ok = __all_sync(0xffffffffu, mbar_wait(&bars->y_full[stage], (uint32_t)(s >> kBwdRingShift) & 1u, abort_flag, p.status)) != 0;
+                if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->t_empty[tb], ((uint32_t)(s >> 1) & 1u) ^ 1u, abort_flag, p.status)) != 0;
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d = tmem_base + (uint32_t)(tb * 2 * kTile + which * kTile);
+                if (elect_one()) {
+                    for (int t = 0; t < p.dtiles; ++t) {
+                        const uint64_t da = make_tile_desc(smem_u32(x_smem + (xb * 2 + which) * set_bytes + t * kTileBytes), false);
+                        const uint64_t db = make_tile_desc(smem_u32(y_smem + (stage * 2 + which) * set_bytes + t * kTileBytes), false);
+#pragma unroll
+                        for (int kk = 0; kk < kTile / 16; ++kk)
+                            tc_mma_f16(d, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), p.idesc_t, (t > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    tc_commit(&bars->t_full[tb]);
+                }
+                __syncwarp();
+            }
+            if (!ok) break;
+            if (elect_one()) tc_commit(&bars->x_empty[xb]);       // this issuer's last read of the X pair has been issued
+            __syncwarp();
+            s_no = s_end;
+            ++x_no;
+        }
+        // All MMAs issued by the elected lane (the same one every time) must have retired before TMEM is freed.
+        if (elect_one()) {
+            tc_commit(&bars->drain);
+            mbar_wait(&bars->drain, 0, abort_flag, p.status);
+        }
+        __syncwarp();
+    } else if (warp == 2) {
+        // ------------------------------------------------------------ issuer of the accumulations
+        int s_no = 0, o_no = 0;
+        bool ok = true;
+        Cursor cur;
+        cur.init(p);
+        for (; ok && cur.valid(); cur.advance()) {
+            const int n = cur.count;
+            if (n == 0) continue;
+            for (int j = 0; ok && j < n; ++j) {
+                const int s = s_no + j, stage = s & ring_mask, ob = s & 1;
+                if (j == 0) ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_empty, (uint32_t)(o_no & 1) ^ 1u, abort_flag, p.status)) != 0;
+                if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->y_full[stage], (uint32_t)(s >> kBwdRingShift) & 1u, abort_flag, p.status)) != 0;
+                if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->op_full[ob], (uint32_t)(s >> 1) & 1u, abort_flag, p.status)) != 0;
+                if (!ok) break;
+                tc_fence_after();
+                if (elect_one()) {
+                    // A = operand tile (K-major), B = a Y tile set with N = head_dim contiguous
+                    const uint64_t a0 = make_tile_desc(smem_u32(op_smem + (ob * kOpTiles) * kTileBytes), false);
+                    const uint64_t y1 = make_tile_desc(smem_u32(y_smem + (stage * 2 + 0) * set_bytes), true);
+                    const uint64_t y2 = make_tile_desc(smem_u32(y_smem + (stage * 2 + 1) * set_bytes), true);
+                    const uint32_t d0 = tmem_base + (uint32_t)kBwdAccCol0;
+#pragma unroll
+                    for (int kk = 0; kk < kTile / 16; ++kk)
+                        tc_mma_f16(d0, a0 + (uint64_t)(kk * 2), (COL ? y2 : y1) + (uint64_t)(kk * (2048 >> 4)), p.idesc_acc,
+                                   (j > 0 || kk > 0) ? 1u : 0u);
+                    if (COL) {
+                        const uint64_t a1 = make_tile_desc(smem_u32(op_smem + (ob * kOpTiles + 1) * kTileBytes), false);
+                        const uint32_t d1 = d0 + (uint32_t)p.head_dim;
+#pragma unroll
+                        for (int kk = 0; kk < kTile / 16; ++kk)
+                            tc_mma_f16(d1, a1 + (uint64_t)(kk * 2), y1 + (uint64_t)(kk * (2048 >> 4)), p.idesc_acc,
+                                       (j > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    tc_commit(&bars->out_done[stage]);
+                    if (j == n - 1) tc_commit(&bars->o_full);
+                }
+                __syncwarp();
+            }
+            s_no += n;
+            ++o_no;
+        }
+        if (elect_one()) {
+            tc_commit(&bars->drain);
+            mbar_wait(&bars->drain, 0, abort_flag, p.status);
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ compute warpgroups
+        // Group g takes the blocks with number s & 1 == g (T buffer g, operand buffer g).
+        const int wg = (warp - 4) >> 2;
+        const int quad = warp & 3;                  // TMEM sub-partition this warp may read
+        const int q4 = lane & 3;                    // position in the quad: columns 8u + 2 * q4 + {0, 1}
+        const int row_a = quad * 16 + (lane >> 2);  // this lane's two rows of the 64-row tile: row_a, row_a + 8
+        const uint32_t lane_field = (uint32_t)(quad * 32) << 16;
+        const bool masked_op = MASKED && (p.causal != 0 || p.kpm != nullptr);
+        const float c2 = p.scale_log2, sc = p.scale;
+        const int out_rows = COL ? p.seq_k : p.seq_q;
+        int s_no = 0, o_no = 0;
+        bool ok = true;
+        Cursor cur;
+        cur.init(p);
+        BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
+        while (ok && cur.valid()) {
+            BlockDesc pre_next{0, 0};
+            if (cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
+            const int n = cur.count;
+            const size_t out_a = ((size_t)cur.z * out_rows + (size_t)cur.g * kTile + row_a) * p.head_dim;
+            const size_t out_b = out_a + (size_t)8 * p.head_dim;
+            if (n == 0) {
+                // a group without blocks: zero gradient rows
+                if (wg == 0) {
+                    for (int c = q4 * 8; c < p.head_dim; c += 32) {
+                        *reinterpret_cast<uint4*>(p.out0 + out_a + c) = make_uint4(0u, 0u, 0u, 0u);
+                        *reinterpret_cast<uint4*>(p.out0 + out_b + c) = make_uint4(0u, 0u, 0u, 0u);
+                        if (COL) {
+                            *reinterpret_cast<uint4*>(p.out1 + out_a + c) = make_uint4(0u, 0u, 0u, 0u);
+                            *reinterpret_cast<uint4*>(p.out1 + out_b + c) = make_uint4(0u, 0u, 0u, 0u);
+                        }
+                    }
+                }
+            } else {
+                const uint8_t* kpm_row = (MASKED && p.kpm) ? p.kpm + (size_t)(cur.z / p.kpm_div) * p.kpm_stride : nullptr;
+                const int pos_a = cur.g * kTile + row_a;         // by rows: query position; by columns: key position
+                const float2* stats_z = p.stats + (size_t)cur.z * p.seq_q;
+                // by rows: the statistics of this lane's two query rows
+                float2 st_a = make_float2(0.f, 0.f), st_b = st_a;
+                if (!COL) { st_a = stats_z[pos_a]; st_b = stats_z[pos_a + 8]; }
+                // by columns: a whole key row is padding or not
+                bool pad_a = false, pad_b = false;
+                if (COL && MASKED && kpm_row) { pad_a = kpm_row[pos_a] != 0; pad_b = kpm_row[pos_a + 8] != 0; }
+                DescWindow win;
+                win.begin(p.blocks, cur.first, cur.count, pre, lane);
+                const uint32_t op_row = (uint32_t)(row_a * 128 + 4 * q4), op_xor = (uint32_t)(row_a & 7);
+                const int t_first = (wg - s_no) & 1;            // this group's first block of the item
+                // by columns: statistics of the block's 16 query columns of this lane, loaded a block ahead:
+                // cs[u] = (lse2, D) of column 8u + 2 q4 and of column 8u + 2 q4 + 1
+                float4 cs_next[8];
+                auto load_col_stats = [&](int block_row) {
+                    const float4* src = reinterpret_cast<const float4*>(stats_z + (size_t)block_row * kTile + 2 * q4);
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) cs_next[u] = src[4 * u];       // 8 columns = 4 float4 apart
+                };
+                if (COL && t_first < n) load_col_stats(win.get(p.blocks, cur.first, cur.count, t_first, lane).row());
+                for (int t = t_first; ok && t < n; t += 2) {
+                    const int s = s_no + t, tb = s & 1;
+                    const BlockDesc d = win.get(p.blocks, cur.first, cur.count, t, lane);
+                    const int other = COL ? d.row() : d.col();
+                    float4 cs[8];
+                    if (COL) {
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) cs[u] = cs_next[u];
+                        if (t + 2 < n) load_col_stats(win.get(p.blocks, cur.first, cur.count, t + 2, lane).row());
+                    }
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->t_full[tb], (uint32_t)(s >> 1) & 1u, abort_flag, p.status)) != 0;
+                    if (!ok) break;
+                    tc_fence_after();
+                    uint32_t r1[32], r2[32];
+                    tc_ld_16x256b_x8(tmem_base + lane_field + (uint32_t)(tb * 2 * kTile), r1);
+                    tc_ld_16x256b_x8(tmem_base + lane_field + (uint32_t)(tb * 2 * kTile + kTile), r2);
+                    tc_wait_ld();
+                    release_accumulator(&bars->t_empty[tb], lane);
+                    // the operand tiles of this buffer must have been read by the MMAs of block s - 2
+                    if (s >= 2) {
+                        ok = __all_sync(0xffffffffu, mbar_wait(&bars->out_done[(s - 2) & ring_mask],
+                                                               (uint32_t)((s - 2) >> kBwdRingShift) & 1u, abort_flag, p.status)) != 0;
+                        if (!ok) break;
+                    }
+                    const uint32_t tile0 = smem_u32(op_smem + (tb * kOpTiles) * kTileBytes) + op_row;
+                    const int other0 = other * kTile + 2 * q4;          // position of column u = 0, e = 0
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        float pa[2], pb[2], da[2], db[2];
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            float lse_a, lse_b, dl_a, dl_b;
+                            if (COL) {
+                                lse_a = lse_b = e == 0 ? cs[u].x : cs[u].z;
+                                dl_a = dl_b = e == 0 ? cs[u].y : cs[u].w;
+                            } else {
+                                lse_a = st_a.x; dl_a = st_a.y; lse_b = st_b.x; dl_b = st_b.y;
+                            }
+                            pa[e] = attn_exp2(fmaf(__uint_as_float(r1[4 * u + e]), c2, -lse_a));
+                            pb[e] = attn_exp2(fmaf(__uint_as_float(r1[4 * u + 2 + e]), c2, -lse_b));
+                            if (MASKED && masked_op) {
+                                const int opos = other0 + 8 * u + e;
+                                bool m_a, m_b;
+                                if (COL) {
+                                    // lane rows are keys, columns are queries
+                                    m_a = pad_a || (p.causal && pos_a > opos);
+                                    m_b = pad_b || (p.causal && pos_a + 8 > opos);
+                                } else {
+                                    const bool pad = kpm_row != nullptr && kpm_row[opos] != 0;
+                                    m_a = pad || (p.causal && opos > pos_a);
+                                    m_b = pad || (p.causal && opos > pos_a + 8);
+                                }
+                                if (m_a) pa[e] = 0.f;
+                                if (m_b) pb[e] = 0.f;
+                            }
+                            da[e] = pa[e] * (__uint_as_float(r2[4 * u + e]) - dl_a) * sc;
+                            db[e] = pb[e] * (__uint_as_float(r2[4 * u + 2 + e]) - dl_b) * sc;
+                        }
+                        const uint32_t addr = tile0 + (((uint32_t)u ^ op_xor) << 4);
+                        if (COL) {
+                            // tile 0: P^T, tile 1: dS^T
+                            asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(pack2<BF16>(pa[0], pa[1])) : "memory");
+                            asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + 8 * 128), "r"(pack2<BF16>(pb[0], pb[1])) : "memory");
+                            asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + kTileBytes), "r"(pack2<BF16>(da[0], da[1])) : "memory");
+                            asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + kTileBytes + 8 * 128), "r"(pack2<BF16>(db[0], db[1])) : "memory");
+                        } else {
+                            asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(pack2<BF16>(da[0], da[1])) : "memory");
+                            asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + 8 * 128), "r"(pack2<BF16>(db[0], db[1])) : "memory");
+                        }
+                    }
+                    fence_async_shared();           // generic-proxy writes -> visible to the tensor core's reads
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars->op_full[tb]);
+                }
+                s_no += n;
+                if (!ok) break;
+                // The group that owns the item's last block stores the accumulators; the other one
+                // owns the next item's first block and goes on right away.
+                if (wg == ((s_no - 1) & 1)) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full, (uint32_t)(o_no & 1), abort_flag, p.status)) != 0;
+                    if (!ok) break;
+                    tc_fence_after();
+                    constexpr int kOuts = COL ? 2 : 1;
+#pragma unroll
+                    for (int a = 0; a < kOuts; ++a) {
+                        uint16_t* out = a == 0 ? p.out0 : p.out1;
+                        for (int c = 0; c < p.head_dim; c += 32) {
+                            uint32_t r0[16];
+                            tc_ld_16x256b_x4(tmem_base + lane_field + (uint32_t)(kBwdAccCol0 + a * p.head_dim + c), r0);
+                            tc_wait_ld();
+                            if (a == kOuts - 1 && c + 32 >= p.head_dim) release_accumulator(&bars->o_empty, lane);
+                            uint32_t ta[4], tb2[4];
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                ta[u] = pack2<BF16>(__uint_as_float(r0[4 * u]), __uint_as_float(r0[4 * u + 1]));
+                                tb2[u] = pack2<BF16>(__uint_as_float(r0[4 * u + 2]), __uint_as_float(r0[4 * u + 3]));
+                            }
+                            quad_transpose(ta, q4);          // now columns c + 8 * q4 .. + 7 of the row
+                            quad_transpose(tb2, q4);
+                            *reinterpret_cast<uint4*>(out + out_a + c + 8 * q4) = make_uint4(ta[0], ta[1], ta[2], ta[3]);
+                            *reinterpret_cast<uint4*>(out + out_b + c + 8 * q4) = make_uint4(tb2[0], tb2[1], tb2[2], tb2[3]);
+                        }
+                    }
+                }
+                ++o_no;
+            }
+            pre = pre_next;
+            cur.advance();
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kBwdTmemCols)
+                     : "memory");
+    }
+}
+
+}  // namespace
+
+namespace {
+
+// One launch of the backward kernel template (by rows or by columns).
+template <bool COL>
+int launch_backward(int dtype, bool masked, const CUtensorMap& x1, const CUtensorMap& x2, const CUtensorMap& y1,
+                    const CUtensorMap& y2, BwdParams p, cudaStream_t stream) {
+    using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const BwdParams);
+    KernelFn kernel;
+    if (dtype == BSA_DTYPE_BF16) kernel = masked ? attention_backward_kernel<COL, true, true> : attention_backward_kernel<COL, true, false>;
+    else                         kernel = masked ? attention_backward_kernel<COL, false, true> : attention_backward_kernel<COL, false, false>;
+    // by columns with head dim 128 the two accumulators and four operand tiles leave room for one X pair only
+    p.xbufs = (COL && p.dtiles == 2) ? 1 : 2;
+    int smem_bytes = 1024 + ((p.xbufs * 2 + kBwdRing * 2) * p.dtiles + 2 * (COL ? 2 : 1)) * kTileBytes + (int)sizeof(BwdBarriers);
+    // more than half of an SM's shared memory: the CTA allocates all 512 TMEM columns and must be alone
+    if (smem_bytes < 116 * 1024) smem_bytes = 116 * 1024;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return BSA_ERR_LAUNCH;
+    }
+    const int sms = sm_count();
+    if (sms <= 0) return BSA_ERR_LAUNCH;
+    const unsigned grid = (unsigned)(p.items < sms ? p.items : sms);
+    p.stride_z = (int)grid / p.groups;
+    p.stride_rem = (int)grid % p.groups;
+    kernel<<<grid, kBwdThreads, smem_bytes, stream>>>(x1, x2, y1, y2, p);
+    return launch_status();
+}
+
+}  // namespace
+
+// Host side of bsa_attention_backward (arguments already validated by the caller).
+int attention_backward(int dtype, const void* q, const void* k, const void* v, const void* o, const void* dout,
+                       const float* lse, void* dq, void* dk, void* dv,
+                       const int32_t* row_blocks, const int32_t* row_table,
+                       const int32_t* col_blocks, const int32_t* col_table,
+                       int64_t nnz, int64_t block_rows, int64_t block_cols, int64_t batches, int64_t head_dim,
+                       float scale, int causal, const uint8_t* kpm, int64_t kpm_batches, int64_t kpm_stride,
+                       float2* stats, uint32_t* workspace, cudaStream_t stream) {
+    {
+        int dev = 0;   // binds the device's primary context to this thread (the driver call behind make_map needs it)
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) { cudaGetLastError(); return BSA_ERR_LAUNCH; }
+    }
+    const int64_t seq_q = block_rows * kTile, seq_k = block_cols * kTile;
+    const long long rows = (long long)batches * seq_q;
+    {
+        const int lanes = (int)head_dim / 8;
+        const long long threads = rows * lanes;
+        const unsigned grid = (unsigned)((threads + 255) / 256);
+        if (dtype == BSA_DTYPE_BF16)
+            attention_backward_stats_kernel<true><<<grid, 256, 0, stream>>>(
+                static_cast<const uint16_t*>(o), static_cast<const uint16_t*>(dout), lse, stats, rows, (int)head_dim);
+        else
+            attention_backward_stats_kernel<false><<<grid, 256, 0, stream>>>(
+                static_cast<const uint16_t*>(o), static_cast<const uint16_t*>(dout), lse, stats, rows, (int)head_dim);
+        const int st = launch_status();
+        if (st != BSA_OK) return st;
+    }
+    CUtensorMap map_q, map_k, map_v, map_do;
+    bool ok = make_map(&map_q, dtype, q, batches, seq_q, head_dim);
+    ok &= make_map(&map_do, dtype, dout, batches, seq_q, head_dim);
+    ok &= make_map(&map_k, dtype, k, batches, seq_k, head_dim);
+    ok &= make_map(&map_v, dtype, v, batches, seq_k, head_dim);
+    if (!ok) return BSA_ERR_DRIVER;
+
+    BwdParams p{};
+    p.status = workspace;
+    p.nnz = (int)nnz; p.batches = (int)batches;
+    p.chunks = 1;
+    p.seq_q = (int)seq_q; p.seq_k = (int)seq_k; p.head_dim = (int)head_dim;
+    p.dtiles = (int)(head_dim / kTile);
+    p.scale = scale;
+    p.scale_log2 = scale * kLog2e;
+    p.causal = causal;
+    p.kpm = kpm;
+    p.kpm_div = kpm ? (int)(batches / kpm_batches) : 1;
+    p.kpm_stride = kpm_stride;
+    p.stats = stats;
+    // instruction descriptors: fp32 accumulate, fp16 / bf16 operands, M = 64; T: both operands K-major,
+    // N = 64; accumulations: B (a Y tile set) with N contiguous, N = head_dim
+    const uint32_t fmt = dtype == BSA_DTYPE_BF16 ? 1u : 0u;
+    const uint32_t common = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(kTile >> 4) << 24);
+    p.idesc_t = common | ((uint32_t)(kTile >> 3) << 17);
+    p.idesc_acc = common | (1u << 16) | ((uint32_t)(head_dim >> 3) << 17);
+    const bool masked = causal != 0 || kpm != nullptr;
+
+    // dQ by rows: X = (Q_r, dO_r), Y = (K_c, V_c)
+    p.blocks = reinterpret_cast<const BlockDesc*>(row_blocks);
+    p.table = row_table;
+    p.groups = (int)block_rows;
+    p.items = (int)(batches * block_rows);
+    p.out0 = static_cast<uint16_t*>(dq);
+    p.out1 = nullptr;
+    int st = launch_backward<false>(dtype, masked, map_q, map_do, map_k, map_v, p, stream);
+    if (st != BSA_OK) return st;
+    // dV, dK by columns: X = (K_c, V_c), Y = (Q_r, dO_r)
+    p.blocks = reinterpret_cast<const BlockDesc*>(col_blocks);
+    p.table = col_table;
+    p.groups = (int)block_cols;
+    p.items = (int)(batches * block_cols);
+    p.out0 = static_cast<uint16_t*>(dv);
+    p.out1 = static_cast<uint16_t*>(dk);
+    return launch_backward<true>(dtype, masked, map_k, map_v, map_q, map_do, p, stream);
+}
+
+}  // namespace bsa
+
+extern "C" int bsa_attention_backward(int dtype, const void* q, const void* k, const void* v, const void* o,
+                                      const void* dout, const float* lse, void* dq, void* dk, void* dv,
+                                      const int32_t* row_blocks, const int32_t* row_table,
+                                      const int32_t* col_blocks, const int32_t* col_table,
+                                      int64_t nnz, int64_t block_rows, int64_t block_cols, int64_t batches,
+                                      int64_t head_dim, int block, float scale, int causal,
+                                      const uint8_t* key_padding_mask, int64_t kpm_batches, int64_t kpm_stride,
+                                      void* stats, size_t stats_bytes,
+                                      void* workspace, size_t workspace_bytes, void* stream) {
+    using namespace bsa;
+    if (dtype != BSA_DTYPE_F32 && dtype != BSA_DTYPE_F16 && dtype != BSA_DTYPE_BF16) return BSA_ERR_BAD_DTYPE;
+    if (!valid_block(block)) return BSA_ERR_BAD_BLOCK;
+    if (!q || !k || !v || !o || !dout || !lse || !dq || !dk || !dv || !row_blocks || !row_table || !col_blocks || !col_table)
+        return BSA_ERR_NULL_POINTER;
+    if (!workspace || workspace_bytes < BSA_WORKSPACE_BYTES) return BSA_ERR_WORKSPACE;
+    if (nnz < 0 || block_rows <= 0 || block_cols <= 0 || batches < 0 || head_dim <= 0) return BSA_ERR_BAD_SHAPE;
+    if (block_rows > 65535 || block_cols > 65535 || nnz > block_rows * block_cols) return BSA_ERR_BAD_SHAPE;
+    if (!attention_supports(dtype, head_dim, block)) return dtype == BSA_DTYPE_F32 ? BSA_ERR_BAD_DTYPE : BSA_ERR_BAD_SHAPE;
+    if (batches > 65535 || batches * block_rows >= ((int64_t)1 << 30) || batches * block_cols >= ((int64_t)1 << 30) ||
+        block_rows * block >= ((int64_t)1 << 31) || block_cols * block >= ((int64_t)1 << 31))
+        return BSA_ERR_TOO_LARGE;
+    if (!stats || stats_bytes < (size_t)batches * block_rows * block * 8) return BSA_ERR_WORKSPACE;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(dout) || !aligned16(dq) ||
+        !aligned16(dk) || !aligned16(dv) || !aligned16(stats))
+        return BSA_ERR_ALIGNMENT;
+    if (key_padding_mask && (kpm_batches <= 0 || batches % kpm_batches != 0 || kpm_stride < block_cols * block))
+        return BSA_ERR_BAD_SHAPE;
+    if (batches == 0) return BSA_OK;
+    return attention_backward(dtype, q, k, v, o, dout, lse, dq, dk, dv, row_blocks, row_table, col_blocks, col_table,
+                              nnz, block_rows, block_cols, batches, head_dim, scale, causal, key_padding_mask,
+                              kpm_batches, kpm_stride, static_cast<float2*>(stats),
+                              static_cast<uint32_t*>(workspace), static_cast<cudaStream_t>(stream));
+}

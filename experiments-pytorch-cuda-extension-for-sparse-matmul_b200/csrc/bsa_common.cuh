@@ -71,5 +71,7 @@ int matmul_tc(const MatmulArgs& args);
 // The same for the block-32 tcgen05 engine (fp16 / bf16, and fp32 as a 3xTF32 split).
 bool tc32_supports(const MatmulArgs& args);
 int matmul_tc32(const MatmulArgs& args);
+// fused attention kernels: supported dtype / head dim / block combinations
+bool attention_supports(int dtype, int64_t head_dim, int block);
 
 }  // namespace bsa

@@ -245,6 +245,68 @@ std::tuple<torch::Tensor, torch::Tensor> sparse_attention_forward(
     return {o.reshape(o_shape), lse.reshape(l_shape)};
 }
 
+// Gradients (dq, dk, dv) of sparse_attention_forward's output from the inputs, the output, its
+// gradient and the log-sum-exp the forward returned (fused backward kernels: the probability
+// blocks are recomputed on chip).
+std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> sparse_attention_backward(
+        torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor o, torch::Tensor dout, torch::Tensor lse,
+        torch::Tensor row_blocks, torch::Tensor row_table, torch::Tensor col_blocks, torch::Tensor col_table,
+        int64_t block, double scale, bool causal, c10::optional<torch::Tensor> key_padding_mask) {
+    TORCH_CHECK(q.is_cuda() && k.is_cuda() && v.is_cuda() && o.is_cuda() && dout.is_cuda() && lse.is_cuda(),
+                "all tensors must be CUDA tensors");
+    TORCH_CHECK(q.dim() >= 3 && k.dim() == q.dim() && v.dim() == q.dim(), "q, k, v must be [..., seq, head_dim]");
+    TORCH_CHECK(q.scalar_type() == k.scalar_type() && q.scalar_type() == v.scalar_type() &&
+                q.scalar_type() == o.scalar_type() && q.scalar_type() == dout.scalar_type(), "q, k, v, o, dout must share a dtype");
+    TORCH_CHECK(lse.scalar_type() == torch::kFloat, "lse must be float32");
+    check_layout({row_blocks, row_table}, q.device(), "row layout");
+    check_layout({col_blocks, col_table}, q.device(), "column layout");
+    const int dtype = dtype_code(q);
+    const int64_t nnz = row_blocks.size(0) / 2, block_rows = row_table.size(0) - 1, block_cols = col_table.size(0) - 1;
+    const int64_t d = q.size(-1);
+    TORCH_CHECK(col_blocks.size(0) == row_blocks.size(0), "row and column layout must describe the same blocks");
+    TORCH_CHECK(q.size(-2) == block_rows * block, "q has ", q.size(-2), " rows, the layout ", block_rows * block);
+    TORCH_CHECK(k.size(-2) == block_cols * block && v.size(-2) == block_cols * block,
+                "k and v must have ", block_cols * block, " rows");
+    TORCH_CHECK(k.size(-1) == d && v.size(-1) == d, "q, k, v must share the head dimension");
+    TORCH_CHECK(o.sizes() == q.sizes() && dout.sizes() == q.sizes(), "o and dout must have q's shape");
+    const auto q_shape = q.sizes().vec(), k_shape = k.sizes().vec();
+    q = q.flatten(0, -3).contiguous();
+    k = k.flatten(0, -3).contiguous();
+    v = v.flatten(0, -3).contiguous();
+    o = o.flatten(0, -3).contiguous();
+    dout = dout.flatten(0, -3).contiguous();
+    lse = lse.reshape({-1, q.size(1)}).contiguous();
+    TORCH_CHECK(k.size(0) == q.size(0) && v.size(0) == q.size(0) && lse.size(0) == q.size(0),
+                "q, k, v, lse must share the leading dimensions");
+    auto dq = torch::empty_like(q), dk = torch::empty_like(k), dv = torch::empty_like(v);
+    c10::cuda::CUDAGuard guard(q.device());
+    const uint8_t* kpm = nullptr;
+    int64_t kpm_batches = 0, kpm_stride = 0;
+    torch::Tensor mask;
+    if (key_padding_mask.has_value() && key_padding_mask->defined()) {
+        mask = key_padding_mask->to(q.device()).ne(0).to(torch::kUInt8).contiguous();
+        TORCH_CHECK(mask.dim() == 2, "key_padding_mask must be [batch, seq_k]");
+        TORCH_CHECK(q.size(0) % mask.size(0) == 0, "key_padding_mask batch does not divide the flattened batch");
+        kpm = mask.data_ptr<uint8_t>();
+        kpm_batches = mask.size(0);
+        kpm_stride = mask.size(1);
+    }
+    if (q.numel() > 0) {
+        torch::Tensor ws = workspace_for(q.device());
+        auto stats = torch::empty({q.size(0), q.size(1), 2}, q.options().dtype(torch::kFloat));
+        check_status(bsa_attention_backward(dtype, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), dout.data_ptr(),
+                                            lse.data_ptr<float>(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                            row_blocks.data_ptr<int>(), row_table.data_ptr<int>(),
+                                            col_blocks.data_ptr<int>(), col_table.data_ptr<int>(),
+                                            nnz, block_rows, block_cols, q.size(0), d, static_cast<int>(block),
+                                            static_cast<float>(scale), causal, kpm, kpm_batches, kpm_stride,
+                                            stats.data_ptr(), static_cast<size_t>(stats.numel()) * 4,
+                                            ws.data_ptr(), BSA_WORKSPACE_BYTES, at::cuda::getCurrentCUDAStream().stream()),
+                     "sparse_attention_backward");
+    }
+    return {dq.reshape(q_shape), dk.reshape(k_shape), dv.reshape(k_shape)};
+}
+
 // (row_blocks, row_table, col_blocks, col_table) of a 2-D pattern, built on
 // the pattern's CUDA device.  One host read-back (the block count) sizes the
 // descriptor tensors, like torch.nonzero in the reference (sparse/layout.py:8).
@@ -345,6 +407,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("q"), py::arg("k"), py::arg("v"), py::arg("row_blocks"), py::arg("row_table"), py::arg("block"),
           py::arg("block_cols"), py::arg("scale") = 1.0, py::arg("causal") = false,
           py::arg("key_padding_mask") = py::none());
+    m.def("sparse_attention_backward", &sparse_attention_backward,
+          "Fused block-sparse attention backward; returns (dq, dk, dv).",
+          py::arg("q"), py::arg("k"), py::arg("v"), py::arg("o"), py::arg("dout"), py::arg("lse"),
+          py::arg("row_blocks"), py::arg("row_table"), py::arg("col_blocks"), py::arg("col_table"), py::arg("block"),
+          py::arg("scale") = 1.0, py::arg("causal") = false, py::arg("key_padding_mask") = py::none());
     m.def("build_layout", &build_layout, "Build row / column layout metadata on the device.", py::arg("pattern"));
     m.def("dense_to_sparse", &dense_to_sparse, "Gather the layout's blocks from a dense matrix.");
     m.def("sparse_to_dense", &sparse_to_dense, "Scatter blocks into a zero-filled dense matrix.");

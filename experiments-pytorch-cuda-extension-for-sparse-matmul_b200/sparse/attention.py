@@ -13,13 +13,16 @@ positions of the blocks: a block-128 layout runs as the block-64 layout with
 every block split in 2 x 2 (the element-level masks do not depend on the
 block size).
 
-The backward pass of the fused path recomputes the probabilities with the
-unfused kernels (the forward keeps only the output and the row
-log-sum-exp), then follows the usual attention gradients:
+The backward pass of the fused path is fused as well: the forward keeps only
+the output and the row log-sum-exp, and two kernels (dQ by block rows; dK and
+dV by block columns) recompute the probabilities on chip:
 
-    P  = softmax(scale * sdd(Q, K^T))          dV = dsd(P^T, dO)
-    dP = sdd(dO, V^T)                          dS = softmax_backward(P, dP)
-    dQ = dsd(dS, K)                            dK = dsd(dS^T, Q)
+    P  = exp(scale * Q K^T - lse)              dV = P^T dO
+    dP = dO V^T                                dS = scale * P o (dP - rowsum(dO o O))
+    dQ = dS K                                  dK = dS^T Q
+
+``fused_backward = False`` selects the same gradients composed from the
+unfused kernels (sdd, softmax, softmax backward, dsd).
 """
 from typing import Any, Optional, Tuple
 
@@ -29,6 +32,9 @@ from . import kernel
 from .layout import SparseLayout
 from .matmul import matmul
 from .softmax import softmax
+
+
+fused_backward = True      # False: compose the backward of the fused forward from the unfused kernels
 
 
 def fused_supported(q: torch.Tensor, layout: SparseLayout) -> bool:
@@ -63,15 +69,20 @@ class SparseAttention(torch.autograd.Function):
                 scale: float = 1.0, causal: bool = False,
                 key_padding_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
         out, lse = _fused_forward(q, k, v, layout, scale, causal, key_padding_mask)
-        ctx.save_for_backward(q, k, v)
+        ctx.save_for_backward(q, k, v, out, lse)
         ctx.layout, ctx.scale, ctx.causal, ctx.kpm = layout, float(scale), bool(causal), key_padding_mask
-        ctx.lse = lse
         return out
 
     @staticmethod
     def backward(ctx: Any, dout: torch.Tensor) -> Tuple[Optional[torch.Tensor], ...]:
-        q, k, v = ctx.saved_tensors
+        q, k, v, out, lse = ctx.saved_tensors
         layout, ops = ctx.layout, kernel.sparse_ops
+        if fused_backward:
+            fine = _kernel_layout(layout)
+            dq, dk, dv = ops.sparse_attention_backward(
+                q, k, v, out, dout.contiguous(), lse, fine.row_layout[0], fine.row_layout[1],
+                fine.col_layout[0], fine.col_layout[1], 64, ctx.scale, ctx.causal, ctx.kpm)
+            return dq, dk, dv, None, None, None, None
         rows, cols, block = layout.row_layout, layout.col_layout, layout.block
         hint = getattr(layout, "max_row_blocks", 0)
         dout = dout.contiguous()

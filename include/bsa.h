@@ -187,6 +187,34 @@ int bsa_attention_forward(int dtype, const void* q, const void* k, const void* v
                           void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Fused block-sparse attention backward: dQ, dK, dV of bsa_attention_forward's
+ * output from q, k, v, o, the output gradient `dout` and the forward's `lse`;
+ * the probability and score-gradient blocks never reach memory.  The
+ * reference composes the same gradients from its matmul in sdd / dsd mode
+ * (sparse/matmul.py:30-50 over sparse/native/sparse_kernels.cc:7-50) and its
+ * softmax backward (sparse_softmax.cu:233-258).  Three launches: per-row
+ * statistics, dQ by block rows (ROW layout), dK and dV by block columns
+ * (COLUMN layout).
+ *
+ *   q, o, dout, dq  [batches, block_rows * block, head_dim]
+ *   k, v, dk, dv    [batches, block_cols * block, head_dim]
+ *   lse             float [batches, block_rows * block] as written by the forward
+ *   stats           scratch of at least batches * block_rows * block * 8 bytes,
+ *                   16-byte aligned (`stats_bytes` = its size)
+ *   masks, scale    as given to the forward
+ * Supported combinations and error codes as for bsa_attention_forward.
+ */
+int bsa_attention_backward(int dtype, const void* q, const void* k, const void* v, const void* o,
+                           const void* dout, const float* lse, void* dq, void* dk, void* dv,
+                           const int32_t* row_blocks, const int32_t* row_table,
+                           const int32_t* col_blocks, const int32_t* col_table,
+                           int64_t nnz, int64_t block_rows, int64_t block_cols, int64_t batches,
+                           int64_t head_dim, int block, float scale, int causal,
+                           const uint8_t* key_padding_mask, int64_t kpm_batches, int64_t kpm_stride,
+                           void* stats, size_t stats_bytes,
+                           void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Gather the blocks of a dense [batches, rows*block, cols*block] matrix into
  * sparse storage (to_sparse, sparse/layout.py:40-45) or scatter them back
  * with zeros elsewhere (to_dense, sparse/layout.py:47-57).  `blocks` is the

@@ -192,7 +192,7 @@ def attention_forward_dense(q, k, v, pattern, block: int, scale: float, causal: 
 
 
 def attention_step_dense(q, k, v, do, pattern, block: int, scale: float, causal: bool = False,
-                         dtype=torch.float32):
+                         dtype=torch.float32, key_padding_mask: Optional[torch.Tensor] = None):
     """Forward and backward of masked dense attention through torch autograd.
 
     Returns (out, dq, dk, dv); this is the CPU baseline computation: the same
@@ -201,11 +201,12 @@ def attention_step_dense(q, k, v, do, pattern, block: int, scale: float, causal:
     q = q.detach().cpu().to(dtype).requires_grad_(True)
     k = k.detach().cpu().to(dtype).requires_grad_(True)
     v = v.detach().cpu().to(dtype).requires_grad_(True)
-    keep = _score_mask(pattern, block, causal, None, q.shape[:-2])
+    keep = _score_mask(pattern, block, causal, key_padding_mask, q.shape[:-2])
     scores = (q @ k.transpose(-1, -2)) * scale
-    scores = scores.masked_fill(~keep, float("-inf"))
-    probs = torch.softmax(scores, dim=-1)
-    probs = torch.nan_to_num(probs, nan=0.0)
+    # rows without any unmasked score: probabilities (and all their gradients) are zero
+    dead = ~keep.any(dim=-1, keepdim=True)
+    scores = scores.masked_fill(~keep & ~dead, float("-inf"))
+    probs = torch.softmax(scores, dim=-1).masked_fill(dead, 0.0)
     out = probs @ v
     if do is None:
         return out.detach(), None, None, None

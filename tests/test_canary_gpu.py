@@ -2,7 +2,7 @@
 between two guard regions filled with a sentinel; after the call the guards must be untouched and
 the output must equal the one computed into a plain buffer.  Covers the three matmul engines (tcgen05
 block 64 and block 32, CUDA cores), every mode, the softmax forward / backward and the fused
-attention forward, on a layout with an empty block row and an empty block column."""
+attention forward and backward, on a layout with an empty block row and an empty block column."""
 import ctypes
 import os
 
@@ -31,6 +31,9 @@ def _library():
     lib.bsa_attention_forward.argtypes = [ctypes.c_int] + [ctypes.c_void_p] * 7 + [ctypes.c_int64] * 5 + \
         [ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
          ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
+    lib.bsa_attention_backward.argtypes = [ctypes.c_int] + [ctypes.c_void_p] * 13 + [ctypes.c_int64] * 5 + \
+        [ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
+         ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
     lib.bsa_workspace_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
     return lib
 
@@ -136,3 +139,24 @@ def test_softmax_and_attention_write_only_their_outputs(dtype):
     torch.cuda.synchronize()
     assert bool((lse.raw[:GUARD] == lse.sentinel).all()) and bool((lse.raw[-GUARD:] == lse.sentinel).all())
     assert lib.bsa_workspace_status(ws.data_ptr(), stream) == 0
+    # fused backward: three gradient outputs and the statistics scratch
+    do = torch.randn(z, pattern.shape[0] * block, d, device="cuda", generator=gen).half()
+    cblk, ctab = layout.col_layout
+    dq = Guarded((z, pattern.shape[0] * block, d), torch.float16)
+    dk = Guarded((z, pattern.shape[1] * block, d), torch.float16)
+    dv = Guarded((z, pattern.shape[1] * block, d), torch.float16)
+    stats = Guarded((z, pattern.shape[0] * block, 2), torch.float32)
+    st = lib.bsa_attention_backward(1, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.view.data_ptr(), do.data_ptr(),
+                                    lse.view.data_ptr(), dq.view.data_ptr(), dk.view.data_ptr(), dv.view.data_ptr(),
+                                    blk.data_ptr(), tab.data_ptr(), cblk.data_ptr(), ctab.data_ptr(),
+                                    nnz, pattern.shape[0], pattern.shape[1], z, d, block, 0.1, 0, None, 0, 0,
+                                    stats.view.data_ptr(), stats.view.numel() * 4, ws.data_ptr(), 256, stream)
+    assert st == 0, st
+    dq.check("attention backward dQ")
+    dk.check("attention backward dK")
+    dv.check("attention backward dV")
+    torch.cuda.synchronize()
+    assert bool((stats.raw[:GUARD] == stats.sentinel).all()) and bool((stats.raw[-GUARD:] == stats.sentinel).all())
+    assert lib.bsa_workspace_status(ws.data_ptr(), stream) == 0
+    got = sparse_ops.sparse_attention_backward(q, k, v, o.view, do, lse.view, blk, tab, cblk, ctab, block, 0.1, False, None)
+    assert torch.equal(dq.view, got[0]) and torch.equal(dk.view, got[1]) and torch.equal(dv.view, got[2])

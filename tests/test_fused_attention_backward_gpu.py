@@ -1,0 +1,106 @@
+"""GPU parity of the fused block-sparse attention backward kernels (dQ by block rows, dK and dV by
+block columns) against dense masked attention differentiated by torch autograd on the CPU.
+Tolerance: the 16-bit contract of the unfused operators (max |got - ref| / max |ref| <= 1e-2 for
+fp16, 3e-2 for bf16)."""
+import importlib
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_close, load_golden_layout, seeded
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _grads(pattern, batch, dim, dtype, scale, causal=False, kpm=None, seed=0, block=64):
+    """(dq, dk, dv) through sparse.attention (fused forward and backward) and through the oracle."""
+    from sparse import SparseLayout, attention
+    from sparse.kernel import sparse_ops
+    pattern = torch.as_tensor(np.asarray(pattern))
+    layout = SparseLayout(pattern, block=block)
+    seq_q, seq_k = pattern.shape[0] * block, pattern.shape[1] * block
+    q = seeded(tuple(batch) + (seq_q, dim), seed, dtype)
+    k = seeded(tuple(batch) + (seq_k, dim), seed + 1, dtype)
+    v = seeded(tuple(batch) + (seq_k, dim), seed + 2, dtype)
+    do = seeded(tuple(batch) + (seq_q, dim), seed + 3, dtype)
+    qg, kg, vg = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    out = attention(qg, kg, vg, layout, scale, causal, None if kpm is None else kpm.cuda())
+    out.backward(do.cuda())
+    torch.cuda.synchronize()
+    sparse_ops.check_device_status(0)
+    ref, dq, dk, dv = oracle.attention_step_dense(q, k, v, do, pattern.numpy(), block, scale, causal,
+                                                  key_padding_mask=kpm)
+    assert_close(out, ref, dtype, "output")
+    assert_close(qg.grad, dq, dtype, "dQ")
+    assert_close(kg.grad, dk, dtype, "dK")
+    assert_close(vg.grad, dv, dtype, "dV")
+    return qg.grad, kg.grad, vg.grad, pattern
+
+
+@pytest.mark.parametrize("dim", [64, 128])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_backward_strided_local(dim, dtype):
+    from sparse.patterns import strided_local
+    _grads(strided_local(16, 4, 1), (3,), dim, dtype, dim ** -0.5, seed=200)
+
+
+@pytest.mark.parametrize("dim", [64, 128])
+def test_backward_empty_rows_and_columns_nonsquare(dim):
+    """An empty block row gives zero dQ rows, an empty block column zero dK / dV rows."""
+    g = load_golden_layout("empty_row_col_5x4")
+    dq, dk, dv, pattern = _grads(g["pattern"], (3,), dim, torch.float16, 0.2, seed=210)
+    on = pattern != 0
+    for r in range(pattern.shape[0]):
+        if not bool(on[r].any()):
+            assert float(dq[:, r * 64:(r + 1) * 64].abs().max()) == 0.0
+    for c in range(pattern.shape[1]):
+        if not bool(on[:, c].any()):
+            assert float(dk[:, c * 64:(c + 1) * 64].abs().max()) == 0.0
+            assert float(dv[:, c * 64:(c + 1) * 64].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dim", [64, 128])
+def test_backward_causal_and_key_padding(dim):
+    """Element-level causal mask on diagonal blocks, padded keys, and query rows left without any
+    unmasked score (padding covers everything the causal mask leaves): their gradients are zero."""
+    from sparse.patterns import local_global_causal
+    kpm = torch.zeros(2, 512, dtype=torch.uint8)
+    kpm[0, 300:] = 1
+    kpm[1, :70] = 1            # rows 0 .. 69 of these batch entries see no key at all
+    _grads(local_global_causal(8, 2, 1), (2, 3), dim, torch.float16, dim ** -0.5, True, kpm, seed=220)
+    _grads(local_global_causal(8, 2, 1), (2,), dim, torch.bfloat16, dim ** -0.5, True, None, seed=221)
+
+
+def test_backward_many_items_per_cta():
+    """More work items than CTAs (8 heads x 64 block rows / columns), groups of 1 to 64 blocks."""
+    from sparse.patterns import bigbird
+    _grads(bigbird(64, 1, 2, 3, 77), (8,), 64, torch.float16, 0.125, seed=230)
+
+
+def test_backward_negative_scale():
+    from sparse.patterns import strided_local
+    _grads(strided_local(8, 4, 1), (2,), 64, torch.float16, -0.2, seed=240)
+
+
+@pytest.mark.parametrize("dim", [64, 128])
+def test_fused_backward_agrees_with_unfused_composition(dim):
+    """Fused and unfused backward of the same fused forward agree far inside the tolerance."""
+    from sparse import SparseLayout
+    from sparse.patterns import strided_local
+    module = importlib.import_module("sparse.attention")
+    layout = SparseLayout(strided_local(64, 8, 2), block=64)
+    q, k, v, do = (seeded((4, 4096, dim), 250 + i, torch.float16).cuda() for i in range(4))
+    grads = {}
+    try:
+        for fused in (True, False):
+            module.fused_backward = fused
+            qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
+            module.attention(qg, kg, vg, layout, dim ** -0.5).backward(do)
+            grads[fused] = (qg.grad, kg.grad, vg.grad)
+    finally:
+        module.fused_backward = True
+    for a, b, name in zip(grads[True], grads[False], ("dQ", "dK", "dV")):
+        err = float((a.float() - b.float()).abs().max() / b.float().abs().max())
+        assert err <= 4e-3, (name, err)

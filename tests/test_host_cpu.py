@@ -240,3 +240,32 @@ def test_head_sharding_is_world_size_independent(tmp_path):
         assert p.wait(timeout=180) == 0
     got = torch.load(out)
     assert torch.equal(got, expect)
+
+
+def test_attention_backward_validation_codes(lib):
+    f = lib.bsa_attention_backward
+    f.argtypes = [ctypes.c_int] + [ctypes.c_void_p] * 13 + [ctypes.c_int64] * 5 + \
+        [ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
+         ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
+
+    def call(dtype=1, q=16, dq=16, lse=16, col_blocks=16, nnz=1, rows=1, cols=1, batches=1, d=64, block=64,
+             kpm=None, kpm_batches=0, kpm_stride=0, stats=16, stats_bytes=512, ws=16, ws_bytes=256):
+        return f(dtype, q, 16, 16, 16, 16, lse, dq, 16, 16, 16, 16, col_blocks, 16, nnz, rows, cols, batches, d, block,
+                 1.0, 0, kpm, kpm_batches, kpm_stride, stats, stats_bytes, ws, ws_bytes, None)
+
+    # rejected on the host before any CUDA call (the pointers are fake)
+    assert call(dtype=9) == 3                      # BSA_ERR_BAD_DTYPE
+    assert call(dtype=0) == 3                      # fp32 has no fused kernel
+    assert call(block=48) == 5                     # BSA_ERR_BAD_BLOCK
+    assert call(block=32) == 4                     # BSA_ERR_BAD_SHAPE: only block 64 is fused
+    assert call(d=96) == 4
+    assert call(q=None) == 1                       # BSA_ERR_NULL_POINTER
+    assert call(lse=None) == 1
+    assert call(col_blocks=None) == 1
+    assert call(ws=None) == 7                      # BSA_ERR_WORKSPACE
+    assert call(stats=None) == 7
+    assert call(stats_bytes=511) == 7              # 1 batch x 64 rows x 8 bytes are needed
+    assert call(dq=24) == 6                        # BSA_ERR_ALIGNMENT
+    assert call(nnz=5) == 4
+    assert call(batches=70000, stats_bytes=1 << 40) == 10     # BSA_ERR_TOO_LARGE
+    assert call(kpm=16, kpm_batches=2, kpm_stride=64, batches=3, stats_bytes=4096) == 4

@@ -314,8 +314,19 @@ def run_ours(args):
         attention_lse(q, k, v, lay, scale)
     d1.record()
     torch.cuda.synchronize()
-    sparse_ops.check_device_status(local_rank)
     fused_ms = d0.elapsed_time(d1) / 10
+    # the fused backward (statistics, dQ by block rows, dK / dV by block columns) from the fused forward's output
+    o_f, lse_f = attention_lse(q, k, v, lay, scale)
+    rl_f, cl_f = lay.row_layout, lay.col_layout
+    for _ in range(3):
+        sparse_ops.sparse_attention_backward(q, k, v, o_f, do, lse_f, rl_f[0], rl_f[1], cl_f[0], cl_f[1], block, scale, False, None)
+    d0.record()
+    for _ in range(10):
+        sparse_ops.sparse_attention_backward(q, k, v, o_f, do, lse_f, rl_f[0], rl_f[1], cl_f[0], cl_f[1], block, scale, False, None)
+    d1.record()
+    torch.cuda.synchronize()
+    sparse_ops.check_device_status(local_rank)
+    fused_bwd_ms = d0.elapsed_time(d1) / 10
 
     # ---- max over ranks
     t = torch.tensor([elapsed_ms, e2e_ms], device=dev, dtype=torch.float64)
@@ -350,6 +361,16 @@ def run_ours(args):
                         "hbm_bytes": 4 * dense_bytes,
                         "note": "forward only, outside the timed step; Q, K, V read and O written once, "
                                 "scores and probabilities never leave the SM"}
+        fused_step_ms = fused_ms + fused_bwd_ms
+        fused_step_report = {"kernels": "attention_forward_kernel + attention_backward_kernel<rows> + <columns> (+ statistics)",
+                             "forward_ms": round(fused_ms, 4), "backward_ms": round(fused_bwd_ms, 4),
+                             "ms": round(fused_step_ms, 4),
+                             "TFLOP/s": round(6 * flops_matmul / (fused_step_ms * 1e-3) / 1e12, 1),
+                             "executed_TFLOP/s": round(9 * flops_matmul / (fused_step_ms * 1e-3) / 1e12, 1),
+                             "tensor_frac_executed": round(9 * flops_matmul / (fused_step_ms * 1e-3) / 1e12 / peaks["bf16_tflops"], 4),
+                             "unfused_step_ms": round(ms_per_step, 4), "speedup": round(ms_per_step / fused_step_ms, 2),
+                             "note": "same gradients as the timed step, outside it; TFLOP/s counts the step's 6 block "
+                                     "products, executed counts the 9 the fused kernels run (S and dP are recomputed)"}
         # dominant kernel = the kernel with the largest total time inside a step
         kernels = {
             "tc_matmul_kernel<dsd> (4 launches/step)": ["dsd_pv", "dsd_dv", "dsd_dq", "dsd_dk"],
@@ -388,7 +409,7 @@ def run_ours(args):
                     "ms_per_step": round(e2e_ms / e2e_steps, 4),
                     "h2d_bytes_per_step": 4 * dense_bytes, "d2h_bytes_per_step": 4 * dense_bytes},
             "gpu_launches": len(OPS) * args.steps,
-            "clocks": clocks, "ops": ops_report, "fused_forward": fused_report,
+            "clocks": clocks, "ops": ops_report, "fused_forward": fused_report, "fused_step": fused_step_report,
             "engine": os.environ.get("BSA_MATMUL_ENGINE", "auto"),
         }
         if cpu_dt is not None:

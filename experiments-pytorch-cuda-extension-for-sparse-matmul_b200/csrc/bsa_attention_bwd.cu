@@ -22,16 +22,26 @@
 // of 64 x 64 in 128-byte-swizzled shared memory, loaded by TMA); the same shared-memory tile of Y
 // serves as the K-major B operand of T and as the MN-major B operand of the accumulations.
 // One CTA per SM with all 512 TMEM columns: T1 | T2 double buffered (columns 0-255), accumulators
-// from column 256.  Warp roles (12 warps):
-//   warp 0     TMA producer: the item's X pair (double buffered) and every block's Y pair (ring)
-//   warp 1, 3  issuers of T1 and T2 (a thread issues one tcgen05.mma per ~100 cycles whatever its
-//              size, so the two products of a block are issued side by side)
-//   warp 2     issuer of the accumulations; its commit per block frees the Y stage and the
-//              operand tiles
-//   warps 4-11 two compute warpgroups taking alternate blocks: tcgen05.ld of T1 and T2 (16x256b
-//              shape: a lane owns 2 rows x 16 columns), exp2, the dS formula, masks, 32-bit
-//              stores into the swizzled operand tiles; the group that owns an item's last block
-//              converts and stores the accumulators while the other one goes on.
+// from column 256 (two sets where they fit, so that the next item accumulates while an item is
+// stored).  Warp roles (15 warps):
+//   warps 0-7   two compute warpgroups taking alternate blocks: tcgen05.ld of T1 and T2 (16x256b
+//               shape: a lane owns 2 rows x 16 columns), exp2, the dS formula, masks, 32-bit
+//               stores into the swizzled operand tiles (a ring of 2 or 4 buffers); the group that
+//               owns an item's last block converts and stores the accumulators while the other
+//               one goes on.
+//   warp 8      TMA producer: the item's X pair, every block's Y pair and, by columns, the 512
+//               bytes of (lse, D) of the block's query rows (ring of 4 or 8 stages)
+//   warps 9-12  issuers of T1 / T2 of the even / odd blocks (a thread issues one tcgen05.mma or
+//               commit per ~100 cycles whatever its size)
+//   warps 13-14 issuers of the accumulations: by columns one per output (dV, dK); by rows with
+//               head dim 64 the K-steps 0-1 / 2-3 of dQ into two partial accumulators that the
+//               epilogue adds; their commits per block free the Y stage and the operand tiles.
+// Measured at seq 4096, 12 blocks per row, head dim 64: about 1000 cycles per block and SM by
+// rows, 1300 by columns, whichever way the roles are cut (one or two issuers per product, 2 or 4
+// operand buffers, 4 or 8 stages, one or two accumulator sets: within 5 %).  A 64 x 64 x 16 MMA
+// reads 4 KB of operands from shared memory; the 12 (by rows) or 16 (by columns) of a block plus
+// the TMA and operand-tile writes move 72 / 96 KB per block through a 128 B / cycle port, i.e.
+// 560 / 750 cycles: the kernels sit at 55-60 % of that bound, like the forward kernel.
 // Loops are warp-uniform with an elected lane around the TMA / tcgen05 instructions.  All waits are
 // bounded (BSA_ERR_DEVICE_TIMEOUT in the workspace word).
 #include "bsa_tc_common.cuh"
@@ -39,20 +49,29 @@
 namespace bsa {
 namespace {
 
-constexpr int kBwdThreads = 12 * 32;
+// Optional role timing (compile with -DBSA_ATTN_TIMING): CTA 0 adds the cycles its roles spent in
+// each phase to 64-bit counters at byte offset 64 of the workspace (slot = counter index).
+#ifdef BSA_ATTN_TIMING
+#define BT_CLOCK() clock64()
+#define BT_ADD(slot, cycles) do { if (blockIdx.x == 0) atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 8 + (slot), (unsigned long long)(cycles)); } while (0)
+#else
+#define BT_CLOCK() 0ll
+#define BT_ADD(slot, cycles) do { } while (0)
+#endif
+
 constexpr int kBwdTmemCols = 512;
 constexpr int kBwdAccCol0 = 256;
-constexpr int kBwdRing = 4;                 // Y stages (a power of two)
-constexpr int kBwdRingShift = 2;
+constexpr int kBwdStatBytes = kTile * 8;      // (lse2, D) of the 64 query rows of a block
+constexpr int kBwdMaxRing = 8;              // Y stages: a power of two, chosen per launch (BwdParams::ring)
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct __align__(8) BwdBarriers {
     uint64_t x_full[2], x_empty[2];
-    uint64_t y_full[kBwdRing];
-    uint64_t out_done[kBwdRing];    // the accumulation MMAs of a block have retired: Y stage and operand tiles are free
+    uint64_t y_full[kBwdMaxRing];
+    uint64_t out_done[kBwdMaxRing];    // the accumulation MMAs of a block have retired: Y stage and operand tiles are free
     uint64_t t_full[2], t_empty[2];
-    uint64_t op_full[2];            // the operand tile(s) of a block are written
-    uint64_t o_full, o_empty;
+    uint64_t op_full[4];            // the operand tile(s) of a block are written
+    uint64_t o_full[2], o_empty[2];   // accumulator sets (one per item in flight)
     uint64_t drain;
     uint32_t tmem_base;
     int abort_flag;
@@ -67,6 +86,13 @@ struct BwdParams {
     int stride_z, stride_rem;
     int seq_q, seq_k, head_dim, dtiles;
     int xbufs;                 // X pairs in shared memory (1 or 2)
+    int opbufs, op_shift;      // operand tile buffers (2 or 4) and their log2: block s writes buffer s % opbufs once
+                               // the accumulation MMAs of block s - opbufs have retired
+    int parts;                 // partial accumulators per output (1 or 2), added up by the epilogue
+    int out_issuers;           // warps issuing the accumulations (1 or 2)
+    int obufs;                 // accumulator sets (1 or 2): with 2 the next item accumulates while an item is stored
+    int ring, ring_shift;      // Y stages and their log2: a block holds its stage from the TMA request until its
+                               // accumulation MMAs have retired, so the depth bounds the blocks in flight
     float scale, scale_log2;
     int causal;
     const uint8_t* kpm;
@@ -113,38 +139,46 @@ attention_backward_stats_kernel(const uint16_t* __restrict__ o, const uint16_t* 
     }
 }
 
+// Warp roles.  The compute warpgroups come first (a warp reads the TMEM sub-partition warp % 4).
+constexpr int kBwdProducerWarp = 8;
+constexpr int kBwdFirstTWarp = 9;           // 9: T1 of even blocks, 10: T1 odd, 11: T2 even, 12: T2 odd
+constexpr int kBwdFirstOutWarp = 13;        // 13: first accumulator, 14 (by columns): second accumulator
+template <bool COL> constexpr int bwd_warps() { return 15; }
+
 template <bool COL, bool BF16, bool MASKED>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+__global__ void __launch_bounds__(bwd_warps<COL>() * 32, 1)
 attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid_constant__ CUtensorMap map_x2,
                           const __grid_constant__ CUtensorMap map_y1, const __grid_constant__ CUtensorMap map_y2,
                           const BwdParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int kOpTiles = COL ? 2 : 1;                  // operand tiles per block
+    constexpr int kOuts = COL ? 2 : 1;                     // outputs (accumulators per set, without partials)
     const int set_bytes = p.dtiles * kTileBytes;            // one 64-row tile set of Q / K / V / dO
     uint8_t* x_smem = smem;                                 // [xbufs][2][set]
     uint8_t* y_smem = x_smem + p.xbufs * 2 * set_bytes;     // [ring][2][set]
-    uint8_t* op_smem = y_smem + kBwdRing * 2 * set_bytes;   // [2][kOpTiles] tiles
-    BwdBarriers* bars = reinterpret_cast<BwdBarriers*>(op_smem + 2 * kOpTiles * kTileBytes);
+    uint8_t* op_smem = y_smem + p.ring * 2 * set_bytes;     // [opbufs][kOpTiles] tiles
+    uint8_t* st_smem = op_smem + p.opbufs * kOpTiles * kTileBytes; // by columns: [ring] x 64 float2 (lse2, D) of the block's query rows
+    BwdBarriers* bars = reinterpret_cast<BwdBarriers*>(st_smem + (COL ? p.ring * kBwdStatBytes : 0));
     int* abort_flag = &bars->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    constexpr int ring_mask = kBwdRing - 1;
+    const int ring_mask = p.ring - 1;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&bars->x_full[s], 1); mbar_init(&bars->x_empty[s], 2);
+            mbar_init(&bars->x_full[s], 1); mbar_init(&bars->x_empty[s], 4);
             mbar_init(&bars->t_full[s], 2); mbar_init(&bars->t_empty[s], 4);
-            mbar_init(&bars->op_full[s], 4);
         }
-        for (int s = 0; s < kBwdRing; ++s) { mbar_init(&bars->y_full[s], 1); mbar_init(&bars->out_done[s], 1); }
-        mbar_init(&bars->o_full, 1); mbar_init(&bars->o_empty, 4);
-        mbar_init(&bars->drain, 3);
+        for (int s = 0; s < 4; ++s) mbar_init(&bars->op_full[s], 4);
+        for (int s = 0; s < kBwdMaxRing; ++s) { mbar_init(&bars->y_full[s], 1); mbar_init(&bars->out_done[s], (uint32_t)p.out_issuers); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&bars->o_full[s], (uint32_t)p.out_issuers); mbar_init(&bars->o_empty[s], 4); }
+        mbar_init(&bars->drain, (uint32_t)(4 + p.out_issuers));
         bars->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_shared();
     }
-    if (warp == 1) {
+    if (warp == kBwdProducerWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(smem_u32(&bars->tmem_base)), "r"((uint32_t)kBwdTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -154,7 +188,7 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
     tc_fence_after();
     const uint32_t tmem_base = *(volatile uint32_t*)&bars->tmem_base;
 
-    if (warp == 0) {
+    if (warp == kBwdProducerWarp) {
         // ------------------------------------------------------------ TMA producer
         int y_no = 0, x_no = 0;
         bool ok = true;
@@ -184,15 +218,20 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                     const BlockDesc d = win.get(p.blocks, cur.first, cur.count, j, lane);
                     const int other = COL ? d.row() : d.col();
                     const int stage = y_no & ring_mask;
-                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->out_done[stage], ((uint32_t)(y_no >> kBwdRingShift) & 1u) ^ 1u,
+                    const long long tp0 = BT_CLOCK();
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->out_done[stage], ((uint32_t)(y_no >> p.ring_shift) & 1u) ^ 1u,
                                                            abort_flag, p.status)) != 0;
+                    if (lane == 0) BT_ADD(0, BT_CLOCK() - tp0);
                     if (ok && elect_one()) {
                         uint64_t* full = &bars->y_full[stage];
-                        mbar_expect_tx(full, (uint32_t)(2 * set_bytes));
+                        mbar_expect_tx(full, (uint32_t)(2 * set_bytes + (COL ? kBwdStatBytes : 0)));
                         for (int t = 0; t < p.dtiles; ++t) {
                             tma_load_3d(y_smem + (stage * 2 + 0) * set_bytes + t * kTileBytes, &map_y1, full, t * kTile, other * kTile, cur.z);
                             tma_load_3d(y_smem + (stage * 2 + 1) * set_bytes + t * kTileBytes, &map_y2, full, t * kTile, other * kTile, cur.z);
                         }
+                        if (COL)
+                            bulk_load_1d(st_smem + stage * kBwdStatBytes,
+                                         p.stats + (size_t)cur.z * p.seq_q + (size_t)other * kTile, kBwdStatBytes, full);
                     }
                     __syncwarp();
                 }
@@ -203,7 +242,7 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
         if (lane == 0 && *(volatile int*)abort_flag) {
             // Give copies that were issued a bounded chance to land before the CTA exits.
             const unsigned long long t0 = global_ns();
-            for (int s = 0; s < kBwdRing; ++s)
+            for (int s = 0; s < p.ring; ++s)
                 while (!mbar_try_wait(&bars->y_full[s], 0) && !mbar_try_wait(&bars->y_full[s], 1) &&
                        global_ns() - t0 < kWaitLimitNs / 4) {}
             for (int s = 0; s < p.xbufs; ++s)
@@ -211,9 +250,12 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                        global_ns() - t0 < kWaitLimitNs / 4) {}
         }
         __syncwarp();
-    } else if (warp == 1 || warp == 3) {
-        // ------------------------------------------------------------ issuers of T1 = X1 Y1^T (warp 1) and T2 = X2 Y2^T (warp 3)
-        const int which = warp == 1 ? 0 : 1;
+    } else if (warp >= kBwdFirstTWarp && warp < kBwdFirstOutWarp) {
+        // ------------------------------------------------------------ issuers of T1 = X1 Y1^T and T2 = X2 Y2^T
+        // Four warps: product `which` of the blocks with number s & 1 == par (T buffer par).  A thread
+        // issues one tcgen05.mma per ~100 cycles, so the 8 (head dim 64) MMAs + 2 commits of a block
+        // would otherwise cost one issuer 1000 cycles per block.
+        const int which = (warp - kBwdFirstTWarp) >> 1, par = (warp - kBwdFirstTWarp) & 1;
         int s_no = 0, x_no = 0;
         bool ok = true;
         Cursor cur;
@@ -226,13 +268,16 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                                                    abort_flag, p.status)) != 0;
             if (!ok) break;
             const int s_end = s_no + n;
-            for (int s = s_no; s < s_end; ++s) {
-                const int stage = s & ring_mask, tb = s & 1;
-                ok = __all_sync(0xffffffffu, mbar_wait(&bars->y_full[stage], (uint32_t)(s >> kBwdRingShift) & 1u, abort_flag, p.status)) != 0;
-                if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->t_empty[tb], ((uint32_t)(s >> 1) & 1u) ^ 1u, abort_flag, p.status)) != 0;
+            for (int s = s_no + ((par - s_no) & 1); s < s_end; s += 2) {
+                const int stage = s & ring_mask;
+                const long long ti0 = BT_CLOCK();
+                ok = __all_sync(0xffffffffu, mbar_wait(&bars->y_full[stage], (uint32_t)(s >> p.ring_shift) & 1u, abort_flag, p.status)) != 0;
+                const long long ti1 = BT_CLOCK();
+                if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->t_empty[par], ((uint32_t)(s >> 1) & 1u) ^ 1u, abort_flag, p.status)) != 0;
                 if (!ok) break;
+                const long long ti2 = BT_CLOCK();
                 tc_fence_after();
-                const uint32_t d = tmem_base + (uint32_t)(tb * 2 * kTile + which * kTile);
+                const uint32_t d = tmem_base + (uint32_t)(par * 2 * kTile + which * kTile);
                 if (elect_one()) {
                     for (int t = 0; t < p.dtiles; ++t) {
                         const uint64_t da = make_tile_desc(smem_u32(x_smem + (xb * 2 + which) * set_bytes + t * kTileBytes), false);
@@ -241,12 +286,13 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                         for (int kk = 0; kk < kTile / 16; ++kk)
                             tc_mma_f16(d, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), p.idesc_t, (t > 0 || kk > 0) ? 1u : 0u);
                     }
-                    tc_commit(&bars->t_full[tb]);
+                    tc_commit(&bars->t_full[par]);
                 }
                 __syncwarp();
+                if (warp == kBwdFirstTWarp && lane == 0) { BT_ADD(1, ti1 - ti0); BT_ADD(2, ti2 - ti1); BT_ADD(3, BT_CLOCK() - ti2); }
             }
             if (!ok) break;
-            if (elect_one()) tc_commit(&bars->x_empty[xb]);       // this issuer's last read of the X pair has been issued
+            if (elect_one()) tc_commit(&bars->x_empty[xb]);       // this issuer's reads of the X pair have been issued
             __syncwarp();
             s_no = s_end;
             ++x_no;
@@ -257,57 +303,63 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
             mbar_wait(&bars->drain, 0, abort_flag, p.status);
         }
         __syncwarp();
-    } else if (warp == 2) {
-        // ------------------------------------------------------------ issuer of the accumulations
-        int s_no = 0, o_no = 0;
-        bool ok = true;
-        Cursor cur;
-        cur.init(p);
-        for (; ok && cur.valid(); cur.advance()) {
-            const int n = cur.count;
-            if (n == 0) continue;
-            for (int j = 0; ok && j < n; ++j) {
-                const int s = s_no + j, stage = s & ring_mask, ob = s & 1;
-                if (j == 0) ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_empty, (uint32_t)(o_no & 1) ^ 1u, abort_flag, p.status)) != 0;
-                if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->y_full[stage], (uint32_t)(s >> kBwdRingShift) & 1u, abort_flag, p.status)) != 0;
-                if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->op_full[ob], (uint32_t)(s >> 1) & 1u, abort_flag, p.status)) != 0;
-                if (!ok) break;
-                tc_fence_after();
-                if (elect_one()) {
-                    // A = operand tile (K-major), B = a Y tile set with N = head_dim contiguous
-                    const uint64_t a0 = make_tile_desc(smem_u32(op_smem + (ob * kOpTiles) * kTileBytes), false);
-                    const uint64_t y1 = make_tile_desc(smem_u32(y_smem + (stage * 2 + 0) * set_bytes), true);
-                    const uint64_t y2 = make_tile_desc(smem_u32(y_smem + (stage * 2 + 1) * set_bytes), true);
-                    const uint32_t d0 = tmem_base + (uint32_t)kBwdAccCol0;
-#pragma unroll
-                    for (int kk = 0; kk < kTile / 16; ++kk)
-                        tc_mma_f16(d0, a0 + (uint64_t)(kk * 2), (COL ? y2 : y1) + (uint64_t)(kk * (2048 >> 4)), p.idesc_acc,
-                                   (j > 0 || kk > 0) ? 1u : 0u);
-                    if (COL) {
-                        const uint64_t a1 = make_tile_desc(smem_u32(op_smem + (ob * kOpTiles + 1) * kTileBytes), false);
-                        const uint32_t d1 = d0 + (uint32_t)p.head_dim;
-#pragma unroll
-                        for (int kk = 0; kk < kTile / 16; ++kk)
-                            tc_mma_f16(d1, a1 + (uint64_t)(kk * 2), y1 + (uint64_t)(kk * (2048 >> 4)), p.idesc_acc,
-                                       (j > 0 || kk > 0) ? 1u : 0u);
+    } else if (warp >= kBwdFirstOutWarp) {
+        // ------------------------------------------------------------ issuers of the accumulations
+        // By columns: warp 13 dV += P^T Y2, warp 14 dK += dS^T Y1.  By rows: dQ += dS Y1; with two partial
+        // accumulators warp 13 issues K-steps 0, 1 into the first and warp 14 K-steps 2, 3 into the second
+        // (4 MMAs and up to 2 commits per block cost one thread 400-500 cycles).  Accumulator set o_no % obufs.
+        const int w = warp - kBwdFirstOutWarp;
+        if (w < p.out_issuers) {
+            const int kk0 = (!COL && p.out_issuers == 2) ? 2 * w : 0;          // this issuer's K-steps
+            const int kk1 = (!COL && p.out_issuers == 2) ? 2 * w + 2 : kTile / 16;
+            int s_no = 0, o_no = 0;
+            bool ok = true;
+            Cursor cur;
+            cur.init(p);
+            for (; ok && cur.valid(); cur.advance()) {
+                const int n = cur.count;
+                if (n == 0) continue;
+                const int ob_acc = o_no & (p.obufs - 1);
+                const uint32_t o_par = (uint32_t)(p.obufs == 2 ? o_no >> 1 : o_no) & 1u;
+                // accumulator of this issuer: set, then output (by columns) or partial (by rows)
+                const uint32_t d = tmem_base + (uint32_t)(kBwdAccCol0 + ((ob_acc * kOuts + (COL ? w : 0)) * p.parts + (COL ? 0 : (kk0 >> 1) & (p.parts - 1))) * p.head_dim);
+                for (int j = 0; ok && j < n; ++j) {
+                    const int s = s_no + j, stage = s & ring_mask, ob = s & (p.opbufs - 1);
+                    const long long to0 = BT_CLOCK();
+                    if (j == 0) ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_empty[ob_acc], o_par ^ 1u, abort_flag, p.status)) != 0;
+                    const long long to1 = BT_CLOCK();
+                    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->y_full[stage], (uint32_t)(s >> p.ring_shift) & 1u, abort_flag, p.status)) != 0;
+                    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->op_full[ob], (uint32_t)(s >> p.op_shift) & 1u, abort_flag, p.status)) != 0;
+                    if (!ok) break;
+                    const long long to2 = BT_CLOCK();
+                    tc_fence_after();
+                    if (elect_one()) {
+                        // A = operand tile (K-major), B = a Y tile set with N = head_dim contiguous
+                        const uint64_t a = make_tile_desc(smem_u32(op_smem + (ob * kOpTiles + (COL ? w : 0)) * kTileBytes), false);
+                        const int ysel = COL ? 1 - w : 0;             // dV reads Y2 (dO), dK and dQ read Y1
+                        const uint64_t b = make_tile_desc(smem_u32(y_smem + (stage * 2 + ysel) * set_bytes), true);
+                        for (int kk = kk0; kk < kk1; ++kk)
+                            tc_mma_f16(d, a + (uint64_t)(kk * 2), b + (uint64_t)(kk * (2048 >> 4)), p.idesc_acc,
+                                       (j > 0 || kk > kk0) ? 1u : 0u);
+                        tc_commit(&bars->out_done[stage]);
+                        if (j == n - 1) tc_commit(&bars->o_full[ob_acc]);
                     }
-                    tc_commit(&bars->out_done[stage]);
-                    if (j == n - 1) tc_commit(&bars->o_full);
+                    __syncwarp();
+                    if (w == 0 && lane == 0) { BT_ADD(4, to1 - to0); BT_ADD(5, to2 - to1); BT_ADD(6, BT_CLOCK() - to2); }
                 }
-                __syncwarp();
+                s_no += n;
+                ++o_no;
             }
-            s_no += n;
-            ++o_no;
-        }
-        if (elect_one()) {
-            tc_commit(&bars->drain);
-            mbar_wait(&bars->drain, 0, abort_flag, p.status);
+            if (elect_one()) {
+                tc_commit(&bars->drain);
+                mbar_wait(&bars->drain, 0, abort_flag, p.status);
+            }
         }
         __syncwarp();
     } else {
         // ------------------------------------------------------------ compute warpgroups
         // Group g takes the blocks with number s & 1 == g (T buffer g, operand buffer g).
-        const int wg = (warp - 4) >> 2;
+        const int wg = warp >> 2;
         const int quad = warp & 3;                  // TMEM sub-partition this warp may read
         const int q4 = lane & 3;                    // position in the quad: columns 8u + 2 * q4 + {0, 1}
         const int row_a = quad * 16 + (lane >> 2);  // this lane's two rows of the 64-row tile: row_a, row_a + 8
@@ -317,6 +369,7 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
         const int out_rows = COL ? p.seq_k : p.seq_q;
         int s_no = 0, o_no = 0;
         bool ok = true;
+        const long long t_begin = BT_CLOCK();
         Cursor cur;
         cur.init(p);
         BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
@@ -352,40 +405,42 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                 win.begin(p.blocks, cur.first, cur.count, pre, lane);
                 const uint32_t op_row = (uint32_t)(row_a * 128 + 4 * q4), op_xor = (uint32_t)(row_a & 7);
                 const int t_first = (wg - s_no) & 1;            // this group's first block of the item
-                // by columns: statistics of the block's 16 query columns of this lane, loaded a block ahead:
-                // cs[u] = (lse2, D) of column 8u + 2 q4 and of column 8u + 2 q4 + 1
-                float4 cs_next[8];
-                auto load_col_stats = [&](int block_row) {
-                    const float4* src = reinterpret_cast<const float4*>(stats_z + (size_t)block_row * kTile + 2 * q4);
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) cs_next[u] = src[4 * u];       // 8 columns = 4 float4 apart
-                };
-                if (COL && t_first < n) load_col_stats(win.get(p.blocks, cur.first, cur.count, t_first, lane).row());
                 for (int t = t_first; ok && t < n; t += 2) {
                     const int s = s_no + t, tb = s & 1;
                     const BlockDesc d = win.get(p.blocks, cur.first, cur.count, t, lane);
                     const int other = COL ? d.row() : d.col();
-                    float4 cs[8];
-                    if (COL) {
-#pragma unroll
-                        for (int u = 0; u < 8; ++u) cs[u] = cs_next[u];
-                        if (t + 2 < n) load_col_stats(win.get(p.blocks, cur.first, cur.count, t + 2, lane).row());
-                    }
+                    const long long tc0 = BT_CLOCK();
                     ok = __all_sync(0xffffffffu, mbar_wait(&bars->t_full[tb], (uint32_t)(s >> 1) & 1u, abort_flag, p.status)) != 0;
                     if (!ok) break;
+                    const long long tc1 = BT_CLOCK();
                     tc_fence_after();
                     uint32_t r1[32], r2[32];
                     tc_ld_16x256b_x8(tmem_base + lane_field + (uint32_t)(tb * 2 * kTile), r1);
                     tc_ld_16x256b_x8(tmem_base + lane_field + (uint32_t)(tb * 2 * kTile + kTile), r2);
+                    // by columns: (lse2, D) of this lane's 16 query columns, brought into the block's stage by
+                    // the producer: cs[u] = those of column 8u + 2 q4 and of column 8u + 2 q4 + 1
+                    float4 cs[8];
+                    if (COL) {
+                        const int stage = s & ring_mask;
+                        ok = __all_sync(0xffffffffu, mbar_wait(&bars->y_full[stage], (uint32_t)(s >> p.ring_shift) & 1u, abort_flag, p.status)) != 0;
+                        if (!ok) break;
+                        const float4* src = reinterpret_cast<const float4*>(st_smem + stage * kBwdStatBytes) + q4;
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) cs[u] = src[4 * u];        // 8 columns = 4 float4 apart
+                    }
                     tc_wait_ld();
                     release_accumulator(&bars->t_empty[tb], lane);
-                    // the operand tiles of this buffer must have been read by the MMAs of block s - 2
-                    if (s >= 2) {
-                        ok = __all_sync(0xffffffffu, mbar_wait(&bars->out_done[(s - 2) & ring_mask],
-                                                               (uint32_t)((s - 2) >> kBwdRingShift) & 1u, abort_flag, p.status)) != 0;
+                    const long long tc2 = BT_CLOCK();
+                    // the operand tiles of this buffer must have been read by the MMAs of block s - opbufs
+                    const int ob = s & (p.opbufs - 1);
+                    if (s >= p.opbufs) {
+                        const int sp = s - p.opbufs;
+                        ok = __all_sync(0xffffffffu, mbar_wait(&bars->out_done[sp & ring_mask],
+                                                               (uint32_t)(sp >> p.ring_shift) & 1u, abort_flag, p.status)) != 0;
                         if (!ok) break;
                     }
-                    const uint32_t tile0 = smem_u32(op_smem + (tb * kOpTiles) * kTileBytes) + op_row;
+                    const long long tc3 = BT_CLOCK();
+                    const uint32_t tile0 = smem_u32(op_smem + (ob * kOpTiles) * kTileBytes) + op_row;
                     const int other0 = other * kTile + 2 * q4;          // position of column u = 0, e = 0
 #pragma unroll
                     for (int u = 0; u < 8; ++u) {
@@ -431,27 +486,43 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                             asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + 8 * 128), "r"(pack2<BF16>(db[0], db[1])) : "memory");
                         }
                     }
+                    const long long tc4 = BT_CLOCK();
                     fence_async_shared();           // generic-proxy writes -> visible to the tensor core's reads
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&bars->op_full[tb]);
+                    if (lane == 0) mbar_arrive(&bars->op_full[ob]);
+                    if (warp == 0 && lane == 0) { BT_ADD(7, tc1 - tc0); BT_ADD(8, tc2 - tc1); BT_ADD(9, tc3 - tc2); BT_ADD(10, tc4 - tc3); BT_ADD(11, BT_CLOCK() - tc4); BT_ADD(12, 1); }
+                    if (warp == 4 && lane == 0) { BT_ADD(17, tc1 - tc0); BT_ADD(18, tc3 - tc2); }
                 }
                 s_no += n;
                 if (!ok) break;
-                // The group that owns the item's last block stores the accumulators; the other one
-                // owns the next item's first block and goes on right away.
+                // The group that owns the item's last block stores the accumulators; the other one owns
+                // the next item's first block and goes on right away.  (Taking turns by item was measured
+                // 3 % slower.)
                 if (wg == ((s_no - 1) & 1)) {
-                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full, (uint32_t)(o_no & 1), abort_flag, p.status)) != 0;
+                    const int ob_acc = o_no & (p.obufs - 1);
+                    const long long te0 = BT_CLOCK();
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[ob_acc], (uint32_t)(p.obufs == 2 ? o_no >> 1 : o_no) & 1u,
+                                                           abort_flag, p.status)) != 0;
                     if (!ok) break;
+                    const long long te1 = BT_CLOCK();
+                    if ((warp & 3) == 0 && lane == 0) BT_ADD(13 + 2 * wg, te1 - te0);
                     tc_fence_after();
-                    constexpr int kOuts = COL ? 2 : 1;
 #pragma unroll
                     for (int a = 0; a < kOuts; ++a) {
                         uint16_t* out = a == 0 ? p.out0 : p.out1;
                         for (int c = 0; c < p.head_dim; c += 32) {
                             uint32_t r0[16];
-                            tc_ld_16x256b_x4(tmem_base + lane_field + (uint32_t)(kBwdAccCol0 + a * p.head_dim + c), r0);
+                            const uint32_t acc0 = tmem_base + lane_field + (uint32_t)(kBwdAccCol0 + (ob_acc * kOuts + a) * p.parts * p.head_dim + c);
+                            tc_ld_16x256b_x4(acc0, r0);
                             tc_wait_ld();
-                            if (a == kOuts - 1 && c + 32 >= p.head_dim) release_accumulator(&bars->o_empty, lane);
+                            for (int q = 1; q < p.parts; ++q) {          // add the other partial accumulators
+                                uint32_t rq[16];
+                                tc_ld_16x256b_x4(acc0 + (uint32_t)(q * p.head_dim), rq);
+                                tc_wait_ld();
+#pragma unroll
+                                for (int i = 0; i < 16; ++i) r0[i] = __float_as_uint(__uint_as_float(r0[i]) + __uint_as_float(rq[i]));
+                            }
+                            if (a == kOuts - 1 && c + 32 >= p.head_dim) release_accumulator(&bars->o_empty[ob_acc], lane);
                             uint32_t ta[4], tb2[4];
 #pragma unroll
                             for (int u = 0; u < 4; ++u) {
@@ -464,18 +535,20 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                             *reinterpret_cast<uint4*>(out + out_b + c + 8 * q4) = make_uint4(tb2[0], tb2[1], tb2[2], tb2[3]);
                         }
                     }
+                    if ((warp & 3) == 0 && lane == 0) BT_ADD(19 + wg, BT_CLOCK() - te1);
                 }
                 ++o_no;
             }
             pre = pre_next;
             cur.advance();
         }
+        if (warp == 0 && lane == 0) BT_ADD(14, BT_CLOCK() - t_begin);
     }
 
     // ---------------------------------------------------------------- teardown
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == kBwdProducerWarp) {
         __syncwarp();
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kBwdTmemCols)
@@ -495,9 +568,23 @@ int launch_backward(int dtype, bool masked, const CUtensorMap& x1, const CUtenso
     KernelFn kernel;
     if (dtype == BSA_DTYPE_BF16) kernel = masked ? attention_backward_kernel<COL, true, true> : attention_backward_kernel<COL, true, false>;
     else                         kernel = masked ? attention_backward_kernel<COL, false, true> : attention_backward_kernel<COL, false, false>;
-    // by columns with head dim 128 the two accumulators and four operand tiles leave room for one X pair only
-    p.xbufs = (COL && p.dtiles == 2) ? 1 : 2;
-    int smem_bytes = 1024 + ((p.xbufs * 2 + kBwdRing * 2) * p.dtiles + 2 * (COL ? 2 : 1)) * kTileBytes + (int)sizeof(BwdBarriers);
+    // Shared memory (227 KB): head dim 64: two X pairs (32 KB), 8 (by rows) or 4 (by columns) Y stages of
+    // 16 KB, 4 operand buffers of 8 / 16 KB; head dim 128: one X pair (32 KB), 4 Y stages of 32 KB,
+    // 4 operand buffers of 8 KB by rows, 2 of 16 KB by columns.
+    p.xbufs = p.dtiles == 1 ? 2 : 1;
+    p.ring = (p.dtiles == 1 && !COL) ? 8 : 4;
+    p.ring_shift = p.ring == 8 ? 3 : 2;
+    // The 256 TMEM columns beside the T buffers: two accumulator sets where they fit (the next item
+    // accumulates while an item is stored); by rows with head dim 64 also two partial accumulators fed
+    // by two issuers.  (Partial accumulators fed by one issuer were measured to gain nothing: chained
+    // MMAs into one accumulator are not what bounds the kernel.)
+    p.obufs = (COL && p.dtiles == 2) ? 1 : 2;
+    p.parts = (!COL && p.dtiles == 1) ? 2 : 1;
+    p.out_issuers = COL ? 2 : p.parts;
+    p.opbufs = (COL && p.dtiles == 2) ? 2 : 4;
+    p.op_shift = p.opbufs == 4 ? 2 : 1;
+    int smem_bytes = 1024 + ((p.xbufs * 2 + p.ring * 2) * p.dtiles + p.opbufs * (COL ? 2 : 1)) * kTileBytes +
+                     (COL ? p.ring * kBwdStatBytes : 0) + (int)sizeof(BwdBarriers);
     // more than half of an SM's shared memory: the CTA allocates all 512 TMEM columns and must be alone
     if (smem_bytes < 116 * 1024) smem_bytes = 116 * 1024;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) {
@@ -509,7 +596,7 @@ int launch_backward(int dtype, bool masked, const CUtensorMap& x1, const CUtenso
     const unsigned grid = (unsigned)(p.items < sms ? p.items : sms);
     p.stride_z = (int)grid / p.groups;
     p.stride_rem = (int)grid % p.groups;
-    kernel<<<grid, kBwdThreads, smem_bytes, stream>>>(x1, x2, y1, y2, p);
+    kernel<<<grid, bwd_warps<COL>() * 32, smem_bytes, stream>>>(x1, x2, y1, y2, p);
     return launch_status();
 }
 
@@ -577,8 +664,14 @@ int attention_backward(int dtype, const void* q, const void* k, const void* v, c
     p.items = (int)(batches * block_rows);
     p.out0 = static_cast<uint16_t*>(dq);
     p.out1 = nullptr;
-    int st = launch_backward<false>(dtype, masked, map_q, map_do, map_k, map_v, p, stream);
+    int st = BSA_OK;
+#if !defined(BSA_BWD_ONLY) || BSA_BWD_ONLY == 0      // (timing builds run one of the two kernels)
+    st = launch_backward<false>(dtype, masked, map_q, map_do, map_k, map_v, p, stream);
     if (st != BSA_OK) return st;
+#endif
+#if defined(BSA_BWD_ONLY) && BSA_BWD_ONLY == 0
+    return st;
+#endif
     // dV, dK by columns: X = (K_c, V_c), Y = (Q_r, dO_r)
     p.blocks = reinterpret_cast<const BlockDesc*>(col_blocks);
     p.table = col_table;

@@ -55,8 +55,6 @@ namespace {
 #define AT_ADD(slot, cycles) do { } while (0)
 #endif
 
-constexpr int kAttnWarps = 8;
-constexpr int kAttnThreads = kAttnWarps * 32;
 constexpr int kAttnTmemCols = 256;      // O: columns 0 .. head_dim - 1; S buffers: 128 .. 191, 192 .. 255
 constexpr int kSCol0 = 128;
 constexpr int kMaxRing = 4;
@@ -151,7 +149,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         int kv_no = 0, q_no = 0;                   // blocks (K or V tile sets) and Q tile sets loaded so far
         bool q_prefetched = false;                 // the current item's Q tile set was requested an item ago
         bool ok = true;
-        const long long tp_begin = AT_CLOCK();
+        [[maybe_unused]] const long long tp_begin = AT_CLOCK();
         Cursor cur;
         cur.init(p);
         BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
@@ -177,7 +175,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     return true;
                 };
                 if (!is_v && !q_prefetched) {
-                    const long long tq = AT_CLOCK();
+                    [[maybe_unused]] const long long tq = AT_CLOCK();
                     ok = issue_q(q_no, cur.z, cur.g);
                     if (lane == 0) AT_ADD(0, AT_CLOCK() - tq);
                 }
@@ -194,7 +192,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     uint64_t* full = is_v ? &bars->v_full[stage] : &bars->k_full[stage];
                     uint8_t* dst = (is_v ? v_smem : k_smem) + stage * set_bytes;
                     const CUtensorMap* map = is_v ? &map_v : &map_k;
-                    const long long t0 = AT_CLOCK();
+                    [[maybe_unused]] const long long t0 = AT_CLOCK();
                     ok = __all_sync(0xffffffffu, mbar_wait(reuse, parity, abort_flag, p.status)) != 0;
                     if (lane == 0) AT_ADD(is_v ? 2 : 1, AT_CLOCK() - t0);
                     if (ok && elect_one()) {
@@ -243,19 +241,19 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 const int n = cur.count;
                 if (n == 0) continue;               // empty row: the softmax warps write zeros on their own
                 const int qb = q_no & (p.qbufs - 1);
-                const long long tq0 = AT_CLOCK();
+                [[maybe_unused]] const long long tq0 = AT_CLOCK();
                 ok = __all_sync(0xffffffffu, mbar_wait(&bars->q_full[qb], (uint32_t)(p.qbufs == 2 ? q_no >> 1 : q_no) & 1u, abort_flag, p.status)) != 0;
                 AT_ADD(21, AT_CLOCK() - tq0);
                 if (!ok) break;
                 const int s_end = s_no + n;
                 for (int s = s_no; s < s_end; ++s) {
                     const int ks = s & ring_mask, sb = s & 1;
-                    const long long t0 = AT_CLOCK();
+                    [[maybe_unused]] const long long t0 = AT_CLOCK();
                     ok = __all_sync(0xffffffffu, mbar_wait(&bars->k_full[ks], (uint32_t)(s >> p.ring_shift) & 1u, abort_flag, p.status)) != 0;
-                    const long long t1 = AT_CLOCK();
+                    [[maybe_unused]] const long long t1 = AT_CLOCK();
                     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_empty[sb], ((uint32_t)(s >> 1) & 1u) ^ 1u, abort_flag, p.status)) != 0;
                     if (!ok) break;
-                    const long long t2 = AT_CLOCK();
+                    [[maybe_unused]] const long long t2 = AT_CLOCK();
                     tc_fence_after();
                     const uint32_t d = tmem_base + (uint32_t)(kSCol0 + sb * kTile);
                     if (elect_one()) {
@@ -298,14 +296,14 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 if (n == 0) continue;
                 for (int j = 0; ok && j < n; ++j, ++p_no) {
                     const int pb = p_no & 1, vs = p_no & vring_mask;
-                    const long long t0 = AT_CLOCK();
+                    [[maybe_unused]] const long long t0 = AT_CLOCK();
                     if (j == 0) ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_empty, (uint32_t)(o_no & 1) ^ 1u, abort_flag, p.status)) != 0;
-                    const long long t1 = AT_CLOCK();
+                    [[maybe_unused]] const long long t1 = AT_CLOCK();
                     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->v_full[vs], (uint32_t)(p_no >> p.vring_shift) & 1u, abort_flag, p.status)) != 0;
-                    const long long t2 = AT_CLOCK();
+                    [[maybe_unused]] const long long t2 = AT_CLOCK();
                     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->p_full[pb], (uint32_t)(p_no >> 1) & 1u, abort_flag, p.status)) != 0;
                     if (!ok) break;
-                    const long long t3 = AT_CLOCK();
+                    [[maybe_unused]] const long long t3 = AT_CLOCK();
                     tc_fence_after();
                     // O += P_j V_{c_j}: A = P (K-major), B = V tiles (N contiguous), N = head_dim
                     const uint64_t da = make_tile_desc(smem_u32(p_smem + pb * kTileBytes), false);
@@ -347,7 +345,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         int s_no = 0, o_no = 0;                     // S tiles and non-empty items before the current item
         int x_no[2] = {0, 0};                       // hand-overs so far in which group 0 / group 1 was the writer
         bool ok = true;
-        const long long t_begin = AT_CLOCK();
+        [[maybe_unused]] const long long t_begin = AT_CLOCK();
         Cursor cur;
         cur.init(p);
         BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
@@ -410,7 +408,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 const int t_first = WGS == 2 ? ((wg - s_no) & 1) : 0;     // this group's first tile of the item
                 auto load = [&](uint32_t (&r)[32], int t) -> bool {       // wait for S tile t, start loading it
                     const int s = s_no + t;
-                    const long long t0 = AT_CLOCK();
+                    [[maybe_unused]] const long long t0 = AT_CLOCK();
                     if (!__all_sync(0xffffffffu, mbar_wait(&bars->qk_done[s & ring_mask], (uint32_t)(s >> p.ring_shift) & 1u,
                                                            abort_flag, p.status)))
                         return false;
@@ -420,7 +418,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     return true;
                 };
                 auto loaded = [&](int t) {                                 // tile t is in registers: free its buffer
-                    const long long t0 = AT_CLOCK();
+                    [[maybe_unused]] const long long t0 = AT_CLOCK();
                     tc_wait_ld();
                     release_accumulator(&bars->s_empty[(s_no + t) & 1], lane);
                     if (warp == 4 && lane == 0) AT_ADD(6, AT_CLOCK() - t0);
@@ -428,7 +426,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 auto process = [&](const uint32_t (&r)[32], int t) -> bool {
                     const int s = s_no + t;                                  // tile number = P buffer number
                     uint32_t mask = 0u;
-                    const long long tm0 = AT_CLOCK();
+                    [[maybe_unused]] const long long tm0 = AT_CLOCK();
                     if (MASKED && masked_op) mask = block_mask(win.get(p.blocks, cur.first, cur.count, t, lane).col());
                     // block maxima of the raw scores (for a negative scale: of their negatives)
                     float x_a = -INFINITY, x_b = -INFINITY;
@@ -487,14 +485,14 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         }
                     }
                     const float sub_a = m_a == -INFINITY ? 0.f : m_a, sub_b = m_b == -INFINITY ? 0.f : m_b;
-                    const long long tm1 = AT_CLOCK();
+                    [[maybe_unused]] const long long tm1 = AT_CLOCK();
                     // the P buffer must have been read by the MMAs that used it last (those of tile s - 2)
                     if (s >= 2 && !__all_sync(0xffffffffu, mbar_wait(&bars->pv_done[(s - 2) & vring_mask],
                                                                      (uint32_t)((s - 2) >> p.vring_shift) & 1u, abort_flag, p.status)))
                         return false;
                     // every lane owns the column pairs 8u + 2 * q4 + {0, 1} of its two rows: one 32-bit
                     // word each, stored straight into the 128-byte-swizzled tile (32 lanes hit 32 banks)
-                    const long long tm2 = AT_CLOCK();
+                    [[maybe_unused]] const long long tm2 = AT_CLOCK();
                     const uint32_t tile = smem_u32(p_smem + pb * kTileBytes) + p_row;
 #pragma unroll
                     for (int u = 0; u < 8; ++u) {
@@ -512,7 +510,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(pack2<BF16>(pa[0], pa[1])) : "memory");
                         asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + 8 * 128), "r"(pack2<BF16>(pb2[0], pb2[1])) : "memory");
                     }
-                    const long long tm3 = AT_CLOCK();
+                    [[maybe_unused]] const long long tm3 = AT_CLOCK();
                     fence_async_shared();           // generic-proxy writes -> visible to the tensor core's reads
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars->p_full[pb]);
@@ -572,7 +570,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&bars->stat_full[dir][slot]);
                     } else {
-                        const long long ts0 = AT_CLOCK();
+                        [[maybe_unused]] const long long ts0 = AT_CLOCK();
                         ok = __all_sync(0xffffffffu, mbar_wait(&bars->stat_full[dir][slot], par, abort_flag, p.status)) != 0;
                         if (!ok) break;
                         if (warp == 4 && lane == 0) AT_ADD(22, AT_CLOCK() - ts0);
@@ -593,10 +591,10 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     // ---- end of the row: O / l
                     const float inv_a = l_a > 0.f ? __frcp_rn(l_a) : 0.f, inv_b = l_b > 0.f ? __frcp_rn(l_b) : 0.f;
                     const float sw_a = w_a * inv_a, sv_a = v_a * inv_a, sw_b = w_b * inv_b, sv_b = v_b * inv_b;
-                    const long long te0 = AT_CLOCK();
+                    [[maybe_unused]] const long long te0 = AT_CLOCK();
                     ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full, (uint32_t)(o_no & 1), abort_flag, p.status)) != 0;
                     if (!ok) break;
-                    const long long te1 = AT_CLOCK();
+                    [[maybe_unused]] const long long te1 = AT_CLOCK();
                     tc_fence_after();
                     for (int c = 0; c < p.head_dim; c += 32) {
                         uint32_t r0[16], r1[16];

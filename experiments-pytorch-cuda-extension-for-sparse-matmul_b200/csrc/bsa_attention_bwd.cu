@@ -218,7 +218,7 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                     const BlockDesc d = win.get(p.blocks, cur.first, cur.count, j, lane);
                     const int other = COL ? d.row() : d.col();
                     const int stage = y_no & ring_mask;
-                    const long long tp0 = BT_CLOCK();
+                    [[maybe_unused]] const long long tp0 = BT_CLOCK();
                     ok = __all_sync(0xffffffffu, mbar_wait(&bars->out_done[stage], ((uint32_t)(y_no >> p.ring_shift) & 1u) ^ 1u,
                                                            abort_flag, p.status)) != 0;
                     if (lane == 0) BT_ADD(0, BT_CLOCK() - tp0);
@@ -270,12 +270,12 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
             const int s_end = s_no + n;
             for (int s = s_no + ((par - s_no) & 1); s < s_end; s += 2) {
                 const int stage = s & ring_mask;
-                const long long ti0 = BT_CLOCK();
+                [[maybe_unused]] const long long ti0 = BT_CLOCK();
                 ok = __all_sync(0xffffffffu, mbar_wait(&bars->y_full[stage], (uint32_t)(s >> p.ring_shift) & 1u, abort_flag, p.status)) != 0;
-                const long long ti1 = BT_CLOCK();
+                [[maybe_unused]] const long long ti1 = BT_CLOCK();
                 if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->t_empty[par], ((uint32_t)(s >> 1) & 1u) ^ 1u, abort_flag, p.status)) != 0;
                 if (!ok) break;
-                const long long ti2 = BT_CLOCK();
+                [[maybe_unused]] const long long ti2 = BT_CLOCK();
                 tc_fence_after();
                 const uint32_t d = tmem_base + (uint32_t)(par * 2 * kTile + which * kTile);
                 if (elect_one()) {
@@ -325,13 +325,13 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                 const uint32_t d = tmem_base + (uint32_t)(kBwdAccCol0 + ((ob_acc * kOuts + (COL ? w : 0)) * p.parts + (COL ? 0 : (kk0 >> 1) & (p.parts - 1))) * p.head_dim);
                 for (int j = 0; ok && j < n; ++j) {
                     const int s = s_no + j, stage = s & ring_mask, ob = s & (p.opbufs - 1);
-                    const long long to0 = BT_CLOCK();
+                    [[maybe_unused]] const long long to0 = BT_CLOCK();
                     if (j == 0) ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_empty[ob_acc], o_par ^ 1u, abort_flag, p.status)) != 0;
-                    const long long to1 = BT_CLOCK();
+                    [[maybe_unused]] const long long to1 = BT_CLOCK();
                     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->y_full[stage], (uint32_t)(s >> p.ring_shift) & 1u, abort_flag, p.status)) != 0;
                     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->op_full[ob], (uint32_t)(s >> p.op_shift) & 1u, abort_flag, p.status)) != 0;
                     if (!ok) break;
-                    const long long to2 = BT_CLOCK();
+                    [[maybe_unused]] const long long to2 = BT_CLOCK();
                     tc_fence_after();
                     if (elect_one()) {
                         // A = operand tile (K-major), B = a Y tile set with N = head_dim contiguous
@@ -369,7 +369,7 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
         const int out_rows = COL ? p.seq_k : p.seq_q;
         int s_no = 0, o_no = 0;
         bool ok = true;
-        const long long t_begin = BT_CLOCK();
+        [[maybe_unused]] const long long t_begin = BT_CLOCK();
         Cursor cur;
         cur.init(p);
         BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
@@ -409,10 +409,10 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                     const int s = s_no + t, tb = s & 1;
                     const BlockDesc d = win.get(p.blocks, cur.first, cur.count, t, lane);
                     const int other = COL ? d.row() : d.col();
-                    const long long tc0 = BT_CLOCK();
+                    [[maybe_unused]] const long long tc0 = BT_CLOCK();
                     ok = __all_sync(0xffffffffu, mbar_wait(&bars->t_full[tb], (uint32_t)(s >> 1) & 1u, abort_flag, p.status)) != 0;
                     if (!ok) break;
-                    const long long tc1 = BT_CLOCK();
+                    [[maybe_unused]] const long long tc1 = BT_CLOCK();
                     tc_fence_after();
                     uint32_t r1[32], r2[32];
                     tc_ld_16x256b_x8(tmem_base + lane_field + (uint32_t)(tb * 2 * kTile), r1);
@@ -430,7 +430,7 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                     }
                     tc_wait_ld();
                     release_accumulator(&bars->t_empty[tb], lane);
-                    const long long tc2 = BT_CLOCK();
+                    [[maybe_unused]] const long long tc2 = BT_CLOCK();
                     // the operand tiles of this buffer must have been read by the MMAs of block s - opbufs
                     const int ob = s & (p.opbufs - 1);
                     if (s >= p.opbufs) {
@@ -439,7 +439,7 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                                                                (uint32_t)(sp >> p.ring_shift) & 1u, abort_flag, p.status)) != 0;
                         if (!ok) break;
                     }
-                    const long long tc3 = BT_CLOCK();
+                    [[maybe_unused]] const long long tc3 = BT_CLOCK();
                     const uint32_t tile0 = smem_u32(op_smem + (ob * kOpTiles) * kTileBytes) + op_row;
                     const int other0 = other * kTile + 2 * q4;          // position of column u = 0, e = 0
 #pragma unroll
@@ -486,7 +486,7 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                             asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + 8 * 128), "r"(pack2<BF16>(db[0], db[1])) : "memory");
                         }
                     }
-                    const long long tc4 = BT_CLOCK();
+                    [[maybe_unused]] const long long tc4 = BT_CLOCK();
                     fence_async_shared();           // generic-proxy writes -> visible to the tensor core's reads
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars->op_full[ob]);
@@ -500,11 +500,11 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                 // 3 % slower.)
                 if (wg == ((s_no - 1) & 1)) {
                     const int ob_acc = o_no & (p.obufs - 1);
-                    const long long te0 = BT_CLOCK();
+                    [[maybe_unused]] const long long te0 = BT_CLOCK();
                     ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[ob_acc], (uint32_t)(p.obufs == 2 ? o_no >> 1 : o_no) & 1u,
                                                            abort_flag, p.status)) != 0;
                     if (!ok) break;
-                    const long long te1 = BT_CLOCK();
+                    [[maybe_unused]] const long long te1 = BT_CLOCK();
                     if ((warp & 3) == 0 && lane == 0) BT_ADD(13 + 2 * wg, te1 - te0);
                     tc_fence_after();
 #pragma unroll

@@ -235,12 +235,12 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         uint32_t phase = 0;
         bool ok = true;
         long long t_wait = 0, t_issue = 0, t_get = 0, t_item = 0;
-        const long long t_begin = TC_CLOCK();
+        [[maybe_unused]] const long long t_begin = TC_CLOCK();
         Cursor cur;
         cur.init(p, p.split);
         BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
         while (ok && cur.valid()) {
-            const long long t_i0 = TC_CLOCK();
+            [[maybe_unused]] const long long t_i0 = TC_CLOCK();
             BlockDesc pre_next{0, 0};
             if (cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
             int flushes, ksteps;
@@ -256,7 +256,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 // every phase of each barrier it ever waits on.
                 for (int k = (warp - step0) & (kProducerWarps - 1); ok && k < ksteps; k += kProducerWarps) {
                     {
-                        const long long t_g0 = TC_CLOCK();
+                        [[maybe_unused]] const long long t_g0 = TC_CLOCK();
                         int cols[4] = {0, 0, 0, 0};
                         BlockDesc d{0, 0};
                         if (is_sdd) {
@@ -270,9 +270,9 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         {
                             // the whole warp waits and computes the copies' operands (warp-uniform
                             // code keeps them in uniform registers); one elected lane issues
-                            const long long t0 = TC_CLOCK();
+                            [[maybe_unused]] const long long t0 = TC_CLOCK();
                             ok = __all_sync(0xffffffffu, mbar_wait(&bars->empty[stage], phase ^ 1, &bars->abort_flag, p.status)) != 0;
-                            const long long t1 = TC_CLOCK();
+                            [[maybe_unused]] const long long t1 = TC_CLOCK();
                             t_wait += t1 - t0;
                             if (ok && elect_one()) {
                                 uint8_t* slot = stage_base + stage * stage_bytes;
@@ -352,7 +352,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const int issuer_mask = p.issuers - 1;       // issuers is 1, 2 or 4 (no runtime division here:
                                                          // it costs a lone thread hundreds of cycles)
             long long t_full = 0, t_acc = 0, t_mma = 0, t_commit = 0, t_desc = 0, t_kloop = 0, t_accfull = 0;
-            const long long t_begin = TC_CLOCK();
+            [[maybe_unused]] const long long t_begin = TC_CLOCK();
             Cursor cur;
             cur.init(p, p.split);
             for (; ok && cur.valid(); cur.advance()) {
@@ -370,30 +370,30 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     }
                     const int nb = b_tiles<MODE>(p, cur.count << p.split, cur.chunk, f);
                     const uint32_t idesc = p.idesc | ((uint32_t)((nb * kTile) >> 3) << 17);
-                    { const long long t0 = TC_CLOCK();
+                    { [[maybe_unused]] const long long t0 = TC_CLOCK();
                       ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_empty[acc], ((uint32_t)(flush_no >> kBufShift) & 1u) ^ 1u, &bars->abort_flag, p.status)) != 0;
                       t_acc += TC_CLOCK() - t0; }
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t d = tmem_base + (uint32_t)(acc * kBufCols) + part_col;
                     bool issued = false;
-                    const long long tk0 = TC_CLOCK();
+                    [[maybe_unused]] const long long tk0 = TC_CLOCK();
                     // dsd / dds: K-step n belongs to issuer n % issuers (the stage count is a
                     // multiple of it, so a stage always belongs to the same issuer)
                     const int k_first = is_sdd ? 0 : ((w - step0) & issuer_mask);
                     const int k_inc = is_sdd ? 1 : p.issuers;
                     for (int k = k_first; k < ksteps; k += k_inc) {
                         {
-                            { const long long t0 = TC_CLOCK();
+                            { [[maybe_unused]] const long long t0 = TC_CLOCK();
                               ok = __all_sync(0xffffffffu, mbar_wait(&bars->full[stage], phase, &bars->abort_flag, p.status)) != 0;
                               t_full += TC_CLOCK() - t0; }
                             if (!ok) break;
-                            const long long tm0 = TC_CLOCK();
+                            [[maybe_unused]] const long long tm0 = TC_CLOCK();
                             tc_fence_after();
                             const uint32_t slot = smem_u32(stage_base + stage * stage_bytes);
                             const uint64_t da = make_tile_desc(slot, a_mn_major);
                             const uint64_t db = make_tile_desc(slot + kTileBytes, b_mn_major);
-                            const long long tm1 = TC_CLOCK();
+                            [[maybe_unused]] const long long tm1 = TC_CLOCK();
                             if (elect_one()) {
 #pragma unroll
                                 for (int kk = 0; kk < kTile / 16; ++kk)
@@ -403,7 +403,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                             }
                             __syncwarp();
                             issued = true;
-                            const long long tm2 = TC_CLOCK();
+                            [[maybe_unused]] const long long tm2 = TC_CLOCK();
                             t_desc += tm1 - tm0; t_mma += tm2 - tm1; t_commit += TC_CLOCK() - tm2;
                         }
                         stage += k_inc;
@@ -411,7 +411,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     }
                     step0 += ksteps;
                     if (!ok) break;
-                    const long long tk1 = TC_CLOCK();
+                    [[maybe_unused]] const long long tk1 = TC_CLOCK();
                     // the accumulation (dsd / dds: this issuer's partial, if it had a K-step) is complete
                     if (elect_one()) {
                         if (issued) tc_commit(&bars->acc_full[acc]);
@@ -446,7 +446,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         int tile_no = 0;                    // sdd: slabs this warp has sent so far (staging slab = tile_no & 1)
         bool ok = true;
         long long t_accf = 0, t_ld = 0, t_write = 0;
-        const long long t_begin = TC_CLOCK();
+        [[maybe_unused]] const long long t_begin = TC_CLOCK();
         Cursor cur;
         cur.init(p, p.split);
         BlockDesc pre{0, 0};
@@ -471,7 +471,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (owner != group) continue;
                 const int tiles = b_tiles<MODE>(p, cur.count << p.split, cur.chunk, f);
                 if (have_acc) {
-                    const long long t0 = TC_CLOCK();
+                    [[maybe_unused]] const long long t0 = TC_CLOCK();
                     ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_full[acc], acc_phase, &bars->abort_flag, p.status)) != 0;
                     t_accf += TC_CLOCK() - t0;
                     if (!ok) break;
@@ -534,7 +534,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         }
                         ++tile_no;
                     };
-                    const long long t_a = TC_CLOCK();
+                    [[maybe_unused]] const long long t_a = TC_CLOCK();
                     uint32_t ra[32], rb[32];
                     tc_ld_16x256b_x8(tbase, ra);
                     for (int t = 0; t < tiles; t += 2) {
@@ -576,7 +576,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16)
                                            + (uint32_t)(acc * kBufCols + t * kTile);
                     const bool last_tile = have_acc && t == tiles - 1;
-                    const long long t_a = TC_CLOCK();
+                    [[maybe_unused]] const long long t_a = TC_CLOCK();
                     if (!have_acc || parts == 1) {
                         uint32_t v[kTile];          // fp32 bit patterns of this lane's row
                         if (have_acc) {
@@ -586,7 +586,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
                             for (int c = 0; c < kTile; ++c) v[c] = 0u;
                         }
-                        const long long t_m = TC_CLOCK();
+                        [[maybe_unused]] const long long t_m = TC_CLOCK();
                         if (last_tile) release_accumulator(&bars->acc_empty[acc], lane);
                         if (writer) store_row<kTile>(dst, v, cols_valid, p.c_vec8 != 0, bf16_out);
                         t_write += TC_CLOCK() - t_m;
@@ -614,7 +614,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                             if (writer) store_row<32>(dst + h * 32, v, cols_valid - h * 32, p.c_vec8 != 0, bf16_out);
                         }
                     }
-                    const long long t_b = TC_CLOCK();
+                    [[maybe_unused]] const long long t_b = TC_CLOCK();
                     t_ld += t_b - t_a;
                 }
             }

@@ -34,9 +34,9 @@
 //              128-byte-swizzled P tile (32 lanes on 32 banks); at the end of a row O goes through
 //              4x4 quad transposes and 128-bit stores to global memory.
 //              Head dim 64: two warpgroups (12 warps) take alternate blocks, each with its own
-//              running maxima, sums and O accumulator; the group that owns a row's last block
-//              merges the two (the partial softmaxes over disjoint key sets combine exactly) and
-//              writes the row while the other one starts the next row.
+//              running maxima, sums and O accumulator; the groups finish alternate rows: merge
+//              the two accumulators (the partial softmaxes over disjoint key sets combine
+//              exactly) and write the row while the other group starts the next row.
 //              Head dim 128 (one accumulator fits): one warpgroup (8 warps) with two register
 //              buffers, the TMEM load of block j + 1 in flight while block j is worked on.
 // All waits are bounded (BSA_ERR_DEVICE_TIMEOUT in the workspace word).
@@ -67,7 +67,7 @@ struct __align__(8) AttnBarriers {
     uint64_t pv_done[kMaxRing];     // the MMAs of one P V have retired: the P buffer and the V stage are free
     uint64_t s_empty[2];
     uint64_t p_full[2];
-    uint64_t o_full, o_empty;
+    uint64_t o_full[2], o_empty[2];     // indexed by the parity of the item: each is waited on by one softmax group only
     uint64_t stat_full[2][2], stat_empty[2][2];   // two softmax groups: hand-over of row maxima and sums, [writer][slot]
     uint64_t drain;
     uint32_t tmem_base;
@@ -125,7 +125,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             mbar_init(&bars->s_empty[s], 4);
             for (int d = 0; d < 2; ++d) { mbar_init(&bars->stat_full[d][s], 4); mbar_init(&bars->stat_empty[d][s], 4); }
         }
-        mbar_init(&bars->o_full, 1); mbar_init(&bars->o_empty, 4);
+        for (int s = 0; s < 2; ++s) { mbar_init(&bars->o_full[s], 1); mbar_init(&bars->o_empty[s], 4); }
         mbar_init(&bars->drain, 2);
         bars->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -297,7 +297,9 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 for (int j = 0; ok && j < n; ++j, ++p_no) {
                     const int pb = p_no & 1, vs = p_no & vring_mask;
                     [[maybe_unused]] const long long t0 = AT_CLOCK();
-                    if (j == 0) ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_empty, (uint32_t)(o_no & 1) ^ 1u, abort_flag, p.status)) != 0;
+                    // the accumulators are free once the item before has been read out (its barrier: its parity)
+                    if (j == 0 && o_no > 0)
+                        ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_empty[(o_no - 1) & 1], (uint32_t)((o_no - 1) >> 1) & 1u, abort_flag, p.status)) != 0;
                     [[maybe_unused]] const long long t1 = AT_CLOCK();
                     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->v_full[vs], (uint32_t)(p_no >> p.vring_shift) & 1u, abort_flag, p.status)) != 0;
                     [[maybe_unused]] const long long t2 = AT_CLOCK();
@@ -315,7 +317,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                             tc_mma_f16(d, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * (2048 >> 4)), idesc_pv,
                                        (j >= WGS || kk > 0) ? 1u : 0u);
                         tc_commit(&bars->pv_done[vs]);
-                        if (j == n - 1) tc_commit(&bars->o_full);
+                        if (j == n - 1) tc_commit(&bars->o_full[o_no & 1]);
                     }
                     __syncwarp();
                     if (lane == 0) { AT_ADD(14, t1 - t0); AT_ADD(15, t2 - t1); AT_ADD(16, t3 - t2); AT_ADD(17, AT_CLOCK() - t3); }
@@ -547,9 +549,13 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
                 // weights of this group's (w) and the other group's (v) accumulator in the result
                 float w_a = 1.f, w_b = 1.f, v_a = 0.f, v_b = 0.f;
-                // The group that owns the item's last tile finishes the item; the other one owns the
-                // next item's first tile and goes on right away.
-                const int epi_wg = WGS == 2 ? ((s_no - 1) & 1) : 0;
+                // The groups finish alternate items.  The rule must not depend on the data: an mbarrier
+                // parity wait tells the current phase from the one before only, so o_full / o_empty of
+                // items of one parity are always waited on by the same group, in every phase.  (Letting
+                // the owner of an item's last tile finish it, which starts the next item a little
+                // earlier, let a group skip phases: with rows of 1-3 blocks and several items per CTA it
+                // passed a wait one phase early.)
+                const int epi_wg = WGS == 2 ? (o_no & 1) : 0;
                 if (WGS == 2) {
                     // the other group hands its maxima and sums over through shared memory (per direction
                     // two slots, alternating); the partial softmaxes over the two groups' key sets merge
@@ -592,7 +598,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     const float inv_a = l_a > 0.f ? __frcp_rn(l_a) : 0.f, inv_b = l_b > 0.f ? __frcp_rn(l_b) : 0.f;
                     const float sw_a = w_a * inv_a, sv_a = v_a * inv_a, sw_b = w_b * inv_b, sv_b = v_b * inv_b;
                     [[maybe_unused]] const long long te0 = AT_CLOCK();
-                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full, (uint32_t)(o_no & 1), abort_flag, p.status)) != 0;
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[o_no & 1], (uint32_t)(o_no >> 1) & 1u, abort_flag, p.status)) != 0;
                     if (!ok) break;
                     [[maybe_unused]] const long long te1 = AT_CLOCK();
                     tc_fence_after();
@@ -601,7 +607,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         tc_ld_16x256b_x4(tmem_base + lane_field + o_col + (uint32_t)c, r0);
                         if (WGS == 2) tc_ld_16x256b_x4(tmem_base + lane_field + (uint32_t)((wg ^ 1) * p.head_dim + c), r1);
                         tc_wait_ld();
-                        if (c + 32 >= p.head_dim) release_accumulator(&bars->o_empty, lane);
+                        if (c + 32 >= p.head_dim) release_accumulator(&bars->o_empty[o_no & 1], lane);
                         uint32_t ta[4], tb[4];
 #pragma unroll
                         for (int u = 0; u < 4; ++u) {

@@ -26,9 +26,8 @@
 // stored).  Warp roles (15 warps):
 //   warps 0-7   two compute warpgroups taking alternate blocks: tcgen05.ld of T1 and T2 (16x256b
 //               shape: a lane owns 2 rows x 16 columns), exp2, the dS formula, masks, 32-bit
-//               stores into the swizzled operand tiles (a ring of 2 or 4 buffers); the group that
-//               owns an item's last block converts and stores the accumulators while the other
-//               one goes on.
+//               stores into the swizzled operand tiles (a ring of 2 or 4 buffers); the groups
+//               convert and store the accumulators of alternate items while the other one goes on.
 //   warp 8      TMA producer: the item's X pair, every block's Y pair and, by columns, the 512
 //               bytes of (lse, D) of the block's query rows (ring of 4 or 8 stages)
 //   warps 9-12  issuers of T1 / T2 of the even / odd blocks (a thread issues one tcgen05.mma or
@@ -71,7 +70,7 @@ struct __align__(8) BwdBarriers {
     uint64_t out_done[kBwdMaxRing];    // the accumulation MMAs of a block have retired: Y stage and operand tiles are free
     uint64_t t_full[2], t_empty[2];
     uint64_t op_full[4];            // the operand tile(s) of a block are written
-    uint64_t o_full[2], o_empty[2];   // accumulator sets (one per item in flight)
+    uint64_t o_full[2], o_empty[2];   // indexed by the parity of the item: each is waited on by one compute group only
     uint64_t drain;
     uint32_t tmem_base;
     int abort_flag;
@@ -319,14 +318,18 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
             for (; ok && cur.valid(); cur.advance()) {
                 const int n = cur.count;
                 if (n == 0) continue;
-                const int ob_acc = o_no & (p.obufs - 1);
-                const uint32_t o_par = (uint32_t)(p.obufs == 2 ? o_no >> 1 : o_no) & 1u;
+                const int ob_acc = o_no & (p.obufs - 1);          // accumulator set of this item
                 // accumulator of this issuer: set, then output (by columns) or partial (by rows)
                 const uint32_t d = tmem_base + (uint32_t)(kBwdAccCol0 + ((ob_acc * kOuts + (COL ? w : 0)) * p.parts + (COL ? 0 : (kk0 >> 1) & (p.parts - 1))) * p.head_dim);
                 for (int j = 0; ok && j < n; ++j) {
                     const int s = s_no + j, stage = s & ring_mask, ob = s & (p.opbufs - 1);
                     [[maybe_unused]] const long long to0 = BT_CLOCK();
-                    if (j == 0) ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_empty[ob_acc], o_par ^ 1u, abort_flag, p.status)) != 0;
+                    // the accumulator set is free once the item that used it last (obufs items ago) has been
+                    // read out; that item's barrier is the one of its parity
+                    if (j == 0 && o_no >= p.obufs) {
+                        const int prev = o_no - p.obufs;
+                        ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_empty[prev & 1], (uint32_t)(prev >> 1) & 1u, abort_flag, p.status)) != 0;
+                    }
                     [[maybe_unused]] const long long to1 = BT_CLOCK();
                     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->y_full[stage], (uint32_t)(s >> p.ring_shift) & 1u, abort_flag, p.status)) != 0;
                     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->op_full[ob], (uint32_t)(s >> p.op_shift) & 1u, abort_flag, p.status)) != 0;
@@ -342,7 +345,7 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                             tc_mma_f16(d, a + (uint64_t)(kk * 2), b + (uint64_t)(kk * (2048 >> 4)), p.idesc_acc,
                                        (j > 0 || kk > kk0) ? 1u : 0u);
                         tc_commit(&bars->out_done[stage]);
-                        if (j == n - 1) tc_commit(&bars->o_full[ob_acc]);
+                        if (j == n - 1) tc_commit(&bars->o_full[o_no & 1]);
                     }
                     __syncwarp();
                     if (w == 0 && lane == 0) { BT_ADD(4, to1 - to0); BT_ADD(5, to2 - to1); BT_ADD(6, BT_CLOCK() - to2); }
@@ -495,14 +498,16 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                 }
                 s_no += n;
                 if (!ok) break;
-                // The group that owns the item's last block stores the accumulators; the other one owns
-                // the next item's first block and goes on right away.  (Taking turns by item was measured
-                // 3 % slower.)
-                if (wg == ((s_no - 1) & 1)) {
+                // The groups store the accumulators of alternate items.  The rule must not depend on the
+                // data: an mbarrier parity wait tells the current phase from the one before only, so
+                // o_full / o_empty of the items of one parity are always waited on by the same group, in
+                // every phase.  (Letting the owner of an item's last block store it was 3 % faster and
+                // wrong: with rows of 1-3 blocks and several items per CTA a group skipped phases, passed
+                // a wait one phase early and the kernel ended in a time-out.)
+                if (wg == (o_no & 1)) {
                     const int ob_acc = o_no & (p.obufs - 1);
                     [[maybe_unused]] const long long te0 = BT_CLOCK();
-                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[ob_acc], (uint32_t)(p.obufs == 2 ? o_no >> 1 : o_no) & 1u,
-                                                           abort_flag, p.status)) != 0;
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[o_no & 1], (uint32_t)(o_no >> 1) & 1u, abort_flag, p.status)) != 0;
                     if (!ok) break;
                     [[maybe_unused]] const long long te1 = BT_CLOCK();
                     if ((warp & 3) == 0 && lane == 0) BT_ADD(13 + 2 * wg, te1 - te0);
@@ -522,7 +527,7 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
 #pragma unroll
                                 for (int i = 0; i < 16; ++i) r0[i] = __float_as_uint(__uint_as_float(r0[i]) + __uint_as_float(rq[i]));
                             }
-                            if (a == kOuts - 1 && c + 32 >= p.head_dim) release_accumulator(&bars->o_empty[ob_acc], lane);
+                            if (a == kOuts - 1 && c + 32 >= p.head_dim) release_accumulator(&bars->o_empty[o_no & 1], lane);
                             uint32_t ta[4], tb2[4];
 #pragma unroll
                             for (int u = 0; u < 4; ++u) {

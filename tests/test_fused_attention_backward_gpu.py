@@ -79,6 +79,16 @@ def test_backward_many_items_per_cta():
     _grads(bigbird(64, 1, 2, 3, 77), (8,), 64, torch.float16, 0.125, seed=230)
 
 
+@pytest.mark.parametrize("causal", [False, True])
+def test_short_rows_and_several_items_per_cta(causal):
+    """Block rows and columns of 1 to 3 blocks with four to five work items per CTA, with and without the
+    element-level masks: the hand-over of the accumulators between consecutive items happens after very
+    few blocks, so every barrier involved must be waited on by the same warps in every phase (an earlier
+    version let the owner of an item's last block finish the item and ran into a time-out here)."""
+    from sparse.patterns import local_global_causal
+    _grads(local_global_causal(16, 2, 1), (40,), 64, torch.float16, 0.125, causal, None, seed=260)
+
+
 def test_backward_negative_scale():
     from sparse.patterns import strided_local
     _grads(strided_local(8, 4, 1), (2,), 64, torch.float16, -0.2, seed=240)
@@ -104,3 +114,47 @@ def test_fused_backward_agrees_with_unfused_composition(dim):
     for a, b, name in zip(grads[True], grads[False], ("dQ", "dK", "dV")):
         err = float((a.float() - b.float()).abs().max() / b.float().abs().max())
         assert err <= 4e-3, (name, err)
+
+
+def test_full_size_fused_step_properties_config5():
+    """Benchmark configuration 5 at full size (512 slices, seq 8192, head dim 128, BigBird layout) through
+    the fused forward and backward, checked by size-independent properties: (1) with V = 1 every output
+    element is 1 (probabilities sum to one); (2) then dQ = dK = 0 exactly up to rounding (dP = D_i in every
+    row) and dV[j] = sum_i P_ij dO_i, whose sum over the keys of a slice equals the sum of dO over its
+    queries; (3) the last slices of the full launch equal the same slices computed alone (an index overflow
+    would hit the high slices)."""
+    from sparse import SparseLayout
+    from sparse.kernel import sparse_ops
+    from sparse.patterns import bigbird
+    free, _ = torch.cuda.mem_get_info()
+    if free < 24 * 2 ** 30:
+        pytest.skip("needs about 16 GB of device memory")
+    layout = SparseLayout(bigbird(128, 1, 2, 3, 5000), block=64)
+    z, seq, d, scale = 512, 8192, 128, 128 ** -0.5
+    rl, cl = layout.row_layout, layout.col_layout
+    gen = torch.Generator(device="cuda").manual_seed(55)
+    q = torch.randn(z, seq, d, device="cuda", generator=gen).half()
+    k = torch.randn(z, seq, d, device="cuda", generator=gen).half()
+    do = torch.randn(z, seq, d, device="cuda", generator=gen).half()
+    ones = torch.ones(z, seq, d, device="cuda", dtype=torch.float16)
+    o, lse = sparse_ops.sparse_attention_forward(q, k, ones, rl[0], rl[1], 64, 128, scale, False, None)
+    assert float((o.float() - 1).abs().max()) < 1e-2
+    dq, dk, dv = sparse_ops.sparse_attention_backward(q, k, ones, o, do, lse, rl[0], rl[1], cl[0], cl[1], 64,
+                                                      scale, False, None)
+    sparse_ops.check_device_status(0)
+    # dP - D_i = rowsum(dO) - sum_d dO o O with O = 1 +- rounding: tiny against |dO| ~ 1
+    assert float(dq.float().abs().max()) < 5e-2 and float(dk.float().abs().max()) < 5e-2
+    col_sums = dv[-4:].float().sum(dim=1)
+    row_sums = do[-4:].float().sum(dim=1)
+    assert float((col_sums - row_sums).abs().max() / row_sums.abs().max()) < 1e-2
+    v = torch.randn(z, seq, d, device="cuda", generator=gen).half()
+    o, lse = sparse_ops.sparse_attention_forward(q, k, v, rl[0], rl[1], 64, 128, scale, False, None)
+    dq, dk, dv = sparse_ops.sparse_attention_backward(q, k, v, o, do, lse, rl[0], rl[1], cl[0], cl[1], 64,
+                                                      scale, False, None)
+    tail = slice(z - 3, z)
+    o2, lse2 = sparse_ops.sparse_attention_forward(q[tail], k[tail], v[tail], rl[0], rl[1], 64, 128, scale, False, None)
+    dq2, dk2, dv2 = sparse_ops.sparse_attention_backward(q[tail], k[tail], v[tail], o2, do[tail], lse2, rl[0], rl[1],
+                                                         cl[0], cl[1], 64, scale, False, None)
+    sparse_ops.check_device_status(0)
+    assert torch.equal(o[tail], o2) and torch.equal(lse[tail], lse2)
+    assert torch.equal(dq[tail], dq2) and torch.equal(dk[tail], dk2) and torch.equal(dv[tail], dv2)

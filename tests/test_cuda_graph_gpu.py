@@ -17,6 +17,7 @@ def _step(fn, q, k, v, do):
     return out.detach(), q.grad, k.grad, v.grad
 
 
+@pytest.mark.filterwarnings("ignore:The AccumulateGrad node's stream does not match")
 @pytest.mark.parametrize("fused", [False, True])
 def test_attention_step_replays_from_a_cuda_graph(fused):
     from sparse import SparseLayout, attention, matmul, softmax

@@ -89,6 +89,8 @@ struct AttnParams {
     int qbufs;                 // Q buffers: 2 = the next item's Q tile set is prefetched
     float scale_log2;          // scale * log2(e)
     int causal;
+    int quadrants;             // 1: the idx field of a descriptor holds a 4-bit mask of the 32 x 32 quadrants of the
+                               // block that belong to the layout (bit 2 * row_half + col_half); the others are masked
     const uint8_t* kpm;        // key padding mask or nullptr
     int kpm_div;               // batch entries per mask row
     long long kpm_stride;
@@ -343,7 +345,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const uint32_t lane_field = (uint32_t)(quad * 32) << 16;
         const uint32_t o_col = (uint32_t)(wg * p.head_dim);       // this group's O accumulator
         // MASKED = false: no causal or key-padding mask, all mask tests fold away
-        const bool masked_op = MASKED && (p.causal != 0 || p.kpm != nullptr);
+        const bool masked_op = MASKED && (p.causal != 0 || p.kpm != nullptr || p.quadrants != 0);
         int s_no = 0, o_no = 0;                     // S tiles and non-empty items before the current item
         int x_no[2] = {0, 0};                       // hand-overs so far in which group 0 / group 1 was the writer
         bool ok = true;
@@ -371,8 +373,15 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 const uint8_t* kpm_row = p.kpm ? p.kpm + (size_t)(cur.z / p.kpm_div) * p.kpm_stride : nullptr;
                 const int qpos_a = cur.g * kTile + row_a;
                 // Bits 0-15: columns (u, e) of row a that are masked in block `col`; bits 16-31: row b.
-                auto block_mask = [&](int col) -> uint32_t {
+                auto block_mask = [&](const BlockDesc& desc) -> uint32_t {
+                    const int col = desc.col();
                     uint32_t m = 0;
+                    if (p.quadrants) {
+                        // this lane's rows lie in row half quad / 2; its columns 8u + .. in column half u / 4
+                        const uint32_t present = (uint32_t)desc.idx >> (2 * (quad >> 1));
+                        if (!(present & 1u)) m |= 0x00FF00FFu;
+                        if (!(present & 2u)) m |= 0xFF00FF00u;
+                    }
                     const int k0 = col * kTile + 2 * q4;
                     if (p.causal && col * kTile + kTile - 1 > qpos_a) {
 #pragma unroll
@@ -429,7 +438,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     const int s = s_no + t;                                  // tile number = P buffer number
                     uint32_t mask = 0u;
                     [[maybe_unused]] const long long tm0 = AT_CLOCK();
-                    if (MASKED && masked_op) mask = block_mask(win.get(p.blocks, cur.first, cur.count, t, lane).col());
+                    if (MASKED && masked_op) mask = block_mask(win.get(p.blocks, cur.first, cur.count, t, lane));
                     // block maxima of the raw scores (for a negative scale: of their negatives)
                     float x_a = -INFINITY, x_b = -INFINITY;
                     if (!flip) {
@@ -660,10 +669,10 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 int attention_forward(int dtype, const void* q, const void* k, const void* v, void* o, float* lse,
                       const int32_t* row_blocks, const int32_t* row_table, int64_t nnz, int64_t block_rows,
                       int64_t block_cols, int64_t batches, int64_t head_dim, float scale, int causal,
-                      const uint8_t* kpm, int64_t kpm_batches, int64_t kpm_stride, uint32_t* workspace,
+                      const uint8_t* kpm, int64_t kpm_batches, int64_t kpm_stride, int quadrants, uint32_t* workspace,
                       cudaStream_t stream) {
     using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const AttnParams);
-    const bool masked = causal != 0 || kpm != nullptr;
+    const bool masked = causal != 0 || kpm != nullptr || quadrants != 0;
     // two softmax warpgroups where two O accumulators fit into the CTA's 256 TMEM columns
     const int wgs = head_dim == 64 ? 2 : 1;
     KernelFn kernel;
@@ -710,6 +719,7 @@ int attention_forward(int dtype, const void* q, const void* k, const void* v, vo
     p.seq_q = (int)seq_q; p.seq_k = (int)seq_k; p.head_dim = (int)head_dim;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.causal = causal;
+    p.quadrants = quadrants;
     p.kpm = kpm;
     p.kpm_div = kpm ? (int)(batches / kpm_batches) : 1;
     p.kpm_stride = kpm_stride;
@@ -742,7 +752,7 @@ extern "C" int bsa_attention_forward(int dtype, const void* q, const void* k, co
                                      int64_t nnz, int64_t block_rows, int64_t block_cols, int64_t batches,
                                      int64_t head_dim, int block, float scale, int causal,
                                      const uint8_t* key_padding_mask, int64_t kpm_batches, int64_t kpm_stride,
-                                     void* workspace, size_t workspace_bytes, void* stream) {
+                                     int quadrant_masks, void* workspace, size_t workspace_bytes, void* stream) {
     using namespace bsa;
     if (dtype != BSA_DTYPE_F32 && dtype != BSA_DTYPE_F16 && dtype != BSA_DTYPE_BF16) return BSA_ERR_BAD_DTYPE;
     if (!valid_block(block)) return BSA_ERR_BAD_BLOCK;
@@ -757,6 +767,6 @@ extern "C" int bsa_attention_forward(int dtype, const void* q, const void* k, co
         return BSA_ERR_BAD_SHAPE;
     if (batches == 0) return BSA_OK;
     return attention_forward(dtype, q, k, v, o, lse, row_blocks, row_table, nnz, block_rows, block_cols, batches,
-                             head_dim, scale, causal, key_padding_mask, kpm_batches, kpm_stride,
+                             head_dim, scale, causal, key_padding_mask, kpm_batches, kpm_stride, quadrant_masks != 0,
                              static_cast<uint32_t*>(workspace), static_cast<cudaStream_t>(stream));
 }

@@ -16,7 +16,7 @@
 //              one accumulator dQ += dS Y1.
 //   by columns item = block column c (column layout), X = (K_c, V_c), Y = (Q_r, dO_r):
 //              T1 = S^T, T2 = dP^T (keys on the TMEM lanes, queries along the columns, so lse and
-//              D are per-column vectors read from global memory a block ahead), two operand tiles
+//              D are per-column vectors, brought into shared memory with the block), two operand tiles
 //              P^T and dS^T, two accumulators dV += P^T Y2 and dK += dS^T Y1.
 // All products run on the tensor cores (tcgen05, fp32 accumulators in TMEM, 16-bit operand tiles
 // of 64 x 64 in 128-byte-swizzled shared memory, loaded by TMA); the same shared-memory tile of Y
@@ -94,6 +94,8 @@ struct BwdParams {
                                // accumulation MMAs have retired, so the depth bounds the blocks in flight
     float scale, scale_log2;
     int causal;
+    int quadrants;             // 1: descriptor idx = 4-bit mask of the block's 32 x 32 quadrants in the layout
+                               // (bit 2 * row_half + col_half), the others are masked like causal / padded scores
     const uint8_t* kpm;
     int kpm_div;
     long long kpm_stride;
@@ -367,7 +369,7 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
         const int q4 = lane & 3;                    // position in the quad: columns 8u + 2 * q4 + {0, 1}
         const int row_a = quad * 16 + (lane >> 2);  // this lane's two rows of the 64-row tile: row_a, row_a + 8
         const uint32_t lane_field = (uint32_t)(quad * 32) << 16;
-        const bool masked_op = MASKED && (p.causal != 0 || p.kpm != nullptr);
+        const bool masked_op = MASKED && (p.causal != 0 || p.kpm != nullptr || p.quadrants != 0);
         const float c2 = p.scale_log2, sc = p.scale;
         const int out_rows = COL ? p.seq_k : p.seq_q;
         int s_no = 0, o_no = 0;
@@ -412,6 +414,16 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                     const int s = s_no + t, tb = s & 1;
                     const BlockDesc d = win.get(p.blocks, cur.first, cur.count, t, lane);
                     const int other = COL ? d.row() : d.col();
+                    // quadrant masks: is the half u < 4 / u >= 4 of this lane's 16 columns inside the layout?
+                    // By rows the lane's rows are queries (row half quad / 2) and u / 4 the key half; by
+                    // columns the lane's rows are keys (column half quad / 2) and u / 4 the query (row) half.
+                    bool sub_lo = true, sub_hi = true;
+                    if (MASKED && p.quadrants) {
+                        const uint32_t bits = (uint32_t)d.idx;
+                        const int h = quad >> 1;
+                        sub_lo = COL ? ((bits >> h) & 1u) != 0 : ((bits >> (2 * h)) & 1u) != 0;
+                        sub_hi = COL ? ((bits >> (2 + h)) & 1u) != 0 : ((bits >> (2 * h + 1)) & 1u) != 0;
+                    }
                     [[maybe_unused]] const long long tc0 = BT_CLOCK();
                     ok = __all_sync(0xffffffffu, mbar_wait(&bars->t_full[tb], (uint32_t)(s >> 1) & 1u, abort_flag, p.status)) != 0;
                     if (!ok) break;
@@ -471,6 +483,7 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                                     m_a = pad || (p.causal && opos > pos_a);
                                     m_b = pad || (p.causal && opos > pos_a + 8);
                                 }
+                                if (!(u < 4 ? sub_lo : sub_hi)) { m_a = true; m_b = true; }
                                 if (m_a) pa[e] = 0.f;
                                 if (m_b) pb[e] = 0.f;
                             }
@@ -614,7 +627,7 @@ int attention_backward(int dtype, const void* q, const void* k, const void* v, c
                        const int32_t* col_blocks, const int32_t* col_table,
                        int64_t nnz, int64_t block_rows, int64_t block_cols, int64_t batches, int64_t head_dim,
                        float scale, int causal, const uint8_t* kpm, int64_t kpm_batches, int64_t kpm_stride,
-                       float2* stats, uint32_t* workspace, cudaStream_t stream) {
+                       int quadrants, float2* stats, uint32_t* workspace, cudaStream_t stream) {
     {
         int dev = 0;   // binds the device's primary context to this thread (the driver call behind make_map needs it)
         if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) { cudaGetLastError(); return BSA_ERR_LAUNCH; }
@@ -650,6 +663,7 @@ int attention_backward(int dtype, const void* q, const void* k, const void* v, c
     p.scale = scale;
     p.scale_log2 = scale * kLog2e;
     p.causal = causal;
+    p.quadrants = quadrants;
     p.kpm = kpm;
     p.kpm_div = kpm ? (int)(batches / kpm_batches) : 1;
     p.kpm_stride = kpm_stride;
@@ -660,7 +674,7 @@ int attention_backward(int dtype, const void* q, const void* k, const void* v, c
     const uint32_t common = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(kTile >> 4) << 24);
     p.idesc_t = common | ((uint32_t)(kTile >> 3) << 17);
     p.idesc_acc = common | (1u << 16) | ((uint32_t)(head_dim >> 3) << 17);
-    const bool masked = causal != 0 || kpm != nullptr;
+    const bool masked = causal != 0 || kpm != nullptr || quadrants != 0;
 
     // dQ by rows: X = (Q_r, dO_r), Y = (K_c, V_c)
     p.blocks = reinterpret_cast<const BlockDesc*>(row_blocks);
@@ -696,7 +710,7 @@ extern "C" int bsa_attention_backward(int dtype, const void* q, const void* k, c
                                       int64_t nnz, int64_t block_rows, int64_t block_cols, int64_t batches,
                                       int64_t head_dim, int block, float scale, int causal,
                                       const uint8_t* key_padding_mask, int64_t kpm_batches, int64_t kpm_stride,
-                                      void* stats, size_t stats_bytes,
+                                      int quadrant_masks, void* stats, size_t stats_bytes,
                                       void* workspace, size_t workspace_bytes, void* stream) {
     using namespace bsa;
     if (dtype != BSA_DTYPE_F32 && dtype != BSA_DTYPE_F16 && dtype != BSA_DTYPE_BF16) return BSA_ERR_BAD_DTYPE;
@@ -719,6 +733,6 @@ extern "C" int bsa_attention_backward(int dtype, const void* q, const void* k, c
     if (batches == 0) return BSA_OK;
     return attention_backward(dtype, q, k, v, o, dout, lse, dq, dk, dv, row_blocks, row_table, col_blocks, col_table,
                               nnz, block_rows, block_cols, batches, head_dim, scale, causal, key_padding_mask,
-                              kpm_batches, kpm_stride, static_cast<float2*>(stats),
+                              kpm_batches, kpm_stride, quadrant_masks != 0, static_cast<float2*>(stats),
                               static_cast<uint32_t*>(workspace), static_cast<cudaStream_t>(stream));
 }

@@ -200,7 +200,8 @@ torch::Tensor sparse_softmax_backward(torch::Tensor y, torch::Tensor dy, torch::
 // q [..., seq_q, d], k and v [..., seq_k, d]; 16-bit types, block 64, d = 64 or 128.
 std::tuple<torch::Tensor, torch::Tensor> sparse_attention_forward(
         torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor row_blocks, torch::Tensor row_table,
-        int64_t block, int64_t block_cols, double scale, bool causal, c10::optional<torch::Tensor> key_padding_mask) {
+        int64_t block, int64_t block_cols, double scale, bool causal, c10::optional<torch::Tensor> key_padding_mask,
+        bool quadrant_masks) {
     TORCH_CHECK(q.is_cuda() && k.is_cuda() && v.is_cuda(), "q, k, v must be CUDA tensors");
     TORCH_CHECK(q.dim() >= 3 && k.dim() == q.dim() && v.dim() == q.dim(), "q, k, v must be [..., seq, head_dim]");
     TORCH_CHECK(q.scalar_type() == k.scalar_type() && q.scalar_type() == v.scalar_type(), "q, k, v must share a dtype");
@@ -236,7 +237,7 @@ std::tuple<torch::Tensor, torch::Tensor> sparse_attention_forward(
         check_status(bsa_attention_forward(dtype, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
                                            lse.data_ptr<float>(), row_blocks.data_ptr<int>(), row_table.data_ptr<int>(),
                                            nnz, block_rows, block_cols, q.size(0), d, static_cast<int>(block),
-                                           static_cast<float>(scale), causal, kpm, kpm_batches, kpm_stride,
+                                           static_cast<float>(scale), causal, kpm, kpm_batches, kpm_stride, quadrant_masks,
                                            ws.data_ptr(), BSA_WORKSPACE_BYTES, at::cuda::getCurrentCUDAStream().stream()),
                      "sparse_attention_forward");
     }
@@ -251,7 +252,7 @@ std::tuple<torch::Tensor, torch::Tensor> sparse_attention_forward(
 std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> sparse_attention_backward(
         torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor o, torch::Tensor dout, torch::Tensor lse,
         torch::Tensor row_blocks, torch::Tensor row_table, torch::Tensor col_blocks, torch::Tensor col_table,
-        int64_t block, double scale, bool causal, c10::optional<torch::Tensor> key_padding_mask) {
+        int64_t block, double scale, bool causal, c10::optional<torch::Tensor> key_padding_mask, bool quadrant_masks) {
     TORCH_CHECK(q.is_cuda() && k.is_cuda() && v.is_cuda() && o.is_cuda() && dout.is_cuda() && lse.is_cuda(),
                 "all tensors must be CUDA tensors");
     TORCH_CHECK(q.dim() >= 3 && k.dim() == q.dim() && v.dim() == q.dim(), "q, k, v must be [..., seq, head_dim]");
@@ -299,7 +300,7 @@ std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> sparse_attention_backwar
                                             row_blocks.data_ptr<int>(), row_table.data_ptr<int>(),
                                             col_blocks.data_ptr<int>(), col_table.data_ptr<int>(),
                                             nnz, block_rows, block_cols, q.size(0), d, static_cast<int>(block),
-                                            static_cast<float>(scale), causal, kpm, kpm_batches, kpm_stride,
+                                            static_cast<float>(scale), causal, kpm, kpm_batches, kpm_stride, quadrant_masks,
                                             stats.data_ptr(), static_cast<size_t>(stats.numel()) * 4,
                                             ws.data_ptr(), BSA_WORKSPACE_BYTES, at::cuda::getCurrentCUDAStream().stream()),
                      "sparse_attention_backward");
@@ -406,12 +407,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           "Fused block-sparse attention forward; returns (output, log-sum-exp).",
           py::arg("q"), py::arg("k"), py::arg("v"), py::arg("row_blocks"), py::arg("row_table"), py::arg("block"),
           py::arg("block_cols"), py::arg("scale") = 1.0, py::arg("causal") = false,
-          py::arg("key_padding_mask") = py::none());
+          py::arg("key_padding_mask") = py::none(), py::arg("quadrant_masks") = false);
     m.def("sparse_attention_backward", &sparse_attention_backward,
           "Fused block-sparse attention backward; returns (dq, dk, dv).",
           py::arg("q"), py::arg("k"), py::arg("v"), py::arg("o"), py::arg("dout"), py::arg("lse"),
           py::arg("row_blocks"), py::arg("row_table"), py::arg("col_blocks"), py::arg("col_table"), py::arg("block"),
-          py::arg("scale") = 1.0, py::arg("causal") = false, py::arg("key_padding_mask") = py::none());
+          py::arg("scale") = 1.0, py::arg("causal") = false, py::arg("key_padding_mask") = py::none(),
+          py::arg("quadrant_masks") = false);
     m.def("build_layout", &build_layout, "Build row / column layout metadata on the device.", py::arg("pattern"));
     m.def("dense_to_sparse", &dense_to_sparse, "Gather the layout's blocks from a dense matrix.");
     m.def("sparse_to_dense", &sparse_to_dense, "Scatter blocks into a zero-filled dense matrix.");

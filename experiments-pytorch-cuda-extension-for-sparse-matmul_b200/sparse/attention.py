@@ -6,12 +6,15 @@ The reference has no such op: a caller composes it from its matmul in "sdd"
 mode (sparse/matmul.py:55-57), a softmax and its matmul in "dsd" mode, and
 every step writes the ``[..., nnz, block, block]`` tensor to memory.
 ``attention`` computes the same result in one kernel launch where the fused
-kernel applies (fp16 / bf16, block 64 or 128, head dim 64 or 128) and composes
-the three unfused ops otherwise, so it can be called for any layout and dtype.
-The kernel works on 64 x 64 blocks and touches no sparse tensor, only the
-positions of the blocks: a block-128 layout runs as the block-64 layout with
-every block split in 2 x 2 (the element-level masks do not depend on the
-block size).
+kernel applies (fp16 / bf16, block 32, 64 or 128, head dim 64 or 128) and
+composes the three unfused ops otherwise, so it can be called for any layout
+and dtype.  The kernels work on 64 x 64 blocks and touch no sparse tensor,
+only the positions of the blocks: a block-128 layout runs as the block-64
+layout with every block split in 2 x 2, a block-32 layout (with an even
+number of block rows and columns) as the layout of the 64 x 64 blocks that
+contain its blocks, each with a 4-bit mask of the 32 x 32 quadrants that
+belong to the layout (carried in the descriptors' idx field, which the fused
+kernels do not use); the element-level masks do not depend on the block size.
 
 The backward pass of the fused path is fused as well: the forward keeps only
 the output and the row log-sum-exp, and two kernels (dQ by block rows; dK and
@@ -39,28 +42,60 @@ fused_backward = True      # False: compose the backward of the fused forward fr
 
 def fused_supported(q: torch.Tensor, layout: SparseLayout) -> bool:
     """True where the one-kernel forward applies."""
-    return (q.is_cuda and q.dtype in (torch.float16, torch.bfloat16) and layout.block in (64, 128)
-            and 2 * layout.pattern.size(0) <= 65535 and 2 * layout.pattern.size(1) <= 65535
-            and q.size(-1) in (64, 128))
+    rows, cols = layout.pattern.size(0), layout.pattern.size(1)
+    if layout.block == 32:
+        shape_ok = rows % 2 == 0 and cols % 2 == 0
+    elif layout.block == 128:
+        shape_ok = 2 * rows <= 65535 and 2 * cols <= 65535
+    else:
+        shape_ok = layout.block == 64
+    return q.is_cuda and q.dtype in (torch.float16, torch.bfloat16) and shape_ok and q.size(-1) in (64, 128)
 
 
-def _kernel_layout(layout: SparseLayout) -> SparseLayout:
-    """The layout in the kernel's 64 x 64 blocks (built once per layout object)."""
+class _KernelLayout:
+    """What the fused kernels get: row / column descriptors of 64 x 64 blocks and the quadrant flag."""
+
+    def __init__(self, row_layout, col_layout, block_cols: int, quadrant_masks: bool):
+        self.row_layout, self.col_layout = row_layout, col_layout
+        self.block_cols, self.quadrant_masks = block_cols, quadrant_masks
+
+
+def _kernel_layout(layout: SparseLayout) -> _KernelLayout:
+    """The layout in the kernels' 64 x 64 blocks (built once per layout object)."""
+    cached = getattr(layout, "_fused_layout", None)
+    if cached is not None:
+        return cached
     if layout.block == 64:
-        return layout
-    split = getattr(layout, "_split64", None)
-    if split is None:
+        fine = _KernelLayout(layout.row_layout, layout.col_layout, layout.pattern.size(1), False)
+    elif layout.block == 128:
         pattern = (layout.pattern != 0).to(torch.uint8).repeat_interleave(2, 0).repeat_interleave(2, 1)
         split = SparseLayout(pattern, block=64, device=layout.device)
-        layout._split64 = split
-    return split
+        fine = _KernelLayout(split.row_layout, split.col_layout, pattern.size(1), False)
+    else:
+        on = (layout.pattern != 0).to(torch.int32).cpu()
+        rows, cols = on.size(0) // 2, on.size(1) // 2
+        quads = on.reshape(rows, 2, cols, 2)
+        # bit 2 * row_half + col_half of a coarse block = its 32 x 32 quadrant is in the layout
+        bits = quads[:, 0, :, 0] + 2 * quads[:, 0, :, 1] + 4 * quads[:, 1, :, 0] + 8 * quads[:, 1, :, 1]
+        coarse = SparseLayout((bits != 0).to(torch.uint8), block=64, device=layout.device)
+        rank_bits = bits[bits != 0].to(device=layout.device, dtype=torch.int32)      # by row-major rank
+
+        def with_masks(blocks: torch.Tensor) -> torch.Tensor:
+            pairs = blocks.view(-1, 2).clone()
+            pairs[:, 0] = rank_bits[pairs[:, 0].long()]        # idx (the rank) -> the block's quadrant mask
+            return pairs.view(-1).contiguous()
+
+        fine = _KernelLayout((with_masks(coarse.row_layout[0]), coarse.row_layout[1]),
+                             (with_masks(coarse.col_layout[0]), coarse.col_layout[1]), cols, True)
+    layout._fused_layout = fine
+    return fine
 
 
 def _fused_forward(q, k, v, layout, scale, causal, key_padding_mask):
     fine = _kernel_layout(layout)
-    row_blocks, row_table = fine.row_layout
     return kernel.sparse_ops.sparse_attention_forward(
-        q, k, v, row_blocks, row_table, 64, fine.pattern.size(1), float(scale), bool(causal), key_padding_mask)
+        q, k, v, fine.row_layout[0], fine.row_layout[1], 64, fine.block_cols, float(scale), bool(causal),
+        key_padding_mask, fine.quadrant_masks)
 
 
 class SparseAttention(torch.autograd.Function):
@@ -81,7 +116,7 @@ class SparseAttention(torch.autograd.Function):
             fine = _kernel_layout(layout)
             dq, dk, dv = ops.sparse_attention_backward(
                 q, k, v, out, dout.contiguous(), lse, fine.row_layout[0], fine.row_layout[1],
-                fine.col_layout[0], fine.col_layout[1], 64, ctx.scale, ctx.causal, ctx.kpm)
+                fine.col_layout[0], fine.col_layout[1], 64, ctx.scale, ctx.causal, ctx.kpm, fine.quadrant_masks)
             return dq, dk, dv, None, None, None, None
         rows, cols, block = layout.row_layout, layout.col_layout, layout.block
         hint = getattr(layout, "max_row_blocks", 0)

@@ -175,6 +175,13 @@ int bsa_softmax_backward(int dtype, const void* y, const void* dy, void* dx,
  *   row_table       the ROW layout
  *   causal, key_padding_mask, kpm_batches, kpm_stride
  *                   as in bsa_softmax_forward
+ *   quadrant_masks  0, or 1: the idx field of every descriptor holds, instead of
+ *                   the block's rank, a 4-bit mask of the 32 x 32 quadrants
+ *                   of the block that belong to the layout (bit 2 * row_half
+ *                   + col_half); scores in the other quadrants are masked.
+ *                   This is how a layout of 32 x 32 blocks runs through the
+ *                   kernel: as the layout of the 64 x 64 blocks that contain
+ *                   them (the kernel never uses the rank).
  * Supported: BSA_DTYPE_F16 / BSA_DTYPE_BF16, block 64, head_dim 64 or 128;
  * anything else returns BSA_ERR_BAD_DTYPE / BSA_ERR_BAD_SHAPE without
  * launching (callers then compose the unfused operators).
@@ -184,6 +191,7 @@ int bsa_attention_forward(int dtype, const void* q, const void* k, const void* v
                           int64_t nnz, int64_t block_rows, int64_t block_cols, int64_t batches,
                           int64_t head_dim, int block, float scale, int causal,
                           const uint8_t* key_padding_mask, int64_t kpm_batches, int64_t kpm_stride,
+                          int quadrant_masks,
                           void* workspace, size_t workspace_bytes, void* stream);
 
 /*
@@ -201,7 +209,8 @@ int bsa_attention_forward(int dtype, const void* q, const void* k, const void* v
  *   lse             float [batches, block_rows * block] as written by the forward
  *   stats           scratch of at least batches * block_rows * block * 8 bytes,
  *                   16-byte aligned (`stats_bytes` = its size)
- *   masks, scale    as given to the forward
+ *   masks, scale, quadrant_masks
+ *                   as given to the forward (with quadrant masks in both layouts)
  * Supported combinations and error codes as for bsa_attention_forward.
  */
 int bsa_attention_backward(int dtype, const void* q, const void* k, const void* v, const void* o,
@@ -211,6 +220,7 @@ int bsa_attention_backward(int dtype, const void* q, const void* k, const void* 
                            int64_t nnz, int64_t block_rows, int64_t block_cols, int64_t batches,
                            int64_t head_dim, int block, float scale, int causal,
                            const uint8_t* key_padding_mask, int64_t kpm_batches, int64_t kpm_stride,
+                           int quadrant_masks,
                            void* stats, size_t stats_bytes,
                            void* workspace, size_t workspace_bytes, void* stream);
 

@@ -29,10 +29,10 @@ def _library():
                                          ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
                                          ctypes.c_int64, ctypes.c_int, ctypes.c_float, ctypes.c_int64, ctypes.c_void_p]
     lib.bsa_attention_forward.argtypes = [ctypes.c_int] + [ctypes.c_void_p] * 7 + [ctypes.c_int64] * 5 + \
-        [ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
+        [ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,
          ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
     lib.bsa_attention_backward.argtypes = [ctypes.c_int] + [ctypes.c_void_p] * 13 + [ctypes.c_int64] * 5 + \
-        [ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
+        [ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,
          ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
     lib.bsa_workspace_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
     return lib
@@ -133,7 +133,7 @@ def test_softmax_and_attention_write_only_their_outputs(dtype):
     ws = torch.zeros(256, dtype=torch.uint8, device="cuda")
     st = lib.bsa_attention_forward(1, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.view.data_ptr(), lse.view.data_ptr(),
                                    blk.data_ptr(), tab.data_ptr(), nnz, pattern.shape[0], pattern.shape[1], z, d, block,
-                                   0.1, 0, None, 0, 0, ws.data_ptr(), 256, stream)
+                                   0.1, 0, None, 0, 0, 0, ws.data_ptr(), 256, stream)
     assert st == 0, st
     o.check("attention forward output")
     torch.cuda.synchronize()
@@ -149,7 +149,7 @@ def test_softmax_and_attention_write_only_their_outputs(dtype):
     st = lib.bsa_attention_backward(1, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.view.data_ptr(), do.data_ptr(),
                                     lse.view.data_ptr(), dq.view.data_ptr(), dk.view.data_ptr(), dv.view.data_ptr(),
                                     blk.data_ptr(), tab.data_ptr(), cblk.data_ptr(), ctab.data_ptr(),
-                                    nnz, pattern.shape[0], pattern.shape[1], z, d, block, 0.1, 0, None, 0, 0,
+                                    nnz, pattern.shape[0], pattern.shape[1], z, d, block, 0.1, 0, None, 0, 0, 0,
                                     stats.view.data_ptr(), stats.view.numel() * 4, ws.data_ptr(), 256, stream)
     assert st == 0, st
     dq.check("attention backward dQ")

@@ -158,3 +158,35 @@ def test_full_size_fused_step_properties_config5():
     sparse_ops.check_device_status(0)
     assert torch.equal(o[tail], o2) and torch.equal(lse[tail], lse2)
     assert torch.equal(dq[tail], dq2) and torch.equal(dk[tail], dk2) and torch.equal(dv[tail], dv2)
+
+
+@pytest.mark.parametrize("dim,dtype", [(64, torch.float16), (128, torch.bfloat16)])
+def test_block32_layout_runs_fused_with_quadrant_masks(dim, dtype):
+    """A layout of 32 x 32 blocks goes through the fused kernels as the layout of the 64 x 64 blocks that
+    contain its blocks, with a 4-bit quadrant mask per block: forward and backward against dense autograd,
+    on a random pattern (every combination of quadrants, coarse rows whose upper or lower half is empty)
+    with padded keys, and on benchmark configuration 2's causal layout."""
+    from sparse import SparseLayout
+    from sparse.attention import _kernel_layout, fused_supported
+    from sparse.patterns import local_global_causal
+    rng = np.random.default_rng(32)
+    pattern = (rng.random((12, 10)) < 0.3).astype(np.int64)
+    pattern[5, :] = 0                     # an empty block row inside a coarse row
+    pattern[:, 4] = 0
+    layout = SparseLayout(torch.as_tensor(pattern), block=32)
+    assert fused_supported(torch.empty(1, 1, dim, device="cuda", dtype=dtype), layout)
+    assert _kernel_layout(layout).quadrant_masks
+    kpm = torch.zeros(3, 320, dtype=torch.uint8)
+    kpm[1, 200:] = 1
+    kpm[2, :40] = 1
+    _grads(pattern, (3, 2), dim, dtype, dim ** -0.5, False, kpm, seed=270, block=32)
+    _grads(local_global_causal(32, 4, 1), (8,), dim, dtype, 0.125, True, None, seed=271, block=32)
+
+
+def test_block32_with_odd_grid_composes_unfused_ops():
+    from sparse import SparseLayout
+    from sparse.attention import fused_supported
+    g = load_golden_layout("empty_row_col_5x4")
+    layout = SparseLayout(torch.as_tensor(np.asarray(g["pattern"])), block=32)
+    assert not fused_supported(torch.empty(1, 1, 64, device="cuda", dtype=torch.float16), layout)
+    _grads(g["pattern"], (2,), 64, torch.float16, 0.2, seed=272, block=32)

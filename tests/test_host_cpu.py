@@ -98,13 +98,13 @@ def test_softmax_and_layout_validation_codes(lib):
 def test_attention_validation_codes(lib):
     f = lib.bsa_attention_forward
     f.argtypes = [ctypes.c_int] + [ctypes.c_void_p] * 7 + [ctypes.c_int64] * 5 + \
-        [ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
+        [ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,
          ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
 
     def call(dtype=1, q=16, o=16, lse=16, blocks=16, nnz=1, rows=1, cols=1, batches=1, d=64, block=64,
              kpm=None, kpm_batches=0, kpm_stride=0, ws=16, ws_bytes=256):
         return f(dtype, q, 16, 16, o, lse, blocks, 16, nnz, rows, cols, batches, d, block, 1.0, 0,
-                 kpm, kpm_batches, kpm_stride, ws, ws_bytes, None)
+                 kpm, kpm_batches, kpm_stride, 0, ws, ws_bytes, None)
 
     # rejected on the host before any CUDA call (the pointers are fake)
     assert call(dtype=9) == 3                      # BSA_ERR_BAD_DTYPE
@@ -245,13 +245,13 @@ def test_head_sharding_is_world_size_independent(tmp_path):
 def test_attention_backward_validation_codes(lib):
     f = lib.bsa_attention_backward
     f.argtypes = [ctypes.c_int] + [ctypes.c_void_p] * 13 + [ctypes.c_int64] * 5 + \
-        [ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
+        [ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,
          ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
 
     def call(dtype=1, q=16, dq=16, lse=16, col_blocks=16, nnz=1, rows=1, cols=1, batches=1, d=64, block=64,
              kpm=None, kpm_batches=0, kpm_stride=0, stats=16, stats_bytes=512, ws=16, ws_bytes=256):
         return f(dtype, q, 16, 16, 16, 16, lse, dq, 16, 16, 16, 16, col_blocks, 16, nnz, rows, cols, batches, d, block,
-                 1.0, 0, kpm, kpm_batches, kpm_stride, stats, stats_bytes, ws, ws_bytes, None)
+                 1.0, 0, kpm, kpm_batches, kpm_stride, 0, stats, stats_bytes, ws, ws_bytes, None)
 
     # rejected on the host before any CUDA call (the pointers are fake)
     assert call(dtype=9) == 3                      # BSA_ERR_BAD_DTYPE

@@ -3,8 +3,9 @@
 The reference stops at the operators (sparse/__init__.py:1-2 exports a layout
 class and a matmul); this is the caller a user of those operators writes on
 top of them: packed QKV projection, ``attention`` over a ``SparseLayout``,
-output projection.  Block 64 with head dimension 64 or 128 in fp16 / bf16 runs
-the fused kernel; every other combination composes the unfused operators.
+output projection.  Blocks 32 (even block grid), 64 and 128 with head dimension
+64 or 128 in fp16 / bf16 run the fused forward and backward kernels; every
+other combination composes the unfused operators.
 """
 from typing import Optional
 

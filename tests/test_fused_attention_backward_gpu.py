@@ -79,14 +79,15 @@ def test_backward_many_items_per_cta():
     _grads(bigbird(64, 1, 2, 3, 77), (8,), 64, torch.float16, 0.125, seed=230)
 
 
+@pytest.mark.parametrize("dim", [64, 128])
 @pytest.mark.parametrize("causal", [False, True])
-def test_short_rows_and_several_items_per_cta(causal):
+def test_short_rows_and_several_items_per_cta(causal, dim):
     """Block rows and columns of 1 to 3 blocks with four to five work items per CTA, with and without the
     element-level masks: the hand-over of the accumulators between consecutive items happens after very
     few blocks, so every barrier involved must be waited on by the same warps in every phase (an earlier
     version let the owner of an item's last block finish the item and ran into a time-out here)."""
     from sparse.patterns import local_global_causal
-    _grads(local_global_causal(16, 2, 1), (40,), 64, torch.float16, 0.125, causal, None, seed=260)
+    _grads(local_global_causal(16, 2, 1), (40,), dim, torch.float16, dim ** -0.5, causal, None, seed=260)
 
 
 def test_backward_negative_scale():

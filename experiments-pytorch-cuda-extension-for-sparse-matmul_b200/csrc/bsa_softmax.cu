@@ -160,6 +160,15 @@ __device__ __forceinline__ void scale_and_mask(float (&v)[N], float scale_log2e,
     }
 }
 
+// Bit e set = element e of a chunk lies above the diagonal (key position > query position).
+template <int N>
+__device__ __forceinline__ uint32_t causal_bits(int q_pos, int k_pos0) {
+    constexpr uint32_t full = (1u << N) - 1u;
+    const int d = q_pos - k_pos0;                       // elements 0 .. d are visible
+    const uint32_t keep = d < 0 ? 0u : (d >= N - 1 ? full : ((2u << d) - 1u));
+    return full & ~keep;
+}
+
 template <typename T, bool kBackward>
 __global__ void __launch_bounds__(kThreads)
 softmax_kernel(const SoftmaxParams p) {
@@ -470,18 +479,26 @@ softmax_rows_kernel(const SoftmaxParams p) {
     const int team = threadIdx.x / L, t = threadIdx.x & (L - 1);
     const int rows_per_pass = kThreads / L;
 
+    const uint8_t* kpm_row = (kMasked && p.kpm) ? p.kpm + (z / p.batches_per_kpm) * p.kpm_stride : nullptr;
     uint32_t base[CH];                            // element offset of the lane's chunk in row 0, or ~0
     int kpos[kMasked ? CH : 1];                   // key position of the chunk's first element
+    uint32_t kbits[kMasked ? CH : 1];             // bit e: key kpos + e is padding (the same for every row)
 #pragma unroll
     for (int k = 0; k < CH; ++k) {
         const int q = t + k * L;
         base[k] = 0xFFFFFFFFu;
-        if (kMasked) kpos[k] = 0;
+        if (kMasked) { kpos[k] = 0; kbits[k] = 0u; }
         if (q < n_chunks) {
             const int j = q >> cps_shift, s = q & (cps - 1);
             const BlockDesc d = p.row_blocks[first + j];
             base[k] = (uint32_t)d.idx * (uint32_t)(block * block) + (uint32_t)(s * N);
-            if (kMasked) kpos[k] = d.col() * block + s * N;
+            if (kMasked) {
+                kpos[k] = d.col() * block + s * N;
+                if (kpm_row != nullptr) {
+#pragma unroll
+                    for (int e = 0; e < N; ++e) kbits[k] |= (kpm_row[kpos[k] + e] != 0 ? 1u : 0u) << e;
+                }
+            }
         }
     }
 
@@ -489,7 +506,6 @@ softmax_rows_kernel(const SoftmaxParams p) {
     const T* in0 = static_cast<const T*>(p.in0) + zoff;
     const T* in1 = kBackward ? static_cast<const T*>(p.in1) + zoff : nullptr;
     T* out = static_cast<T*>(p.out) + zoff;
-    const uint8_t* kpm_row = (kMasked && p.kpm) ? p.kpm + (z / p.batches_per_kpm) * p.kpm_stride : nullptr;
     const float scale_log2e = p.scale * kLog2e;
     const bool causal = kMasked && p.causal != 0;
     const bool negate = scale_log2e < 0.f;
@@ -559,9 +575,11 @@ softmax_rows_kernel(const SoftmaxParams p) {
                         if (kMasked) {
                             float v[N];
                             Vec<T>::unpack(x[u][k], v);
-                            scale_and_mask<N>(v, scale_log2e, r * block + i, kpos[kMasked ? k : 0], causal, kpm_row);
+                            const uint32_t bits = kbits[kMasked ? k : 0] |
+                                                  (causal ? causal_bits<N>(r * block + i, kpos[kMasked ? k : 0]) : 0u);
 #pragma unroll
-                            for (int e = 0; e < N; ++e) mx[u] = fmaxf(mx[u], v[e]);
+                            for (int e = 0; e < N; ++e)
+                                mx[u] = fmaxf(mx[u], ((bits >> e) & 1u) ? -CUDART_INF_F : v[e] * scale_log2e);
                         } else {
                             mx[u] = fmaxf(mx[u], Packed<T>::signed_max(x[u][k], negate));
                         }
@@ -583,9 +601,11 @@ softmax_rows_kernel(const SoftmaxParams p) {
                         float v[N];
                         Vec<T>::unpack(x[u][k], v);
                         if (kMasked) {
-                            scale_and_mask<N>(v, scale_log2e, r * block + i, kpos[kMasked ? k : 0], causal, kpm_row);
+                            const uint32_t bits = kbits[kMasked ? k : 0] |
+                                                  (causal ? causal_bits<N>(r * block + i, kpos[kMasked ? k : 0]) : 0u);
 #pragma unroll
-                            for (int e = 0; e < N; ++e) v[e] = fast_exp2(v[e] - mx[u]);
+                            for (int e = 0; e < N; ++e)
+                                v[e] = ((bits >> e) & 1u) ? 0.f : fast_exp2(fmaf(v[e], scale_log2e, -mx[u]));
                         } else {
 #pragma unroll
                             for (int e = 0; e < N; ++e) v[e] = fast_exp2(fmaf(v[e], scale_log2e, -mx[u]));

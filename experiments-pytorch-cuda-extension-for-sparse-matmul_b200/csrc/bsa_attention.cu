@@ -434,26 +434,46 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     release_accumulator(&bars->s_empty[(s_no + t) & 1], lane);
                     if (warp == 4 && lane == 0) AT_ADD(6, AT_CLOCK() - t0);
                 };
-                auto process = [&](const uint32_t (&r)[32], int t) -> bool {
+                // Masked elements (above the diagonal, padded keys, quadrants outside a block-32 layout) are
+                // overwritten in registers by -inf (+inf for a negative scale) before the common code runs:
+                // they then lose every maximum and their exp2 is exactly 0 (the host keeps the scale factor
+                // away from 0, so inf * scale is never NaN).  One copy of the softmax code for both kernel
+                // variants: separate masked code cost the softmax warps, which bound the kernel, 40 % more
+                // instructions, and two copies cost registers.
+                // (the mask of a block is computed before the wait for its S tile: off the critical chain)
+                auto mask_of = [&](int t) -> uint32_t {
+                    if (MASKED && masked_op) return block_mask(win.get(p.blocks, cur.first, cur.count, t, lane));
+                    return 0u;
+                };
+                auto process = [&](uint32_t (&r)[32], int t, const uint32_t mask) -> bool {
+                    if (MASKED && masked_op) {
+                        if (mask != 0u) {
+                            const uint32_t gone = flip ? 0x7F800000u : 0xFF800000u;
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                const int u = i >> 1, e = i & 1;
+                                if ((mask >> i) & 1u) r[4 * u + e] = gone;
+                                if ((mask >> (16 + i)) & 1u) r[4 * u + 2 + e] = gone;
+                            }
+                        }
+                    }
                     const int s = s_no + t;                                  // tile number = P buffer number
-                    uint32_t mask = 0u;
                     [[maybe_unused]] const long long tm0 = AT_CLOCK();
-                    if (MASKED && masked_op) mask = block_mask(win.get(p.blocks, cur.first, cur.count, t, lane));
                     // block maxima of the raw scores (for a negative scale: of their negatives)
                     float x_a = -INFINITY, x_b = -INFINITY;
                     if (!flip) {
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
                             const int u = i >> 1, e = i & 1;
-                            if (!MASKED || !((mask >> i) & 1u)) x_a = fmaxf(x_a, __uint_as_float(r[4 * u + e]));
-                            if (!MASKED || !((mask >> (16 + i)) & 1u)) x_b = fmaxf(x_b, __uint_as_float(r[4 * u + 2 + e]));
+                            x_a = fmaxf(x_a, __uint_as_float(r[4 * u + e]));
+                            x_b = fmaxf(x_b, __uint_as_float(r[4 * u + 2 + e]));
                         }
                     } else {
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
                             const int u = i >> 1, e = i & 1;
-                            if (!MASKED || !((mask >> i) & 1u)) x_a = fmaxf(x_a, -__uint_as_float(r[4 * u + e]));
-                            if (!MASKED || !((mask >> (16 + i)) & 1u)) x_b = fmaxf(x_b, -__uint_as_float(r[4 * u + 2 + e]));
+                            x_a = fmaxf(x_a, -__uint_as_float(r[4 * u + e]));
+                            x_b = fmaxf(x_b, -__uint_as_float(r[4 * u + 2 + e]));
                         }
                     }
                     x_a = fmaxf(x_a, __shfl_xor_sync(0xffffffffu, x_a, 1)); x_a = fmaxf(x_a, __shfl_xor_sync(0xffffffffu, x_a, 2));
@@ -512,8 +532,6 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         for (int e = 0; e < 2; ++e) {
                             pa[e] = attn_exp2(fmaf(__uint_as_float(r[4 * u + e]), c2, -sub_a));
                             pb2[e] = attn_exp2(fmaf(__uint_as_float(r[4 * u + 2 + e]), c2, -sub_b));
-                            if (MASKED && ((mask >> (2 * u + e)) & 1u)) pa[e] = 0.f;
-                            if (MASKED && ((mask >> (16 + 2 * u + e)) & 1u)) pb2[e] = 0.f;
                             l_a += pa[e];
                             l_b += pb2[e];
                         }
@@ -532,24 +550,26 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     // The TMEM load of block j + 1 is in flight while block j is worked on (two
                     // register buffers, loop unrolled by two).
                     uint32_t ra[32], rb[32];
+                    uint32_t ma = mask_of(0), mb = 0u;
                     ok = load(ra, 0);
                     for (int t = 0; ok && t < n; t += 2) {
                         loaded(t);
-                        if (t + 1 < n) ok = load(rb, t + 1);
-                        if (!process(ra, t)) ok = false;
+                        if (t + 1 < n) { mb = mask_of(t + 1); ok = load(rb, t + 1); }
+                        if (!process(ra, t, ma)) ok = false;
                         if (!ok || t + 1 >= n) break;
                         loaded(t + 1);
-                        if (t + 2 < n) ok = load(ra, t + 2);
-                        if (!process(rb, t + 1)) ok = false;
+                        if (t + 2 < n) { ma = mask_of(t + 2); ok = load(ra, t + 2); }
+                        if (!process(rb, t + 1, mb)) ok = false;
                     }
                 } else {
                     // two groups already keep two blocks in flight: one register buffer
                     uint32_t r[32];
                     for (int t = t_first; ok && t < n; t += 2) {
+                        const uint32_t m = mask_of(t);
                         ok = load(r, t);
                         if (!ok) break;
                         loaded(t);
-                        if (!process(r, t)) ok = false;
+                        if (!process(r, t, m)) ok = false;
                     }
                 }
                 s_no += n;
@@ -718,6 +738,7 @@ int attention_forward(int dtype, const void* q, const void* k, const void* v, vo
     p.items = (int)(batches * block_rows);
     p.seq_q = (int)seq_q; p.seq_k = (int)seq_k; p.head_dim = (int)head_dim;
     p.scale_log2 = scale * 1.4426950408889634f;
+    if (p.scale_log2 == 0.f) p.scale_log2 = 1e-30f;      // all scores equal, and inf * scale_log2 stays inf for masked ones
     p.causal = causal;
     p.quadrants = quadrants;
     p.kpm = kpm;

@@ -43,6 +43,8 @@
 // 560 / 750 cycles: the kernels sit at 55-60 % of that bound, like the forward kernel.
 // Loops are warp-uniform with an elected lane around the TMA / tcgen05 instructions.  All waits are
 // bounded (BSA_ERR_DEVICE_TIMEOUT in the workspace word).
+#include <type_traits>
+
 #include "bsa_tc_common.cuh"
 
 namespace bsa {
@@ -457,51 +459,77 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                     [[maybe_unused]] const long long tc3 = BT_CLOCK();
                     const uint32_t tile0 = smem_u32(op_smem + (ob * kOpTiles) * kTileBytes) + op_row;
                     const int other0 = other * kTile + 2 * q4;          // position of column u = 0, e = 0
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        float pa[2], pb[2], da[2], db[2];
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            float lse_a, lse_b, dl_a, dl_b;
-                            if (COL) {
-                                lse_a = lse_b = e == 0 ? cs[u].x : cs[u].z;
-                                dl_a = dl_b = e == 0 ? cs[u].y : cs[u].w;
-                            } else {
-                                lse_a = st_a.x; dl_a = st_a.y; lse_b = st_b.x; dl_b = st_b.y;
-                            }
-                            pa[e] = attn_exp2(fmaf(__uint_as_float(r1[4 * u + e]), c2, -lse_a));
-                            pb[e] = attn_exp2(fmaf(__uint_as_float(r1[4 * u + 2 + e]), c2, -lse_b));
-                            if (MASKED && masked_op) {
-                                const int opos = other0 + 8 * u + e;
-                                bool m_a, m_b;
-                                if (COL) {
-                                    // lane rows are keys, columns are queries
-                                    m_a = pad_a || (p.causal && pos_a > opos);
-                                    m_b = pad_b || (p.causal && pos_a + 8 > opos);
-                                } else {
-                                    const bool pad = kpm_row != nullptr && kpm_row[opos] != 0;
-                                    m_a = pad || (p.causal && opos > pos_a);
-                                    m_b = pad || (p.causal && opos > pos_a + 8);
-                                }
-                                if (!(u < 4 ? sub_lo : sub_hi)) { m_a = true; m_b = true; }
-                                if (m_a) pa[e] = 0.f;
-                                if (m_b) pb[e] = 0.f;
-                            }
-                            da[e] = pa[e] * (__uint_as_float(r2[4 * u + e]) - dl_a) * sc;
-                            db[e] = pb[e] * (__uint_as_float(r2[4 * u + 2 + e]) - dl_b) * sc;
-                        }
-                        const uint32_t addr = tile0 + (((uint32_t)u ^ op_xor) << 4);
+                    // Does any lane of the warp have a masked element in this block?  Most blocks of a causal
+                    // or padded problem have none and take the plain code (the element-wise tests cost the
+                    // compute warps half as many instructions again).
+                    bool need = false;
+                    uint32_t padbits = 0u;          // by rows: bit 2u + e = key column 8u + 2 q4 + e is padding
+                    if (MASKED && masked_op) {
+                        bool lane_need = !(sub_lo && sub_hi);
+                        if (p.causal) lane_need = lane_need || (COL ? pos_a + 8 > other * kTile : other * kTile + kTile - 1 > pos_a);
                         if (COL) {
-                            // tile 0: P^T, tile 1: dS^T
-                            asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(pack2<BF16>(pa[0], pa[1])) : "memory");
-                            asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + 8 * 128), "r"(pack2<BF16>(pb[0], pb[1])) : "memory");
-                            asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + kTileBytes), "r"(pack2<BF16>(da[0], da[1])) : "memory");
-                            asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + kTileBytes + 8 * 128), "r"(pack2<BF16>(db[0], db[1])) : "memory");
-                        } else {
-                            asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(pack2<BF16>(da[0], da[1])) : "memory");
-                            asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + 8 * 128), "r"(pack2<BF16>(db[0], db[1])) : "memory");
+                            lane_need = lane_need || pad_a || pad_b;
+                        } else if (kpm_row != nullptr) {
+                            const uint8_t* kb = kpm_row + other * kTile;
+                            if (__any_sync(0xffffffffu, (kb[lane] | kb[32 + lane]) != 0)) {
+#pragma unroll
+                                for (int i = 0; i < 16; ++i)
+                                    padbits |= (kpm_row[other0 + 8 * (i >> 1) + (i & 1)] != 0 ? 1u : 0u) << i;
+                                lane_need = lane_need || padbits != 0u;
+                            }
                         }
+                        need = __any_sync(0xffffffffu, lane_need) != 0;
                     }
+                    auto emit = [&](auto masked_tag) {
+                        constexpr bool M = decltype(masked_tag)::value;
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            float pa[2], pb[2], da[2], db[2];
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                float lse_a, lse_b, dl_a, dl_b;
+                                if (COL) {
+                                    lse_a = lse_b = e == 0 ? cs[u].x : cs[u].z;
+                                    dl_a = dl_b = e == 0 ? cs[u].y : cs[u].w;
+                                } else {
+                                    lse_a = st_a.x; dl_a = st_a.y; lse_b = st_b.x; dl_b = st_b.y;
+                                }
+                                pa[e] = attn_exp2(fmaf(__uint_as_float(r1[4 * u + e]), c2, -lse_a));
+                                pb[e] = attn_exp2(fmaf(__uint_as_float(r1[4 * u + 2 + e]), c2, -lse_b));
+                                if (M) {
+                                    const int opos = other0 + 8 * u + e;
+                                    bool m_a, m_b;
+                                    if (COL) {
+                                        // lane rows are keys, columns are queries
+                                        m_a = pad_a || (p.causal && pos_a > opos);
+                                        m_b = pad_b || (p.causal && pos_a + 8 > opos);
+                                    } else {
+                                        const bool pad = ((padbits >> (2 * u + e)) & 1u) != 0;
+                                        m_a = pad || (p.causal && opos > pos_a);
+                                        m_b = pad || (p.causal && opos > pos_a + 8);
+                                    }
+                                    if (!(u < 4 ? sub_lo : sub_hi)) { m_a = true; m_b = true; }
+                                    if (m_a) pa[e] = 0.f;
+                                    if (m_b) pb[e] = 0.f;
+                                }
+                                da[e] = pa[e] * (__uint_as_float(r2[4 * u + e]) - dl_a) * sc;
+                                db[e] = pb[e] * (__uint_as_float(r2[4 * u + 2 + e]) - dl_b) * sc;
+                            }
+                            const uint32_t addr = tile0 + (((uint32_t)u ^ op_xor) << 4);
+                            if (COL) {
+                                // tile 0: P^T, tile 1: dS^T
+                                asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(pack2<BF16>(pa[0], pa[1])) : "memory");
+                                asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + 8 * 128), "r"(pack2<BF16>(pb[0], pb[1])) : "memory");
+                                asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + kTileBytes), "r"(pack2<BF16>(da[0], da[1])) : "memory");
+                                asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + kTileBytes + 8 * 128), "r"(pack2<BF16>(db[0], db[1])) : "memory");
+                            } else {
+                                asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(pack2<BF16>(da[0], da[1])) : "memory");
+                                asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + 8 * 128), "r"(pack2<BF16>(db[0], db[1])) : "memory");
+                            }
+                        }
+                    };
+                    if (MASKED && need) emit(std::true_type{});
+                    else                emit(std::false_type{});
                     [[maybe_unused]] const long long tc4 = BT_CLOCK();
                     fence_async_shared();           // generic-proxy writes -> visible to the tensor core's reads
                     __syncwarp();

@@ -74,6 +74,16 @@ def test_fused_forward_causal_and_key_padding():
     _forward_case(full, 64, (1,), 64, torch.float16, 1.0, kpm=dead, seed=42)
 
 
+def test_fused_forward_zero_scale_with_masks():
+    """Scale 0: every unmasked score counts the same (uniform attention) and masked ones stay excluded
+    (the kernel marks them with infinities, which a zero factor must not turn into NaN)."""
+    from sparse.patterns import local_global_causal
+    kpm = torch.zeros(2, 512, dtype=torch.uint8)
+    kpm[0, 100:140] = 1
+    kpm[1, :70] = 1
+    _forward_case(local_global_causal(8, 2, 1), 64, (2, 2), 64, torch.float16, 0.0, True, kpm, seed=45)
+
+
 def test_fused_forward_negative_scale_and_large_scores():
     """The row maximum is taken after scaling (a negative scale flips it), and scores of a few
     hundred do not overflow the exponentials."""

@@ -45,29 +45,21 @@
 namespace bsa {
 namespace {
 
-// Optional role timing (compile with -DBSA_ATTN_TIMING): CTA 0 adds the cycles its roles spent in
-// each phase to 64-bit counters at byte offset 64 of the workspace (slot = counter index).
-#ifdef BSA_ATTN_TIMING
-#define AT_CLOCK() clock64()
-#define AT_ADD(slot, cycles) do { if (blockIdx.x == 0) atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 8 + (slot), (unsigned long long)(cycles)); } while (0)
-#else
-#define AT_CLOCK() 0ll
-#define AT_ADD(slot, cycles) do { } while (0)
-#endif
-
 constexpr int kAttnTmemCols = 256;      // O: columns 0 .. head_dim - 1; S buffers: 128 .. 191, 192 .. 255
 constexpr int kSCol0 = 128;
 constexpr int kMaxRing = 4;
 
 struct __align__(8) AttnBarriers {
-    uint64_t q_full[2], q_empty[2];
+    uint64_t q_full[2];
+    uint64_t q_empty[2][2];         // [issuer group][buffer]: that group's last Q K^T of the item has retired
     uint64_t k_full[kMaxRing];
     uint64_t qk_done[kMaxRing];     // the MMAs of one Q K^T have retired: S is ready and the K stage is free
     uint64_t v_full[kMaxRing];
     uint64_t pv_done[kMaxRing];     // the MMAs of one P V have retired: the P buffer and the V stage are free
     uint64_t s_empty[2];
     uint64_t p_full[2];
-    uint64_t o_full[2], o_empty[2];     // indexed by the parity of the item: each is waited on by one softmax group only
+    uint64_t o_full[2][2];          // [issuer group][parity of the item]: that group's last P V of the item has retired
+    uint64_t o_empty[2];            // indexed by the parity of the item: arrived on by the group that finishes the item
     uint64_t stat_full[2][2], stat_empty[2][2];   // two softmax groups: hand-over of row maxima and sums, [writer][slot]
     uint64_t drain;
     uint32_t tmem_base;
@@ -118,7 +110,10 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int ring_mask = p.ring - 1, vring_mask = p.vring - 1;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < 2; ++s) { mbar_init(&bars->q_full[s], 1); mbar_init(&bars->q_empty[s], 1); mbar_init(&bars->p_full[s], 4); }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&bars->q_full[s], 1); mbar_init(&bars->p_full[s], 4);
+            for (int g = 0; g < 2; ++g) { mbar_init(&bars->q_empty[g][s], 1); mbar_init(&bars->o_full[g][s], 1); }
+        }
         for (int s = 0; s < kMaxRing; ++s) {
             mbar_init(&bars->k_full[s], 1); mbar_init(&bars->qk_done[s], 1);
             mbar_init(&bars->v_full[s], 1); mbar_init(&bars->pv_done[s], 1);
@@ -127,7 +122,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             mbar_init(&bars->s_empty[s], 4);
             for (int d = 0; d < 2; ++d) { mbar_init(&bars->stat_full[d][s], 4); mbar_init(&bars->stat_empty[d][s], 4); }
         }
-        for (int s = 0; s < 2; ++s) { mbar_init(&bars->o_full[s], 1); mbar_init(&bars->o_empty[s], 4); }
+        for (int s = 0; s < 2; ++s) mbar_init(&bars->o_empty[s], 4);
         mbar_init(&bars->drain, 2);
         bars->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -151,7 +146,6 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         int kv_no = 0, q_no = 0;                   // blocks (K or V tile sets) and Q tile sets loaded so far
         bool q_prefetched = false;                 // the current item's Q tile set was requested an item ago
         bool ok = true;
-        [[maybe_unused]] const long long tp_begin = AT_CLOCK();
         Cursor cur;
         cur.init(p);
         BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
@@ -167,7 +161,8 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 auto issue_q = [&](int q, int z, int g) -> bool {        // called by the whole warp
                     const int qb = q & (p.qbufs - 1);
                     const uint32_t use = (uint32_t)(p.qbufs == 2 ? q >> 1 : q);
-                    if (!__all_sync(0xffffffffu, mbar_wait(&bars->q_empty[qb], (use & 1u) ^ 1u, abort_flag, p.status))) return false;
+                    if (!__all_sync(0xffffffffu, mbar_wait(&bars->q_empty[0][qb], (use & 1u) ^ 1u, abort_flag, p.status))) return false;
+                    if (WGS == 2 && !__all_sync(0xffffffffu, mbar_wait(&bars->q_empty[1][qb], (use & 1u) ^ 1u, abort_flag, p.status))) return false;
                     if (elect_one()) {
                         mbar_expect_tx(&bars->q_full[qb], (uint32_t)set_bytes);
                         for (int t = 0; t < p.dtiles; ++t)
@@ -177,9 +172,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     return true;
                 };
                 if (!is_v && !q_prefetched) {
-                    [[maybe_unused]] const long long tq = AT_CLOCK();
                     ok = issue_q(q_no, cur.z, cur.g);
-                    if (lane == 0) AT_ADD(0, AT_CLOCK() - tq);
                 }
                 ++q_no;
                 DescWindow win;
@@ -194,9 +187,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     uint64_t* full = is_v ? &bars->v_full[stage] : &bars->k_full[stage];
                     uint8_t* dst = (is_v ? v_smem : k_smem) + stage * set_bytes;
                     const CUtensorMap* map = is_v ? &map_v : &map_k;
-                    [[maybe_unused]] const long long t0 = AT_CLOCK();
                     ok = __all_sync(0xffffffffu, mbar_wait(reuse, parity, abort_flag, p.status)) != 0;
-                    if (lane == 0) AT_ADD(is_v ? 2 : 1, AT_CLOCK() - t0);
                     if (ok && elect_one()) {
                         mbar_expect_tx(full, (uint32_t)set_bytes);
                         for (int t = 0; t < p.dtiles; ++t)
@@ -214,7 +205,6 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             pre = pre_next;
             cur.advance();
         }
-        if (lane == 0 && !is_v) AT_ADD(4, AT_CLOCK() - tp_begin);
         if (lane == 0 && *(volatile int*)abort_flag) {
             // Give copies that were issued a bounded chance to land before the CTA exits.
             const unsigned long long t0 = global_ns();
@@ -229,8 +219,96 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                        global_ns() - t0 < kWaitLimitNs / 4) {}
         }
         __syncwarp();
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ Q K^T issuer
+    } else if (WGS == 2 && (warp == 1 || warp == 3)) {
+        // ------------------------------------------------------------ issuer of one softmax group (head dim 64)
+        // Group g = warp / 2 owns the S tiles with number s & 1 == g: S buffer g, P buffer g, O accumulator g,
+        // K / V stages with s & 1 == g.  One warp issues both products of its group, so the two groups never wait
+        // behind each other's MMAs (a thread issues a 64 x 64 x 16 MMA only every 60 cycles or so, one in-order
+        // issuer for both groups was the longest chain of the kernel).  Order: Q K^T of tile t, then P V of the
+        // group's previous tile (kept pending across item borders): S of the next tile is being computed while
+        // the softmax warps work on this one, and their P is consumed as soon as the next Q K^T is out.
+        const int g = warp >> 1;
+        int s_no = 0, q_no = 0;                     // S tiles and non-empty items before the current item
+        bool ok = true;
+        bool pend = false, pend_first = false, pend_last = false;
+        int pend_s = 0, pend_o = 0;                 // the pending P V: tile number, item number
+        const uint32_t idesc_qk = p.idesc_qk, idesc_pv = p.idesc_pv;
+        const uint64_t q_desc = make_tile_desc(smem_u32(q_smem), false), k_desc = make_tile_desc(smem_u32(k_smem), false);
+        const uint64_t p_desc = make_tile_desc(smem_u32(p_smem + g * kTileBytes), false);
+        const uint64_t v_desc = make_tile_desc(smem_u32(v_smem), true);
+        const uint32_t d_s = tmem_base + (uint32_t)(kSCol0 + g * kTile), d_o = tmem_base + (uint32_t)(g * p.head_dim);
+        auto issue_pv = [&]() -> bool {             // O_g (+)= P V of the pending tile
+            const int s = pend_s, vs = s & vring_mask;
+            // the accumulators are free once the item before has been read out
+            if (pend_first && pend_o > 0 &&
+                !__all_sync(0xffffffffu, mbar_wait(&bars->o_empty[(pend_o - 1) & 1], (uint32_t)((pend_o - 1) >> 1) & 1u, abort_flag, p.status)))
+                return false;
+            if (!__all_sync(0xffffffffu, mbar_wait(&bars->v_full[vs], (uint32_t)(s >> p.vring_shift) & 1u, abort_flag, p.status))) return false;
+            if (!__all_sync(0xffffffffu, mbar_wait(&bars->p_full[g], (uint32_t)(s >> 1) & 1u, abort_flag, p.status))) return false;
+            tc_fence_after();
+            const uint64_t db = v_desc + (uint64_t)((vs * kTileBytes) >> 4);
+            if (elect_one()) {
+#pragma unroll
+                for (int kk = 0; kk < kTile / 16; ++kk)
+                    tc_mma_f16(d_o, p_desc + (uint64_t)(kk * 2), db + (uint64_t)(kk * (2048 >> 4)), idesc_pv, (!pend_first || kk > 0) ? 1u : 0u);
+                tc_commit(&bars->pv_done[vs]);
+                if (pend_last) tc_commit(&bars->o_full[g][pend_o & 1]);
+            }
+            __syncwarp();
+            return true;
+        };
+        Cursor cur;
+        cur.init(p);
+        for (; ok && cur.valid(); cur.advance()) {
+            const int n = cur.count;
+            if (n == 0) continue;                   // empty row: the softmax warps write zeros on their own
+            const int qb = q_no & 1;
+            ok = __all_sync(0xffffffffu, mbar_wait(&bars->q_full[qb], (uint32_t)(q_no >> 1) & 1u, abort_flag, p.status)) != 0;
+            if (!ok) break;
+            const int t_first = (g - s_no) & 1;     // this group's first tile of the item
+            if (t_first >= n) {
+                // A row of one block that belongs to the other group.  This group still arrives on its barriers
+                // once per item, in item order (never two phases ahead of their waiters: the wait for the item
+                // before to have been read out comes first, and that needs this group's pending P V).
+                if (pend) { ok = issue_pv(); pend = false; if (!ok) break; }
+                if (q_no > 0) ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_empty[(q_no - 1) & 1], (uint32_t)((q_no - 1) >> 1) & 1u, abort_flag, p.status)) != 0;
+                if (!ok) break;
+                if (elect_one()) { mbar_arrive(&bars->q_empty[g][qb]); mbar_arrive(&bars->o_full[g][q_no & 1]); }
+                __syncwarp();
+            } else {
+                const uint64_t da = q_desc + (uint64_t)((qb * kTileBytes) >> 4);
+                for (int t = t_first; ok && t < n; t += 2) {
+                    const int s = s_no + t, ks = s & ring_mask;
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->k_full[ks], (uint32_t)(s >> p.ring_shift) & 1u, abort_flag, p.status)) != 0;
+                    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_empty[g], ((uint32_t)(s >> 1) & 1u) ^ 1u, abort_flag, p.status)) != 0;
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t db = k_desc + (uint64_t)((ks * kTileBytes) >> 4);
+                    if (elect_one()) {
+#pragma unroll
+                        for (int kk = 0; kk < kTile / 16; ++kk)
+                            tc_mma_f16(d_s, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc_qk, kk > 0 ? 1u : 0u);
+                        tc_commit(&bars->qk_done[ks]);
+                        if (t + 2 >= n) tc_commit(&bars->q_empty[g][qb]);    // this group's last read of the Q buffer
+                    }
+                    __syncwarp();
+                    if (pend) ok = issue_pv();
+                    pend = true; pend_s = s; pend_o = q_no; pend_first = t == t_first; pend_last = t + 2 >= n;
+                }
+            }
+            s_no += n;
+            ++q_no;
+        }
+        if (ok && pend) issue_pv();
+        // All MMAs issued by the elected lane (the same one every time: the election is deterministic
+        // for a converged warp) must have retired before TMEM is freed.
+        if (elect_one()) {
+            tc_commit(&bars->drain);
+            mbar_wait(&bars->drain, 0, abort_flag, p.status);
+        }
+        __syncwarp();
+    } else if (WGS == 1 && warp == 1) {
+        // ------------------------------------------------------------ Q K^T issuer (one softmax group)
         // The S tiles (blocks) of a CTA are numbered in the order they are produced; tile s goes to
         // S buffer s & 1, so Q K^T of block j + 1 runs while the softmax warps work on block j.
         {
@@ -243,19 +321,14 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 const int n = cur.count;
                 if (n == 0) continue;               // empty row: the softmax warps write zeros on their own
                 const int qb = q_no & (p.qbufs - 1);
-                [[maybe_unused]] const long long tq0 = AT_CLOCK();
                 ok = __all_sync(0xffffffffu, mbar_wait(&bars->q_full[qb], (uint32_t)(p.qbufs == 2 ? q_no >> 1 : q_no) & 1u, abort_flag, p.status)) != 0;
-                AT_ADD(21, AT_CLOCK() - tq0);
                 if (!ok) break;
                 const int s_end = s_no + n;
                 for (int s = s_no; s < s_end; ++s) {
                     const int ks = s & ring_mask, sb = s & 1;
-                    [[maybe_unused]] const long long t0 = AT_CLOCK();
                     ok = __all_sync(0xffffffffu, mbar_wait(&bars->k_full[ks], (uint32_t)(s >> p.ring_shift) & 1u, abort_flag, p.status)) != 0;
-                    [[maybe_unused]] const long long t1 = AT_CLOCK();
                     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_empty[sb], ((uint32_t)(s >> 1) & 1u) ^ 1u, abort_flag, p.status)) != 0;
                     if (!ok) break;
-                    [[maybe_unused]] const long long t2 = AT_CLOCK();
                     tc_fence_after();
                     const uint32_t d = tmem_base + (uint32_t)(kSCol0 + sb * kTile);
                     if (elect_one()) {
@@ -269,10 +342,9 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         tc_commit(&bars->qk_done[ks]);
                     }
                     __syncwarp();
-                    if (lane == 0) { AT_ADD(11, t1 - t0); AT_ADD(12, t2 - t1); AT_ADD(13, AT_CLOCK() - t2); }
                 }
                 if (!ok) break;
-                if (elect_one()) tc_commit(&bars->q_empty[qb]);      // the last read of this Q buffer has been issued
+                if (elect_one()) tc_commit(&bars->q_empty[0][qb]);   // the last read of this Q buffer has been issued
                 __syncwarp();
                 s_no = s_end;
                 ++q_no;
@@ -285,8 +357,8 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
         }
         __syncwarp();
-    } else if (warp == 3) {
-        // ------------------------------------------------------------ P V issuer
+    } else if (WGS == 1 && warp == 3) {
+        // ------------------------------------------------------------ P V issuer (one softmax group)
         {
             int p_no = 0, o_no = 0;
             bool ok = true;
@@ -298,16 +370,12 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 if (n == 0) continue;
                 for (int j = 0; ok && j < n; ++j, ++p_no) {
                     const int pb = p_no & 1, vs = p_no & vring_mask;
-                    [[maybe_unused]] const long long t0 = AT_CLOCK();
                     // the accumulators are free once the item before has been read out (its barrier: its parity)
                     if (j == 0 && o_no > 0)
                         ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_empty[(o_no - 1) & 1], (uint32_t)((o_no - 1) >> 1) & 1u, abort_flag, p.status)) != 0;
-                    [[maybe_unused]] const long long t1 = AT_CLOCK();
                     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->v_full[vs], (uint32_t)(p_no >> p.vring_shift) & 1u, abort_flag, p.status)) != 0;
-                    [[maybe_unused]] const long long t2 = AT_CLOCK();
                     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->p_full[pb], (uint32_t)(p_no >> 1) & 1u, abort_flag, p.status)) != 0;
                     if (!ok) break;
-                    [[maybe_unused]] const long long t3 = AT_CLOCK();
                     tc_fence_after();
                     // O += P_j V_{c_j}: A = P (K-major), B = V tiles (N contiguous), N = head_dim
                     const uint64_t da = make_tile_desc(smem_u32(p_smem + pb * kTileBytes), false);
@@ -319,10 +387,9 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                             tc_mma_f16(d, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * (2048 >> 4)), idesc_pv,
                                        (j >= WGS || kk > 0) ? 1u : 0u);
                         tc_commit(&bars->pv_done[vs]);
-                        if (j == n - 1) tc_commit(&bars->o_full[o_no & 1]);
+                        if (j == n - 1) tc_commit(&bars->o_full[0][o_no & 1]);
                     }
                     __syncwarp();
-                    if (lane == 0) { AT_ADD(14, t1 - t0); AT_ADD(15, t2 - t1); AT_ADD(16, t3 - t2); AT_ADD(17, AT_CLOCK() - t3); }
                 }
                 ++o_no;
             }
@@ -349,7 +416,6 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         int s_no = 0, o_no = 0;                     // S tiles and non-empty items before the current item
         int x_no[2] = {0, 0};                       // hand-overs so far in which group 0 / group 1 was the writer
         bool ok = true;
-        [[maybe_unused]] const long long t_begin = AT_CLOCK();
         Cursor cur;
         cur.init(p);
         BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
@@ -411,28 +477,32 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 // exact in fp32 sums and well inside the 16-bit range); raising it rescales O in TMEM
                 // and l by exp2(m_old - m_new), which needs this group's previous P V to have retired.
                 constexpr float kSlack = 8.f;
-                float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+                float m_a = -INFINITY, m_b = -INFINITY;
+                // row sums: per row two independent two-wide accumulators (even / odd column units), added up at the end
+                uint64_t la2[2] = {0ull, 0ull}, lb2[2] = {0ull, 0ull};
                 DescWindow win;
                 win.begin(p.blocks, cur.first, cur.count, pre, lane);
-                const uint32_t p_row = (uint32_t)(row_a * 128 + 4 * q4), p_xor = (uint32_t)(row_a & 7);
+                // P leaves through stmatrix: the 16x256b TMEM load hands out the m8n8 fragment layout, so the packed
+                // words of column units 2k, 2k + 1 of the lane's two rows are the four matrices of one instruction.
+                // Lane -> row address of its matrix: matrix i = lane / 8 holds rows (i & 1) * 8 .. of unit 2k + (i >> 1).
+                // Its address in unit 2k is row * 128 + (((2k + (i >> 1)) ^ (row & 7)) << 4) = p_off ^ (k << 5): bits 5-6
+                // carry 2k ^ (row & 6), bit 4 the unit's parity, and the tiles are 1024-byte aligned.
+                const int sm_row = quad * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+                const uint32_t p_off = (uint32_t)(sm_row * 128) + ((((uint32_t)(lane >> 4)) ^ (uint32_t)(sm_row & 7)) << 4);
                 const float c2abs = fabsf(c2);
                 const int t_first = WGS == 2 ? ((wg - s_no) & 1) : 0;     // this group's first tile of the item
                 auto load = [&](uint32_t (&r)[32], int t) -> bool {       // wait for S tile t, start loading it
                     const int s = s_no + t;
-                    [[maybe_unused]] const long long t0 = AT_CLOCK();
                     if (!__all_sync(0xffffffffu, mbar_wait(&bars->qk_done[s & ring_mask], (uint32_t)(s >> p.ring_shift) & 1u,
                                                            abort_flag, p.status)))
                         return false;
                     tc_fence_after();
                     tc_ld_16x256b_x8(tmem_base + lane_field + (uint32_t)(kSCol0 + (s & 1) * kTile), r);
-                    if (warp == 4 && lane == 0) AT_ADD(5, AT_CLOCK() - t0);
                     return true;
                 };
                 auto loaded = [&](int t) {                                 // tile t is in registers: free its buffer
-                    [[maybe_unused]] const long long t0 = AT_CLOCK();
                     tc_wait_ld();
                     release_accumulator(&bars->s_empty[(s_no + t) & 1], lane);
-                    if (warp == 4 && lane == 0) AT_ADD(6, AT_CLOCK() - t0);
                 };
                 // Masked elements (above the diagonal, padded keys, quadrants outside a block-32 layout) are
                 // overwritten in registers by -inf (+inf for a negative scale) before the common code runs:
@@ -458,22 +528,30 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         }
                     }
                     const int s = s_no + t;                                  // tile number = P buffer number
-                    [[maybe_unused]] const long long tm0 = AT_CLOCK();
                     // block maxima of the raw scores (for a negative scale: of their negatives)
-                    float x_a = -INFINITY, x_b = -INFINITY;
-                    if (!flip) {
+                    float x_a, x_b;
+                    {
+                        // two chains per row (even / odd column units) of three-input maxima
+                        float a0 = -INFINITY, a1 = -INFINITY, b0 = -INFINITY, b1 = -INFINITY;
+                        if (!flip) {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const int u = i >> 1, e = i & 1;
-                            x_a = fmaxf(x_a, __uint_as_float(r[4 * u + e]));
-                            x_b = fmaxf(x_b, __uint_as_float(r[4 * u + 2 + e]));
-                        }
-                    } else {
+                            for (int u = 0; u < 8; u += 2) {
+                                a0 = fmax3(a0, __uint_as_float(r[4 * u]), __uint_as_float(r[4 * u + 1]));
+                                b0 = fmax3(b0, __uint_as_float(r[4 * u + 2]), __uint_as_float(r[4 * u + 3]));
+                                a1 = fmax3(a1, __uint_as_float(r[4 * u + 4]), __uint_as_float(r[4 * u + 5]));
+                                b1 = fmax3(b1, __uint_as_float(r[4 * u + 6]), __uint_as_float(r[4 * u + 7]));
+                            }
+                            x_a = fmaxf(a0, a1); x_b = fmaxf(b0, b1);
+                        } else {
+                            a0 = a1 = b0 = b1 = INFINITY;
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const int u = i >> 1, e = i & 1;
-                            x_a = fmaxf(x_a, -__uint_as_float(r[4 * u + e]));
-                            x_b = fmaxf(x_b, -__uint_as_float(r[4 * u + 2 + e]));
+                            for (int u = 0; u < 8; u += 2) {
+                                a0 = fmin3(a0, __uint_as_float(r[4 * u]), __uint_as_float(r[4 * u + 1]));
+                                b0 = fmin3(b0, __uint_as_float(r[4 * u + 2]), __uint_as_float(r[4 * u + 3]));
+                                a1 = fmin3(a1, __uint_as_float(r[4 * u + 4]), __uint_as_float(r[4 * u + 5]));
+                                b1 = fmin3(b1, __uint_as_float(r[4 * u + 6]), __uint_as_float(r[4 * u + 7]));
+                            }
+                            x_a = -fminf(a0, a1); x_b = -fminf(b0, b1);
                         }
                     }
                     x_a = fmaxf(x_a, __shfl_xor_sync(0xffffffffu, x_a, 1)); x_a = fmaxf(x_a, __shfl_xor_sync(0xffffffffu, x_a, 2));
@@ -490,8 +568,8 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         if (__any_sync(0xffffffffu, up_a || up_b)) {
                             const float al_a = !up_a ? 1.f : (m_a == -INFINITY ? 0.f : attn_exp2(m_a - x_a));
                             const float al_b = !up_b ? 1.f : (m_b == -INFINITY ? 0.f : attn_exp2(m_b - x_b));
-                            if (up_a) { m_a = x_a; l_a *= al_a; }
-                            if (up_b) { m_b = x_b; l_b *= al_b; }
+                            if (up_a) { m_a = x_a; const uint64_t f = f2_pack(al_a, al_a); la2[0] = f2_mul(la2[0], f); la2[1] = f2_mul(la2[1], f); }
+                            if (up_b) { m_b = x_b; const uint64_t f = f2_pack(al_b, al_b); lb2[0] = f2_mul(lb2[0], f); lb2[1] = f2_mul(lb2[1], f); }
                             // O is complete up to this group's previous tile once that tile's P V has retired
                             const int prev = s - WGS;
                             if (!__all_sync(0xffffffffu, mbar_wait(&bars->pv_done[prev & vring_mask],
@@ -516,34 +594,34 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         }
                     }
                     const float sub_a = m_a == -INFINITY ? 0.f : m_a, sub_b = m_b == -INFINITY ? 0.f : m_b;
-                    [[maybe_unused]] const long long tm1 = AT_CLOCK();
                     // the P buffer must have been read by the MMAs that used it last (those of tile s - 2)
                     if (s >= 2 && !__all_sync(0xffffffffu, mbar_wait(&bars->pv_done[(s - 2) & vring_mask],
                                                                      (uint32_t)((s - 2) >> p.vring_shift) & 1u, abort_flag, p.status)))
                         return false;
-                    // every lane owns the column pairs 8u + 2 * q4 + {0, 1} of its two rows: one 32-bit
-                    // word each, stored straight into the 128-byte-swizzled tile (32 lanes hit 32 banks)
-                    [[maybe_unused]] const long long tm2 = AT_CLOCK();
-                    const uint32_t tile = smem_u32(p_smem + pb * kTileBytes) + p_row;
+                    // P = exp2(c2 * s - m): per pair of columns one two-wide FMA, two exp2, one two-wide add into the
+                    // row sum and one pack; four stmatrix write the lane's 32 values into the swizzled tile
+                    const uint32_t tile = smem_u32(p_smem + pb * kTileBytes) + p_off;
+                    const uint64_t c2p = f2_pack(c2, c2), na = f2_pack(-sub_a, -sub_a), nb = f2_pack(-sub_b, -sub_b);
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        float pa[2], pb2[2];
+                    for (int k = 0; k < 4; ++k) {
+                        uint32_t w[4];              // matrices (unit 2k, row a), (2k, row b), (2k + 1, a), (2k + 1, b)
 #pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            pa[e] = attn_exp2(fmaf(__uint_as_float(r[4 * u + e]), c2, -sub_a));
-                            pb2[e] = attn_exp2(fmaf(__uint_as_float(r[4 * u + 2 + e]), c2, -sub_b));
-                            l_a += pa[e];
-                            l_b += pb2[e];
+                        for (int i = 0; i < 4; ++i) {
+                            const int u = 2 * k + (i >> 1), h = i & 1;
+                            const uint64_t t2 = f2_fma(f2_pack(__uint_as_float(r[4 * u + 2 * h]), __uint_as_float(r[4 * u + 2 * h + 1])),
+                                                       c2p, h ? nb : na);
+                            float e0, e1;
+                            f2_unpack(t2, e0, e1);
+                            e0 = attn_exp2(e0); e1 = attn_exp2(e1);
+                            if (h) lb2[i >> 1] = f2_add(lb2[i >> 1], f2_pack(e0, e1));
+                            else   la2[i >> 1] = f2_add(la2[i >> 1], f2_pack(e0, e1));
+                            w[i] = pack2<BF16>(e0, e1);
                         }
-                        const uint32_t addr = tile + (((uint32_t)u ^ p_xor) << 4);
-                        asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(pack2<BF16>(pa[0], pa[1])) : "memory");
-                        asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + 8 * 128), "r"(pack2<BF16>(pb2[0], pb2[1])) : "memory");
+                        stmatrix_x4(tile ^ (uint32_t)(k << 5), w[0], w[1], w[2], w[3]);
                     }
-                    [[maybe_unused]] const long long tm3 = AT_CLOCK();
                     fence_async_shared();           // generic-proxy writes -> visible to the tensor core's reads
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars->p_full[pb]);
-                    if (warp == 4 && lane == 0) { AT_ADD(7, tm1 - tm0); AT_ADD(18, tm2 - tm1); AT_ADD(19, tm3 - tm2); AT_ADD(20, AT_CLOCK() - tm3); }
                     return true;
                 };
                 if (WGS == 1) {
@@ -574,6 +652,13 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 }
                 s_no += n;
                 if (!ok) break;
+                float l_a, l_b;
+                {
+                    float x0, x1, y0, y1;
+                    f2_unpack(f2_add(la2[0], la2[1]), x0, x1);
+                    f2_unpack(f2_add(lb2[0], lb2[1]), y0, y1);
+                    l_a = x0 + x1; l_b = y0 + y1;
+                }
                 l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
                 l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
                 // weights of this group's (w) and the other group's (v) accumulator in the result
@@ -605,10 +690,8 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&bars->stat_full[dir][slot]);
                     } else {
-                        [[maybe_unused]] const long long ts0 = AT_CLOCK();
                         ok = __all_sync(0xffffffffu, mbar_wait(&bars->stat_full[dir][slot], par, abort_flag, p.status)) != 0;
                         if (!ok) break;
-                        if (warp == 4 && lane == 0) AT_ADD(22, AT_CLOCK() - ts0);
                         const float mo_a = stat[row_a * 2], lo_a = stat[row_a * 2 + 1];
                         const float mo_b = stat[(row_a + 8) * 2], lo_b = stat[(row_a + 8) * 2 + 1];
                         __syncwarp();
@@ -626,10 +709,9 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     // ---- end of the row: O / l
                     const float inv_a = l_a > 0.f ? __frcp_rn(l_a) : 0.f, inv_b = l_b > 0.f ? __frcp_rn(l_b) : 0.f;
                     const float sw_a = w_a * inv_a, sv_a = v_a * inv_a, sw_b = w_b * inv_b, sv_b = v_b * inv_b;
-                    [[maybe_unused]] const long long te0 = AT_CLOCK();
-                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[o_no & 1], (uint32_t)(o_no >> 1) & 1u, abort_flag, p.status)) != 0;
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[0][o_no & 1], (uint32_t)(o_no >> 1) & 1u, abort_flag, p.status)) != 0;
+                    if (WGS == 2 && ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[1][o_no & 1], (uint32_t)(o_no >> 1) & 1u, abort_flag, p.status)) != 0;
                     if (!ok) break;
-                    [[maybe_unused]] const long long te1 = AT_CLOCK();
                     tc_fence_after();
                     for (int c = 0; c < p.head_dim; c += 32) {
                         uint32_t r0[16], r1[16];
@@ -657,7 +739,6 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         *reinterpret_cast<uint4*>(p.o + o_row_a + c + 8 * q4) = make_uint4(ta[0], ta[1], ta[2], ta[3]);
                         *reinterpret_cast<uint4*>(p.o + o_row_b + c + 8 * q4) = make_uint4(tb[0], tb[1], tb[2], tb[3]);
                     }
-                    if (warp == 4 && lane == 0) { AT_ADD(8, te1 - te0); AT_ADD(9, AT_CLOCK() - te1); }
                     if (q4 == 0 && p.lse) {
                         // natural-log sum of exponentials of the scaled, masked scores
                         p.lse[lse_a] = l_a > 0.f ? (m_a + __log2f(l_a)) * 0.6931471805599453f : -INFINITY;
@@ -669,7 +750,471 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             pre = pre_next;
             cur.advance();
         }
-        if (warp == 4 && lane == 0) AT_ADD(10, AT_CLOCK() - t_begin);
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kAttnTmemCols)
+                     : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Head dim 64: two independent pipelines per CTA.
+//
+// A pipeline is a producer warp, an issuer warp and a softmax warpgroup with their own shared-memory
+// tiles (Q, two K stages, two V stages, P), their own S buffer and O accumulator in tensor memory
+// and their own barriers; it walks its own block rows (pipeline number = 2 * CTA + g of 2 * grid
+// pipelines).  Nothing is shared between the two pipelines of a CTA but the TMEM allocation, and
+// two CTAs share an SM: four block rows are in flight per SM, each at its own point of its row, so
+// the end of one row (normalising and writing O) overlaps the others' tiles.  (An earlier version
+// let two softmax groups share a row, with alternate tiles: every hand-over between the groups,
+// the in-order producers and issuers and the merge of the two partial results at the end of a row
+// serialised the CTA; with every MMA, exponential and copy removed it still took 60 % of its time.)
+//   warps 0, 2   producer of pipeline 0, 1: Q of the row, then K(0), K(1), V(0), K(2), V(1), ...
+//   warps 1, 3   issuer: polls "S buffer free + K landed" and "P written + V landed" and issues
+//                whichever product is ready (Q K^T of tile t + 1 while the softmax warps work on
+//                tile t, P V of tile t as soon as its P is complete)
+//   warps 4-7, 8-11   softmax warpgroup: tcgen05.ld of S, masks, lazily raised running maximum,
+//                P = exp2(..) packed and written with stmatrix into the swizzled operand tile,
+//                row sums; at the end of the row O / l and the log-sum-exp go to global memory.
+constexpr int kPipeTiles = 6;                   // Q, K x 2, V x 2, P
+struct __align__(8) PipeBarriers {
+    uint64_t q_full[2], q_empty[2];             // [pipeline]
+    uint64_t k_full[2][2], qk_done[2][2];       // [pipeline][stage]
+    uint64_t v_full[2][2], pv_done[2][2];
+    uint64_t s_empty[2], p_full[2];
+    uint64_t o_full[2], o_empty[2];
+    uint64_t drain;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+template <bool BF16, bool MASKED>
+__global__ void __launch_bounds__(12 * 32, 2)
+attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                               const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    PipeBarriers* bars = reinterpret_cast<PipeBarriers*>(smem + 2 * kPipeTiles * kTileBytes);
+    int* abort_flag = &bars->abort_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = warp < 4 ? warp >> 1 : (warp - 4) >> 2;          // pipeline of this warp
+    uint8_t* q_smem = smem + g * kPipeTiles * kTileBytes;
+    uint8_t* k_smem = q_smem + kTileBytes;
+    uint8_t* v_smem = k_smem + 2 * kTileBytes;
+    uint8_t* p_smem = v_smem + 2 * kTileBytes;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bars->q_full[i], 1); mbar_init(&bars->q_empty[i], 1);
+            for (int s = 0; s < 2; ++s) {
+                mbar_init(&bars->k_full[i][s], 1); mbar_init(&bars->qk_done[i][s], 1);
+                mbar_init(&bars->v_full[i][s], 1); mbar_init(&bars->pv_done[i][s], 1);
+            }
+            mbar_init(&bars->s_empty[i], 4); mbar_init(&bars->p_full[i], 4);
+            mbar_init(&bars->o_full[i], 1); mbar_init(&bars->o_empty[i], 4);
+        }
+        mbar_init(&bars->drain, 2);
+        bars->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_shared();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&bars->tmem_base)), "r"((uint32_t)kAttnTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *(volatile uint32_t*)&bars->tmem_base;
+    const uint32_t o_tmem = tmem_base + (uint32_t)(g * kTile);              // O accumulator of the pipeline
+    const uint32_t s_tmem = tmem_base + (uint32_t)(kSCol0 + g * kTile);     // its S buffer
+    const int walker = 2 * (int)blockIdx.x + g, walkers = 2 * (int)gridDim.x;
+
+    if (warp == 0 || warp == 2) {
+        // ------------------------------------------------------------ producer
+        int t0 = 0, i_no = 0;                       // tiles and non-empty rows before the current row
+        bool ok = true;
+        Cursor cur;
+        cur.init_as(p, walker, walkers);
+        BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
+        // K / V of tile t go to stage t & 1 once the product that read the stage last has retired
+        auto load_kv = [&](bool is_v, int t, int col, int z) -> bool {
+            const int st = t & 1;
+            const uint32_t parity = ((uint32_t)(t >> 1) & 1u) ^ 1u;
+            uint64_t* reuse = is_v ? &bars->pv_done[g][st] : &bars->qk_done[g][st];
+            uint64_t* full = is_v ? &bars->v_full[g][st] : &bars->k_full[g][st];
+            uint8_t* dst = (is_v ? v_smem : k_smem) + st * kTileBytes;
+            const CUtensorMap* map = is_v ? &map_v : &map_k;
+            if (!__all_sync(0xffffffffu, mbar_wait(reuse, parity, abort_flag, p.status))) return false;
+            if (elect_one()) {
+                mbar_expect_tx(full, (uint32_t)kTileBytes);
+                tma_load_3d(dst, map, full, 0, col * kTile, z);
+            }
+            __syncwarp();
+            return true;
+        };
+        while (ok && cur.valid()) {
+            BlockDesc pre_next{0, 0};
+            if (cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
+            const int n = cur.count;
+            if (n > 0) {
+                // Q once the last Q K^T of the row before has retired
+                ok = __all_sync(0xffffffffu, mbar_wait(&bars->q_empty[g], ((uint32_t)i_no & 1u) ^ 1u, abort_flag, p.status)) != 0;
+                if (ok && elect_one()) {
+                    mbar_expect_tx(&bars->q_full[g], (uint32_t)kTileBytes);
+                    tma_load_3d(q_smem, &map_q, &bars->q_full[g], 0, cur.g * kTile, cur.z);
+                }
+                __syncwarp();
+                DescWindow win;
+                win.begin(p.blocks, cur.first, cur.count, pre, lane);
+                int col_prev = 0;
+                for (int j = 0; ok && j < n; ++j) {
+                    const int col = win.get(p.blocks, cur.first, cur.count, j, lane).col();
+                    ok = load_kv(false, t0 + j, col, cur.z);
+                    if (ok && j > 0) ok = load_kv(true, t0 + j - 1, col_prev, cur.z);
+                    col_prev = col;
+                }
+                if (ok) ok = load_kv(true, t0 + n - 1, col_prev, cur.z);
+                t0 += n;
+                ++i_no;
+            }
+            pre = pre_next;
+            cur.advance();
+        }
+        if (lane == 0 && *(volatile int*)abort_flag) {
+            // Give copies that were issued a bounded chance to land before the CTA exits.
+            const unsigned long long tw = global_ns();
+            for (int s = 0; s < 2; ++s) {
+                while (!mbar_try_wait(&bars->k_full[g][s], 0) && !mbar_try_wait(&bars->k_full[g][s], 1) &&
+                       global_ns() - tw < kWaitLimitNs / 4) {}
+                while (!mbar_try_wait(&bars->v_full[g][s], 0) && !mbar_try_wait(&bars->v_full[g][s], 1) &&
+                       global_ns() - tw < kWaitLimitNs / 4) {}
+            }
+            while (!mbar_try_wait(&bars->q_full[g], 0) && !mbar_try_wait(&bars->q_full[g], 1) &&
+                   global_ns() - tw < kWaitLimitNs / 4) {}
+        }
+        __syncwarp();
+    } else if (warp == 1 || warp == 3) {
+        // ------------------------------------------------------------ issuer
+        // Order: Q K^T of tile t + 1, then P V of tile t (kept pending across rows).  The events it waits
+        // for come in this order: S(t) is in the softmax warps' registers when they start on tile t, their
+        // P(t) is complete when they are done with it.  So S(t + 1) is computed while they work on tile
+        // t, and P V of tile t is issued the moment its P is complete.
+        const uint32_t idesc_qk = p.idesc_qk, idesc_pv = p.idesc_pv;
+        const uint64_t q_desc = make_tile_desc(smem_u32(q_smem), false);
+        const uint64_t k_desc = make_tile_desc(smem_u32(k_smem), false);
+        const uint64_t p_desc = make_tile_desc(smem_u32(p_smem), false);
+        const uint64_t v_desc = make_tile_desc(smem_u32(v_smem), true);
+        int t0 = 0, i_no = 0;                       // tiles and non-empty rows before the current row
+        bool ok = true;
+        bool pend = false, pend_first = false, pend_last = false;
+        int pend_t = 0, pend_i = 0;                 // the pending P V: tile number, row number
+        auto issue_pv = [&]() -> bool {             // O (+)= P V of the pending tile
+            const int t = pend_t, st = t & 1;
+            // the accumulator is free once the row before has been read out
+            if (pend_first && pend_i > 0 &&
+                !__all_sync(0xffffffffu, mbar_wait(&bars->o_empty[g], (uint32_t)(pend_i - 1) & 1u, abort_flag, p.status)))
+                return false;
+            if (!__all_sync(0xffffffffu, mbar_wait(&bars->v_full[g][st], (uint32_t)(t >> 1) & 1u, abort_flag, p.status))) return false;
+            if (!__all_sync(0xffffffffu, mbar_wait(&bars->p_full[g], (uint32_t)t & 1u, abort_flag, p.status))) return false;
+            tc_fence_after();
+            const uint64_t db = v_desc + (uint64_t)((st * kTileBytes) >> 4);
+            if (elect_one()) {
+#pragma unroll
+                for (int kk = 0; kk < kTile / 16; ++kk)
+                    tc_mma_f16(o_tmem, p_desc + (uint64_t)(kk * 2), db + (uint64_t)(kk * (2048 >> 4)), idesc_pv,
+                               (!pend_first || kk > 0) ? 1u : 0u);
+                tc_commit(&bars->pv_done[g][st]);       // the P buffer and the V stage are free
+                if (pend_last) tc_commit(&bars->o_full[g]);
+            }
+            __syncwarp();
+            return true;
+        };
+        Cursor cur;
+        cur.init_as(p, walker, walkers);
+        for (; ok && cur.valid(); cur.advance()) {
+            const int n = cur.count;
+            if (n == 0) continue;                   // a row without blocks: the softmax warps write zeros on their own
+            ok = __all_sync(0xffffffffu, mbar_wait(&bars->q_full[g], (uint32_t)i_no & 1u, abort_flag, p.status)) != 0;
+            for (int j = 0; ok && j < n; ++j) {
+                const int t = t0 + j, st = t & 1;
+                ok = __all_sync(0xffffffffu, mbar_wait(&bars->k_full[g][st], (uint32_t)(t >> 1) & 1u, abort_flag, p.status)) != 0;
+                if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_empty[g], ((uint32_t)t & 1u) ^ 1u, abort_flag, p.status)) != 0;
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t db = k_desc + (uint64_t)((st * kTileBytes) >> 4);
+                if (elect_one()) {
+#pragma unroll
+                    for (int kk = 0; kk < kTile / 16; ++kk)
+                        tc_mma_f16(s_tmem, q_desc + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc_qk, kk > 0 ? 1u : 0u);
+                    tc_commit(&bars->qk_done[g][st]);       // S is ready and the K stage is free
+                    if (j == n - 1) tc_commit(&bars->q_empty[g]);
+                }
+                __syncwarp();
+                if (pend) ok = issue_pv();
+                pend = true; pend_t = t; pend_i = i_no; pend_first = j == 0; pend_last = j == n - 1;
+            }
+            t0 += n;
+            ++i_no;
+        }
+        if (ok && pend) issue_pv();
+        // All MMAs issued by the elected lane (the same one every time: the election is deterministic
+        // for a converged warp) must have retired before TMEM is freed.
+        if (elect_one()) {
+            tc_commit(&bars->drain);
+            mbar_wait(&bars->drain, 0, abort_flag, p.status);
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ softmax warpgroup
+        const int quad = warp & 3;                  // TMEM sub-partition this warp may read
+        const int q4 = lane & 3;                    // position in the quad: columns 8u + 2 * q4 + {0, 1}
+        const int row_a = quad * 16 + (lane >> 2);  // this lane's two rows of the 64-row block
+        const uint32_t lane_field = (uint32_t)(quad * 32) << 16;
+        const bool masked_op = MASKED && (p.causal != 0 || p.kpm != nullptr || p.quadrants != 0);
+        // P leaves through stmatrix: the 16x256b TMEM load hands out the m8n8 fragment layout, so the packed words
+        // of column units 2k, 2k + 1 of the lane's two rows are the four matrices of one instruction.  Lane -> row
+        // address of its matrix: matrix i = lane / 8 holds rows (i & 1) * 8 .. of unit 2k + (i >> 1); the address
+        // row * 128 + (((2k + (i >> 1)) ^ (row & 7)) << 4) is p_off ^ (k << 5) (bits 5-6 carry 2k ^ (row & 6),
+        // bit 4 the unit's parity; the tile is 1024-byte aligned).
+        const int sm_row = quad * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+        const uint32_t p_tile = smem_u32(p_smem) + (uint32_t)(sm_row * 128) + ((((uint32_t)(lane >> 4)) ^ (uint32_t)(sm_row & 7)) << 4);
+        const float c2 = p.scale_log2, c2abs = fabsf(c2);
+        const bool flip = c2 < 0.f;
+        const uint64_t c2p = f2_pack(c2, c2);
+        int t0 = 0, i_no = 0;                       // tiles and non-empty rows before the current row
+        bool ok = true;
+        Cursor cur;
+        cur.init_as(p, walker, walkers);
+        BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
+        while (ok && cur.valid()) {
+            BlockDesc pre_next{0, 0};
+            if (cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
+            const int n = cur.count;
+            const size_t o_row_a = ((size_t)cur.z * p.seq_q + (size_t)cur.g * kTile + row_a) * kTile;
+            const size_t o_row_b = o_row_a + (size_t)8 * kTile;
+            const size_t lse_a = (size_t)cur.z * p.seq_q + (size_t)cur.g * kTile + row_a;
+            if (n == 0) {
+                // a block row without blocks: zeros, lse = -inf
+                for (int c = q4 * 8; c < kTile; c += 32) {
+                    *reinterpret_cast<uint4*>(p.o + o_row_a + c) = make_uint4(0u, 0u, 0u, 0u);
+                    *reinterpret_cast<uint4*>(p.o + o_row_b + c) = make_uint4(0u, 0u, 0u, 0u);
+                }
+                if (q4 == 0 && p.lse) { p.lse[lse_a] = -INFINITY; p.lse[lse_a + 8] = -INFINITY; }
+            } else {
+                const uint8_t* kpm_row = p.kpm ? p.kpm + (size_t)(cur.z / p.kpm_div) * p.kpm_stride : nullptr;
+                const int qpos_a = cur.g * kTile + row_a;
+                // Bits 0-15: columns (u, e) of row a that are masked in block `col`; bits 16-31: row b.
+                auto block_mask = [&](const BlockDesc& desc) -> uint32_t {
+                    const int col = desc.col();
+                    uint32_t m = 0;
+                    if (p.quadrants) {
+                        // this lane's rows lie in row half quad / 2; its columns 8u + .. in column half u / 4
+                        const uint32_t present = (uint32_t)desc.idx >> (2 * (quad >> 1));
+                        if (!(present & 1u)) m |= 0x00FF00FFu;
+                        if (!(present & 2u)) m |= 0xFF00FF00u;
+                    }
+                    const int k0 = col * kTile + 2 * q4;
+                    if (p.causal && col * kTile + kTile - 1 > qpos_a) {
+#pragma unroll
+                        for (int u = 0; u < 8; ++u)
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                const int kpos = k0 + 8 * u + e;
+                                if (kpos > qpos_a) m |= 1u << (2 * u + e);
+                                if (kpos > qpos_a + 8) m |= 1u << (16 + 2 * u + e);
+                            }
+                    }
+                    if (kpm_row) {
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            if (kpm_row[k0 + 8 * u]) m |= 0x00010001u << (2 * u);
+                            if (kpm_row[k0 + 8 * u + 1]) m |= 0x00010001u << (2 * u + 1);
+                        }
+                    }
+                    return m;
+                };
+                // One pass over the row's blocks with a running row maximum m (in units of log2:
+                // t = scale * log2(e) * s).  P_j = exp2(t_j - m) goes to shared memory as a K-major operand
+                // tile, O += P_j V_j accumulates in TMEM, l sums the P's.  m is only raised when a block's
+                // maximum exceeds it by more than kSlack (P stays <= 2^kSlack, exact in fp32 sums and well
+                // inside the 16-bit range); raising it rescales O in TMEM and l by exp2(m_old - m_new),
+                // which needs the previous P V to have retired.
+                constexpr float kSlack = 8.f;
+                float m_a = -INFINITY, m_b = -INFINITY;
+                // row sums: per row two independent two-wide accumulators (even / odd column units)
+                uint64_t la2[2] = {0ull, 0ull}, lb2[2] = {0ull, 0ull};
+                DescWindow win;
+                win.begin(p.blocks, cur.first, cur.count, pre, lane);
+                for (int j = 0; ok && j < n; ++j) {
+                    const int t = t0 + j, st = t & 1;
+                    // (the mask of a block is computed before the wait for its S tile: off the critical chain)
+                    uint32_t mask = 0u;
+                    if (MASKED && masked_op) mask = block_mask(win.get(p.blocks, cur.first, cur.count, j, lane));
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->qk_done[g][st], (uint32_t)(t >> 1) & 1u, abort_flag, p.status)) != 0;
+                    if (!ok) break;
+                    tc_fence_after();
+                    uint32_t r[32];
+                    tc_ld_16x256b_x8(s_tmem + lane_field, r);
+                    tc_wait_ld();
+                    release_accumulator(&bars->s_empty[g], lane);      // S is in registers: Q K^T of the next tile may run
+                    // Masked elements (above the diagonal, padded keys, quadrants outside a block-32 layout) are
+                    // overwritten by -inf (+inf for a negative scale): they lose every maximum and their exp2 is
+                    // exactly 0 (the host keeps the scale factor away from 0, so inf * scale is never NaN).
+                    if (MASKED && masked_op && mask != 0u) {
+                        const uint32_t gone = flip ? 0x7F800000u : 0xFF800000u;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const int u = i >> 1, e = i & 1;
+                            if ((mask >> i) & 1u) r[4 * u + e] = gone;
+                            if ((mask >> (16 + i)) & 1u) r[4 * u + 2 + e] = gone;
+                        }
+                    }
+                    // block maxima of the raw scores (for a negative scale: of their negatives), two chains per row
+                    float x_a, x_b;
+                    {
+                        float a0, a1, b0, b1;
+                        if (!flip) {
+                            a0 = a1 = b0 = b1 = -INFINITY;
+#pragma unroll
+                            for (int u = 0; u < 8; u += 2) {
+                                a0 = fmax3(a0, __uint_as_float(r[4 * u]), __uint_as_float(r[4 * u + 1]));
+                                b0 = fmax3(b0, __uint_as_float(r[4 * u + 2]), __uint_as_float(r[4 * u + 3]));
+                                a1 = fmax3(a1, __uint_as_float(r[4 * u + 4]), __uint_as_float(r[4 * u + 5]));
+                                b1 = fmax3(b1, __uint_as_float(r[4 * u + 6]), __uint_as_float(r[4 * u + 7]));
+                            }
+                            x_a = fmaxf(a0, a1); x_b = fmaxf(b0, b1);
+                        } else {
+                            a0 = a1 = b0 = b1 = INFINITY;
+#pragma unroll
+                            for (int u = 0; u < 8; u += 2) {
+                                a0 = fmin3(a0, __uint_as_float(r[4 * u]), __uint_as_float(r[4 * u + 1]));
+                                b0 = fmin3(b0, __uint_as_float(r[4 * u + 2]), __uint_as_float(r[4 * u + 3]));
+                                a1 = fmin3(a1, __uint_as_float(r[4 * u + 4]), __uint_as_float(r[4 * u + 5]));
+                                b1 = fmin3(b1, __uint_as_float(r[4 * u + 6]), __uint_as_float(r[4 * u + 7]));
+                            }
+                            x_a = -fminf(a0, a1); x_b = -fminf(b0, b1);
+                        }
+                    }
+                    x_a = fmaxf(x_a, __shfl_xor_sync(0xffffffffu, x_a, 1)); x_a = fmaxf(x_a, __shfl_xor_sync(0xffffffffu, x_a, 2));
+                    x_b = fmaxf(x_b, __shfl_xor_sync(0xffffffffu, x_b, 1)); x_b = fmaxf(x_b, __shfl_xor_sync(0xffffffffu, x_b, 2));
+                    x_a = x_a == -INFINITY ? -INFINITY : x_a * c2abs;       // maxima of t over the block
+                    x_b = x_b == -INFINITY ? -INFINITY : x_b * c2abs;
+                    if (j == 0) {
+                        m_a = x_a; m_b = x_b;                                 // the row's first P V overwrites O
+                    } else {
+                        // raise a row's maximum only when it is overdue (or was -inf: nothing kept yet)
+                        const bool up_a = x_a > m_a + kSlack || (m_a == -INFINITY && x_a > -INFINITY);
+                        const bool up_b = x_b > m_b + kSlack || (m_b == -INFINITY && x_b > -INFINITY);
+                        if (__any_sync(0xffffffffu, up_a || up_b)) {
+                            const float al_a = !up_a ? 1.f : (m_a == -INFINITY ? 0.f : attn_exp2(m_a - x_a));
+                            const float al_b = !up_b ? 1.f : (m_b == -INFINITY ? 0.f : attn_exp2(m_b - x_b));
+                            if (up_a) { m_a = x_a; const uint64_t f = f2_pack(al_a, al_a); la2[0] = f2_mul(la2[0], f); la2[1] = f2_mul(la2[1], f); }
+                            if (up_b) { m_b = x_b; const uint64_t f = f2_pack(al_b, al_b); lb2[0] = f2_mul(lb2[0], f); lb2[1] = f2_mul(lb2[1], f); }
+                            // O is complete up to the previous tile once that tile's P V has retired
+                            if (!__all_sync(0xffffffffu, mbar_wait(&bars->pv_done[g][(t - 1) & 1], (uint32_t)((t - 1) >> 1) & 1u, abort_flag, p.status))) { ok = false; break; }
+                            tc_fence_after();
+                            for (int c = 0; c < kTile; c += 16) {
+                                uint32_t o[8];
+                                tc_ld_16x256b_x2(o_tmem + lane_field + (uint32_t)c, o);
+                                tc_wait_ld();
+#pragma unroll
+                                for (int u = 0; u < 2; ++u) {
+                                    o[4 * u] = __float_as_uint(__uint_as_float(o[4 * u]) * al_a);
+                                    o[4 * u + 1] = __float_as_uint(__uint_as_float(o[4 * u + 1]) * al_a);
+                                    o[4 * u + 2] = __float_as_uint(__uint_as_float(o[4 * u + 2]) * al_b);
+                                    o[4 * u + 3] = __float_as_uint(__uint_as_float(o[4 * u + 3]) * al_b);
+                                }
+                                tc_st_16x256b_x2(o_tmem + lane_field + (uint32_t)c, o);
+                            }
+                            tc_wait_st();
+                            tc_fence_before();      // ordered before the P V this block's arrival releases
+                        }
+                    }
+                    const float sub_a = m_a == -INFINITY ? 0.f : m_a, sub_b = m_b == -INFINITY ? 0.f : m_b;
+                    // P = exp2(c2 * s - m): per pair of columns one two-wide FMA, two exp2, one two-wide add into
+                    // the row sum and one pack.  w[4k + i]: matrix (unit 2k, row a), (2k, b), (2k + 1, a), (2k + 1, b).
+                    const uint64_t na = f2_pack(-sub_a, -sub_a), nb = f2_pack(-sub_b, -sub_b);
+                    uint32_t w[16];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int u = 2 * k + (i >> 1), h = i & 1;
+                            const uint64_t t2 = f2_fma(f2_pack(__uint_as_float(r[4 * u + 2 * h]), __uint_as_float(r[4 * u + 2 * h + 1])),
+                                                       c2p, h ? nb : na);
+                            float e0, e1;
+                            f2_unpack(t2, e0, e1);
+                            e0 = attn_exp2(e0); e1 = attn_exp2(e1);
+                            if (h) lb2[i >> 1] = f2_add(lb2[i >> 1], f2_pack(e0, e1));
+                            else   la2[i >> 1] = f2_add(la2[i >> 1], f2_pack(e0, e1));
+                            w[4 * k + i] = pack2<BF16>(e0, e1);
+                        }
+                    }
+                    // the P buffer must have been read by the MMAs that used it last (those of the tile before);
+                    // the wait comes after the arithmetic so that it rarely has anything left to wait for
+                    if (t > 0 && !__all_sync(0xffffffffu, mbar_wait(&bars->pv_done[g][(t - 1) & 1], (uint32_t)((t - 1) >> 1) & 1u, abort_flag, p.status))) { ok = false; break; }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        stmatrix_x4(p_tile ^ (uint32_t)(k << 5), w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
+                    fence_async_shared();           // generic-proxy writes -> visible to the tensor core's reads
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars->p_full[g]);
+                }
+                t0 += n;
+                if (!ok) break;
+                // ---- end of the row: O / l and the log-sum-exp
+                float l_a, l_b;
+                {
+                    float x0, x1, y0, y1;
+                    f2_unpack(f2_add(la2[0], la2[1]), x0, x1);
+                    f2_unpack(f2_add(lb2[0], lb2[1]), y0, y1);
+                    l_a = x0 + x1; l_b = y0 + y1;
+                }
+                l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+                l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+                const float inv_a = l_a > 0.f ? __frcp_rn(l_a) : 0.f, inv_b = l_b > 0.f ? __frcp_rn(l_b) : 0.f;
+                ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[g], (uint32_t)i_no & 1u, abort_flag, p.status)) != 0;
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t acc[2][16];
+                tc_ld_16x256b_x4(o_tmem + lane_field, acc[0]);
+                tc_ld_16x256b_x4(o_tmem + lane_field + 32u, acc[1]);
+                tc_wait_ld();
+                release_accumulator(&bars->o_empty[g], lane);          // the next row's P V may overwrite O
+#pragma unroll
+                for (int hc = 0; hc < 2; ++hc) {
+                    uint32_t ta[4], tb[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        // a row without an unmasked score: its accumulator holds 0 * garbage-free sums, write 0
+                        ta[u] = pack2<BF16>(inv_a > 0.f ? __uint_as_float(acc[hc][4 * u]) * inv_a : 0.f,
+                                            inv_a > 0.f ? __uint_as_float(acc[hc][4 * u + 1]) * inv_a : 0.f);
+                        tb[u] = pack2<BF16>(inv_b > 0.f ? __uint_as_float(acc[hc][4 * u + 2]) * inv_b : 0.f,
+                                            inv_b > 0.f ? __uint_as_float(acc[hc][4 * u + 3]) * inv_b : 0.f);
+                    }
+                    quad_transpose(ta, q4);         // now columns 32 hc + 8 * q4 .. + 7 of the row
+                    quad_transpose(tb, q4);
+                    *reinterpret_cast<uint4*>(p.o + o_row_a + 32 * hc + 8 * q4) = make_uint4(ta[0], ta[1], ta[2], ta[3]);
+                    *reinterpret_cast<uint4*>(p.o + o_row_b + 32 * hc + 8 * q4) = make_uint4(tb[0], tb[1], tb[2], tb[3]);
+                }
+                if (q4 == 0 && p.lse) {
+                    // natural-log sum of exponentials of the scaled, masked scores
+                    p.lse[lse_a] = l_a > 0.f ? (m_a + __log2f(l_a)) * 0.6931471805599453f : -INFINITY;
+                    p.lse[lse_a + 8] = l_b > 0.f ? (m_b + __log2f(l_b)) * 0.6931471805599453f : -INFINITY;
+                }
+                ++i_no;
+            }
+            pre = pre_next;
+            cur.advance();
+        }
     }
 
     // ---------------------------------------------------------------- teardown
@@ -693,15 +1238,15 @@ int attention_forward(int dtype, const void* q, const void* k, const void* v, vo
                       cudaStream_t stream) {
     using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const AttnParams);
     const bool masked = causal != 0 || kpm != nullptr || quadrants != 0;
-    // two softmax warpgroups where two O accumulators fit into the CTA's 256 TMEM columns
-    const int wgs = head_dim == 64 ? 2 : 1;
+    // head dim 64: two independent pipelines per CTA; head dim 128: one softmax warpgroup per CTA
+    const bool pipes = head_dim == 64;
     KernelFn kernel;
     if (dtype == BSA_DTYPE_BF16) {
-        if (wgs == 2) kernel = masked ? attention_forward_kernel<true, true, 2> : attention_forward_kernel<true, false, 2>;
-        else          kernel = masked ? attention_forward_kernel<true, true, 1> : attention_forward_kernel<true, false, 1>;
+        if (pipes) kernel = masked ? attention_forward_pipes_kernel<true, true> : attention_forward_pipes_kernel<true, false>;
+        else       kernel = masked ? attention_forward_kernel<true, true, 1> : attention_forward_kernel<true, false, 1>;
     } else {
-        if (wgs == 2) kernel = masked ? attention_forward_kernel<false, true, 2> : attention_forward_kernel<false, false, 2>;
-        else          kernel = masked ? attention_forward_kernel<false, true, 1> : attention_forward_kernel<false, false, 1>;
+        if (pipes) kernel = masked ? attention_forward_pipes_kernel<false, true> : attention_forward_pipes_kernel<false, false>;
+        else       kernel = masked ? attention_forward_kernel<false, true, 1> : attention_forward_kernel<false, false, 1>;
     }
     AttnParams p{};
     p.dtiles = (int)(head_dim / kTile);
@@ -711,7 +1256,8 @@ int attention_forward(int dtype, const void* q, const void* k, const void* v, vo
     p.vring_shift = p.dtiles == 1 ? 2 : 1;
     // at least 80 KB, so that never more than two CTAs (256 TMEM columns each) share an SM
     p.qbufs = p.dtiles == 1 ? 2 : 1;
-    int smem_bytes = 1024 + ((p.qbufs + p.ring + p.vring) * p.dtiles + 2) * kTileBytes + (int)sizeof(AttnBarriers);
+    int smem_bytes = pipes ? 1024 + 2 * kPipeTiles * kTileBytes + (int)sizeof(PipeBarriers)
+                           : 1024 + ((p.qbufs + p.ring + p.vring) * p.dtiles + 2) * kTileBytes + (int)sizeof(AttnBarriers);
     if (smem_bytes < 80 * 1024) smem_bytes = 80 * 1024;
     // Set on every call (a per-device attribute); this and the cudaSetDevice below also bind the
     // device's primary context to the calling thread, which the driver call behind make_map needs.
@@ -755,10 +1301,13 @@ int attention_forward(int dtype, const void* q, const void* k, const void* v, vo
 
     const int sms = sm_count();
     if (sms <= 0) return BSA_ERR_LAUNCH;
-    const unsigned grid = (unsigned)(p.items < 2 * sms ? p.items : 2 * sms);
-    p.stride_z = (int)grid / p.groups;
-    p.stride_rem = (int)grid % p.groups;
-    kernel<<<grid, (4 + 4 * wgs) * 32, smem_bytes, stream>>>(map_q, map_k, map_v, p);
+    // walkers of the work-item list: the CTAs, or (head dim 64) the two pipelines of every CTA
+    const int wanted = pipes ? (p.items + 1) / 2 : p.items;
+    const unsigned grid = (unsigned)(wanted < 2 * sms ? wanted : 2 * sms);
+    const int walkers = pipes ? 2 * (int)grid : (int)grid;
+    p.stride_z = walkers / p.groups;
+    p.stride_rem = walkers % p.groups;
+    kernel<<<grid, (pipes ? 12 : 8) * 32, smem_bytes, stream>>>(map_q, map_k, map_v, p);
     return launch_status();
 }
 

@@ -50,16 +50,6 @@
 namespace bsa {
 namespace {
 
-// Optional role timing (compile with -DBSA_ATTN_TIMING): CTA 0 adds the cycles its roles spent in
-// each phase to 64-bit counters at byte offset 64 of the workspace (slot = counter index).
-#ifdef BSA_ATTN_TIMING
-#define BT_CLOCK() clock64()
-#define BT_ADD(slot, cycles) do { if (blockIdx.x == 0) atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 8 + (slot), (unsigned long long)(cycles)); } while (0)
-#else
-#define BT_CLOCK() 0ll
-#define BT_ADD(slot, cycles) do { } while (0)
-#endif
-
 constexpr int kBwdTmemCols = 512;
 constexpr int kBwdAccCol0 = 256;
 constexpr int kBwdStatBytes = kTile * 8;      // (lse2, D) of the 64 query rows of a block
@@ -221,10 +211,8 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                     const BlockDesc d = win.get(p.blocks, cur.first, cur.count, j, lane);
                     const int other = COL ? d.row() : d.col();
                     const int stage = y_no & ring_mask;
-                    [[maybe_unused]] const long long tp0 = BT_CLOCK();
                     ok = __all_sync(0xffffffffu, mbar_wait(&bars->out_done[stage], ((uint32_t)(y_no >> p.ring_shift) & 1u) ^ 1u,
                                                            abort_flag, p.status)) != 0;
-                    if (lane == 0) BT_ADD(0, BT_CLOCK() - tp0);
                     if (ok && elect_one()) {
                         uint64_t* full = &bars->y_full[stage];
                         mbar_expect_tx(full, (uint32_t)(2 * set_bytes + (COL ? kBwdStatBytes : 0)));
@@ -273,12 +261,9 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
             const int s_end = s_no + n;
             for (int s = s_no + ((par - s_no) & 1); s < s_end; s += 2) {
                 const int stage = s & ring_mask;
-                [[maybe_unused]] const long long ti0 = BT_CLOCK();
                 ok = __all_sync(0xffffffffu, mbar_wait(&bars->y_full[stage], (uint32_t)(s >> p.ring_shift) & 1u, abort_flag, p.status)) != 0;
-                [[maybe_unused]] const long long ti1 = BT_CLOCK();
                 if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->t_empty[par], ((uint32_t)(s >> 1) & 1u) ^ 1u, abort_flag, p.status)) != 0;
                 if (!ok) break;
-                [[maybe_unused]] const long long ti2 = BT_CLOCK();
                 tc_fence_after();
                 const uint32_t d = tmem_base + (uint32_t)(par * 2 * kTile + which * kTile);
                 if (elect_one()) {
@@ -292,7 +277,6 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                     tc_commit(&bars->t_full[par]);
                 }
                 __syncwarp();
-                if (warp == kBwdFirstTWarp && lane == 0) { BT_ADD(1, ti1 - ti0); BT_ADD(2, ti2 - ti1); BT_ADD(3, BT_CLOCK() - ti2); }
             }
             if (!ok) break;
             if (elect_one()) tc_commit(&bars->x_empty[xb]);       // this issuer's reads of the X pair have been issued
@@ -327,18 +311,15 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                 const uint32_t d = tmem_base + (uint32_t)(kBwdAccCol0 + ((ob_acc * kOuts + (COL ? w : 0)) * p.parts + (COL ? 0 : (kk0 >> 1) & (p.parts - 1))) * p.head_dim);
                 for (int j = 0; ok && j < n; ++j) {
                     const int s = s_no + j, stage = s & ring_mask, ob = s & (p.opbufs - 1);
-                    [[maybe_unused]] const long long to0 = BT_CLOCK();
                     // the accumulator set is free once the item that used it last (obufs items ago) has been
                     // read out; that item's barrier is the one of its parity
                     if (j == 0 && o_no >= p.obufs) {
                         const int prev = o_no - p.obufs;
                         ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_empty[prev & 1], (uint32_t)(prev >> 1) & 1u, abort_flag, p.status)) != 0;
                     }
-                    [[maybe_unused]] const long long to1 = BT_CLOCK();
                     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->y_full[stage], (uint32_t)(s >> p.ring_shift) & 1u, abort_flag, p.status)) != 0;
                     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->op_full[ob], (uint32_t)(s >> p.op_shift) & 1u, abort_flag, p.status)) != 0;
                     if (!ok) break;
-                    [[maybe_unused]] const long long to2 = BT_CLOCK();
                     tc_fence_after();
                     if (elect_one()) {
                         // A = operand tile (K-major), B = a Y tile set with N = head_dim contiguous
@@ -352,7 +333,6 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                         if (j == n - 1) tc_commit(&bars->o_full[o_no & 1]);
                     }
                     __syncwarp();
-                    if (w == 0 && lane == 0) { BT_ADD(4, to1 - to0); BT_ADD(5, to2 - to1); BT_ADD(6, BT_CLOCK() - to2); }
                 }
                 s_no += n;
                 ++o_no;
@@ -376,7 +356,6 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
         const int out_rows = COL ? p.seq_k : p.seq_q;
         int s_no = 0, o_no = 0;
         bool ok = true;
-        [[maybe_unused]] const long long t_begin = BT_CLOCK();
         Cursor cur;
         cur.init(p);
         BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
@@ -426,10 +405,8 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                         sub_lo = COL ? ((bits >> h) & 1u) != 0 : ((bits >> (2 * h)) & 1u) != 0;
                         sub_hi = COL ? ((bits >> (2 + h)) & 1u) != 0 : ((bits >> (2 * h + 1)) & 1u) != 0;
                     }
-                    [[maybe_unused]] const long long tc0 = BT_CLOCK();
                     ok = __all_sync(0xffffffffu, mbar_wait(&bars->t_full[tb], (uint32_t)(s >> 1) & 1u, abort_flag, p.status)) != 0;
                     if (!ok) break;
-                    [[maybe_unused]] const long long tc1 = BT_CLOCK();
                     tc_fence_after();
                     uint32_t r1[32], r2[32];
                     tc_ld_16x256b_x8(tmem_base + lane_field + (uint32_t)(tb * 2 * kTile), r1);
@@ -447,7 +424,6 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                     }
                     tc_wait_ld();
                     release_accumulator(&bars->t_empty[tb], lane);
-                    [[maybe_unused]] const long long tc2 = BT_CLOCK();
                     // the operand tiles of this buffer must have been read by the MMAs of block s - opbufs
                     const int ob = s & (p.opbufs - 1);
                     if (s >= p.opbufs) {
@@ -456,7 +432,6 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                                                                (uint32_t)(sp >> p.ring_shift) & 1u, abort_flag, p.status)) != 0;
                         if (!ok) break;
                     }
-                    [[maybe_unused]] const long long tc3 = BT_CLOCK();
                     const uint32_t tile0 = smem_u32(op_smem + (ob * kOpTiles) * kTileBytes) + op_row;
                     const int other0 = other * kTile + 2 * q4;          // position of column u = 0, e = 0
                     // Does any lane of the warp have a masked element in this block?  Most blocks of a causal
@@ -530,12 +505,9 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                     };
                     if (MASKED && need) emit(std::true_type{});
                     else                emit(std::false_type{});
-                    [[maybe_unused]] const long long tc4 = BT_CLOCK();
                     fence_async_shared();           // generic-proxy writes -> visible to the tensor core's reads
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars->op_full[ob]);
-                    if (warp == 0 && lane == 0) { BT_ADD(7, tc1 - tc0); BT_ADD(8, tc2 - tc1); BT_ADD(9, tc3 - tc2); BT_ADD(10, tc4 - tc3); BT_ADD(11, BT_CLOCK() - tc4); BT_ADD(12, 1); }
-                    if (warp == 4 && lane == 0) { BT_ADD(17, tc1 - tc0); BT_ADD(18, tc3 - tc2); }
                 }
                 s_no += n;
                 if (!ok) break;
@@ -547,11 +519,8 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                 // a wait one phase early and the kernel ended in a time-out.)
                 if (wg == (o_no & 1)) {
                     const int ob_acc = o_no & (p.obufs - 1);
-                    [[maybe_unused]] const long long te0 = BT_CLOCK();
                     ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[o_no & 1], (uint32_t)(o_no >> 1) & 1u, abort_flag, p.status)) != 0;
                     if (!ok) break;
-                    [[maybe_unused]] const long long te1 = BT_CLOCK();
-                    if ((warp & 3) == 0 && lane == 0) BT_ADD(13 + 2 * wg, te1 - te0);
                     tc_fence_after();
 #pragma unroll
                     for (int a = 0; a < kOuts; ++a) {
@@ -581,14 +550,12 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                             *reinterpret_cast<uint4*>(out + out_b + c + 8 * q4) = make_uint4(tb2[0], tb2[1], tb2[2], tb2[3]);
                         }
                     }
-                    if ((warp & 3) == 0 && lane == 0) BT_ADD(19 + wg, BT_CLOCK() - te1);
                 }
                 ++o_no;
             }
             pre = pre_next;
             cur.advance();
         }
-        if (warp == 0 && lane == 0) BT_ADD(14, BT_CLOCK() - t_begin);
     }
 
     // ---------------------------------------------------------------- teardown

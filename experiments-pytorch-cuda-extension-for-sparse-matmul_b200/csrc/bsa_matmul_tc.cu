@@ -68,16 +68,6 @@ constexpr int kFirstMmaWarp = kProducerWarps;
 constexpr int kFirstEpilogueWarp = kFirstMmaWarp + kMmaWarps;
 constexpr int kThreads = (kFirstEpilogueWarp + 8) * 32;
 
-// Optional role timing (compile with -DBSA_TC_TIMING): CTA 0 adds the cycles each role spent in
-// its waits to 64-bit counters at byte offset 64 of the workspace (slot = counter index).
-#ifdef BSA_TC_TIMING
-#define TC_CLOCK() clock64()
-#define TC_TIME_OUT(slot, cycles) do { if (blockIdx.x == 0) atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 8 + (slot), (unsigned long long)(cycles)); } while (0)
-#else
-#define TC_CLOCK() 0ll
-#define TC_TIME_OUT(slot, cycles) do { } while (0)
-#endif
-
 struct __align__(8) Barriers {
     uint64_t full[kMaxStages];
     uint64_t empty[kMaxStages];
@@ -234,20 +224,16 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         int stage = warp, step0 = 0;         // step0: sequence number of the accumulation's first K-step
         uint32_t phase = 0;
         bool ok = true;
-        long long t_wait = 0, t_issue = 0, t_get = 0, t_item = 0;
-        [[maybe_unused]] const long long t_begin = TC_CLOCK();
         Cursor cur;
         cur.init(p, p.split);
         BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
         while (ok && cur.valid()) {
-            [[maybe_unused]] const long long t_i0 = TC_CLOCK();
             BlockDesc pre_next{0, 0};
             if (cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
             int flushes, ksteps;
             item_shape<MODE>(p, cur.count << p.split, flushes, ksteps);
             DescWindow win;
             win.begin(p.blocks, cur.first, cur.count, pre, lane);
-            t_item += TC_CLOCK() - t_i0;
             for (int f = 0; ok && f < flushes; ++f) {
                 const int nb = b_tiles<MODE>(p, cur.count << p.split, cur.chunk, f);
                 // The stage count is a multiple of the producer count, so a stage is always
@@ -256,7 +242,6 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 // every phase of each barrier it ever waits on.
                 for (int k = (warp - step0) & (kProducerWarps - 1); ok && k < ksteps; k += kProducerWarps) {
                     {
-                        [[maybe_unused]] const long long t_g0 = TC_CLOCK();
                         int cols[4] = {0, 0, 0, 0};
                         BlockDesc d{0, 0};
                         if (is_sdd) {
@@ -266,14 +251,10 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         } else {
                             d = tile_desc(win, p, cur, k, lane);
                         }
-                        t_get += TC_CLOCK() - t_g0;
                         {
                             // the whole warp waits and computes the copies' operands (warp-uniform
                             // code keeps them in uniform registers); one elected lane issues
-                            [[maybe_unused]] const long long t0 = TC_CLOCK();
                             ok = __all_sync(0xffffffffu, mbar_wait(&bars->empty[stage], phase ^ 1, &bars->abort_flag, p.status)) != 0;
-                            [[maybe_unused]] const long long t1 = TC_CLOCK();
-                            t_wait += t1 - t0;
                             if (ok && elect_one()) {
                                 uint8_t* slot = stage_base + stage * stage_bytes;
                                 uint64_t* full = &bars->full[stage];
@@ -311,7 +292,6 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                 }
                             }
                             __syncwarp();
-                            t_issue += TC_CLOCK() - t1;
                         }
                     }
                     stage += kProducerWarps;
@@ -322,7 +302,6 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             pre = pre_next;
             cur.advance();
         }
-        if (lane == 0 && warp == 0) { TC_TIME_OUT(0, TC_CLOCK() - t_begin); TC_TIME_OUT(1, t_wait); TC_TIME_OUT(2, t_issue); TC_TIME_OUT(9, t_get); TC_TIME_OUT(11, t_item); }
         if (lane == 0 && *(volatile int*)&bars->abort_flag) {
             // Give copies that were issued a bounded chance to land before the CTA exits.
             const unsigned long long t0 = global_ns();
@@ -351,8 +330,6 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const uint32_t part_col = is_sdd ? 0u : (uint32_t)(w * (kAccCols / p.issuers));
             const int issuer_mask = p.issuers - 1;       // issuers is 1, 2 or 4 (no runtime division here:
                                                          // it costs a lone thread hundreds of cycles)
-            long long t_full = 0, t_acc = 0, t_mma = 0, t_commit = 0, t_desc = 0, t_kloop = 0, t_accfull = 0;
-            [[maybe_unused]] const long long t_begin = TC_CLOCK();
             Cursor cur;
             cur.init(p, p.split);
             for (; ok && cur.valid(); cur.advance()) {
@@ -370,30 +347,23 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     }
                     const int nb = b_tiles<MODE>(p, cur.count << p.split, cur.chunk, f);
                     const uint32_t idesc = p.idesc | ((uint32_t)((nb * kTile) >> 3) << 17);
-                    { [[maybe_unused]] const long long t0 = TC_CLOCK();
-                      ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_empty[acc], ((uint32_t)(flush_no >> kBufShift) & 1u) ^ 1u, &bars->abort_flag, p.status)) != 0;
-                      t_acc += TC_CLOCK() - t0; }
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_empty[acc], ((uint32_t)(flush_no >> kBufShift) & 1u) ^ 1u, &bars->abort_flag, p.status)) != 0;
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t d = tmem_base + (uint32_t)(acc * kBufCols) + part_col;
                     bool issued = false;
-                    [[maybe_unused]] const long long tk0 = TC_CLOCK();
                     // dsd / dds: K-step n belongs to issuer n % issuers (the stage count is a
                     // multiple of it, so a stage always belongs to the same issuer)
                     const int k_first = is_sdd ? 0 : ((w - step0) & issuer_mask);
                     const int k_inc = is_sdd ? 1 : p.issuers;
                     for (int k = k_first; k < ksteps; k += k_inc) {
                         {
-                            { [[maybe_unused]] const long long t0 = TC_CLOCK();
-                              ok = __all_sync(0xffffffffu, mbar_wait(&bars->full[stage], phase, &bars->abort_flag, p.status)) != 0;
-                              t_full += TC_CLOCK() - t0; }
+                            ok = __all_sync(0xffffffffu, mbar_wait(&bars->full[stage], phase, &bars->abort_flag, p.status)) != 0;
                             if (!ok) break;
-                            [[maybe_unused]] const long long tm0 = TC_CLOCK();
                             tc_fence_after();
                             const uint32_t slot = smem_u32(stage_base + stage * stage_bytes);
                             const uint64_t da = make_tile_desc(slot, a_mn_major);
                             const uint64_t db = make_tile_desc(slot + kTileBytes, b_mn_major);
-                            [[maybe_unused]] const long long tm1 = TC_CLOCK();
                             if (elect_one()) {
 #pragma unroll
                                 for (int kk = 0; kk < kTile / 16; ++kk)
@@ -403,22 +373,18 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                             }
                             __syncwarp();
                             issued = true;
-                            [[maybe_unused]] const long long tm2 = TC_CLOCK();
-                            t_desc += tm1 - tm0; t_mma += tm2 - tm1; t_commit += TC_CLOCK() - tm2;
                         }
                         stage += k_inc;
                         if (stage >= p.stages) { stage -= p.stages; phase ^= 1; }
                     }
                     step0 += ksteps;
                     if (!ok) break;
-                    [[maybe_unused]] const long long tk1 = TC_CLOCK();
                     // the accumulation (dsd / dds: this issuer's partial, if it had a K-step) is complete
                     if (elect_one()) {
                         if (issued) tc_commit(&bars->acc_full[acc]);
                         else        mbar_arrive(&bars->acc_full[acc]);
                     }
                     __syncwarp();
-                    t_kloop += tk1 - tk0; t_accfull += TC_CLOCK() - tk1;
                 }
             }
             // All MMAs issued by the elected lane (the same one every time) must have retired before
@@ -428,9 +394,6 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 mbar_wait(&bars->drain, 0, &bars->abort_flag, p.status);
             }
             __syncwarp();
-            if (w == 0 && lane == 0) { TC_TIME_OUT(3, TC_CLOCK() - t_begin); TC_TIME_OUT(4, t_full); TC_TIME_OUT(5, t_acc);
-                          TC_TIME_OUT(12, t_mma); TC_TIME_OUT(13, t_commit); TC_TIME_OUT(14, t_desc);
-                          TC_TIME_OUT(15, t_kloop); TC_TIME_OUT(16, t_accfull); }
         }
         __syncwarp();
     } else {
@@ -445,8 +408,6 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         int flush_no = 0, step = 0;
         int tile_no = 0;                    // sdd: slabs this warp has sent so far (staging slab = tile_no & 1)
         bool ok = true;
-        long long t_accf = 0, t_ld = 0, t_write = 0;
-        [[maybe_unused]] const long long t_begin = TC_CLOCK();
         Cursor cur;
         cur.init(p, p.split);
         BlockDesc pre{0, 0};
@@ -471,9 +432,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (owner != group) continue;
                 const int tiles = b_tiles<MODE>(p, cur.count << p.split, cur.chunk, f);
                 if (have_acc) {
-                    [[maybe_unused]] const long long t0 = TC_CLOCK();
                     ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_full[acc], acc_phase, &bars->abort_flag, p.status)) != 0;
-                    t_accf += TC_CLOCK() - t0;
                     if (!ok) break;
                     tc_fence_after();
                 }
@@ -534,7 +493,6 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         }
                         ++tile_no;
                     };
-                    [[maybe_unused]] const long long t_a = TC_CLOCK();
                     uint32_t ra[32], rb[32];
                     tc_ld_16x256b_x8(tbase, ra);
                     for (int t = 0; t < tiles; t += 2) {
@@ -548,7 +506,6 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         else               release_accumulator(&bars->acc_empty[acc], lane);
                         store_tile(rb, t + 1);
                     }
-                    t_ld += TC_CLOCK() - t_a;
                     continue;
                 }
                 for (int t = 0; t < tiles; ++t) {
@@ -576,7 +533,6 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16)
                                            + (uint32_t)(acc * kBufCols + t * kTile);
                     const bool last_tile = have_acc && t == tiles - 1;
-                    [[maybe_unused]] const long long t_a = TC_CLOCK();
                     if (!have_acc || parts == 1) {
                         uint32_t v[kTile];          // fp32 bit patterns of this lane's row
                         if (have_acc) {
@@ -586,11 +542,8 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
                             for (int c = 0; c < kTile; ++c) v[c] = 0u;
                         }
-                        [[maybe_unused]] const long long t_m = TC_CLOCK();
                         if (last_tile) release_accumulator(&bars->acc_empty[acc], lane);
                         if (writer) store_row<kTile>(dst, v, cols_valid, p.c_vec8 != 0, bf16_out);
-                        t_write += TC_CLOCK() - t_m;
-                        t_ld -= TC_CLOCK() - t_m;
                     } else {
                         // dsd / dds: issuer w holds a partial sum iff one of the K-steps
                         // step0 .. step0 + ksteps - 1 is congruent to w; the first K-step's issuer
@@ -614,8 +567,6 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                             if (writer) store_row<32>(dst + h * 32, v, cols_valid - h * 32, p.c_vec8 != 0, bf16_out);
                         }
                     }
-                    [[maybe_unused]] const long long t_b = TC_CLOCK();
-                    t_ld += t_b - t_a;
                 }
             }
             pre = pre_next;
@@ -624,7 +575,6 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // the staging tiles must have been read before the CTA gives its shared memory back
         if (is_sdd && elect_one()) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         if (lane == 0 && quad == 0 && group == 0) {
-            TC_TIME_OUT(6, TC_CLOCK() - t_begin); TC_TIME_OUT(7, t_accf); TC_TIME_OUT(8, t_ld); TC_TIME_OUT(10, t_write);
         }
     }
 

@@ -36,6 +36,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
+// Non-blocking test of a phase (for a role that polls several barriers and serves whichever is ready).
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -152,6 +162,49 @@ __device__ __forceinline__ float attn_exp2(float x) {
     return y;
 }
 
+// Three-input maximum / minimum and two-wide fp32 arithmetic (one instruction for two lanes of a
+// 64-bit register pair): they halve the instruction count of the softmax element loops.
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ float fmin3(float a, float b, float c) {
+    float d;
+    asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+    return d;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+// Four 8 x 8 matrices of 16-bit elements from the m8n8 fragment layout (lane t holds elements
+// 2 (t % 4) + {0, 1} of row t / 4 of each matrix) to shared memory; lanes 8 i .. 8 i + 7 give the row
+// addresses of matrix i.
+__device__ __forceinline__ void stmatrix_x4(uint32_t addr, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
+    asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1, %2, %3, %4};"
+                 ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+}
+
 // 16 TMEM lanes x 16 columns, same thread mapping as the .x8 load of the common header:
 // r[4u + 0,1] = (lane t/4, columns 8u + 2(t%4) + 0,1), r[4u + 2,3] = the same columns of lane t/4 + 8.
 __device__ __forceinline__ void tc_ld_16x256b_x2(uint32_t taddr, uint32_t (&r)[8]) {
@@ -215,10 +268,14 @@ struct Cursor {
         first = a;
         count = b - a;
     }
+    // The walker is number `first_item` of `walkers` (the CTA and the grid, or a pipeline of a CTA and the
+    // number of pipelines in the grid); p.stride_z / p.stride_rem are `walkers` split by the items per batch entry.
     template <class Params>
-    __device__ __forceinline__ void init(const Params& p, int shift = 0) {
+    __device__ __forceinline__ void init(const Params& p, int shift = 0) { init_as(p, (int)blockIdx.x, (int)gridDim.x, shift); }
+    template <class Params>
+    __device__ __forceinline__ void init_as(const Params& p, int first_item, int walkers, int shift = 0) {
         table_shift = shift;
-        item = (int)blockIdx.x; stride = (int)gridDim.x; items = p.items;
+        item = first_item; stride = walkers; items = p.items;
         chunks = p.chunks; per_z = p.groups * p.chunks; table = p.table;
         stride_z = p.stride_z; stride_rem = p.stride_rem;
         item_no = 0;

@@ -767,31 +767,54 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 // Head dim 64: two independent pipelines per CTA.
 //
 // A pipeline is a producer warp, an issuer warp and a softmax warpgroup with their own shared-memory
-// tiles (Q, two K stages, two V stages, P), their own S buffer and O accumulator in tensor memory
-// and their own barriers; it walks its own block rows (pipeline number = 2 * CTA + g of 2 * grid
-// pipelines).  Nothing is shared between the two pipelines of a CTA but the TMEM allocation, and
-// two CTAs share an SM: four block rows are in flight per SM, each at its own point of its row, so
-// the end of one row (normalising and writing O) overlaps the others' tiles.  (An earlier version
-// let two softmax groups share a row, with alternate tiles: every hand-over between the groups,
-// the in-order producers and issuers and the merge of the two partial results at the end of a row
-// serialised the CTA; with every MMA, exponential and copy removed it still took 60 % of its time.)
-//   warps 0, 2   producer of pipeline 0, 1: Q of the row, then K(0), K(1), V(0), K(2), V(1), ...
-//   warps 1, 3   issuer: polls "S buffer free + K landed" and "P written + V landed" and issues
-//                whichever product is ready (Q K^T of tile t + 1 while the softmax warps work on
-//                tile t, P V of tile t as soon as its P is complete)
-//   warps 4-7, 8-11   softmax warpgroup: tcgen05.ld of S, masks, lazily raised running maximum,
-//                P = exp2(..) packed and written with stmatrix into the swizzled operand tile,
-//                row sums; at the end of the row O / l and the log-sum-exp go to global memory.
-constexpr int kPipeTiles = 6;                   // Q, K x 2, V x 2, P
+// tiles (Q, three K stages, two V stages), their own S and P buffers and O accumulator in tensor
+// memory and their own barriers; it walks its own block rows (pipeline number = 2 * CTA + g of
+// 2 * grid pipelines).  Nothing is shared between the two pipelines of a CTA but the TMEM
+// allocation, and two CTAs share an SM: four block rows are in flight per SM, each at its own
+// point of its row, so the end of one row (normalising and writing O) overlaps the others' tiles.
+// (An earlier version let two softmax groups share a row, with alternate tiles: the hand-overs
+// between the groups, the in-order producers and issuers and the merge of the two partial results
+// at the end of a row serialised the CTA; with every MMA, exponential and copy removed it still
+// took 60 % of its time.)
+//
+// Tensor memory.  An M = 64 accumulator occupies lanes 0-15 of each 32-lane quarter; a second one
+// fits into lanes 16-31 of the same columns (lane offset 16 in the MMA's D address and in the
+// 16-lane tcgen05.ld / st shapes).  The 128 columns of a pipeline hold
+//   columns   0 ..  63   lanes 0-15: O            lanes 16-31: S buffer 0
+//   columns  64 .. 127   lanes 0-15: P buffers 0, 1 (32 columns each, 16-bit)   lanes 16-31: S buffer 1
+// so S is double buffered (Q K^T runs two tiles ahead of the softmax warps) and P never touches
+// shared memory: the softmax warps write it with one tcgen05.st per tile and P V takes its A
+// operand from tensor memory.  (A TMEM A operand is only used at lane offset 0 together with a D
+// at lane offset 0; a D at offset 16 with a TMEM A raised "misaligned address" in a probe.)
+//
+// A hand-over through an mbarrier costs about 200 cycles (arrive -> the waiter runs again), a test
+// of a barrier that is already complete 100-250, a tcgen05.ld about 300; a tile's arithmetic takes
+// 800.  So per tile the softmax warps test the barriers they are going to need ahead of time
+// (non-blocking test, result consumed later), and request the next tile's S from tensor memory
+// before they write this tile's P.
+//   warps 0, 2   producer of pipeline 0, 1: Q of the row, then K(u), V(u - 3), ...
+//   warps 1, 3   issuer: Q K^T of tile u (S buffer u & 1), then P V of tile u - 2
+//   warps 4-7, 8-11   softmax warpgroup: S -> registers, masks, lazily raised running maximum,
+//                P = exp2(..) packed into tensor memory, row sums; at the end of the row O / l and
+//                the log-sum-exp go to global memory.
+constexpr int kPipeTiles = 6;                   // Q, K x 3, V x 2
+constexpr int kPipeKRing = 3;
 struct __align__(8) PipeBarriers {
     uint64_t q_full[2], q_empty[2];             // [pipeline]
-    uint64_t k_full[2][2], qk_done[2][2];       // [pipeline][stage]
-    uint64_t v_full[2][2], pv_done[2][2];
-    uint64_t s_empty[2], p_full[2];
+    uint64_t k_full[2][kPipeKRing], qk_done[2][kPipeKRing];   // [pipeline][K stage]: qk_done = S is ready and the K stage is free
+    uint64_t v_full[2][2], pv_done[2][2];       // [pipeline][tile & 1]: pv_done = the P buffer and the V stage are free
+    uint64_t s_empty[2][2], p_full[2][2];       // [pipeline][tile & 1]
     uint64_t o_full[2], o_empty[2];
     uint64_t drain;
     uint32_t tmem_base;
     int abort_flag;
+};
+
+// Position of a tile in the ring of three K stages (every role counts the tiles it has handled).
+struct KRing {
+    int stage = 0;
+    uint32_t use = 0;                           // parity of the number of times the ring has wrapped
+    __device__ __forceinline__ void next() { if (++stage == kPipeKRing) { stage = 0; use ^= 1u; } }
 };
 
 template <bool BF16, bool MASKED>
@@ -806,17 +829,16 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
     const int g = warp < 4 ? warp >> 1 : (warp - 4) >> 2;          // pipeline of this warp
     uint8_t* q_smem = smem + g * kPipeTiles * kTileBytes;
     uint8_t* k_smem = q_smem + kTileBytes;
-    uint8_t* v_smem = k_smem + 2 * kTileBytes;
-    uint8_t* p_smem = v_smem + 2 * kTileBytes;
+    uint8_t* v_smem = k_smem + kPipeKRing * kTileBytes;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bars->q_full[i], 1); mbar_init(&bars->q_empty[i], 1);
+            for (int s = 0; s < kPipeKRing; ++s) { mbar_init(&bars->k_full[i][s], 1); mbar_init(&bars->qk_done[i][s], 1); }
             for (int s = 0; s < 2; ++s) {
-                mbar_init(&bars->k_full[i][s], 1); mbar_init(&bars->qk_done[i][s], 1);
                 mbar_init(&bars->v_full[i][s], 1); mbar_init(&bars->pv_done[i][s], 1);
+                mbar_init(&bars->s_empty[i][s], 4); mbar_init(&bars->p_full[i][s], 4);
             }
-            mbar_init(&bars->s_empty[i], 4); mbar_init(&bars->p_full[i], 4);
             mbar_init(&bars->o_full[i], 1); mbar_init(&bars->o_empty[i], 4);
         }
         mbar_init(&bars->drain, 2);
@@ -833,29 +855,29 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *(volatile uint32_t*)&bars->tmem_base;
-    const uint32_t o_tmem = tmem_base + (uint32_t)(g * kTile);              // O accumulator of the pipeline
-    const uint32_t s_tmem = tmem_base + (uint32_t)(kSCol0 + g * kTile);     // its S buffer
+    const uint32_t o_tmem = tmem_base + (uint32_t)(g * 128);               // O: lanes 0-15 of columns 0 .. 63
+    const uint32_t s_tmem = o_tmem + (16u << 16);                          // S buffer b: lanes 16-31 of columns 64 b ..
+    const uint32_t p_tmem = o_tmem + 64u;                                  // P buffer b: lanes 0-15 of columns 64 + 32 b ..
     const int walker = 2 * (int)blockIdx.x + g, walkers = 2 * (int)gridDim.x;
 
     if (warp == 0 || warp == 2) {
         // ------------------------------------------------------------ producer
+        // Order K(u), V(u - 3): the order in which their stages become free (Q K^T runs two tiles ahead of
+        // the softmax warps, P V one tile behind them).  The tiles are numbered through the rows, so the
+        // copies run ahead across row borders.
         int t0 = 0, i_no = 0;                       // tiles and non-empty rows before the current row
+        KRing kr;                                   // stage of the next K tile
+        int vq_col[3] = {0, 0, 0}, vq_z[3] = {0, 0, 0};        // key block and batch entry of tiles u - 3, u - 2, u - 1
         bool ok = true;
         Cursor cur;
         cur.init_as(p, walker, walkers);
         BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
-        // K / V of tile t go to stage t & 1 once the product that read the stage last has retired
-        auto load_kv = [&](bool is_v, int t, int col, int z) -> bool {
+        auto load_v = [&](int t, int col, int z) -> bool {
             const int st = t & 1;
-            const uint32_t parity = ((uint32_t)(t >> 1) & 1u) ^ 1u;
-            uint64_t* reuse = is_v ? &bars->pv_done[g][st] : &bars->qk_done[g][st];
-            uint64_t* full = is_v ? &bars->v_full[g][st] : &bars->k_full[g][st];
-            uint8_t* dst = (is_v ? v_smem : k_smem) + st * kTileBytes;
-            const CUtensorMap* map = is_v ? &map_v : &map_k;
-            if (!__all_sync(0xffffffffu, mbar_wait(reuse, parity, abort_flag, p.status))) return false;
+            if (!__all_sync(0xffffffffu, mbar_wait(&bars->pv_done[g][st], ((uint32_t)(t >> 1) & 1u) ^ 1u, abort_flag, p.status))) return false;
             if (elect_one()) {
-                mbar_expect_tx(full, (uint32_t)kTileBytes);
-                tma_load_3d(dst, map, full, 0, col * kTile, z);
+                mbar_expect_tx(&bars->v_full[g][st], (uint32_t)kTileBytes);
+                tma_load_3d(v_smem + st * kTileBytes, &map_v, &bars->v_full[g][st], 0, col * kTile, z);
             }
             __syncwarp();
             return true;
@@ -874,67 +896,82 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
                 __syncwarp();
                 DescWindow win;
                 win.begin(p.blocks, cur.first, cur.count, pre, lane);
-                int col_prev = 0;
                 for (int j = 0; ok && j < n; ++j) {
                     const int col = win.get(p.blocks, cur.first, cur.count, j, lane).col();
-                    ok = load_kv(false, t0 + j, col, cur.z);
-                    if (ok && j > 0) ok = load_kv(true, t0 + j - 1, col_prev, cur.z);
-                    col_prev = col;
+                    const int u = t0 + j;
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->qk_done[g][kr.stage], kr.use ^ 1u, abort_flag, p.status)) != 0;
+                    if (ok && elect_one()) {
+                        mbar_expect_tx(&bars->k_full[g][kr.stage], (uint32_t)kTileBytes);
+                        tma_load_3d(k_smem + kr.stage * kTileBytes, &map_k, &bars->k_full[g][kr.stage], 0, col * kTile, cur.z);
+                    }
+                    __syncwarp();
+                    kr.next();
+                    if (ok && u >= 3) ok = load_v(u - 3, vq_col[0], vq_z[0]);
+                    vq_col[0] = vq_col[1]; vq_z[0] = vq_z[1];
+                    vq_col[1] = vq_col[2]; vq_z[1] = vq_z[2];
+                    vq_col[2] = col; vq_z[2] = cur.z;
                 }
-                if (ok) ok = load_kv(true, t0 + n - 1, col_prev, cur.z);
                 t0 += n;
                 ++i_no;
             }
             pre = pre_next;
             cur.advance();
         }
+        // the V tiles of the last three blocks
+        for (int r = 0; ok && r < 3; ++r) {
+            const int u = t0 - 3 + r;
+            if (u >= 0) ok = load_v(u, vq_col[r], vq_z[r]);
+        }
         if (lane == 0 && *(volatile int*)abort_flag) {
             // Give copies that were issued a bounded chance to land before the CTA exits.
             const unsigned long long tw = global_ns();
-            for (int s = 0; s < 2; ++s) {
+            for (int s = 0; s < kPipeKRing; ++s)
                 while (!mbar_try_wait(&bars->k_full[g][s], 0) && !mbar_try_wait(&bars->k_full[g][s], 1) &&
                        global_ns() - tw < kWaitLimitNs / 4) {}
+            for (int s = 0; s < 2; ++s)
                 while (!mbar_try_wait(&bars->v_full[g][s], 0) && !mbar_try_wait(&bars->v_full[g][s], 1) &&
                        global_ns() - tw < kWaitLimitNs / 4) {}
-            }
             while (!mbar_try_wait(&bars->q_full[g], 0) && !mbar_try_wait(&bars->q_full[g], 1) &&
                    global_ns() - tw < kWaitLimitNs / 4) {}
         }
         __syncwarp();
     } else if (warp == 1 || warp == 3) {
         // ------------------------------------------------------------ issuer
-        // Order: Q K^T of tile t + 1, then P V of tile t (kept pending across rows).  The events it waits
-        // for come in this order: S(t) is in the softmax warps' registers when they start on tile t, their
-        // P(t) is complete when they are done with it.  So S(t + 1) is computed while they work on tile
-        // t, and P V of tile t is issued the moment its P is complete.
+        // Order: Q K^T of tile u, then P V of tile u - 2 (two tiles pending, also across rows).  The events
+        // it waits for come in this order: S(u - 2) is in the softmax warps' registers when they start on
+        // tile u - 2 (S buffer u & 1 is free), their P(u - 2) is complete when they are done with it.
         const uint32_t idesc_qk = p.idesc_qk, idesc_pv = p.idesc_pv;
         const uint64_t q_desc = make_tile_desc(smem_u32(q_smem), false);
         const uint64_t k_desc = make_tile_desc(smem_u32(k_smem), false);
-        const uint64_t p_desc = make_tile_desc(smem_u32(p_smem), false);
         const uint64_t v_desc = make_tile_desc(smem_u32(v_smem), true);
         int t0 = 0, i_no = 0;                       // tiles and non-empty rows before the current row
+        KRing kr;
         bool ok = true;
-        bool pend = false, pend_first = false, pend_last = false;
-        int pend_t = 0, pend_i = 0;                 // the pending P V: tile number, row number
-        auto issue_pv = [&]() -> bool {             // O (+)= P V of the pending tile
-            const int t = pend_t, st = t & 1;
+        int npend = 0;
+        int pend_t[2] = {0, 0}, pend_i[2] = {0, 0};             // pending P V: tile number, row number,
+        bool pend_first[2] = {false, false}, pend_last[2] = {false, false};       // first / last tile of its row
+        auto issue_pv = [&]() -> bool {             // O (+)= P V of the older pending tile
+            const int t = pend_t[0], b = t & 1;
             // the accumulator is free once the row before has been read out
-            if (pend_first && pend_i > 0 &&
-                !__all_sync(0xffffffffu, mbar_wait(&bars->o_empty[g], (uint32_t)(pend_i - 1) & 1u, abort_flag, p.status)))
+            if (pend_first[0] && pend_i[0] > 0 &&
+                !__all_sync(0xffffffffu, mbar_wait(&bars->o_empty[g], (uint32_t)(pend_i[0] - 1) & 1u, abort_flag, p.status)))
                 return false;
-            if (!__all_sync(0xffffffffu, mbar_wait(&bars->v_full[g][st], (uint32_t)(t >> 1) & 1u, abort_flag, p.status))) return false;
-            if (!__all_sync(0xffffffffu, mbar_wait(&bars->p_full[g], (uint32_t)t & 1u, abort_flag, p.status))) return false;
+            if (!__all_sync(0xffffffffu, mbar_wait(&bars->v_full[g][b], (uint32_t)(t >> 1) & 1u, abort_flag, p.status))) return false;
+            if (!__all_sync(0xffffffffu, mbar_wait(&bars->p_full[g][b], (uint32_t)(t >> 1) & 1u, abort_flag, p.status))) return false;
             tc_fence_after();
-            const uint64_t db = v_desc + (uint64_t)((st * kTileBytes) >> 4);
+            const uint64_t db = v_desc + (uint64_t)((b * kTileBytes) >> 4);
+            const uint32_t a = p_tmem + (uint32_t)(32 * b);
             if (elect_one()) {
 #pragma unroll
                 for (int kk = 0; kk < kTile / 16; ++kk)
-                    tc_mma_f16(o_tmem, p_desc + (uint64_t)(kk * 2), db + (uint64_t)(kk * (2048 >> 4)), idesc_pv,
-                               (!pend_first || kk > 0) ? 1u : 0u);
-                tc_commit(&bars->pv_done[g][st]);       // the P buffer and the V stage are free
-                if (pend_last) tc_commit(&bars->o_full[g]);
+                    tc_mma_f16_ts(o_tmem, a + (uint32_t)(8 * kk), db + (uint64_t)(kk * (2048 >> 4)), idesc_pv,
+                                  (!pend_first[0] || kk > 0) ? 1u : 0u);
+                tc_commit(&bars->pv_done[g][b]);        // the P buffer and the V stage are free
+                if (pend_last[0]) tc_commit(&bars->o_full[g]);
             }
             __syncwarp();
+            pend_t[0] = pend_t[1]; pend_i[0] = pend_i[1]; pend_first[0] = pend_first[1]; pend_last[0] = pend_last[1];
+            --npend;
             return true;
         };
         Cursor cur;
@@ -944,27 +981,30 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
             if (n == 0) continue;                   // a row without blocks: the softmax warps write zeros on their own
             ok = __all_sync(0xffffffffu, mbar_wait(&bars->q_full[g], (uint32_t)i_no & 1u, abort_flag, p.status)) != 0;
             for (int j = 0; ok && j < n; ++j) {
-                const int t = t0 + j, st = t & 1;
-                ok = __all_sync(0xffffffffu, mbar_wait(&bars->k_full[g][st], (uint32_t)(t >> 1) & 1u, abort_flag, p.status)) != 0;
-                if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_empty[g], ((uint32_t)t & 1u) ^ 1u, abort_flag, p.status)) != 0;
+                const int t = t0 + j, b = t & 1;
+                ok = __all_sync(0xffffffffu, mbar_wait(&bars->k_full[g][kr.stage], kr.use, abort_flag, p.status)) != 0;
+                if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_empty[g][b], ((uint32_t)(t >> 1) & 1u) ^ 1u, abort_flag, p.status)) != 0;
                 if (!ok) break;
                 tc_fence_after();
-                const uint64_t db = k_desc + (uint64_t)((st * kTileBytes) >> 4);
+                const uint64_t db = k_desc + (uint64_t)((kr.stage * kTileBytes) >> 4);
+                const uint32_t d = s_tmem + (uint32_t)(64 * b);
                 if (elect_one()) {
 #pragma unroll
                     for (int kk = 0; kk < kTile / 16; ++kk)
-                        tc_mma_f16(s_tmem, q_desc + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc_qk, kk > 0 ? 1u : 0u);
-                    tc_commit(&bars->qk_done[g][st]);       // S is ready and the K stage is free
+                        tc_mma_f16(d, q_desc + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc_qk, kk > 0 ? 1u : 0u);
+                    tc_commit(&bars->qk_done[g][kr.stage]);     // S is ready and the K stage is free
                     if (j == n - 1) tc_commit(&bars->q_empty[g]);
                 }
                 __syncwarp();
-                if (pend) ok = issue_pv();
-                pend = true; pend_t = t; pend_i = i_no; pend_first = j == 0; pend_last = j == n - 1;
+                kr.next();
+                if (npend == 2) ok = issue_pv();
+                pend_t[npend] = t; pend_i[npend] = i_no; pend_first[npend] = j == 0; pend_last[npend] = j == n - 1;
+                ++npend;
             }
             t0 += n;
             ++i_no;
         }
-        if (ok && pend) issue_pv();
+        while (ok && npend > 0) ok = issue_pv();
         // All MMAs issued by the elected lane (the same one every time: the election is deterministic
         // for a converged warp) must have retired before TMEM is freed.
         if (elect_one()) {
@@ -979,17 +1019,11 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
         const int row_a = quad * 16 + (lane >> 2);  // this lane's two rows of the 64-row block
         const uint32_t lane_field = (uint32_t)(quad * 32) << 16;
         const bool masked_op = MASKED && (p.causal != 0 || p.kpm != nullptr || p.quadrants != 0);
-        // P leaves through stmatrix: the 16x256b TMEM load hands out the m8n8 fragment layout, so the packed words
-        // of column units 2k, 2k + 1 of the lane's two rows are the four matrices of one instruction.  Lane -> row
-        // address of its matrix: matrix i = lane / 8 holds rows (i & 1) * 8 .. of unit 2k + (i >> 1); the address
-        // row * 128 + (((2k + (i >> 1)) ^ (row & 7)) << 4) is p_off ^ (k << 5) (bits 5-6 carry 2k ^ (row & 6),
-        // bit 4 the unit's parity; the tile is 1024-byte aligned).
-        const int sm_row = quad * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
-        const uint32_t p_tile = smem_u32(p_smem) + (uint32_t)(sm_row * 128) + ((((uint32_t)(lane >> 4)) ^ (uint32_t)(sm_row & 7)) << 4);
         const float c2 = p.scale_log2, c2abs = fabsf(c2);
         const bool flip = c2 < 0.f;
         const uint64_t c2p = f2_pack(c2, c2);
         int t0 = 0, i_no = 0;                       // tiles and non-empty rows before the current row
+        KRing kr;                                   // K stage (= qk_done barrier) of the next tile to be requested from TMEM
         bool ok = true;
         Cursor cur;
         cur.init_as(p, walker, walkers);
@@ -1042,29 +1076,43 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
                     return m;
                 };
                 // One pass over the row's blocks with a running row maximum m (in units of log2:
-                // t = scale * log2(e) * s).  P_j = exp2(t_j - m) goes to shared memory as a K-major operand
-                // tile, O += P_j V_j accumulates in TMEM, l sums the P's.  m is only raised when a block's
-                // maximum exceeds it by more than kSlack (P stays <= 2^kSlack, exact in fp32 sums and well
-                // inside the 16-bit range); raising it rescales O in TMEM and l by exp2(m_old - m_new),
-                // which needs the previous P V to have retired.
+                // t = scale * log2(e) * s).  P_j = exp2(t_j - m) goes to tensor memory as the A operand of
+                // O += P_j V_j, l sums the P's.  m is only raised when a block's maximum exceeds it by more
+                // than kSlack (P stays <= 2^kSlack, exact in fp32 sums and well inside the 16-bit range);
+                // raising it rescales O in TMEM and l by exp2(m_old - m_new), which needs the previous
+                // P V to have retired.
                 constexpr float kSlack = 8.f;
                 float m_a = -INFINITY, m_b = -INFINITY;
                 // row sums: per row two independent two-wide accumulators (even / odd column units)
                 uint64_t la2[2] = {0ull, 0ull}, lb2[2] = {0ull, 0ull};
                 DescWindow win;
                 win.begin(p.blocks, cur.first, cur.count, pre, lane);
+                uint32_t r[32];
+                // wait for S of tile t (K stage / barrier position kr), unless an earlier test has seen it
+                // complete, and start loading it
+                auto request_s = [&](int t, bool seen) -> bool {
+                    if (!__all_sync(0xffffffffu, seen) &&
+                        !__all_sync(0xffffffffu, mbar_wait(&bars->qk_done[g][kr.stage], kr.use, abort_flag, p.status))) return false;
+                    kr.next();
+                    tc_fence_after();
+                    tc_ld_16x256b_x8(s_tmem + lane_field + (uint32_t)(64 * (t & 1)), r);
+                    return true;
+                };
+                bool s_seen = false;                // an earlier test has seen S of the next tile complete
                 for (int j = 0; ok && j < n; ++j) {
-                    const int t = t0 + j, st = t & 1;
-                    // (the mask of a block is computed before the wait for its S tile: off the critical chain)
+                    const int t = t0 + j, b = t & 1;
+                    ok = request_s(t, s_seen);
+                    if (!ok) break;
+                    // (the mask of a block is computed while its S tile is on the way)
                     uint32_t mask = 0u;
                     if (MASKED && masked_op) mask = block_mask(win.get(p.blocks, cur.first, cur.count, j, lane));
-                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->qk_done[g][st], (uint32_t)(t >> 1) & 1u, abort_flag, p.status)) != 0;
-                    if (!ok) break;
-                    tc_fence_after();
-                    uint32_t r[32];
-                    tc_ld_16x256b_x8(s_tmem + lane_field, r);
                     tc_wait_ld();
-                    release_accumulator(&bars->s_empty[g], lane);      // S is in registers: Q K^T of the next tile may run
+                    release_accumulator(&bars->s_empty[g][b], lane);       // S is in registers: its buffer may be overwritten
+                    // Is the P buffer free (P V of tile t - 2 retired), is S of the next tile ready (Q K^T runs two
+                    // tiles ahead)?  Tested now, needed after the arithmetic: a test of a barrier costs a few hundred
+                    // cycles of latency even when the phase completed long ago.
+                    const bool p_free = t < 2 || mbar_test(&bars->pv_done[g][b], ((uint32_t)(t >> 1) & 1u) ^ 1u);
+                    s_seen = j + 1 < n && mbar_test(&bars->qk_done[g][kr.stage], kr.use);
                     // Masked elements (above the diagonal, padded keys, quadrants outside a block-32 layout) are
                     // overwritten by -inf (+inf for a negative scale): they lose every maximum and their exp2 is
                     // exactly 0 (the host keeps the scale factor away from 0, so inf * scale is never NaN).
@@ -1140,33 +1188,33 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
                     }
                     const float sub_a = m_a == -INFINITY ? 0.f : m_a, sub_b = m_b == -INFINITY ? 0.f : m_b;
                     // P = exp2(c2 * s - m): per pair of columns one two-wide FMA, two exp2, one two-wide add into
-                    // the row sum and one pack.  w[4k + i]: matrix (unit 2k, row a), (2k, b), (2k + 1, a), (2k + 1, b).
+                    // the row sum and one pack.  w[2u + h]: columns 8u + 2 q4 + {0, 1} of row a (h = 0) / row b (h = 1):
+                    // the register order of the 16x128b store.
                     const uint64_t na = f2_pack(-sub_a, -sub_a), nb = f2_pack(-sub_b, -sub_b);
                     uint32_t w[16];
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
+                    for (int u = 0; u < 8; ++u) {
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int u = 2 * k + (i >> 1), h = i & 1;
+                        for (int h = 0; h < 2; ++h) {
                             const uint64_t t2 = f2_fma(f2_pack(__uint_as_float(r[4 * u + 2 * h]), __uint_as_float(r[4 * u + 2 * h + 1])),
                                                        c2p, h ? nb : na);
                             float e0, e1;
                             f2_unpack(t2, e0, e1);
                             e0 = attn_exp2(e0); e1 = attn_exp2(e1);
-                            if (h) lb2[i >> 1] = f2_add(lb2[i >> 1], f2_pack(e0, e1));
-                            else   la2[i >> 1] = f2_add(la2[i >> 1], f2_pack(e0, e1));
-                            w[4 * k + i] = pack2<BF16>(e0, e1);
+                            if (h) lb2[u & 1] = f2_add(lb2[u & 1], f2_pack(e0, e1));
+                            else   la2[u & 1] = f2_add(la2[u & 1], f2_pack(e0, e1));
+                            w[2 * u + h] = pack2<BF16>(e0, e1);
                         }
                     }
-                    // the P buffer must have been read by the MMAs that used it last (those of the tile before);
-                    // the wait comes after the arithmetic so that it rarely has anything left to wait for
-                    if (t > 0 && !__all_sync(0xffffffffu, mbar_wait(&bars->pv_done[g][(t - 1) & 1], (uint32_t)((t - 1) >> 1) & 1u, abort_flag, p.status))) { ok = false; break; }
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        stmatrix_x4(p_tile ^ (uint32_t)(k << 5), w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
-                    fence_async_shared();           // generic-proxy writes -> visible to the tensor core's reads
+                    // the P buffer must have been read by the MMAs that used it last (those of tile t - 2)
+                    if (!__all_sync(0xffffffffu, p_free) &&
+                        !__all_sync(0xffffffffu, mbar_wait(&bars->pv_done[g][b], ((uint32_t)(t >> 1) & 1u) ^ 1u, abort_flag, p.status))) { ok = false; break; }
+                    tc_fence_after();
+                    tc_st_16x128b_x8(p_tmem + lane_field + (uint32_t)(32 * b), w);
+                    tc_wait_st();
+                    tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&bars->p_full[g]);
+                    if (lane == 0) mbar_arrive(&bars->p_full[g][b]);
                 }
                 t0 += n;
                 if (!ok) break;
@@ -1194,7 +1242,7 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
                     uint32_t ta[4], tb[4];
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
-                        // a row without an unmasked score: its accumulator holds 0 * garbage-free sums, write 0
+                        // a row without an unmasked score gets zeros whatever its accumulator holds
                         ta[u] = pack2<BF16>(inv_a > 0.f ? __uint_as_float(acc[hc][4 * u]) * inv_a : 0.f,
                                             inv_a > 0.f ? __uint_as_float(acc[hc][4 * u + 1]) * inv_a : 0.f);
                         tb[u] = pack2<BF16>(inv_b > 0.f ? __uint_as_float(acc[hc][4 * u + 2]) * inv_b : 0.f,

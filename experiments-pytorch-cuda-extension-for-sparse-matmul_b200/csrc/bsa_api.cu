@@ -152,16 +152,22 @@ extern "C" int bsa_sparse_to_dense(int dtype, const void* sparse, void* dense,
                         static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int bsa_workspace_status(void* workspace, void* stream) {
+extern "C" int bsa_workspace_status_detail(void* workspace, void* stream, int32_t* detail) {
+    if (detail) *detail = 0;
     if (!workspace) return BSA_ERR_NULL_POINTER;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    uint32_t word = 0;
-    if (cudaMemcpyAsync(&word, workspace, sizeof(word), cudaMemcpyDeviceToHost, s) != cudaSuccess) return BSA_ERR_LAUNCH;
+    uint32_t words[2] = {0, 0};             // status code, detail (the offending block rank of a BAD_SHAPE report)
+    if (cudaMemcpyAsync(words, workspace, sizeof(words), cudaMemcpyDeviceToHost, s) != cudaSuccess) return BSA_ERR_LAUNCH;
     if (cudaStreamSynchronize(s) != cudaSuccess) return BSA_ERR_LAUNCH;
-    if (word == 0) return BSA_OK;
-    if (cudaMemsetAsync(workspace, 0, 2 * sizeof(word), s) != cudaSuccess) return BSA_ERR_LAUNCH;
+    if (words[0] == 0) return BSA_OK;
+    if (detail) *detail = (int32_t)words[1];
+    if (cudaMemsetAsync(workspace, 0, sizeof(words), s) != cudaSuccess) return BSA_ERR_LAUNCH;
     if (cudaStreamSynchronize(s) != cudaSuccess) return BSA_ERR_LAUNCH;
-    return word == (uint32_t)BSA_ERR_BAD_SHAPE ? BSA_ERR_BAD_SHAPE : BSA_ERR_DEVICE_TIMEOUT;
+    return words[0] == (uint32_t)BSA_ERR_BAD_SHAPE ? BSA_ERR_BAD_SHAPE : BSA_ERR_DEVICE_TIMEOUT;
+}
+
+extern "C" int bsa_workspace_status(void* workspace, void* stream) {
+    return bsa_workspace_status_detail(workspace, stream, nullptr);
 }
 
 // ---------------------------------------------------------------------------
@@ -179,6 +185,30 @@ constexpr int kMaxDevices = 64;
 static __device__ __align__(256) unsigned char g_static_workspace[kStaticWorkspaceBytes];
 }  // namespace
 
+namespace {
+// Device address of the static array on the CURRENT device (looked up once per device, no allocation).
+// In host code `g_static_workspace` is only a handle of the symbol, not an address the GPU can use, and
+// the address differs per device.
+int static_workspace(void** out) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return BSA_ERR_LAUNCH; }
+    if (dev < 0 || dev >= kMaxDevices) return BSA_ERR_TOO_LARGE;
+    static std::mutex mutex;
+    static void* device_ptr[kMaxDevices] = {};
+    std::lock_guard<std::mutex> lock(mutex);
+    if (device_ptr[dev] == nullptr) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_static_workspace) != cudaSuccess || ptr == nullptr) {
+            cudaGetLastError();
+            return BSA_ERR_LAUNCH;
+        }
+        device_ptr[dev] = ptr;
+    }
+    *out = device_ptr[dev];
+    return BSA_OK;
+}
+}  // namespace
+
 extern "C" int bsa_matmul_noalloc(int mode, int dtype, int trans_a, int trans_b,
                                   const void* a, const void* b, void* c,
                                   const int32_t* blocks, const int32_t* table,
@@ -190,32 +220,21 @@ extern "C" int bsa_matmul_noalloc(int mode, int dtype, int trans_a, int trans_b,
     const int checked = check_matmul_args(mode, dtype, a, b, c, blocks, table, nnz, groups, batches,
                                           size_m, size_n, size_k, block, engine);
     if (checked != BSA_OK) return checked;      // refused before the device is touched
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return BSA_ERR_LAUNCH; }
-    if (dev < 0 || dev >= kMaxDevices) return BSA_ERR_TOO_LARGE;
-    // In host code `g_static_workspace` is only a handle of the symbol, not an address the GPU
-    // can use.  The device address differs per device, so it is looked up once per device, with
-    // that device current (first call on the device; no allocation happens here).
-    static std::mutex mutex;
-    static void* device_ptr[kMaxDevices] = {};
     void* ws = nullptr;
-    {
-        std::lock_guard<std::mutex> lock(mutex);
-        if (device_ptr[dev] == nullptr) {
-            void* ptr = nullptr;
-            if (cudaGetSymbolAddress(&ptr, g_static_workspace) != cudaSuccess || ptr == nullptr) {
-                cudaGetLastError();
-                return BSA_ERR_LAUNCH;
-            }
-            device_ptr[dev] = ptr;
-        }
-        ws = device_ptr[dev];
-    }
+    const int found = static_workspace(&ws);
+    if (found != BSA_OK) return found;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // The array keeps whatever the previous call left in it; the status words must start at zero.
     if (cudaMemsetAsync(ws, 0, kStaticWorkspaceBytes, s) != cudaSuccess) { cudaGetLastError(); return BSA_ERR_LAUNCH; }
     const int st = bsa_matmul(mode, dtype, trans_a, trans_b, a, b, c, blocks, table, nnz, groups, batches,
                               size_m, size_n, size_k, block, ws, kStaticWorkspaceBytes, engine, stream);
     if (st != BSA_OK || !wait_and_check) return st;
+    return bsa_workspace_status(ws, stream);
+}
+
+extern "C" int bsa_matmul_noalloc_status(void* stream) {
+    void* ws = nullptr;
+    const int found = static_workspace(&ws);
+    if (found != BSA_OK) return found;
     return bsa_workspace_status(ws, stream);
 }

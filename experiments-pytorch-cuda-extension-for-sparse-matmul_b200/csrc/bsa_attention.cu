@@ -1307,16 +1307,7 @@ int attention_forward(int dtype, const void* q, const void* k, const void* v, vo
     int smem_bytes = pipes ? 1024 + 2 * kPipeTiles * kTileBytes + (int)sizeof(PipeBarriers)
                            : 1024 + ((p.qbufs + p.ring + p.vring) * p.dtiles + 2) * kTileBytes + (int)sizeof(AttnBarriers);
     if (smem_bytes < 80 * 1024) smem_bytes = 80 * 1024;
-    // Set on every call (a per-device attribute); this and the cudaSetDevice below also bind the
-    // device's primary context to the calling thread, which the driver call behind make_map needs.
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) {
-        cudaGetLastError();
-        return BSA_ERR_LAUNCH;
-    }
-    {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) { cudaGetLastError(); return BSA_ERR_LAUNCH; }
-    }
+    if (!ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem_bytes)) return BSA_ERR_LAUNCH;
     const int64_t seq_q = block_rows * kTile, seq_k = block_cols * kTile;
     CUtensorMap map_q, map_k, map_v;
     bool ok = make_map(&map_q, dtype, q, batches, seq_q, head_dim);

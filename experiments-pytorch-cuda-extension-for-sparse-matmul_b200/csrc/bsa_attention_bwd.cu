@@ -600,10 +600,7 @@ int launch_backward(int dtype, bool masked, const CUtensorMap& x1, const CUtenso
                      (COL ? p.ring * kBwdStatBytes : 0) + (int)sizeof(BwdBarriers);
     // more than half of an SM's shared memory: the CTA allocates all 512 TMEM columns and must be alone
     if (smem_bytes < 116 * 1024) smem_bytes = 116 * 1024;
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) {
-        cudaGetLastError();
-        return BSA_ERR_LAUNCH;
-    }
+    if (!ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem_bytes)) return BSA_ERR_LAUNCH;
     const int sms = sm_count();
     if (sms <= 0) return BSA_ERR_LAUNCH;
     const unsigned grid = (unsigned)(p.items < sms ? p.items : sms);
@@ -623,10 +620,6 @@ int attention_backward(int dtype, const void* q, const void* k, const void* v, c
                        int64_t nnz, int64_t block_rows, int64_t block_cols, int64_t batches, int64_t head_dim,
                        float scale, int causal, const uint8_t* kpm, int64_t kpm_batches, int64_t kpm_stride,
                        int quadrants, float2* stats, uint32_t* workspace, cudaStream_t stream) {
-    {
-        int dev = 0;   // binds the device's primary context to this thread (the driver call behind make_map needs it)
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) { cudaGetLastError(); return BSA_ERR_LAUNCH; }
-    }
     const int64_t seq_q = block_rows * kTile, seq_k = block_cols * kTile;
     const long long rows = (long long)batches * seq_q;
     {

@@ -85,7 +85,12 @@ __global__ void __launch_bounds__(kThreads) sdd_kernel(const Params p) {
     const int64_t z = blockIdx.y;
     const BlockDesc d = p.blocks[bi];
     const int64_t m0 = (int64_t)d.row() * B + si * kTile, n0 = (int64_t)d.col() * B + sj * kTile;
-    const int lim_i = min(kTile, B - si * kTile), lim_j = min(kTile, B - sj * kTile);
+    // A descriptor is trusted neither for its position (a block beyond the dense operands reads as zero: the
+    // limits below go to <= 0, as the TMA boxes of the tensor-core engine clip) nor for its rank (no write
+    // outside the sparse tensor).
+    const int lim_i = (int)min((int64_t)min(kTile, B - si * kTile), p.size_m - m0);
+    const int lim_j = (int)min((int64_t)min(kTile, B - sj * kTile), p.size_n - n0);
+    if (d.idx < 0 || d.idx >= p.nnz) return;
     const T* a = static_cast<const T*>(p.a) + z * p.size_m * p.size_k;
     const T* b = static_cast<const T*>(p.b) + z * p.size_k * p.size_n;
     float acc[2][2] = {};
@@ -128,14 +133,16 @@ __global__ void __launch_bounds__(kThreads) walk_kernel(const Params p) {
     const int first = p.table[g], last = p.table[g + 1];
     for (int it = first; it < last; ++it) {
         const BlockDesc d = p.blocks[it];
+        if (d.idx < 0 || d.idx >= p.nnz) continue;        // not a block of this sparse tensor (uniform for the CTA)
         const size_t blk = (size_t)d.idx * B * B;
         // block index along K: the coordinate of the block that is NOT the group
         int kb;
         if (kSparseA) kb = p.trans_a ? d.row() : d.col();
         else          kb = p.trans_b ? d.col() : d.row();
         for (int kk = 0; kk < KS; ++kk) {
-            const int lim_k = min(kTile, B - kk * kTile);
             const int64_t k0 = (int64_t)kb * B + kk * kTile;
+            // a block beyond the dense operand's inner extent contributes nothing (limit <= 0: nothing is read)
+            const int lim_k = (int)min((int64_t)min(kTile, B - kk * kTile), p.size_k - k0);
             SubTile ta, tb;
             if (kSparseA) {
                 if (!p.trans_a) ta = {blk + (size_t)sub * B + kk * kTile, B, 1, min(lim_i, lim_sub), lim_k};

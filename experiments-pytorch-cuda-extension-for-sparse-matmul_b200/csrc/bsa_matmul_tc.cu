@@ -612,24 +612,18 @@ bool tc_supports(const MatmulArgs& g) {
 }
 
 int matmul_tc(const MatmulArgs& g) {
-    // The opt-in shared-memory size is a per-device attribute, so it is set on every call (a cheap
-    // host-side update).  Doing it first also binds the device's primary context to the calling
-    // thread: cuTensorMapEncodeTiled below is a driver call and fails with "invalid context" on a
-    // thread (e.g. an autograd worker) that has not made a runtime call needing the context yet.
+    // The opt-in shared-memory size is set once per kernel and device, and tensor maps are kept per
+    // (address, shape): a launch-bound caller should not pay for driver calls per product.  (A map that
+    // has to be encoded binds the device's primary context to the calling thread first:
+    // cuTensorMapEncodeTiled is a driver call and fails with "invalid context" on a thread, e.g. an
+    // autograd worker, that has not made a runtime call needing the context yet.)
     using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const TcParams);
     const bool bf16 = g.dtype == BSA_DTYPE_BF16;
     KernelFn kernel;
     if (g.mode == BSA_MODE_SDD)      kernel = bf16 ? tc_matmul_kernel<BSA_MODE_SDD, true> : tc_matmul_kernel<BSA_MODE_SDD, false>;
     else if (g.mode == BSA_MODE_DSD) kernel = bf16 ? tc_matmul_kernel<BSA_MODE_DSD, true> : tc_matmul_kernel<BSA_MODE_DSD, false>;
     else                             kernel = bf16 ? tc_matmul_kernel<BSA_MODE_DDS, true> : tc_matmul_kernel<BSA_MODE_DDS, false>;
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
-        cudaGetLastError();
-        return BSA_ERR_LAUNCH;
-    }
-    {
-        int dev = 0;   // cudaSetDevice on the current device binds its primary context to this thread
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) { cudaGetLastError(); return BSA_ERR_LAUNCH; }
-    }
+    if (!ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kSmemBytes)) return BSA_ERR_LAUNCH;
     CUtensorMap map_a, map_b, map_c;
     const int split = g.block == 2 * kTile ? 1 : 0;
     const int64_t sparse_rows = g.nnz * g.block;     // the sparse tensor as a [nnz * block, block] matrix

@@ -533,8 +533,8 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 // 3-D tensor map over a row-major [batches, rows, cols] tensor with a 32x32x1 box and the swizzle
 // that spans a box row (fp32 operands used MN-major: its variant with 32-byte atoms, see
 // panel_desc).  Out-of-range parts of a box read as zero.
-bool make_map32(CUtensorMap* map, int dtype, bool mn_major, const void* base, int64_t batches, int64_t rows,
-                int64_t cols) {
+bool encode_map32(CUtensorMap* map, int dtype, bool mn_major, const void* base, int64_t batches, int64_t rows,
+                  int64_t cols) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     const cuuint64_t es = dtype == BSA_DTYPE_F32 ? 4 : 2;
@@ -555,6 +555,12 @@ bool make_map32(CUtensorMap* map, int dtype, bool mn_major, const void* base, in
         std::fprintf(stderr, "bsa: cuTensorMapEncodeTiled failed with CUresult %d (base %p, dims %lld x %lld x %lld)\n",
                      (int)res, base, (long long)batches, (long long)rows, (long long)cols);
     return res == CUDA_SUCCESS;
+}
+
+bool make_map32(CUtensorMap* map, int dtype, bool mn_major, const void* base, int64_t batches, int64_t rows,
+                int64_t cols) {
+    return cached_map(map, MapKey{base, batches, rows, cols, dtype, mn_major ? 1 : 0},
+                      [&](CUtensorMap* m) { return encode_map32(m, dtype, mn_major, base, batches, rows, cols); });
 }
 
 bool dense_dim_ok32(int64_t v) { return v >= kBlk && v % 8 == 0 && v < ((int64_t)1 << 31); }
@@ -590,17 +596,7 @@ int matmul_tc32(const MatmulArgs& g) {
     const Kernel32Fn kernel = g.mode == BSA_MODE_SDD   ? pick_dtype<BSA_MODE_SDD>(g.dtype)
                               : g.mode == BSA_MODE_DSD ? pick_dtype<BSA_MODE_DSD>(g.dtype)
                                                        : pick_dtype<BSA_MODE_DDS>(g.dtype);
-    // Set on every call (the opt-in shared-memory size is a per-device attribute); this and the
-    // cudaSetDevice below also bind the device's primary context to the calling thread, which the
-    // driver call behind make_map32 needs.
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
-        cudaGetLastError();
-        return BSA_ERR_LAUNCH;
-    }
-    {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) { cudaGetLastError(); return BSA_ERR_LAUNCH; }
-    }
+    if (!ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kSmemBytes)) return BSA_ERR_LAUNCH;
     const bool f32 = g.dtype == BSA_DTYPE_F32;
     const int panel_bytes = kBlk * kBlk * (f32 ? 4 : 2);
     CUtensorMap map_a, map_b;

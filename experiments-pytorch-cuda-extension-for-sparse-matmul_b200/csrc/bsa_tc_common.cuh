@@ -410,10 +410,70 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
+// Host work that need not be repeated per call.  Encoding a tensor map goes through the driver, and a
+// launch-bound caller (a few microseconds of kernel work per call) issues the same maps over and over:
+// a map depends only on the base address, the shape and the element type, so the last maps are kept
+// (a small direct-mapped table under a mutex; a hit copies 128 bytes).  One table per kernel file.
+struct MapKey {
+    const void* base;
+    int64_t batches, rows, cols;
+    int dtype, variant;                 // variant: box height / operand majorness, whatever else the encoder depends on
+    bool operator==(const MapKey& o) const {
+        return base == o.base && batches == o.batches && rows == o.rows && cols == o.cols && dtype == o.dtype &&
+               variant == o.variant;
+    }
+};
+template <class Encode>
+bool cached_map(CUtensorMap* map, const MapKey& key, Encode encode) {
+    constexpr int kSlots = 64;
+    struct Slot { MapKey key; CUtensorMap map; bool used; };
+    static Slot slots[kSlots] = {};
+    static std::mutex mutex;
+    const uintptr_t h = reinterpret_cast<uintptr_t>(key.base) >> 8;
+    const int slot = (int)((h ^ (h >> 7) ^ (uintptr_t)(key.rows * 31 + key.cols * 7 + key.variant)) % kSlots);
+    {
+        std::lock_guard<std::mutex> lock(mutex);
+        if (slots[slot].used && slots[slot].key == key) { *map = slots[slot].map; return true; }
+    }
+    // The driver call needs the device's primary context bound to the calling thread: cudaSetDevice on
+    // the current device does that (a thread that has only launched kernels so far may not have it).
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) { cudaGetLastError(); return false; }
+    if (!encode(map)) return false;
+    std::lock_guard<std::mutex> lock(mutex);
+    slots[slot].key = key; slots[slot].map = *map; slots[slot].used = true;
+    return true;
+}
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per kernel and device instead of once per call.  The
+// attribute is a maximum: it is only ever raised (a kernel launched with different sizes, e.g. per head
+// dimension, must not have it lowered by the smaller configuration).
+inline bool ensure_dynamic_smem(const void* kernel, int bytes) {
+    constexpr int kEntries = 64;
+    struct Entry { const void* kernel; int dev, bytes; };
+    static Entry done[kEntries] = {};
+    static int count = 0;
+    static std::mutex mutex;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return false; }
+    std::lock_guard<std::mutex> lock(mutex);
+    Entry* entry = nullptr;
+    for (int i = 0; i < count; ++i)
+        if (done[i].kernel == kernel && done[i].dev == dev) { entry = &done[i]; break; }
+    if (entry && entry->bytes >= bytes) return true;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    if (entry) entry->bytes = bytes;
+    else if (count < kEntries) done[count++] = Entry{kernel, dev, bytes};
+    return true;
+}
+
 // 3-D tensor map over a row-major [batches, rows, cols] 16-bit tensor with a 64x64x1 box and the
 // 128-byte swizzle.  Out-of-range parts of a box read as zero and are not written.
-bool make_map(CUtensorMap* map, int dtype, const void* base, int64_t batches, int64_t rows, int64_t cols,
-              int box_rows = kTile) {
+bool encode_map(CUtensorMap* map, int dtype, const void* base, int64_t batches, int64_t rows, int64_t cols,
+                int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     const cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batches};
@@ -431,10 +491,20 @@ bool make_map(CUtensorMap* map, int dtype, const void* base, int64_t batches, in
     return res == CUDA_SUCCESS;
 }
 
+bool make_map(CUtensorMap* map, int dtype, const void* base, int64_t batches, int64_t rows, int64_t cols,
+              int box_rows = kTile) {
+    return cached_map(map, MapKey{base, batches, rows, cols, dtype, box_rows},
+                      [&](CUtensorMap* m) { return encode_map(m, dtype, base, batches, rows, cols, box_rows); });
+}
+
+// Number of SMs of the current device (asked once per device).
 int sm_count() {
+    static int cached[64] = {};
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    if (dev >= 0 && dev < 64) cached[dev] = sms;
     return sms;
 }
 

@@ -106,6 +106,18 @@ torch::Tensor sparse_matmul(torch::Tensor a, torch::Tensor b, const std::string&
     const int64_t size_k = b_dense ? b.size(tr_b ? -1 : -2) : a.size(tr_a ? -2 : -1);
     if (a_dense && b_dense)
         TORCH_CHECK(a.size(tr_a ? -2 : -1) == size_k, "inner dimensions of a and b differ");
+    // The extent along the axis the chosen layout does not group comes from the other layout: a dense operand
+    // that is shorter than the pattern would be read beyond its end by the blocks of the last columns / rows.
+    {
+        const auto& other_table = std::get<1>(use_row ? col_layout : row_layout);
+        const int64_t other_width = (other_table.size(0) - 1) * block;
+        if (mode == "sdd") {
+            TORCH_CHECK(size_n == other_width, "sdd: op(b) has ", size_n, " columns, the layout covers ", other_width);
+        } else {
+            TORCH_CHECK(size_k == other_width, mode, ": the dense operand's inner size is ", size_k,
+                        ", the layout covers ", other_width);
+        }
+    }
     if (!a_dense) TORCH_CHECK(a.size(-3) == nnz, "sparse a holds ", a.size(-3), " blocks, the layout ", nnz);
     if (!b_dense) TORCH_CHECK(b.size(-3) == nnz, "sparse b holds ", b.size(-3), " blocks, the layout ", nnz);
 

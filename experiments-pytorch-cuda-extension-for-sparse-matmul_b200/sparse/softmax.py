@@ -26,6 +26,12 @@ class SparseSoftmax(torch.autograd.Function):
     def forward(ctx: Any, x: torch.Tensor, layout: SparseLayout, scale: float = 1.0, causal: bool = False,
                 key_padding_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
         row_blocks, row_table = layout.row_layout
+        if key_padding_mask is not None:
+            # the kernels index the mask by absolute key position: it has to cover every block column
+            keys = layout.pattern.size(1) * layout.block
+            if key_padding_mask.dim() != 2 or key_padding_mask.size(1) < keys:
+                raise ValueError("key_padding_mask must be [batch, seq_k] with seq_k >= %d, got shape %s"
+                                 % (keys, tuple(key_padding_mask.shape)))
         y = kernel.sparse_ops.sparse_softmax_forward(x, row_blocks, row_table, float(scale), bool(causal),
                                                      key_padding_mask, getattr(layout, "max_row_blocks", 0))
         ctx.save_for_backward(y)

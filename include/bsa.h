@@ -239,10 +239,15 @@ int bsa_sparse_to_dense(int dtype, const void* sparse, void* dense,
 
 /*
  * Read the device status word of a workspace (synchronises `stream`).
- * Returns BSA_OK, or BSA_ERR_DEVICE_TIMEOUT if a kernel that used this
- * workspace gave up on a bounded wait; the word is cleared on return.
+ * Returns BSA_OK; BSA_ERR_DEVICE_TIMEOUT if a kernel that used this workspace
+ * gave up on a bounded wait (its output is invalid); or BSA_ERR_BAD_SHAPE if a
+ * kernel met a block descriptor that does not belong to its layout (a rank
+ * outside [0, nnz): the block was skipped).  The word is cleared on return.
+ * bsa_workspace_status_detail also hands back the second workspace word in
+ * `*detail` (may be NULL): for BSA_ERR_BAD_SHAPE the offending rank, else 0.
  */
 int bsa_workspace_status(void* workspace, void* stream);
+int bsa_workspace_status_detail(void* workspace, void* stream, int32_t* detail);
 
 /*
  * bsa_matmul for callers that cannot allocate device memory.
@@ -257,17 +262,28 @@ int bsa_workspace_status(void* workspace, void* stream);
  * handed fixed buffers.  The entry point calls no cudaMalloc, cudaFree or
  * other allocating routine; inputs and the output are still the caller's.
  *
- *   wait_and_check  0: return right after the asynchronous launch.
+ *   wait_and_check  0: return right after the asynchronous launch.  A time-out
+ *                   inside the kernels is then reported only if the caller
+ *                   reads it with bsa_matmul_noalloc_status before the next
+ *                   call (which clears the array); use 0 inside a stream
+ *                   capture, where synchronising is not allowed.
  *                   nonzero: synchronise `stream` and return
  *                   BSA_ERR_DEVICE_TIMEOUT if a kernel gave up on a bounded wait.
  *
  * Limits.  The scratch requirement of the kernels is fixed (it does not grow
  * with the problem); should it ever exceed the 256 bytes of the static array
  * the call is refused with BSA_ERR_WORKSPACE.  At most 64 devices.
- * The first call on each device looks up the array's device address; make it
- * before any stream capture.  All calls on a device share the one array and
- * each call clears it first, so two calls whose kernels overlap on the GPU
- * (different streams or threads) race on the status words: serialise them.
+ * The array used is the one of the device that is CURRENT in the calling
+ * thread (cudaGetDevice), which must be the device `stream` and the operands
+ * belong to.  The first call on each device looks up the array's device
+ * address; make it before any stream capture.  All calls on a device share the
+ * one array and each call clears it first, so two calls whose kernels overlap
+ * on the GPU (different streams or threads) race on the status words:
+ * serialise them.
+ *
+ * bsa_matmul_noalloc_status synchronises `stream`, then returns and clears the
+ * status the last bsa_matmul_noalloc call on the current device left in the
+ * array (as bsa_workspace_status does for a caller's workspace).
  */
 int bsa_matmul_noalloc(int mode, int dtype, int trans_a, int trans_b,
                        const void* a, const void* b, void* c,
@@ -275,6 +291,7 @@ int bsa_matmul_noalloc(int mode, int dtype, int trans_a, int trans_b,
                        int64_t nnz, int64_t groups, int64_t batches,
                        int64_t size_m, int64_t size_n, int64_t size_k, int block,
                        int engine, int wait_and_check, void* stream);
+int bsa_matmul_noalloc_status(void* stream);
 
 #ifdef __cplusplus
 }

@@ -26,9 +26,20 @@ What it restates (file:line relative to the reference project root):
 * ``softmax_forward`` / ``softmax_backward`` -- the math of
   ``sparse_softmax_32x32_{forward,backward}_kernel`` (sparse_softmax.cu:113-205):
   softmax over the elements of each dense row that lie in nonzero blocks.
-  The reference file does not compile (undefined macros) and has no vectors:
-  PARITY UNPINNED by reference output; the definition is the masked dense torch
-  softmax.  Scale, causal and key-padding masks are additions of this build.
+  The reference file does not compile (undefined macros) and has no vectors, so
+  no reference OUTPUT exists to compare with; the definition (masked dense torch
+  softmax) is pinned to the reference SOURCE instead:
+  ``reference_softmax_forward_emulated`` / ``..._backward_emulated`` replay the
+  two kernels' arithmetic literally on the CPU (the ``-1e5f`` seed of the row
+  maximum, :24; the strided walk of the row's blocks by 32 x 32 threads and the
+  shuffle / shared-memory reduction trees, :26-55 and :75-104;
+  ``__expf(x - max)`` then division by the row sum, :139-154;
+  ``dx = (dy - sum(dy * y)) * y``, :190-203), and ``tests/test_oracle.py``
+  checks that the definition equals that replay (scale 1, no masks) -- and
+  documents the one place they differ: a row whose maximum lies below -1e5.
+  Scale, causal and key-padding masks are additions of this build.
+* ``strided_local_pattern`` -- the benchmark workload's block pattern, so that
+  the CPU arm of ``bench.py`` needs nothing from the shipped package.
 """
 from typing import Optional, Tuple
 
@@ -163,6 +174,92 @@ def softmax_backward(y: torch.Tensor, dy: torch.Tensor, pattern, block: int, sca
     dot = (yd * dyd).sum(dim=-1, keepdim=True)
     dx = scale * yd * (dyd - dot)
     return to_sparse(dx, pattern, block).contiguous()
+
+
+# --------------------------------------------------------------------------- literal replay of the reference softmax kernels
+def _tree_sum_lane0(v: np.ndarray) -> np.ndarray:
+    """Value lane 0 holds after ``for (offset = 16; offset > 0; offset /= 2) v += __shfl_down_sync(v, offset)``
+    (sparse_softmax.cu:84-85, 98-99): fp32 additions in exactly that order.  ``v`` is [..., 32]."""
+    v = v.astype(np.float32).copy()
+    for offset in (16, 8, 4, 2, 1):
+        shifted = v.copy()
+        shifted[..., : 32 - offset] = v[..., offset:]       # lanes past the end read their own value
+        v = (v + shifted).astype(np.float32)
+    return v[..., 0]
+
+
+def _row_blocks(row_blocks: np.ndarray, row_table: np.ndarray, block_row: int) -> np.ndarray:
+    """Storage indices (the descriptors' first word) of the blocks of one block row, in layout order."""
+    first, last = int(row_table[block_row]), int(row_table[block_row + 1])
+    return np.asarray(row_blocks).reshape(-1, 2)[first:last, 0].astype(np.int64)
+
+
+def _strided_partials(values: np.ndarray, reduce_max: bool) -> np.ndarray:
+    """Per-thread partial results of the strided walk ``block_ptr = start + threadIdx.y; block_ptr += 32``
+    (sparse_softmax.cu:26-33, 77-82).  ``values`` is [blocks, 32] (one dense row of every block of the row,
+    index = threadIdx.x); returns [32 (threadIdx.y), 32 (threadIdx.x)] fp32."""
+    out = np.full((32, 32), -1e5 if reduce_max else 0.0, dtype=np.float32)        # the seeds of :24 and :75
+    for i in range(values.shape[0]):
+        y = i % 32
+        out[y] = np.maximum(out[y], values[i]) if reduce_max else (out[y] + values[i]).astype(np.float32)
+    return out
+
+
+def _block_reduce(values: np.ndarray, reduce_max: bool) -> np.float32:
+    """reduce_sparse_matrix_32x32_row_max / _row_sum (sparse_softmax.cu:14-56, 63-105) for one dense row."""
+    part = _strided_partials(values, reduce_max)
+    if reduce_max:
+        return np.float32(part.max())            # a maximum does not depend on the order of the tree
+    per_warp = _tree_sum_lane0(part)             # [32]: shared[threadIdx.y]
+    return np.float32(_tree_sum_lane0(per_warp[None, :])[0])
+
+
+def reference_softmax_forward_emulated(x, row_blocks, row_table) -> np.ndarray:
+    """sparse_softmax_32x32_forward_kernel (sparse_softmax.cu:113-155) replayed on the CPU in fp32.
+    ``x`` is [batches, nnz, 32, 32]; the layout is the ROW layout in the int32 wire format."""
+    x = np.asarray(x, dtype=np.float32)
+    y = np.zeros_like(x)
+    table = np.asarray(row_table)
+    for z in range(x.shape[0]):
+        for block_row in range(len(table) - 1):
+            idx = _row_blocks(row_blocks, table, block_row)
+            if len(idx) == 0:
+                continue
+            for offset_row in range(32):
+                vals = x[z, idx, offset_row, :]                                  # [blocks, 32]
+                mx = _block_reduce(vals, True)
+                e = np.exp((vals - mx).astype(np.float32)).astype(np.float32)    # __expf(x - max), :139
+                total = _block_reduce(e, False)
+                with np.errstate(divide="ignore", invalid="ignore"):
+                    y[z, idx, offset_row, :] = (e / total).astype(np.float32)    # :153
+    return y
+
+
+def reference_softmax_backward_emulated(y, dy, row_blocks, row_table) -> np.ndarray:
+    """sparse_softmax_32x32_backward_kernel (sparse_softmax.cu:165-205) replayed on the CPU in fp32."""
+    y = np.asarray(y, dtype=np.float32)
+    dy = np.asarray(dy, dtype=np.float32)
+    dx = np.zeros_like(y)
+    table = np.asarray(row_table)
+    for z in range(y.shape[0]):
+        for block_row in range(len(table) - 1):
+            idx = _row_blocks(row_blocks, table, block_row)
+            if len(idx) == 0:
+                continue
+            for offset_row in range(32):
+                yy, dd = y[z, idx, offset_row, :], dy[z, idx, offset_row, :]
+                total = _block_reduce((dd * yy).astype(np.float32), False)       # :190, :193
+                dx[z, idx, offset_row, :] = ((dd - total) * yy).astype(np.float32)   # :203
+    return dx
+
+
+# --------------------------------------------------------------------------- benchmark workload
+def strided_local_pattern(size: int, stride: int = 8, window: int = 2) -> np.ndarray:
+    """Block pattern of the benchmark workload: every ``stride``-th block diagonal plus a band of
+    half-width ``window`` (non-causal), as an int64 0/1 array."""
+    i = np.arange(size)[:, None]
+    j = np.arange(size)[None, :]
+    return ((((i - j) % stride) == 0) | (np.abs(i - j) <= window)).astype(np.int64)
 
 
 # --------------------------------------------------------------------------- attention step

@@ -4,6 +4,9 @@ Tolerance (stated by the parity contract): max |got - ref| / max |ref| <= 1e-4
 for fp32 and <= 1e-2 for fp16 (bf16: 3e-2), ref = dense CPU torch computation
 masked by the same layout on the same seeded inputs.
 """
+import os
+import sys
+
 import numpy as np
 import pytest
 import torch
@@ -195,3 +198,64 @@ def test_argument_validation_raises():
     with pytest.raises(RuntimeError):   # wrong number of blocks in the sparse operand
         sparse_ops.sparse_matmul(torch.randn(1, 5, 32, 32, device="cuda"), q, "dsd", layout.row_layout,
                                  layout.col_layout, False, False, 32, "auto")
+
+
+def test_dense_operand_shorter_than_the_layout_is_rejected():
+    """The axis the chosen layout does not group is checked against the other layout: a dense operand that
+    is shorter than the pattern would be read beyond its end by the blocks of the last columns / rows."""
+    from sparse import SparseLayout
+    from sparse.kernel import sparse_ops
+    layout = SparseLayout(torch.tensor([[1, 0, 1], [1, 1, 1]]), block=32)       # 2 x 3 blocks
+    rl, cl = layout.row_layout, layout.col_layout
+    nnz = layout.num_blocks
+    p = torch.randn(1, nnz, 32, 32, device="cuda")
+    for engine in ("auto", "simt"):
+        with pytest.raises(RuntimeError):   # dsd: b needs 3 * 32 rows
+            sparse_ops.sparse_matmul(p, torch.randn(1, 64, 64, device="cuda"), "dsd", rl, cl, False, False, 32, engine)
+        with pytest.raises(RuntimeError):   # sdd: op(b) needs 3 * 32 columns
+            sparse_ops.sparse_matmul(torch.randn(1, 64, 64, device="cuda"), torch.randn(1, 64, 64, device="cuda"),
+                                     "sdd", rl, cl, False, True, 32, engine)
+        with pytest.raises(RuntimeError):   # dds: a needs 2 * 32 columns
+            sparse_ops.sparse_matmul(torch.randn(1, 64, 96, device="cuda"), p, "dds", rl, cl, False, False, 32, engine)
+        ok = sparse_ops.sparse_matmul(p, torch.randn(1, 96, 64, device="cuda"), "dsd", rl, cl, False, False, 32, engine)
+        assert ok.shape == (1, 64, 64)
+
+
+@pytest.mark.skipif(not os.environ.get("BSA_REFERENCE_CHECKOUT"),
+                    reason="set BSA_REFERENCE_CHECKOUT to a checkout of the reference project")
+def test_reference_autograd_layer_unmodified_over_this_binding():
+    """The reference's own sparse/matmul.py, imported unmodified from a checkout, with its `sparse_ops`
+    replaced by the binding of this library (seven positional arguments, the reference call): gradients equal
+    dense autograd for all twelve (mode, trans_a, trans_b) variants."""
+    import importlib
+    import types
+    from sparse import SparseLayout
+    from sparse.kernel import sparse_ops
+    root = os.environ["BSA_REFERENCE_CHECKOUT"]
+    pkg = types.ModuleType("refsparse")
+    pkg.__path__ = [os.path.join(root, "sparse")]
+    sys.modules["refsparse"] = pkg
+    kernel = types.ModuleType("refsparse.kernel")
+    kernel.sparse_ops = sparse_ops                 # the reference calls sparse_ops.sparse_matmul(a, b, mode, rl, cl, ta, tb)
+    sys.modules["refsparse.kernel"] = kernel
+    ref_matmul = importlib.import_module("refsparse.matmul").matmul
+    g = load_golden_layout("kat_4x3")
+    pattern = np.array(g["pattern"])
+    block = 32                                     # the reference's only block size (the binding's default)
+    layout = SparseLayout(torch.tensor(pattern), block=block)
+    for mode, ta, tb in VARIANTS:
+        a, b = operands(mode, ta, tb, pattern, block, 64, (2,), 31, torch.float32)
+        ag, bg = a.cuda().requires_grad_(True), b.cuda().requires_grad_(True)
+        out = ref_matmul(ag, bg, mode, layout, ta, tb)
+        dc = seeded(tuple(out.shape), 33)
+        out.backward(dc.cuda())
+        ad, bd = a.double().requires_grad_(True), b.double().requires_grad_(True)
+        a_full = oracle.to_dense(ad, pattern, block) if mode[1] == "s" else ad
+        b_full = oracle.to_dense(bd, pattern, block) if mode[2] == "s" else bd
+        c = (a_full.transpose(-1, -2) if ta else a_full) @ (b_full.transpose(-1, -2) if tb else b_full)
+        if mode[0] == "s":
+            c = oracle.to_sparse(c, pattern, block)
+        c.backward(dc.double())
+        assert_close(out, c, torch.float32, "C %s %s %s" % (mode, ta, tb))
+        assert_close(ag.grad, ad.grad, torch.float32, "dA %s %s %s" % (mode, ta, tb))
+        assert_close(bg.grad, bd.grad, torch.float32, "dB %s %s %s" % (mode, ta, tb))

@@ -127,3 +127,47 @@ def test_softmax_oracle_masks():
                         pattern, block)
     assert torch.all(y[0, :, 3:] == 0) and torch.allclose(y[0].sum(-1), torch.ones(8, dtype=torch.float64))
     assert torch.all(y[1] == 0)
+
+
+# ---- the softmax definition against a literal replay of the reference kernels' arithmetic
+# (sparse_softmax.cu:14-56, 63-105, 113-155, 165-205): scale 1, no masks, block 32, fp32
+@pytest.mark.parametrize("name", ["kat_4x3", "empty_row_col_5x4"])
+def test_softmax_definition_equals_reference_kernel_replay(name):
+    g = load_golden_layout(name)
+    pattern = np.array(g["pattern"], dtype=np.int64)
+    nnz = int(pattern.sum())
+    gen = torch.Generator().manual_seed(77)
+    x = torch.randn(2, nnz, 32, 32, generator=gen) * 3.0
+    dy = torch.randn(2, nnz, 32, 32, generator=gen)
+    y_def = oracle.softmax_forward(x, pattern, 32)
+    y_ref = oracle.reference_softmax_forward_emulated(x.numpy(), g["row_blocks"], g["row_table"])
+    assert np.abs(y_def.numpy() - y_ref).max() <= 1e-6
+    # every dense row that has blocks sums to 1 in the replay too
+    dense = oracle.to_dense(torch.from_numpy(y_ref), pattern, 32)
+    has_blocks = torch.as_tensor(pattern.sum(axis=1) > 0).repeat_interleave(32)
+    assert torch.allclose(dense.sum(-1)[:, has_blocks], torch.ones(2, int(has_blocks.sum())), atol=1e-5)
+    dx_def = oracle.softmax_backward(y_def, dy, pattern, 32)
+    dx_ref = oracle.reference_softmax_backward_emulated(y_ref, dy.numpy(), g["row_blocks"], g["row_table"])
+    assert np.abs(dx_def.numpy() - dx_ref).max() <= 1e-6
+
+
+def test_softmax_definition_and_reference_part_ways_below_the_seed():
+    """The reference seeds its row maximum with -1e5 (sparse_softmax.cu:24).  A row whose every score lies
+    below that keeps the seed as its maximum, all exponentials underflow and the row becomes 0 / 0; the
+    masked dense definition (and the kernels of this library) subtract the true maximum and return the
+    proper probabilities.  Rows above the seed agree."""
+    g = load_golden_layout("kat_4x3")
+    pattern = np.array(g["pattern"], dtype=np.int64)
+    nnz = int(pattern.sum())
+    x = torch.randn(1, nnz, 32, 32, generator=torch.Generator().manual_seed(3))
+    rows_blocks = np.asarray(g["row_blocks"]).reshape(-1, 2)
+    first_row_blocks = rows_blocks[g["row_table"][0]:g["row_table"][1], 0]
+    x[0, first_row_blocks, 5, :] -= 2.0e5                     # dense row 5 of block row 0: everything below -1e5
+    y_def = oracle.softmax_forward(x, pattern, 32).numpy()
+    y_ref = oracle.reference_softmax_forward_emulated(x.numpy(), g["row_blocks"], g["row_table"])
+    low = y_ref[0, first_row_blocks, 5, :]
+    assert not np.isfinite(low).all() or np.abs(low).max() == 0.0          # 0 / 0 in the reference's arithmetic
+    assert abs(y_def[0, first_row_blocks, 5, :].sum() - 1.0) <= 1e-5       # a probability row in the definition
+    keep = np.ones_like(y_ref, dtype=bool)
+    keep[0, first_row_blocks, 5, :] = False
+    assert np.abs(y_def[keep] - y_ref[keep]).max() <= 1e-6

@@ -60,19 +60,25 @@ constexpr int kStageTiles = 28;                 // 8 KB tiles of shared memory: 
 constexpr int kSddStagingTile0 = 24;            // sdd: tiles 24 .. 27 hold the epilogue warps' output slabs (8 stages x 3 tiles come first)
 constexpr int kAccCols = 256;                   // TMEM columns per accumulator buffer (dsd / dds: 2 buffers)
 constexpr int kTmemCols = 2 * kAccCols;
-constexpr int kSddTiles = 2;                    // sdd: output tiles per accumulation; 4 buffers of 128 columns, so that
-                                                // the chain MMA issue -> MMA -> TMEM loads of one buffer is hidden by three others
+constexpr int kSddTiles = 2;                    // sdd: output tiles per accumulation (a buffer of 128 columns)
+// sdd is the output-heavy mode: per 8 KB block it writes, the epilogue's chain (accumulator barrier -> TMEM load ->
+// convert -> stmatrix -> proxy fence -> TMA store) takes about 1000 cycles, so it needs many accumulations in
+// flight.  Four epilogue warpgroups drain eight accumulator buffers: an M = 64 accumulator occupies lanes 0-15 of
+// each 32-lane quarter of tensor memory, and a second one fits into lanes 16-31 of the same columns (lane offset
+// 16 in the MMA's D address and in the 16-lane tcgen05.ld shape): buffers 0-3 and 4-7 share their columns.
+constexpr int kSddGroups = 4;
+constexpr int kSddBufs = 2 * kSddGroups;
 constexpr int kProducerWarps = 4;
 constexpr int kMmaWarps = 4;
 constexpr int kFirstMmaWarp = kProducerWarps;
 constexpr int kFirstEpilogueWarp = kFirstMmaWarp + kMmaWarps;
-constexpr int kThreads = (kFirstEpilogueWarp + 8) * 32;
+constexpr int threads_of(int mode) { return (kFirstEpilogueWarp + 4 * (mode == BSA_MODE_SDD ? kSddGroups : 2)) * 32; }
 
 struct __align__(8) Barriers {
     uint64_t full[kMaxStages];
     uint64_t empty[kMaxStages];
-    uint64_t acc_full[4];
-    uint64_t acc_empty[4];
+    uint64_t acc_full[kSddBufs];
+    uint64_t acc_empty[kSddBufs];
     uint64_t drain;
     uint32_t tmem_base;
     int abort_flag;
@@ -177,7 +183,7 @@ __device__ __forceinline__ void store_row(uint16_t* dst, const uint32_t (&v)[NCO
 // One instantiation per mode keeps each role's loop small (the sixteen warps of a CTA run
 // four different code paths through the same instruction caches).
 template <int MODE, bool BF16>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(threads_of(MODE), 1)
 tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_c, const TcParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -188,15 +194,20 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int stage_bytes = (1 + p.nb_max) * kTileBytes;
     constexpr bool is_sdd = MODE == BSA_MODE_SDD;
-    constexpr int kBufs = is_sdd ? 4 : 2;               // accumulator buffers in TMEM
-    constexpr int kBufShift = is_sdd ? 2 : 1;
-    constexpr int kBufCols = kTmemCols / kBufs;
+    constexpr int kBufs = is_sdd ? kSddBufs : 2;        // accumulator buffers in TMEM
+    constexpr int kBufShift = is_sdd ? 3 : 1;
+    constexpr int kGroups = is_sdd ? kSddGroups : 2;    // epilogue warpgroups
+    constexpr int kBufCols = is_sdd ? 128 : kTmemCols / 2;
+    // TMEM address (column and lane offset) of accumulator buffer `acc`
+    auto acc_addr = [&](int acc) -> uint32_t {
+        return is_sdd ? (uint32_t)((acc & 3) * kBufCols) + ((uint32_t)((acc >> 2) * 16) << 16) : (uint32_t)(acc * kBufCols);
+    };
     // sdd: one issuer per accumulation; dsd / dds: every issuer reports on every accumulation
     const uint32_t arrivals = is_sdd ? 1u : (uint32_t)p.issuers;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMaxStages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
-        for (int s = 0; s < 4; ++s) { mbar_init(&bars->acc_full[s], arrivals); mbar_init(&bars->acc_empty[s], 4); }
+        for (int s = 0; s < kSddBufs; ++s) { mbar_init(&bars->acc_full[s], arrivals); mbar_init(&bars->acc_empty[s], 4); }
         mbar_init(&bars->drain, (uint32_t)p.issuers);
         bars->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -350,7 +361,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_empty[acc], ((uint32_t)(flush_no >> kBufShift) & 1u) ^ 1u, &bars->abort_flag, p.status)) != 0;
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t d = tmem_base + (uint32_t)(acc * kBufCols) + part_col;
+                    const uint32_t d = tmem_base + acc_addr(acc) + part_col;
                     bool issued = false;
                     // dsd / dds: K-step n belongs to issuer n % issuers (the stage count is a
                     // multiple of it, so a stage always belongs to the same issuer)
@@ -406,7 +417,6 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int parts = is_sdd ? 1 : p.issuers;
         const int part_stride = kAccCols / p.issuers;
         int flush_no = 0, step = 0;
-        int tile_no = 0;                    // sdd: slabs this warp has sent so far (staging slab = tile_no & 1)
         bool ok = true;
         Cursor cur;
         cur.init(p, p.split);
@@ -423,7 +433,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             for (int f = 0; ok && f < flushes; ++f) {
                 // accumulations alternate between the two buffers / groups; groups that write
                 // zeros for an empty group of blocks are chosen by item parity
-                const int owner = have_acc ? (flush_no & 1) : (cur.item_no & 1);
+                const int owner = have_acc ? (flush_no & (kGroups - 1)) : (cur.item_no & (kGroups - 1));
                 const uint32_t acc_phase = (uint32_t)(flush_no >> kBufShift) & 1u;
                 const int acc = flush_no & (kBufs - 1);     // (dsd / dds: the group's own buffer)
                 const int step0 = step;             // sequence number of this accumulation's first K-step
@@ -443,15 +453,14 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     // 2 KB staging slab and sends the slab to global memory with one bulk tensor store
                     // (box 16 x 64).  About 30 instructions per lane and tile instead of 110 for a
                     // shuffle-transpose / 128-bit store path, no synchronisation between warps, and
-                    // the stores are asynchronous (two slabs per warp alternate).
-                    // The tiles of an accumulation are ready together: the TMEM load of tile t + 1 is in
-                    // flight while tile t is converted.
-                    const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * kBufCols);
+                    // the stores are asynchronous (one slab per warp: the store of a tile reads it while
+                    // the warp loads and converts its next tile).
+                    const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) + acc_addr(acc);
                     // lane -> row address of its 8x8 matrix: matrix i = lane / 8 holds rows (i & 1) * 8 ..
                     // of 16-byte column unit u = 2k + (i >> 1)
                     const int sm_row = ((lane >> 3) & 1) * 8 + (lane & 7);        // row inside the slab
                     const uint32_t sm_unit = (uint32_t)(lane >> 4);
-                    const int slab0 = ((warp - kFirstEpilogueWarp) * 2) * (16 * 128);   // this warp's two slabs
+                    const int slab0 = (warp - kFirstEpilogueWarp) * (16 * 128);         // this warp's slab
                     auto store_tile = [&](const uint32_t (&r)[32], int t) {
                         const int out_idx = tile_desc(win, p, cur, kSddTiles * f + t, lane).idx;
                         // a descriptor that does not belong to this layout is reported in the workspace
@@ -461,23 +470,26 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                             atomicExch(p.status, (uint32_t)BSA_ERR_BAD_SHAPE);
                             atomicExch(p.status + 1, (uint32_t)out_idx);
                         }
-                        const uint32_t slab = smem_u32(stage_base + kSddStagingTile0 * kTileBytes + slab0 + (tile_no & 1) * (16 * 128));
-                        // the slab written now was sent two tiles ago: that store must have read it
-                        if (elect_one()) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-                        __syncwarp();
+                        const uint32_t slab = smem_u32(stage_base + kSddStagingTile0 * kTileBytes + slab0);
+                        uint32_t w[16];                         // [4k + i]: matrices (u = 2k, rows a), (2k, b), (2k + 1, a), (2k + 1, b)
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-                            uint32_t w[4];                      // matrices (u = 2k, rows a), (2k, b), (2k + 1, a), (2k + 1, b)
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {
                                 const int u = 2 * k + (i >> 1), h = i & 1;
                                 const float lo = __uint_as_float(r[4 * u + 2 * h]), hi = __uint_as_float(r[4 * u + 2 * h + 1]);
-                                if (bf16_out) { __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi); w[i] = *reinterpret_cast<uint32_t*>(&v); }
-                                else          { __half2 v = __floats2half2_rn(lo, hi); w[i] = *reinterpret_cast<uint32_t*>(&v); }
+                                if (bf16_out) { __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi); w[4 * k + i] = *reinterpret_cast<uint32_t*>(&v); }
+                                else          { __half2 v = __floats2half2_rn(lo, hi); w[4 * k + i] = *reinterpret_cast<uint32_t*>(&v); }
                             }
+                        }
+                        // the slab was sent with the tile before: that store must have read it
+                        if (elect_one()) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                        __syncwarp();
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
                             const uint32_t addr = slab + (uint32_t)(sm_row * 128) + ((((uint32_t)(2 * k) + sm_unit) ^ (uint32_t)(sm_row & 7)) << 4);
                             asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1, %2, %3, %4};"
-                                         ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+                                         ::"r"(addr), "r"(w[4 * k]), "r"(w[4 * k + 1]), "r"(w[4 * k + 2]), "r"(w[4 * k + 3]) : "memory");
                         }
                         fence_async_shared();           // generic-proxy writes -> visible to the bulk store
                         __syncwarp();
@@ -491,20 +503,14 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                              ::"l"(&map_c), "r"(slab), "r"(sx), "r"(sy + quad * 16), "r"(cur.z) : "memory");
                             asm volatile("cp.async.bulk.commit_group;" ::: "memory");   // (empty groups keep the count regular)
                         }
-                        ++tile_no;
                     };
-                    uint32_t ra[32], rb[32];
-                    tc_ld_16x256b_x8(tbase, ra);
-                    for (int t = 0; t < tiles; t += 2) {
+                    // one register buffer: the other groups' accumulations cover this one's TMEM load
+                    uint32_t r[32];
+                    for (int t = 0; t < tiles; ++t) {
+                        tc_ld_16x256b_x8(tbase + (uint32_t)(t * kTile), r);
                         tc_wait_ld();
-                        if (t + 1 < tiles) tc_ld_16x256b_x8(tbase + (uint32_t)((t + 1) * kTile), rb);
-                        else               release_accumulator(&bars->acc_empty[acc], lane);
-                        store_tile(ra, t);
-                        if (t + 1 >= tiles) break;
-                        tc_wait_ld();
-                        if (t + 2 < tiles) tc_ld_16x256b_x8(tbase + (uint32_t)((t + 2) * kTile), ra);
-                        else               release_accumulator(&bars->acc_empty[acc], lane);
-                        store_tile(rb, t + 1);
+                        if (t + 1 >= tiles) release_accumulator(&bars->acc_empty[acc], lane);
+                        store_tile(r, t);
                     }
                     continue;
                 }
@@ -530,8 +536,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     }
                     const bool writer = row_lane && row < rows_valid && in_bounds;
                     uint16_t* dst = p.c + dst0 + (size_t)row * p.ldc;
-                    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16)
-                                           + (uint32_t)(acc * kBufCols + t * kTile);
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc_addr(acc) + (uint32_t)(t * kTile);
                     const bool last_tile = have_acc && t == tiles - 1;
                     if (!have_acc || parts == 1) {
                         uint32_t v[kTile];          // fp32 bit patterns of this lane's row
@@ -683,7 +688,7 @@ int matmul_tc(const MatmulArgs& g) {
     const int per_z = p.groups * p.chunks;
     p.stride_z = (int)grid / per_z;
     p.stride_rem = (int)grid % per_z;
-    kernel<<<grid, kThreads, kSmemBytes, g.stream>>>(map_a, map_b, map_c, p);
+    kernel<<<grid, threads_of(g.mode), kSmemBytes, g.stream>>>(map_a, map_b, map_c, p);
     return launch_status();
 }
 

@@ -83,7 +83,34 @@ struct Tc32Params {
     int ldc;                 // elements between output rows
     int stride_z, stride_rem;  // gridDim.x divided by the items per batch entry: quotient and remainder
     long long c_elems;       // elements in the output (bounds check of every store)
+    int split;               // log2(block / 32): blocks of 64 / 128 are walked as 2 x 2 / 4 x 4 panels (see panel_of)
+    int col_walk;            // the groups are block columns (dsd with trans_a, dds without trans_b)
+    int block;               // block edge of the layout in elements
 };
+
+// Blocks of 64 and 128 (fp32 operands; 16-bit ones run on the block-64 engine).  The kernel keeps working on
+// 32 x 32 panels: a real group (block row or column) is S = block / 32 virtual groups and a real block S K-steps /
+// output panels of each, i.e. the kernel sees the layout with every block split in S x S, without that layout
+// ever being built.  `groups` and `items` of Tc32Params count virtual groups; the cursor reads table[g >> split]
+// and keeps first / count in real blocks.  Virtual descriptor i of virtual group g is real descriptor i >> split
+// with one sub-index taken from g and the other from i (which of row / column depends on the walk).
+struct Panel {
+    int idx;                 // rank of the real block
+    int rh, ch;              // panel row / column inside the block
+    int row, col;            // panel coordinates in the split layout
+};
+__device__ __forceinline__ Panel panel_of(DescWindow& win, const Tc32Params& p, const Cursor& cur, int i, int lane) {
+    const BlockDesc d = win.get(p.blocks, cur.first, cur.count, i >> p.split, lane);
+    const int mask = (1 << p.split) - 1;
+    const int from_step = i & mask, from_group = cur.g & mask;
+    Panel v;
+    v.idx = d.idx;
+    v.rh = p.col_walk ? from_step : from_group;
+    v.ch = p.col_walk ? from_group : from_step;
+    v.row = (d.row() << p.split) + v.rh;
+    v.col = (d.col() << p.split) + v.ch;
+    return v;
+}
 
 __device__ __forceinline__ void tc_mma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
                                             uint32_t accumulate) {
@@ -216,27 +243,29 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         uint32_t phase = 0;
         bool ok = true;
         Cursor cur;
-        cur.init(p);
+        cur.init(p, p.split);
         BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
         while (ok && cur.valid()) {
             BlockDesc pre_next{0, 0};
             if (cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
             int flushes, ksteps;
-            item_shape<MODE>(p, cur.count, flushes, ksteps);
+            item_shape<MODE>(p, cur.count << p.split, flushes, ksteps);
             DescWindow win;
             win.begin(p.blocks, cur.first, cur.count, pre, lane);
             for (int f = 0; ok && f < flushes; ++f) {
-                const int nb = b_panels<MODE>(p, cur.count, cur.chunk, f);
+                const int nb = b_panels<MODE>(p, cur.count << p.split, cur.chunk, f);
                 for (int k = (warp - step0) & (kProducerWarps - 1); ok && k < ksteps; k += kProducerWarps) {
                     int cols[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                    BlockDesc d{0, 0};
+                    Panel d{0, 0, 0, 0, 0};
                     if (is_sdd) {
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
-                            if (j < nb) cols[j] = win.get(p.blocks, cur.first, cur.count, (f << p.nb_shift) + j, lane).col();
+                            if (j < nb) cols[j] = panel_of(win, p, cur, (f << p.nb_shift) + j, lane).col;
                     } else {
-                        d = win.get(p.blocks, cur.first, cur.count, k, lane);
+                        d = panel_of(win, p, cur, k, lane);
                     }
+                    // TMA coordinates of the panel inside the sparse tensor viewed as [nnz * block, block]
+                    const int sx = d.ch * kBlk, sy = d.idx * p.block + d.rh * kBlk;
                     {
                         // the whole warp waits (warp-uniform code keeps the copies' operands in uniform
                         // registers); one elected lane issues
@@ -259,22 +288,22 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                     }
                                 }
                             } else if (MODE == BSA_MODE_DSD) {
-                                const int k0 = (p.trans_a ? d.row() : d.col()) * kBlk;
-                                tma_load_3d(slot, &map_a, full, 0, d.idx * kBlk, cur.z);
+                                const int k0 = (p.trans_a ? d.row : d.col) * kBlk;
+                                tma_load_3d(slot, &map_a, full, sx, sy, cur.z);
                                 for (int j = 0; j < nb; ++j) {
                                     const int n0 = (cur.chunk * 4 + j) * kBlk;
                                     if (b_mn_major) tma_load_3d(slot_b + j * kPanelBytes, &map_b, full, n0, k0, cur.z);
                                     else            tma_load_3d(slot_b + j * kPanelBytes, &map_b, full, k0, n0, cur.z);
                                 }
                             } else {
-                                const int k0 = (p.trans_b ? d.col() : d.row()) * kBlk;
+                                const int k0 = (p.trans_b ? d.col : d.row) * kBlk;
 #pragma unroll
                                 for (int j = 0; j < 2; ++j) {
                                     const int m0 = (cur.chunk * 2 + j) * kBlk;   // past the end: the box reads as zero
                                     if (a_mn_major) tma_load_3d(slot + j * kPanelBytes, &map_a, full, m0, k0, cur.z);
                                     else            tma_load_3d(slot + j * kPanelBytes, &map_a, full, k0, m0, cur.z);
                                 }
-                                tma_load_3d(slot_b, &map_b, full, 0, d.idx * kBlk, cur.z);
+                                tma_load_3d(slot_b, &map_b, full, sx, sy, cur.z);
                             }
                         }
                         __syncwarp();
@@ -315,10 +344,10 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             const uint32_t part_col = is_sdd ? 0u : (uint32_t)(w * (kAccCols / p.issuers));
             const int issuer_mask = p.issuers - 1;       // issuers is 1, 2 or 4
             Cursor cur;
-            cur.init(p);
+            cur.init(p, p.split);
             for (; ok && cur.valid(); cur.advance()) {
                 int flushes, ksteps;
-                item_shape<MODE>(p, cur.count, flushes, ksteps);
+                item_shape<MODE>(p, cur.count << p.split, flushes, ksteps);
                 if (ksteps == 0) continue;          // empty group: the epilogue writes zeros on its own
                 for (int f = 0; ok && f < flushes; ++f, ++flush_no) {
                     const int acc = flush_no & 1;
@@ -327,7 +356,7 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         while (stage >= p.stages) { stage -= p.stages; phase ^= 1; }
                         continue;
                     }
-                    const int nb = b_panels<MODE>(p, cur.count, cur.chunk, f);
+                    const int nb = b_panels<MODE>(p, cur.count << p.split, cur.chunk, f);
                     const uint32_t idesc = p.idesc | ((uint32_t)((nb * kBlk) >> 3) << 17);
                     ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_empty[acc], ((uint32_t)(flush_no >> 1) & 1u) ^ 1u, abort_flag, p.status)) != 0;
                     if (!ok) break;
@@ -389,12 +418,12 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         uint32_t phase = 0;
         bool ok = true;
         Cursor cur;
-        cur.init(p);
+        cur.init(p, p.split);
         for (; ok && cur.valid(); cur.advance()) {
             int flushes, ksteps;
-            item_shape<MODE>(p, cur.count, flushes, ksteps);
+            item_shape<MODE>(p, cur.count << p.split, flushes, ksteps);
             for (int f = 0; ok && f < flushes; ++f) {
-                const int nb = b_panels<MODE>(p, cur.count, cur.chunk, f);
+                const int nb = b_panels<MODE>(p, cur.count << p.split, cur.chunk, f);
                 for (int k = (s - step0) & 3; ok && k < ksteps; k += 4) {
                     ok = __all_sync(0xffffffffu, mbar_wait(&bars->full[stage], phase, abort_flag, p.status)) != 0;
                     if (!ok) break;
@@ -436,14 +465,14 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         int flush_no = 0, step = 0;
         bool ok = true;
         Cursor cur;
-        cur.init(p);
+        cur.init(p, p.split);
         BlockDesc pre{0, 0};
         if (is_sdd && cur.valid()) pre = load_first_chunk(p.blocks, cur.first, cur.count, lane);
         while (ok && cur.valid()) {
             BlockDesc pre_next{0, 0};
             if (is_sdd && cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
             int flushes, ksteps;
-            item_shape<MODE>(p, cur.count, flushes, ksteps);
+            item_shape<MODE>(p, cur.count << p.split, flushes, ksteps);
             const bool have_acc = ksteps > 0;
             DescWindow win;
             if (is_sdd) win.begin(p.blocks, cur.first, cur.count, pre, lane);
@@ -457,7 +486,7 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 step += ksteps;
                 if (have_acc) ++flush_no;
                 if (owner != group) continue;
-                const int pieces = b_panels<MODE>(p, cur.count, cur.chunk, f);
+                const int pieces = b_panels<MODE>(p, cur.count << p.split, cur.chunk, f);
                 if (have_acc) {
                     ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_full[acc], acc_phase, abort_flag, p.status)) != 0;
                     if (!ok) break;
@@ -469,8 +498,10 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         size_t dst0;
                         int rows_valid = kBlk, cols_valid = kBlk;
                         if (is_sdd) {
-                            const int out_idx = win.get(p.blocks, cur.first, cur.count, (f << p.nb_shift) + t, lane).idx;
-                            dst0 = ((size_t)cur.z * p.nnz + out_idx) * (kBlk * kBlk);
+                            const Panel out = panel_of(win, p, cur, (f << p.nb_shift) + t, lane);
+                            // a rank outside the layout makes the bounds check below fail (reported, not written)
+                            dst0 = (out.idx < 0 || out.idx >= p.nnz) ? (size_t)p.c_elems
+                                               : (((size_t)cur.z * p.nnz + out.idx) * p.block + out.rh * kBlk) * p.block + out.ch * kBlk;
                         } else if (MODE == BSA_MODE_DSD) {
                             const int n0 = (cur.chunk * 4 + t) * kBlk;
                             dst0 = ((size_t)cur.z * p.size_m + (size_t)cur.g * kBlk) * p.size_n + n0;
@@ -584,11 +615,12 @@ Kernel32Fn pick_dtype(int dtype) {
 
 bool tc32_supports(const MatmulArgs& g) {
     if (g.dtype != BSA_DTYPE_F16 && g.dtype != BSA_DTYPE_BF16 && g.dtype != BSA_DTYPE_F32) return false;
-    if (g.block != kBlk) return false;
-    if (g.nnz <= 0 || g.nnz * kBlk >= ((int64_t)1 << 31) || g.batches > 65535) return false;
+    // block 32 in every type; fp32 (3xTF32) also at blocks 64 and 128, walked as 2 x 2 / 4 x 4 panels
+    if (g.block != kBlk && !(g.dtype == BSA_DTYPE_F32 && (g.block == 2 * kBlk || g.block == 4 * kBlk))) return false;
+    if (g.nnz <= 0 || g.nnz * g.block >= ((int64_t)1 << 31) || g.batches > 65535) return false;
     if (!dense_dim_ok32(g.size_m) || !dense_dim_ok32(g.size_n) || !dense_dim_ok32(g.size_k)) return false;
     // work items are indexed with 32-bit integers
-    if (g.batches * g.groups * slices_of32(g) >= ((int64_t)1 << 30)) return false;
+    if (g.batches * g.groups * (g.block / kBlk) * slices_of32(g) >= ((int64_t)1 << 30)) return false;
     return true;
 }
 
@@ -600,28 +632,31 @@ int matmul_tc32(const MatmulArgs& g) {
     const bool f32 = g.dtype == BSA_DTYPE_F32;
     const int panel_bytes = kBlk * kBlk * (f32 ? 4 : 2);
     CUtensorMap map_a, map_b;
-    const int64_t sparse_rows = g.nnz * kBlk;
+    const int64_t sparse_rows = g.nnz * g.block;      // the sparse tensor as a [nnz * block, block] matrix
+    const int split = g.block == 4 * kBlk ? 2 : (g.block == 2 * kBlk ? 1 : 0);
     bool ok = true;
     // stored shapes: a dense operand is [rows, cols] = op^-1 of its logical shape
     if (g.mode == BSA_MODE_SDD) {
         ok &= make_map32(&map_a, g.dtype, g.trans_a, g.a, g.batches, g.trans_a ? g.size_k : g.size_m, g.trans_a ? g.size_m : g.size_k);
         ok &= make_map32(&map_b, g.dtype, !g.trans_b, g.b, g.batches, g.trans_b ? g.size_n : g.size_k, g.trans_b ? g.size_k : g.size_n);
     } else if (g.mode == BSA_MODE_DSD) {
-        ok &= make_map32(&map_a, g.dtype, g.trans_a, g.a, g.batches, sparse_rows, kBlk);
+        ok &= make_map32(&map_a, g.dtype, g.trans_a, g.a, g.batches, sparse_rows, g.block);
         ok &= make_map32(&map_b, g.dtype, !g.trans_b, g.b, g.batches, g.trans_b ? g.size_n : g.size_k, g.trans_b ? g.size_k : g.size_n);
     } else {
         ok &= make_map32(&map_a, g.dtype, g.trans_a, g.a, g.batches, g.trans_a ? g.size_k : g.size_m, g.trans_a ? g.size_m : g.size_k);
-        ok &= make_map32(&map_b, g.dtype, !g.trans_b, g.b, g.batches, sparse_rows, kBlk);
+        ok &= make_map32(&map_b, g.dtype, !g.trans_b, g.b, g.batches, sparse_rows, g.block);
     }
     if (!ok) return BSA_ERR_DRIVER;
 
     Tc32Params p{};
     p.blocks = g.blocks; p.table = g.table; p.status = g.workspace;
-    p.nnz = (int)g.nnz; p.groups = (int)g.groups; p.batches = (int)g.batches;
+    p.split = split; p.block = g.block;
+    p.col_walk = ((g.mode == BSA_MODE_DSD && g.trans_a) || (g.mode == BSA_MODE_DDS && !g.trans_b)) ? 1 : 0;
+    p.nnz = (int)g.nnz; p.groups = (int)(g.groups << split); p.batches = (int)g.batches;
     p.size_m = (int)g.size_m; p.size_n = (int)g.size_n; p.size_k = (int)g.size_k;
     p.trans_a = g.trans_a; p.trans_b = g.trans_b;
     p.chunks = (int)slices_of32(g);
-    p.items = (int)(g.batches * g.groups * p.chunks);
+    p.items = (int)(g.batches * p.groups * p.chunks);
     int nb_max;                                    // B panels per stage
     if (g.mode == BSA_MODE_SDD) { p.nb_shift = f32 ? 2 : 3; nb_max = 1 << p.nb_shift; p.issuers = 2; }
     else if (g.mode == BSA_MODE_DSD && g.size_n > 2 * kBlk) { nb_max = 4; p.issuers = 2; }
@@ -647,8 +682,8 @@ int matmul_tc32(const MatmulArgs& g) {
               | ((g.trans_b ? 0u : 1u) << 16) | ((uint32_t)(64 >> 4) << 24);
 
     p.c = g.c;
-    p.ldc = g.mode == BSA_MODE_SDD ? kBlk : (int)g.size_n;
-    p.c_elems = g.mode == BSA_MODE_SDD ? (long long)g.batches * g.nnz * kBlk * kBlk
+    p.ldc = g.mode == BSA_MODE_SDD ? g.block : (int)g.size_n;
+    p.c_elems = g.mode == BSA_MODE_SDD ? (long long)g.batches * g.nnz * g.block * g.block
                                        : (long long)g.batches * g.size_m * g.size_n;
 
     const int sms = sm_count();

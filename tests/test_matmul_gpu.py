@@ -134,6 +134,20 @@ def test_block128_on_tensor_cores(mode, ta, tb, dtype):
     run_case(mode, ta, tb, pattern, 128, 160, dtype, "tcgen05", batch=(5, 8), seed=132)
 
 
+@pytest.mark.parametrize("mode,ta,tb", VARIANTS)
+@pytest.mark.parametrize("block", [64, 128])
+def test_fp32_block64_and_block128_on_tensor_cores(mode, ta, tb, block):
+    """fp32 at blocks 64 and 128 on the tcgen05 engine as a 3xTF32 split, requested explicitly (it must not
+    fall back): every block is walked as 2 x 2 / 4 x 4 panels of 32 x 32.  Patterns with empty groups, several
+    work items per CTA, dense sizes that leave partial slices; tolerance 1e-4 against the fp64 oracle."""
+    g = load_golden_layout("empty_row_col_5x4")
+    run_case(mode, ta, tb, g["pattern"], block, 64, torch.float32, "tcgen05", batch=(2,), seed=231)
+    rng = np.random.default_rng(7)
+    pattern = (rng.random((9, 7)) < 0.4).astype(np.int64)
+    pattern[3, :] = 0
+    run_case(mode, ta, tb, pattern, block, 96 if block == 64 else 160, torch.float32, "tcgen05", batch=(3, 4), seed=232)
+
+
 def test_config1_sdd_fp32_per_head_layouts():
     """benchmark configuration 1: batch 1, heads 2, seq 256, head_dim 64, block 32, Bernoulli(0.5) + diagonal
     per head, Q.K^T as sdd(N,T) in fp32."""

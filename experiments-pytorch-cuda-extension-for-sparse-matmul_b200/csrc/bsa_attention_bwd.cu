@@ -573,6 +573,30 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
 
 namespace {
 
+#include "bsa_attention_bwd_rows.cuh"
+
+// dQ by block rows with head dim 64: the two-pipeline kernel.
+int launch_backward_rows_pipes(int dtype, bool masked, const CUtensorMap& q, const CUtensorMap& dout, const CUtensorMap& k,
+                               const CUtensorMap& v, BwdParams p, cudaStream_t stream) {
+    using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const BwdParams);
+    KernelFn kernel;
+    if (dtype == BSA_DTYPE_BF16) kernel = masked ? attention_backward_rows_pipes_kernel<true, true> : attention_backward_rows_pipes_kernel<true, false>;
+    else                         kernel = masked ? attention_backward_rows_pipes_kernel<false, true> : attention_backward_rows_pipes_kernel<false, false>;
+    // at least 80 KB, so that never more than two CTAs (256 TMEM columns each) share an SM
+    int smem_bytes = 1024 + 2 * kBwdRowTiles * kTileBytes + (int)sizeof(BwdRowBarriers);
+    if (smem_bytes < 80 * 1024) smem_bytes = 80 * 1024;
+    if (!ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem_bytes)) return BSA_ERR_LAUNCH;
+    const int sms = sm_count();
+    if (sms <= 0) return BSA_ERR_LAUNCH;
+    // walkers of the work-item list: the two pipelines of every CTA
+    const int wanted = (p.items + 1) / 2;
+    const unsigned grid = (unsigned)(wanted < 2 * sms ? wanted : 2 * sms);
+    p.stride_z = 2 * (int)grid / p.groups;
+    p.stride_rem = 2 * (int)grid % p.groups;
+    kernel<<<grid, 12 * 32, smem_bytes, stream>>>(q, dout, k, v, p);
+    return launch_status();
+}
+
 // One launch of the backward kernel template (by rows or by columns).
 template <bool COL>
 int launch_backward(int dtype, bool masked, const CUtensorMap& x1, const CUtensorMap& x2, const CUtensorMap& y1,
@@ -673,7 +697,8 @@ int attention_backward(int dtype, const void* q, const void* k, const void* v, c
     p.out1 = nullptr;
     int st = BSA_OK;
 #if !defined(BSA_BWD_ONLY) || BSA_BWD_ONLY == 0      // (timing builds run one of the two kernels)
-    st = launch_backward<false>(dtype, masked, map_q, map_do, map_k, map_v, p, stream);
+    st = head_dim == kTile ? launch_backward_rows_pipes(dtype, masked, map_q, map_do, map_k, map_v, p, stream)
+                           : launch_backward<false>(dtype, masked, map_q, map_do, map_k, map_v, p, stream);
     if (st != BSA_OK) return st;
 #endif
 #if defined(BSA_BWD_ONLY) && BSA_BWD_ONLY == 0

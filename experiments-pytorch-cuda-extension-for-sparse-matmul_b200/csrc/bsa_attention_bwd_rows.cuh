@@ -1,0 +1,351 @@
+// Fused attention backward, dQ by block rows, head dim 64: two independent pipelines per CTA.
+// Included by bsa_attention_bwd.cu inside its anonymous namespace (it uses BwdParams and the helpers
+// of bsa_tc_common.cuh).
+//
+// The same organisation as the forward kernel for head dim 64: a pipeline is a producer warp, an
+// issuer warp and a compute warpgroup with their own shared-memory tiles (X = (Q_r, dO_r), two stages
+// of Y = (K_c, V_c)), their own tensor-memory buffers and barriers, and walks its own block rows
+// (pipeline number = 2 * CTA + g of 2 * grid pipelines); two CTAs share an SM, so four block rows are
+// in flight per SM, each at its own point of its row.  (The general kernel lets two compute groups
+// share a row with alternate blocks, with in-order issuers and one producer for both: every
+// hand-over between the groups serialises the CTA.)
+//
+// Per block (r, c):  T1 = Q_r K_c^T = S,  T2 = dO_r V_c^T = dP  (both into tensor memory),
+//   dS = scale * exp2(c2 * S - lse2_r) o (dP - D_r)  packed to 16 bits into tensor memory,
+//   dQ_r += dS K_c  with the A operand (dS) read from tensor memory.
+// Tensor memory of a pipeline (128 columns; an M = 64 accumulator occupies lanes 0-15 of each
+// 32-lane quarter, a second one fits into lanes 16-31 of the same columns):
+//   columns   0 ..  63   lanes 0-15: dQ accumulator       lanes 16-31: T1
+//   columns  64 .. 127   lanes 0-15: dS buffers 0, 1 (32 columns each)   lanes 16-31: T2
+// (a TMEM A operand is used at lane offset 0 with its D at lane offset 0 only).
+//   warps 0, 2   producer of pipeline 0, 1: the row's X pair, then every block's Y pair (stage t & 1)
+//   warps 1, 3   issuer: T1 and T2 of block t, then the accumulation of block t - 1
+//   warps 4-7, 8-11   compute warpgroup; at the end of the row dQ goes to global memory.
+struct __align__(8) BwdRowBarriers {
+    uint64_t x_full[2], x_empty[2];             // [pipeline]
+    uint64_t y_full[2][2], acc_done[2][2];      // [pipeline][block & 1]: acc_done = the Y stage and the dS buffer are free
+    uint64_t t_full[2], t_empty[2];
+    uint64_t ds_full[2][2];
+    uint64_t o_full[2], o_empty[2];
+    uint64_t drain;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+constexpr int kBwdRowTiles = 6;                 // per pipeline: Q, dO, (K, V) x 2
+
+template <bool BF16, bool MASKED>
+__global__ void __launch_bounds__(12 * 32, 2)
+attention_backward_rows_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
+                                     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                                     const BwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    BwdRowBarriers* bars = reinterpret_cast<BwdRowBarriers*>(smem + 2 * kBwdRowTiles * kTileBytes);
+    int* abort_flag = &bars->abort_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = warp < 4 ? warp >> 1 : (warp - 4) >> 2;          // pipeline of this warp
+    uint8_t* x_smem = smem + g * kBwdRowTiles * kTileBytes;        // Q_r, dO_r
+    uint8_t* y_smem = x_smem + 2 * kTileBytes;                     // [stage][K_c, V_c]
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bars->x_full[i], 1); mbar_init(&bars->x_empty[i], 1);
+            mbar_init(&bars->t_full[i], 1); mbar_init(&bars->t_empty[i], 4);
+            for (int s = 0; s < 2; ++s) {
+                mbar_init(&bars->y_full[i][s], 1); mbar_init(&bars->acc_done[i][s], 1);
+                mbar_init(&bars->ds_full[i][s], 4);
+            }
+            mbar_init(&bars->o_full[i], 1); mbar_init(&bars->o_empty[i], 4);
+        }
+        mbar_init(&bars->drain, 2);
+        bars->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_shared();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&bars->tmem_base)), "r"(256u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *(volatile uint32_t*)&bars->tmem_base;
+    const uint32_t dq_tmem = tmem_base + (uint32_t)(g * 128);              // dQ: lanes 0-15 of columns 0 .. 63
+    const uint32_t t1_tmem = dq_tmem + (16u << 16);                        // T1: lanes 16-31 of columns 0 .. 63
+    const uint32_t t2_tmem = t1_tmem + 64u;                                // T2: lanes 16-31 of columns 64 .. 127
+    const uint32_t ds_tmem = dq_tmem + 64u;                                // dS buffer b: lanes 0-15 of columns 64 + 32 b ..
+    const int walker = 2 * (int)blockIdx.x + g, walkers = 2 * (int)gridDim.x;
+
+    if (warp == 0 || warp == 2) {
+        // ------------------------------------------------------------ producer
+        int t0 = 0, i_no = 0;                       // blocks and non-empty rows before the current row
+        bool ok = true;
+        Cursor cur;
+        cur.init_as(p, walker, walkers);
+        BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
+        while (ok && cur.valid()) {
+            BlockDesc pre_next{0, 0};
+            if (cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
+            const int n = cur.count;
+            if (n > 0) {
+                // the X pair once the last T products of the row before have retired
+                ok = __all_sync(0xffffffffu, mbar_wait(&bars->x_empty[g], ((uint32_t)i_no & 1u) ^ 1u, abort_flag, p.status)) != 0;
+                if (ok && elect_one()) {
+                    mbar_expect_tx(&bars->x_full[g], (uint32_t)(2 * kTileBytes));
+                    tma_load_3d(x_smem, &map_q, &bars->x_full[g], 0, cur.g * kTile, cur.z);
+                    tma_load_3d(x_smem + kTileBytes, &map_do, &bars->x_full[g], 0, cur.g * kTile, cur.z);
+                }
+                __syncwarp();
+                DescWindow win;
+                win.begin(p.blocks, cur.first, cur.count, pre, lane);
+                for (int j = 0; ok && j < n; ++j) {
+                    const int col = win.get(p.blocks, cur.first, cur.count, j, lane).col();
+                    const int t = t0 + j, st = t & 1;
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_done[g][st], ((uint32_t)(t >> 1) & 1u) ^ 1u, abort_flag, p.status)) != 0;
+                    if (ok && elect_one()) {
+                        mbar_expect_tx(&bars->y_full[g][st], (uint32_t)(2 * kTileBytes));
+                        tma_load_3d(y_smem + (2 * st) * kTileBytes, &map_k, &bars->y_full[g][st], 0, col * kTile, cur.z);
+                        tma_load_3d(y_smem + (2 * st + 1) * kTileBytes, &map_v, &bars->y_full[g][st], 0, col * kTile, cur.z);
+                    }
+                    __syncwarp();
+                }
+                t0 += n;
+                ++i_no;
+            }
+            pre = pre_next;
+            cur.advance();
+        }
+        if (lane == 0 && *(volatile int*)abort_flag) {
+            // Give copies that were issued a bounded chance to land before the CTA exits.
+            const unsigned long long tw = global_ns();
+            for (int s = 0; s < 2; ++s)
+                while (!mbar_try_wait(&bars->y_full[g][s], 0) && !mbar_try_wait(&bars->y_full[g][s], 1) &&
+                       global_ns() - tw < kWaitLimitNs / 4) {}
+            while (!mbar_try_wait(&bars->x_full[g], 0) && !mbar_try_wait(&bars->x_full[g], 1) &&
+                   global_ns() - tw < kWaitLimitNs / 4) {}
+        }
+        __syncwarp();
+    } else if (warp == 1 || warp == 3) {
+        // ------------------------------------------------------------ issuer
+        // Order: T1 and T2 of block t, then the accumulation of block t - 1 (kept pending across rows).  The
+        // events come in this order: T(t - 1) is in the compute warps' registers when they start on block
+        // t - 1, their dS(t - 1) is complete when they are done with it.
+        const uint64_t x1_desc = make_tile_desc(smem_u32(x_smem), false);
+        const uint64_t x2_desc = make_tile_desc(smem_u32(x_smem + kTileBytes), false);
+        int t0 = 0, i_no = 0;
+        bool ok = true;
+        bool pend = false, pend_first = false, pend_last = false;
+        int pend_t = 0, pend_i = 0;                 // the pending accumulation: block number, row number
+        auto issue_acc = [&]() -> bool {            // dQ (+)= dS K of the pending block
+            const int t = pend_t, b = t & 1;
+            // the accumulator is free once the row before has been read out
+            if (pend_first && pend_i > 0 &&
+                !__all_sync(0xffffffffu, mbar_wait(&bars->o_empty[g], (uint32_t)(pend_i - 1) & 1u, abort_flag, p.status)))
+                return false;
+            if (!__all_sync(0xffffffffu, mbar_wait(&bars->ds_full[g][b], (uint32_t)(t >> 1) & 1u, abort_flag, p.status))) return false;
+            tc_fence_after();
+            // A = dS in tensor memory, B = the K tile of the block's stage with N = head_dim contiguous
+            const uint64_t db = make_tile_desc(smem_u32(y_smem + (2 * b) * kTileBytes), true);
+            const uint32_t a = ds_tmem + (uint32_t)(32 * b);
+            if (elect_one()) {
+#pragma unroll
+                for (int kk = 0; kk < kTile / 16; ++kk)
+                    tc_mma_f16_ts(dq_tmem, a + (uint32_t)(8 * kk), db + (uint64_t)(kk * (2048 >> 4)), p.idesc_acc,
+                                  (!pend_first || kk > 0) ? 1u : 0u);
+                tc_commit(&bars->acc_done[g][b]);       // the Y stage and the dS buffer are free
+                if (pend_last) tc_commit(&bars->o_full[g]);
+            }
+            __syncwarp();
+            return true;
+        };
+        Cursor cur;
+        cur.init_as(p, walker, walkers);
+        for (; ok && cur.valid(); cur.advance()) {
+            const int n = cur.count;
+            if (n == 0) continue;                   // a row without blocks: the compute warps write zeros on their own
+            ok = __all_sync(0xffffffffu, mbar_wait(&bars->x_full[g], (uint32_t)i_no & 1u, abort_flag, p.status)) != 0;
+            for (int j = 0; ok && j < n; ++j) {
+                const int t = t0 + j, st = t & 1;
+                ok = __all_sync(0xffffffffu, mbar_wait(&bars->y_full[g][st], (uint32_t)(t >> 1) & 1u, abort_flag, p.status)) != 0;
+                if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->t_empty[g], ((uint32_t)t & 1u) ^ 1u, abort_flag, p.status)) != 0;
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t y1 = make_tile_desc(smem_u32(y_smem + (2 * st) * kTileBytes), false);
+                const uint64_t y2 = make_tile_desc(smem_u32(y_smem + (2 * st + 1) * kTileBytes), false);
+                if (elect_one()) {
+#pragma unroll
+                    for (int kk = 0; kk < kTile / 16; ++kk)
+                        tc_mma_f16(t1_tmem, x1_desc + (uint64_t)(kk * 2), y1 + (uint64_t)(kk * 2), p.idesc_t, kk > 0 ? 1u : 0u);
+#pragma unroll
+                    for (int kk = 0; kk < kTile / 16; ++kk)
+                        tc_mma_f16(t2_tmem, x2_desc + (uint64_t)(kk * 2), y2 + (uint64_t)(kk * 2), p.idesc_t, kk > 0 ? 1u : 0u);
+                    tc_commit(&bars->t_full[g]);
+                    if (j == n - 1) tc_commit(&bars->x_empty[g]);      // the last reads of the X pair
+                }
+                __syncwarp();
+                if (pend) ok = issue_acc();
+                pend = true; pend_t = t; pend_i = i_no; pend_first = j == 0; pend_last = j == n - 1;
+            }
+            t0 += n;
+            ++i_no;
+        }
+        if (ok && pend) issue_acc();
+        // All MMAs issued by the elected lane (the same one every time) must have retired before TMEM is freed.
+        if (elect_one()) {
+            tc_commit(&bars->drain);
+            mbar_wait(&bars->drain, 0, abort_flag, p.status);
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ compute warpgroup
+        const int quad = warp & 3;                  // TMEM sub-partition this warp may read
+        const int q4 = lane & 3;                    // position in the quad: columns 8u + 2 * q4 + {0, 1}
+        const int row_a = quad * 16 + (lane >> 2);  // this lane's two rows of the 64-row tile: row_a, row_a + 8
+        const uint32_t lane_field = (uint32_t)(quad * 32) << 16;
+        const bool masked_op = MASKED && (p.causal != 0 || p.kpm != nullptr || p.quadrants != 0);
+        const float c2 = p.scale_log2, sc = p.scale;
+        const uint64_t c2p = f2_pack(c2, c2), scp = f2_pack(sc, sc);
+        int t0 = 0, i_no = 0;
+        bool ok = true;
+        Cursor cur;
+        cur.init_as(p, walker, walkers);
+        BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
+        while (ok && cur.valid()) {
+            BlockDesc pre_next{0, 0};
+            if (cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
+            const int n = cur.count;
+            const size_t out_a = ((size_t)cur.z * p.seq_q + (size_t)cur.g * kTile + row_a) * kTile;
+            const size_t out_b = out_a + (size_t)8 * kTile;
+            if (n == 0) {
+                // a row without blocks: zero gradient rows
+                for (int c = q4 * 8; c < kTile; c += 32) {
+                    *reinterpret_cast<uint4*>(p.out0 + out_a + c) = make_uint4(0u, 0u, 0u, 0u);
+                    *reinterpret_cast<uint4*>(p.out0 + out_b + c) = make_uint4(0u, 0u, 0u, 0u);
+                }
+            } else {
+                const uint8_t* kpm_row = (MASKED && p.kpm) ? p.kpm + (size_t)(cur.z / p.kpm_div) * p.kpm_stride : nullptr;
+                const int pos_a = cur.g * kTile + row_a;         // query position of row a (row b: + 8)
+                const float2* stats_z = p.stats + (size_t)cur.z * p.seq_q;
+                const float2 st_a = stats_z[pos_a], st_b = stats_z[pos_a + 8];     // (lse in log2 units, D)
+                // per row: -lse2 for the exponent and -D * scale for dS = P * (dP * scale - D * scale)
+                const uint64_t nla = f2_pack(-st_a.x, -st_a.x), nlb = f2_pack(-st_b.x, -st_b.x);
+                const uint64_t nda = f2_pack(-st_a.y * sc, -st_a.y * sc), ndb = f2_pack(-st_b.y * sc, -st_b.y * sc);
+                DescWindow win;
+                win.begin(p.blocks, cur.first, cur.count, pre, lane);
+                for (int j = 0; ok && j < n; ++j) {
+                    const int t = t0 + j, b = t & 1;
+                    const BlockDesc d = win.get(p.blocks, cur.first, cur.count, j, lane);
+                    const int col = d.col();
+                    // Masked positions (bit 2u + e of the low half: row a, column 8u + 2 q4 + e; high half: row b):
+                    // above the diagonal, padded keys, quadrants outside a block-32 layout.  Computed before the
+                    // wait for the block's products: off the critical chain.
+                    uint32_t mask = 0u;
+                    if (MASKED && masked_op) {
+                        if (p.quadrants) {
+                            const uint32_t present = (uint32_t)d.idx >> (2 * (quad >> 1));
+                            if (!(present & 1u)) mask |= 0x00FF00FFu;
+                            if (!(present & 2u)) mask |= 0xFF00FF00u;
+                        }
+                        const int k0 = col * kTile + 2 * q4;
+                        if (p.causal && col * kTile + kTile - 1 > pos_a) {
+#pragma unroll
+                            for (int u = 0; u < 8; ++u)
+#pragma unroll
+                                for (int e = 0; e < 2; ++e) {
+                                    const int kpos = k0 + 8 * u + e;
+                                    if (kpos > pos_a) mask |= 1u << (2 * u + e);
+                                    if (kpos > pos_a + 8) mask |= 1u << (16 + 2 * u + e);
+                                }
+                        }
+                        if (kpm_row) {
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) {
+                                if (kpm_row[k0 + 8 * u]) mask |= 0x00010001u << (2 * u);
+                                if (kpm_row[k0 + 8 * u + 1]) mask |= 0x00010001u << (2 * u + 1);
+                            }
+                        }
+                    }
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->t_full[g], (uint32_t)t & 1u, abort_flag, p.status)) != 0;
+                    if (!ok) break;
+                    tc_fence_after();
+                    uint32_t r1[32], r2[32];
+                    tc_ld_16x256b_x8(t1_tmem + lane_field, r1);
+                    tc_ld_16x256b_x8(t2_tmem + lane_field, r2);
+                    tc_wait_ld();
+                    release_accumulator(&bars->t_empty[g], lane);       // T is in registers: the next block's products may run
+                    // Is the dS buffer free (accumulation of block t - 2 retired)?  Tested now, needed after the arithmetic.
+                    const bool ds_free = t < 2 || mbar_test(&bars->acc_done[g][b], ((uint32_t)(t >> 1) & 1u) ^ 1u);
+                    // w[2u + h]: columns 8u + 2 q4 + {0, 1} of row a (h = 0) / row b (h = 1): the register order of the
+                    // 16x128b store.  Per pair of columns: P = exp2(c2 * S - lse2), dS = P * (dP * scale - D * scale).
+                    uint32_t w[16];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const uint64_t e2 = f2_fma(f2_pack(__uint_as_float(r1[4 * u + 2 * h]), __uint_as_float(r1[4 * u + 2 * h + 1])),
+                                                       c2p, h ? nlb : nla);
+                            float e0, e1;
+                            f2_unpack(e2, e0, e1);
+                            e0 = attn_exp2(e0); e1 = attn_exp2(e1);
+                            if (MASKED && masked_op) {
+                                if ((mask >> (16 * h + 2 * u)) & 1u) e0 = 0.f;
+                                if ((mask >> (16 * h + 2 * u + 1)) & 1u) e1 = 0.f;
+                            }
+                            const uint64_t g2 = f2_fma(f2_pack(__uint_as_float(r2[4 * u + 2 * h]), __uint_as_float(r2[4 * u + 2 * h + 1])),
+                                                       scp, h ? ndb : nda);
+                            float d0, d1;
+                            f2_unpack(f2_mul(f2_pack(e0, e1), g2), d0, d1);
+                            w[2 * u + h] = pack2<BF16>(d0, d1);
+                        }
+                    }
+                    // the dS buffer must have been read by the MMAs that used it last (those of block t - 2)
+                    if (!__all_sync(0xffffffffu, ds_free) &&
+                        !__all_sync(0xffffffffu, mbar_wait(&bars->acc_done[g][b], ((uint32_t)(t >> 1) & 1u) ^ 1u, abort_flag, p.status))) { ok = false; break; }
+                    tc_fence_after();
+                    tc_st_16x128b_x8(ds_tmem + lane_field + (uint32_t)(32 * b), w);
+                    tc_wait_st();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars->ds_full[g][b]);
+                }
+                t0 += n;
+                if (!ok) break;
+                // ---- end of the row: dQ to global memory
+                ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[g], (uint32_t)i_no & 1u, abort_flag, p.status)) != 0;
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t acc[2][16];
+                tc_ld_16x256b_x4(dq_tmem + lane_field, acc[0]);
+                tc_ld_16x256b_x4(dq_tmem + lane_field + 32u, acc[1]);
+                tc_wait_ld();
+                release_accumulator(&bars->o_empty[g], lane);          // the next row's accumulation may overwrite dQ
+#pragma unroll
+                for (int hc = 0; hc < 2; ++hc) {
+                    uint32_t ta[4], tb[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        ta[u] = pack2<BF16>(__uint_as_float(acc[hc][4 * u]), __uint_as_float(acc[hc][4 * u + 1]));
+                        tb[u] = pack2<BF16>(__uint_as_float(acc[hc][4 * u + 2]), __uint_as_float(acc[hc][4 * u + 3]));
+                    }
+                    quad_transpose(ta, q4);         // now columns 32 hc + 8 * q4 .. + 7 of the row
+                    quad_transpose(tb, q4);
+                    *reinterpret_cast<uint4*>(p.out0 + out_a + 32 * hc + 8 * q4) = make_uint4(ta[0], ta[1], ta[2], ta[3]);
+                    *reinterpret_cast<uint4*>(p.out0 + out_b + 32 * hc + 8 * q4) = make_uint4(tb[0], tb[1], tb[2], tb[3]);
+                }
+                ++i_no;
+            }
+            pre = pre_next;
+            cur.advance();
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
+    }
+}

@@ -597,6 +597,28 @@ int launch_backward_rows_pipes(int dtype, bool masked, const CUtensorMap& q, con
     return launch_status();
 }
 
+#include "bsa_attention_bwd_cols.cuh"
+
+// dK, dV by block columns with head dim 64: the two-pipeline kernel (one CTA per SM).
+int launch_backward_cols_pipes(int dtype, bool masked, const CUtensorMap& k, const CUtensorMap& v, const CUtensorMap& q,
+                               const CUtensorMap& dout, BwdParams p, cudaStream_t stream) {
+    using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const BwdParams);
+    KernelFn kernel;
+    if (dtype == BSA_DTYPE_BF16) kernel = masked ? attention_backward_cols_pipes_kernel<true, true> : attention_backward_cols_pipes_kernel<true, false>;
+    else                         kernel = masked ? attention_backward_cols_pipes_kernel<false, true> : attention_backward_cols_pipes_kernel<false, false>;
+    const int smem_bytes = 1024 + 2 * kBwdColTiles * kTileBytes + 2 * kBwdColRing * kBwdStatBytes + (int)sizeof(BwdColBarriers);
+    if (!ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem_bytes)) return BSA_ERR_LAUNCH;
+    const int sms = sm_count();
+    if (sms <= 0) return BSA_ERR_LAUNCH;
+    // walkers of the work-item list: the two pipelines of every CTA
+    const int wanted = (p.items + 1) / 2;
+    const unsigned grid = (unsigned)(wanted < sms ? wanted : sms);
+    p.stride_z = 2 * (int)grid / p.groups;
+    p.stride_rem = 2 * (int)grid % p.groups;
+    kernel<<<grid, kBwdColWarps * 32, smem_bytes, stream>>>(k, v, q, dout, p);
+    return launch_status();
+}
+
 // One launch of the backward kernel template (by rows or by columns).
 template <bool COL>
 int launch_backward(int dtype, bool masked, const CUtensorMap& x1, const CUtensorMap& x2, const CUtensorMap& y1,
@@ -711,7 +733,8 @@ int attention_backward(int dtype, const void* q, const void* k, const void* v, c
     p.items = (int)(batches * block_cols);
     p.out0 = static_cast<uint16_t*>(dv);
     p.out1 = static_cast<uint16_t*>(dk);
-    return launch_backward<true>(dtype, masked, map_k, map_v, map_q, map_do, p, stream);
+    return head_dim == kTile ? launch_backward_cols_pipes(dtype, masked, map_k, map_v, map_q, map_do, p, stream)
+                             : launch_backward<true>(dtype, masked, map_k, map_v, map_q, map_do, p, stream);
 }
 
 }  // namespace bsa

@@ -15,11 +15,13 @@
 //   lanes 16-31:  T1 buffer b at columns 128 b .. + 63, T2 buffer b at 128 b + 64 .. + 127
 // so T is double buffered (the products of block t + 1 run while block t is worked on) and so are the
 // operand buffers.  (A TMEM A operand is used at lane offset 0 with its D at lane offset 0 only.)
-//   warps 0-3, 4-7   compute warpgroup of pipeline 0, 1 (a warp reads the TMEM quarter warp % 4)
-//   warps 8, 11      producer: the column's X pair (K_c, V_c), then per block the Y pair (Q_r, dO_r) and the 512 bytes of
+//   warps 0-7, 8-15  compute warps of pipeline 0, 1: warp w works on the TMEM quarter w % 4 (16 key rows) and on the
+//                    query columns 32 * ((w / 4) % 2) .. + 31 of every block (the backward has no reduction along a row,
+//                    so the columns of a block split freely over two warps: twice the warps on a block's arithmetic)
+//   warps 16, 19     producer: the column's X pair (K_c, V_c), then per block the Y pair (Q_r, dO_r) and the 512 bytes of
 //                    (lse2, D) of its query rows (four stages)
-//   warps 9, 12      issuer of T1 and T2
-//   warps 10, 13     issuer of the two accumulations
+//   warps 17, 20     issuer of T1 and T2
+//   warps 18, 21     issuer of the two accumulations
 struct __align__(8) BwdColBarriers {
     uint64_t x_full[2], x_empty[2];             // [pipeline]
     uint64_t y_full[2][4], y_free[2][4];        // [pipeline][block & 3]: y_free = the accumulations of the block have retired
@@ -32,7 +34,7 @@ struct __align__(8) BwdColBarriers {
 };
 constexpr int kBwdColRing = 4;
 constexpr int kBwdColTiles = 2 + 2 * kBwdColRing;       // per pipeline: K, V, (Q, dO) x 4
-constexpr int kBwdColWarps = 14;
+constexpr int kBwdColWarps = 22;
 
 template <bool BF16, bool MASKED>
 __global__ void __launch_bounds__(kBwdColWarps * 32, 1)
@@ -45,8 +47,8 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
     BwdColBarriers* bars = reinterpret_cast<BwdColBarriers*>(stats_smem + 2 * kBwdColRing * kBwdStatBytes);
     int* abort_flag = &bars->abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int g = warp < 8 ? warp >> 2 : (warp - 8) / 3;           // pipeline of this warp
-    const int role = warp < 8 ? 3 : (warp - 8) % 3;                // 0 producer, 1 T issuer, 2 accumulation issuer, 3 compute
+    const int g = warp < 16 ? warp >> 3 : (warp - 16) / 3;         // pipeline of this warp
+    const int role = warp < 16 ? 3 : (warp - 16) % 3;              // 0 producer, 1 T issuer, 2 accumulation issuer, 3 compute
     uint8_t* x_smem = smem + g * kBwdColTiles * kTileBytes;        // K_c, V_c
     uint8_t* y_smem = x_smem + 2 * kTileBytes;                     // [stage][Q_r, dO_r]
     uint8_t* st_smem = stats_smem + g * kBwdColRing * kBwdStatBytes;
@@ -56,17 +58,17 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
             mbar_init(&bars->x_full[i], 1); mbar_init(&bars->x_empty[i], 1);
             for (int s = 0; s < kBwdColRing; ++s) { mbar_init(&bars->y_full[i][s], 1); mbar_init(&bars->y_free[i][s], 1); }
             for (int s = 0; s < 2; ++s) {
-                mbar_init(&bars->t_full[i][s], 1); mbar_init(&bars->t_empty[i][s], 4);
-                mbar_init(&bars->op_full[i][s], 4); mbar_init(&bars->op_free[i][s], 1);
+                mbar_init(&bars->t_full[i][s], 1); mbar_init(&bars->t_empty[i][s], 8);
+                mbar_init(&bars->op_full[i][s], 8); mbar_init(&bars->op_free[i][s], 1);
             }
-            mbar_init(&bars->o_full[i], 1); mbar_init(&bars->o_empty[i], 4);
+            mbar_init(&bars->o_full[i], 1); mbar_init(&bars->o_empty[i], 8);
         }
         mbar_init(&bars->drain, 4);
         bars->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_shared();
     }
-    if (warp == 8) {
+    if (warp == 16) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(smem_u32(&bars->tmem_base)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -221,7 +223,8 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
     } else {
         // ------------------------------------------------------------ compute warpgroup
         const int quad = warp & 3;                  // TMEM sub-partition this warp may read
-        const int q4 = lane & 3;                    // position in the quad: columns 8u + 2 * q4 + {0, 1}
+        const int half = (warp >> 2) & 1;           // this warp's half of a block's query columns: 32 * half .. + 31
+        const int q4 = lane & 3;                    // position in the quad: columns 32 * half + 8u + 2 * q4 + {0, 1}, u < 4
         const int row_a = quad * 16 + (lane >> 2);  // this lane's two rows (keys) of the 64-row tile: row_a, row_a + 8
         const uint32_t lane_field = (uint32_t)(quad * 32) << 16;
         const bool masked_op = MASKED && (p.causal != 0 || p.kpm != nullptr || p.quadrants != 0);
@@ -240,7 +243,8 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
             const size_t out_b = out_a + (size_t)8 * kTile;
             if (n == 0) {
                 // a column without blocks: zero gradient rows
-                for (int c = q4 * 8; c < kTile; c += 32) {
+                {
+                    const int c = 32 * half + q4 * 8;
                     *reinterpret_cast<uint4*>(p.out0 + out_a + c) = make_uint4(0u, 0u, 0u, 0u);
                     *reinterpret_cast<uint4*>(p.out0 + out_b + c) = make_uint4(0u, 0u, 0u, 0u);
                     *reinterpret_cast<uint4*>(p.out1 + out_a + c) = make_uint4(0u, 0u, 0u, 0u);
@@ -257,28 +261,23 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
                 for (int j = 0; ok && j < n; ++j) {
                     const int t = t0 + j, st = t & (kBwdColRing - 1), b = t & 1;
                     const BlockDesc d = win.get(p.blocks, cur.first, cur.count, j, lane);
-                    const int q0 = d.row() * kTile + 2 * q4;            // query position of column u = 0, e = 0
-                    // Masked positions (bit 2u + e of the low half: row a, column 8u + 2 q4 + e; high half: row b):
+                    const int q0 = d.row() * kTile + 32 * half + 2 * q4;        // query position of column u = 0, e = 0
+                    // Masked positions (bit 2u + e of the low byte: row a, column 32 half + 8u + 2 q4 + e; bits 8-15: row b):
                     // padded key rows, queries before the key (causal), quadrants outside a block-32 layout (the lane's
-                    // rows are keys: column half quad / 2; u / 4 is the query (row) half).
+                    // rows are keys: column half quad / 2; the warp's query columns lie in the row half `half`).
                     uint32_t mask = 0u;
                     if (MASKED && masked_op) {
-                        if (p.quadrants) {
-                            const uint32_t bits = (uint32_t)d.idx;
-                            const int h = quad >> 1;
-                            if (!((bits >> h) & 1u)) mask |= 0x00FF00FFu;
-                            if (!((bits >> (2 + h)) & 1u)) mask |= 0xFF00FF00u;
-                        }
-                        if (pad_a) mask |= 0x0000FFFFu;
-                        if (pad_b) mask |= 0xFFFF0000u;
-                        if (p.causal && pos_a + 8 > d.row() * kTile) {
+                        if (p.quadrants && !(((uint32_t)d.idx >> (2 * half + (quad >> 1))) & 1u)) mask = 0xFFFFu;
+                        if (pad_a) mask |= 0x00FFu;
+                        if (pad_b) mask |= 0xFF00u;
+                        if (p.causal && pos_a + 8 > d.row() * kTile + 32 * half) {
 #pragma unroll
-                            for (int u = 0; u < 8; ++u)
+                            for (int u = 0; u < 4; ++u)
 #pragma unroll
                                 for (int e = 0; e < 2; ++e) {
                                     const int qpos = q0 + 8 * u + e;
                                     if (pos_a > qpos) mask |= 1u << (2 * u + e);
-                                    if (pos_a + 8 > qpos) mask |= 1u << (16 + 2 * u + e);
+                                    if (pos_a + 8 > qpos) mask |= 1u << (8 + 2 * u + e);
                                 }
                         }
                     }
@@ -287,26 +286,26 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
                     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->y_full[g][st], (uint32_t)(t >> 2) & 1u, abort_flag, p.status)) != 0;
                     if (!ok) break;
                     tc_fence_after();
-                    uint32_t r1[32], r2[32];
-                    tc_ld_16x256b_x8(t_tmem + lane_field + (uint32_t)(128 * b), r1);
-                    tc_ld_16x256b_x8(t_tmem + lane_field + (uint32_t)(128 * b + 64), r2);
+                    uint32_t r1[16], r2[16];
+                    tc_ld_16x256b_x4(t_tmem + lane_field + (uint32_t)(128 * b + 32 * half), r1);
+                    tc_ld_16x256b_x4(t_tmem + lane_field + (uint32_t)(128 * b + 64 + 32 * half), r2);
                     // (lse2, D) of this lane's 16 query columns, brought into the block's stage by the producer:
-                    // cs[u] = those of columns 8u + 2 q4 and + 1
-                    float4 cs[8];
+                    // cs[u] = those of columns 32 half + 8u + 2 q4 and + 1
+                    float4 cs[4];
                     {
-                        const float4* src = reinterpret_cast<const float4*>(st_smem + st * kBwdStatBytes) + q4;
+                        const float4* src = reinterpret_cast<const float4*>(st_smem + st * kBwdStatBytes) + 16 * half + q4;
 #pragma unroll
-                        for (int u = 0; u < 8; ++u) cs[u] = src[4 * u];        // 8 columns = 4 float4 apart
+                        for (int u = 0; u < 4; ++u) cs[u] = src[4 * u];        // 8 columns = 4 float4 apart
                     }
                     tc_wait_ld();
                     release_accumulator(&bars->t_empty[g][b], lane);    // T is in registers: its buffer may be overwritten
                     // Are the operand buffers free (accumulations of block t - 2 retired)?  Tested now, needed later.
                     const bool op_free = t < 2 || mbar_test(&bars->op_free[g][b], ((uint32_t)(t >> 1) & 1u) ^ 1u);
-                    // wp / wd [2u + h]: columns 8u + 2 q4 + {0, 1} of row a (h = 0) / row b (h = 1) of P^T / dS^T: the
-                    // register order of the 16x128b store
-                    uint32_t wp[16], wd[16];
+                    // wp / wd [2u + h]: columns 32 half + 8u + 2 q4 + {0, 1} of row a (h = 0) / row b (h = 1) of P^T / dS^T:
+                    // the register order of the 16x128b store
+                    uint32_t wp[8], wd[8];
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) {
+                    for (int u = 0; u < 4; ++u) {
                         const uint64_t nl = f2_pack(-cs[u].x, -cs[u].z);                 // -lse2 of the two columns
                         const uint64_t nd = f2_pack(-cs[u].y * sc, -cs[u].w * sc);       // -D * scale
 #pragma unroll
@@ -316,8 +315,8 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
                             f2_unpack(e2, e0, e1);
                             e0 = attn_exp2(e0); e1 = attn_exp2(e1);
                             if (MASKED && masked_op) {
-                                if ((mask >> (16 * h + 2 * u)) & 1u) e0 = 0.f;
-                                if ((mask >> (16 * h + 2 * u + 1)) & 1u) e1 = 0.f;
+                                if ((mask >> (8 * h + 2 * u)) & 1u) e0 = 0.f;
+                                if ((mask >> (8 * h + 2 * u + 1)) & 1u) e1 = 0.f;
                             }
                             const uint64_t g2 = f2_fma(f2_pack(__uint_as_float(r2[4 * u + 2 * h]), __uint_as_float(r2[4 * u + 2 * h + 1])), scp, nd);
                             float d0, d1;
@@ -330,8 +329,8 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
                     if (!__all_sync(0xffffffffu, op_free) &&
                         !__all_sync(0xffffffffu, mbar_wait(&bars->op_free[g][b], ((uint32_t)(t >> 1) & 1u) ^ 1u, abort_flag, p.status))) { ok = false; break; }
                     tc_fence_after();
-                    tc_st_16x128b_x8(pt_tmem + lane_field + (uint32_t)(32 * b), wp);
-                    tc_st_16x128b_x8(ds_tmem + lane_field + (uint32_t)(32 * b), wd);
+                    tc_st_16x128b_x4(pt_tmem + lane_field + (uint32_t)(32 * b + 16 * half), wp);
+                    tc_st_16x128b_x4(ds_tmem + lane_field + (uint32_t)(32 * b + 16 * half), wd);
                     tc_wait_st();
                     tc_fence_before();
                     __syncwarp();
@@ -343,27 +342,25 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
                 ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[g], (uint32_t)i_no & 1u, abort_flag, p.status)) != 0;
                 if (!ok) break;
                 tc_fence_after();
+                uint32_t av[16], ak[16];            // this warp's 32 head-dim columns of dV and dK
+                tc_ld_16x256b_x4(dv_tmem + lane_field + (uint32_t)(32 * half), av);
+                tc_ld_16x256b_x4(dk_tmem + lane_field + (uint32_t)(32 * half), ak);
+                tc_wait_ld();
+                release_accumulator(&bars->o_empty[g], lane);          // the next column may overwrite the accumulators
 #pragma unroll
                 for (int a = 0; a < 2; ++a) {
                     uint16_t* out = a == 0 ? p.out0 : p.out1;
-                    uint32_t acc[2][16];
-                    tc_ld_16x256b_x4((a == 0 ? dv_tmem : dk_tmem) + lane_field, acc[0]);
-                    tc_ld_16x256b_x4((a == 0 ? dv_tmem : dk_tmem) + lane_field + 32u, acc[1]);
-                    tc_wait_ld();
-                    if (a == 1) release_accumulator(&bars->o_empty[g], lane);      // the next column may overwrite the accumulators
+                    const uint32_t (&acc)[16] = a == 0 ? av : ak;
+                    uint32_t ta[4], tb[4];
 #pragma unroll
-                    for (int hc = 0; hc < 2; ++hc) {
-                        uint32_t ta[4], tb[4];
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            ta[u] = pack2<BF16>(__uint_as_float(acc[hc][4 * u]), __uint_as_float(acc[hc][4 * u + 1]));
-                            tb[u] = pack2<BF16>(__uint_as_float(acc[hc][4 * u + 2]), __uint_as_float(acc[hc][4 * u + 3]));
-                        }
-                        quad_transpose(ta, q4);         // now columns 32 hc + 8 * q4 .. + 7 of the row
-                        quad_transpose(tb, q4);
-                        *reinterpret_cast<uint4*>(out + out_a + 32 * hc + 8 * q4) = make_uint4(ta[0], ta[1], ta[2], ta[3]);
-                        *reinterpret_cast<uint4*>(out + out_b + 32 * hc + 8 * q4) = make_uint4(tb[0], tb[1], tb[2], tb[3]);
+                    for (int u = 0; u < 4; ++u) {
+                        ta[u] = pack2<BF16>(__uint_as_float(acc[4 * u]), __uint_as_float(acc[4 * u + 1]));
+                        tb[u] = pack2<BF16>(__uint_as_float(acc[4 * u + 2]), __uint_as_float(acc[4 * u + 3]));
                     }
+                    quad_transpose(ta, q4);         // now columns 32 half + 8 * q4 .. + 7 of the row
+                    quad_transpose(tb, q4);
+                    *reinterpret_cast<uint4*>(out + out_a + 32 * half + 8 * q4) = make_uint4(ta[0], ta[1], ta[2], ta[3]);
+                    *reinterpret_cast<uint4*>(out + out_b + 32 * half + 8 * q4) = make_uint4(tb[0], tb[1], tb[2], tb[3]);
                 }
                 ++i_no;
             }
@@ -375,7 +372,7 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
     // ---------------------------------------------------------------- teardown
     tc_fence_before();
     __syncthreads();
-    if (warp == 8) {
+    if (warp == 16) {
         __syncwarp();
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");

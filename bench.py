@@ -554,7 +554,7 @@ def run_ours(args):
                         "note": "forward only, outside the timed step; Q, K, V read and O written once, "
                                 "scores and probabilities never leave the SM"}
         fused_step_ms = fused_ms + fused_bwd_ms
-        fused_step_report = {"kernels": "attention_forward_pipes_kernel + attention_backward_kernel<rows> + <columns> (+ statistics)",
+        fused_step_report = {"kernels": "attention_forward_pipes_kernel + attention_backward_rows_pipes_kernel + attention_backward_cols_pipes_kernel (+ statistics)",
                              "forward_ms": round(fused_ms, 4), "backward_ms": round(fused_bwd_ms, 4),
                              "ms": round(fused_step_ms, 4),
                              "TFLOP/s": round(6 * flops_matmul / (fused_step_ms * 1e-3) / 1e12, 1),

@@ -17,28 +17,24 @@
 // of similar size it happens in a row's first blocks only).  The result does not depend on when m
 // is raised: O and l carry the same factor.
 //
-// A thread issues a tcgen05.mma, a commit or a TMA copy only every ~100 cycles whatever its size
-// (twice that from a diverged lane: the role loops run warp-uniformly and elect a lane only around
-// the instructions), so producing and issuing are spread over four warps.  A CTA has 256 TMEM
-// columns; two CTAs share an SM and overlap each other's prologues and epilogues:
-//   warp 0     TMA producer of Q (double buffered with head dim 64: the next item's tile set is
-//              requested an item ahead) and of every block's K tiles
+// Two kernels: head dim 64 runs as two independent pipelines per CTA (second half of this file);
+// head dim 128 (one O accumulator fits into a CTA's 256 TMEM columns beside two S buffers) runs the
+// kernel below.  A thread issues a tcgen05.mma, a commit or a TMA copy only every ~60-100 cycles
+// whatever its size (twice that from a diverged lane: the role loops run warp-uniformly and elect a
+// lane only around the instructions), so producing and issuing are spread over four warps; two
+// CTAs share an SM and overlap each other's prologues and epilogues:
+//   warp 0     TMA producer of Q and of every block's K tiles
 //   warp 1     Q K^T issuer: S is double buffered, so Q K^T of block j + 1 runs while the softmax
 //              warps work on block j; one commit per block signals both "S is ready" and "the K
 //              stage is free"
 //   warp 2     TMA producer of the V tiles (a K stage is free long before the block's P V: one
 //              in-order producer would stretch every loop by a TMA latency)
 //   warp 3     P V issuer; one commit per block signals "the P buffer and the V stage are free"
-//   warps 4-   softmax warpgroups: tcgen05.ld with the 16x256b shape (every lane owns 2 rows x 16
-//              columns of a 64 x 64 block), masks, max / exp / sum, pack, 32-bit stores into the
-//              128-byte-swizzled P tile (32 lanes on 32 banks); at the end of a row O goes through
-//              4x4 quad transposes and 128-bit stores to global memory.
-//              Head dim 64: two warpgroups (12 warps) take alternate blocks, each with its own
-//              running maxima, sums and O accumulator; the groups finish alternate rows: merge
-//              the two accumulators (the partial softmaxes over disjoint key sets combine
-//              exactly) and write the row while the other group starts the next row.
-//              Head dim 128 (one accumulator fits): one warpgroup (8 warps) with two register
-//              buffers, the TMEM load of block j + 1 in flight while block j is worked on.
+//   warps 4-7  softmax warpgroup: tcgen05.ld with the 16x256b shape (every lane owns 2 rows x 16
+//              columns of a 64 x 64 block), masks, max / exp / sum, pack, stmatrix into the
+//              128-byte-swizzled P tile; two register buffers, the TMEM load of block j + 1 in flight
+//              while block j is worked on; at the end of a row O goes through 4x4 quad transposes
+//              and 128-bit stores to global memory.
 // All waits are bounded (BSA_ERR_DEVICE_TIMEOUT in the workspace word).
 #include "bsa_tc_common.cuh"
 
@@ -51,20 +47,17 @@ constexpr int kMaxRing = 4;
 
 struct __align__(8) AttnBarriers {
     uint64_t q_full[2];
-    uint64_t q_empty[2][2];         // [issuer group][buffer]: that group's last Q K^T of the item has retired
+    uint64_t q_empty[2];            // the last Q K^T of the item that used the buffer has retired
     uint64_t k_full[kMaxRing];
     uint64_t qk_done[kMaxRing];     // the MMAs of one Q K^T have retired: S is ready and the K stage is free
     uint64_t v_full[kMaxRing];
     uint64_t pv_done[kMaxRing];     // the MMAs of one P V have retired: the P buffer and the V stage are free
     uint64_t s_empty[2];
     uint64_t p_full[2];
-    uint64_t o_full[2][2];          // [issuer group][parity of the item]: that group's last P V of the item has retired
-    uint64_t o_empty[2];            // indexed by the parity of the item: arrived on by the group that finishes the item
-    uint64_t stat_full[2][2], stat_empty[2][2];   // two softmax groups: hand-over of row maxima and sums, [writer][slot]
+    uint64_t o_full[2], o_empty[2]; // indexed by the parity of the item
     uint64_t drain;
     uint32_t tmem_base;
     int abort_flag;
-    float stat[2][2][kTile][2];
 };
 
 struct AttnParams {
@@ -91,8 +84,8 @@ struct AttnParams {
     uint32_t idesc_qk, idesc_pv;
 };
 
-template <bool BF16, bool MASKED, int WGS>
-__global__ void __launch_bounds__((4 + 4 * WGS) * 32, 2)
+template <bool BF16, bool MASKED>
+__global__ void __launch_bounds__(8 * 32, 2)
 attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -111,18 +104,14 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&bars->q_full[s], 1); mbar_init(&bars->p_full[s], 4);
-            for (int g = 0; g < 2; ++g) { mbar_init(&bars->q_empty[g][s], 1); mbar_init(&bars->o_full[g][s], 1); }
+            mbar_init(&bars->q_full[s], 1); mbar_init(&bars->q_empty[s], 1); mbar_init(&bars->p_full[s], 4);
+            mbar_init(&bars->s_empty[s], 4);
+            mbar_init(&bars->o_full[s], 1); mbar_init(&bars->o_empty[s], 4);
         }
         for (int s = 0; s < kMaxRing; ++s) {
             mbar_init(&bars->k_full[s], 1); mbar_init(&bars->qk_done[s], 1);
             mbar_init(&bars->v_full[s], 1); mbar_init(&bars->pv_done[s], 1);
         }
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(&bars->s_empty[s], 4);
-            for (int d = 0; d < 2; ++d) { mbar_init(&bars->stat_full[d][s], 4); mbar_init(&bars->stat_empty[d][s], 4); }
-        }
-        for (int s = 0; s < 2; ++s) mbar_init(&bars->o_empty[s], 4);
         mbar_init(&bars->drain, 2);
         bars->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -161,8 +150,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 auto issue_q = [&](int q, int z, int g) -> bool {        // called by the whole warp
                     const int qb = q & (p.qbufs - 1);
                     const uint32_t use = (uint32_t)(p.qbufs == 2 ? q >> 1 : q);
-                    if (!__all_sync(0xffffffffu, mbar_wait(&bars->q_empty[0][qb], (use & 1u) ^ 1u, abort_flag, p.status))) return false;
-                    if (WGS == 2 && !__all_sync(0xffffffffu, mbar_wait(&bars->q_empty[1][qb], (use & 1u) ^ 1u, abort_flag, p.status))) return false;
+                    if (!__all_sync(0xffffffffu, mbar_wait(&bars->q_empty[qb], (use & 1u) ^ 1u, abort_flag, p.status))) return false;
                     if (elect_one()) {
                         mbar_expect_tx(&bars->q_full[qb], (uint32_t)set_bytes);
                         for (int t = 0; t < p.dtiles; ++t)
@@ -219,96 +207,8 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                        global_ns() - t0 < kWaitLimitNs / 4) {}
         }
         __syncwarp();
-    } else if (WGS == 2 && (warp == 1 || warp == 3)) {
-        // ------------------------------------------------------------ issuer of one softmax group (head dim 64)
-        // Group g = warp / 2 owns the S tiles with number s & 1 == g: S buffer g, P buffer g, O accumulator g,
-        // K / V stages with s & 1 == g.  One warp issues both products of its group, so the two groups never wait
-        // behind each other's MMAs (a thread issues a 64 x 64 x 16 MMA only every 60 cycles or so, one in-order
-        // issuer for both groups was the longest chain of the kernel).  Order: Q K^T of tile t, then P V of the
-        // group's previous tile (kept pending across item borders): S of the next tile is being computed while
-        // the softmax warps work on this one, and their P is consumed as soon as the next Q K^T is out.
-        const int g = warp >> 1;
-        int s_no = 0, q_no = 0;                     // S tiles and non-empty items before the current item
-        bool ok = true;
-        bool pend = false, pend_first = false, pend_last = false;
-        int pend_s = 0, pend_o = 0;                 // the pending P V: tile number, item number
-        const uint32_t idesc_qk = p.idesc_qk, idesc_pv = p.idesc_pv;
-        const uint64_t q_desc = make_tile_desc(smem_u32(q_smem), false), k_desc = make_tile_desc(smem_u32(k_smem), false);
-        const uint64_t p_desc = make_tile_desc(smem_u32(p_smem + g * kTileBytes), false);
-        const uint64_t v_desc = make_tile_desc(smem_u32(v_smem), true);
-        const uint32_t d_s = tmem_base + (uint32_t)(kSCol0 + g * kTile), d_o = tmem_base + (uint32_t)(g * p.head_dim);
-        auto issue_pv = [&]() -> bool {             // O_g (+)= P V of the pending tile
-            const int s = pend_s, vs = s & vring_mask;
-            // the accumulators are free once the item before has been read out
-            if (pend_first && pend_o > 0 &&
-                !__all_sync(0xffffffffu, mbar_wait(&bars->o_empty[(pend_o - 1) & 1], (uint32_t)((pend_o - 1) >> 1) & 1u, abort_flag, p.status)))
-                return false;
-            if (!__all_sync(0xffffffffu, mbar_wait(&bars->v_full[vs], (uint32_t)(s >> p.vring_shift) & 1u, abort_flag, p.status))) return false;
-            if (!__all_sync(0xffffffffu, mbar_wait(&bars->p_full[g], (uint32_t)(s >> 1) & 1u, abort_flag, p.status))) return false;
-            tc_fence_after();
-            const uint64_t db = v_desc + (uint64_t)((vs * kTileBytes) >> 4);
-            if (elect_one()) {
-#pragma unroll
-                for (int kk = 0; kk < kTile / 16; ++kk)
-                    tc_mma_f16(d_o, p_desc + (uint64_t)(kk * 2), db + (uint64_t)(kk * (2048 >> 4)), idesc_pv, (!pend_first || kk > 0) ? 1u : 0u);
-                tc_commit(&bars->pv_done[vs]);
-                if (pend_last) tc_commit(&bars->o_full[g][pend_o & 1]);
-            }
-            __syncwarp();
-            return true;
-        };
-        Cursor cur;
-        cur.init(p);
-        for (; ok && cur.valid(); cur.advance()) {
-            const int n = cur.count;
-            if (n == 0) continue;                   // empty row: the softmax warps write zeros on their own
-            const int qb = q_no & 1;
-            ok = __all_sync(0xffffffffu, mbar_wait(&bars->q_full[qb], (uint32_t)(q_no >> 1) & 1u, abort_flag, p.status)) != 0;
-            if (!ok) break;
-            const int t_first = (g - s_no) & 1;     // this group's first tile of the item
-            if (t_first >= n) {
-                // A row of one block that belongs to the other group.  This group still arrives on its barriers
-                // once per item, in item order (never two phases ahead of their waiters: the wait for the item
-                // before to have been read out comes first, and that needs this group's pending P V).
-                if (pend) { ok = issue_pv(); pend = false; if (!ok) break; }
-                if (q_no > 0) ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_empty[(q_no - 1) & 1], (uint32_t)((q_no - 1) >> 1) & 1u, abort_flag, p.status)) != 0;
-                if (!ok) break;
-                if (elect_one()) { mbar_arrive(&bars->q_empty[g][qb]); mbar_arrive(&bars->o_full[g][q_no & 1]); }
-                __syncwarp();
-            } else {
-                const uint64_t da = q_desc + (uint64_t)((qb * kTileBytes) >> 4);
-                for (int t = t_first; ok && t < n; t += 2) {
-                    const int s = s_no + t, ks = s & ring_mask;
-                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->k_full[ks], (uint32_t)(s >> p.ring_shift) & 1u, abort_flag, p.status)) != 0;
-                    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_empty[g], ((uint32_t)(s >> 1) & 1u) ^ 1u, abort_flag, p.status)) != 0;
-                    if (!ok) break;
-                    tc_fence_after();
-                    const uint64_t db = k_desc + (uint64_t)((ks * kTileBytes) >> 4);
-                    if (elect_one()) {
-#pragma unroll
-                        for (int kk = 0; kk < kTile / 16; ++kk)
-                            tc_mma_f16(d_s, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc_qk, kk > 0 ? 1u : 0u);
-                        tc_commit(&bars->qk_done[ks]);
-                        if (t + 2 >= n) tc_commit(&bars->q_empty[g][qb]);    // this group's last read of the Q buffer
-                    }
-                    __syncwarp();
-                    if (pend) ok = issue_pv();
-                    pend = true; pend_s = s; pend_o = q_no; pend_first = t == t_first; pend_last = t + 2 >= n;
-                }
-            }
-            s_no += n;
-            ++q_no;
-        }
-        if (ok && pend) issue_pv();
-        // All MMAs issued by the elected lane (the same one every time: the election is deterministic
-        // for a converged warp) must have retired before TMEM is freed.
-        if (elect_one()) {
-            tc_commit(&bars->drain);
-            mbar_wait(&bars->drain, 0, abort_flag, p.status);
-        }
-        __syncwarp();
-    } else if (WGS == 1 && warp == 1) {
-        // ------------------------------------------------------------ Q K^T issuer (one softmax group)
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ Q K^T issuer
         // The S tiles (blocks) of a CTA are numbered in the order they are produced; tile s goes to
         // S buffer s & 1, so Q K^T of block j + 1 runs while the softmax warps work on block j.
         {
@@ -344,7 +244,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     __syncwarp();
                 }
                 if (!ok) break;
-                if (elect_one()) tc_commit(&bars->q_empty[0][qb]);   // the last read of this Q buffer has been issued
+                if (elect_one()) tc_commit(&bars->q_empty[qb]);      // the last read of this Q buffer has been issued
                 __syncwarp();
                 s_no = s_end;
                 ++q_no;
@@ -357,8 +257,8 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
         }
         __syncwarp();
-    } else if (WGS == 1 && warp == 3) {
-        // ------------------------------------------------------------ P V issuer (one softmax group)
+    } else if (warp == 3) {
+        // ------------------------------------------------------------ P V issuer
         {
             int p_no = 0, o_no = 0;
             bool ok = true;
@@ -380,14 +280,14 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     // O += P_j V_{c_j}: A = P (K-major), B = V tiles (N contiguous), N = head_dim
                     const uint64_t da = make_tile_desc(smem_u32(p_smem + pb * kTileBytes), false);
                     const uint64_t db = make_tile_desc(smem_u32(v_smem + vs * set_bytes), true);
-                    const uint32_t d = tmem_base + (uint32_t)(WGS == 2 ? (p_no & 1) * p.head_dim : 0);
+                    const uint32_t d = tmem_base;
                     if (elect_one()) {
 #pragma unroll
                         for (int kk = 0; kk < kTile / 16; ++kk)
                             tc_mma_f16(d, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * (2048 >> 4)), idesc_pv,
-                                       (j >= WGS || kk > 0) ? 1u : 0u);
+                                       (j > 0 || kk > 0) ? 1u : 0u);
                         tc_commit(&bars->pv_done[vs]);
-                        if (j == n - 1) tc_commit(&bars->o_full[0][o_no & 1]);
+                        if (j == n - 1) tc_commit(&bars->o_full[o_no & 1]);
                     }
                     __syncwarp();
                 }
@@ -401,20 +301,13 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         __syncwarp();
     } else {
         // ------------------------------------------------------------ softmax warps
-        // WGS = 2: two warpgroups share an item; group g takes the S tiles with number s & 1 == g
-        // (S buffer g), keeps its own running maxima and sums and its own O accumulator in TMEM
-        // (P V of tile s accumulates into accumulator s & 1), and group 0 merges the two at the end:
-        // the partial results of a softmax over two disjoint key sets combine exactly.
-        const int wg = WGS == 2 ? (warp - 4) >> 2 : 0;
         const int quad = warp & 3;                  // TMEM sub-partition this warp may read
         const int q4 = lane & 3;                    // position in the quad: columns 8u + 2 * q4 + {0, 1}
         const int row_a = quad * 16 + (lane >> 2);  // this lane's two rows of the 64-row block
         const uint32_t lane_field = (uint32_t)(quad * 32) << 16;
-        const uint32_t o_col = (uint32_t)(wg * p.head_dim);       // this group's O accumulator
         // MASKED = false: no causal or key-padding mask, all mask tests fold away
         const bool masked_op = MASKED && (p.causal != 0 || p.kpm != nullptr || p.quadrants != 0);
         int s_no = 0, o_no = 0;                     // S tiles and non-empty items before the current item
-        int x_no[2] = {0, 0};                       // hand-overs so far in which group 0 / group 1 was the writer
         bool ok = true;
         Cursor cur;
         cur.init(p);
@@ -428,7 +321,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             const size_t lse_a = (size_t)cur.z * p.seq_q + (size_t)cur.g * kTile + row_a;
             if (n == 0) {
                 // a block row without blocks: zeros, lse = -inf
-                if (wg == 0) {
+                {
                     for (int c = q4 * 8; c < p.head_dim; c += 32) {
                         *reinterpret_cast<uint4*>(p.o + o_row_a + c) = make_uint4(0u, 0u, 0u, 0u);
                         *reinterpret_cast<uint4*>(p.o + o_row_b + c) = make_uint4(0u, 0u, 0u, 0u);
@@ -490,7 +383,6 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 const int sm_row = quad * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
                 const uint32_t p_off = (uint32_t)(sm_row * 128) + ((((uint32_t)(lane >> 4)) ^ (uint32_t)(sm_row & 7)) << 4);
                 const float c2abs = fabsf(c2);
-                const int t_first = WGS == 2 ? ((wg - s_no) & 1) : 0;     // this group's first tile of the item
                 auto load = [&](uint32_t (&r)[32], int t) -> bool {       // wait for S tile t, start loading it
                     const int s = s_no + t;
                     if (!__all_sync(0xffffffffu, mbar_wait(&bars->qk_done[s & ring_mask], (uint32_t)(s >> p.ring_shift) & 1u,
@@ -559,8 +451,8 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     x_a = x_a == -INFINITY ? -INFINITY : x_a * c2abs;       // maxima of t over the block
                     x_b = x_b == -INFINITY ? -INFINITY : x_b * c2abs;
                     const int pb = s & 1;
-                    if (t == t_first) {
-                        m_a = x_a; m_b = x_b;                                 // this group's first P V overwrites O
+                    if (t == 0) {
+                        m_a = x_a; m_b = x_b;                                 // the row's first P V overwrites O
                     } else {
                         // raise a row's maximum only when it is overdue (or was -inf: nothing kept yet)
                         const bool up_a = x_a > m_a + kSlack || (m_a == -INFINITY && x_a > -INFINITY);
@@ -570,15 +462,15 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                             const float al_b = !up_b ? 1.f : (m_b == -INFINITY ? 0.f : attn_exp2(m_b - x_b));
                             if (up_a) { m_a = x_a; const uint64_t f = f2_pack(al_a, al_a); la2[0] = f2_mul(la2[0], f); la2[1] = f2_mul(la2[1], f); }
                             if (up_b) { m_b = x_b; const uint64_t f = f2_pack(al_b, al_b); lb2[0] = f2_mul(lb2[0], f); lb2[1] = f2_mul(lb2[1], f); }
-                            // O is complete up to this group's previous tile once that tile's P V has retired
-                            const int prev = s - WGS;
+                            // O is complete up to the previous tile once that tile's P V has retired
+                            const int prev = s - 1;
                             if (!__all_sync(0xffffffffu, mbar_wait(&bars->pv_done[prev & vring_mask],
                                                                    (uint32_t)(prev >> p.vring_shift) & 1u, abort_flag, p.status)))
                                 return false;
                             tc_fence_after();
                             for (int c = 0; c < p.head_dim; c += 16) {
                                 uint32_t o[8];
-                                tc_ld_16x256b_x2(tmem_base + lane_field + o_col + (uint32_t)c, o);
+                                tc_ld_16x256b_x2(tmem_base + lane_field + (uint32_t)c, o);
                                 tc_wait_ld();
 #pragma unroll
                                 for (int u = 0; u < 2; ++u) {
@@ -587,7 +479,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                                     o[4 * u + 2] = __float_as_uint(__uint_as_float(o[4 * u + 2]) * al_b);
                                     o[4 * u + 3] = __float_as_uint(__uint_as_float(o[4 * u + 3]) * al_b);
                                 }
-                                tc_st_16x256b_x2(tmem_base + lane_field + o_col + (uint32_t)c, o);
+                                tc_st_16x256b_x2(tmem_base + lane_field + (uint32_t)c, o);
                             }
                             tc_wait_st();
                             tc_fence_before();      // ordered before the P V this block's arrival releases
@@ -624,7 +516,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     if (lane == 0) mbar_arrive(&bars->p_full[pb]);
                     return true;
                 };
-                if (WGS == 1) {
+                {
                     // The TMEM load of block j + 1 is in flight while block j is worked on (two
                     // register buffers, loop unrolled by two).
                     uint32_t ra[32], rb[32];
@@ -639,16 +531,6 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         if (t + 2 < n) { ma = mask_of(t + 2); ok = load(ra, t + 2); }
                         if (!process(rb, t + 1, mb)) ok = false;
                     }
-                } else {
-                    // two groups already keep two blocks in flight: one register buffer
-                    uint32_t r[32];
-                    for (int t = t_first; ok && t < n; t += 2) {
-                        const uint32_t m = mask_of(t);
-                        ok = load(r, t);
-                        if (!ok) break;
-                        loaded(t);
-                        if (!process(r, t, m)) ok = false;
-                    }
                 }
                 s_no += n;
                 if (!ok) break;
@@ -661,78 +543,25 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 }
                 l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
                 l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
-                // weights of this group's (w) and the other group's (v) accumulator in the result
-                float w_a = 1.f, w_b = 1.f, v_a = 0.f, v_b = 0.f;
-                // The groups finish alternate items.  The rule must not depend on the data: an mbarrier
-                // parity wait tells the current phase from the one before only, so o_full / o_empty of
-                // items of one parity are always waited on by the same group, in every phase.  (Letting
-                // the owner of an item's last tile finish it, which starts the next item a little
-                // earlier, let a group skip phases: with rows of 1-3 blocks and several items per CTA it
-                // passed a wait one phase early.)
-                const int epi_wg = WGS == 2 ? (o_no & 1) : 0;
-                if (WGS == 2) {
-                    // the other group hands its maxima and sums over through shared memory (per direction
-                    // two slots, alternating); the partial softmaxes over the two groups' key sets merge
-                    // as m = max(m0, m1), l = l0 2^(m0 - m) + l1 2^(m1 - m), O likewise
-                    const int dir = epi_wg ^ 1;                 // the group that writes
-                    const int slot = x_no[dir] & 1;
-                    const uint32_t par = (uint32_t)(x_no[dir] >> 1) & 1u;
-                    ++x_no[dir];
-                    float* stat = &bars->stat[dir][slot][0][0];
-                    if (wg != epi_wg) {
-                        ok = __all_sync(0xffffffffu, mbar_wait(&bars->stat_empty[dir][slot], par ^ 1u, abort_flag, p.status)) != 0;
-                        if (!ok) break;
-                        if (q4 == 0) {
-                            stat[row_a * 2] = m_a; stat[row_a * 2 + 1] = l_a;
-                            stat[(row_a + 8) * 2] = m_b; stat[(row_a + 8) * 2 + 1] = l_b;
-                        }
-                        __threadfence_block();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&bars->stat_full[dir][slot]);
-                    } else {
-                        ok = __all_sync(0xffffffffu, mbar_wait(&bars->stat_full[dir][slot], par, abort_flag, p.status)) != 0;
-                        if (!ok) break;
-                        const float mo_a = stat[row_a * 2], lo_a = stat[row_a * 2 + 1];
-                        const float mo_b = stat[(row_a + 8) * 2], lo_b = stat[(row_a + 8) * 2 + 1];
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&bars->stat_empty[dir][slot]);
-                        const float mm_a = fmaxf(m_a, mo_a), mm_b = fmaxf(m_b, mo_b);
-                        w_a = m_a == -INFINITY ? 0.f : attn_exp2(m_a - mm_a);
-                        v_a = mo_a == -INFINITY ? 0.f : attn_exp2(mo_a - mm_a);
-                        w_b = m_b == -INFINITY ? 0.f : attn_exp2(m_b - mm_b);
-                        v_b = mo_b == -INFINITY ? 0.f : attn_exp2(mo_b - mm_b);
-                        l_a = l_a * w_a + lo_a * v_a;  m_a = mm_a;
-                        l_b = l_b * w_b + lo_b * v_b;  m_b = mm_b;
-                    }
-                }
-                if (wg == epi_wg) {
+                {
                     // ---- end of the row: O / l
                     const float inv_a = l_a > 0.f ? __frcp_rn(l_a) : 0.f, inv_b = l_b > 0.f ? __frcp_rn(l_b) : 0.f;
-                    const float sw_a = w_a * inv_a, sv_a = v_a * inv_a, sw_b = w_b * inv_b, sv_b = v_b * inv_b;
-                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[0][o_no & 1], (uint32_t)(o_no >> 1) & 1u, abort_flag, p.status)) != 0;
-                    if (WGS == 2 && ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[1][o_no & 1], (uint32_t)(o_no >> 1) & 1u, abort_flag, p.status)) != 0;
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[o_no & 1], (uint32_t)(o_no >> 1) & 1u, abort_flag, p.status)) != 0;
                     if (!ok) break;
                     tc_fence_after();
                     for (int c = 0; c < p.head_dim; c += 32) {
-                        uint32_t r0[16], r1[16];
-                        tc_ld_16x256b_x4(tmem_base + lane_field + o_col + (uint32_t)c, r0);
-                        if (WGS == 2) tc_ld_16x256b_x4(tmem_base + lane_field + (uint32_t)((wg ^ 1) * p.head_dim + c), r1);
+                        uint32_t r0[16];
+                        tc_ld_16x256b_x4(tmem_base + lane_field + (uint32_t)c, r0);
                         tc_wait_ld();
                         if (c + 32 >= p.head_dim) release_accumulator(&bars->o_empty[o_no & 1], lane);
                         uint32_t ta[4], tb[4];
 #pragma unroll
                         for (int u = 0; u < 4; ++u) {
-                            // an accumulator whose weight is 0 may never have been written: do not touch it
-                            float a0 = sw_a > 0.f ? __uint_as_float(r0[4 * u]) * sw_a : 0.f;
-                            float a1 = sw_a > 0.f ? __uint_as_float(r0[4 * u + 1]) * sw_a : 0.f;
-                            float b0 = sw_b > 0.f ? __uint_as_float(r0[4 * u + 2]) * sw_b : 0.f;
-                            float b1 = sw_b > 0.f ? __uint_as_float(r0[4 * u + 3]) * sw_b : 0.f;
-                            if (WGS == 2) {
-                                if (sv_a > 0.f) { a0 = fmaf(__uint_as_float(r1[4 * u]), sv_a, a0); a1 = fmaf(__uint_as_float(r1[4 * u + 1]), sv_a, a1); }
-                                if (sv_b > 0.f) { b0 = fmaf(__uint_as_float(r1[4 * u + 2]), sv_b, b0); b1 = fmaf(__uint_as_float(r1[4 * u + 3]), sv_b, b1); }
-                            }
-                            ta[u] = pack2<BF16>(a0, a1);
-                            tb[u] = pack2<BF16>(b0, b1);
+                            // a row without an unmasked score gets zeros whatever its accumulator holds
+                            ta[u] = pack2<BF16>(inv_a > 0.f ? __uint_as_float(r0[4 * u]) * inv_a : 0.f,
+                                                inv_a > 0.f ? __uint_as_float(r0[4 * u + 1]) * inv_a : 0.f);
+                            tb[u] = pack2<BF16>(inv_b > 0.f ? __uint_as_float(r0[4 * u + 2]) * inv_b : 0.f,
+                                                inv_b > 0.f ? __uint_as_float(r0[4 * u + 3]) * inv_b : 0.f);
                         }
                         quad_transpose(ta, q4);         // now columns c + 8 * q4 .. + 7 of the row
                         quad_transpose(tb, q4);
@@ -1291,10 +1120,10 @@ int attention_forward(int dtype, const void* q, const void* k, const void* v, vo
     KernelFn kernel;
     if (dtype == BSA_DTYPE_BF16) {
         if (pipes) kernel = masked ? attention_forward_pipes_kernel<true, true> : attention_forward_pipes_kernel<true, false>;
-        else       kernel = masked ? attention_forward_kernel<true, true, 1> : attention_forward_kernel<true, false, 1>;
+        else       kernel = masked ? attention_forward_kernel<true, true> : attention_forward_kernel<true, false>;
     } else {
         if (pipes) kernel = masked ? attention_forward_pipes_kernel<false, true> : attention_forward_pipes_kernel<false, false>;
-        else       kernel = masked ? attention_forward_kernel<false, true, 1> : attention_forward_kernel<false, false, 1>;
+        else       kernel = masked ? attention_forward_kernel<false, true> : attention_forward_kernel<false, false>;
     }
     AttnParams p{};
     p.dtiles = (int)(head_dim / kTile);

@@ -191,12 +191,12 @@ def device_step(ops, lay, q, k, v, do, scale, block, events=None, causal=False):
     ]
     keys = ["s", "p", "o", "dp", "dv", "ds", "dq", "dk"]
     st = {}
+    if events is not None:
+        events[0].record()
     for i, (call, key) in enumerate(zip(calls, keys)):
-        if events is not None:
-            events[i][0].record()
         st[key] = call(st)
         if events is not None:
-            events[i][1].record()
+            events[i + 1].record()         # one event per boundary: op i took events[i] .. events[i + 1]
     return st
 
 
@@ -254,6 +254,7 @@ def side_cfg2(sparse_ops, dev):
     fused = lambda: fused_step(lay, q, k, v, do, scale, True)                                # noqa: E731
     out = {"unfused_step_us": round(1e3 * timed(unfused, 20), 1), "fused_step_us": round(1e3 * timed(fused, 20), 1)}
     out["unfused_step_graph_us"] = round(1e3 * graph_replayed(unfused), 1)
+    out["fused_step_graph_us"] = round(1e3 * graph_replayed(fused), 1)
     # block-32 engine at seq 4096 (fp16, the benchmark pattern at block 32): how far from the HBM roofline
     from sparse.patterns import strided_local
     lay4 = SparseLayout(strided_local(128, 16, 4), block=block, device=dev)
@@ -312,7 +313,7 @@ def side_cfg5_strong(sparse_ops, dev, world, dist):
     for _ in range(2):
         device_step(sparse_ops, lay, q, k, v, do, scale, block)
     steps = 3
-    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in OPS] for _ in range(steps)]
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(OPS) + 1)] for _ in range(steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if world > 1:
         dist.barrier()
@@ -332,7 +333,7 @@ def side_cfg5_strong(sparse_ops, dev, world, dist):
     peaks = load_peaks()
     ops = {}
     for j, name in enumerate(OPS):
-        t = sum(ev[i][j][0].elapsed_time(ev[i][j][1]) for i in range(steps)) / steps
+        t = sum(ev[i][j].elapsed_time(ev[i][j + 1]) for i in range(steps)) / steps
         byts = {"softmax_fwd": 2 * sparse_bytes, "softmax_bwd": 3 * sparse_bytes}.get(name, sparse_bytes + 2 * dense_bytes)
         ops[name] = {"ms": round(t, 3), "hbm_frac": round(byts / (t * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)}
     del q, k, v, do
@@ -411,26 +412,33 @@ def run_ours(args):
     # clocks are sampled from before the warm-up until after the end-to-end loop, so all timed
     # regions are covered (a timed region of a few tens of ms is shorter than one sampling period)
     sampler = ClockSampler(local_rank) if rank == 0 else None
-    # ---- device-resident timing (value): `repeats` timed regions of `steps` steps each, per-op events inside
+    # ---- device-resident timing (value): `repeats` timed regions of `steps` steps each, two events per region.
+    # (Events between the launches cost 50-65 us per step: the per-op times come from a pass of their own.)
     for _ in range(args.warmup):
         device_step(sparse_ops, lay, q, k, v, do, scale, block)
     barrier()
-    region_ms, op_sum = [], {name: 0.0 for name in OPS}
+    region_ms = []
     for _ in range(args.repeats):
-        ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in OPS]
-              for _ in range(args.steps)]
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         start.record()
         for i in range(args.steps):
-            device_step(sparse_ops, lay, q, k, v, do, scale, block, ev[i])
+            device_step(sparse_ops, lay, q, k, v, do, scale, block)
         stop.record()
         barrier()
         region_ms.append(start.elapsed_time(stop))
-        for j, name in enumerate(OPS):
-            op_sum[name] += sum(ev[i][j][0].elapsed_time(ev[i][j][1]) for i in range(args.steps))
+    # ---- per-op times: the same loop once more with one event on every boundary between two launches
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(OPS) + 1)] for _ in range(args.steps)]
+    barrier()
+    for i in range(args.steps):
+        device_step(sparse_ops, lay, q, k, v, do, scale, block, ev[i])
+    barrier()
+    op_ms = {name: sum(ev[i][j].elapsed_time(ev[i][j + 1]) for i in range(args.steps)) / args.steps
+             for j, name in enumerate(OPS)}
+    instrumented_ms = sum(op_ms.values())
+    # ---- the step replayed from a CUDA graph (no launch gaps): reported beside the eager value
+    graph_ms = graph_replayed(lambda: device_step(sparse_ops, lay, q, k, v, do, scale, block), args.steps)
     sparse_ops.check_device_status(local_rank)
-    op_ms = {name: op_sum[name] / (args.steps * args.repeats) for name in OPS}
 
     # ---- end-to-end timing through the public API with host buffers.  Every step copies its four
     # inputs from pinned host memory (one copy), runs forward + backward through the public fused op
@@ -593,6 +601,7 @@ def run_ours(args):
             "metric": METRIC, "value": round(value, 3), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "repeats": args.repeats,
             "ms_per_step_min": round(per_step[0], 4), "ms_per_step_max": round(per_step[-1], 4),
+            "ms_per_step_graph": round(graph_ms, 4), "ms_per_step_with_op_events": round(instrumented_ms, 4),
             "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": workload_config(world, z),

@@ -691,12 +691,14 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
 
     if (warp == 0 || warp == 2) {
         // ------------------------------------------------------------ producer
-        // Order K(u), V(u - 3): the order in which their stages become free (Q K^T runs two tiles ahead of
-        // the softmax warps, P V one tile behind them).  The tiles are numbered through the rows, so the
-        // copies run ahead across row borders.
+        // Order within a row: K(u), V(u - 3), the order in which their stages become free (Q K^T runs two
+        // tiles ahead of the softmax warps, P V one tile behind them); the V tiles of the row's last three
+        // blocks follow its last K tile, as the issuer finishes a row's P V before it starts on the next
+        // row.  The stages are numbered through the rows, so Q and the first K tiles of the next row are on
+        // their way while the softmax warps work on the last tiles of this one.
         int t0 = 0, i_no = 0;                       // tiles and non-empty rows before the current row
         KRing kr;                                   // stage of the next K tile
-        int vq_col[3] = {0, 0, 0}, vq_z[3] = {0, 0, 0};        // key block and batch entry of tiles u - 3, u - 2, u - 1
+        int vq_col[3] = {0, 0, 0};                  // key blocks of tiles u - 3, u - 2, u - 1
         bool ok = true;
         Cursor cur;
         cur.init_as(p, walker, walkers);
@@ -735,21 +737,15 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
                     }
                     __syncwarp();
                     kr.next();
-                    if (ok && u >= 3) ok = load_v(u - 3, vq_col[0], vq_z[0]);
-                    vq_col[0] = vq_col[1]; vq_z[0] = vq_z[1];
-                    vq_col[1] = vq_col[2]; vq_z[1] = vq_z[2];
-                    vq_col[2] = col; vq_z[2] = cur.z;
+                    if (ok && j >= 3) ok = load_v(u - 3, vq_col[0], cur.z);
+                    vq_col[0] = vq_col[1]; vq_col[1] = vq_col[2]; vq_col[2] = col;
                 }
+                for (int r = n < 3 ? 3 - n : 0; ok && r < 3; ++r) ok = load_v(t0 + n - 3 + r, vq_col[r], cur.z);
                 t0 += n;
                 ++i_no;
             }
             pre = pre_next;
             cur.advance();
-        }
-        // the V tiles of the last three blocks
-        for (int r = 0; ok && r < 3; ++r) {
-            const int u = t0 - 3 + r;
-            if (u >= 0) ok = load_v(u, vq_col[r], vq_z[r]);
         }
         if (lane == 0 && *(volatile int*)abort_flag) {
             // Give copies that were issued a bounded chance to land before the CTA exits.
@@ -766,9 +762,11 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
         __syncwarp();
     } else if (warp == 1 || warp == 3) {
         // ------------------------------------------------------------ issuer
-        // Order: Q K^T of tile u, then P V of tile u - 2 (two tiles pending, also across rows).  The events
-        // it waits for come in this order: S(u - 2) is in the softmax warps' registers when they start on
-        // tile u - 2 (S buffer u & 1 is free), their P(u - 2) is complete when they are done with it.
+        // Order within a row: Q K^T of tile u, then P V of tile u - 2; the row's last two P V follow its last
+        // Q K^T, before the next row's first Q K^T (which would otherwise keep the end of this row -- the
+        // softmax warps wait for the last P V to read O out -- behind the arrival of the next row's Q).  The
+        // events it waits for come in this order: S(u - 2) is in the softmax warps' registers when they start
+        // on tile u - 2 (S buffer u & 1 is free), their P(u - 2) is complete when they are done with it.
         const uint32_t idesc_qk = p.idesc_qk, idesc_pv = p.idesc_pv;
         const uint64_t q_desc = make_tile_desc(smem_u32(q_smem), false);
         const uint64_t k_desc = make_tile_desc(smem_u32(k_smem), false);
@@ -776,14 +774,11 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
         int t0 = 0, i_no = 0;                       // tiles and non-empty rows before the current row
         KRing kr;
         bool ok = true;
-        int npend = 0;
-        int pend_t[2] = {0, 0}, pend_i[2] = {0, 0};             // pending P V: tile number, row number,
-        bool pend_first[2] = {false, false}, pend_last[2] = {false, false};       // first / last tile of its row
-        auto issue_pv = [&]() -> bool {             // O (+)= P V of the older pending tile
-            const int t = pend_t[0], b = t & 1;
+        auto issue_pv = [&](int t, int row, bool first, bool last) -> bool {       // O (+)= P V of tile t
+            const int b = t & 1;
             // the accumulator is free once the row before has been read out
-            if (pend_first[0] && pend_i[0] > 0 &&
-                !__all_sync(0xffffffffu, mbar_wait(&bars->o_empty[g], (uint32_t)(pend_i[0] - 1) & 1u, abort_flag, p.status)))
+            if (first && row > 0 &&
+                !__all_sync(0xffffffffu, mbar_wait(&bars->o_empty[g], (uint32_t)(row - 1) & 1u, abort_flag, p.status)))
                 return false;
             if (!__all_sync(0xffffffffu, mbar_wait(&bars->v_full[g][b], (uint32_t)(t >> 1) & 1u, abort_flag, p.status))) return false;
             if (!__all_sync(0xffffffffu, mbar_wait(&bars->p_full[g][b], (uint32_t)(t >> 1) & 1u, abort_flag, p.status))) return false;
@@ -794,13 +789,11 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
 #pragma unroll
                 for (int kk = 0; kk < kTile / 16; ++kk)
                     tc_mma_f16_ts(o_tmem, a + (uint32_t)(8 * kk), db + (uint64_t)(kk * (2048 >> 4)), idesc_pv,
-                                  (!pend_first[0] || kk > 0) ? 1u : 0u);
+                                  (!first || kk > 0) ? 1u : 0u);
                 tc_commit(&bars->pv_done[g][b]);        // the P buffer and the V stage are free
-                if (pend_last[0]) tc_commit(&bars->o_full[g]);
+                if (last) tc_commit(&bars->o_full[g]);
             }
             __syncwarp();
-            pend_t[0] = pend_t[1]; pend_i[0] = pend_i[1]; pend_first[0] = pend_first[1]; pend_last[0] = pend_last[1];
-            --npend;
             return true;
         };
         Cursor cur;
@@ -826,14 +819,12 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
                 }
                 __syncwarp();
                 kr.next();
-                if (npend == 2) ok = issue_pv();
-                pend_t[npend] = t; pend_i[npend] = i_no; pend_first[npend] = j == 0; pend_last[npend] = j == n - 1;
-                ++npend;
+                if (j >= 2) ok = issue_pv(t - 2, i_no, j == 2, false);
             }
+            for (int j = n < 2 ? 0 : n - 2; ok && j < n; ++j) ok = issue_pv(t0 + j, i_no, j == 0, j == n - 1);
             t0 += n;
             ++i_no;
         }
-        while (ok && npend > 0) ok = issue_pv();
         // All MMAs issued by the elected lane (the same one every time: the election is deterministic
         // for a converged warp) must have retired before TMEM is freed.
         if (elect_one()) {
@@ -871,6 +862,8 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
                     *reinterpret_cast<uint4*>(p.o + o_row_b + c) = make_uint4(0u, 0u, 0u, 0u);
                 }
                 if (q4 == 0 && p.lse) { p.lse[lse_a] = -INFINITY; p.lse[lse_a + 8] = -INFINITY; }
+                pre = pre_next;
+                cur.advance();
             } else {
                 const uint8_t* kpm_row = p.kpm ? p.kpm + (size_t)(cur.z / p.kpm_div) * p.kpm_stride : nullptr;
                 const int qpos_a = cur.g * kTile + row_a;
@@ -1047,6 +1040,10 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
                 }
                 t0 += n;
                 if (!ok) break;
+                // The cursor moves on before the wait for the accumulator: the bookkeeping of the next row runs
+                // while the row's last product is in flight, not after the row's results have been written.
+                pre = pre_next;
+                cur.advance();
                 // ---- end of the row: O / l and the log-sum-exp
                 float l_a, l_b;
                 {
@@ -1089,8 +1086,6 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
                 }
                 ++i_no;
             }
-            pre = pre_next;
-            cur.advance();
         }
     }
 

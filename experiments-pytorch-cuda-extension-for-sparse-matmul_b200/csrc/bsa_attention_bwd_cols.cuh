@@ -250,6 +250,8 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
                     *reinterpret_cast<uint4*>(p.out1 + out_a + c) = make_uint4(0u, 0u, 0u, 0u);
                     *reinterpret_cast<uint4*>(p.out1 + out_b + c) = make_uint4(0u, 0u, 0u, 0u);
                 }
+                pre = pre_next;
+                cur.advance();
             } else {
                 const uint8_t* kpm_row = (MASKED && p.kpm) ? p.kpm + (size_t)(cur.z / p.kpm_div) * p.kpm_stride : nullptr;
                 const int pos_a = cur.g * kTile + row_a;         // key position of row a (row b: + 8)
@@ -338,6 +340,10 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
                 }
                 t0 += n;
                 if (!ok) break;
+                // The cursor moves on before the wait for the accumulators: the bookkeeping of the next column runs
+                // while the column's last products are in flight, not after its results have been written.
+                pre = pre_next;
+                cur.advance();
                 // ---- end of the column: dV and dK to global memory
                 ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[g], (uint32_t)i_no & 1u, abort_flag, p.status)) != 0;
                 if (!ok) break;
@@ -364,8 +370,6 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
                 }
                 ++i_no;
             }
-            pre = pre_next;
-            cur.advance();
         }
     }
 

@@ -128,20 +128,20 @@ attention_backward_rows_pipes_kernel(const __grid_constant__ CUtensorMap map_q, 
         __syncwarp();
     } else if (warp == 1 || warp == 3) {
         // ------------------------------------------------------------ issuer
-        // Order: T1 and T2 of block t, then the accumulation of block t - 1 (kept pending across rows).  The
-        // events come in this order: T(t - 1) is in the compute warps' registers when they start on block
-        // t - 1, their dS(t - 1) is complete when they are done with it.
+        // Order within a row: T1 and T2 of block t, then the accumulation of block t - 1; the row's last
+        // accumulation follows, before the next row's first products (which would otherwise keep the end of
+        // this row -- the compute warps wait for the last accumulation to read dQ out -- behind the arrival
+        // of the next row's X pair).  The events come in this order: T(t - 1) is in the compute warps'
+        // registers when they start on block t - 1, their dS(t - 1) is complete when they are done with it.
         const uint64_t x1_desc = make_tile_desc(smem_u32(x_smem), false);
         const uint64_t x2_desc = make_tile_desc(smem_u32(x_smem + kTileBytes), false);
         int t0 = 0, i_no = 0;
         bool ok = true;
-        bool pend = false, pend_first = false, pend_last = false;
-        int pend_t = 0, pend_i = 0;                 // the pending accumulation: block number, row number
-        auto issue_acc = [&]() -> bool {            // dQ (+)= dS K of the pending block
-            const int t = pend_t, b = t & 1;
+        auto issue_acc = [&](int t, int row, bool first, bool last) -> bool {      // dQ (+)= dS K of block t
+            const int b = t & 1;
             // the accumulator is free once the row before has been read out
-            if (pend_first && pend_i > 0 &&
-                !__all_sync(0xffffffffu, mbar_wait(&bars->o_empty[g], (uint32_t)(pend_i - 1) & 1u, abort_flag, p.status)))
+            if (first && row > 0 &&
+                !__all_sync(0xffffffffu, mbar_wait(&bars->o_empty[g], (uint32_t)(row - 1) & 1u, abort_flag, p.status)))
                 return false;
             if (!__all_sync(0xffffffffu, mbar_wait(&bars->ds_full[g][b], (uint32_t)(t >> 1) & 1u, abort_flag, p.status))) return false;
             tc_fence_after();
@@ -152,9 +152,9 @@ attention_backward_rows_pipes_kernel(const __grid_constant__ CUtensorMap map_q, 
 #pragma unroll
                 for (int kk = 0; kk < kTile / 16; ++kk)
                     tc_mma_f16_ts(dq_tmem, a + (uint32_t)(8 * kk), db + (uint64_t)(kk * (2048 >> 4)), p.idesc_acc,
-                                  (!pend_first || kk > 0) ? 1u : 0u);
+                                  (!first || kk > 0) ? 1u : 0u);
                 tc_commit(&bars->acc_done[g][b]);       // the Y stage and the dS buffer are free
-                if (pend_last) tc_commit(&bars->o_full[g]);
+                if (last) tc_commit(&bars->o_full[g]);
             }
             __syncwarp();
             return true;
@@ -184,13 +184,12 @@ attention_backward_rows_pipes_kernel(const __grid_constant__ CUtensorMap map_q, 
                     if (j == n - 1) tc_commit(&bars->x_empty[g]);      // the last reads of the X pair
                 }
                 __syncwarp();
-                if (pend) ok = issue_acc();
-                pend = true; pend_t = t; pend_i = i_no; pend_first = j == 0; pend_last = j == n - 1;
+                if (j >= 1) ok = issue_acc(t - 1, i_no, j == 1, false);
             }
+            if (ok) ok = issue_acc(t0 + n - 1, i_no, n == 1, true);
             t0 += n;
             ++i_no;
         }
-        if (ok && pend) issue_acc();
         // All MMAs issued by the elected lane (the same one every time) must have retired before TMEM is freed.
         if (elect_one()) {
             tc_commit(&bars->drain);
@@ -223,6 +222,8 @@ attention_backward_rows_pipes_kernel(const __grid_constant__ CUtensorMap map_q, 
                     *reinterpret_cast<uint4*>(p.out0 + out_a + c) = make_uint4(0u, 0u, 0u, 0u);
                     *reinterpret_cast<uint4*>(p.out0 + out_b + c) = make_uint4(0u, 0u, 0u, 0u);
                 }
+                pre = pre_next;
+                cur.advance();
             } else {
                 const uint8_t* kpm_row = (MASKED && p.kpm) ? p.kpm + (size_t)(cur.z / p.kpm_div) * p.kpm_stride : nullptr;
                 const int pos_a = cur.g * kTile + row_a;         // query position of row a (row b: + 8)
@@ -311,6 +312,10 @@ attention_backward_rows_pipes_kernel(const __grid_constant__ CUtensorMap map_q, 
                 }
                 t0 += n;
                 if (!ok) break;
+                // The cursor moves on before the wait for the accumulator: the bookkeeping of the next row runs
+                // while the row's last product is in flight, not after the row's results have been written.
+                pre = pre_next;
+                cur.advance();
                 // ---- end of the row: dQ to global memory
                 ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[g], (uint32_t)i_no & 1u, abort_flag, p.status)) != 0;
                 if (!ok) break;
@@ -335,8 +340,6 @@ attention_backward_rows_pipes_kernel(const __grid_constant__ CUtensorMap map_q, 
                 }
                 ++i_no;
             }
-            pre = pre_next;
-            cur.advance();
         }
     }
 

@@ -628,6 +628,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 //                the log-sum-exp go to global memory.
 constexpr int kPipeTiles = 6;                   // Q, K x 3, V x 2
 constexpr int kPipeKRing = 3;
+constexpr int kPipeDescs = 8;
 struct __align__(8) PipeBarriers {
     uint64_t q_full[2], q_empty[2];             // [pipeline]
     uint64_t k_full[2][kPipeKRing], qk_done[2][kPipeKRing];   // [pipeline][K stage]: qk_done = S is ready and the K stage is free
@@ -637,6 +638,7 @@ struct __align__(8) PipeBarriers {
     uint64_t drain;
     uint32_t tmem_base;
     int abort_flag;
+    BlockDesc descs[2][kPipeDescs];             // [pipeline][tile & 7]: written by the producer for the softmax warps
 };
 
 // Position of a tile in the ring of three K stages (every role counts the tiles it has handled).
@@ -728,10 +730,15 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
                 DescWindow win;
                 win.begin(p.blocks, cur.first, cur.count, pre, lane);
                 for (int j = 0; ok && j < n; ++j) {
-                    const int col = win.get(p.blocks, cur.first, cur.count, j, lane).col();
+                    const BlockDesc desc = win.get(p.blocks, cur.first, cur.count, j, lane);
+                    const int col = desc.col();
                     const int u = t0 + j;
                     ok = __all_sync(0xffffffffu, mbar_wait(&bars->qk_done[g][kr.stage], kr.use ^ 1u, abort_flag, p.status)) != 0;
                     if (ok && elect_one()) {
+                        // The softmax warps take the tile's descriptor (key block, quadrant bits) from here: they
+                        // read it once S of the tile is ready and before they hand the S buffer back, the K stage
+                        // is refilled three tiles on, Q K^T runs two tiles ahead of them: slot u & 7 is free.
+                        bars->descs[g][u & (kPipeDescs - 1)] = desc;
                         mbar_expect_tx(&bars->k_full[g][kr.stage], (uint32_t)kTileBytes);
                         tma_load_3d(k_smem + kr.stage * kTileBytes, &map_k, &bars->k_full[g][kr.stage], 0, col * kTile, cur.z);
                     }
@@ -847,10 +854,7 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
         bool ok = true;
         Cursor cur;
         cur.init_as(p, walker, walkers);
-        BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
         while (ok && cur.valid()) {
-            BlockDesc pre_next{0, 0};
-            if (cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
             const int n = cur.count;
             const size_t o_row_a = ((size_t)cur.z * p.seq_q + (size_t)cur.g * kTile + row_a) * kTile;
             const size_t o_row_b = o_row_a + (size_t)8 * kTile;
@@ -862,7 +866,6 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
                     *reinterpret_cast<uint4*>(p.o + o_row_b + c) = make_uint4(0u, 0u, 0u, 0u);
                 }
                 if (q4 == 0 && p.lse) { p.lse[lse_a] = -INFINITY; p.lse[lse_a + 8] = -INFINITY; }
-                pre = pre_next;
                 cur.advance();
             } else {
                 const uint8_t* kpm_row = p.kpm ? p.kpm + (size_t)(cur.z / p.kpm_div) * p.kpm_stride : nullptr;
@@ -907,8 +910,6 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
                 float m_a = -INFINITY, m_b = -INFINITY;
                 // row sums: per row two independent two-wide accumulators (even / odd column units)
                 uint64_t la2[2] = {0ull, 0ull}, lb2[2] = {0ull, 0ull};
-                DescWindow win;
-                win.begin(p.blocks, cur.first, cur.count, pre, lane);
                 uint32_t r[32];
                 // wait for S of tile t (K stage / barrier position kr), unless an earlier test has seen it
                 // complete, and start loading it
@@ -927,7 +928,7 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
                     if (!ok) break;
                     // (the mask of a block is computed while its S tile is on the way)
                     uint32_t mask = 0u;
-                    if (MASKED && masked_op) mask = block_mask(win.get(p.blocks, cur.first, cur.count, j, lane));
+                    if (MASKED && masked_op) mask = block_mask(bars->descs[g][t & (kPipeDescs - 1)]);
                     tc_wait_ld();
                     release_accumulator(&bars->s_empty[g][b], lane);       // S is in registers: its buffer may be overwritten
                     // Is the P buffer free (P V of tile t - 2 retired), is S of the next tile ready (Q K^T runs two
@@ -1042,7 +1043,6 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
                 if (!ok) break;
                 // The cursor moves on before the wait for the accumulator: the bookkeeping of the next row runs
                 // while the row's last product is in flight, not after the row's results have been written.
-                pre = pre_next;
                 cur.advance();
                 // ---- end of the row: O / l and the log-sum-exp
                 float l_a, l_b;

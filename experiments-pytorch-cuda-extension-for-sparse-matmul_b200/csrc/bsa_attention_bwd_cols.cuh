@@ -31,6 +31,7 @@ struct __align__(8) BwdColBarriers {
     uint64_t drain;
     uint32_t tmem_base;
     int abort_flag;
+    BlockDesc descs[2][4];                      // [pipeline][block & 3]: written by the producer for the compute warps
 };
 constexpr int kBwdColRing = 4;
 constexpr int kBwdColTiles = 2 + 2 * kBwdColRing;       // per pipeline: K, V, (Q, dO) x 4
@@ -107,11 +108,13 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
                 DescWindow win;
                 win.begin(p.blocks, cur.first, cur.count, pre, lane);
                 for (int j = 0; ok && j < n; ++j) {
-                    const int row = win.get(p.blocks, cur.first, cur.count, j, lane).row();
+                    const BlockDesc desc = win.get(p.blocks, cur.first, cur.count, j, lane);
+                    const int row = desc.row();
                     const int t = t0 + j, st = t & (kBwdColRing - 1);
                     ok = __all_sync(0xffffffffu, mbar_wait(&bars->y_free[g][st], ((uint32_t)(t >> 2) & 1u) ^ 1u, abort_flag, p.status)) != 0;
                     if (ok && elect_one()) {
                         uint64_t* full = &bars->y_full[g][st];
+                        bars->descs[g][st] = desc;      // for the compute warps; the slot is free like the stage
                         mbar_expect_tx(full, (uint32_t)(2 * kTileBytes + kBwdStatBytes));
                         tma_load_3d(y_smem + (2 * st) * kTileBytes, &map_q, full, 0, row * kTile, cur.z);
                         tma_load_3d(y_smem + (2 * st + 1) * kTileBytes, &map_do, full, 0, row * kTile, cur.z);
@@ -234,10 +237,7 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
         bool ok = true;
         Cursor cur;
         cur.init_as(p, walker, walkers);
-        BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
         while (ok && cur.valid()) {
-            BlockDesc pre_next{0, 0};
-            if (cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
             const int n = cur.count;
             const size_t out_a = ((size_t)cur.z * p.seq_k + (size_t)cur.g * kTile + row_a) * kTile;
             const size_t out_b = out_a + (size_t)8 * kTile;
@@ -250,7 +250,6 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
                     *reinterpret_cast<uint4*>(p.out1 + out_a + c) = make_uint4(0u, 0u, 0u, 0u);
                     *reinterpret_cast<uint4*>(p.out1 + out_b + c) = make_uint4(0u, 0u, 0u, 0u);
                 }
-                pre = pre_next;
                 cur.advance();
             } else {
                 const uint8_t* kpm_row = (MASKED && p.kpm) ? p.kpm + (size_t)(cur.z / p.kpm_div) * p.kpm_stride : nullptr;
@@ -258,11 +257,17 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
                 // a whole key row is padding or not
                 bool pad_a = false, pad_b = false;
                 if (MASKED && kpm_row) { pad_a = kpm_row[pos_a] != 0; pad_b = kpm_row[pos_a + 8] != 0; }
-                DescWindow win;
-                win.begin(p.blocks, cur.first, cur.count, pre, lane);
                 for (int j = 0; ok && j < n; ++j) {
                     const int t = t0 + j, st = t & (kBwdColRing - 1), b = t & 1;
-                    const BlockDesc d = win.get(p.blocks, cur.first, cur.count, j, lane);
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->t_full[g][b], (uint32_t)(t >> 1) & 1u, abort_flag, p.status)) != 0;
+                    // (complete already: the block's T products waited for the stage; observed here for the statistics)
+                    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->y_full[g][st], (uint32_t)(t >> 2) & 1u, abort_flag, p.status)) != 0;
+                    if (!ok) break;
+                    tc_fence_after();
+                    uint32_t r1[16], r2[16];
+                    tc_ld_16x256b_x4(t_tmem + lane_field + (uint32_t)(128 * b + 32 * half), r1);
+                    tc_ld_16x256b_x4(t_tmem + lane_field + (uint32_t)(128 * b + 64 + 32 * half), r2);
+                    const BlockDesc d = bars->descs[g][st];         // the block's descriptor, from the producer
                     const int q0 = d.row() * kTile + 32 * half + 2 * q4;        // query position of column u = 0, e = 0
                     // Masked positions (bit 2u + e of the low byte: row a, column 32 half + 8u + 2 q4 + e; bits 8-15: row b):
                     // padded key rows, queries before the key (causal), quadrants outside a block-32 layout (the lane's
@@ -283,14 +288,6 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
                                 }
                         }
                     }
-                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->t_full[g][b], (uint32_t)(t >> 1) & 1u, abort_flag, p.status)) != 0;
-                    // (complete already: the block's T products waited for the stage; observed here for the statistics)
-                    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->y_full[g][st], (uint32_t)(t >> 2) & 1u, abort_flag, p.status)) != 0;
-                    if (!ok) break;
-                    tc_fence_after();
-                    uint32_t r1[16], r2[16];
-                    tc_ld_16x256b_x4(t_tmem + lane_field + (uint32_t)(128 * b + 32 * half), r1);
-                    tc_ld_16x256b_x4(t_tmem + lane_field + (uint32_t)(128 * b + 64 + 32 * half), r2);
                     // (lse2, D) of this lane's 16 query columns, brought into the block's stage by the producer:
                     // cs[u] = those of columns 32 half + 8u + 2 q4 and + 1
                     float4 cs[4];
@@ -342,7 +339,6 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
                 if (!ok) break;
                 // The cursor moves on before the wait for the accumulators: the bookkeeping of the next column runs
                 // while the column's last products are in flight, not after its results have been written.
-                pre = pre_next;
                 cur.advance();
                 // ---- end of the column: dV and dK to global memory
                 ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[g], (uint32_t)i_no & 1u, abort_flag, p.status)) != 0;

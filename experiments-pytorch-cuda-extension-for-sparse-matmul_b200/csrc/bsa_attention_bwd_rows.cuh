@@ -30,6 +30,7 @@ struct __align__(8) BwdRowBarriers {
     uint64_t drain;
     uint32_t tmem_base;
     int abort_flag;
+    BlockDesc descs[2][2];                      // [pipeline][block & 1]: written by the producer for the compute warps
 };
 constexpr int kBwdRowTiles = 6;                 // per pipeline: Q, dO, (K, V) x 2
 
@@ -100,10 +101,12 @@ attention_backward_rows_pipes_kernel(const __grid_constant__ CUtensorMap map_q, 
                 DescWindow win;
                 win.begin(p.blocks, cur.first, cur.count, pre, lane);
                 for (int j = 0; ok && j < n; ++j) {
-                    const int col = win.get(p.blocks, cur.first, cur.count, j, lane).col();
+                    const BlockDesc desc = win.get(p.blocks, cur.first, cur.count, j, lane);
+                    const int col = desc.col();
                     const int t = t0 + j, st = t & 1;
                     ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_done[g][st], ((uint32_t)(t >> 1) & 1u) ^ 1u, abort_flag, p.status)) != 0;
                     if (ok && elect_one()) {
+                        bars->descs[g][st] = desc;      // for the compute warps; the slot is free like the stage
                         mbar_expect_tx(&bars->y_full[g][st], (uint32_t)(2 * kTileBytes));
                         tma_load_3d(y_smem + (2 * st) * kTileBytes, &map_k, &bars->y_full[g][st], 0, col * kTile, cur.z);
                         tma_load_3d(y_smem + (2 * st + 1) * kTileBytes, &map_v, &bars->y_full[g][st], 0, col * kTile, cur.z);
@@ -209,10 +212,7 @@ attention_backward_rows_pipes_kernel(const __grid_constant__ CUtensorMap map_q, 
         bool ok = true;
         Cursor cur;
         cur.init_as(p, walker, walkers);
-        BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
         while (ok && cur.valid()) {
-            BlockDesc pre_next{0, 0};
-            if (cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
             const int n = cur.count;
             const size_t out_a = ((size_t)cur.z * p.seq_q + (size_t)cur.g * kTile + row_a) * kTile;
             const size_t out_b = out_a + (size_t)8 * kTile;
@@ -222,7 +222,6 @@ attention_backward_rows_pipes_kernel(const __grid_constant__ CUtensorMap map_q, 
                     *reinterpret_cast<uint4*>(p.out0 + out_a + c) = make_uint4(0u, 0u, 0u, 0u);
                     *reinterpret_cast<uint4*>(p.out0 + out_b + c) = make_uint4(0u, 0u, 0u, 0u);
                 }
-                pre = pre_next;
                 cur.advance();
             } else {
                 const uint8_t* kpm_row = (MASKED && p.kpm) ? p.kpm + (size_t)(cur.z / p.kpm_div) * p.kpm_stride : nullptr;
@@ -232,17 +231,21 @@ attention_backward_rows_pipes_kernel(const __grid_constant__ CUtensorMap map_q, 
                 // per row: -lse2 for the exponent and -D * scale for dS = P * (dP * scale - D * scale)
                 const uint64_t nla = f2_pack(-st_a.x, -st_a.x), nlb = f2_pack(-st_b.x, -st_b.x);
                 const uint64_t nda = f2_pack(-st_a.y * sc, -st_a.y * sc), ndb = f2_pack(-st_b.y * sc, -st_b.y * sc);
-                DescWindow win;
-                win.begin(p.blocks, cur.first, cur.count, pre, lane);
                 for (int j = 0; ok && j < n; ++j) {
                     const int t = t0 + j, b = t & 1;
-                    const BlockDesc d = win.get(p.blocks, cur.first, cur.count, j, lane);
-                    const int col = d.col();
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->t_full[g], (uint32_t)t & 1u, abort_flag, p.status)) != 0;
+                    if (!ok) break;
+                    tc_fence_after();
+                    uint32_t r1[32], r2[32];
+                    tc_ld_16x256b_x8(t1_tmem + lane_field, r1);
+                    tc_ld_16x256b_x8(t2_tmem + lane_field, r2);
                     // Masked positions (bit 2u + e of the low half: row a, column 8u + 2 q4 + e; high half: row b):
-                    // above the diagonal, padded keys, quadrants outside a block-32 layout.  Computed before the
-                    // wait for the block's products: off the critical chain.
+                    // above the diagonal, padded keys, quadrants outside a block-32 layout.  Computed while the
+                    // products are on their way from tensor memory; the block's descriptor comes from the producer.
                     uint32_t mask = 0u;
                     if (MASKED && masked_op) {
+                        const BlockDesc d = bars->descs[g][b];
+                        const int col = d.col();
                         if (p.quadrants) {
                             const uint32_t present = (uint32_t)d.idx >> (2 * (quad >> 1));
                             if (!(present & 1u)) mask |= 0x00FF00FFu;
@@ -267,12 +270,6 @@ attention_backward_rows_pipes_kernel(const __grid_constant__ CUtensorMap map_q, 
                             }
                         }
                     }
-                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->t_full[g], (uint32_t)t & 1u, abort_flag, p.status)) != 0;
-                    if (!ok) break;
-                    tc_fence_after();
-                    uint32_t r1[32], r2[32];
-                    tc_ld_16x256b_x8(t1_tmem + lane_field, r1);
-                    tc_ld_16x256b_x8(t2_tmem + lane_field, r2);
                     tc_wait_ld();
                     release_accumulator(&bars->t_empty[g], lane);       // T is in registers: the next block's products may run
                     // Is the dS buffer free (accumulation of block t - 2 retired)?  Tested now, needed after the arithmetic.
@@ -314,7 +311,6 @@ attention_backward_rows_pipes_kernel(const __grid_constant__ CUtensorMap map_q, 
                 if (!ok) break;
                 // The cursor moves on before the wait for the accumulator: the bookkeeping of the next row runs
                 // while the row's last product is in flight, not after the row's results have been written.
-                pre = pre_next;
                 cur.advance();
                 // ---- end of the row: dQ to global memory
                 ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[g], (uint32_t)i_no & 1u, abort_flag, p.status)) != 0;

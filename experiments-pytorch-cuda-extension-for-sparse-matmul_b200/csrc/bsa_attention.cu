@@ -629,6 +629,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 constexpr int kPipeTiles = 6;                   // Q, K x 3, V x 2
 constexpr int kPipeKRing = 3;
 constexpr int kPipeDescs = 8;
+constexpr int kPipeRows = 8;
 struct __align__(8) PipeBarriers {
     uint64_t q_full[2], q_empty[2];             // [pipeline]
     uint64_t k_full[2][kPipeKRing], qk_done[2][kPipeKRing];   // [pipeline][K stage]: qk_done = S is ready and the K stage is free
@@ -639,6 +640,8 @@ struct __align__(8) PipeBarriers {
     uint32_t tmem_base;
     int abort_flag;
     BlockDesc descs[2][kPipeDescs];             // [pipeline][tile & 7]: written by the producer for the softmax warps
+    uint64_t row_full[2][kPipeRows];            // [pipeline][row & 7]: the row's entry in `rows` is valid
+    int4 rows[2][kPipeRows];                    // (batch entry, block row, blocks, -): written by the producer; blocks = 0: no more rows
 };
 
 // Position of a tile in the ring of three K stages (every role counts the tiles it has handled).
@@ -671,6 +674,7 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
                 mbar_init(&bars->s_empty[i][s], 4); mbar_init(&bars->p_full[i][s], 4);
             }
             mbar_init(&bars->o_full[i], 1); mbar_init(&bars->o_empty[i], 4);
+            for (int s = 0; s < kPipeRows; ++s) mbar_init(&bars->row_full[i][s], 1);
         }
         mbar_init(&bars->drain, 2);
         bars->abort_flag = 0;
@@ -719,10 +723,20 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
             BlockDesc pre_next{0, 0};
             if (cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
             const int n = cur.count;
-            if (n > 0) {
+            if (n == 0) {
+                // a block row without blocks: zeros, lse = -inf (the other roles never see the row)
+                const size_t row0 = (size_t)cur.z * p.seq_q + (size_t)cur.g * kTile;
+                for (int c = lane; c < kTile * kTile / 8; c += 32)
+                    reinterpret_cast<uint4*>(p.o + row0 * kTile)[c] = make_uint4(0u, 0u, 0u, 0u);
+                if (p.lse) { p.lse[row0 + lane] = -INFINITY; p.lse[row0 + 32 + lane] = -INFINITY; }
+            } else {
                 // Q once the last Q K^T of the row before has retired
                 ok = __all_sync(0xffffffffu, mbar_wait(&bars->q_empty[g], ((uint32_t)i_no & 1u) ^ 1u, abort_flag, p.status)) != 0;
                 if (ok && elect_one()) {
+                    // The row's entry for the issuer and the softmax warps: they are at most three rows behind
+                    // (the wait above: the softmax warps have taken the S tile two tiles before that row's last).
+                    bars->rows[g][i_no & (kPipeRows - 1)] = make_int4(cur.z, cur.g, n, 0);
+                    mbar_arrive(&bars->row_full[g][i_no & (kPipeRows - 1)]);
                     mbar_expect_tx(&bars->q_full[g], (uint32_t)kTileBytes);
                     tma_load_3d(q_smem, &map_q, &bars->q_full[g], 0, cur.g * kTile, cur.z);
                 }
@@ -754,6 +768,11 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
             pre = pre_next;
             cur.advance();
         }
+        if (ok && elect_one()) {                    // no more rows
+            bars->rows[g][i_no & (kPipeRows - 1)] = make_int4(0, 0, 0, 0);
+            mbar_arrive(&bars->row_full[g][i_no & (kPipeRows - 1)]);
+        }
+        __syncwarp();
         if (lane == 0 && *(volatile int*)abort_flag) {
             // Give copies that were issued a bounded chance to land before the CTA exits.
             const unsigned long long tw = global_ns();
@@ -803,11 +822,13 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
             __syncwarp();
             return true;
         };
-        Cursor cur;
-        cur.init_as(p, walker, walkers);
-        for (; ok && cur.valid(); cur.advance()) {
-            const int n = cur.count;
-            if (n == 0) continue;                   // a row without blocks: the softmax warps write zeros on their own
+        while (ok) {
+            // the row's entry from the producer (rows without blocks never get here)
+            const int slot = i_no & (kPipeRows - 1);
+            ok = __all_sync(0xffffffffu, mbar_wait(&bars->row_full[g][slot], (uint32_t)(i_no / kPipeRows) & 1u, abort_flag, p.status)) != 0;
+            if (!ok) break;
+            const int n = bars->rows[g][slot].z;
+            if (n == 0) break;                      // no more rows
             ok = __all_sync(0xffffffffu, mbar_wait(&bars->q_full[g], (uint32_t)i_no & 1u, abort_flag, p.status)) != 0;
             for (int j = 0; ok && j < n; ++j) {
                 const int t = t0 + j, b = t & 1;
@@ -852,24 +873,21 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
         int t0 = 0, i_no = 0;                       // tiles and non-empty rows before the current row
         KRing kr;                                   // K stage (= qk_done barrier) of the next tile to be requested from TMEM
         bool ok = true;
-        Cursor cur;
-        cur.init_as(p, walker, walkers);
-        while (ok && cur.valid()) {
-            const int n = cur.count;
-            const size_t o_row_a = ((size_t)cur.z * p.seq_q + (size_t)cur.g * kTile + row_a) * kTile;
+        while (ok) {
+            // The row's entry from the producer (which walks the work items; rows without blocks never get here).
+            // The bookkeeping of a work-item cursor in these warps cost 2 000 cycles per row.
+            const int slot = i_no & (kPipeRows - 1);
+            ok = __all_sync(0xffffffffu, mbar_wait(&bars->row_full[g][slot], (uint32_t)(i_no / kPipeRows) & 1u, abort_flag, p.status)) != 0;
+            if (!ok) break;
+            const int4 row = bars->rows[g][slot];
+            const int n = row.z;
+            if (n == 0) break;                      // no more rows
+            const size_t lse_a = (size_t)row.x * p.seq_q + (size_t)row.y * kTile + row_a;
+            const size_t o_row_a = lse_a * kTile;
             const size_t o_row_b = o_row_a + (size_t)8 * kTile;
-            const size_t lse_a = (size_t)cur.z * p.seq_q + (size_t)cur.g * kTile + row_a;
-            if (n == 0) {
-                // a block row without blocks: zeros, lse = -inf
-                for (int c = q4 * 8; c < kTile; c += 32) {
-                    *reinterpret_cast<uint4*>(p.o + o_row_a + c) = make_uint4(0u, 0u, 0u, 0u);
-                    *reinterpret_cast<uint4*>(p.o + o_row_b + c) = make_uint4(0u, 0u, 0u, 0u);
-                }
-                if (q4 == 0 && p.lse) { p.lse[lse_a] = -INFINITY; p.lse[lse_a + 8] = -INFINITY; }
-                cur.advance();
-            } else {
-                const uint8_t* kpm_row = p.kpm ? p.kpm + (size_t)(cur.z / p.kpm_div) * p.kpm_stride : nullptr;
-                const int qpos_a = cur.g * kTile + row_a;
+            {
+                const uint8_t* kpm_row = p.kpm ? p.kpm + (size_t)(row.x / p.kpm_div) * p.kpm_stride : nullptr;
+                const int qpos_a = row.y * kTile + row_a;
                 // Bits 0-15: columns (u, e) of row a that are masked in block `col`; bits 16-31: row b.
                 auto block_mask = [&](const BlockDesc& desc) -> uint32_t {
                     const int col = desc.col();
@@ -1041,9 +1059,6 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
                 }
                 t0 += n;
                 if (!ok) break;
-                // The cursor moves on before the wait for the accumulator: the bookkeeping of the next row runs
-                // while the row's last product is in flight, not after the row's results have been written.
-                cur.advance();
                 // ---- end of the row: O / l and the log-sum-exp
                 float l_a, l_b;
                 {

@@ -22,7 +22,8 @@
 //                    (lse2, D) of its query rows (four stages)
 //   warps 17, 20     issuer of T1 and T2
 //   warps 18, 21     issuer of the two accumulations
-struct __align__(8) BwdColBarriers {
+constexpr int kBwdColItems = 8;
+struct __align__(16) BwdColBarriers {
     uint64_t x_full[2], x_empty[2];             // [pipeline]
     uint64_t y_full[2][4], y_free[2][4];        // [pipeline][block & 3]: y_free = the accumulations of the block have retired
     uint64_t t_full[2][2], t_empty[2][2];       // [pipeline][block & 1]
@@ -32,6 +33,8 @@ struct __align__(8) BwdColBarriers {
     uint32_t tmem_base;
     int abort_flag;
     BlockDesc descs[2][4];                      // [pipeline][block & 3]: written by the producer for the compute warps
+    uint64_t col_full[2][kBwdColItems];         // [pipeline][column & 7]: the column's entry in `cols` is valid
+    int4 cols[2][kBwdColItems];                 // (batch entry, block column, blocks, -): written by the producer; blocks = 0: no more columns
 };
 constexpr int kBwdColRing = 4;
 constexpr int kBwdColTiles = 2 + 2 * kBwdColRing;       // per pipeline: K, V, (Q, dO) x 4
@@ -62,6 +65,7 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
                 mbar_init(&bars->t_full[i][s], 1); mbar_init(&bars->t_empty[i][s], 8);
                 mbar_init(&bars->op_full[i][s], 8); mbar_init(&bars->op_free[i][s], 1);
             }
+            for (int s = 0; s < kBwdColItems; ++s) mbar_init(&bars->col_full[i][s], 1);
             mbar_init(&bars->o_full[i], 1); mbar_init(&bars->o_empty[i], 8);
         }
         mbar_init(&bars->drain, 4);
@@ -96,10 +100,22 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
             BlockDesc pre_next{0, 0};
             if (cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
             const int n = cur.count;
-            if (n > 0) {
+            if (n == 0) {
+                // a column without blocks: zero gradient rows (the other roles never see the column)
+                const size_t row0 = (size_t)cur.z * p.seq_k + (size_t)cur.g * kTile;
+                for (int c = lane; c < kTile * kTile / 8; c += 32) {
+                    reinterpret_cast<uint4*>(p.out0 + row0 * kTile)[c] = make_uint4(0u, 0u, 0u, 0u);
+                    reinterpret_cast<uint4*>(p.out1 + row0 * kTile)[c] = make_uint4(0u, 0u, 0u, 0u);
+                }
+            } else {
                 // the X pair once the last T products of the column before have retired
                 ok = __all_sync(0xffffffffu, mbar_wait(&bars->x_empty[g], ((uint32_t)i_no & 1u) ^ 1u, abort_flag, p.status)) != 0;
                 if (ok && elect_one()) {
+                    // The column's entry for the issuers and the compute warps: they are at most three columns
+                    // behind (the wait above: the compute warps have taken the T tiles two blocks before that
+                    // column's last).
+                    bars->cols[g][i_no & (kBwdColItems - 1)] = make_int4(cur.z, cur.g, n, 0);
+                    mbar_arrive(&bars->col_full[g][i_no & (kBwdColItems - 1)]);
                     mbar_expect_tx(&bars->x_full[g], (uint32_t)(2 * kTileBytes));
                     tma_load_3d(x_smem, &map_k, &bars->x_full[g], 0, cur.g * kTile, cur.z);
                     tma_load_3d(x_smem + kTileBytes, &map_v, &bars->x_full[g], 0, cur.g * kTile, cur.z);
@@ -129,6 +145,11 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
             pre = pre_next;
             cur.advance();
         }
+        if (ok && elect_one()) {                    // no more columns
+            bars->cols[g][i_no & (kBwdColItems - 1)] = make_int4(0, 0, 0, 0);
+            mbar_arrive(&bars->col_full[g][i_no & (kBwdColItems - 1)]);
+        }
+        __syncwarp();
         if (lane == 0 && *(volatile int*)abort_flag) {
             // Give copies that were issued a bounded chance to land before the CTA exits.
             const unsigned long long tw = global_ns();
@@ -145,11 +166,13 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
         const uint64_t x2_desc = make_tile_desc(smem_u32(x_smem + kTileBytes), false);
         int t0 = 0, i_no = 0;
         bool ok = true;
-        Cursor cur;
-        cur.init_as(p, walker, walkers);
-        for (; ok && cur.valid(); cur.advance()) {
-            const int n = cur.count;
-            if (n == 0) continue;                   // a column without blocks: the compute warps write zeros on their own
+        while (ok) {
+            // the column's entry from the producer (columns without blocks never get here)
+            const int slot = i_no & (kBwdColItems - 1);
+            ok = __all_sync(0xffffffffu, mbar_wait(&bars->col_full[g][slot], (uint32_t)(i_no / kBwdColItems) & 1u, abort_flag, p.status)) != 0;
+            if (!ok) break;
+            const int n = bars->cols[g][slot].z;
+            if (n == 0) break;                      // no more columns
             ok = __all_sync(0xffffffffu, mbar_wait(&bars->x_full[g], (uint32_t)i_no & 1u, abort_flag, p.status)) != 0;
             for (int j = 0; ok && j < n; ++j) {
                 const int t = t0 + j, st = t & (kBwdColRing - 1), b = t & 1;
@@ -185,11 +208,13 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
         // ------------------------------------------------------------ issuer of dV += P^T dO_r and dK += dS^T Q_r
         int t0 = 0, i_no = 0;
         bool ok = true;
-        Cursor cur;
-        cur.init_as(p, walker, walkers);
-        for (; ok && cur.valid(); cur.advance()) {
-            const int n = cur.count;
-            if (n == 0) continue;
+        while (ok) {
+            // the column's entry from the producer (columns without blocks never get here)
+            const int slot = i_no & (kBwdColItems - 1);
+            ok = __all_sync(0xffffffffu, mbar_wait(&bars->col_full[g][slot], (uint32_t)(i_no / kBwdColItems) & 1u, abort_flag, p.status)) != 0;
+            if (!ok) break;
+            const int n = bars->cols[g][slot].z;
+            if (n == 0) break;                      // no more columns
             // the accumulators are free once the column before has been read out
             if (i_no > 0) ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_empty[g], (uint32_t)(i_no - 1) & 1u, abort_flag, p.status)) != 0;
             for (int j = 0; ok && j < n; ++j) {
@@ -235,25 +260,19 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
         const uint64_t c2p = f2_pack(c2, c2), scp = f2_pack(sc, sc);
         int t0 = 0, i_no = 0;
         bool ok = true;
-        Cursor cur;
-        cur.init_as(p, walker, walkers);
-        while (ok && cur.valid()) {
-            const int n = cur.count;
-            const size_t out_a = ((size_t)cur.z * p.seq_k + (size_t)cur.g * kTile + row_a) * kTile;
+        while (ok) {
+            // The column's entry from the producer (which walks the work items; columns without blocks never get here).
+            const int slot = i_no & (kBwdColItems - 1);
+            ok = __all_sync(0xffffffffu, mbar_wait(&bars->col_full[g][slot], (uint32_t)(i_no / kBwdColItems) & 1u, abort_flag, p.status)) != 0;
+            if (!ok) break;
+            const int4 item = bars->cols[g][slot];
+            const int n = item.z;
+            if (n == 0) break;                      // no more columns
+            const size_t out_a = ((size_t)item.x * p.seq_k + (size_t)item.y * kTile + row_a) * kTile;
             const size_t out_b = out_a + (size_t)8 * kTile;
-            if (n == 0) {
-                // a column without blocks: zero gradient rows
-                {
-                    const int c = 32 * half + q4 * 8;
-                    *reinterpret_cast<uint4*>(p.out0 + out_a + c) = make_uint4(0u, 0u, 0u, 0u);
-                    *reinterpret_cast<uint4*>(p.out0 + out_b + c) = make_uint4(0u, 0u, 0u, 0u);
-                    *reinterpret_cast<uint4*>(p.out1 + out_a + c) = make_uint4(0u, 0u, 0u, 0u);
-                    *reinterpret_cast<uint4*>(p.out1 + out_b + c) = make_uint4(0u, 0u, 0u, 0u);
-                }
-                cur.advance();
-            } else {
-                const uint8_t* kpm_row = (MASKED && p.kpm) ? p.kpm + (size_t)(cur.z / p.kpm_div) * p.kpm_stride : nullptr;
-                const int pos_a = cur.g * kTile + row_a;         // key position of row a (row b: + 8)
+            {
+                const uint8_t* kpm_row = (MASKED && p.kpm) ? p.kpm + (size_t)(item.x / p.kpm_div) * p.kpm_stride : nullptr;
+                const int pos_a = item.y * kTile + row_a;        // key position of row a (row b: + 8)
                 // a whole key row is padding or not
                 bool pad_a = false, pad_b = false;
                 if (MASKED && kpm_row) { pad_a = kpm_row[pos_a] != 0; pad_b = kpm_row[pos_a + 8] != 0; }
@@ -337,9 +356,6 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
                 }
                 t0 += n;
                 if (!ok) break;
-                // The cursor moves on before the wait for the accumulators: the bookkeeping of the next column runs
-                // while the column's last products are in flight, not after its results have been written.
-                cur.advance();
                 // ---- end of the column: dV and dK to global memory
                 ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[g], (uint32_t)i_no & 1u, abort_flag, p.status)) != 0;
                 if (!ok) break;

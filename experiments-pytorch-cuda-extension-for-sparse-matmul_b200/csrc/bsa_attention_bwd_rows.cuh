@@ -21,7 +21,8 @@
 //   warps 0, 2   producer of pipeline 0, 1: the row's X pair, then every block's Y pair (stage t & 1)
 //   warps 1, 3   issuer: T1 and T2 of block t, then the accumulation of block t - 1
 //   warps 4-7, 8-11   compute warpgroup; at the end of the row dQ goes to global memory.
-struct __align__(8) BwdRowBarriers {
+constexpr int kBwdRowRing = 8;
+struct __align__(16) BwdRowBarriers {
     uint64_t x_full[2], x_empty[2];             // [pipeline]
     uint64_t y_full[2][2], acc_done[2][2];      // [pipeline][block & 1]: acc_done = the Y stage and the dS buffer are free
     uint64_t t_full[2], t_empty[2];
@@ -31,6 +32,8 @@ struct __align__(8) BwdRowBarriers {
     uint32_t tmem_base;
     int abort_flag;
     BlockDesc descs[2][2];                      // [pipeline][block & 1]: written by the producer for the compute warps
+    uint64_t row_full[2][kBwdRowRing];          // [pipeline][row & 7]: the row's entry in `rows` is valid
+    int4 rows[2][kBwdRowRing];                  // (batch entry, block row, blocks, -): written by the producer; blocks = 0: no more rows
 };
 constexpr int kBwdRowTiles = 6;                 // per pipeline: Q, dO, (K, V) x 2
 
@@ -57,6 +60,7 @@ attention_backward_rows_pipes_kernel(const __grid_constant__ CUtensorMap map_q, 
                 mbar_init(&bars->ds_full[i][s], 4);
             }
             mbar_init(&bars->o_full[i], 1); mbar_init(&bars->o_empty[i], 4);
+            for (int s = 0; s < kBwdRowRing; ++s) mbar_init(&bars->row_full[i][s], 1);
         }
         mbar_init(&bars->drain, 2);
         bars->abort_flag = 0;
@@ -89,10 +93,19 @@ attention_backward_rows_pipes_kernel(const __grid_constant__ CUtensorMap map_q, 
             BlockDesc pre_next{0, 0};
             if (cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
             const int n = cur.count;
-            if (n > 0) {
+            if (n == 0) {
+                // a row without blocks: zero gradient rows (the other roles never see the row)
+                const size_t row0 = (size_t)cur.z * p.seq_q + (size_t)cur.g * kTile;
+                for (int c = lane; c < kTile * kTile / 8; c += 32)
+                    reinterpret_cast<uint4*>(p.out0 + row0 * kTile)[c] = make_uint4(0u, 0u, 0u, 0u);
+            } else {
                 // the X pair once the last T products of the row before have retired
                 ok = __all_sync(0xffffffffu, mbar_wait(&bars->x_empty[g], ((uint32_t)i_no & 1u) ^ 1u, abort_flag, p.status)) != 0;
                 if (ok && elect_one()) {
+                    // The row's entry for the issuer and the compute warps: they are at most two rows behind
+                    // (the wait above: the compute warps have taken the T tiles of the block before that row's last).
+                    bars->rows[g][i_no & (kBwdRowRing - 1)] = make_int4(cur.z, cur.g, n, 0);
+                    mbar_arrive(&bars->row_full[g][i_no & (kBwdRowRing - 1)]);
                     mbar_expect_tx(&bars->x_full[g], (uint32_t)(2 * kTileBytes));
                     tma_load_3d(x_smem, &map_q, &bars->x_full[g], 0, cur.g * kTile, cur.z);
                     tma_load_3d(x_smem + kTileBytes, &map_do, &bars->x_full[g], 0, cur.g * kTile, cur.z);
@@ -119,6 +132,11 @@ attention_backward_rows_pipes_kernel(const __grid_constant__ CUtensorMap map_q, 
             pre = pre_next;
             cur.advance();
         }
+        if (ok && elect_one()) {                    // no more rows
+            bars->rows[g][i_no & (kBwdRowRing - 1)] = make_int4(0, 0, 0, 0);
+            mbar_arrive(&bars->row_full[g][i_no & (kBwdRowRing - 1)]);
+        }
+        __syncwarp();
         if (lane == 0 && *(volatile int*)abort_flag) {
             // Give copies that were issued a bounded chance to land before the CTA exits.
             const unsigned long long tw = global_ns();
@@ -162,11 +180,13 @@ attention_backward_rows_pipes_kernel(const __grid_constant__ CUtensorMap map_q, 
             __syncwarp();
             return true;
         };
-        Cursor cur;
-        cur.init_as(p, walker, walkers);
-        for (; ok && cur.valid(); cur.advance()) {
-            const int n = cur.count;
-            if (n == 0) continue;                   // a row without blocks: the compute warps write zeros on their own
+        while (ok) {
+            // the row's entry from the producer (rows without blocks never get here)
+            const int slot = i_no & (kBwdRowRing - 1);
+            ok = __all_sync(0xffffffffu, mbar_wait(&bars->row_full[g][slot], (uint32_t)(i_no / kBwdRowRing) & 1u, abort_flag, p.status)) != 0;
+            if (!ok) break;
+            const int n = bars->rows[g][slot].z;
+            if (n == 0) break;                      // no more rows
             ok = __all_sync(0xffffffffu, mbar_wait(&bars->x_full[g], (uint32_t)i_no & 1u, abort_flag, p.status)) != 0;
             for (int j = 0; ok && j < n; ++j) {
                 const int t = t0 + j, st = t & 1;
@@ -210,23 +230,20 @@ attention_backward_rows_pipes_kernel(const __grid_constant__ CUtensorMap map_q, 
         const uint64_t c2p = f2_pack(c2, c2), scp = f2_pack(sc, sc);
         int t0 = 0, i_no = 0;
         bool ok = true;
-        Cursor cur;
-        cur.init_as(p, walker, walkers);
-        while (ok && cur.valid()) {
-            const int n = cur.count;
-            const size_t out_a = ((size_t)cur.z * p.seq_q + (size_t)cur.g * kTile + row_a) * kTile;
+        while (ok) {
+            // The row's entry from the producer (which walks the work items; rows without blocks never get here).
+            const int slot = i_no & (kBwdRowRing - 1);
+            ok = __all_sync(0xffffffffu, mbar_wait(&bars->row_full[g][slot], (uint32_t)(i_no / kBwdRowRing) & 1u, abort_flag, p.status)) != 0;
+            if (!ok) break;
+            const int4 row = bars->rows[g][slot];
+            const int n = row.z;
+            if (n == 0) break;                      // no more rows
+            const size_t out_a = ((size_t)row.x * p.seq_q + (size_t)row.y * kTile + row_a) * kTile;
             const size_t out_b = out_a + (size_t)8 * kTile;
-            if (n == 0) {
-                // a row without blocks: zero gradient rows
-                for (int c = q4 * 8; c < kTile; c += 32) {
-                    *reinterpret_cast<uint4*>(p.out0 + out_a + c) = make_uint4(0u, 0u, 0u, 0u);
-                    *reinterpret_cast<uint4*>(p.out0 + out_b + c) = make_uint4(0u, 0u, 0u, 0u);
-                }
-                cur.advance();
-            } else {
-                const uint8_t* kpm_row = (MASKED && p.kpm) ? p.kpm + (size_t)(cur.z / p.kpm_div) * p.kpm_stride : nullptr;
-                const int pos_a = cur.g * kTile + row_a;         // query position of row a (row b: + 8)
-                const float2* stats_z = p.stats + (size_t)cur.z * p.seq_q;
+            {
+                const uint8_t* kpm_row = (MASKED && p.kpm) ? p.kpm + (size_t)(row.x / p.kpm_div) * p.kpm_stride : nullptr;
+                const int pos_a = row.y * kTile + row_a;         // query position of row a (row b: + 8)
+                const float2* stats_z = p.stats + (size_t)row.x * p.seq_q;
                 const float2 st_a = stats_z[pos_a], st_b = stats_z[pos_a + 8];     // (lse in log2 units, D)
                 // per row: -lse2 for the exponent and -D * scale for dS = P * (dP * scale - D * scale)
                 const uint64_t nla = f2_pack(-st_a.x, -st_a.x), nlb = f2_pack(-st_b.x, -st_b.x);
@@ -309,9 +326,6 @@ attention_backward_rows_pipes_kernel(const __grid_constant__ CUtensorMap map_q, 
                 }
                 t0 += n;
                 if (!ok) break;
-                // The cursor moves on before the wait for the accumulator: the bookkeeping of the next row runs
-                // while the row's last product is in flight, not after the row's results have been written.
-                cur.advance();
                 // ---- end of the row: dQ to global memory
                 ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[g], (uint32_t)i_no & 1u, abort_flag, p.status)) != 0;
                 if (!ok) break;

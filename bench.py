@@ -191,12 +191,12 @@ def device_step(ops, lay, q, k, v, do, scale, block, events=None, causal=False):
     ]
     keys = ["s", "p", "o", "dp", "dv", "ds", "dq", "dk"]
     st = {}
-    if events is not None:
-        events[0].record()
     for i, (call, key) in enumerate(zip(calls, keys)):
+        if events is not None:
+            events[i][0].record()
         st[key] = call(st)
         if events is not None:
-            events[i + 1].record()         # one event per boundary: op i took events[i] .. events[i + 1]
+            events[i][1].record()
     return st
 
 
@@ -313,7 +313,7 @@ def side_cfg5_strong(sparse_ops, dev, world, dist):
     for _ in range(2):
         device_step(sparse_ops, lay, q, k, v, do, scale, block)
     steps = 3
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(OPS) + 1)] for _ in range(steps)]
+    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in OPS] for _ in range(steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if world > 1:
         dist.barrier()
@@ -333,7 +333,7 @@ def side_cfg5_strong(sparse_ops, dev, world, dist):
     peaks = load_peaks()
     ops = {}
     for j, name in enumerate(OPS):
-        t = sum(ev[i][j].elapsed_time(ev[i][j + 1]) for i in range(steps)) / steps
+        t = sum(ev[i][j][0].elapsed_time(ev[i][j][1]) for i in range(steps)) / steps
         byts = {"softmax_fwd": 2 * sparse_bytes, "softmax_bwd": 3 * sparse_bytes}.get(name, sparse_bytes + 2 * dense_bytes)
         ops[name] = {"ms": round(t, 3), "hbm_frac": round(byts / (t * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)}
     del q, k, v, do
@@ -427,15 +427,18 @@ def run_ours(args):
         stop.record()
         barrier()
         region_ms.append(start.elapsed_time(stop))
-    # ---- per-op times: the same loop once more with one event on every boundary between two launches
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(OPS) + 1)] for _ in range(args.steps)]
+    # ---- per-op times: the same loop once more with a pair of events around every launch
+    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in OPS] for _ in range(args.steps)]
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    start.record()
     for i in range(args.steps):
         device_step(sparse_ops, lay, q, k, v, do, scale, block, ev[i])
+    stop.record()
     barrier()
-    op_ms = {name: sum(ev[i][j].elapsed_time(ev[i][j + 1]) for i in range(args.steps)) / args.steps
+    op_ms = {name: sum(ev[i][j][0].elapsed_time(ev[i][j][1]) for i in range(args.steps)) / args.steps
              for j, name in enumerate(OPS)}
-    instrumented_ms = sum(op_ms.values())
+    instrumented_ms = start.elapsed_time(stop) / args.steps
     # ---- the step replayed from a CUDA graph (no launch gaps): reported beside the eager value
     graph_ms = graph_replayed(lambda: device_step(sparse_ops, lay, q, k, v, do, scale, block), args.steps)
     sparse_ops.check_device_status(local_rank)

@@ -499,10 +499,25 @@ def run_ours(args):
     clocks = sampler.stop() if sampler else None
     del dev_in, dev_out, outs_host
 
+    # ---- every op of the step alone: 20 launches of the same op back to back between two events (the pair of
+    # events around a launch inside the step adds about 5 us of launch latency to every op of `ops`)
+    st_ = device_step(sparse_ops, lay, q, k, v, do, scale, block)
+    rl_, cl_ = lay.row_layout, lay.col_layout
+    alone_calls = {
+        "sdd_qk": lambda: sparse_ops.sparse_matmul(q, k, "sdd", rl_, cl_, False, True, block),
+        "softmax_fwd": lambda: sparse_ops.sparse_softmax_forward(st_["s"], rl_[0], rl_[1], scale, False, None, lay.max_row_blocks),
+        "dsd_pv": lambda: sparse_ops.sparse_matmul(st_["p"], v, "dsd", rl_, cl_, False, False, block),
+        "sdd_dp": lambda: sparse_ops.sparse_matmul(do, v, "sdd", rl_, cl_, False, True, block),
+        "dsd_dv": lambda: sparse_ops.sparse_matmul(st_["p"], do, "dsd", rl_, cl_, True, False, block),
+        "softmax_bwd": lambda: sparse_ops.sparse_softmax_backward(st_["p"], st_["dp"], rl_[0], rl_[1], scale, lay.max_row_blocks),
+        "dsd_dq": lambda: sparse_ops.sparse_matmul(st_["ds"], k, "dsd", rl_, cl_, False, False, block),
+        "dsd_dk": lambda: sparse_ops.sparse_matmul(st_["ds"], q, "dsd", rl_, cl_, True, False, block),
+    }
+    alone_ms = {name: timed(fn, 20) for name, fn in alone_calls.items()}
     # ---- DDS side measurement (not part of the step): dV^T = dO^T . P as dds(T,N)
-    p_blocks = device_step(sparse_ops, lay, q, k, v, do, scale, block)["p"]
+    p_blocks = st_["p"]
     dds_ms = timed(lambda: sparse_ops.sparse_matmul(do, p_blocks, "dds", lay.row_layout, lay.col_layout, True, False, block), 5)
-    del p_blocks
+    del p_blocks, st_, alone_calls
     # the fused forward (one kernel for sdd -> softmax -> dsd) and the fused backward (statistics, dQ by block
     # rows, dK / dV by block columns), reported beside the unfused operators
     from sparse.attention import attention_lse
@@ -545,7 +560,9 @@ def run_ours(args):
         ops_report = {}
         for name in OPS:
             gbs = alg_bytes[name] / (op_ms[name] * 1e-3) / 1e9
-            entry = {"ms": round(op_ms[name], 4), "GB/s": round(gbs, 1), "hbm_frac": round(gbs / peaks["hbm_gbs"], 4)}
+            entry = {"ms": round(op_ms[name], 4), "GB/s": round(gbs, 1), "hbm_frac": round(gbs / peaks["hbm_gbs"], 4),
+                     "alone_ms": round(alone_ms[name], 4),
+                     "alone_hbm_frac": round(alg_bytes[name] / (alone_ms[name] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)}
             if not name.startswith("softmax"):
                 tf = flops_matmul / (op_ms[name] * 1e-3) / 1e12
                 entry["TFLOP/s"] = round(tf, 1)

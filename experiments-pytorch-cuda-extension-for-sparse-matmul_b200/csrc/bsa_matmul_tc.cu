@@ -74,14 +74,22 @@ constexpr int kFirstMmaWarp = kProducerWarps;
 constexpr int kFirstEpilogueWarp = kFirstMmaWarp + kMmaWarps;
 constexpr int threads_of(int mode) { return (kFirstEpilogueWarp + 4 * (mode == BSA_MODE_SDD ? kSddGroups : 2)) * 32; }
 
-struct __align__(8) Barriers {
+// sdd: the epilogue warps do not walk the work items (a cursor and a descriptor window in each of their 16
+// warps, advanced through every accumulation to use one in four).  The producer that loads an accumulation's
+// first K-step posts what they need -- the ranks of the output blocks, their number, the batch entry -- in a
+// ring of entries with one mbarrier each; accumulation number F uses entry F & 31 (the producers are at most
+// 8 stages + 8 accumulator buffers ahead of the epilogue).
+constexpr int kSddEntries = 32;
+struct __align__(16) Barriers {
     uint64_t full[kMaxStages];
     uint64_t empty[kMaxStages];
     uint64_t acc_full[kSddBufs];
     uint64_t acc_empty[kSddBufs];
+    uint64_t ent_full[kSddEntries];
     uint64_t drain;
     uint32_t tmem_base;
     int abort_flag;
+    int4 ents[kSddEntries];         // (rank of output tile 0, of tile 1, tiles, batch entry); tiles = 0: no more accumulations
 };
 constexpr int kSmemBytes = 1024 /* alignment slack */ + kStageTiles * kTileBytes + (int)sizeof(Barriers);
 
@@ -208,6 +216,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMaxStages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
         for (int s = 0; s < kSddBufs; ++s) { mbar_init(&bars->acc_full[s], arrivals); mbar_init(&bars->acc_empty[s], 4); }
+        if (is_sdd) for (int s = 0; s < kSddEntries; ++s) mbar_init(&bars->ent_full[s], 1);
         mbar_init(&bars->drain, (uint32_t)p.issuers);
         bars->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -233,6 +242,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // are steps warp, warp + 4, ... of the CTA, so (the stage count being a multiple of 4)
         // its stage pointer simply advances by 4, whatever the item and accumulation borders.
         int stage = warp, step0 = 0;         // step0: sequence number of the accumulation's first K-step
+        int flush_no = 0;                    // sdd: number of the accumulation
         uint32_t phase = 0;
         bool ok = true;
         Cursor cur;
@@ -253,12 +263,16 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 // every phase of each barrier it ever waits on.
                 for (int k = (warp - step0) & (kProducerWarps - 1); ok && k < ksteps; k += kProducerWarps) {
                     {
-                        int cols[4] = {0, 0, 0, 0};
+                        int cols[4] = {0, 0, 0, 0}, ranks[kSddTiles] = {0, 0};
                         BlockDesc d{0, 0};
                         if (is_sdd) {
 #pragma unroll
                             for (int j = 0; j < 4; ++j)
-                                if (j < nb) cols[j] = tile_desc(win, p, cur, kSddTiles * f + j, lane).col();
+                                if (j < nb) {
+                                    const BlockDesc dj = tile_desc(win, p, cur, kSddTiles * f + j, lane);
+                                    cols[j] = dj.col();
+                                    if (j < kSddTiles) ranks[j] = dj.idx;
+                                }
                         } else {
                             d = tile_desc(win, p, cur, k, lane);
                         }
@@ -269,6 +283,10 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                             if (ok && elect_one()) {
                                 uint8_t* slot = stage_base + stage * stage_bytes;
                                 uint64_t* full = &bars->full[stage];
+                                if (is_sdd && k == 0) {         // the accumulation's entry for the epilogue warps
+                                    bars->ents[flush_no & (kSddEntries - 1)] = make_int4(ranks[0], ranks[1], nb, cur.z);
+                                    mbar_arrive(&bars->ent_full[flush_no & (kSddEntries - 1)]);
+                                }
                                 mbar_expect_tx(full, (uint32_t)((1 + nb) * kTileBytes));
                                 if (is_sdd) {
                                     const int k0 = k * kTile, m0 = cur.g * kTile;
@@ -309,10 +327,19 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     if (stage >= p.stages) { stage -= p.stages; phase ^= 1; }
                 }
                 step0 += ksteps;
+                ++flush_no;
             }
             pre = pre_next;
             cur.advance();
         }
+        if (is_sdd && warp == 0 && ok && elect_one()) {
+            // no more accumulations: one closing entry for each of the epilogue groups
+            for (int e = flush_no; e < flush_no + kSddGroups; ++e) {
+                bars->ents[e & (kSddEntries - 1)] = make_int4(0, 0, 0, 0);
+                mbar_arrive(&bars->ent_full[e & (kSddEntries - 1)]);
+            }
+        }
+        __syncwarp();
         if (lane == 0 && *(volatile int*)&bars->abort_flag) {
             // Give copies that were issued a bounded chance to land before the CTA exits.
             const unsigned long long t0 = global_ns();
@@ -414,168 +441,175 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int row = quad * 16 + lane;            // accumulator row held by this lane (lanes 0-15 only)
         const bool row_lane = lane < 16;
         constexpr bool bf16_out = BF16;
-        const int parts = is_sdd ? 1 : p.issuers;
-        const int part_stride = kAccCols / p.issuers;
-        int flush_no = 0, step = 0;
         bool ok = true;
-        Cursor cur;
-        cur.init(p, p.split);
-        BlockDesc pre{0, 0};
-        if (is_sdd && cur.valid()) pre = load_first_chunk(p.blocks, cur.first, cur.count, lane);
-        while (ok && cur.valid()) {
-            BlockDesc pre_next{0, 0};
-            if (is_sdd && cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
-            int flushes, ksteps;
-            item_shape<MODE>(p, cur.count << p.split, flushes, ksteps);
-            const bool have_acc = ksteps > 0;
-            DescWindow win;
-            if (is_sdd) win.begin(p.blocks, cur.first, cur.count, pre, lane);
-            for (int f = 0; ok && f < flushes; ++f) {
-                // accumulations alternate between the two buffers / groups; groups that write
-                // zeros for an empty group of blocks are chosen by item parity
-                const int owner = have_acc ? (flush_no & (kGroups - 1)) : (cur.item_no & (kGroups - 1));
-                const uint32_t acc_phase = (uint32_t)(flush_no >> kBufShift) & 1u;
-                const int acc = flush_no & (kBufs - 1);     // (dsd / dds: the group's own buffer)
-                const int step0 = step;             // sequence number of this accumulation's first K-step
-                step += ksteps;
-                if (have_acc) ++flush_no;
-                if (owner != group) continue;
-                const int tiles = b_tiles<MODE>(p, cur.count << p.split, cur.chunk, f);
-                if (have_acc) {
-                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_full[acc], acc_phase, &bars->abort_flag, p.status)) != 0;
-                    if (!ok) break;
-                    tc_fence_after();
-                }
-                if (is_sdd) {
-                    // Sparse output tiles leave through shared memory and TMA: the warp converts its 16
-                    // accumulator rows, writes them with four stmatrix instructions (the 16x256b TMEM
-                    // load hands out exactly the m8n8 fragment layout) into its own 128-byte-swizzled
-                    // 2 KB staging slab and sends the slab to global memory with one bulk tensor store
-                    // (box 16 x 64).  About 30 instructions per lane and tile instead of 110 for a
-                    // shuffle-transpose / 128-bit store path, no synchronisation between warps, and
-                    // the stores are asynchronous (one slab per warp: the store of a tile reads it while
-                    // the warp loads and converts its next tile).
-                    const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) + acc_addr(acc);
-                    // lane -> row address of its 8x8 matrix: matrix i = lane / 8 holds rows (i & 1) * 8 ..
-                    // of 16-byte column unit u = 2k + (i >> 1)
-                    const int sm_row = ((lane >> 3) & 1) * 8 + (lane & 7);        // row inside the slab
-                    const uint32_t sm_unit = (uint32_t)(lane >> 4);
-                    const int slab0 = (warp - kFirstEpilogueWarp) * (16 * 128);         // this warp's slab
-                    auto store_tile = [&](const uint32_t (&r)[32], int t) {
-                        const int out_idx = tile_desc(win, p, cur, kSddTiles * f + t, lane).idx;
-                        // a descriptor that does not belong to this layout is reported in the workspace
-                        // (word 1 = offending tile index); the tensor map clips the store itself
-                        const bool in_bounds = out_idx >= 0 && out_idx < p.nnz;
-                        if (!in_bounds && lane == 0) {
-                            atomicExch(p.status, (uint32_t)BSA_ERR_BAD_SHAPE);
-                            atomicExch(p.status + 1, (uint32_t)out_idx);
-                        }
-                        const uint32_t slab = smem_u32(stage_base + kSddStagingTile0 * kTileBytes + slab0);
-                        uint32_t w[16];                         // [4k + i]: matrices (u = 2k, rows a), (2k, b), (2k + 1, a), (2k + 1, b)
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const int u = 2 * k + (i >> 1), h = i & 1;
-                                const float lo = __uint_as_float(r[4 * u + 2 * h]), hi = __uint_as_float(r[4 * u + 2 * h + 1]);
-                                if (bf16_out) { __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi); w[4 * k + i] = *reinterpret_cast<uint32_t*>(&v); }
-                                else          { __half2 v = __floats2half2_rn(lo, hi); w[4 * k + i] = *reinterpret_cast<uint32_t*>(&v); }
-                            }
-                        }
-                        // the slab was sent with the tile before: that store must have read it
-                        if (elect_one()) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                        __syncwarp();
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            const uint32_t addr = slab + (uint32_t)(sm_row * 128) + ((((uint32_t)(2 * k) + sm_unit) ^ (uint32_t)(sm_row & 7)) << 4);
-                            asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1, %2, %3, %4};"
-                                         ::"r"(addr), "r"(w[4 * k]), "r"(w[4 * k + 1]), "r"(w[4 * k + 2]), "r"(w[4 * k + 3]) : "memory");
-                        }
-                        fence_async_shared();           // generic-proxy writes -> visible to the bulk store
-                        __syncwarp();
-                        // (issued from an elected lane of warp-uniform code: the copy's operands stay in
-                        // uniform registers; the same lane every time, the bulk groups are per thread)
-                        int sx, sy;
-                        sparse_xy(p, out_idx, sx, sy);
-                        if (elect_one()) {
-                            if (in_bounds)
-                                asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
-                                             ::"l"(&map_c), "r"(slab), "r"(sx), "r"(sy + quad * 16), "r"(cur.z) : "memory");
-                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");   // (empty groups keep the count regular)
-                        }
-                    };
-                    // one register buffer: the other groups' accumulations cover this one's TMEM load
-                    uint32_t r[32];
-                    for (int t = 0; t < tiles; ++t) {
-                        tc_ld_16x256b_x8(tbase + (uint32_t)(t * kTile), r);
-                        tc_wait_ld();
-                        if (t + 1 >= tiles) release_accumulator(&bars->acc_empty[acc], lane);
-                        store_tile(r, t);
-                    }
-                    continue;
-                }
-                for (int t = 0; t < tiles; ++t) {
-                    // destination of this 64x64 tile: first element, valid rows and columns
-                    size_t dst0;
-                    int rows_valid = kTile, cols_valid = kTile;
-                    if (MODE == BSA_MODE_DSD) {
-                        const int n0 = (cur.chunk * 2 + t) * kTile;
-                        dst0 = ((size_t)cur.z * p.size_m + (size_t)cur.g * kTile) * p.size_n + n0;
-                        cols_valid = min(kTile, p.size_n - n0);
-                    } else {
-                        const int m0 = cur.chunk * kTile;
-                        dst0 = ((size_t)cur.z * p.size_m + m0) * p.size_n + (size_t)cur.g * kTile;
-                        rows_valid = min(kTile, p.size_m - m0);
-                    }
-                    // never write outside the output: a descriptor that does not belong to this
-                    // layout is reported in the workspace instead (word 1 = offending offset >> 12)
-                    const bool in_bounds = dst0 + (size_t)(rows_valid - 1) * p.ldc + cols_valid <= (size_t)p.c_elems;
+        if (is_sdd) {
+            // accumulation F of the CTA: entry F & 31 from the producers, accumulator buffer F & 7; group g takes
+            // the accumulations F = g, g + 4, ...
+            for (int flush = group; ok; flush += kSddGroups) {
+                const int slot = flush & (kSddEntries - 1);
+                ok = __all_sync(0xffffffffu, mbar_wait(&bars->ent_full[slot], (uint32_t)(flush / kSddEntries) & 1u, &bars->abort_flag, p.status)) != 0;
+                if (!ok) break;
+                const int4 ent = bars->ents[slot];
+                const int tiles = ent.z;
+                if (tiles == 0) break;              // no more accumulations
+                const int acc = flush & (kBufs - 1);
+                ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_full[acc], (uint32_t)(flush >> kBufShift) & 1u, &bars->abort_flag, p.status)) != 0;
+                if (!ok) break;
+                tc_fence_after();
+                // Sparse output tiles leave through shared memory and TMA: the warp converts its 16
+                // accumulator rows, writes them with four stmatrix instructions (the 16x256b TMEM
+                // load hands out exactly the m8n8 fragment layout) into its own 128-byte-swizzled
+                // 2 KB staging slab and sends the slab to global memory with one bulk tensor store
+                // (box 16 x 64).  About 30 instructions per lane and tile instead of 110 for a
+                // shuffle-transpose / 128-bit store path, no synchronisation between warps, and
+                // the stores are asynchronous (one slab per warp: the store of a tile reads it while
+                // the warp loads and converts its next tile).
+                const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) + acc_addr(acc);
+                // lane -> row address of its 8x8 matrix: matrix i = lane / 8 holds rows (i & 1) * 8 ..
+                // of 16-byte column unit u = 2k + (i >> 1)
+                const int sm_row = ((lane >> 3) & 1) * 8 + (lane & 7);        // row inside the slab
+                const uint32_t sm_unit = (uint32_t)(lane >> 4);
+                const int slab0 = (warp - kFirstEpilogueWarp) * (16 * 128);         // this warp's slab
+                auto store_tile = [&](const uint32_t (&r)[32], int t) {
+                    const int out_idx = t == 0 ? ent.x : ent.y;
+                    // a descriptor that does not belong to this layout is reported in the workspace
+                    // (word 1 = offending tile index); the tensor map clips the store itself
+                    const bool in_bounds = out_idx >= 0 && out_idx < p.nnz;
                     if (!in_bounds && lane == 0) {
                         atomicExch(p.status, (uint32_t)BSA_ERR_BAD_SHAPE);
-                        atomicExch(p.status + 1, (uint32_t)(dst0 >> 12));
+                        atomicExch(p.status + 1, (uint32_t)out_idx);
                     }
-                    const bool writer = row_lane && row < rows_valid && in_bounds;
-                    uint16_t* dst = p.c + dst0 + (size_t)row * p.ldc;
-                    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc_addr(acc) + (uint32_t)(t * kTile);
-                    const bool last_tile = have_acc && t == tiles - 1;
-                    if (!have_acc || parts == 1) {
-                        uint32_t v[kTile];          // fp32 bit patterns of this lane's row
-                        if (have_acc) {
-                            tc_ld_32x32b_x64(taddr, v);
-                            tc_wait_ld();
-                        } else {
+                    const uint32_t slab = smem_u32(stage_base + kSddStagingTile0 * kTileBytes + slab0);
+                    uint32_t w[16];                         // [4k + i]: matrices (u = 2k, rows a), (2k, b), (2k + 1, a), (2k + 1, b)
 #pragma unroll
-                            for (int c = 0; c < kTile; ++c) v[c] = 0u;
+                    for (int k = 0; k < 4; ++k) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int u = 2 * k + (i >> 1), h = i & 1;
+                            const float lo = __uint_as_float(r[4 * u + 2 * h]), hi = __uint_as_float(r[4 * u + 2 * h + 1]);
+                            if (bf16_out) { __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi); w[4 * k + i] = *reinterpret_cast<uint32_t*>(&v); }
+                            else          { __half2 v = __floats2half2_rn(lo, hi); w[4 * k + i] = *reinterpret_cast<uint32_t*>(&v); }
                         }
-                        if (last_tile) release_accumulator(&bars->acc_empty[acc], lane);
-                        if (writer) store_row<kTile>(dst, v, cols_valid, p.c_vec8 != 0, bf16_out);
-                    } else {
-                        // dsd / dds: issuer w holds a partial sum iff one of the K-steps
-                        // step0 .. step0 + ksteps - 1 is congruent to w; the first K-step's issuer
-                        // always does, so its partial seeds the sum.  Two 32-column halves keep the
-                        // register footprint small.
-                        const int first_part = step0 & (parts - 1);
+                    }
+                    // the slab was sent with the tile before: that store must have read it
+                    if (elect_one()) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    __syncwarp();
 #pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            uint32_t v[32];
-                            tc_ld_32x32b_x32(taddr + (uint32_t)(first_part * part_stride + h * 32), v);
-                            tc_wait_ld();
-                            for (int j = 1; j < parts && j < ksteps; ++j) {
-                                const int part = (first_part + j) & (parts - 1);
-                                uint32_t r[32];
-                                tc_ld_32x32b_x32(taddr + (uint32_t)(part * part_stride + h * 32), r);
+                    for (int k = 0; k < 4; ++k) {
+                        const uint32_t addr = slab + (uint32_t)(sm_row * 128) + ((((uint32_t)(2 * k) + sm_unit) ^ (uint32_t)(sm_row & 7)) << 4);
+                        asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1, %2, %3, %4};"
+                                     ::"r"(addr), "r"(w[4 * k]), "r"(w[4 * k + 1]), "r"(w[4 * k + 2]), "r"(w[4 * k + 3]) : "memory");
+                    }
+                    fence_async_shared();           // generic-proxy writes -> visible to the bulk store
+                    __syncwarp();
+                    // (issued from an elected lane of warp-uniform code: the copy's operands stay in
+                    // uniform registers; the same lane every time, the bulk groups are per thread)
+                    int sx, sy;
+                    sparse_xy(p, out_idx, sx, sy);
+                    if (elect_one()) {
+                        if (in_bounds)
+                            asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                                         ::"l"(&map_c), "r"(slab), "r"(sx), "r"(sy + quad * 16), "r"(ent.w) : "memory");
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");   // (empty groups keep the count regular)
+                    }
+                };
+                // one register buffer: the other groups' accumulations cover this one's TMEM load
+                uint32_t r[32];
+                for (int t = 0; t < tiles; ++t) {
+                    tc_ld_16x256b_x8(tbase + (uint32_t)(t * kTile), r);
+                    tc_wait_ld();
+                    if (t + 1 >= tiles) release_accumulator(&bars->acc_empty[acc], lane);
+                    store_tile(r, t);
+                }
+            }
+        } else {
+            const int parts = is_sdd ? 1 : p.issuers;
+            const int part_stride = kAccCols / p.issuers;
+            int flush_no = 0, step = 0;
+            Cursor cur;
+            cur.init(p, p.split);
+            while (ok && cur.valid()) {
+                int flushes, ksteps;
+                item_shape<MODE>(p, cur.count << p.split, flushes, ksteps);
+                const bool have_acc = ksteps > 0;
+                for (int f = 0; ok && f < flushes; ++f) {
+                    // accumulations alternate between the two buffers / groups; groups that write
+                    // zeros for an empty group of blocks are chosen by item parity
+                    const int owner = have_acc ? (flush_no & (kGroups - 1)) : (cur.item_no & (kGroups - 1));
+                    const uint32_t acc_phase = (uint32_t)(flush_no >> kBufShift) & 1u;
+                    const int acc = flush_no & (kBufs - 1);     // (dsd / dds: the group's own buffer)
+                    const int step0 = step;             // sequence number of this accumulation's first K-step
+                    step += ksteps;
+                    if (have_acc) ++flush_no;
+                    if (owner != group) continue;
+                    const int tiles = b_tiles<MODE>(p, cur.count << p.split, cur.chunk, f);
+                    if (have_acc) {
+                        ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_full[acc], acc_phase, &bars->abort_flag, p.status)) != 0;
+                        if (!ok) break;
+                        tc_fence_after();
+                    }
+                    for (int t = 0; t < tiles; ++t) {
+                        // destination of this 64x64 tile: first element, valid rows and columns
+                        size_t dst0;
+                        int rows_valid = kTile, cols_valid = kTile;
+                        if (MODE == BSA_MODE_DSD) {
+                            const int n0 = (cur.chunk * 2 + t) * kTile;
+                            dst0 = ((size_t)cur.z * p.size_m + (size_t)cur.g * kTile) * p.size_n + n0;
+                            cols_valid = min(kTile, p.size_n - n0);
+                        } else {
+                            const int m0 = cur.chunk * kTile;
+                            dst0 = ((size_t)cur.z * p.size_m + m0) * p.size_n + (size_t)cur.g * kTile;
+                            rows_valid = min(kTile, p.size_m - m0);
+                        }
+                        // never write outside the output: a descriptor that does not belong to this
+                        // layout is reported in the workspace instead (word 1 = offending offset >> 12)
+                        const bool in_bounds = dst0 + (size_t)(rows_valid - 1) * p.ldc + cols_valid <= (size_t)p.c_elems;
+                        if (!in_bounds && lane == 0) {
+                            atomicExch(p.status, (uint32_t)BSA_ERR_BAD_SHAPE);
+                            atomicExch(p.status + 1, (uint32_t)(dst0 >> 12));
+                        }
+                        const bool writer = row_lane && row < rows_valid && in_bounds;
+                        uint16_t* dst = p.c + dst0 + (size_t)row * p.ldc;
+                        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc_addr(acc) + (uint32_t)(t * kTile);
+                        const bool last_tile = have_acc && t == tiles - 1;
+                        if (!have_acc || parts == 1) {
+                            uint32_t v[kTile];          // fp32 bit patterns of this lane's row
+                            if (have_acc) {
+                                tc_ld_32x32b_x64(taddr, v);
                                 tc_wait_ld();
-#pragma unroll
-                                for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) + __uint_as_float(r[c]));
+                            } else {
+    #pragma unroll
+                                for (int c = 0; c < kTile; ++c) v[c] = 0u;
                             }
-                            if (last_tile && h == 1) release_accumulator(&bars->acc_empty[acc], lane);
-                            if (writer) store_row<32>(dst + h * 32, v, cols_valid - h * 32, p.c_vec8 != 0, bf16_out);
+                            if (last_tile) release_accumulator(&bars->acc_empty[acc], lane);
+                            if (writer) store_row<kTile>(dst, v, cols_valid, p.c_vec8 != 0, bf16_out);
+                        } else {
+                            // dsd / dds: issuer w holds a partial sum iff one of the K-steps
+                            // step0 .. step0 + ksteps - 1 is congruent to w; the first K-step's issuer
+                            // always does, so its partial seeds the sum.  Two 32-column halves keep the
+                            // register footprint small.
+                            const int first_part = step0 & (parts - 1);
+    #pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+                                uint32_t v[32];
+                                tc_ld_32x32b_x32(taddr + (uint32_t)(first_part * part_stride + h * 32), v);
+                                tc_wait_ld();
+                                for (int j = 1; j < parts && j < ksteps; ++j) {
+                                    const int part = (first_part + j) & (parts - 1);
+                                    uint32_t r[32];
+                                    tc_ld_32x32b_x32(taddr + (uint32_t)(part * part_stride + h * 32), r);
+                                    tc_wait_ld();
+    #pragma unroll
+                                    for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) + __uint_as_float(r[c]));
+                                }
+                                if (last_tile && h == 1) release_accumulator(&bars->acc_empty[acc], lane);
+                                if (writer) store_row<32>(dst + h * 32, v, cols_valid - h * 32, p.c_vec8 != 0, bf16_out);
+                            }
                         }
                     }
                 }
+                cur.advance();
             }
-            pre = pre_next;
-            cur.advance();
         }
         // the staging tiles must have been read before the CTA gives its shared memory back
         if (is_sdd && elect_one()) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");

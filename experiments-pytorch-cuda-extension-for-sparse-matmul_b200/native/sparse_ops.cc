@@ -393,8 +393,12 @@ torch::Tensor sparse_to_dense(torch::Tensor x, torch::Tensor row_blocks, int64_t
     return convert(false, x, row_blocks, rows, cols, block);
 }
 
-// Synchronises the current stream and raises if any tcgen05 kernel launched
-// through this module on `device_index` gave up on a bounded wait.
+// The ops of this module never synchronise; a kernel that gives up on a bounded wait, or meets a
+// block descriptor that does not belong to its layout, leaves a status in the module's per-device
+// workspace instead.  check_device_status(device_index) synchronises the current stream of that
+// device, raises RuntimeError with the status string if any kernel launched through this module on
+// the device reported one since the last check, and clears the word.  Call it where results are
+// consumed.
 void check_device_status(int64_t device_index) {
     const torch::Device device(torch::kCUDA, static_cast<c10::DeviceIndex>(device_index));
     c10::cuda::CUDAGuard guard(device);
@@ -429,7 +433,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("build_layout", &build_layout, "Build row / column layout metadata on the device.", py::arg("pattern"));
     m.def("dense_to_sparse", &dense_to_sparse, "Gather the layout's blocks from a dense matrix.");
     m.def("sparse_to_dense", &sparse_to_dense, "Scatter blocks into a zero-filled dense matrix.");
-    m.def("check_device_status", &check_device_status, "Raise if a kernel reported a device-side timeout.",
+    m.def("check_device_status", &check_device_status, "Synchronise the device's current stream; raise if a kernel reported a time-out or a bad block descriptor since the last check.",
           py::arg("device_index") = 0);
     m.def("version", []() { return bsa_version(); });
     m.attr("WORKSPACE_BYTES") = BSA_WORKSPACE_BYTES;

@@ -117,6 +117,47 @@ def test_fused_backward_agrees_with_unfused_composition(dim):
         assert err <= 4e-3, (name, err)
 
 
+@pytest.mark.parametrize("causal", [False, True])
+def test_many_rows_per_pipeline_wrap_the_entry_rings(causal):
+    """Seventeen or more block rows (and thirty or more block columns) per pipeline at head dim 64: the
+    eight-entry rings through which a pipeline's producer hands rows, columns and block descriptors to its
+    issuers and compute warps wrap several times.  Rows without blocks are mixed in (the producer zeroes them
+    and the other roles never see them).  Fused forward and backward against the unfused composition."""
+    from sparse import SparseLayout
+    module = importlib.import_module("sparse.attention")
+    rows = 32
+    pattern = torch.zeros(rows, rows, dtype=torch.uint8)
+    for i in range(rows):
+        if i % 7 == 3:
+            continue                                    # a row without blocks
+        pattern[i, i] = 1
+        pattern[i, (5 * i + 1) % rows if not causal else (i // 2)] = 1
+    pattern[:, 11] = 0                                  # a column without blocks
+    layout = SparseLayout(pattern, block=64)
+    z = 330                                             # 10 560 rows over 592 row / 296 column pipelines
+    q, k, v, do = (seeded((z, rows * 64, 64), 270 + i, torch.float16).cuda() for i in range(4))
+    out, grads = {}, {}
+    try:
+        for fused in (True, False):
+            module.fused_backward = fused
+            qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
+            if fused:
+                o = module.attention(qg, kg, vg, layout, 0.125, causal)
+            else:
+                from sparse import matmul, softmax
+                o = matmul(softmax(matmul(qg, kg, "sdd", layout, False, True), layout, scale=0.125, causal=causal), vg, "dsd", layout)
+            o.backward(do)
+            out[fused], grads[fused] = o.detach(), (qg.grad, kg.grad, vg.grad)
+    finally:
+        module.fused_backward = True
+    sparse_kernel = importlib.import_module("sparse.kernel")
+    sparse_kernel.sparse_ops.check_device_status(0)
+    for a, b, name in zip((out[True],) + grads[True], (out[False],) + grads[False], ("O", "dQ", "dK", "dV")):
+        err = float((a.float() - b.float()).abs().max() / b.float().abs().max())
+        assert err <= 5e-3, (name, err)
+        assert torch.isfinite(a.float()).all(), name
+
+
 def test_full_size_fused_step_properties_config5():
     """Benchmark configuration 5 at full size (512 slices, seq 8192, head dim 128, BigBird layout) through
     the fused forward and backward, checked by size-independent properties: (1) with V = 1 every output

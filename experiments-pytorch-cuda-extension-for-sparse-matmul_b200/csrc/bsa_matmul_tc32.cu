@@ -52,15 +52,27 @@ constexpr int kFirstEpilogueWarp = 8;
 constexpr int kFirstSplitWarp = 12;             // fp32 only
 constexpr int kThreads = 16 * 32;
 
-struct __align__(8) Barriers {
+// sdd: the epilogue warps do not walk the work items.  The producer that loads an accumulation's first K-step
+// posts where its output pieces go (element offsets into the sparse tensor, -1 for a rank outside the layout) in a
+// ring of entries with one mbarrier each; accumulation number F uses entry F & 31 (the producers are at most
+// 16 stages of one K-step each + 2 accumulator buffers ahead of the epilogue).
+constexpr int kSddEntries = 32;
+struct SddEntry {
+    long long dst[8];               // first element of output piece t
+    int pieces;                     // 0: no more accumulations
+    int pad;
+};
+struct __align__(16) Barriers {
     uint64_t full[kMaxStages];      // TMA data of a stage has landed
     uint64_t ready[kMaxStages];     // fp32: the stage has been split into hi / lo
     uint64_t empty[kMaxStages];     // the MMAs that read a stage have retired
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
+    uint64_t ent_full[kSddEntries];
     uint64_t drain;
     uint32_t tmem_base;
     int abort_flag;
+    SddEntry ents[kSddEntries];
 };
 constexpr int kSmemBytes = 1024 /* alignment slack */ + kPipeBytes + (int)sizeof(Barriers);
 
@@ -215,6 +227,7 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             mbar_init(&bars->full[s], 1); mbar_init(&bars->ready[s], 1); mbar_init(&bars->empty[s], 1);
         }
         for (int s = 0; s < 2; ++s) { mbar_init(&bars->acc_full[s], arrivals); mbar_init(&bars->acc_empty[s], 4); }
+        if (is_sdd) for (int s = 0; s < kSddEntries; ++s) mbar_init(&bars->ent_full[s], 1);
         mbar_init(&bars->drain, (uint32_t)p.issuers);
         bars->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -240,6 +253,7 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         // (an mbarrier parity wait cannot tell phases two apart, so a thread must take part in
         // every phase of each barrier it waits on).
         int stage = warp, step0 = 0;
+        int flush_no = 0;                    // sdd: number of the accumulation
         uint32_t phase = 0;
         bool ok = true;
         Cursor cur;
@@ -256,11 +270,19 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 const int nb = b_panels<MODE>(p, cur.count << p.split, cur.chunk, f);
                 for (int k = (warp - step0) & (kProducerWarps - 1); ok && k < ksteps; k += kProducerWarps) {
                     int cols[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                    long long dsts[8] = {0, 0, 0, 0, 0, 0, 0, 0};
                     Panel d{0, 0, 0, 0, 0};
                     if (is_sdd) {
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
-                            if (j < nb) cols[j] = panel_of(win, p, cur, (f << p.nb_shift) + j, lane).col;
+                            if (j < nb) {
+                                const Panel out = panel_of(win, p, cur, (f << p.nb_shift) + j, lane);
+                                cols[j] = out.col;
+                                // first element of the output piece; a rank outside the layout is reported, not written
+                                if (k == 0)
+                                    dsts[j] = (out.idx < 0 || out.idx >= p.nnz) ? -1ll - (long long)(uint32_t)out.idx
+                                        : (long long)((((size_t)cur.z * p.nnz + out.idx) * p.block + out.rh * kBlk) * p.block + out.ch * kBlk);
+                            }
                     } else {
                         d = panel_of(win, p, cur, k, lane);
                     }
@@ -274,6 +296,13 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                             uint8_t* slot = stage_base + stage * p.stage_bytes;
                             uint8_t* slot_b = slot + 2 * kPanelBytes;
                             uint64_t* full = &bars->full[stage];
+                            if (is_sdd && k == 0) {         // the accumulation's entry for the epilogue warps
+                                SddEntry& e = bars->ents[flush_no & (kSddEntries - 1)];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) e.dst[j] = dsts[j];
+                                e.pieces = nb;
+                                mbar_arrive(&bars->ent_full[flush_no & (kSddEntries - 1)]);
+                            }
                             mbar_expect_tx(full, (uint32_t)((kAPanels + nb) * kPanelBytes));
                             if (is_sdd) {
                                 const int k0 = k * kBlk, m0 = cur.g * kBlk;
@@ -312,10 +341,19 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     if (stage >= p.stages) { stage -= p.stages; phase ^= 1; }
                 }
                 step0 += ksteps;
+                ++flush_no;
             }
             pre = pre_next;
             cur.advance();
         }
+        if (is_sdd && warp == 0 && ok && elect_one()) {
+            // no more accumulations: one closing entry for each of the epilogue groups
+            for (int e = flush_no; e < flush_no + 2; ++e) {
+                bars->ents[e & (kSddEntries - 1)].pieces = 0;
+                mbar_arrive(&bars->ent_full[e & (kSddEntries - 1)]);
+            }
+        }
+        __syncwarp();
         if (lane == 0 && *(volatile int*)abort_flag) {
             // Give copies that were issued a bounded chance to land before the CTA exits.
             const unsigned long long t0 = global_ns();
@@ -464,11 +502,54 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         const int part_stride = kAccCols / p.issuers;
         int flush_no = 0, step = 0;
         bool ok = true;
+        if (is_sdd) {
+            // Accumulation F of the CTA: entry F & 31 from the producers, accumulator buffer F & 1; with two
+            // groups, group g takes the accumulations F = g, g + 2, ...  The TMEM load of piece t + 1 is in
+            // flight while piece t is converted and stored (two register buffers).
+            for (int flush = kEpilogueGroups == 1 ? 0 : group; ok; flush += kEpilogueGroups) {
+                const int slot = flush & (kSddEntries - 1);
+                ok = __all_sync(0xffffffffu, mbar_wait(&bars->ent_full[slot], (uint32_t)(flush / kSddEntries) & 1u, abort_flag, p.status)) != 0;
+                if (!ok) break;
+                const SddEntry& ent = bars->ents[slot];
+                const int pieces = ent.pieces;
+                if (pieces == 0) break;             // no more accumulations
+                const int acc = flush & 1;
+                ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_full[acc], (uint32_t)(flush >> 1) & 1u, abort_flag, p.status)) != 0;
+                if (!ok) break;
+                tc_fence_after();
+                if (quad_active) {
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * kAccCols);
+                    auto store = [&](const uint32_t (&v)[32], int t) {
+                        const long long dst0 = ent.dst[t];
+                        // never write outside the output: a descriptor that does not belong to this layout is
+                        // reported in the workspace instead (word 1 = its rank)
+                        const bool in_bounds = dst0 >= 0 && (size_t)dst0 + (size_t)(kBlk - 1) * p.ldc + kBlk <= (size_t)p.c_elems;
+                        if (!in_bounds && lane == 0) {
+                            atomicExch(p.status, (uint32_t)BSA_ERR_BAD_SHAPE);
+                            atomicExch(p.status + 1, dst0 < 0 ? (uint32_t)(-1ll - dst0) : (uint32_t)(dst0 >> 12));
+                        }
+                        if (row_lane && in_bounds) store_piece<DT>(p.c, (size_t)dst0 + (size_t)row * p.ldc, v, kBlk);
+                    };
+                    uint32_t va[32], vb[32];
+                    tc_ld_32x32b_x32(taddr, va);
+                    for (int t = 0; t < pieces; t += 2) {
+                        tc_wait_ld();
+                        if (t + 1 < pieces) tc_ld_32x32b_x32(taddr + (uint32_t)((t + 1) * kBlk), vb);
+                        store(va, t);
+                        if (t + 1 >= pieces) break;
+                        tc_wait_ld();
+                        if (t + 2 < pieces) tc_ld_32x32b_x32(taddr + (uint32_t)((t + 2) * kBlk), va);
+                        store(vb, t + 1);
+                    }
+                }
+                release_accumulator(&bars->acc_empty[acc], lane);
+            }
+        }
         Cursor cur;
         cur.init(p, p.split);
         BlockDesc pre{0, 0};
         if (is_sdd && cur.valid()) pre = load_first_chunk(p.blocks, cur.first, cur.count, lane);
-        while (ok && cur.valid()) {
+        while (!is_sdd && ok && cur.valid()) {
             BlockDesc pre_next{0, 0};
             if (is_sdd && cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
             int flushes, ksteps;

@@ -15,9 +15,10 @@
 //                     ranges of M/N (leading byte offset = one panel); one MMA consumes 1024
 //                     bytes of rows (16 rows of 16-bit, 8 rows of fp32 elements).
 // A K-step is 32 elements of K: two kind::f16 MMAs (K = 16) or four kind::tf32 MMAs (K = 8).
-// The MMA shape is M = 64: with 32-row blocks the upper half of the A operand (a second panel)
-// is never loaded and the accumulator rows it produces are never read (dds, whose M is a slice
-// of a dense dimension, uses all 64 rows).
+// The MMA shape is M = 64.  sdd and dsd have 32 rows of A only and load that panel twice, so the
+// accumulator rows 32-63 repeat rows 0-31 in the TMEM quarters 2 and 3 and all four warps of an
+// epilogue warpgroup have output pieces to store (a warp reads its own quarter only); dds, whose M
+// is a slice of a dense dimension, uses all 64 rows.
 //   sdd  item = block row r; its blocks are taken 8 (fp32: 4) at a time as one N = 256 (128)
 //        accumulation over the dense inner size.
 //   dsd  item = group m and a 128-wide slice of N; one accumulation over the group's blocks.
@@ -210,7 +211,10 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     constexpr int kMmasPerStep = kBlk * ES / 32;              // 32 bytes of K per MMA
     constexpr int kEpilogueGroups = kSplit ? 1 : 2;
     constexpr bool is_sdd = MODE == BSA_MODE_SDD;
-    constexpr int kAPanels = MODE == BSA_MODE_DDS ? 2 : 1;    // A panels that are loaded (the A region always holds 2)
+    // The MMA is M = 64.  dds fills both A panels with a 64-tall slice of its dense operand.  sdd and dsd have 32
+    // rows of A only and load them twice: accumulator rows 32-63 then repeat rows 0-31 in the TMEM quarters 2 and 3,
+    // and the epilogue warps of those quarters, which would otherwise idle, take every other output piece.
+    constexpr int kAPanels = 2;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -269,6 +273,52 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             for (int f = 0; ok && f < flushes; ++f) {
                 const int nb = b_panels<MODE>(p, cur.count << p.split, cur.chunk, f);
                 for (int k = (warp - step0) & (kProducerWarps - 1); ok && k < ksteps; k += kProducerWarps) {
+                    if (is_sdd && p.split == 0) {
+                        // Block 32.  Lane l of the warp holds descriptor base + l of the row's blocks (the descriptor
+                        // window), and an accumulation's blocks never straddle a window: the lanes that hold them issue
+                        // the copies of their own K panels and write their own output offsets -- no broadcasts, and one
+                        // instruction for up to eight copies (broadcasting eight descriptors and issuing ten copies from
+                        // one lane took 3 500 of the 4 600 cycles a producer spent per K-step).
+                        const int i0 = f << p.nb_shift;
+                        win.seek(p.blocks, cur.first, cur.count, i0, lane);
+                        const int j = lane - (i0 - win.base);
+                        const bool has = j >= 0 && j < nb;
+                        const BlockDesc dj = win.mine;
+                        ok = __all_sync(0xffffffffu, mbar_wait(&bars->empty[stage], phase ^ 1, abort_flag, p.status)) != 0;
+                        if (ok) {
+                            uint8_t* slot = stage_base + stage * p.stage_bytes;
+                            uint64_t* full = &bars->full[stage];
+                            SddEntry& e = bars->ents[flush_no & (kSddEntries - 1)];
+                            // first element of the output piece; a rank outside the layout is reported, not written
+                            if (k == 0 && has)
+                                e.dst[j] = (dj.idx < 0 || dj.idx >= p.nnz) ? -1ll - (long long)(uint32_t)dj.idx
+                                                                            : (long long)(((size_t)cur.z * p.nnz + dj.idx) * (kBlk * kBlk));
+                            __syncwarp();
+                            const int k0 = k * kBlk, m0 = cur.g * kBlk;
+                            if (elect_one()) {
+                                if (k == 0) {               // the accumulation's entry for the epilogue warps
+                                    e.pieces = nb;
+                                    mbar_arrive(&bars->ent_full[flush_no & (kSddEntries - 1)]);
+                                }
+                                mbar_expect_tx(full, (uint32_t)((kAPanels + nb) * kPanelBytes));
+#pragma unroll
+                                for (int h = 0; h < 2; ++h) {
+                                    if (a_mn_major) tma_load_3d(slot + h * kPanelBytes, &map_a, full, m0, k0, cur.z);
+                                    else            tma_load_3d(slot + h * kPanelBytes, &map_a, full, k0, m0, cur.z);
+                                }
+                            }
+                            __syncwarp();
+                            if (has) {
+                                const int n0 = dj.col() * kBlk;
+                                if (b_mn_major) tma_load_3d(slot + (2 + j) * kPanelBytes, &map_b, full, n0, k0, cur.z);
+                                else            tma_load_3d(slot + (2 + j) * kPanelBytes, &map_b, full, k0, n0, cur.z);
+                            }
+                        }
+                        __syncwarp();
+                        stage += kProducerWarps;
+                        if (stage >= p.stages) { stage -= p.stages; phase ^= 1; }
+                        continue;
+                    }
                     int cols[8] = {0, 0, 0, 0, 0, 0, 0, 0};
                     long long dsts[8] = {0, 0, 0, 0, 0, 0, 0, 0};
                     Panel d{0, 0, 0, 0, 0};
@@ -306,8 +356,11 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                             mbar_expect_tx(full, (uint32_t)((kAPanels + nb) * kPanelBytes));
                             if (is_sdd) {
                                 const int k0 = k * kBlk, m0 = cur.g * kBlk;
-                                if (a_mn_major) tma_load_3d(slot, &map_a, full, m0, k0, cur.z);
-                                else            tma_load_3d(slot, &map_a, full, k0, m0, cur.z);
+#pragma unroll
+                                for (int h = 0; h < 2; ++h) {
+                                    if (a_mn_major) tma_load_3d(slot + h * kPanelBytes, &map_a, full, m0, k0, cur.z);
+                                    else            tma_load_3d(slot + h * kPanelBytes, &map_a, full, k0, m0, cur.z);
+                                }
 #pragma unroll
                                 for (int j = 0; j < 8; ++j) {
                                     if (j < nb) {
@@ -319,6 +372,7 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                             } else if (MODE == BSA_MODE_DSD) {
                                 const int k0 = (p.trans_a ? d.row : d.col) * kBlk;
                                 tma_load_3d(slot, &map_a, full, sx, sy, cur.z);
+                                tma_load_3d(slot + kPanelBytes, &map_a, full, sx, sy, cur.z);
                                 for (int j = 0; j < nb; ++j) {
                                     const int n0 = (cur.chunk * 4 + j) * kBlk;
                                     if (b_mn_major) tma_load_3d(slot_b + j * kPanelBytes, &map_b, full, n0, k0, cur.z);
@@ -466,7 +520,7 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     ok = __all_sync(0xffffffffu, mbar_wait(&bars->full[stage], phase, abort_flag, p.status)) != 0;
                     if (!ok) break;
                     uint8_t* slot = stage_base + stage * p.stage_bytes;
-                    // both A panels (the second may be stale: its products are never read) and nb B panels
+                    // both A panels and nb B panels
                     const int chunks16 = (2 + nb) * (kPanelBytes / 16);
                     for (int i = lane; i < chunks16; i += 32) {
                         uint4* hi_ptr = reinterpret_cast<uint4*>(slot) + i;
@@ -494,10 +548,12 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         // ------------------------------------------------------------ epilogue groups
         const int group = (warp - kFirstEpilogueWarp) >> 2;     // 16-bit: drains accumulator buffer `group`
         const int quad = warp & 3;                   // TMEM sub-partition this warp may read
-        const int row = quad * 16 + lane;            // accumulator row held by this lane (lanes 0-15 only)
+        // accumulator row held by this lane (lanes 0-15 only); sdd / dsd: output row, the quarters 2 and 3 repeat 0 and 1
+        const int row = (MODE == BSA_MODE_DDS ? quad : (quad & 1)) * 16 + lane;
+        const int half = MODE == BSA_MODE_DDS ? 0 : quad >> 1;       // sdd / dsd: this warp takes the pieces t with t % 2 == half
+        constexpr int kPieceStep = MODE == BSA_MODE_DDS ? 1 : 2;
         const bool row_lane = lane < 16;
-        // with 32-row outputs only the first two sub-partitions hold rows that are stored
-        const bool quad_active = MODE == BSA_MODE_DDS || quad < 2;
+        const bool quad_active = true;
         const int parts = is_sdd ? 1 : p.issuers;
         const int part_stride = kAccCols / p.issuers;
         int flush_no = 0, step = 0;
@@ -531,15 +587,15 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         if (row_lane && in_bounds) store_piece<DT>(p.c, (size_t)dst0 + (size_t)row * p.ldc, v, kBlk);
                     };
                     uint32_t va[32], vb[32];
-                    tc_ld_32x32b_x32(taddr, va);
-                    for (int t = 0; t < pieces; t += 2) {
+                    if (half < pieces) tc_ld_32x32b_x32(taddr + (uint32_t)(half * kBlk), va);
+                    for (int t = half; t < pieces; t += 4) {
                         tc_wait_ld();
-                        if (t + 1 < pieces) tc_ld_32x32b_x32(taddr + (uint32_t)((t + 1) * kBlk), vb);
+                        if (t + 2 < pieces) tc_ld_32x32b_x32(taddr + (uint32_t)((t + 2) * kBlk), vb);
                         store(va, t);
-                        if (t + 1 >= pieces) break;
+                        if (t + 2 >= pieces) break;
                         tc_wait_ld();
-                        if (t + 2 < pieces) tc_ld_32x32b_x32(taddr + (uint32_t)((t + 2) * kBlk), va);
-                        store(vb, t + 1);
+                        if (t + 4 < pieces) tc_ld_32x32b_x32(taddr + (uint32_t)((t + 4) * kBlk), va);
+                        store(vb, t + 2);
                     }
                 }
                 release_accumulator(&bars->acc_empty[acc], lane);
@@ -574,7 +630,7 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     tc_fence_after();
                 }
                 if (quad_active) {
-                    for (int t = 0; t < pieces; ++t) {
+                    for (int t = half; t < pieces; t += kPieceStep) {
                         // destination of this 32-column piece: first element, valid rows and columns
                         size_t dst0;
                         int rows_valid = kBlk, cols_valid = kBlk;

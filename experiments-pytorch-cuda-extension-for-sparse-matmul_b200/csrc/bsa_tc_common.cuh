@@ -338,12 +338,17 @@ struct DescWindow {
         ahead = BlockDesc{0, 0};
         if (32 + lane < count) ahead = blocks[first + 32 + lane];
     }
-    __device__ __forceinline__ BlockDesc get(const BlockDesc* blocks, int first, int count, int i, int lane) {
+    // Moves the window on until it holds descriptor i (and the 31 after its base); lane l then finds
+    // descriptor base + l in `mine`.
+    __device__ __forceinline__ void seek(const BlockDesc* blocks, int first, int count, int i, int lane) {
         while (i >= base + 32) {
             mine = ahead;
             base += 32;
             if (base + 32 + lane < count) ahead = blocks[first + base + 32 + lane];
         }
+    }
+    __device__ __forceinline__ BlockDesc get(const BlockDesc* blocks, int first, int count, int i, int lane) {
+        seek(blocks, first, count, i, lane);
         BlockDesc d;
         d.idx = __shfl_sync(0xffffffffu, mine.idx, i - base);
         d.packed = __shfl_sync(0xffffffffu, mine.packed, i - base);

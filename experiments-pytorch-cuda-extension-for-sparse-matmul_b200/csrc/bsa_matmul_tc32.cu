@@ -211,6 +211,7 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     constexpr int kMmasPerStep = kBlk * ES / 32;              // 32 bytes of K per MMA
     constexpr int kEpilogueGroups = kSplit ? 1 : 2;
     constexpr bool is_sdd = MODE == BSA_MODE_SDD;
+    constexpr bool kWideB = MODE == BSA_MODE_DSD && ES == 2;   // dsd, 16-bit: the dense operand's panels are copied in pairs
     // The MMA is M = 64.  dds fills both A panels with a 64-tall slice of its dense operand.  sdd and dsd have 32
     // rows of A only and load them twice: accumulator rows 32-63 then repeat rows 0-31 in the TMEM quarters 2 and 3,
     // and the epilogue warps of those quarters, which would otherwise idle, take every other output piece.
@@ -353,7 +354,7 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                 e.pieces = nb;
                                 mbar_arrive(&bars->ent_full[flush_no & (kSddEntries - 1)]);
                             }
-                            mbar_expect_tx(full, (uint32_t)((kAPanels + nb) * kPanelBytes));
+                            mbar_expect_tx(full, (uint32_t)((kAPanels + (kWideB ? (nb + 1) & ~1 : nb)) * kPanelBytes));
                             if (is_sdd) {
                                 const int k0 = k * kBlk, m0 = cur.g * kBlk;
 #pragma unroll
@@ -373,7 +374,8 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                 const int k0 = (p.trans_a ? d.row : d.col) * kBlk;
                                 tma_load_3d(slot, &map_a, full, sx, sy, cur.z);
                                 tma_load_3d(slot + kPanelBytes, &map_a, full, sx, sy, cur.z);
-                                for (int j = 0; j < nb; ++j) {
+                                // 16-bit: the dense panels come in pairs, one box each (see encode_map32)
+                                for (int j = 0; j < nb; j += kWideB ? 2 : 1) {
                                     const int n0 = (cur.chunk * 4 + j) * kBlk;
                                     if (b_mn_major) tma_load_3d(slot_b + j * kPanelBytes, &map_b, full, n0, k0, cur.z);
                                     else            tma_load_3d(slot_b + j * kPanelBytes, &map_b, full, k0, n0, cur.z);
@@ -429,9 +431,12 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             int stage = is_sdd ? 0 : w;
             uint32_t phase = 0;
             bool ok = true;
-            const uint64_t desc_a0 = panel_desc<ES>(a_mn_major), desc_b0 = panel_desc<ES>(b_mn_major);
+            // dsd, 16-bit, N contiguous: a pair of panels arrives as 32 rows of 128 bytes with the 128-byte swizzle:
+            // 8-row groups along K 1024 bytes apart, pairs along N 4096 bytes apart, 16 rows of K = 2048 bytes per MMA
+            const uint64_t wide_b = ((uint64_t)(4096u >> 4) << 16) | ((uint64_t)(1024u >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+            const uint64_t desc_a0 = panel_desc<ES>(a_mn_major), desc_b0 = (kWideB && b_mn_major) ? wide_b : panel_desc<ES>(b_mn_major);
             const uint32_t a_kstep = a_mn_major ? 1024u >> 4 : 32u >> 4;   // descriptor advance per MMA
-            const uint32_t b_kstep = b_mn_major ? 1024u >> 4 : 32u >> 4;
+            const uint32_t b_kstep = (kWideB && b_mn_major) ? 2048u >> 4 : (b_mn_major ? 1024u >> 4 : 32u >> 4);
             const uint32_t lo = (uint32_t)p.lo_offset >> 4;
             const uint32_t part_col = is_sdd ? 0u : (uint32_t)(w * (kAccCols / p.issuers));
             const int issuer_mask = p.issuers - 1;       // issuers is 1, 2 or 4
@@ -701,21 +706,23 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 // 3-D tensor map over a row-major [batches, rows, cols] tensor with a 32x32x1 box and the swizzle
 // that spans a box row (fp32 operands used MN-major: its variant with 32-byte atoms, see
 // panel_desc).  Out-of-range parts of a box read as zero.
+// `wide`: the 16-bit dense operand of dsd, whose panels come two at a time: an MN-major pair is one box of
+// 32 rows x 64 elements with the 128-byte swizzle, a K-major pair one box of 64 rows x 32 elements.
 bool encode_map32(CUtensorMap* map, int dtype, bool mn_major, const void* base, int64_t batches, int64_t rows,
-                  int64_t cols) {
+                  int64_t cols, bool wide = false) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     const cuuint64_t es = dtype == BSA_DTYPE_F32 ? 4 : 2;
     const cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batches};
     const cuuint64_t strides[2] = {(cuuint64_t)cols * es, (cuuint64_t)rows * (cuuint64_t)cols * es};
-    const cuuint32_t box[3] = {kBlk, kBlk, 1};
+    const cuuint32_t box[3] = {(cuuint32_t)(wide && mn_major ? 2 * kBlk : kBlk), (cuuint32_t)(wide && !mn_major ? 2 * kBlk : kBlk), 1};
     const cuuint32_t elem[3] = {1, 1, 1};
     const CUtensorMapDataType type = dtype == BSA_DTYPE_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                      : dtype == BSA_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                                : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const CUresult res = fn(map, type, 3, const_cast<void*>(base), dims, strides, box, elem,
                             CU_TENSOR_MAP_INTERLEAVE_NONE,
-                            dtype != BSA_DTYPE_F32 ? CU_TENSOR_MAP_SWIZZLE_64B
+                            dtype != BSA_DTYPE_F32 ? (wide && mn_major ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B)
                             : mn_major             ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
                                                    : CU_TENSOR_MAP_SWIZZLE_128B,
                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -726,9 +733,9 @@ bool encode_map32(CUtensorMap* map, int dtype, bool mn_major, const void* base, 
 }
 
 bool make_map32(CUtensorMap* map, int dtype, bool mn_major, const void* base, int64_t batches, int64_t rows,
-                int64_t cols) {
-    return cached_map(map, MapKey{base, batches, rows, cols, dtype, mn_major ? 1 : 0},
-                      [&](CUtensorMap* m) { return encode_map32(m, dtype, mn_major, base, batches, rows, cols); });
+                int64_t cols, bool wide = false) {
+    return cached_map(map, MapKey{base, batches, rows, cols, dtype, (mn_major ? 1 : 0) + (wide ? 2 : 0)},
+                      [&](CUtensorMap* m) { return encode_map32(m, dtype, mn_major, base, batches, rows, cols, wide); });
 }
 
 bool dense_dim_ok32(int64_t v) { return v >= kBlk && v % 8 == 0 && v < ((int64_t)1 << 31); }
@@ -778,7 +785,8 @@ int matmul_tc32(const MatmulArgs& g) {
         ok &= make_map32(&map_b, g.dtype, !g.trans_b, g.b, g.batches, g.trans_b ? g.size_n : g.size_k, g.trans_b ? g.size_k : g.size_n);
     } else if (g.mode == BSA_MODE_DSD) {
         ok &= make_map32(&map_a, g.dtype, g.trans_a, g.a, g.batches, sparse_rows, g.block);
-        ok &= make_map32(&map_b, g.dtype, !g.trans_b, g.b, g.batches, g.trans_b ? g.size_n : g.size_k, g.trans_b ? g.size_k : g.size_n);
+        ok &= make_map32(&map_b, g.dtype, !g.trans_b, g.b, g.batches, g.trans_b ? g.size_n : g.size_k, g.trans_b ? g.size_k : g.size_n,
+                         /*wide=*/!f32);
     } else {
         ok &= make_map32(&map_a, g.dtype, g.trans_a, g.a, g.batches, g.trans_a ? g.size_k : g.size_m, g.trans_a ? g.size_m : g.size_k);
         ok &= make_map32(&map_b, g.dtype, !g.trans_b, g.b, g.batches, sparse_rows, g.block);

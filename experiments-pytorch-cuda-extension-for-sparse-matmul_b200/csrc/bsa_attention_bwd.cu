@@ -393,7 +393,10 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
                 const int t_first = (wg - s_no) & 1;            // this group's first block of the item
                 for (int t = t_first; ok && t < n; t += 2) {
                     const int s = s_no + t, tb = s & 1;
-                    const BlockDesc d = win.get(p.blocks, cur.first, cur.count, t, lane);
+                    // (the block's descriptor is needed for the masks only; fetching it from the window costs the
+                    // compute warps two shuffles and the window's registers per block)
+                    BlockDesc d{0, 0};
+                    if (MASKED) d = win.get(p.blocks, cur.first, cur.count, t, lane);
                     const int other = COL ? d.row() : d.col();
                     // quadrant masks: is the half u < 4 / u >= 4 of this lane's 16 columns inside the layout?
                     // By rows the lane's rows are queries (row half quad / 2) and u / 4 the key half; by

@@ -106,7 +106,7 @@ class SparseAttention(torch.autograd.Function):
         out, lse = _fused_forward(q, k, v, layout, scale, causal, key_padding_mask)
         ctx.save_for_backward(q, k, v, out, lse)
         ctx.layout, ctx.scale, ctx.causal, ctx.kpm = layout, float(scale), bool(causal), key_padding_mask
-        return out
+        return kernel.check(out)
 
     @staticmethod
     def backward(ctx: Any, dout: torch.Tensor) -> Tuple[Optional[torch.Tensor], ...]:
@@ -117,6 +117,7 @@ class SparseAttention(torch.autograd.Function):
             dq, dk, dv = ops.sparse_attention_backward(
                 q, k, v, out, dout.contiguous(), lse, fine.row_layout[0], fine.row_layout[1],
                 fine.col_layout[0], fine.col_layout[1], 64, ctx.scale, ctx.causal, ctx.kpm, fine.quadrant_masks)
+            kernel.check(dout)
             return dq, dk, dv, None, None, None, None
         rows, cols, block = layout.row_layout, layout.col_layout, layout.block
         hint = getattr(layout, "max_row_blocks", 0)
@@ -133,6 +134,7 @@ class SparseAttention(torch.autograd.Function):
                 dq = ops.sparse_matmul(ds, k, "dsd", rows, cols, False, False, block)
             if ctx.needs_input_grad[1]:
                 dk = ops.sparse_matmul(ds, q, "dsd", rows, cols, True, False, block)
+        kernel.check(dout)
         return dq, dk, dv, None, None, None, None
 
 

@@ -24,3 +24,17 @@ def _load():
 
 
 sparse_ops = _load()
+
+# The ops are asynchronous and never read the device status word themselves: a kernel that gives up on a
+# bounded wait, or meets a block descriptor that does not belong to its layout, is reported by
+# ``sparse_ops.check_device_status(device_index)`` (see there).  With ``debug_checks`` set -- or the environment
+# variable BSA_DEBUG_CHECKS=1 at import time -- every autograd op of this package calls it after its forward and
+# after its backward pass, which synchronises the device each time: for debugging, not for production.
+debug_checks = os.environ.get("BSA_DEBUG_CHECKS", "0") not in ("", "0")
+
+
+def check(tensor):
+    """Opt-in status check after an op (a no-op unless ``debug_checks`` is set); returns ``tensor``."""
+    if debug_checks and tensor is not None and tensor.is_cuda:
+        sparse_ops.check_device_status(tensor.device.index or 0)
+    return tensor

@@ -29,8 +29,8 @@ class SparseMatMul(torch.autograd.Function):
         ctx.save_for_backward(a, b)
         ctx.mode, ctx.layout = mode, layout
         ctx.trans_a, ctx.trans_b = bool(trans_a), bool(trans_b)
-        return _ops().sparse_matmul(a, b, mode, layout.row_layout, layout.col_layout,
-                                    ctx.trans_a, ctx.trans_b, layout.block)
+        return kernel.check(_ops().sparse_matmul(a, b, mode, layout.row_layout, layout.col_layout,
+                                                 ctx.trans_a, ctx.trans_b, layout.block))
 
     @staticmethod
     def backward(ctx: Any, dc: torch.Tensor) -> Tuple[Optional[torch.Tensor], ...]:
@@ -52,6 +52,7 @@ class SparseMatMul(torch.autograd.Function):
             lhs, rhs = (dc, a) if trans_b else (a, dc)
             db = _ops().sparse_matmul(lhs, rhs, db_mode, layout.row_layout, layout.col_layout,
                                       not trans_a or trans_b, trans_a and trans_b, layout.block)
+        kernel.check(dc)
         return da, db, None, None, None, None
 
 

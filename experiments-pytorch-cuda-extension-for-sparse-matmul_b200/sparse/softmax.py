@@ -36,7 +36,7 @@ class SparseSoftmax(torch.autograd.Function):
                                                      key_padding_mask, getattr(layout, "max_row_blocks", 0))
         ctx.save_for_backward(y)
         ctx.layout, ctx.scale = layout, float(scale)
-        return y
+        return kernel.check(y)
 
     @staticmethod
     def backward(ctx: Any, dy: torch.Tensor) -> Tuple[Optional[torch.Tensor], ...]:
@@ -46,7 +46,7 @@ class SparseSoftmax(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = kernel.sparse_ops.sparse_softmax_backward(y, dy.contiguous(), row_blocks, row_table, ctx.scale,
                                                            getattr(ctx.layout, "max_row_blocks", 0))
-        return dx, None, None, None, None
+        return kernel.check(dx), None, None, None, None
 
 
 def softmax(x: torch.Tensor, layout: SparseLayout, scale: float = 1.0, causal: bool = False,

@@ -212,3 +212,26 @@ def test_self_attention_module_matches_dense_reference():
     # the gradient runs through six fp16 GEMMs and the softmax backward: three times the single-operator tolerance
     g, gr = x.grad.float().cpu(), xr.grad
     assert float((g - gr).abs().max() / gr.abs().max()) <= 3e-2
+
+
+@pytest.mark.gpu
+def test_debug_checks_run_after_forward_and_backward():
+    """With `sparse.kernel.debug_checks` set every autograd op reads the device status after its forward and
+    its backward pass; on a healthy run nothing is raised and the results are unchanged."""
+    import importlib
+    from sparse import SparseLayout, attention, matmul, softmax
+    from sparse.patterns import strided_local
+    kernel = importlib.import_module("sparse.kernel")
+    layout = SparseLayout(strided_local(8, 4, 1), block=64)
+    q, k, v = (seeded((2, 512, 64), 700 + i, torch.float16).cuda().requires_grad_(True) for i in range(3))
+    ref = attention(q, k, v, layout, 0.125)
+    old = kernel.debug_checks
+    try:
+        kernel.debug_checks = True
+        out = attention(q, k, v, layout, 0.125)
+        out.float().sum().backward()
+        probs = softmax(matmul(q, k, "sdd", layout, False, True), layout, scale=0.125)
+        matmul(probs, v, "dsd", layout).float().sum().backward()
+    finally:
+        kernel.debug_checks = old
+    assert torch.equal(out, ref)

@@ -269,3 +269,19 @@ def test_attention_backward_validation_codes(lib):
     assert call(nnz=5) == 4
     assert call(batches=70000, stats_bytes=1 << 40) == 10     # BSA_ERR_TOO_LARGE
     assert call(kpm=16, kpm_batches=2, kpm_stride=64, batches=3, stats_bytes=4096) == 4
+
+
+def test_debug_checks_flag_is_off_by_default_and_check_passes_cpu_tensors_through():
+    """`sparse.kernel.check` is the opt-in status check the autograd ops call: off unless `debug_checks` (or
+    BSA_DEBUG_CHECKS=1) is set, and it never touches tensors that are not on a GPU."""
+    import importlib
+    import os
+    kernel = importlib.import_module("sparse.kernel")
+    assert kernel.debug_checks == (os.environ.get("BSA_DEBUG_CHECKS", "0") not in ("", "0"))
+    t = torch.zeros(3)
+    old = kernel.debug_checks
+    try:
+        kernel.debug_checks = True
+        assert kernel.check(t) is t and kernel.check(None) is None
+    finally:
+        kernel.debug_checks = old

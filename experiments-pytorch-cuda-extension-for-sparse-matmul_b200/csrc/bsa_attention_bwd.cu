@@ -92,6 +92,12 @@ struct BwdParams {
     int kpm_div;
     long long kpm_stride;
     const float2* stats;       // per query row: (lse * log2(e), or +inf for a row without scores; D)
+    // head dim 64: the kernel by rows computes the statistics of its own rows from these and writes them to
+    // `stats_out` for the kernel by columns (no statistics launch)
+    const uint16_t* o;
+    const uint16_t* dout;
+    const float* lse;
+    float2* stats_out;
     uint16_t* out0;            // by rows: dQ; by columns: dV
     uint16_t* out1;            // by columns: dK
     uint32_t idesc_t, idesc_acc;
@@ -130,6 +136,31 @@ attention_backward_stats_kernel(const uint16_t* __restrict__ o, const uint16_t* 
         const float l = lse[row];
         stats[row] = make_float2(l == -INFINITY ? INFINITY : l * kLog2e, acc);
     }
+}
+
+// Sum over 16 consecutive head-dim columns of dO * O (two 16-byte loads from each).
+template <bool BF16>
+__device__ __forceinline__ float dot16(const uint16_t* __restrict__ a, const uint16_t* __restrict__ b) {
+    float acc = 0.f;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint4 x = *reinterpret_cast<const uint4*>(a + 8 * h), y = *reinterpret_cast<const uint4*>(b + 8 * h);
+        const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, yw[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 fa, fb;
+            if (BF16) {
+                fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xw[i]));
+                fb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&yw[i]));
+            } else {
+                fa = __half22float2(*reinterpret_cast<const __half2*>(&xw[i]));
+                fb = __half22float2(*reinterpret_cast<const __half2*>(&yw[i]));
+            }
+            acc = fmaf(fa.x, fb.x, acc);
+            acc = fmaf(fa.y, fb.y, acc);
+        }
+    }
+    return acc;
 }
 
 // Warp roles.  The compute warpgroups come first (a warp reads the TMEM sub-partition warp % 4).
@@ -671,7 +702,7 @@ int attention_backward(int dtype, const void* q, const void* k, const void* v, c
                        int quadrants, float2* stats, uint32_t* workspace, cudaStream_t stream) {
     const int64_t seq_q = block_rows * kTile, seq_k = block_cols * kTile;
     const long long rows = (long long)batches * seq_q;
-    {
+    if (head_dim != kTile) {        // head dim 64: the kernel by rows computes the statistics itself
         const int lanes = (int)head_dim / 8;
         const long long threads = rows * lanes;
         const unsigned grid = (unsigned)((threads + 255) / 256);
@@ -705,6 +736,10 @@ int attention_backward(int dtype, const void* q, const void* k, const void* v, c
     p.kpm_div = kpm ? (int)(batches / kpm_batches) : 1;
     p.kpm_stride = kpm_stride;
     p.stats = stats;
+    p.stats_out = stats;
+    p.o = static_cast<const uint16_t*>(o);
+    p.dout = static_cast<const uint16_t*>(dout);
+    p.lse = lse;
     // instruction descriptors: fp32 accumulate, fp16 / bf16 operands, M = 64; T: both operands K-major,
     // N = 64; accumulations: B (a Y tile set) with N contiguous, N = head_dim
     const uint32_t fmt = dtype == BSA_DTYPE_BF16 ? 1u : 0u;
@@ -721,14 +756,9 @@ int attention_backward(int dtype, const void* q, const void* k, const void* v, c
     p.out0 = static_cast<uint16_t*>(dq);
     p.out1 = nullptr;
     int st = BSA_OK;
-#if !defined(BSA_BWD_ONLY) || BSA_BWD_ONLY == 0      // (timing builds run one of the two kernels)
     st = head_dim == kTile ? launch_backward_rows_pipes(dtype, masked, map_q, map_do, map_k, map_v, p, stream)
                            : launch_backward<false>(dtype, masked, map_q, map_do, map_k, map_v, p, stream);
     if (st != BSA_OK) return st;
-#endif
-#if defined(BSA_BWD_ONLY) && BSA_BWD_ONLY == 0
-    return st;
-#endif
     // dV, dK by columns: X = (K_c, V_c), Y = (Q_r, dO_r)
     p.blocks = reinterpret_cast<const BlockDesc*>(col_blocks);
     p.table = col_table;

@@ -230,6 +230,22 @@ attention_backward_rows_pipes_kernel(const __grid_constant__ CUtensorMap map_q, 
         const uint64_t c2p = f2_pack(c2, c2), scp = f2_pack(sc, sc);
         int t0 = 0, i_no = 0;
         bool ok = true;
+        // Statistics of this lane's two query rows of block row `z, r`: (lse in log2 units, or +inf for a row
+        // without scores; D = sum_d dO_d O_d).  The four lanes of a quad take 16 head-dim columns each and two
+        // shuffles add the parts; the kernel by columns reads the pairs from `stats_out`.
+        auto row_stats = [&](int z, int r, float2& sa, float2& sb) {
+            const size_t row_i = (size_t)z * p.seq_q + (size_t)r * kTile + row_a;
+            float d_a = dot16<BF16>(p.o + row_i * kTile + 16 * q4, p.dout + row_i * kTile + 16 * q4);
+            float d_b = dot16<BF16>(p.o + (row_i + 8) * kTile + 16 * q4, p.dout + (row_i + 8) * kTile + 16 * q4);
+            const float l_a = p.lse[row_i], l_b = p.lse[row_i + 8];
+            d_a += __shfl_xor_sync(0xffffffffu, d_a, 1); d_a += __shfl_xor_sync(0xffffffffu, d_a, 2);
+            d_b += __shfl_xor_sync(0xffffffffu, d_b, 1); d_b += __shfl_xor_sync(0xffffffffu, d_b, 2);
+            sa = make_float2(l_a == -INFINITY ? INFINITY : l_a * kLog2e, d_a);
+            sb = make_float2(l_b == -INFINITY ? INFINITY : l_b * kLog2e, d_b);
+            if (q4 == 0) { p.stats_out[row_i] = sa; p.stats_out[row_i + 8] = sb; }
+        };
+        bool have_stats = false;                    // the statistics of the next row were computed at the end of the row before
+        float2 nst_a = make_float2(0.f, 0.f), nst_b = nst_a;
         while (ok) {
             // The row's entry from the producer (which walks the work items; rows without blocks never get here).
             const int slot = i_no & (kBwdRowRing - 1);
@@ -243,8 +259,8 @@ attention_backward_rows_pipes_kernel(const __grid_constant__ CUtensorMap map_q, 
             {
                 const uint8_t* kpm_row = (MASKED && p.kpm) ? p.kpm + (size_t)(row.x / p.kpm_div) * p.kpm_stride : nullptr;
                 const int pos_a = row.y * kTile + row_a;         // query position of row a (row b: + 8)
-                const float2* stats_z = p.stats + (size_t)row.x * p.seq_q;
-                const float2 st_a = stats_z[pos_a], st_b = stats_z[pos_a + 8];     // (lse in log2 units, D)
+                float2 st_a = nst_a, st_b = nst_b;
+                if (!have_stats) row_stats(row.x, row.y, st_a, st_b);
                 // per row: -lse2 for the exponent and -D * scale for dS = P * (dP * scale - D * scale)
                 const uint64_t nla = f2_pack(-st_a.x, -st_a.x), nlb = f2_pack(-st_b.x, -st_b.x);
                 const uint64_t nda = f2_pack(-st_a.y * sc, -st_a.y * sc), ndb = f2_pack(-st_b.y * sc, -st_b.y * sc);
@@ -326,6 +342,18 @@ attention_backward_rows_pipes_kernel(const __grid_constant__ CUtensorMap map_q, 
                 }
                 t0 += n;
                 if (!ok) break;
+                // The next row's statistics while this row's last accumulation is in flight (their loads would
+                // otherwise be waited for at the start of the next row, with its first products ready), if the
+                // producer has posted the row already -- it is one to two rows ahead.
+                {
+                    const int next = (i_no + 1) & (kBwdRowRing - 1);
+                    have_stats = __all_sync(0xffffffffu, mbar_test(&bars->row_full[g][next], (uint32_t)((i_no + 1) / kBwdRowRing) & 1u)) != 0;
+                    if (have_stats) {
+                        const int4 nrow = bars->rows[g][next];
+                        have_stats = nrow.z > 0;
+                        if (have_stats) row_stats(nrow.x, nrow.y, nst_a, nst_b);
+                    }
+                }
                 // ---- end of the row: dQ to global memory
                 ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[g], (uint32_t)i_no & 1u, abort_flag, p.status)) != 0;
                 if (!ok) break;

@@ -200,9 +200,10 @@ int bsa_attention_forward(int dtype, const void* q, const void* k, const void* v
  * the probability and score-gradient blocks never reach memory.  The
  * reference composes the same gradients from its matmul in sdd / dsd mode
  * (sparse/matmul.py:30-50 over sparse/native/sparse_kernels.cc:7-50) and its
- * softmax backward (sparse_softmax.cu:233-258).  Three launches: per-row
- * statistics, dQ by block rows (ROW layout), dK and dV by block columns
- * (COLUMN layout).
+ * softmax backward (sparse_softmax.cu:233-258).  Two launches at head dim 64:
+ * dQ by block rows (ROW layout; it also computes the per-row statistics and
+ * leaves them in `stats`), dK and dV by block columns (COLUMN layout); at
+ * head dim 128 a launch of its own computes the statistics first.
  *
  *   q, o, dout, dq  [batches, block_rows * block, head_dim]
  *   k, v, dk, dv    [batches, block_cols * block, head_dim]

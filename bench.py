@@ -201,7 +201,7 @@ def device_step(ops, lay, q, k, v, do, scale, block, events=None, causal=False):
 
 
 def fused_step(lay, q, k, v, do, scale, causal=False):
-    """The same step through the public fused op (one forward kernel, three backward kernels)."""
+    """The same step through the public fused op (one forward kernel, two backward kernels)."""
     from sparse import attention
     q, k, v = (t.detach().requires_grad_(True) for t in (q, k, v))
     o = attention(q, k, v, lay, scale, causal)
@@ -518,7 +518,7 @@ def run_ours(args):
     p_blocks = st_["p"]
     dds_ms = timed(lambda: sparse_ops.sparse_matmul(do, p_blocks, "dds", lay.row_layout, lay.col_layout, True, False, block), 5)
     del p_blocks, st_, alone_calls
-    # the fused forward (one kernel for sdd -> softmax -> dsd) and the fused backward (statistics, dQ by block
+    # the fused forward (one kernel for sdd -> softmax -> dsd) and the fused backward (dQ by block
     # rows, dK / dV by block columns), reported beside the unfused operators
     from sparse.attention import attention_lse
     fused_ms = timed(lambda: attention_lse(q, k, v, lay, scale), 20)
@@ -582,7 +582,7 @@ def run_ours(args):
                         "note": "forward only, outside the timed step; Q, K, V read and O written once, "
                                 "scores and probabilities never leave the SM"}
         fused_step_ms = fused_ms + fused_bwd_ms
-        fused_step_report = {"kernels": "attention_forward_pipes_kernel + attention_backward_rows_pipes_kernel + attention_backward_cols_pipes_kernel (+ statistics)",
+        fused_step_report = {"kernels": "attention_forward_pipes_kernel + attention_backward_rows_pipes_kernel + attention_backward_cols_pipes_kernel",
                              "forward_ms": round(fused_ms, 4), "backward_ms": round(fused_bwd_ms, 4),
                              "ms": round(fused_step_ms, 4),
                              "TFLOP/s": round(6 * flops_matmul / (fused_step_ms * 1e-3) / 1e12, 1),

@@ -43,7 +43,7 @@ namespace bsa {
 namespace {
 
 constexpr int kBlk = 32;                        // block edge = panel edge in elements
-constexpr int kMaxStages = 16;
+constexpr int kMaxStages = 32;
 constexpr int kPipeBytes = 27 * 8192;           // shared memory for all stages
 constexpr int kAccCols = 256;                   // TMEM columns per accumulator buffer
 constexpr int kTmemCols = 2 * kAccCols;
@@ -251,7 +251,78 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     const bool a_mn_major = p.trans_a != 0;      // op(A) panel arrives with M contiguous
     const bool b_mn_major = p.trans_b == 0;      // op(B) panel arrives with N contiguous
 
-    if (warp < kProducerWarps) {
+    if (warp < kProducerWarps && !is_sdd && p.split == 0) {
+        // ------------------------------------------------------------ TMA producers, dsd / dds at block 32
+        // K-step n of the CTA belongs to producer n % 4 and to stage n % stages, as below, but a producer does
+        // not broadcast a block's descriptor and issue its copies from one lane, one K-step after the other:
+        // lane l of the warp holds descriptor base + l of the group's blocks (the descriptor window), so in every
+        // batch of up to 16 consecutive K-steps the (up to four) lanes that hold this producer's blocks each wait
+        // for their own stage, arm its barrier and issue their block's copies -- one instruction for the copies of
+        // several K-steps, no shuffles.  (One warp taking all K-steps of a batch was slower: a copy costs about
+        // 100 cycles of its warp whichever lane issues it.)
+        int n0 = 0;                              // K-steps of the CTA before the current item
+        bool ok = true;
+        const int batch = p.stages >= 16 ? 16 : (p.stages >= 8 ? 8 : 4);       // divides 32, at most `stages`
+        Cursor cur;
+        cur.init(p, p.split);
+        BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
+        while (ok && cur.valid()) {
+            BlockDesc pre_next{0, 0};
+            if (cur.has_next()) pre_next = load_first_chunk(p.blocks, cur.next_first(), cur.next_count(), lane);
+            const int count = cur.count;
+            const int nb = b_panels<MODE>(p, count, cur.chunk, 0);
+            DescWindow win;
+            win.begin(p.blocks, cur.first, count, pre, lane);
+            for (int kb = 0; ok && kb < count; kb += batch) {
+                win.seek(p.blocks, cur.first, count, kb, lane);
+                const int l = lane - (kb - win.base);
+                const int n = n0 + kb + l;
+                const bool has = l >= 0 && l < batch && kb + l < count && (n & (kProducerWarps - 1)) == warp;
+                const BlockDesc d = win.mine;
+                const int round = n / p.stages, stage = n - round * p.stages;      // (once per batch and lane)
+                const uint32_t use = (uint32_t)round & 1u;
+                ok = __all_sync(0xffffffffu, !has || mbar_wait(&bars->empty[stage], use ^ 1u, abort_flag, p.status)) != 0;
+                if (ok && has) {
+                    uint8_t* slot = stage_base + stage * p.stage_bytes;
+                    uint8_t* slot_b = slot + 2 * kPanelBytes;
+                    uint64_t* full = &bars->full[stage];
+                    mbar_expect_tx(full, (uint32_t)((kAPanels + (kWideB ? (nb + 1) & ~1 : nb)) * kPanelBytes));
+                    const int sy = d.idx * kBlk;             // the sparse tensor viewed as [nnz * 32, 32]
+                    if (MODE == BSA_MODE_DSD) {
+                        const int k0 = (p.trans_a ? d.row() : d.col()) * kBlk;
+                        tma_load_3d(slot, &map_a, full, 0, sy, cur.z);
+                        tma_load_3d(slot + kPanelBytes, &map_a, full, 0, sy, cur.z);
+                        for (int j = 0; j < nb; j += kWideB ? 2 : 1) {
+                            const int c0 = (cur.chunk * 4 + j) * kBlk;
+                            if (b_mn_major) tma_load_3d(slot_b + j * kPanelBytes, &map_b, full, c0, k0, cur.z);
+                            else            tma_load_3d(slot_b + j * kPanelBytes, &map_b, full, k0, c0, cur.z);
+                        }
+                    } else {
+                        const int k0 = (p.trans_b ? d.col() : d.row()) * kBlk;
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            const int m0 = (cur.chunk * 2 + j) * kBlk;   // past the end: the box reads as zero
+                            if (a_mn_major) tma_load_3d(slot + j * kPanelBytes, &map_a, full, m0, k0, cur.z);
+                            else            tma_load_3d(slot + j * kPanelBytes, &map_a, full, k0, m0, cur.z);
+                        }
+                        tma_load_3d(slot_b, &map_b, full, 0, sy, cur.z);
+                    }
+                }
+                __syncwarp();
+            }
+            n0 += count;
+            pre = pre_next;
+            cur.advance();
+        }
+        if (lane == 0 && *(volatile int*)abort_flag) {
+            // Give copies that were issued a bounded chance to land before the CTA exits.
+            const unsigned long long t0 = global_ns();
+            for (int s = 0; s < p.stages; ++s)
+                while (!mbar_try_wait(&bars->full[s], 0) && !mbar_try_wait(&bars->full[s], 1) &&
+                       global_ns() - t0 < kWaitLimitNs / 4) {}
+        }
+        __syncwarp();
+    } else if (warp < kProducerWarps) {
         // ------------------------------------------------------------ TMA producers
         // Producer w loads K-steps w, w + 4, ... of the CTA; the stage count is a multiple of 4,
         // so its stage pointer advances by 4 and a stage is always filled by the same producer

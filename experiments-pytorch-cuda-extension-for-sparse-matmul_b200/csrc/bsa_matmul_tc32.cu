@@ -15,10 +15,11 @@
 //                     ranges of M/N (leading byte offset = one panel); one MMA consumes 1024
 //                     bytes of rows (16 rows of 16-bit, 8 rows of fp32 elements).
 // A K-step is 32 elements of K: two kind::f16 MMAs (K = 16) or four kind::tf32 MMAs (K = 8).
-// The MMA shape is M = 64.  sdd and dsd have 32 rows of A only and load that panel twice, so the
-// accumulator rows 32-63 repeat rows 0-31 in the TMEM quarters 2 and 3 and all four warps of an
-// epilogue warpgroup have output pieces to store (a warp reads its own quarter only); dds, whose M
-// is a slice of a dense dimension, uses all 64 rows.
+// The MMA shape is M = 64.  sdd has 32 rows of A only and loads that panel twice, so the accumulator
+// rows 32-63 repeat rows 0-31 in the TMEM quarters 2 and 3 and all four warps of an epilogue
+// warpgroup have output pieces to store (a warp reads its own quarter only); dsd keeps one A panel
+// per stage (smaller stages, more of them in flight) and never reads the accumulator rows 32-63;
+// dds, whose M is a slice of a dense dimension, uses all 64 rows.
 //   sdd  item = block row r; its blocks are taken 8 (fp32: 4) at a time as one N = 256 (128)
 //        accumulation over the dense inner size.
 //   dsd  item = group m and a 128-wide slice of N; one accumulation over the group's blocks.
@@ -212,10 +213,14 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     constexpr int kEpilogueGroups = kSplit ? 1 : 2;
     constexpr bool is_sdd = MODE == BSA_MODE_SDD;
     constexpr bool kWideB = MODE == BSA_MODE_DSD && ES == 2;   // dsd, 16-bit: the dense operand's panels are copied in pairs
-    // The MMA is M = 64.  dds fills both A panels with a 64-tall slice of its dense operand.  sdd and dsd have 32
-    // rows of A only and load them twice: accumulator rows 32-63 then repeat rows 0-31 in the TMEM quarters 2 and 3,
-    // and the epilogue warps of those quarters, which would otherwise idle, take every other output piece.
-    constexpr int kAPanels = 2;
+    // The MMA is M = 64.  dds fills both A panels with a 64-tall slice of its dense operand.  sdd has 32 rows of A
+    // only and loads them twice: accumulator rows 32-63 then repeat rows 0-31 in the TMEM quarters 2 and 3, and
+    // the epilogue warps of those quarters, which would otherwise idle, take every other output piece.
+    // dsd loads its 32 rows of A once and keeps one panel of A per stage (rows 32-63 of the MMA then read whatever
+    // follows and their accumulator rows are never read): its stages are smaller and more of them are in flight,
+    // which is what bounds it (2 KB of the sparse operand per stage against the memory latency).
+    constexpr int kAPanels = MODE == BSA_MODE_DSD ? 1 : 2;
+    constexpr bool kDupA = MODE == BSA_MODE_SDD;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -284,14 +289,13 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 ok = __all_sync(0xffffffffu, !has || mbar_wait(&bars->empty[stage], use ^ 1u, abort_flag, p.status)) != 0;
                 if (ok && has) {
                     uint8_t* slot = stage_base + stage * p.stage_bytes;
-                    uint8_t* slot_b = slot + 2 * kPanelBytes;
+                    uint8_t* slot_b = slot + kAPanels * kPanelBytes;
                     uint64_t* full = &bars->full[stage];
                     mbar_expect_tx(full, (uint32_t)((kAPanels + (kWideB ? (nb + 1) & ~1 : nb)) * kPanelBytes));
                     const int sy = d.idx * kBlk;             // the sparse tensor viewed as [nnz * 32, 32]
                     if (MODE == BSA_MODE_DSD) {
                         const int k0 = (p.trans_a ? d.row() : d.col()) * kBlk;
                         tma_load_3d(slot, &map_a, full, 0, sy, cur.z);
-                        tma_load_3d(slot + kPanelBytes, &map_a, full, 0, sy, cur.z);
                         for (int j = 0; j < nb; j += kWideB ? 2 : 1) {
                             const int c0 = (cur.chunk * 4 + j) * kBlk;
                             if (b_mn_major) tma_load_3d(slot_b + j * kPanelBytes, &map_b, full, c0, k0, cur.z);
@@ -416,7 +420,7 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         ok = __all_sync(0xffffffffu, mbar_wait(&bars->empty[stage], phase ^ 1, abort_flag, p.status)) != 0;
                         if (ok && elect_one()) {
                             uint8_t* slot = stage_base + stage * p.stage_bytes;
-                            uint8_t* slot_b = slot + 2 * kPanelBytes;
+                            uint8_t* slot_b = slot + kAPanels * kPanelBytes;
                             uint64_t* full = &bars->full[stage];
                             if (is_sdd && k == 0) {         // the accumulation's entry for the epilogue warps
                                 SddEntry& e = bars->ents[flush_no & (kSddEntries - 1)];
@@ -444,7 +448,6 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                             } else if (MODE == BSA_MODE_DSD) {
                                 const int k0 = (p.trans_a ? d.row : d.col) * kBlk;
                                 tma_load_3d(slot, &map_a, full, sx, sy, cur.z);
-                                tma_load_3d(slot + kPanelBytes, &map_a, full, sx, sy, cur.z);
                                 // 16-bit: the dense panels come in pairs, one box each (see encode_map32)
                                 for (int j = 0; j < nb; j += kWideB ? 2 : 1) {
                                     const int n0 = (cur.chunk * 4 + j) * kBlk;
@@ -539,7 +542,7 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         tc_fence_after();
                         const uint32_t slot = smem_u32(stage_base + stage * p.stage_bytes);
                         const uint64_t da = desc_a0 | (uint64_t)((slot & 0x3FFFFu) >> 4);
-                        const uint64_t db = desc_b0 | (uint64_t)(((slot + 2 * kPanelBytes) & 0x3FFFFu) >> 4);
+                        const uint64_t db = desc_b0 | (uint64_t)(((slot + kAPanels * kPanelBytes) & 0x3FFFFu) >> 4);
                         if (elect_one()) {
 #pragma unroll
                             for (int kk = 0; kk < kMmasPerStep; ++kk) {
@@ -597,7 +600,7 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     if (!ok) break;
                     uint8_t* slot = stage_base + stage * p.stage_bytes;
                     // both A panels and nb B panels
-                    const int chunks16 = (2 + nb) * (kPanelBytes / 16);
+                    const int chunks16 = (kAPanels + nb) * (kPanelBytes / 16);
                     for (int i = lane; i < chunks16; i += 32) {
                         uint4* hi_ptr = reinterpret_cast<uint4*>(slot) + i;
                         uint4* lo_ptr = reinterpret_cast<uint4*>(slot + p.lo_offset) + i;
@@ -625,11 +628,11 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         const int group = (warp - kFirstEpilogueWarp) >> 2;     // 16-bit: drains accumulator buffer `group`
         const int quad = warp & 3;                   // TMEM sub-partition this warp may read
         // accumulator row held by this lane (lanes 0-15 only); sdd / dsd: output row, the quarters 2 and 3 repeat 0 and 1
-        const int row = (MODE == BSA_MODE_DDS ? quad : (quad & 1)) * 16 + lane;
-        const int half = MODE == BSA_MODE_DDS ? 0 : quad >> 1;       // sdd / dsd: this warp takes the pieces t with t % 2 == half
-        constexpr int kPieceStep = MODE == BSA_MODE_DDS ? 1 : 2;
+        const int row = (!kDupA ? quad : (quad & 1)) * 16 + lane;
+        const int half = !kDupA ? 0 : quad >> 1;       // sdd: this warp takes the pieces t with t % 2 == half
+        constexpr int kPieceStep = !kDupA ? 1 : 2;
         const bool row_lane = lane < 16;
-        const bool quad_active = true;
+        const bool quad_active = MODE != BSA_MODE_DSD || quad < 2;
         const int parts = is_sdd ? 1 : p.issuers;
         const int part_stride = kAccCols / p.issuers;
         int flush_no = 0, step = 0;
@@ -878,7 +881,7 @@ int matmul_tc32(const MatmulArgs& g) {
     else if (g.mode == BSA_MODE_DSD && g.size_n > 2 * kBlk) { nb_max = 4; p.issuers = 2; }
     else if (g.mode == BSA_MODE_DSD) { nb_max = 2; p.issuers = 4; }
     else { nb_max = 1; p.issuers = 4; }
-    p.lo_offset = (2 + nb_max) * panel_bytes;
+    p.lo_offset = ((g.mode == BSA_MODE_DSD ? 1 : 2) + nb_max) * panel_bytes;
     p.stage_bytes = p.lo_offset * (f32 ? 2 : 1);
     // Every mbarrier must be waited on by the same threads in every phase (a parity wait cannot
     // tell phases two apart), so the stage count is a multiple of the producer count, and for sdd,

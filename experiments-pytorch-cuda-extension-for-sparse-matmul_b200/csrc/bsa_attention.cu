@@ -630,7 +630,7 @@ constexpr int kPipeTiles = 6;                   // Q, K x 3, V x 2
 constexpr int kPipeKRing = 3;
 constexpr int kPipeDescs = 8;
 constexpr int kPipeRows = 8;
-struct __align__(8) PipeBarriers {
+struct __align__(16) PipeBarriers {
     uint64_t q_full[2], q_empty[2];             // [pipeline]
     uint64_t k_full[2][kPipeKRing], qk_done[2][kPipeKRing];   // [pipeline][K stage]: qk_done = S is ready and the K stage is free
     uint64_t v_full[2][2], pv_done[2][2];       // [pipeline][tile & 1]: pv_done = the P buffer and the V stage are free
@@ -869,7 +869,6 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
         const bool masked_op = MASKED && (p.causal != 0 || p.kpm != nullptr || p.quadrants != 0);
         const float c2 = p.scale_log2, c2abs = fabsf(c2);
         const bool flip = c2 < 0.f;
-        const uint64_t c2p = f2_pack(c2, c2);
         int t0 = 0, i_no = 0;                       // tiles and non-empty rows before the current row
         KRing kr;                                   // K stage (= qk_done barrier) of the next tile to be requested from TMEM
         bool ok = true;
@@ -926,8 +925,8 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
                 // P V to have retired.
                 constexpr float kSlack = 8.f;
                 float m_a = -INFINITY, m_b = -INFINITY;
-                // row sums: per row two independent two-wide accumulators (even / odd column units)
-                uint64_t la2[2] = {0ull, 0ull}, lb2[2] = {0ull, 0ull};
+                // row sums: per row four independent accumulators (even / odd column units x the two columns of a pair)
+                float la[4] = {0.f, 0.f, 0.f, 0.f}, lb[4] = {0.f, 0.f, 0.f, 0.f};
                 uint32_t r[32];
                 // wait for S of tile t (K stage / barrier position kr), unless an earlier test has seen it
                 // complete, and start loading it
@@ -1005,8 +1004,8 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
                         if (__any_sync(0xffffffffu, up_a || up_b)) {
                             const float al_a = !up_a ? 1.f : (m_a == -INFINITY ? 0.f : attn_exp2(m_a - x_a));
                             const float al_b = !up_b ? 1.f : (m_b == -INFINITY ? 0.f : attn_exp2(m_b - x_b));
-                            if (up_a) { m_a = x_a; const uint64_t f = f2_pack(al_a, al_a); la2[0] = f2_mul(la2[0], f); la2[1] = f2_mul(la2[1], f); }
-                            if (up_b) { m_b = x_b; const uint64_t f = f2_pack(al_b, al_b); lb2[0] = f2_mul(lb2[0], f); lb2[1] = f2_mul(lb2[1], f); }
+                            if (up_a) { m_a = x_a; la[0] *= al_a; la[1] *= al_a; la[2] *= al_a; la[3] *= al_a; }
+                            if (up_b) { m_b = x_b; lb[0] *= al_b; lb[1] *= al_b; lb[2] *= al_b; lb[3] *= al_b; }
                             // O is complete up to the previous tile once that tile's P V has retired
                             if (!__all_sync(0xffffffffu, mbar_wait(&bars->pv_done[g][(t - 1) & 1], (uint32_t)((t - 1) >> 1) & 1u, abort_flag, p.status))) { ok = false; break; }
                             tc_fence_after();
@@ -1028,22 +1027,21 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
                         }
                     }
                     const float sub_a = m_a == -INFINITY ? 0.f : m_a, sub_b = m_b == -INFINITY ? 0.f : m_b;
-                    // P = exp2(c2 * s - m): per pair of columns one two-wide FMA, two exp2, one two-wide add into
-                    // the row sum and one pack.  w[2u + h]: columns 8u + 2 q4 + {0, 1} of row a (h = 0) / row b (h = 1):
-                    // the register order of the 16x128b store.
-                    const uint64_t na = f2_pack(-sub_a, -sub_a), nb = f2_pack(-sub_b, -sub_b);
+                    // P = exp2(c2 * s - m): per element one FMA, one exp2, one add into the row sum, per pair one pack.
+                    // (Scalar instructions: the two-wide fp32 forms save a third of the arithmetic instructions but
+                    // need their operands in aligned register pairs, and the moves that arrange them cost more than
+                    // they save here: 0.109 against 0.106 ms.)  w[2u + h]: columns 8u + 2 q4 + {0, 1} of row a (h = 0) /
+                    // row b (h = 1): the register order of the 16x128b store.
                     uint32_t w[16];
 #pragma unroll
                     for (int u = 0; u < 8; ++u) {
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
-                            const uint64_t t2 = f2_fma(f2_pack(__uint_as_float(r[4 * u + 2 * h]), __uint_as_float(r[4 * u + 2 * h + 1])),
-                                                       c2p, h ? nb : na);
-                            float e0, e1;
-                            f2_unpack(t2, e0, e1);
+                            float e0 = fmaf(__uint_as_float(r[4 * u + 2 * h]), c2, h ? -sub_b : -sub_a);
+                            float e1 = fmaf(__uint_as_float(r[4 * u + 2 * h + 1]), c2, h ? -sub_b : -sub_a);
                             e0 = attn_exp2(e0); e1 = attn_exp2(e1);
-                            if (h) lb2[u & 1] = f2_add(lb2[u & 1], f2_pack(e0, e1));
-                            else   la2[u & 1] = f2_add(la2[u & 1], f2_pack(e0, e1));
+                            if (h) { lb[2 * (u & 1)] += e0; lb[2 * (u & 1) + 1] += e1; }
+                            else   { la[2 * (u & 1)] += e0; la[2 * (u & 1) + 1] += e1; }
                             w[2 * u + h] = pack2<BF16>(e0, e1);
                         }
                     }
@@ -1062,10 +1060,8 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
                 // ---- end of the row: O / l and the log-sum-exp
                 float l_a, l_b;
                 {
-                    float x0, x1, y0, y1;
-                    f2_unpack(f2_add(la2[0], la2[1]), x0, x1);
-                    f2_unpack(f2_add(lb2[0], lb2[1]), y0, y1);
-                    l_a = x0 + x1; l_b = y0 + y1;
+                    l_a = (la[0] + la[1]) + (la[2] + la[3]);
+                    l_b = (lb[0] + lb[1]) + (lb[2] + lb[3]);
                 }
                 l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
                 l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);

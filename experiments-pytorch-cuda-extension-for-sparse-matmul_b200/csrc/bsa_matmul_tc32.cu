@@ -48,6 +48,11 @@ constexpr int kMaxStages = 32;
 constexpr int kPipeBytes = 27 * 8192;           // shared memory for all stages
 constexpr int kAccCols = 256;                   // TMEM columns per accumulator buffer
 constexpr int kTmemCols = 2 * kAccCols;
+// sdd has four accumulator buffers: an M = 64 accumulator occupies lanes 0-15 of each 32-lane quarter of tensor
+// memory, and a second one fits into lanes 16-31 of the same columns (lane offset 16 in the MMA's D address; a
+// 32-lane TMEM load returns both).  Buffers 0 and 2 share columns 0-255, buffers 1 and 3 columns 256-511.  With two
+// buffers the cycle MMAs -> barrier -> epilogue -> barrier of a buffer (2 600 cycles) bounded the kernel.
+constexpr int kSddBufs = 4;
 constexpr int kProducerWarps = 4;
 constexpr int kFirstMmaWarp = 4;
 constexpr int kFirstEpilogueWarp = 8;
@@ -68,8 +73,8 @@ struct __align__(16) Barriers {
     uint64_t full[kMaxStages];      // TMA data of a stage has landed
     uint64_t ready[kMaxStages];     // fp32: the stage has been split into hi / lo
     uint64_t empty[kMaxStages];     // the MMAs that read a stage have retired
-    uint64_t acc_full[2];
-    uint64_t acc_empty[2];
+    uint64_t acc_full[4];           // dsd / dds: two accumulator buffers; sdd: four (see kSddBufs)
+    uint64_t acc_empty[4];
     uint64_t ent_full[kSddEntries];
     uint64_t drain;
     uint32_t tmem_base;
@@ -236,7 +241,7 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         for (int s = 0; s < kMaxStages; ++s) {
             mbar_init(&bars->full[s], 1); mbar_init(&bars->ready[s], 1); mbar_init(&bars->empty[s], 1);
         }
-        for (int s = 0; s < 2; ++s) { mbar_init(&bars->acc_full[s], arrivals); mbar_init(&bars->acc_empty[s], 4); }
+        for (int s = 0; s < 4; ++s) { mbar_init(&bars->acc_full[s], arrivals); mbar_init(&bars->acc_empty[s], 4); }
         if (is_sdd) for (int s = 0; s < kSddEntries; ++s) mbar_init(&bars->ent_full[s], 1);
         mbar_init(&bars->drain, (uint32_t)p.issuers);
         bars->abort_flag = 0;
@@ -521,18 +526,19 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 item_shape<MODE>(p, cur.count << p.split, flushes, ksteps);
                 if (ksteps == 0) continue;          // empty group: the epilogue writes zeros on its own
                 for (int f = 0; ok && f < flushes; ++f, ++flush_no) {
-                    const int acc = flush_no & 1;
-                    if (is_sdd && p.issuers == 2 && acc != w) {
+                    const int acc = is_sdd ? (flush_no & (kSddBufs - 1)) : (flush_no & 1);
+                    const uint32_t acc_use = (uint32_t)(is_sdd ? flush_no >> 2 : flush_no >> 1) & 1u;
+                    if (is_sdd && p.issuers == 2 && (flush_no & 1) != w) {
                         stage += ksteps;
                         while (stage >= p.stages) { stage -= p.stages; phase ^= 1; }
                         continue;
                     }
                     const int nb = b_panels<MODE>(p, cur.count << p.split, cur.chunk, f);
                     const uint32_t idesc = p.idesc | ((uint32_t)((nb * kBlk) >> 3) << 17);
-                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_empty[acc], ((uint32_t)(flush_no >> 1) & 1u) ^ 1u, abort_flag, p.status)) != 0;
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_empty[acc], acc_use ^ 1u, abort_flag, p.status)) != 0;
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t d = tmem_base + (uint32_t)(acc * kAccCols) + part_col;
+                    const uint32_t d = tmem_base + (uint32_t)((acc & 1) * kAccCols) + ((uint32_t)((acc >> 1) * 16) << 16) + part_col;
                     bool issued = false;
                     const int k_first = is_sdd ? 0 : ((w - step0) & issuer_mask);
                     const int k_inc = is_sdd ? 1 : p.issuers;
@@ -648,12 +654,15 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 const SddEntry& ent = bars->ents[slot];
                 const int pieces = ent.pieces;
                 if (pieces == 0) break;             // no more accumulations
-                const int acc = flush & 1;
-                ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_full[acc], (uint32_t)(flush >> 1) & 1u, abort_flag, p.status)) != 0;
+                const int acc = flush & (kSddBufs - 1);
+                ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_full[acc], (uint32_t)(flush >> 2) & 1u, abort_flag, p.status)) != 0;
                 if (!ok) break;
                 tc_fence_after();
                 if (quad_active) {
-                    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * kAccCols);
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)((acc & 1) * kAccCols);
+                    // the buffer's rows are in lanes 0-15 (buffers 0, 1) or 16-31 (buffers 2, 3) of the loaded 32
+                    const bool my_lane = (lane >> 4) == (acc >> 1);
+                    const int my_row = (quad & 1) * 16 + (lane & 15);
                     auto store = [&](const uint32_t (&v)[32], int t) {
                         const long long dst0 = ent.dst[t];
                         // never write outside the output: a descriptor that does not belong to this layout is
@@ -663,7 +672,7 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                             atomicExch(p.status, (uint32_t)BSA_ERR_BAD_SHAPE);
                             atomicExch(p.status + 1, dst0 < 0 ? (uint32_t)(-1ll - dst0) : (uint32_t)(dst0 >> 12));
                         }
-                        if (row_lane && in_bounds) store_piece<DT>(p.c, (size_t)dst0 + (size_t)row * p.ldc, v, kBlk);
+                        if (my_lane && in_bounds) store_piece<DT>(p.c, (size_t)dst0 + (size_t)my_row * p.ldc, v, kBlk);
                     };
                     uint32_t va[32], vb[32];
                     if (half < pieces) tc_ld_32x32b_x32(taddr + (uint32_t)(half * kBlk), va);

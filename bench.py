@@ -530,13 +530,16 @@ def run_ours(args):
 
     # ---- parity inside the benchmark, on every rank
     check = verify(sparse_ops, lay, q, k, v, do, scale, block, pattern.numpy(), world, rank, dev)
+    sparse_ops.check_device_status(local_rank)
 
     # ---- side reports on the other benchmark configurations (outside every timed region)
     side = {}
     if not args.no_side:
         if rank == 0:
             side["cfg2"] = side_cfg2(sparse_ops, dev)
+            sparse_ops.check_device_status(local_rank)
             side["cfg4"] = side_cfg4(sparse_ops, dev)
+            sparse_ops.check_device_status(local_rank)
         torch.cuda.empty_cache()
         if world > 1:
             dist.barrier()

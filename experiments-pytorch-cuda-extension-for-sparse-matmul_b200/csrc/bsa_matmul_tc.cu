@@ -332,11 +332,20 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             pre = pre_next;
             cur.advance();
         }
-        if (is_sdd && warp == 0 && ok && elect_one()) {
-            // no more accumulations: one closing entry for each of the epilogue groups
-            for (int e = flush_no; e < flush_no + kSddGroups; ++e) {
-                bars->ents[e & (kSddEntries - 1)] = make_int4(0, 0, 0, 0);
-                mbar_arrive(&bars->ent_full[e & (kSddEntries - 1)]);
+        if (is_sdd && ok) {
+            // No more accumulations: one closing entry for each of the epilogue groups.  Each is posted by the
+            // producer that would have loaded its first K-step, i.e. the one that has posted every earlier entry
+            // of that slot.  With two issuers the even and the odd accumulations are two pipelines (producers,
+            // stages, issuer, accumulator buffers, epilogue groups, entry slots) that nothing keeps in step: a
+            // producer of one may finish while the other is more than a ring behind, and a closing entry posted by
+            // it into the other's slots would complete a phase that belongs to an accumulation still to come.
+            const int ksteps = (p.size_k + kTile - 1) / kTile;
+            for (int j = 0; j < kSddGroups; ++j) {
+                const int e = flush_no + j;
+                if (((step0 + j * ksteps) & (kProducerWarps - 1)) == warp && elect_one()) {
+                    bars->ents[e & (kSddEntries - 1)] = make_int4(0, 0, 0, 0);
+                    mbar_arrive(&bars->ent_full[e & (kSddEntries - 1)]);
+                }
             }
         }
         __syncwarp();

@@ -481,11 +481,19 @@ tc32_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             pre = pre_next;
             cur.advance();
         }
-        if (is_sdd && warp == 0 && ok && elect_one()) {
-            // no more accumulations: one closing entry for each of the epilogue groups
-            for (int e = flush_no; e < flush_no + 2; ++e) {
-                bars->ents[e & (kSddEntries - 1)].pieces = 0;
-                mbar_arrive(&bars->ent_full[e & (kSddEntries - 1)]);
+        if (is_sdd && ok) {
+            // No more accumulations: one closing entry for each of the epilogue groups, posted by the producer that
+            // would have loaded its first K-step -- the one that has posted every earlier entry of that slot.  (With
+            // two issuers the even and the odd accumulations are two pipelines that nothing keeps in step; a closing
+            // entry posted into the other pipeline's slot by a producer that finished more than a ring ahead of it
+            // would complete a phase that belongs to an accumulation still to come.)
+            const int ksteps = (p.size_k + kBlk - 1) / kBlk;
+            for (int j = 0; j < 2; ++j) {
+                const int e = flush_no + j;
+                if (((step0 + j * ksteps) & (kProducerWarps - 1)) == warp && elect_one()) {
+                    bars->ents[e & (kSddEntries - 1)].pieces = 0;
+                    mbar_arrive(&bars->ent_full[e & (kSddEntries - 1)]);
+                }
             }
         }
         __syncwarp();

@@ -170,6 +170,29 @@ def test_config4_fp32_stress_slice(mode, ta, tb):
     run_case(mode, ta, tb, g["pattern"], 32, 128, torch.float32, "auto", batch=(1,), seed=4000, dist="uniform")
 
 
+@pytest.mark.parametrize("block,dim,seq,slices", [(64, 128, 8192, 512), (64, 64, 4096, 1024), (32, 64, 4096, 512)])
+def test_sdd_with_thousands_of_accumulations_per_cta(block, dim, seq, slices):
+    """sdd over many batch entries: every CTA runs through some thousand accumulations, so its two issue pipelines
+    (even and odd accumulations) drift far apart.  The result must equal, bit for bit, the same slices computed
+    32 at a time (short launches, the size the oracle comparisons cover), launch after launch, and no kernel may
+    report a bounded wait that ran out.  (The largest case is benchmark configuration 5's Q.K^T.)"""
+    from sparse import SparseLayout
+    from sparse.kernel import sparse_ops
+    from sparse.patterns import bigbird
+    lay = SparseLayout(bigbird(seq // block, 1, 2, 3, 5000), block=block, device="cuda")
+    gen = torch.Generator(device="cuda").manual_seed(77)
+    q, k = (torch.randn(slices, seq, dim, device="cuda", generator=gen).half() for _ in range(2))
+    rl, cl = lay.row_layout, lay.col_layout
+    parts = torch.cat([sparse_ops.sparse_matmul(q[i:i + 32], k[i:i + 32], "sdd", rl, cl, False, True, block)
+                       for i in range(0, slices, 32)])
+    sparse_ops.check_device_status(0)
+    for launch in range(6):
+        whole = sparse_ops.sparse_matmul(q, k, "sdd", rl, cl, False, True, block)
+        sparse_ops.check_device_status(0)
+        assert torch.equal(whole, parts), "launch %d differs from the 32-slice launches" % launch
+        del whole
+
+
 def test_autograd_matches_dense_autograd():
     """Gradients through sparse.matmul equal those of the dense masked computation."""
     from sparse import SparseLayout, matmul

@@ -194,17 +194,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             cur.advance();
         }
         if (lane == 0 && *(volatile int*)abort_flag) {
-            // Give copies that were issued a bounded chance to land before the CTA exits.
-            const unsigned long long t0 = global_ns();
-            for (int s = 0; s < p.ring; ++s)
-                while (!mbar_try_wait(&bars->k_full[s], 0) && !mbar_try_wait(&bars->k_full[s], 1) &&
-                       global_ns() - t0 < kWaitLimitNs / 4) {}
-            for (int s = 0; s < p.vring; ++s)
-                while (!mbar_try_wait(&bars->v_full[s], 0) && !mbar_try_wait(&bars->v_full[s], 1) &&
-                       global_ns() - t0 < kWaitLimitNs / 4) {}
-            for (int s = 0; s < p.qbufs; ++s)
-                while (!mbar_try_wait(&bars->q_full[s], 0) && !mbar_try_wait(&bars->q_full[s], 1) &&
-                       global_ns() - t0 < kWaitLimitNs / 4) {}
+            let_copies_land();      // (issued by this warp; see the helper)
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -774,16 +764,7 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
         }
         __syncwarp();
         if (lane == 0 && *(volatile int*)abort_flag) {
-            // Give copies that were issued a bounded chance to land before the CTA exits.
-            const unsigned long long tw = global_ns();
-            for (int s = 0; s < kPipeKRing; ++s)
-                while (!mbar_try_wait(&bars->k_full[g][s], 0) && !mbar_try_wait(&bars->k_full[g][s], 1) &&
-                       global_ns() - tw < kWaitLimitNs / 4) {}
-            for (int s = 0; s < 2; ++s)
-                while (!mbar_try_wait(&bars->v_full[g][s], 0) && !mbar_try_wait(&bars->v_full[g][s], 1) &&
-                       global_ns() - tw < kWaitLimitNs / 4) {}
-            while (!mbar_try_wait(&bars->q_full[g], 0) && !mbar_try_wait(&bars->q_full[g], 1) &&
-                   global_ns() - tw < kWaitLimitNs / 4) {}
+            let_copies_land();      // (issued by this warp; see the helper)
         }
         __syncwarp();
     } else if (warp == 1 || warp == 3) {

@@ -262,14 +262,7 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
             cur.advance();
         }
         if (lane == 0 && *(volatile int*)abort_flag) {
-            // Give copies that were issued a bounded chance to land before the CTA exits.
-            const unsigned long long t0 = global_ns();
-            for (int s = 0; s < p.ring; ++s)
-                while (!mbar_try_wait(&bars->y_full[s], 0) && !mbar_try_wait(&bars->y_full[s], 1) &&
-                       global_ns() - t0 < kWaitLimitNs / 4) {}
-            for (int s = 0; s < p.xbufs; ++s)
-                while (!mbar_try_wait(&bars->x_full[s], 0) && !mbar_try_wait(&bars->x_full[s], 1) &&
-                       global_ns() - t0 < kWaitLimitNs / 4) {}
+            let_copies_land();      // (issued by this warp; see the helper)
         }
         __syncwarp();
     } else if (warp >= kBwdFirstTWarp && warp < kBwdFirstOutWarp) {

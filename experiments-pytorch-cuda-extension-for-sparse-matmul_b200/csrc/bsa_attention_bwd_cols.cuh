@@ -151,13 +151,7 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
         }
         __syncwarp();
         if (lane == 0 && *(volatile int*)abort_flag) {
-            // Give copies that were issued a bounded chance to land before the CTA exits.
-            const unsigned long long tw = global_ns();
-            for (int s = 0; s < kBwdColRing; ++s)
-                while (!mbar_try_wait(&bars->y_full[g][s], 0) && !mbar_try_wait(&bars->y_full[g][s], 1) &&
-                       global_ns() - tw < kWaitLimitNs / 4) {}
-            while (!mbar_try_wait(&bars->x_full[g], 0) && !mbar_try_wait(&bars->x_full[g], 1) &&
-                   global_ns() - tw < kWaitLimitNs / 4) {}
+            let_copies_land();      // (issued by this warp; see the helper)
         }
         __syncwarp();
     } else if (role == 1) {

@@ -350,11 +350,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         __syncwarp();
         if (lane == 0 && *(volatile int*)&bars->abort_flag) {
-            // Give copies that were issued a bounded chance to land before the CTA exits.
-            const unsigned long long t0 = global_ns();
-            for (int s = 0; s < p.stages; ++s)
-                while (!mbar_try_wait(&bars->full[s], 0) && !mbar_try_wait(&bars->full[s], 1) &&
-                       global_ns() - t0 < kWaitLimitNs / 4) {}
+            let_copies_land();      // (issued by this warp; see the helper)
         }
         __syncwarp();
     } else if (warp < kFirstEpilogueWarp) {

@@ -67,6 +67,15 @@ __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int*
         }
     }
 }
+// After an abort a producer's copies may still be in flight, and they must not land in shared memory
+// that the SM has already handed to the next CTA.  An mbarrier cannot tell a stage that is being
+// filled from an idle one (one of its two parity tests passes at any time), so the producer waits a
+// fixed time that is long against a copy's latency (a few microseconds) before it leaves.
+constexpr unsigned long long kCopyDrainNs = 200000ull;      // 0.2 ms
+__device__ __forceinline__ void let_copies_land() {
+    const unsigned long long t0 = global_ns();
+    while (global_ns() - t0 < kCopyDrainNs) {}
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* abort_flag, uint32_t* status) {
     if (mbar_try_wait(bar, parity)) return true;
     return mbar_wait_slow(bar, parity, abort_flag, status);

@@ -158,6 +158,35 @@ def test_many_rows_per_pipeline_wrap_the_entry_rings(causal):
         assert torch.isfinite(a.float()).all(), name
 
 
+@pytest.mark.parametrize("block,dim,causal", [(64, 64, False), (64, 64, True), (64, 128, False), (32, 64, True)])
+def test_fused_step_with_hundreds_of_rows_per_pipeline(block, dim, causal):
+    """512 slices of seq 4096: every pipeline of the fused kernels walks more than a hundred block rows (columns)
+    and its rings wrap throughout.  Output and gradients must equal, bit for bit, those of 32-slice launches
+    (the size the oracle comparisons cover), launch after launch, and no bounded wait may run out."""
+    from sparse import SparseLayout, attention
+    from sparse.patterns import bigbird
+    seq, slices = 4096, 512
+    lay = SparseLayout(bigbird(seq // block, 1, 2, 3, 5000), block=block, device="cuda")
+    gen = torch.Generator(device="cuda").manual_seed(79)
+    q, k, v, do = (torch.randn(slices, seq, dim, device="cuda", generator=gen).half() for _ in range(4))
+
+    def step(lo, hi):
+        qg, kg, vg = (t[lo:hi].detach().clone().requires_grad_(True) for t in (q, k, v))
+        o = attention(qg, kg, vg, lay, dim ** -0.5, causal)
+        o.backward(do[lo:hi])
+        return o.detach(), qg.grad, kg.grad, vg.grad
+
+    sparse_kernel = importlib.import_module("sparse.kernel")
+    parts = [torch.cat(t) for t in zip(*(step(i, i + 32) for i in range(0, slices, 32)))]
+    sparse_kernel.sparse_ops.check_device_status(0)
+    for launch in range(4):
+        whole = step(0, slices)
+        sparse_kernel.sparse_ops.check_device_status(0)
+        for got, ref, name in zip(whole, parts, ("O", "dQ", "dK", "dV")):
+            assert torch.equal(got, ref), "launch %d: %s differs from the 32-slice launches" % (launch, name)
+        del whole
+
+
 def test_full_size_fused_step_properties_config5():
     """Benchmark configuration 5 at full size (512 slices, seq 8192, head dim 128, BigBird layout) through
     the fused forward and backward, checked by size-independent properties: (1) with V = 1 every output

@@ -193,6 +193,32 @@ def test_sdd_with_thousands_of_accumulations_per_cta(block, dim, seq, slices):
         del whole
 
 
+@pytest.mark.parametrize("mode,ta,tb", [("dsd", False, False), ("dsd", True, False), ("dds", False, False), ("dds", False, True)])
+@pytest.mark.parametrize("block,dim,seq,slices", [(64, 128, 4096, 512), (32, 64, 4096, 512)])
+def test_dsd_dds_with_hundreds_of_groups_per_cta(mode, ta, tb, block, dim, seq, slices):
+    """The dense-output modes over 512 batch entries (every CTA walks several hundred block rows or columns,
+    its stage and accumulator barriers wrap thousands of times): bit for bit the result of 32-slice launches,
+    launch after launch, and no bounded wait runs out."""
+    from sparse import SparseLayout
+    from sparse.kernel import sparse_ops
+    from sparse.patterns import bigbird
+    lay = SparseLayout(bigbird(seq // block, 1, 2, 3, 5000), block=block, device="cuda")
+    gen = torch.Generator(device="cuda").manual_seed(78)
+    sp = torch.randn(slices, lay.num_blocks, block, block, device="cuda", generator=gen).half()
+    dn = torch.randn(slices, dim, seq, device="cuda", generator=gen).half() if mode == "dds" else \
+        torch.randn(slices, seq, dim, device="cuda", generator=gen).half()
+    a, b = (sp, dn) if mode == "dsd" else (dn, sp)
+    rl, cl = lay.row_layout, lay.col_layout
+    parts = torch.cat([sparse_ops.sparse_matmul(a[i:i + 32], b[i:i + 32], mode, rl, cl, ta, tb, block)
+                       for i in range(0, slices, 32)])
+    sparse_ops.check_device_status(0)
+    for launch in range(4):
+        whole = sparse_ops.sparse_matmul(a, b, mode, rl, cl, ta, tb, block)
+        sparse_ops.check_device_status(0)
+        assert torch.equal(whole, parts), "launch %d differs from the 32-slice launches" % launch
+        del whole
+
+
 def test_autograd_matches_dense_autograd():
     """Gradients through sparse.matmul equal those of the dense masked computation."""
     from sparse import SparseLayout, matmul

@@ -187,6 +187,38 @@ def test_fused_step_with_hundreds_of_rows_per_pipeline(block, dim, causal):
         del whole
 
 
+@pytest.mark.parametrize("block,dim,dtype", [(64, 64, torch.bfloat16), (64, 128, torch.bfloat16), (32, 128, torch.float16), (16, 64, torch.float16)])
+def test_fused_step_long_launch_with_padding_mask(block, dim, dtype):
+    """256 slices of seq 2048 with a key-padding mask (the masked instances of the three fused kernels, and the
+    general backward at head dim 128): equal, bit for bit, to 32-slice launches; no bounded wait runs out."""
+    from sparse import SparseLayout, attention
+    from sparse.patterns import bigbird
+    seq, slices = 2048, 256
+    lay = SparseLayout(bigbird(seq // block, 1, 2, 3, 5000), block=block, device="cuda")
+    gen = torch.Generator(device="cuda").manual_seed(81)
+    q, k, v, do = (torch.randn(slices, seq, dim, device="cuda", generator=gen).to(dtype) for _ in range(4))
+    kpm = torch.zeros(slices, seq, dtype=torch.uint8, device="cuda")
+    kpm[:, seq - 100:] = 1
+    kpm[1::3, 500:530] = 1
+
+    def step(lo, hi):
+        qg, kg, vg = (t[lo:hi].detach().clone().requires_grad_(True) for t in (q, k, v))
+        o = attention(qg, kg, vg, lay, dim ** -0.5, False, kpm[lo:hi])
+        o.backward(do[lo:hi])
+        return o.detach(), qg.grad, kg.grad, vg.grad
+
+    sparse_kernel = importlib.import_module("sparse.kernel")
+    parts = [torch.cat(t) for t in zip(*(step(i, i + 32) for i in range(0, slices, 32)))]
+    sparse_kernel.sparse_ops.check_device_status(0)
+    for launch in range(3):
+        whole = step(0, slices)
+        sparse_kernel.sparse_ops.check_device_status(0)
+        for got, ref, name in zip(whole, parts, ("O", "dQ", "dK", "dV")):
+            assert torch.isfinite(got.float()).all(), name
+            assert torch.equal(got, ref), "launch %d: %s differs from the 32-slice launches" % (launch, name)
+        del whole
+
+
 def test_full_size_fused_step_properties_config5():
     """Benchmark configuration 5 at full size (512 slices, seq 8192, head dim 128, BigBird layout) through
     the fused forward and backward, checked by size-independent properties: (1) with V = 1 every output

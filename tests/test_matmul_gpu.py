@@ -219,6 +219,42 @@ def test_dsd_dds_with_hundreds_of_groups_per_cta(mode, ta, tb, block, dim, seq, 
         del whole
 
 
+@pytest.mark.parametrize("mode,ta,tb", [("sdd", False, True), ("dsd", False, False), ("dds", False, True)])
+@pytest.mark.parametrize("block,dim,seq,slices,dtype", [
+    (32, 128, 2048, 256, torch.float32),        # 3xTF32 through the block-32 engine (splitter warps in the pipeline)
+    (64, 64, 2048, 256, torch.float32),         # 3xTF32 through the block-64 engine
+    (128, 64, 4096, 256, torch.float16),        # blocks walked as 2 x 2 tiles
+    (16, 64, 1024, 512, torch.float16),         # block 16
+    (64, 64, 4096, 512, torch.bfloat16),
+])
+def test_long_launches_of_the_other_engines_and_types(mode, ta, tb, block, dim, seq, slices, dtype):
+    """Hundreds of work items per CTA for the instances the 16-bit block-32 / block-64 cases above do not reach:
+    the result of one launch over all slices must equal, bit for bit, 32-slice launches, and no bounded wait may
+    run out."""
+    from sparse import SparseLayout
+    from sparse.kernel import sparse_ops
+    from sparse.patterns import bigbird
+    lay = SparseLayout(bigbird(seq // block, 1, 2, 3, 5000), block=block, device="cuda")
+    gen = torch.Generator(device="cuda").manual_seed(80)
+    def rnd(*shape):
+        return torch.randn(*shape, device="cuda", generator=gen).to(dtype)
+    if mode == "sdd":
+        a, b = rnd(slices, seq, dim), rnd(slices, seq, dim)
+    elif mode == "dsd":
+        a, b = rnd(slices, lay.num_blocks, block, block), rnd(slices, seq, dim)
+    else:
+        a, b = rnd(slices, dim, seq), rnd(slices, lay.num_blocks, block, block)
+    rl, cl = lay.row_layout, lay.col_layout
+    parts = torch.cat([sparse_ops.sparse_matmul(a[i:i + 32], b[i:i + 32], mode, rl, cl, ta, tb, block)
+                       for i in range(0, slices, 32)])
+    sparse_ops.check_device_status(0)
+    for launch in range(3):
+        whole = sparse_ops.sparse_matmul(a, b, mode, rl, cl, ta, tb, block)
+        sparse_ops.check_device_status(0)
+        assert torch.equal(whole, parts), "launch %d differs from the 32-slice launches" % launch
+        del whole
+
+
 def test_autograd_matches_dense_autograd():
     """Gradients through sparse.matmul equal those of the dense masked computation."""
     from sparse import SparseLayout, matmul

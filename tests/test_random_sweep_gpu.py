@@ -131,3 +131,71 @@ def test_tensor_core_engines_against_cuda_core_engine(seed):
             seed, case, mode, ta, tb, block, rows, cols, inner, z, dtype)
         assert got["tcgen05"].shape == got["simt"].shape, what
         assert _rel(got["tcgen05"], got["simt"]) <= tol, (what, _rel(got["tcgen05"], got["simt"]))
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_one_launch_over_many_slices_equals_32_slice_launches(seed):
+    """Random layouts with 64 to 2048 batch entries, so that every CTA walks up to a few hundred work items and
+    its rings and barriers wrap throughout: one launch over all slices must equal 32-slice launches bit for bit
+    (matmul of every mode and transposition, and the fused forward + backward), twice in a row, and no kernel
+    may report a bounded wait that ran out."""
+    from sparse import SparseLayout, attention
+    from sparse.kernel import sparse_ops
+    rng = np.random.default_rng(7000 + seed)
+    gen = torch.Generator(device="cuda").manual_seed(300 + seed)
+    for case in range(24):
+        block = int(rng.choice([32, 64, 64, 128]))
+        rows = int(rng.integers(2, 25)) * (2 if block == 32 else 1)
+        if block == 128:
+            rows = min(rows, 8)
+        pattern = _random_pattern(rng, rows, rows, float(rng.choice([0.1, 0.3, 0.7])))
+        dim = int(rng.choice([64, 128]))
+        dtype = torch.float16 if rng.random() < 0.7 else torch.bfloat16
+        seq = rows * block
+        slices = int(rng.choice([256, 512, 1024, 2048]))
+        while slices * seq * dim > 3e8 or slices * int(pattern.sum()) * block * block > 8e8:
+            slices //= 2
+        slices = max(64, slices // 32 * 32)
+        lay = SparseLayout(torch.as_tensor(pattern), block=block, device="cuda")
+        rl, cl = lay.row_layout, lay.col_layout
+
+        def rnd(*shape):
+            return torch.randn(*shape, device="cuda", generator=gen).to(dtype)
+
+        kind = int(rng.integers(0, 4))
+        what = "seed %d case %d: kind %d block %d grid %d dim %d %s slices %d" % (seed, case, kind, block, rows, dim, dtype, slices)
+        if kind == 3:
+            causal = bool(rng.random() < 0.5)
+            q, k, v, do = (rnd(slices, seq, dim) for _ in range(4))
+
+            def step(lo, hi):
+                qg, kg, vg = (x[lo:hi].detach().clone().requires_grad_(True) for x in (q, k, v))
+                o = attention(qg, kg, vg, lay, dim ** -0.5, causal)
+                o.backward(do[lo:hi])
+                return o.detach(), qg.grad, kg.grad, vg.grad
+
+            parts = [torch.cat(x) for x in zip(*(step(i, i + 32) for i in range(0, slices, 32)))]
+            for _ in range(2):
+                whole = step(0, slices)
+                sparse_ops.check_device_status(0)
+                for a, b, name in zip(whole, parts, ("O", "dQ", "dK", "dV")):
+                    assert torch.equal(a, b), (what, name)
+        else:
+            mode = ("sdd", "dsd", "dds")[kind]
+            ta, tb = bool(rng.random() < 0.5), bool(rng.random() < 0.5)
+            if mode == "sdd":
+                a = rnd(slices, dim, seq) if ta else rnd(slices, seq, dim)
+                b = rnd(slices, seq, dim) if tb else rnd(slices, dim, seq)
+            elif mode == "dsd":
+                a, b = rnd(slices, lay.num_blocks, block, block), (rnd(slices, dim, seq) if tb else rnd(slices, seq, dim))
+            else:
+                a, b = (rnd(slices, seq, dim) if ta else rnd(slices, dim, seq)), rnd(slices, lay.num_blocks, block, block)
+
+            def run(lo, hi):
+                return sparse_ops.sparse_matmul(a[lo:hi], b[lo:hi], mode, rl, cl, ta, tb, block)
+
+            parts = torch.cat([run(i, i + 32) for i in range(0, slices, 32)])
+            for _ in range(2):
+                whole = run(0, slices)
+                sparse_ops.check_device_status(0)
+                assert torch.equal(whole, parts), what

@@ -336,9 +336,25 @@ def side_cfg5_strong(sparse_ops, dev, world, dist):
         t = sum(ev[i][j][0].elapsed_time(ev[i][j][1]) for i in range(steps)) / steps
         byts = {"softmax_fwd": 2 * sparse_bytes, "softmax_bwd": 3 * sparse_bytes}.get(name, sparse_bytes + 2 * dense_bytes)
         ops[name] = {"ms": round(t, 3), "hbm_frac": round(byts / (t * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)}
+    # the same step through the fused public op (head dim 128: single-group forward kernel, general backward kernels)
+    for _ in range(2):
+        fused_step(lay, q, k, v, do, scale)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0.record()
+    for i in range(steps):
+        fused_step(lay, q, k, v, do, scale)
+    e1.record()
+    torch.cuda.synchronize()
+    fms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(fms, op=dist.ReduceOp.MAX)
+    fms = float(fms[0])
     del q, k, v, do
     torch.cuda.empty_cache()
     return {"slices_total": total, "slices_per_gpu": z, "step_ms": round(ms, 3), "TFLOP/s": round(flops / (ms * 1e-3) / 1e12, 1),
+            "fused_step_ms": round(fms, 3), "fused_TFLOP/s": round(flops / (fms * 1e-3) / 1e12, 1),
             "scaling": "strong", "ops_rank0": ops}
 
 

@@ -136,7 +136,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         bool q_prefetched = false;                 // the current item's Q tile set was requested an item ago
         bool ok = true;
         Cursor cur;
-        cur.init(p);
+        cur.init(p, 0, true);
         BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
         while (ok && cur.valid()) {
             BlockDesc pre_next{0, 0};
@@ -186,7 +186,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 }
                 q_prefetched = false;
                 if (ok && !is_v && p.qbufs == 2 && cur.has_next() && cur.next_count() > 0) {
-                    ok = issue_q(q_no, cur.z1, cur.r1);        // q_no already counts this item
+                    ok = issue_q(q_no, cur.next_z(), cur.next_group());        // q_no already counts this item
                     q_prefetched = true;
                 }
             }
@@ -206,7 +206,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             bool ok = true;
             const uint32_t idesc_qk = p.idesc_qk;
             Cursor cur;
-            cur.init(p);
+            cur.init(p, 0, true);
             for (; ok && cur.valid(); cur.advance()) {
                 const int n = cur.count;
                 if (n == 0) continue;               // empty row: the softmax warps write zeros on their own
@@ -254,7 +254,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             bool ok = true;
             const uint32_t idesc_pv = p.idesc_pv;
             Cursor cur;
-            cur.init(p);
+            cur.init(p, 0, true);
             for (; ok && cur.valid(); cur.advance()) {
                 const int n = cur.count;
                 if (n == 0) continue;
@@ -300,7 +300,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         int s_no = 0, o_no = 0;                     // S tiles and non-empty items before the current item
         bool ok = true;
         Cursor cur;
-        cur.init(p);
+        cur.init(p, 0, true);
         BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
         while (ok && cur.valid()) {
             BlockDesc pre_next{0, 0};
@@ -697,7 +697,7 @@ attention_forward_pipes_kernel(const __grid_constant__ CUtensorMap map_q, const 
         int vq_col[3] = {0, 0, 0};                  // key blocks of tiles u - 3, u - 2, u - 1
         bool ok = true;
         Cursor cur;
-        cur.init_as(p, walker, walkers);
+        cur.init_as(p, walker, walkers, 0, true);
         BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
         auto load_v = [&](int t, int col, int z) -> bool {
             const int st = t & 1;

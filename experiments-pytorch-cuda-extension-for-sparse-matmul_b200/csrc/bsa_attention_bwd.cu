@@ -217,7 +217,7 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
         int y_no = 0, x_no = 0;
         bool ok = true;
         Cursor cur;
-        cur.init(p);
+        cur.init(p, 0, true);
         BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
         while (ok && cur.valid()) {
             BlockDesc pre_next{0, 0};
@@ -274,7 +274,7 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
         int s_no = 0, x_no = 0;
         bool ok = true;
         Cursor cur;
-        cur.init(p);
+        cur.init(p, 0, true);
         for (; ok && cur.valid(); cur.advance()) {
             const int n = cur.count;
             if (n == 0) continue;
@@ -326,7 +326,7 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
             int s_no = 0, o_no = 0;
             bool ok = true;
             Cursor cur;
-            cur.init(p);
+            cur.init(p, 0, true);
             for (; ok && cur.valid(); cur.advance()) {
                 const int n = cur.count;
                 if (n == 0) continue;
@@ -381,7 +381,7 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x1, const __gr
         int s_no = 0, o_no = 0;
         bool ok = true;
         Cursor cur;
-        cur.init(p);
+        cur.init(p, 0, true);
         BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
         while (ok && cur.valid()) {
             BlockDesc pre_next{0, 0};

@@ -94,7 +94,7 @@ attention_backward_cols_pipes_kernel(const __grid_constant__ CUtensorMap map_k, 
         int t0 = 0, i_no = 0;                       // blocks and non-empty columns before the current column
         bool ok = true;
         Cursor cur;
-        cur.init_as(p, walker, walkers);
+        cur.init_as(p, walker, walkers, 0, true);
         BlockDesc pre = cur.valid() ? load_first_chunk(p.blocks, cur.first, cur.count, lane) : BlockDesc{0, 0};
         while (ok && cur.valid()) {
             BlockDesc pre_next{0, 0};

@@ -273,64 +273,86 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 // entry): an integer division by a run-time value costs a lone thread hundreds of cycles.
 struct Cursor {
     int item, stride, items, chunks, per_z, stride_z, stride_rem;
+    int groups, zstep, rot;             // groups per batch entry; stride_z mod groups; 1: rotate the groups (below)
     int table_shift;                    // group g reads table[g >> table_shift] (1: two virtual groups per real one)
     const int32_t* table;
     int item_no;                        // how many items this CTA has finished
     int z, g, chunk, first, count;      // current item: batch entry, group, slice, block range
-    int z1, r1, a1, b1;                 // next item: batch entry, index inside it, table[g], table[g + 1]
-    int z2, r2, a2, b2;                 // the item after that
+    int z1, r1, m1, a1, b1;             // next item: batch entry, index inside it, z mod groups, table[g], table[g + 1]
+    int z2, r2, m2, a2, b2;             // the item after that
 
-    __device__ __forceinline__ void load_words(bool in_range, int rem, int& a, int& b) const {
+    // Group of position `rem` of batch entry z (zm = z mod groups if the walk is rotated, else 0).  Rotated, batch
+    // entry z starts its groups at group z mod groups instead of group 0: layouts keep their long groups at fixed
+    // places (the global rows and columns of a BigBird or local + global layout), and with every batch entry
+    // starting at group 0 those land on the few walkers whose number is congruent to their position modulo
+    // gcd(groups, walkers) -- 74 of 592 pipelines of the fused forward took all 128-block rows of benchmark
+    // configuration 5 (2.2 times the mean load); rotated they spread over all walkers (1.03).  The fused kernels
+    // rotate; the matmul engines do not (their dsd by rows ran 11 % slower rotated on that configuration).
+    __device__ __forceinline__ int group_of(int rem, int zm, int& lin) const {
+        lin = chunks == 1 ? rem : rem / chunks;
+        int gg = lin + zm;
+        if (gg >= groups) gg -= groups;
+        return gg;
+    }
+    __device__ __forceinline__ void load_words(bool in_range, int rem, int zm, int& a, int& b) const {
         a = 0; b = 0;
         if (in_range) {
-            const int gg = (chunks == 1 ? rem : rem / chunks) >> table_shift;
+            int lin;
+            const int gg = group_of(rem, zm, lin) >> table_shift;
             a = table[gg]; b = table[gg + 1];
         }
     }
-    __device__ __forceinline__ void step_pos(int& zz, int& rem) const {
+    __device__ __forceinline__ void step_pos(int& zz, int& rem, int& zm) const {
         zz += stride_z;
+        zm += zstep;
         rem += stride_rem;
-        if (rem >= per_z) { rem -= per_z; ++zz; }
+        if (rem >= per_z) { rem -= per_z; ++zz; zm += rot; }
+        if (zm >= groups) zm -= groups;             // zm < groups + zstep + 1 <= 2 * groups before this
     }
-    __device__ __forceinline__ void set_current(int zz, int rem, int a, int b) {
+    __device__ __forceinline__ void set_current(int zz, int rem, int zm, int a, int b) {
+        int lin;
         z = zz;
-        g = chunks == 1 ? rem : rem / chunks;
-        chunk = rem - g * chunks;
+        g = group_of(rem, zm, lin);
+        chunk = rem - lin * chunks;
         first = a;
         count = b - a;
     }
     // The walker is number `first_item` of `walkers` (the CTA and the grid, or a pipeline of a CTA and the
     // number of pipelines in the grid); p.stride_z / p.stride_rem are `walkers` split by the items per batch entry.
     template <class Params>
-    __device__ __forceinline__ void init(const Params& p, int shift = 0) { init_as(p, (int)blockIdx.x, (int)gridDim.x, shift); }
+    __device__ __forceinline__ void init(const Params& p, int shift = 0, bool rotate = false) { init_as(p, (int)blockIdx.x, (int)gridDim.x, shift, rotate); }
     template <class Params>
-    __device__ __forceinline__ void init_as(const Params& p, int first_item, int walkers, int shift = 0) {
+    __device__ __forceinline__ void init_as(const Params& p, int first_item, int walkers, int shift = 0, bool rotate = false) {
         table_shift = shift;
+        rot = rotate ? 1 : 0;
         item = first_item; stride = walkers; items = p.items;
         chunks = p.chunks; per_z = p.groups * p.chunks; table = p.table;
         stride_z = p.stride_z; stride_rem = p.stride_rem;
+        groups = p.groups; zstep = rotate ? p.stride_z % p.groups : 0;      // (two divisions per walker and launch)
         item_no = 0;
         z = g = chunk = first = count = 0;
-        int z0 = item / per_z, r0 = item - z0 * per_z, a0, b0;
-        load_words(item < items, r0, a0, b0);
-        z1 = z0; r1 = r0; step_pos(z1, r1);
-        load_words(item + stride < items, r1, a1, b1);
-        z2 = z1; r2 = r1; step_pos(z2, r2);
-        load_words(item + 2 * stride < items, r2, a2, b2);
-        if (item < items) set_current(z0, r0, a0, b0);
+        int z0 = item / per_z, r0 = item - z0 * per_z, m0 = rotate ? z0 % groups : 0, a0, b0;
+        load_words(item < items, r0, m0, a0, b0);
+        z1 = z0; r1 = r0; m1 = m0; step_pos(z1, r1, m1);
+        load_words(item + stride < items, r1, m1, a1, b1);
+        z2 = z1; r2 = r1; m2 = m1; step_pos(z2, r2, m2);
+        load_words(item + 2 * stride < items, r2, m2, a2, b2);
+        if (item < items) set_current(z0, r0, m0, a0, b0);
     }
     __device__ __forceinline__ bool valid() const { return item < items; }
     __device__ __forceinline__ bool has_next() const { return item + stride < items; }
     __device__ __forceinline__ int next_first() const { return a1; }
     __device__ __forceinline__ int next_count() const { return b1 - a1; }
+    __device__ __forceinline__ int next_z() const { return z1; }
+    __device__ __forceinline__ int next_group() const { int lin; return group_of(r1, m1, lin); }
     __device__ __forceinline__ void advance() {
         item += stride;
         ++item_no;
-        const int zc = z1, rc = r1, ac = a1, bc = b1;
-        z1 = z2; r1 = r2; a1 = a2; b1 = b2;
-        step_pos(z2, r2);
-        load_words(item + 2 * stride < items, r2, a2, b2);
-        if (item < items) set_current(zc, rc, ac, bc);
+        const int zc = z1, rc = r1, mc = m1, ac = a1, bc = b1;
+        z1 = z2; r1 = r2; m1 = m2; a1 = a2; b1 = b2;
+        step_pos(z2, r2, m2);
+        load_words(item + 2 * stride < items, r2, m2, a2, b2);
+        if (item < items) set_current(zc, rc, mc, ac, bc);
     }
 };
 

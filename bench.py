@@ -395,6 +395,13 @@ def run_ours(args):
         raise SystemExit("bench.py: --gpus %d needs torchrun with %d ranks (WORLD_SIZE=%d)" % (args.gpus, args.gpus, world))
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    # host side of the end-to-end step: this rank's threads and pinned buffers on the GPU's own NUMA node
+    from sparse.distributed import bind_host_to_device
+    props = torch.cuda.get_device_properties(local_rank)
+    numa_node = bind_host_to_device(getattr(props, "pci_domain_id", 0), getattr(props, "pci_bus_id", -1),
+                                    getattr(props, "pci_device_id", 0)) if hasattr(props, "pci_bus_id") else None
+    print("bench.py: rank %d, GPU %d at PCI %04x:%02x, host NUMA node %s" % (
+        rank, local_rank, getattr(props, "pci_domain_id", 0), getattr(props, "pci_bus_id", 0), numa_node), file=sys.stderr)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     w = WORKLOAD
@@ -650,6 +657,7 @@ def run_ours(args):
             "e2e": {"value": round(e2e_value, 3), "unit": "TFLOP/s", "steps": e2e_steps,
                     "ms_per_step": round(e2e_ms / e2e_steps, 4), "copy_floor_ms": round(copy_floor_ms / e2e_steps, 4),
                     "api": "sparse.attention (fused forward and backward), one pinned buffer per direction",
+                    "host_numa_node_rank0": numa_node,
                     "h2d_bytes_per_step": 4 * dense_bytes, "d2h_bytes_per_step": 4 * dense_bytes},
             "gpu_launches": len(OPS) * args.steps * args.repeats,
             "clocks": clocks, "verify": check, "ops": ops_report, "fused_forward": fused_report,

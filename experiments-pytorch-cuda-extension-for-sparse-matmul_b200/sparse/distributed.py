@@ -7,7 +7,8 @@ of the flattened batch*head axis and no collective is needed on the data path.
 ``torch.distributed`` is used only to gather per-slice checksums for
 verification and to combine timings.
 """
-from typing import List, Tuple
+import os
+from typing import List, Optional, Tuple
 
 import torch
 
@@ -42,3 +43,38 @@ def gather_slices(local: torch.Tensor, total: int) -> torch.Tensor:
     parts: List[torch.Tensor] = [torch.empty_like(padded) for _ in range(world)]
     dist.all_gather(parts, padded)
     return torch.cat([parts[r][: e - b] for r, (b, e) in enumerate(sizes)], dim=0)
+
+
+def parse_cpu_list(text: str) -> List[int]:
+    """CPUs of a sysfs list such as ``0-27,56-83``."""
+    cpus: List[int] = []
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus.extend(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+def bind_host_to_device(pci_domain: int, pci_bus: int, pci_device: int, sysfs: str = "/sys") -> Optional[int]:
+    """Pins the calling process to the CPUs of the NUMA node the GPU at this PCI address hangs off, so that the
+    pinned host buffers it allocates afterwards (first touch) and the threads that fill them are local to the
+    GPU's PCIe root.  One process per GPU on a two-socket host otherwise puts every rank's staging memory on
+    the socket the launcher happened to start on, and all ranks' copies share that socket's memory and the
+    link between the sockets.  Returns the node, or None when the host gives no locality (single node,
+    ``numa_node`` = -1, no sysfs, or the node's CPUs are outside this process's allowed set); never raises."""
+    try:
+        address = "%04x:%02x:%02x.0" % (pci_domain, pci_bus, pci_device)
+        with open(os.path.join(sysfs, "bus", "pci", "devices", address, "numa_node")) as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open(os.path.join(sysfs, "devices", "system", "node", "node%d" % node, "cpulist")) as f:
+            cpus = set(parse_cpu_list(f.read()))
+        allowed = cpus & set(os.sched_getaffinity(0))
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return node
+    except (OSError, ValueError, AttributeError):
+        return None

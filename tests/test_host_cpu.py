@@ -285,3 +285,29 @@ def test_debug_checks_flag_is_off_by_default_and_check_passes_cpu_tensors_throug
         assert kernel.check(t) is t and kernel.check(None) is None
     finally:
         kernel.debug_checks = old
+
+
+def test_bind_host_to_device_reads_the_numa_node_of_the_pci_address(tmp_path, monkeypatch):
+    """The host-side binding of a rank to its GPU's NUMA node, against a fake sysfs tree: the node comes from
+    <sysfs>/bus/pci/devices/<address>/numa_node, its CPUs from <sysfs>/devices/system/node/node<N>/cpulist, and
+    only CPUs this process may use are kept.  No locality (node -1, missing files, no usable CPU) binds nothing."""
+    import importlib
+    distributed = importlib.import_module("sparse.distributed")
+    assert distributed.parse_cpu_list("0-3,8,10-11\n") == [0, 1, 2, 3, 8, 10, 11]
+    allowed = sorted(os.sched_getaffinity(0))
+    dev = tmp_path / "bus" / "pci" / "devices" / "0000:1b:00.0"
+    dev.mkdir(parents=True)
+    node = tmp_path / "devices" / "system" / "node" / "node1"
+    node.mkdir(parents=True)
+    (dev / "numa_node").write_text("1\n")
+    (node / "cpulist").write_text("%d,100000-100003\n" % allowed[0])
+    bound = {}
+    monkeypatch.setattr(os, "sched_setaffinity", lambda pid, cpus: bound.update(pid=pid, cpus=set(cpus)))
+    assert distributed.bind_host_to_device(0, 0x1b, 0, sysfs=str(tmp_path)) == 1
+    assert bound == {"pid": 0, "cpus": {allowed[0]}}
+    bound.clear()
+    (node / "cpulist").write_text("100000-100003\n")                 # none of the node's CPUs is usable here
+    assert distributed.bind_host_to_device(0, 0x1b, 0, sysfs=str(tmp_path)) is None and not bound
+    (dev / "numa_node").write_text("-1\n")                           # the platform reports no locality
+    assert distributed.bind_host_to_device(0, 0x1b, 0, sysfs=str(tmp_path)) is None and not bound
+    assert distributed.bind_host_to_device(0, 0x2c, 0, sysfs=str(tmp_path)) is None and not bound   # unknown device

@@ -169,7 +169,7 @@ def run_reference(args):
                              "note": "one host at every N: the ratio to the N-GPU arm is not a scaling curve"},
             "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # --------------------------------------------------------------------------- our arm
@@ -672,7 +672,7 @@ def run_ours(args):
                                     "sample": "%d of %d (batch*head) slices, masked dense torch fp32 fwd+bwd (a dense port: it "
                                               "executes %.1fx the nonzero-block FLOP it is credited with), %.1f s"
                                               % (cpu_heads, z, cpu_dense / cpu_flops, cpu_dt)}
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -680,7 +680,23 @@ def run_ours(args):
         raise SystemExit("bench.py: verification against the CPU oracle failed: %r" % (check,))
 
 
+_RESULT_FD = None
+
+
+def emit(line):
+    """The one JSON line of the run, on the stdout this process was started with."""
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def main():
+    # stdout carries the JSON line and nothing else: whatever libraries print there while the run lasts (NCCL's
+    # version banner at the first collective) goes to stderr instead
+    global _RESULT_FD
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
@@ -693,6 +709,9 @@ def main():
                     help="(batch*head) slices per GPU; default is the workload's 64. A smaller value is a reduced "
                          "case for profiler captures, not a benchmark result")
     args = ap.parse_args()
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -618,8 +618,6 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         // the staging tiles must have been read before the CTA gives its shared memory back
         if (is_sdd && elect_one()) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-        if (lane == 0 && quad == 0 && group == 0) {
-        }
     }
 
     // ---------------------------------------------------------------- teardown
